@@ -1,0 +1,190 @@
+"""Node fusion.
+
+Patterns (the reference names them but never matches, because its graphs have no edges:
+crates/ronn-graph/src/passes/fusion.rs:15-83; fusion table in
+crates/ronn-providers/src/compiler.rs:267-314):
+
+* Conv -> BatchNormalization            => Conv with folded weights
+      W' = W * gamma / sqrt(var + eps),  b' = (b - mean) * gamma / sqrt(var + eps) + beta
+* Conv [-> Add(residual)] -> Relu       => com.ronn::FusedConv(activation, optional 4th input)
+* MatMul -> Add(constant bias)          => com.ronn::FusedGemm
+* Gemm / FusedGemm -> Relu | Gelu       => FusedGemm(activation)
+* FusedGemm -> Add(residual)            => FusedGemm with 4th input
+* Add -> LayerNormalization             => com.ronn::SkipLayerNorm (when the sum is used only by the norm
+                                           and, at most, one more residual consumer)
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ir import GraphNode, ModelGraph
+from .base import OptimizationPass, PassStats
+
+RONN = "com.ronn"
+
+
+class NodeFusionPass(OptimizationPass):
+    name = "NodeFusion"
+
+    def run(self, graph: ModelGraph) -> PassStats:
+        stats = PassStats()
+        progress = True
+        while progress:
+            progress = False
+            for fn in (self._fold_bn, self._conv_act, self._matmul_bias, self._gemm_act, self._gemm_residual):
+                n = fn(graph)
+                if n:
+                    stats.nodes_fused += n
+                    progress = True
+        return stats
+
+    # -------------------------------------------------------------- helpers
+    @staticmethod
+    def _single_consumer(graph, cons, name):
+        if name in set(graph.output_names()):
+            return None
+        c = cons.get(name, [])
+        return c[0] if len(c) == 1 else None
+
+    # -------------------------------------------------------------- Conv + BN
+    def _fold_bn(self, graph: ModelGraph) -> int:
+        cons = graph.consumers()
+        for conv in graph.nodes:
+            if conv.op_type not in ("Conv", "FusedConv") or conv.attr("activation") or len(conv.inputs) > 3:
+                continue
+            bn = self._single_consumer(graph, cons, conv.outputs[0])
+            if bn is None or bn.op_type != "BatchNormalization" or bn.inputs[0] != conv.outputs[0]:
+                continue
+            names = [conv.inputs[1]] + bn.inputs[1:5] + ([conv.inputs[2]] if len(conv.inputs) > 2 and conv.inputs[2] else [])
+            if any(n not in graph.initializers for n in names):
+                continue
+            if len(cons.get(conv.inputs[1], [])) != 1:
+                continue                # shared weights: folding would change the other user
+            w = graph.initializers[conv.inputs[1]]
+            gamma, beta, mean, var = (graph.initializers[n].float() for n in bn.inputs[1:5])
+            eps = float(bn.attr("epsilon", 1e-5))
+            scale = gamma * torch.rsqrt(var + eps)
+            b = graph.initializers[conv.inputs[2]].float() if len(conv.inputs) > 2 and conv.inputs[2] else torch.zeros_like(mean)
+            w2 = (w.float() * scale.reshape([-1] + [1] * (w.dim() - 1))).to(w.dtype)
+            b2 = ((b - mean) * scale + beta).to(w.dtype)
+            wn, bn_name = graph.fresh_name(conv.inputs[1] + "_bnfold"), graph.fresh_name(conv.outputs[0] + "_bias")
+            graph.initializers[wn] = w2
+            graph.initializers[bn_name] = b2
+            conv.inputs = [conv.inputs[0], wn, bn_name]
+            conv.outputs = [bn.outputs[0]]
+            graph.remove_nodes([bn.id])
+            return 1
+        return 0
+
+    # -------------------------------------------------------------- Conv (+Add) + Relu
+    def _conv_act(self, graph: ModelGraph) -> int:
+        cons = graph.consumers()
+        prod = graph.producers()
+        for conv in graph.nodes:
+            if conv.op_type not in ("Conv", "FusedConv") or conv.attr("activation"):
+                continue
+            nxt = self._single_consumer(graph, cons, conv.outputs[0])
+            if nxt is None:
+                continue
+            if nxt.op_type == "Relu":
+                self._to_fused_conv(conv)
+                conv.attributes["activation"] = "Relu"
+                conv.outputs = [nxt.outputs[0]]
+                graph.remove_nodes([nxt.id])
+                return 1
+            if nxt.op_type == "Add" and len(conv.inputs) <= 3 and len(nxt.inputs) == 2:
+                other = nxt.inputs[1] if nxt.inputs[0] == conv.outputs[0] else nxt.inputs[0]
+                if other == conv.outputs[0] or other in graph.initializers:
+                    continue
+                # the residual must already exist when the conv runs
+                p = prod.get(other)
+                order = {n.id: k for k, n in enumerate(graph.nodes)}
+                if p is not None and order[p.id] > order[conv.id]:
+                    continue
+                self._to_fused_conv(conv)
+                ins = list(conv.inputs)
+                while len(ins) < 3:
+                    ins.append("")
+                if not ins[2]:
+                    zb = graph.fresh_name(conv.outputs[0] + "_zero_bias")
+                    w = graph.initializers.get(ins[1])
+                    if w is None:
+                        continue
+                    graph.initializers[zb] = torch.zeros(w.shape[0], dtype=w.dtype)
+                    ins[2] = zb
+                conv.inputs = ins + [other]
+                conv.outputs = [nxt.outputs[0]]
+                graph.remove_nodes([nxt.id])
+                return 1
+        return 0
+
+    @staticmethod
+    def _to_fused_conv(conv: GraphNode):
+        if conv.op_type == "Conv":
+            conv.op_type = "FusedConv"
+            conv.domain = RONN
+
+    # -------------------------------------------------------------- MatMul + Add(bias)
+    def _matmul_bias(self, graph: ModelGraph) -> int:
+        cons = graph.consumers()
+        for mm in graph.nodes:
+            if mm.op_type != "MatMul" or mm.inputs[1] not in graph.initializers:
+                continue
+            if graph.initializers[mm.inputs[1]].dim() != 2:
+                continue
+            add = self._single_consumer(graph, cons, mm.outputs[0])
+            if add is None or add.op_type != "Add":
+                continue
+            other = add.inputs[1] if add.inputs[0] == mm.outputs[0] else add.inputs[0]
+            bias = graph.initializers.get(other)
+            n = graph.initializers[mm.inputs[1]].shape[1]
+            if bias is None or bias.dim() != 1 or bias.shape[0] != n:
+                continue
+            mm.op_type, mm.domain = "FusedGemm", RONN
+            mm.inputs = [mm.inputs[0], mm.inputs[1], other]
+            mm.outputs = [add.outputs[0]]
+            graph.remove_nodes([add.id])
+            return 1
+        return 0
+
+    def _gemm_act(self, graph: ModelGraph) -> int:
+        cons = graph.consumers()
+        for g in graph.nodes:
+            if g.op_type not in ("Gemm", "FusedGemm") or g.attr("activation") or len(g.inputs) > 3:
+                continue
+            if g.op_type == "Gemm" and (int(g.attr("transA", 0)) or float(g.attr("alpha", 1.0)) != 1.0
+                                        or float(g.attr("beta", 1.0)) != 1.0):
+                continue
+            act = self._single_consumer(graph, cons, g.outputs[0])
+            if act is None or act.op_type not in ("Relu", "Gelu"):
+                continue
+            if act.op_type == "Gelu" and act.attr("approximate", "tanh") != "tanh":
+                continue
+            g.op_type, g.domain = "FusedGemm", RONN
+            g.attributes = {"transB": int(g.attr("transB", 0)), "activation": act.op_type}
+            g.outputs = [act.outputs[0]]
+            graph.remove_nodes([act.id])
+            return 1
+        return 0
+
+    def _gemm_residual(self, graph: ModelGraph) -> int:
+        cons = graph.consumers()
+        prod = graph.producers()
+        order = {n.id: k for k, n in enumerate(graph.nodes)}
+        for g in graph.nodes:
+            if g.op_type != "FusedGemm" or len(g.inputs) != 3 or not g.inputs[2]:
+                continue
+            add = self._single_consumer(graph, cons, g.outputs[0])
+            if add is None or add.op_type != "Add" or len(add.inputs) != 2:
+                continue
+            other = add.inputs[1] if add.inputs[0] == g.outputs[0] else add.inputs[0]
+            if other == g.outputs[0] or other in graph.initializers:
+                continue
+            p = prod.get(other)
+            if p is not None and order[p.id] > order[g.id]:
+                continue
+            g.inputs = g.inputs + [other]
+            g.outputs = [add.outputs[0]]
+            graph.remove_nodes([add.id])
+            return 1
+        return 0

@@ -1,0 +1,116 @@
+"""CPU execution provider (crates/ronn-providers/src/cpu/provider.rs:25-375,
+crates/ronn-providers/src/cpu/kernels.rs:20-478).
+
+Nodes resolve to the operator registry on CPU tensors; small fp32 GEMMs tagged by the CPU
+optimisation pass run on the native AVX2/AVX-512 kernel, which is where the batch-1 MLP
+spends its time once per-node dispatch is a table lookup.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict
+
+import torch
+
+from .. import _native
+from ..api.errors import ProviderError
+from ..core.types import (DataType, MemoryType, PerformanceProfile, ProviderCapability, ProviderConfig, ProviderType,
+                          ResourceRequirements)
+from ..graph.ir import ModelGraph
+from ..onnx.registry import default_registry
+from .allocator import PooledMemoryAllocator
+from .base import CompiledKernel, ExecutionProvider, build_kernel
+
+
+def detect_simd_features():
+    lvl = _native.host().ronn_cpu_simd_level()
+    feats = []
+    if lvl >= 1:
+        feats += ["avx2", "fma"]
+    if lvl >= 2:
+        feats += ["avx512f"]
+    return feats
+
+
+def _simd_gemm(inputs, attrs, ctx):
+    x, w = inputs[0], inputs[1]
+    bias = inputs[2] if len(inputs) > 2 else None
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or x.device.type != "cpu":
+        return default_registry().get("FusedGemm").fn(inputs, attrs, ctx)
+    M, K = x.shape
+    N = w.shape[1]
+    out = torch.empty((M, N), dtype=torch.float32)
+    act = 1 if attrs.get("activation", "") == "Relu" else 0
+    _native.host().ronn_cpu_gemm_f32(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                     out.data_ptr(), M, N, K, act)
+    return [out]
+
+
+class CpuExecutionProvider(ExecutionProvider):
+    provider_id = ProviderType.CPU
+    name = "CpuExecutionProvider"
+
+    def __init__(self, thread_count: int = None, enable_simd: bool = True, numa_node: int = -1,
+                 enable_fusion: bool = True, pool_name: str = "ronn-cpu"):
+        cores = os.cpu_count() or 1
+        self.thread_count = thread_count if thread_count else max(cores - 1, 1)
+        if self.thread_count < 0:
+            raise ProviderError("thread_count must be positive")
+        self.enable_simd = enable_simd
+        self.enable_fusion = enable_fusion
+        self.numa_node = numa_node
+        self.pool_name = pool_name
+        self.simd_features = detect_simd_features() if enable_simd else []
+        self.allocator = PooledMemoryAllocator()
+        self._shutdown = False
+
+    def get_capability(self) -> ProviderCapability:
+        return ProviderCapability(
+            supported_ops=set(default_registry().supported_ops()) - {"BitLinear"},
+            data_types=[DataType.F32, DataType.F16, DataType.BF16, DataType.F64, DataType.I8, DataType.I32,
+                        DataType.I64, DataType.U8, DataType.BOOL],
+            memory_types=[MemoryType.SYSTEM],
+            performance_profile=PerformanceProfile.CPU,
+            resource_requirements=ResourceRequirements(cpu_features=list(self.simd_features)),
+            features={"simd": list(self.simd_features), "threads": self.thread_count, "numa_node": self.numa_node})
+
+    def configure(self, config: ProviderConfig) -> None:
+        if config.thread_count is not None:
+            if config.thread_count <= 0:
+                raise ProviderError("thread_count must be positive")
+            self.thread_count = config.thread_count
+        opts = config.custom_options
+        if "numa_node" in opts:
+            try:
+                self.numa_node = int(opts["numa_node"])
+            except ValueError:
+                raise ProviderError(f"invalid numa_node '{opts['numa_node']}'") from None
+        if "enable_simd" in opts:
+            self.enable_simd = opts["enable_simd"].lower() in ("1", "true", "yes")
+            self.simd_features = detect_simd_features() if self.enable_simd else []
+        if "enable_fusion" in opts:
+            self.enable_fusion = opts["enable_fusion"].lower() in ("1", "true", "yes")
+
+    def compile_graph(self, graph: ModelGraph, profiler=None) -> CompiledKernel:
+        reg = default_registry()
+        dev = torch.device("cpu")
+
+        def resolve(node, g):
+            if node.attr("cpu_kernel") == "simd_gemm" and self.enable_simd:
+                return _simd_gemm
+            return reg.get(node.op_type).fn
+
+        def place(name, t, users):
+            return t if t.device.type == "cpu" else t.cpu()
+
+        return build_kernel(graph, dev, resolve, place, self, profiler)
+
+    def get_allocator(self):
+        return self.allocator
+
+    def shutdown(self) -> None:
+        self._shutdown = True
+
+
+def create_cpu_provider(**kw) -> CpuExecutionProvider:
+    return CpuExecutionProvider(**kw)
