@@ -89,7 +89,7 @@ def host():
         _sig(lib, "ronn_sched_schedule", I32, [V])
         _sig(lib, "ronn_sched_plan_size", I32, [V])
         _sig(lib, "ronn_sched_plan_tokens", I32, [V])
-        _sig(lib, "ronn_sched_fill", I32, [V, V, V, V, V, V, V, V, V, I32])
+        _sig(lib, "ronn_sched_fill", I32, [V, V, V, V, V, V, V, V, V, V, I32])
         _sig(lib, "ronn_sched_commit", I32, [V, V, I32, V])
         _sig(lib, "ronn_sched_abort_step", None, [V])
         for name in ("state", "num_tokens", "prompt_len", "preemptions"):

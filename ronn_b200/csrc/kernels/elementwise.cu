@@ -1,0 +1,378 @@
+// Memory-bound kernels: LayerNorm / RMSNorm (optionally fused with a residual add), row softmax,
+// activations, binary elementwise, embedding gather (+ position add), row argmax, casts.
+//
+// Numeric definitions follow the reference: LayerNorm over the last axis with population variance
+// (crates/ronn-core/src/tensor.rs:566-611), max-shifted softmax (crates/ronn-core/src/ops/reduction.rs:432-450),
+// tanh-form GELU and x*sigmoid(1.702x) "fast GELU" (crates/ronn-core/src/ops/arithmetic.rs:281-296,
+// crates/ronn-providers/src/gpu/cuda_kernels.rs:537-562), embedding = gather on axis 0
+// (crates/ronn-onnx/src/ops/tensor_ops.rs:463-489), argmax (crates/ronn-core/src/ops/reduction.rs:282-304).
+// All kernels move 16 bytes per thread per access and keep a row in registers between passes.
+#include "common.cuh"
+
+namespace ronn {
+
+constexpr int NORM_MAX_CHUNKS = 4;     // a thread keeps up to 4 x 8 values of its row
+
+// y = norm(x [+ res]) * gamma [+ beta];  if sum_out != null the pre-norm sum (x + res) is also written.
+// RMS = true: y = v * rsqrt(mean(v^2) + eps) * gamma.
+template <class T, bool RMS>
+__global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
+                            const T* __restrict__ beta, T* __restrict__ y, T* __restrict__ sum_out, int H,
+                            long ld_x, long ld_res, long ld_y, float eps) {
+  __shared__ float scratch[32];
+  const long row = blockIdx.x;
+  const T* xr = x + row * ld_x;
+  const T* rr = res ? res + row * ld_res : nullptr;
+  const int nchunk = H >> 3;
+  float v[NORM_MAX_CHUNKS][8];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+      unpack8<T>(*reinterpret_cast<const Vec8*>(xr + ch * 8), v[c]);
+      if (rr) {
+        float r[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(rr + ch * 8), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += r[i];
+      }
+      if (sum_out) *reinterpret_cast<Vec8*>(sum_out + row * ld_y + ch * 8) = pack8<T>(v[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += RMS ? v[c][i] * v[c][i] : v[c][i];
+    }
+  }
+  float mean = 0.f, inv;
+  if (RMS) {
+    const float ms = block_sum(s, scratch) / float(H);
+    inv = rsqrtf(ms + eps);
+  } else {
+    mean = block_sum(s, scratch) / float(H);
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[c][i] - mean;
+          q += d * d;
+        }
+      }
+    }
+    const float var = block_sum(q, scratch) / float(H);
+    inv = rsqrtf(var + eps);
+  }
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+      float g[8], b[8], o[8];
+      if (gamma) unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + ch * 8), g);
+      if (beta) unpack8<T>(*reinterpret_cast<const Vec8*>(beta + ch * 8), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = (v[c][i] - mean) * inv;
+        if (gamma) t *= g[i];
+        if (beta) t += b[i];
+        o[i] = t;
+      }
+      *reinterpret_cast<Vec8*>(y + row * ld_y + ch * 8) = pack8<T>(o);
+    }
+  }
+}
+
+// Row softmax over the last dimension of [rows, cols]; any cols (scalar accesses when cols % 8 != 0).
+template <class T>
+__global__ void softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int cols) {
+  __shared__ float scratch[32];
+  const T* xr = x + long(blockIdx.x) * cols;
+  T* yr = y + long(blockIdx.x) * cols;
+  float m = -INFINITY;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) m = fmaxf(m, Cvt<T>::to_f(xr[i]));
+  m = block_max(m, scratch);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) s += __expf(Cvt<T>::to_f(xr[i]) - m);
+  s = block_sum(s, scratch);
+  const float inv = 1.f / s;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) yr[i] = Cvt<T>::from_f(__expf(Cvt<T>::to_f(xr[i]) - m) * inv);
+}
+
+// op: 0 relu, 1 gelu(tanh), 2 fast gelu, 3 sigmoid, 4 silu, 5 tanh
+__device__ __forceinline__ float act_apply(float x, int op) {
+  switch (op) {
+    case 0: return fmaxf(x, 0.f);
+    case 1: return gelu_tanh_f(x);
+    case 2: return x / (1.f + __expf(-1.702f * x));
+    case 3: return 1.f / (1.f + __expf(-x));
+    case 4: return x / (1.f + __expf(-x));
+    default: {
+      const float e = __expf(2.f * x);
+      return 1.f - 2.f / (e + 1.f);
+    }
+  }
+}
+
+template <class T>
+__global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n, int op) {
+  const long n8 = n >> 3;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += long(gridDim.x) * blockDim.x) {
+    float f[8];
+    unpack8<T>(reinterpret_cast<const Vec8*>(x)[i], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = act_apply(f[k], op);
+    reinterpret_cast<Vec8*>(y)[i] = pack8<T>(f);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const long i = (n8 << 3) + threadIdx.x;
+    y[i] = Cvt<T>::from_f(act_apply(Cvt<T>::to_f(x[i]), op));
+  }
+}
+
+// op: 0 add, 1 mul, 2 sub, 3 swiglu (silu(a) * b), 4 add+relu
+template <class T>
+__global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long n, int op) {
+  const long n8 = n >> 3;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += long(gridDim.x) * blockDim.x) {
+    float fa[8], fb[8];
+    unpack8<T>(reinterpret_cast<const Vec8*>(a)[i], fa);
+    unpack8<T>(reinterpret_cast<const Vec8*>(b)[i], fb);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float r;
+      switch (op) {
+        case 0: r = fa[k] + fb[k]; break;
+        case 1: r = fa[k] * fb[k]; break;
+        case 2: r = fa[k] - fb[k]; break;
+        case 3: r = fa[k] / (1.f + __expf(-fa[k])) * fb[k]; break;
+        default: r = fmaxf(fa[k] + fb[k], 0.f); break;
+      }
+      fa[k] = r;
+    }
+    reinterpret_cast<Vec8*>(y)[i] = pack8<T>(fa);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+    const long i = (n8 << 3) + threadIdx.x;
+    const float fa = Cvt<T>::to_f(a[i]), fb = Cvt<T>::to_f(b[i]);
+    float r = op == 0 ? fa + fb : op == 1 ? fa * fb : op == 2 ? fa - fb
+              : op == 3 ? fa / (1.f + __expf(-fa)) * fb : fmaxf(fa + fb, 0.f);
+    y[i] = Cvt<T>::from_f(r);
+  }
+}
+
+// SwiGLU on a fused [rows, 2*F] gate|up projection: y[r, f] = silu(x[r, f]) * x[r, F + f]
+template <class T>
+__global__ void swiglu_fused_kernel(const T* __restrict__ x, T* __restrict__ y, int F, long rows) {
+  const int f8 = F >> 3;
+  const long total = rows * f8;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const long r = i / f8;
+    const int c = int(i - r * f8) * 8;
+    float g[8], u[8];
+    unpack8<T>(*reinterpret_cast<const Vec8*>(x + r * 2 * F + c), g);
+    unpack8<T>(*reinterpret_cast<const Vec8*>(x + r * 2 * F + F + c), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    *reinterpret_cast<Vec8*>(y + r * F + c) = pack8<T>(g);
+  }
+}
+
+// out[t, :] = table[ids[t], :] (+ pos_table[pos[t], :]).  H % 8 == 0.  Out-of-range ids produce zeros.
+template <class T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const T* __restrict__ table,
+                                 const T* __restrict__ pos_table, T* __restrict__ out, int H, int vocab, int max_pos,
+                                 long ld_out) {
+  const long t = blockIdx.x;
+  const int id = ids[t];
+  const int p = pos ? pos[t] : 0;
+  const bool ok = id >= 0 && id < vocab;
+  const bool pok = pos_table && p >= 0 && p < max_pos;
+  for (int ch = threadIdx.x; ch < (H >> 3); ch += blockDim.x) {
+    float f[8];
+    if (ok) unpack8<T>(*reinterpret_cast<const Vec8*>(table + long(id) * H + ch * 8), f);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    }
+    if (pok) {
+      float g[8];
+      unpack8<T>(*reinterpret_cast<const Vec8*>(pos_table + long(p) * H + ch * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+    }
+    *reinterpret_cast<Vec8*>(out + t * ld_out + ch * 8) = pack8<T>(f);
+  }
+}
+
+// Row argmax with lowest-index tie break.  Writes idx_out[row] (+ col_offset) and optionally max_out[row].
+template <class T>
+__global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out, float* __restrict__ max_out, int cols,
+                              long ld, int col_offset) {
+  __shared__ float smax[32];
+  __shared__ int sidx[32];
+  const T* xr = x + long(blockIdx.x) * ld;
+  float m = -INFINITY;
+  int mi = 0x7fffffff;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    const float v = Cvt<T>::to_f(xr[i]);
+    if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+    if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  if (lane == 0) { smax[warp] = m; sidx[warp] = mi; }
+  __syncthreads();
+  if (warp == 0) {
+    m = lane < nw ? smax[lane] : -INFINITY;
+    mi = lane < nw ? sidx[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+      if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+    }
+    if (lane == 0) {
+      idx_out[blockIdx.x] = mi + col_offset;
+      if (max_out) max_out[blockIdx.x] = m;
+    }
+  }
+}
+
+// Combine per-shard (max, idx) pairs: vals/idx are [shards, rows]; picks the largest value, lowest index on ties.
+__global__ void argmax_combine_kernel(const float* __restrict__ vals, const int* __restrict__ idx, int* __restrict__ out,
+                                      int shards, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float m = -INFINITY;
+  int mi = 0x7fffffff;
+  for (int s = 0; s < shards; ++s) {
+    const float v = vals[s * rows + r];
+    const int i = idx[s * rows + r];
+    if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+  }
+  out[r] = mi;
+}
+
+template <class TI, class TO>
+__global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long n) {
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n; i += long(gridDim.x) * blockDim.x)
+    y[i] = Cvt<TO>::from_f(Cvt<TI>::to_f(x[i]));
+}
+
+static inline int grid_for(long work, int threads, int cap = 148 * 16) {
+  long g = (work + threads - 1) / threads;
+  if (g < 1) g = 1;
+  return int(g > cap ? cap : g);
+}
+
+}  // namespace ronn
+
+using namespace ronn;
+
+#define RONN_BY_DTYPE(dtype, ...)                           \
+  do {                                                      \
+    if ((dtype) == 0) { using T = __nv_bfloat16; __VA_ARGS__; } \
+    else if ((dtype) == 1) { using T = __half; __VA_ARGS__; }   \
+    else return -1;                                         \
+  } while (0)
+
+static inline int check_launch() { return cudaGetLastError() == cudaSuccess ? 0 : -100; }
+
+// dtype: 0 bf16, 1 fp16.  rms: 0 LayerNorm, 1 RMSNorm.  H % 8 == 0 and H <= 32768.
+extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, const void* beta, void* y, void* sum_out,
+                         long rows, int H, long ld_x, long ld_res, long ld_y, float eps, int rms, int dtype,
+                         cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) || H > 1024 * 8 * NORM_MAX_CHUNKS || (ld_x & 7) || (ld_y & 7) || (res && (ld_res & 7))) return -2;
+  int threads = ((H >> 3) + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS;
+  threads = ((threads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 1024) threads = 1024;
+  RONN_BY_DTYPE(dtype, {
+    if (rms) norm_kernel<T, true><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (const T*)res, (const T*)gamma,
+                                                                          (const T*)beta, (T*)y, (T*)sum_out, H, ld_x,
+                                                                          ld_res, ld_y, eps);
+    else norm_kernel<T, false><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (const T*)res, (const T*)gamma,
+                                                                       (const T*)beta, (T*)y, (T*)sum_out, H, ld_x,
+                                                                       ld_res, ld_y, eps);
+  });
+  return check_launch();
+}
+
+// dtype: 0 bf16, 1 fp16, 2 fp32
+extern "C" int ronn_softmax(const void* x, void* y, long rows, int cols, int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
+  if (dtype == 2) softmax_kernel<float><<<unsigned(rows), threads, 0, stream>>>((const float*)x, (float*)y, cols);
+  else RONN_BY_DTYPE(dtype, (softmax_kernel<T><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (T*)y, cols)));
+  return check_launch();
+}
+
+extern "C" int ronn_unary(const void* x, void* y, long n, int op, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
+  RONN_BY_DTYPE(dtype, (unary_kernel<T><<<grid_for(n >> 3, 256), 256, 0, stream>>>((const T*)x, (T*)y, n, op)));
+  return check_launch();
+}
+
+extern "C" int ronn_binary(const void* a, const void* b, void* y, long n, int op, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
+  RONN_BY_DTYPE(dtype, (binary_kernel<T><<<grid_for(n >> 3, 256), 256, 0, stream>>>((const T*)a, (const T*)b, (T*)y, n, op)));
+  return check_launch();
+}
+
+extern "C" int ronn_swiglu_fused(const void* x, void* y, long rows, int F, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (F & 7) return -2;
+  RONN_BY_DTYPE(dtype, (swiglu_fused_kernel<T><<<grid_for(rows * (F >> 3), 256), 256, 0, stream>>>((const T*)x, (T*)y, F, rows)));
+  return check_launch();
+}
+
+extern "C" int ronn_embedding(const int* ids, const int* pos, const void* table, const void* pos_table, void* out,
+                              long tokens, int H, int vocab, int max_pos, long ld_out, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if ((H & 7) || (ld_out & 7)) return -2;
+  int threads = (H >> 3) >= 128 ? 128 : 64;
+  RONN_BY_DTYPE(dtype, (embedding_kernel<T><<<unsigned(tokens), threads, 0, stream>>>(ids, pos, (const T*)table,
+                                                                                     (const T*)pos_table, (T*)out, H,
+                                                                                     vocab, max_pos, ld_out)));
+  return check_launch();
+}
+
+// dtype: 0 bf16, 1 fp16, 2 fp32
+extern "C" int ronn_argmax(const void* x, int* idx_out, float* max_out, long rows, int cols, long ld, int col_offset,
+                           int dtype, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  const int threads = cols >= 8192 ? 1024 : 256;
+  if (dtype == 2) argmax_kernel<float><<<unsigned(rows), threads, 0, stream>>>((const float*)x, idx_out, max_out, cols, ld, col_offset);
+  else RONN_BY_DTYPE(dtype, (argmax_kernel<T><<<unsigned(rows), threads, 0, stream>>>((const T*)x, idx_out, max_out, cols, ld, col_offset)));
+  return check_launch();
+}
+
+extern "C" int ronn_argmax_combine(const float* vals, const int* idx, int* out, int shards, int rows,
+                                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  argmax_combine_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(vals, idx, out, shards, rows);
+  return check_launch();
+}
+
+// from/to: 0 bf16, 1 fp16, 2 fp32
+extern "C" int ronn_cast(const void* x, void* y, long n, int from, int to, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int g = grid_for(n, 256);
+#define RONN_CAST(FI, TI, FO, TO) \
+  if (from == FI && to == FO) { cast_kernel<TI, TO><<<g, 256, 0, stream>>>((const TI*)x, (TO*)y, n); return check_launch(); }
+  RONN_CAST(0, __nv_bfloat16, 2, float)
+  RONN_CAST(1, __half, 2, float)
+  RONN_CAST(2, float, 0, __nv_bfloat16)
+  RONN_CAST(2, float, 1, __half)
+  RONN_CAST(0, __nv_bfloat16, 1, __half)
+  RONN_CAST(1, __half, 0, __nv_bfloat16)
+#undef RONN_CAST
+  return -1;
+}

@@ -396,11 +396,11 @@ int32_t ronn_sched_plan_tokens(void* h) {
 // Flatten the current plan into kernel-ready arrays.
 //   req_ids[n_items], q_start[n_items+1] (token offsets), seq_lens[n_items] (context length after this step),
 //   sample_index[n_items] (flat token index whose logits are sampled, or -1),
-//   token_ids/positions/slot_mapping[n_tokens], block_tables[n_items * max_blocks] (-1 padded)
+//   token_ids/positions/slot_mapping/token_item[n_tokens] (token_item = plan item of the token), block_tables[n_items * max_blocks] (-1 padded)
 // Returns the number of tokens, or -1 when the block-table stride is too small.
 int32_t ronn_sched_fill(void* h, int64_t* req_ids, int32_t* q_start, int32_t* seq_lens, int32_t* sample_index,
-                        int32_t* token_ids, int32_t* positions, int32_t* slot_mapping, int32_t* block_tables,
-                        int32_t max_blocks) {
+                        int32_t* token_ids, int32_t* positions, int32_t* slot_mapping, int32_t* token_item,
+                        int32_t* block_tables, int32_t max_blocks) {
   Scheduler* s = static_cast<Scheduler*>(h);
   int32_t tok = 0;
   int32_t bs = s->cfg.block_size;
@@ -417,6 +417,7 @@ int32_t ronn_sched_fill(void* h, int64_t* req_ids, int32_t* q_start, int32_t* se
       token_ids[tok] = r.tokens[size_t(pos)];
       positions[tok] = pos;
       slot_mapping[tok] = r.blocks[size_t(pos / bs)] * bs + pos % bs;
+      token_item[tok] = int32_t(i);
       ++tok;
     }
     int32_t* bt = block_tables + size_t(i) * max_blocks;

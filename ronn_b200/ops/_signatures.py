@@ -1,0 +1,36 @@
+"""ctypes prototypes of the sm_100a kernel library's extern "C" launchers."""
+import ctypes as C
+
+V, I, L, F = C.c_void_p, C.c_int, C.c_long, C.c_float
+
+
+def declare(lib):
+    def sig(name, args, optional=False):
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            if optional:
+                return
+            raise
+        fn.restype = C.c_int
+        fn.argtypes = args
+
+    sig("ronn_gemm", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, V, V])
+    sig("ronn_norm", [V, V, V, V, V, V, L, I, L, L, L, F, I, I, V])
+    sig("ronn_softmax", [V, V, L, I, I, V])
+    sig("ronn_unary", [V, V, L, I, I, V])
+    sig("ronn_binary", [V, V, V, L, I, I, V])
+    sig("ronn_swiglu_fused", [V, V, L, I, I, V])
+    sig("ronn_embedding", [V, V, V, V, V, L, I, I, I, L, I, V])
+    sig("ronn_argmax", [V, V, V, L, I, L, I, I, V])
+    sig("ronn_argmax_combine", [V, V, V, I, I, V])
+    sig("ronn_cast", [V, V, L, I, I, V])
+    sig("ronn_kv_append", [V, L, I, I, V, V, V, V, L, I, I, I, F, I, I, V])
+    sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, V])
+    sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, V], optional=True)
+    sig("ronn_maxpool_nhwc", [V, V, I, I, I, I, I, I, I, I, I, I, V], optional=True)
+    sig("ronn_global_avgpool_nhwc", [V, V, I, I, I, I, V], optional=True)
+    sig("ronn_act_quant_int8", [V, V, V, L, I, I, V], optional=True)
+    sig("ronn_norm_quant_int8", [V, V, V, V, V, L, I, F, I, V], optional=True)
+    sig("ronn_bitlinear", [V, V, V, F, V, V, V, I, I, I, I, I, V, V], optional=True)
+    sig("ronn_ternary_pack", [V, V, L, I, V], optional=True)

@@ -1,0 +1,227 @@
+"""Thin launch wrappers: torch tensors in, raw pointers + current stream into the native library.
+
+Every wrapper raises ``KernelError`` when the native launcher reports a bad configuration; nothing
+here falls back to PyTorch.  A status word on the device records abandoned waits inside the
+tensor-core kernels; ``check_status`` reads it (one small device-to-host copy) and raises.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ..api.errors import CommTimeoutError, RonnError
+
+
+class KernelError(RonnError):
+    prefix = "Kernel error: "
+
+
+_DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+_ACT = {"": 0, None: 0, "none": 0, "Relu": 1, "relu": 1, "Gelu": 2, "gelu": 2}
+_STATUS = {}
+_STATUS_NAMES = {1: "TMA stage never arrived", 2: "pipeline stage never released", 3: "accumulator never committed",
+                 4: "peer flag never raised", 5: "epilogue never drained"}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+def status_word(device=None) -> torch.Tensor:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    w = _STATUS.get(dev)
+    if w is None:
+        w = torch.zeros(4, dtype=torch.int32, device=dev)
+        _STATUS[dev] = w
+    return w
+
+
+def check_status(device=None) -> None:
+    """Raise if a bounded wait inside a kernel gave up since the last check."""
+    w = status_word(device)
+    code = int(w[0].item())
+    if code:
+        w.zero_()
+        raise CommTimeoutError(f"a device-side wait was abandoned: {_STATUS_NAMES.get(code, code)}")
+
+
+def gemm(a: torch.Tensor, w_nk: torch.Tensor, bias: Optional[torch.Tensor] = None,
+         residual: Optional[torch.Tensor] = None, activation: str = "", out: Optional[torch.Tensor] = None,
+         out_fp32: bool = False, bn: int = 0) -> torch.Tensor:
+    """out[M,N] = act(a[M,K] @ w_nk[N,K]^T + bias) + residual on the tcgen05 tensor cores."""
+    if a.dim() != 2 or w_nk.dim() != 2 or a.shape[1] != w_nk.shape[1]:
+        raise KernelError(f"gemm shape mismatch: a {tuple(a.shape)} w {tuple(w_nk.shape)}")
+    if a.dtype not in (torch.bfloat16, torch.float16) or w_nk.dtype != a.dtype:
+        raise KernelError(f"gemm needs bf16/fp16 operands of one dtype, got {a.dtype} and {w_nk.dtype}")
+    if a.stride(1) != 1 or w_nk.stride(1) != 1:
+        raise KernelError("gemm operands must be K-contiguous")
+    M, K = a.shape
+    N = w_nk.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32 if out_fp32 else a.dtype, device=a.device)
+    if residual is not None and (residual.stride(0) != out.stride(0) or residual.stride(1) != 1):
+        residual = residual.contiguous()
+        if residual.stride(0) != out.stride(0):
+            raise KernelError("gemm residual must share the output's row stride")
+    if bias is not None and bias.dtype != a.dtype:
+        bias = bias.to(a.dtype)
+    rc = _native.cuda().ronn_gemm(a.data_ptr(), w_nk.data_ptr(), out.data_ptr(), _ptr(bias), _ptr(residual), M, N, K,
+                                  a.stride(0), w_nk.stride(0), out.stride(0), _DT[a.dtype], _ACT[activation],
+                                  1 if out.dtype == torch.float32 else 0, bn, status_word(a.device).data_ptr(),
+                                  _stream())
+    _check(rc, "gemm")
+    return out
+
+
+def _norm(x, gamma, beta, residual, eps, rms, sum_out):
+    H = x.shape[-1]
+    x2 = x.reshape(-1, H)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    y = torch.empty((rows, H), dtype=x.dtype, device=x.device)
+    r2 = None
+    if residual is not None:
+        r2 = residual.reshape(-1, H)
+        if r2.stride(1) != 1:
+            r2 = r2.contiguous()
+    s = torch.empty_like(y) if sum_out else None
+    rc = _native.cuda().ronn_norm(x2.data_ptr(), _ptr(r2), _ptr(gamma), _ptr(beta), y.data_ptr(), _ptr(s), rows, H,
+                                  x2.stride(0), r2.stride(0) if r2 is not None else 0, y.stride(0), float(eps),
+                                  1 if rms else 0, _DT[x.dtype], _stream())
+    _check(rc, "norm")
+    y = y.reshape(x.shape)
+    return (y, s.reshape(x.shape)) if sum_out else y
+
+
+def layernorm(x, gamma=None, beta=None, eps: float = 1e-5, residual=None, return_sum: bool = False):
+    """LayerNorm over the last axis of (x + residual); optionally also returns the sum."""
+    return _norm(x, gamma, beta, residual, eps, False, return_sum)
+
+
+def rmsnorm(x, gamma, eps: float = 1e-5, residual=None, return_sum: bool = False):
+    return _norm(x, gamma, None, residual, eps, True, return_sum)
+
+
+def softmax(x: torch.Tensor) -> torch.Tensor:
+    """Softmax over the last axis."""
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    cols = xc.shape[-1]
+    _check(_native.cuda().ronn_softmax(xc.data_ptr(), y.data_ptr(), xc.numel() // cols, cols, _DT[x.dtype], _stream()),
+           "softmax")
+    return y
+
+
+_UNARY = {"relu": 0, "gelu": 1, "fast_gelu": 2, "sigmoid": 3, "silu": 4, "tanh": 5}
+_BINARY = {"add": 0, "mul": 1, "sub": 2, "swiglu": 3, "add_relu": 4}
+
+
+def unary(x: torch.Tensor, op: str) -> torch.Tensor:
+    xc = x.contiguous()
+    y = torch.empty_like(xc)
+    _check(_native.cuda().ronn_unary(xc.data_ptr(), y.data_ptr(), xc.numel(), _UNARY[op], _DT[x.dtype], _stream()),
+           f"unary {op}")
+    return y
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, op: str) -> torch.Tensor:
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise KernelError("binary kernel needs operands of one shape and dtype")
+    ac, bc = a.contiguous(), b.contiguous()
+    y = torch.empty_like(ac)
+    _check(_native.cuda().ronn_binary(ac.data_ptr(), bc.data_ptr(), y.data_ptr(), ac.numel(), _BINARY[op],
+                                      _DT[a.dtype], _stream()), f"binary {op}")
+    return y
+
+
+def swiglu_fused(x: torch.Tensor) -> torch.Tensor:
+    """x = [rows, 2F] (gate | up) -> silu(gate) * up."""
+    F2 = x.shape[-1]
+    xc = x.reshape(-1, F2).contiguous()
+    y = torch.empty((xc.shape[0], F2 // 2), dtype=x.dtype, device=x.device)
+    _check(_native.cuda().ronn_swiglu_fused(xc.data_ptr(), y.data_ptr(), xc.shape[0], F2 // 2, _DT[x.dtype], _stream()),
+           "swiglu")
+    return y.reshape(*x.shape[:-1], F2 // 2)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, positions: Optional[torch.Tensor] = None,
+              pos_table: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    ids32 = ids.reshape(-1).to(torch.int32)
+    pos32 = positions.reshape(-1).to(torch.int32) if positions is not None else None
+    T, H = ids32.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+    _check(_native.cuda().ronn_embedding(ids32.data_ptr(), _ptr(pos32), table.data_ptr(), _ptr(pos_table),
+                                         out.data_ptr(), T, H, table.shape[0],
+                                         pos_table.shape[0] if pos_table is not None else 0, out.stride(0),
+                                         _DT[table.dtype], _stream()), "embedding")
+    return out
+
+
+def argmax(x: torch.Tensor, col_offset: int = 0, return_max: bool = False, out: Optional[torch.Tensor] = None):
+    """Row argmax of a 2-D tensor (lowest index wins ties) as int32."""
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=x.device)
+    mx = torch.empty(rows, dtype=torch.float32, device=x.device) if return_max else None
+    _check(_native.cuda().ronn_argmax(x.data_ptr(), out.data_ptr(), _ptr(mx), rows, cols, x.stride(0), col_offset,
+                                      _DT[x.dtype], _stream()), "argmax")
+    return (out, mx) if return_max else out
+
+
+def argmax_combine(vals: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    shards, rows = vals.shape
+    out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+    _check(_native.cuda().ronn_argmax_combine(vals.data_ptr(), idx.data_ptr(), out.data_ptr(), shards, rows, _stream()),
+           "argmax_combine")
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    if x.dtype == dtype:
+        return x
+    xc = x.contiguous()
+    y = torch.empty(xc.shape, dtype=dtype, device=x.device)
+    _check(_native.cuda().ronn_cast(xc.data_ptr(), y.data_ptr(), xc.numel(), _DT[x.dtype], _DT[dtype], _stream()), "cast")
+    return y
+
+
+def kv_append(qkv: torch.Tensor, k_off: int, v_off: int, slots: torch.Tensor, kcache: torch.Tensor,
+              vcache: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
+              positions: Optional[torch.Tensor] = None, rope_base: float = 0.0) -> None:
+    """Scatter the K/V columns of a fused QKV activation into the paged cache (optionally after rotary)."""
+    T = qkv.shape[0]
+    use_rope = 1 if rope_base > 0 and positions is not None else 0
+    _check(_native.cuda().ronn_kv_append(qkv.data_ptr(), qkv.stride(0), k_off, v_off, slots.data_ptr(),
+                                         _ptr(positions), kcache.data_ptr(), vcache.data_ptr(), T, heads, kv_heads,
+                                         head_dim, float(rope_base), use_rope, _DT[qkv.dtype], _stream()), "kv_append")
+
+
+def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
+                    ctx_len: torch.Tensor, heads: int, kv_heads: int, head_dim: int, max_ctx: int,
+                    bt_row: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                    scale: Optional[float] = None) -> torch.Tensor:
+    """q: [rows, >= heads*head_dim] (row stride free).  Returns [rows, heads*head_dim]."""
+    rows = q.shape[0]
+    if out is None:
+        out = torch.empty((rows, heads * head_dim), dtype=q.dtype, device=q.device)
+    sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    _check(_native.cuda().ronn_paged_attention(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+                                               block_tables.data_ptr(), block_tables.shape[1], ctx_len.data_ptr(),
+                                               _ptr(bt_row), out.data_ptr(), out.stride(0), rows, heads, kv_heads,
+                                               head_dim, int(max_ctx), float(sc), _DT[q.dtype], _stream()),
+           "paged_attention")
+    return out

@@ -1,0 +1,34 @@
+"""Engine configuration (docs/new/RONN-Continuous-Batching-Branch-Prompt.md:156-255:
+max_batch_size, max_batch_tokens, prefill_chunk_size; KV block size 16 from
+docs/new/RONN-KV-Cache-Compression-Branch-Prompt.md:125-195)."""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+
+@dataclass
+class EngineConfig:
+    block_size: int = 16
+    num_blocks: int = 0                 # 0 = size from gpu_memory_utilization / max_num_seqs * max_model_len
+    max_num_seqs: int = 256
+    max_batch_tokens: int = 8192
+    max_model_len: int = 1024
+    prefill_chunk: int = 0              # 0 = whole prompts
+    policy: str = "fcfs"                # "fcfs" | "priority"
+    enable_prefix_cache: bool = False
+    eos_token_id: int = -1              # -1 = never stop on a token
+    use_cuda_graph: bool = True
+    dtype: str = "bf16"
+    tp_size: int = 1
+    backend: str = "kernels"            # "kernels" (hand-written sm_100a) | "torch" (library baseline / CPU)
+    tp_comm: str = "fused"              # "fused" (in-kernel NVLink) | "nccl" (library collectives baseline)
+    gpu_memory_utilization: float = 0.85
+
+    def __post_init__(self):
+        if self.block_size != 16:
+            raise ValueError("the paged attention kernels are built for 16-token blocks")
+        for k in ("max_num_seqs", "max_batch_tokens", "max_model_len"):
+            env = os.environ.get("RONN_" + k.upper())
+            if env:
+                setattr(self, k, int(env))

@@ -1,0 +1,242 @@
+"""Paged-KV decoder runner: turns the initializers of a GPT-2 or Llama/BitNet-style ONNX model into
+sharded device weights and runs prefill / decode steps over the operator backend.
+
+Tensor parallelism (Megatron layout): QKV and MLP-up are column-parallel (heads / FFN columns
+sharded), attention-out and MLP-down are row-parallel; the vocabulary of the LM head is sharded
+and the greedy token is chosen by a cross-rank (max, index) combine.  The collective after a
+row-parallel GEMM is delegated to ``self.comm`` (library all-reduce on the baseline path, fused
+in-kernel exchange on the product path).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+
+from ..api.errors import SessionError
+from .config import EngineConfig
+from .ops_backend import make_ops
+
+KV_BLOCK = 16
+
+
+@dataclass
+class DecoderArch:
+    name: str
+    n_layer: int
+    hidden: int
+    n_head: int
+    n_kv_head: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    max_pos: int
+    norm: str = "layernorm"        # "layernorm" | "rmsnorm"
+    mlp: str = "gelu"              # "gelu" | "swiglu"
+    rope_base: float = 0.0         # 0 = learned absolute positions
+    eps: float = 1e-5
+    bitlinear: bool = False
+
+    @staticmethod
+    def from_metadata(md: Dict[str, str]) -> "DecoderArch":
+        arch = md.get("ronn.arch")
+        if arch == "gpt2":
+            H, nh = int(md["ronn.n_embd"]), int(md["ronn.n_head"])
+            return DecoderArch("gpt2", int(md["ronn.n_layer"]), H, nh, nh, H // nh, 4 * H, int(md["ronn.vocab_size"]),
+                               int(md["ronn.n_positions"]), eps=float(md.get("ronn.eps", 1e-5)))
+        if arch in ("llama", "bitnet"):
+            H, nh = int(md["ronn.hidden"]), int(md["ronn.n_head"])
+            return DecoderArch(arch, int(md["ronn.n_layer"]), H, nh, int(md.get("ronn.n_kv_head", nh)),
+                               int(md.get("ronn.head_dim", H // nh)), int(md["ronn.ffn"]), int(md["ronn.vocab_size"]),
+                               int(md.get("ronn.max_pos", 4096)), norm="rmsnorm", mlp="swiglu",
+                               rope_base=float(md.get("ronn.rope_base", 10000.0)), eps=float(md.get("ronn.eps", 1e-5)),
+                               bitlinear=(arch == "bitnet"))
+        raise SessionError(f"model metadata does not describe a decoder architecture (ronn.arch={arch!r})")
+
+
+def shard_heads(n_head: int, tp: int, rank: int):
+    """Contiguous head ranges; the first (n_head % tp) ranks take one extra head."""
+    base, extra = divmod(n_head, tp)
+    start = rank * base + min(rank, extra)
+    return start, base + (1 if rank < extra else 0)
+
+
+class NoComm:
+    world = 1
+    rank = 0
+
+    def all_reduce(self, x):
+        return x
+
+    def all_gather_small(self, x):
+        return x.unsqueeze(0)
+
+    def barrier(self):
+        pass
+
+
+class LinearW:
+    """A dense [N,K] weight (+ optional bias) or a packed ternary BitLinear weight."""
+    __slots__ = ("w", "bias", "scale", "packed", "n", "k")
+
+    def __init__(self, w=None, bias=None, packed=None, scale=None, n=0, k=0):
+        self.w, self.bias, self.packed, self.scale, self.n, self.k = w, bias, packed, scale, n, k
+
+
+class DecoderRunner:
+    def __init__(self, arch: DecoderArch, initializers: Dict[str, torch.Tensor], cfg: EngineConfig,
+                 device: torch.device, comm=None, num_blocks: Optional[int] = None):
+        self.arch, self.cfg, self.device = arch, cfg, device
+        self.comm = comm or NoComm()
+        self.tp, self.rank = self.comm.world, self.comm.rank
+        self.dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg.dtype]
+        self.ops = make_ops(cfg.backend, device)
+        if cfg.backend == "kernels" and self.dtype == torch.float32:
+            raise SessionError("the kernel backend computes in bf16 or fp16")
+        a = arch
+        self.h0, self.n_head_local = shard_heads(a.n_head, self.tp, self.rank)
+        if a.n_kv_head == a.n_head:
+            self.kv0, self.n_kv_local = self.h0, self.n_head_local
+        else:
+            if a.n_kv_head % self.tp:
+                raise SessionError("grouped KV heads must divide by the tensor-parallel size")
+            self.kv0, self.n_kv_local = shard_heads(a.n_kv_head, self.tp, self.rank)
+        if self.n_head_local == 0:
+            raise SessionError("tensor-parallel size exceeds the number of attention heads")
+        if a.ffn % self.tp:
+            raise SessionError("FFN width must divide by the tensor-parallel size")
+        self.ffn_local = a.ffn // self.tp
+        vs = -(-a.vocab // self.tp)
+        vs = (vs + 7) // 8 * 8
+        self.vocab_start = min(self.rank * vs, a.vocab)
+        self.vocab_local = max(min(vs, a.vocab - self.vocab_start), 0)
+        self._load_weights(initializers)
+        self.num_blocks = num_blocks or cfg.num_blocks
+        self.max_blocks_per_seq = (cfg.max_model_len + KV_BLOCK - 1) // KV_BLOCK
+        self._alloc_cache()
+        self.launches = 0
+
+    # ------------------------------------------------------------------ weights
+    def _dev(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(self.device, self.dtype).contiguous()
+
+    def _load_weights(self, init: Dict[str, torch.Tensor]) -> None:
+        a, d = self.arch, self.arch.head_dim
+        hs, hn = self.h0 * d, self.n_head_local * d
+        ks, kn = self.kv0 * d, self.n_kv_local * d
+        self.layers: List[Dict[str, object]] = []
+        if a.name == "gpt2":
+            self.wte = self._dev(init["wte"])
+            self.wpe = self._dev(init["wpe"])
+            self.lnf = (self._dev(init["ln_f.weight"]), self._dev(init["ln_f.bias"]))
+            H = a.hidden
+            for i in range(a.n_layer):
+                p = f"h.{i}"
+                wqkv, bqkv = init[f"{p}.attn.c_attn.weight"], init[f"{p}.attn.c_attn.bias"]      # [H, 3H] (K,N)
+                cols = torch.cat([torch.arange(hs, hs + hn), H + torch.arange(hs, hs + hn),
+                                  2 * H + torch.arange(hs, hs + hn)])
+                wo = init[f"{p}.attn.c_proj.weight"]                                              # [H(in), H(out)]
+                wfc, bfc = init[f"{p}.mlp.c_fc.weight"], init[f"{p}.mlp.c_fc.bias"]              # [H, 4H]
+                wpr = init[f"{p}.mlp.c_proj.weight"]                                              # [4H, H]
+                f0, f1 = self.rank * self.ffn_local, (self.rank + 1) * self.ffn_local
+                self.layers.append({
+                    "ln1": (self._dev(init[f"{p}.ln_1.weight"]), self._dev(init[f"{p}.ln_1.bias"])),
+                    "ln2": (self._dev(init[f"{p}.ln_2.weight"]), self._dev(init[f"{p}.ln_2.bias"])),
+                    "qkv": LinearW(self._dev(wqkv[:, cols].t()), self._dev(bqkv[cols])),
+                    "out": LinearW(self._dev(wo[hs:hs + hn, :].t()), self._dev(init[f"{p}.attn.c_proj.bias"])),
+                    "up": LinearW(self._dev(wfc[:, f0:f1].t()), self._dev(bfc[f0:f1])),
+                    "down": LinearW(self._dev(wpr[f0:f1, :].t()), self._dev(init[f"{p}.mlp.c_proj.bias"])),
+                })
+            self.lm_head = self.wte[self.vocab_start:self.vocab_start + self.vocab_local]
+        else:
+            from ..models.bitnet_llama import load_decoder_weights
+            load_decoder_weights(self, init)
+
+    def _alloc_cache(self) -> None:
+        a = self.arch
+        if self.num_blocks <= 0:
+            per_block = a.n_layer * 2 * self.n_kv_local * KV_BLOCK * a.head_dim * torch.finfo(self.dtype).bits // 8
+            want = self.cfg.max_num_seqs * self.max_blocks_per_seq
+            if self.device.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(self.device)
+                cap = int(free * self.cfg.gpu_memory_utilization) // per_block
+                want = min(want, cap)
+            self.num_blocks = max(want, 1)
+        shape = (self.num_blocks, self.n_kv_local, KV_BLOCK, a.head_dim)
+        self.kcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
+        self.vcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
+
+    # ------------------------------------------------------------------ forward
+    def _linear(self, x, lw: LinearW, residual=None, activation="", reduce=False):
+        ops = self.ops
+        if lw.packed is not None:
+            from ..providers.bitnet import kernels as BK
+            y = BK.bitlinear(x, lw, backend=ops.name)
+            if reduce and self.tp > 1:
+                y = self.comm.all_reduce(y)
+            if residual is not None:
+                y = y + residual
+            return y
+        if reduce and self.tp > 1:
+            # bias and residual are applied once, after the partial sums are combined
+            y = ops.gemm(x, lw.w)
+            y = self.comm.all_reduce(y)
+            if lw.bias is not None:
+                y = y + lw.bias
+            if residual is not None:
+                y = y + residual
+            return y
+        return ops.gemm(x, lw.w, lw.bias, residual, activation)
+
+    def _norm(self, x, p):
+        if self.arch.norm == "layernorm":
+            return self.ops.layernorm(x, p[0], p[1], self.arch.eps)
+        return self.ops.rmsnorm(x, p[0], self.arch.eps)
+
+    def forward(self, b: Dict[str, torch.Tensor], decode: bool, n_tokens: int, n_items: int,
+                want_logits: bool = False) -> torch.Tensor:
+        """Runs one step over device-side batch tensors (already sliced to n_tokens / n_items) and returns the
+        greedy token of every item as int32 [n_items] (or, with ``want_logits`` and TP=1, the fp32 logits)."""
+        a, ops, d = self.arch, self.ops, self.arch.head_dim
+        ids, pos, slots = b["token_ids"], b["positions"], b["slot_mapping"]
+        if a.rope_base > 0:
+            x = ops.embedding(ids, self.wte)
+        else:
+            x = ops.embedding(ids, self.wte, pos, self.wpe)
+        if decode:
+            ctx, bt_row = b["seq_lens"], None
+        else:
+            ctx, bt_row = b["ctx_per_token"], b["token_item"]
+        hn, kn = self.n_head_local * d, self.n_kv_local * d
+        max_ctx = self.cfg.max_model_len
+        for li, L in enumerate(self.layers):
+            h = self._norm(x, L["ln1"])
+            qkv = self._linear(h, L["qkv"])
+            ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
+                          self.n_kv_local, d, pos, a.rope_base)
+            att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
+                                      self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
+            x = self._linear(att, L["out"], residual=x, reduce=True)
+            h = self._norm(x, L["ln2"])
+            if a.mlp == "gelu":
+                f = self._linear(h, L["up"], activation="gelu")
+            else:
+                f = ops.swiglu_fused(self._linear(h, L["up"]))
+            x = self._linear(f, L["down"], residual=x, reduce=True)
+        if not decode:
+            x = ops.gather_rows(x, b["sample_index_clamped"])
+        x = self._norm(x, self.lnf)
+        logits = ops.gemm(x, self.lm_head, out_fp32=True)
+        if want_logits:
+            if self.tp != 1:
+                raise SessionError("full logits are only available without tensor parallelism")
+            return logits
+        if self.tp == 1:
+            return ops.argmax(logits)
+        idx, mx = ops.argmax(logits, col_offset=self.vocab_start, return_max=True)
+        vals = self.comm.all_gather_small(mx)
+        idxs = self.comm.all_gather_small(idx)
+        return ops.argmax_combine(vals.contiguous(), idxs.contiguous())
+

@@ -1,0 +1,157 @@
+"""Operator backends of the decoder runner.
+
+``KernelOps`` launches the hand-written sm_100a kernels.  ``TorchOps`` expresses the same
+operators with PyTorch library calls (cuBLAS matmul, SDPA-style attention on gathered KV): it is
+the CPU path of the engine tests and, on a GPU, the measured library baseline - never the product
+path.  Both work on the same paged KV layout [num_blocks, kv_heads, 16, head_dim].
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..onnx.registry import rotary
+
+KV_BLOCK = 16
+
+
+class TorchOps:
+    name = "torch"
+
+    def gemm(self, a, w_nk, bias=None, residual=None, activation="", out_fp32=False):
+        y = torch.matmul(a, w_nk.t())
+        if bias is not None:
+            y = y + bias
+        if activation in ("gelu", "Gelu"):
+            y = F.gelu(y.float(), approximate="tanh").to(y.dtype)
+        elif activation in ("relu", "Relu"):
+            y = torch.relu(y)
+        if residual is not None:
+            y = y + residual
+        return y.float() if out_fp32 else y
+
+    def layernorm(self, x, w, b, eps):
+        return F.layer_norm(x.float(), (x.shape[-1],), w.float(), None if b is None else b.float(), eps).to(x.dtype)
+
+    def rmsnorm(self, x, w, eps):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+    def embedding(self, ids, table, positions=None, pos_table=None):
+        y = F.embedding(ids.long(), table)
+        if pos_table is not None:
+            y = y + F.embedding(positions.long(), pos_table)
+        return y
+
+    def gather_rows(self, x, idx):
+        return x.index_select(0, idx.long())
+
+    def swiglu_fused(self, x):
+        f = x.shape[-1] // 2
+        return (F.silu(x[..., :f].float()) * x[..., f:].float()).to(x.dtype)
+
+    def kv_append(self, qkv, k_off, v_off, slots, kcache, vcache, heads, kv_heads, d, positions=None, rope_base=0.0):
+        T = qkv.shape[0]
+        if rope_base > 0 and positions is not None:
+            q = rotary(qkv[:, :heads * d], positions, rope_base, heads)
+            k = rotary(qkv[:, k_off:k_off + kv_heads * d], positions, rope_base, kv_heads)
+            qkv[:, :heads * d] = q
+            qkv[:, k_off:k_off + kv_heads * d] = k
+        k = qkv[:, k_off:k_off + kv_heads * d].reshape(T, kv_heads, d)
+        v = qkv[:, v_off:v_off + kv_heads * d].reshape(T, kv_heads, d)
+        valid = slots >= 0
+        s = slots[valid].long()
+        blk, off = s // KV_BLOCK, s % KV_BLOCK
+        kcache[blk, :, off, :] = k[valid]
+        vcache[blk, :, off, :] = v[valid]
+
+    def paged_attention(self, q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row=None):
+        rows = q.shape[0]
+        qh = q[:, :heads * d].reshape(rows, heads, d).float()
+        bt = block_tables if bt_row is None else block_tables.index_select(0, bt_row.long())
+        nb = (max_ctx + KV_BLOCK - 1) // KV_BLOCK
+        nb = min(nb, bt.shape[1])
+        idx = bt[:, :nb].long().clamp_min(0)                                   # [rows, nb]
+        k = kcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).float()
+        v = vcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).float()
+        if kv_heads != heads:
+            rep = heads // kv_heads
+            k = k.repeat_interleave(rep, dim=1)
+            v = v.repeat_interleave(rep, dim=1)
+        scores = torch.einsum("rhd,rhld->rhl", qh, k) / math.sqrt(d)
+        pos = torch.arange(nb * KV_BLOCK, device=q.device)
+        mask = pos[None, :] >= ctx_len[:, None].long()
+        scores = scores.masked_fill(mask[:, None, :], float("-inf"))
+        p = torch.softmax(scores, dim=-1)
+        p = torch.nan_to_num(p, nan=0.0)                                         # rows with ctx_len == 0
+        v = torch.where(mask[:, None, :, None], torch.zeros((), device=v.device), v)
+        out = torch.einsum("rhl,rhld->rhd", p, v)
+        return out.reshape(rows, heads * d).to(q.dtype)
+
+    def argmax(self, logits, col_offset=0, return_max=False):
+        m, i = logits.float().max(dim=-1)
+        idx = (i + col_offset).to(torch.int32)
+        return (idx, m) if return_max else idx
+
+    def argmax_combine(self, vals, idx):
+        # largest value wins, lowest index on ties
+        best = vals.max(dim=0).values
+        cand = torch.where(vals == best[None, :], idx, torch.full_like(idx, 2 ** 31 - 1))
+        return cand.min(dim=0).values.to(torch.int32)
+
+    def check(self):
+        pass
+
+
+class KernelOps:
+    name = "kernels"
+
+    def __init__(self):
+        from .. import ops as K
+        self.K = K
+
+    def gemm(self, a, w_nk, bias=None, residual=None, activation="", out_fp32=False):
+        return self.K.gemm(a, w_nk, bias, residual, activation, out_fp32=out_fp32)
+
+    def layernorm(self, x, w, b, eps):
+        return self.K.layernorm(x, w, b, eps)
+
+    def rmsnorm(self, x, w, eps):
+        return self.K.rmsnorm(x, w, eps)
+
+    def embedding(self, ids, table, positions=None, pos_table=None):
+        return self.K.embedding(ids, table, positions, pos_table)
+
+    def gather_rows(self, x, idx):
+        return self.K.embedding(idx, x)
+
+    def swiglu_fused(self, x):
+        return self.K.swiglu_fused(x)
+
+    def kv_append(self, qkv, k_off, v_off, slots, kcache, vcache, heads, kv_heads, d, positions=None, rope_base=0.0):
+        self.K.kv_append(qkv, k_off, v_off, slots, kcache, vcache, heads, kv_heads, d, positions, rope_base)
+
+    def paged_attention(self, q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row=None):
+        return self.K.paged_attention(q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row)
+
+    def argmax(self, logits, col_offset=0, return_max=False):
+        return self.K.argmax(logits, col_offset, return_max)
+
+    def argmax_combine(self, vals, idx):
+        return self.K.argmax_combine(vals, idx)
+
+    def check(self):
+        self.K.check_status()
+
+
+def make_ops(backend: str, device: torch.device):
+    if backend == "kernels":
+        if device.type != "cuda":
+            raise RuntimeError("the 'kernels' backend needs a CUDA device; use backend='torch' on CPU")
+        return KernelOps()
+    if backend == "torch":
+        return TorchOps()
+    raise ValueError(f"unknown backend '{backend}'")
