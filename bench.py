@@ -1,0 +1,204 @@
+#!/usr/bin/env python
+"""Headline benchmark: GPT-2-medium decode tokens/s under continuous batching.
+
+Workload (fixed by the benchmark definition): GPT-2 medium (24 layers, hidden 1024, 16 heads,
+vocab 50257), bf16, paged KV cache with 16-token blocks, 256 concurrent requests with prompt
+lengths U(64,512) and 256 generated tokens each, random token ids and random-init weights,
+tensor-parallel over N GPUs of one node.
+
+    python bench.py --gpus N --steps K --warmup W          (N>1: launched once per rank by torchrun)
+
+A "step" is one engine iteration that decodes one token for every one of the 256 sequences.
+All prompts are prefilled first, the engine is advanced so that the timed window is centred on
+the middle of the 256-token generation, W untimed warm-up steps run, then exactly K steps are
+timed between barrier + synchronize pairs.  Two numbers come from those same K steps:
+
+  value  device time: CUDA events around each step on the launching stream (from the start of the
+         step's input upload to the end of its token read-back), summed, max over ranks
+  e2e    wall clock of the K ``engine.step()`` calls (host scheduling, pinned-memory H2D of the
+         step inputs, graph replay, D2H of the sampled tokens), max over ranks
+
+``--impl reference`` reports that the reference cannot be built here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference is a Rust/Cargo workspace (no setup.py/pyproject at its root, no cargo/"
+                                     "rustc/maturin in the image, 12 workspace members missing, gpu feature does not "
+                                     "compile); offline pip install fails, nothing to run"}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) >= 7:
+                    self.samples.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.15)
+
+    def start(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join(timeout=6)
+        sm = sorted(float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit())
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
+    ap.add_argument("--requests", type=int, default=256)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--tp-comm", default=os.environ.get("RONN_TP_COMM", "fused"), choices=["fused", "nccl"])
+    ap.add_argument("--layers", type=int, default=24, help=argparse.SUPPRESS)       # smoke runs only
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+
+    import numpy as np
+    import torch
+    from ronn_b200.api.model import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    from ronn_b200.parallel.group import TPComm, init_distributed
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+
+    rank, world, local = init_distributed()
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    K, W = args.steps, max(args.warmup, 3)
+    new_tokens = max(args.new_tokens, K + W + 2)
+
+    cfg = GPT2Config(n_layer=args.layers)
+    graph = build_gpt2(cfg, dtype=torch.bfloat16, seed=0, with_lm_head=False)
+    model = Model.from_graph(graph)
+    backend = "torch" if args.impl == "baseline" else "kernels"
+    ecfg = EngineConfig(max_num_seqs=args.requests, max_batch_tokens=8192, max_model_len=1024, dtype="bf16",
+                        backend=backend, use_cuda_graph=True, tp_size=world,
+                        tp_comm="nccl" if args.impl == "baseline" else args.tp_comm,
+                        num_blocks=args.requests * 50)
+    if world > 1:
+        from ronn_b200.parallel.fused import make_comm
+        comm = make_comm(ecfg.tp_comm, dev)
+    else:
+        comm = None
+    eng = LLMEngine(model, ecfg, device=dev, comm=comm)
+    launches_per_step = 1 + 8 * cfg.n_layer + 3
+
+    rng = np.random.default_rng(1234)
+    lens = rng.integers(64, 513, size=args.requests)
+    for n in lens:
+        eng.add_request(rng.integers(0, cfg.vocab_size, size=int(n)).tolist(), SamplingParams(max_new_tokens=new_tokens))
+
+    # ---- prefill everything, then advance to the window centred on the middle of the generation
+    t_pf = time.perf_counter()
+    while eng.sched.num_waiting > 0:
+        eng.step()
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t_pf
+    advance = max((args.new_tokens - K) // 2 - W, 0)
+    for _ in range(advance):
+        eng.step()
+    for _ in range(W):
+        eng.step()
+    assert eng.sched.num_running == args.requests, "all requests must be decoding in the timed window"
+
+    def sync_all():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
+    sync_all()
+    sampler.start()
+    t0 = time.perf_counter()
+    h2d = d2h = 0
+    for i in range(K):
+        starts[i].record()
+        out = eng.step()
+        ends[i].record()
+        h2d += eng.h2d_bytes_last
+        d2h += eng.d2h_bytes_last
+        assert len(out) == args.requests
+    sync_all()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    dev_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    if world > 1:
+        c = TPComm()
+        dev_ms = c.max_over_ranks(dev_ms)
+        wall = c.max_over_ranks(wall)
+    tokens = args.requests * K
+    value = tokens / (dev_ms / 1e3)
+    e2e = tokens / wall
+    mean_ctx = float(np.mean(lens)) + advance + W + K / 2
+    if rank == 0:
+        print(json.dumps({
+            "metric": "GPT-2 decode tokens/s (continuous batching, paged KV)", "value": round(value, 1),
+            "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours" if args.impl == "ours" else "library-baseline",
+            "config": {"model": "gpt2-medium" if cfg.n_layer == 24 else f"gpt2-medium-{cfg.n_layer}L",
+                       "global_batch": args.requests, "seq_len": "prompts U(64,512) + 256 new tokens",
+                       "kv_block": 16, "parallelism": f"tp{world}", "tp_comm": ecfg.tp_comm if world > 1 else "none",
+                       "mean_context_in_window": round(mean_ctx, 1),
+                       "timed_window": "K consecutive decode steps centred on token 128 of 256",
+                       "l2": "inputs larger than L2 (KV read per step >> 126 MB)",
+                       "prefill_seconds_untimed": round(prefill_s, 3)},
+            "clocks": clocks,
+            "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // K,
+                    "d2h_bytes_per_step": d2h // K, "ms_per_step": round(wall * 1e3 / K, 4)},
+            "gpu_launches": launches_per_step * K if backend == "kernels" else 0,
+        }))
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

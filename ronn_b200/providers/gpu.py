@@ -1,0 +1,103 @@
+"""GPU execution provider for B200.
+
+The reference's GPU provider dispatches each node to a Candle library call with a host round
+trip per node (crates/ronn-providers/src/gpu/provider.rs:1135-1436, 1439-1455, 1601-1613) and
+its "custom kernels" are uncompiled templates (gpu/cuda_kernels.rs:317-563).  Here a graph is
+compiled once: initializers are moved to the device in the session's compute dtype, GEMM weights
+are stored K-major for the tcgen05 kernel, and every node resolves to a hand-written sm_100a
+kernel where one exists (GEMM with fused bias/activation/residual, LayerNorm, Softmax, activations,
+elementwise, embedding gather, implicit-GEMM convolution, pooling).  Remaining operators (shape
+manipulation and the long tail) run as PyTorch CUDA ops on the same stream.  Tensors stay on the
+device between nodes; the whole run can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..api.errors import ProviderError
+from ..core.types import (DataType, MemoryType, PerformanceProfile, ProviderCapability, ProviderConfig, ProviderType)
+from ..graph.ir import ModelGraph
+from ..onnx.registry import default_registry
+from .base import CompiledKernel, ExecutionProvider, build_kernel
+
+_HALF = (torch.bfloat16, torch.float16)
+
+
+@dataclass
+class GpuProviderConfig:
+    device_ids: List[int] = field(default_factory=lambda: [0])
+    primary_device_id: int = 0
+    memory_limit: Optional[int] = None
+    enable_mixed_precision: bool = True
+    enable_tensor_cores: bool = True
+    stream_count: int = 1
+    enable_multi_gpu: bool = False
+    enable_p2p_transfer: bool = True
+    load_balancing: str = "round_robin"
+    enable_custom_kernels: bool = True
+    compute_dtype: Optional[str] = None     # "bf16" | "fp16" | None (keep the model's dtype)
+
+
+def _dtype_of(name: Optional[str]):
+    return {None: None, "bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[name]
+
+
+class GpuExecutionProvider(ExecutionProvider):
+    provider_id = ProviderType.GPU
+    name = "GpuExecutionProvider"
+
+    def __init__(self, config: GpuProviderConfig = None):
+        if not torch.cuda.is_available():
+            raise ProviderError("no CUDA device is available")
+        self.config = config or GpuProviderConfig()
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        from .. import _native
+        _native.cuda()                      # fail loudly when the kernel library is missing
+        self.kernel_launches = 0
+
+    def set_session_options(self, opts) -> None:
+        if opts.dtype:
+            self.config.compute_dtype = opts.dtype
+
+    def has_tensor_cores(self) -> bool:
+        return torch.cuda.get_device_capability(self.device)[0] >= 7
+
+    def get_capability(self) -> ProviderCapability:
+        return ProviderCapability(
+            supported_ops=set(default_registry().supported_ops()),
+            data_types=[DataType.F32, DataType.F16, DataType.BF16, DataType.I8, DataType.I32, DataType.I64,
+                        DataType.U8, DataType.BOOL],
+            memory_types=[MemoryType.DEVICE, MemoryType.PINNED],
+            performance_profile=PerformanceProfile.GPU,
+            features={"device": torch.cuda.get_device_name(self.device), "tcgen05": True,
+                      "compute_capability": torch.cuda.get_device_capability(self.device)})
+
+    def configure(self, config: ProviderConfig) -> None:
+        opts = config.custom_options
+        if "compute_dtype" in opts:
+            self.config.compute_dtype = opts["compute_dtype"]
+        if "enable_custom_kernels" in opts:
+            self.config.enable_custom_kernels = opts["enable_custom_kernels"].lower() in ("1", "true", "yes")
+
+    # ------------------------------------------------------------------ compile
+    def compile_graph(self, graph: ModelGraph, profiler=None) -> CompiledKernel:
+        from .gpu_ops import GpuOpTable
+        cdt = _dtype_of(self.config.compute_dtype)
+        table = GpuOpTable(self, graph, cdt)
+        kernel = build_kernel(graph, self.device, table.resolve, table.place_const, self, profiler)
+        if cdt is not None:
+            kernel.input_cast = cdt
+            inner = kernel.execute
+
+            def execute(inputs, _inner=inner, _cdt=cdt):
+                feed = {k: (v.to(_cdt) if v.is_floating_point() and v.dtype != _cdt else v) for k, v in inputs.items()}
+                return _inner(feed)
+            kernel.execute = execute
+        return kernel
+
+
+def create_gpu_provider(**kw) -> GpuExecutionProvider:
+    return GpuExecutionProvider(**kw)

@@ -1,0 +1,179 @@
+"""Numerics of every hand-written kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ronn_b200 import ops
+    return ops
+
+
+def _rand(*shape, dtype=torch.bfloat16, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(dtype)
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(128, 128, 64, 0), (256, 1024, 1024, 0), (200, 264, 320, 32), (256, 3072, 1024, 64),
+                                       (300, 512, 4096, 128), (128, 256, 128, 256), (1, 50264, 256, 0), (77, 72, 136, 0)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_plain(K, M, N, K_, bn, dtype):
+    a, w = _rand(M, K_, dtype=dtype), _rand(N, K_, dtype=dtype, scale=0.05)
+    y = K.gemm(a, w, bn=bn)
+    K.check_status()
+    ref = a.float() @ w.float().t()
+    assert y.shape == (M, N)
+    torch.testing.assert_close(y.float(), ref, atol=2e-2 * math.sqrt(K_ / 64), rtol=2e-2)
+
+
+@pytest.mark.parametrize("act", ["", "relu", "gelu"])
+def test_gemm_epilogue(K, act):
+    M, N, K_ = 256, 1024, 512
+    a, w = _rand(M, K_), _rand(N, K_, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    y = K.gemm(a, w, bias, res, act)
+    K.check_status()
+    ref = a.float() @ w.float().t() + bias.float()
+    if act == "relu":
+        ref = torch.relu(ref)
+    elif act == "gelu":
+        ref = F.gelu(ref, approximate="tanh")
+    ref = ref + res.float()
+    torch.testing.assert_close(y.float(), ref, atol=6e-2, rtol=2e-2)
+    y32 = K.gemm(a, w, bias, None, act, out_fp32=True)
+    assert y32.dtype == torch.float32
+    torch.testing.assert_close(y32, ref - res.float(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("H", [128, 768, 1024, 2560])
+def test_layernorm_rmsnorm(K, H):
+    x, r = _rand(37, H), _rand(37, H)
+    g, b = _rand(H), _rand(H)
+    y = K.layernorm(x, g, b, 1e-5)
+    ref = F.layer_norm(x.float(), (H,), g.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=2e-2)
+    y2, s2 = K.layernorm(x, g, b, 1e-5, residual=r, return_sum=True)
+    sref = (x.float() + r.float())
+    torch.testing.assert_close(s2.float(), sref, atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(y2.float(), F.layer_norm(sref, (H,), g.float(), b.float(), 1e-5), atol=5e-2, rtol=2e-2)
+    y3 = K.rmsnorm(x, g, 1e-6)
+    xf = x.float()
+    torch.testing.assert_close(y3.float(), xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float(),
+                               atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("cols", [10, 128, 1000, 5000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_softmax(K, cols, dtype):
+    x = _rand(19, cols, dtype=dtype, scale=3.0)
+    y = K.softmax(x)
+    torch.testing.assert_close(y.float(), torch.softmax(x.float(), -1), atol=1e-2 if dtype != torch.float32 else 1e-5,
+                               rtol=2e-2 if dtype != torch.float32 else 1e-4)
+
+
+def test_elementwise(K):
+    x, y = _rand(1000, 77), _rand(1000, 77)
+    torch.testing.assert_close(K.unary(x, "relu").float(), torch.relu(x.float()))
+    torch.testing.assert_close(K.unary(x, "gelu").float(), F.gelu(x.float(), approximate="tanh"), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(K.unary(x, "fast_gelu").float(), x.float() * torch.sigmoid(1.702 * x.float()), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(K.unary(x, "sigmoid").float(), torch.sigmoid(x.float()), atol=1e-2, rtol=2e-2)
+    torch.testing.assert_close(K.unary(x, "silu").float(), F.silu(x.float()), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(K.unary(x, "tanh").float(), torch.tanh(x.float()), atol=1e-2, rtol=2e-2)
+    torch.testing.assert_close(K.binary(x, y, "add").float(), (x.float() + y.float()), atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(K.binary(x, y, "mul").float(), (x.float() * y.float()), atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(K.binary(x, y, "add_relu").float(), torch.relu(x.float() + y.float()), atol=2e-2, rtol=1e-2)
+    z = _rand(33, 256)
+    torch.testing.assert_close(K.swiglu_fused(z).float(), F.silu(z[:, :128].float()) * z[:, 128:].float(), atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(K.cast(x, torch.float32), x.float())
+
+
+def test_embedding_argmax(K):
+    table, ptab = _rand(1000, 256), _rand(64, 256)
+    ids = torch.randint(0, 1000, (50,), device="cuda", dtype=torch.int32)
+    pos = torch.randint(0, 64, (50,), device="cuda", dtype=torch.int32)
+    y = K.embedding(ids, table, pos, ptab)
+    torch.testing.assert_close(y.float(), table[ids.long()].float() + ptab[pos.long()].float(), atol=2e-2, rtol=1e-2)
+    torch.testing.assert_close(K.embedding(ids, table), table[ids.long()])
+    lg = torch.randn(37, 50257, device="cuda")
+    idx, mx = K.argmax(lg, return_max=True)
+    assert torch.equal(idx.long(), lg.argmax(-1))
+    torch.testing.assert_close(mx, lg.max(-1).values)
+    lb = lg.bfloat16()
+    idx_b = K.argmax(lb)
+    assert torch.equal(lb.float().gather(1, idx_b.long()[:, None])[:, 0], lb.float().max(-1).values)
+    vals = torch.stack([mx, mx - 1.0])
+    comb = K.argmax_combine(vals, torch.stack([idx, idx + 7]))
+    assert torch.equal(comb, idx)
+
+
+def _fill_cache(tokens_per_seq, heads, d, nblocks, dtype):
+    kc = torch.zeros(nblocks, heads, 16, d, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    return kc, vc
+
+
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (128, 4, 2), (64, 16, 16)])
+def test_kv_append_and_paged_attention(K, d, heads, kv_heads):
+    torch.manual_seed(0)
+    dtype = torch.bfloat16
+    lens = [1, 15, 16, 17, 100, 333]
+    B = len(lens)
+    max_blocks = 24
+    nblocks = B * max_blocks
+    perm = torch.randperm(nblocks)[: B * max_blocks].reshape(B, max_blocks).to(torch.int32).cuda()
+    kc, vc = _fill_cache(lens, kv_heads, d, nblocks, dtype)
+    ld = (heads + 2 * kv_heads) * d
+    ks, vs, last_q = [], [], []
+    for b, L in enumerate(lens):
+        qkv = _rand(L, ld, dtype=dtype)
+        slots = torch.tensor([int(perm[b, t // 16]) * 16 + t % 16 for t in range(L)], device="cuda", dtype=torch.int32)
+        K.kv_append(qkv, heads * d, (heads + kv_heads) * d, slots, kc, vc, heads, kv_heads, d)
+        ks.append(qkv[:, heads * d:(heads + kv_heads) * d].reshape(L, kv_heads, d).float())
+        vs.append(qkv[:, (heads + kv_heads) * d:].reshape(L, kv_heads, d).float())
+        last_q.append(qkv[-1:].clone())
+    q = torch.cat(last_q)
+    ctx = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    out = K.paged_attention(q, kc, vc, perm, ctx, heads, kv_heads, d, max_ctx=384)
+    rep = heads // kv_heads
+    for b, L in enumerate(lens):
+        qh = q[b, :heads * d].reshape(heads, d).float()
+        kk = ks[b].repeat_interleave(rep, dim=1)
+        vv = vs[b].repeat_interleave(rep, dim=1)
+        s = torch.einsum("hd,lhd->hl", qh, kk) / math.sqrt(d)
+        ref = torch.einsum("hl,lhd->hd", torch.softmax(s, -1), vv).reshape(-1)
+        torch.testing.assert_close(out[b].float(), ref, atol=2e-2, rtol=2e-2)
+    # ragged causal rows: every token of the longest sequence, length = position + 1
+    b, L = B - 1, lens[-1]
+    # rebuild that sequence's queries
+    torch.manual_seed(1)
+    qs = _rand(L, heads * d, dtype=dtype)
+    ctx_t = torch.arange(1, L + 1, device="cuda", dtype=torch.int32)
+    bt_row = torch.full((L,), b, device="cuda", dtype=torch.int32)
+    out2 = K.paged_attention(qs, kc, vc, perm, ctx_t, heads, kv_heads, d, max_ctx=384, bt_row=bt_row)
+    kk = ks[b].repeat_interleave(rep, dim=1)
+    vv = vs[b].repeat_interleave(rep, dim=1)
+    s = torch.einsum("qhd,lhd->hql", qs.reshape(L, heads, d).float(), kk) / math.sqrt(d)
+    s = s + torch.full((L, L), float("-inf"), device="cuda").triu(1)
+    ref2 = torch.einsum("hql,lhd->qhd", torch.softmax(s, -1), vv).reshape(L, -1)
+    torch.testing.assert_close(out2.float(), ref2, atol=2e-2, rtol=2e-2)
+
+
+def test_kv_append_rope(K):
+    from ronn_b200.onnx.registry import rotary
+    heads, kv_heads, d, T = 4, 2, 128, 9
+    ld = (heads + 2 * kv_heads) * d
+    qkv = _rand(T, ld)
+    ref_q = rotary(qkv[:, :heads * d].clone(), torch.arange(T, device="cuda"), 10000.0, heads)
+    ref_k = rotary(qkv[:, heads * d:(heads + kv_heads) * d].clone(), torch.arange(T, device="cuda"), 10000.0, kv_heads)
+    kc = torch.zeros(2, kv_heads, 16, d, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    slots = torch.arange(T, device="cuda", dtype=torch.int32)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    K.kv_append(qkv, heads * d, (heads + kv_heads) * d, slots, kc, vc, heads, kv_heads, d, pos, 10000.0)
+    torch.testing.assert_close(qkv[:, :heads * d].float(), ref_q.float(), atol=3e-2, rtol=2e-2)
+    got_k = kc[0, :, :T, :].permute(1, 0, 2).reshape(T, -1)
+    torch.testing.assert_close(got_k.float(), ref_k.float(), atol=3e-2, rtol=2e-2)
