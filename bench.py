@@ -157,12 +157,15 @@ def main():
     sampler.start()
     t0 = time.perf_counter()
     h2d = d2h = 0
+    host_dev = host_book = 0.0
     for i in range(K):
         starts[i].record()
         out = eng.step()
         ends[i].record()
         h2d += eng.h2d_bytes_last
         d2h += eng.d2h_bytes_last
+        host_dev += eng.host_seconds_last[0]
+        host_book += eng.host_seconds_last[1]
         assert len(out) == args.requests
     sync_all()
     wall = time.perf_counter() - t0
@@ -188,7 +191,10 @@ def main():
                        "mean_context_in_window": round(mean_ctx, 1),
                        "timed_window": "K consecutive decode steps centred on token 128 of 256",
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)",
-                       "prefill_seconds_untimed": round(prefill_s, 3)},
+                       "prefill_seconds_untimed": round(prefill_s, 3),
+                       "pdl": os.environ.get("RONN_PDL", "1") != "0",
+                       "host_ms_per_step": {"schedule_upload_replay_wait": round(host_dev * 1e3 / K, 4),
+                                            "commit_bookkeeping": round(host_book * 1e3 / K, 4)}},
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // K,
                     "d2h_bytes_per_step": d2h // K, "ms_per_step": round(wall * 1e3 / K, 4)},

@@ -27,6 +27,8 @@ template <class T, int D>
 __global__ void kv_append_kernel(T* __restrict__ qkv, long ld, int k_off, int v_off, const int* __restrict__ slots,
                                  const int* __restrict__ positions, T* __restrict__ kcache, T* __restrict__ vcache,
                                  int heads, int kv_heads, float rope_base, int use_rope) {
+  pdl_wait();
+  pdl_trigger();
   const long t = blockIdx.x;
   const int slot = slots[t];
   T* row = qkv + t * ld;
@@ -75,6 +77,7 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, const T* __restrict__
   __shared__ float red[32];
   __shared__ float oacc[NW][D];
 
+  pdl_wait();
   const int row = blockIdx.x, head = blockIdx.y;
   const int L = min(ctx_len[row], ATTN_MAX_CTX);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -157,6 +160,7 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, const T* __restrict__
 #pragma unroll
     for (int i = 0; i < 8; ++i) oacc[warp][chunk * 8 + i] = acc[i];
   }
+  pdl_trigger();               // all K/V traffic of this CTA is done: the successor may start launching
   __syncthreads();
   const float inv = 1.f / denom;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -179,7 +183,7 @@ extern "C" int ronn_kv_append(void* qkv, long ld, int k_off, int v_off, const in
                               float rope_base, int use_rope, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if ((ld & 7) || (k_off & 7) || (v_off & 7)) return -2;
-#define RONN_KVA(T, D) kv_append_kernel<T, D><<<unsigned(tokens), 128, 0, stream>>>((T*)qkv, ld, k_off, v_off, slots, positions, (T*)kcache, (T*)vcache, heads, kv_heads, rope_base, use_rope)
+#define RONN_KVA(T, D) launch(kv_append_kernel<T, D>, dim3(unsigned(tokens)), dim3(128), 0, stream, (T*)qkv, ld, k_off, v_off, slots, positions, (T*)kcache, (T*)vcache, heads, kv_heads, rope_base, use_rope)
   if (dtype == 0 && head_dim == 64) RONN_KVA(__nv_bfloat16, 64);
   else if (dtype == 0 && head_dim == 128) RONN_KVA(__nv_bfloat16, 128);
   else if (dtype == 1 && head_dim == 64) RONN_KVA(__half, 64);
@@ -199,7 +203,7 @@ extern "C" int ronn_paged_attention(const void* q, long ld_q, const void* kcache
   const int padded = (max_ctx + KV_BLOCK - 1) / KV_BLOCK * KV_BLOCK;
   const size_t smem = size_t(padded) * sizeof(float);
   dim3 grid((unsigned)rows, (unsigned)heads);
-#define RONN_PA(T, D) paged_attention_kernel<T, D><<<grid, ATTN_THREADS, smem, stream>>>((const T*)q, ld_q, (const T*)kcache, (const T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale)
+#define RONN_PA(T, D) launch(paged_attention_kernel<T, D>, grid, dim3(ATTN_THREADS), smem, stream, (const T*)q, ld_q, (const T*)kcache, (const T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale)
   if (dtype == 0 && head_dim == 64) RONN_PA(__nv_bfloat16, 64);
   else if (dtype == 0 && head_dim == 128) RONN_PA(__nv_bfloat16, 128);
   else if (dtype == 1 && head_dim == 64) RONN_PA(__half, 64);

@@ -7,6 +7,32 @@
 
 namespace ronn {
 
+// ---- programmatic dependent launch ------------------------------------------------------------------
+// A kernel launched through ronn::launch may start while its predecessor in the stream is still draining.
+// pdl_wait() blocks until the predecessor has completed and its writes are visible (a no-op for a normal
+// launch); everything a kernel does before it must not touch data the predecessor produces or reads.
+// pdl_trigger() lets the successor begin launching once every CTA has called it or exited.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool pdl_enabled();          // defined in elementwise.cu; RONN_PDL=0 disables
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 template <class T> struct Cvt;
 template <> struct Cvt<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }

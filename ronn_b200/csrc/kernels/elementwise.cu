@@ -7,11 +7,21 @@
 // crates/ronn-providers/src/gpu/cuda_kernels.rs:537-562), embedding = gather on axis 0
 // (crates/ronn-onnx/src/ops/tensor_ops.rs:463-489), argmax (crates/ronn-core/src/ops/reduction.rs:282-304).
 // All kernels move 16 bytes per thread per access and keep a row in registers between passes.
+#include <cstdlib>
 #include "common.cuh"
 
 namespace ronn {
 
 constexpr int NORM_MAX_CHUNKS = 4;     // a thread keeps up to 4 x 8 values of its row
+
+static int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("RONN_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
 
 // y = norm(x [+ res]) * gamma [+ beta];  if sum_out != null the pre-norm sum (x + res) is also written.
 // RMS = true: y = v * rsqrt(mean(v^2) + eps) * gamma.
@@ -20,6 +30,8 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, 
                             const T* __restrict__ beta, T* __restrict__ y, T* __restrict__ sum_out, int H,
                             long ld_x, long ld_res, long ld_y, float eps) {
   __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
   const long row = blockIdx.x;
   const T* xr = x + row * ld_x;
   const T* rr = res ? res + row * ld_res : nullptr;
@@ -78,6 +90,103 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, 
         o[i] = t;
       }
       *reinterpret_cast<Vec8*>(y + row * ld_y + ch * 8) = pack8<T>(o);
+    }
+  }
+}
+
+// Split-K finalize: v = sum_s ws[s][row][:] + bias + residual; optional activation; writes v as `sum_out`
+// and, when NORM != 0, norm(v) * gamma (+ beta) as `y`.  NORM: 0 none, 1 LayerNorm, 2 RMSNorm.
+// ws: [S, rows, N] fp32.  N % 8 == 0, N <= 8 * NORM_MAX_CHUNKS * blockDim.x.
+template <class T, int NORM>
+__global__ void splitk_finalize_kernel(const float* __restrict__ ws, int S, const T* __restrict__ bias,
+                                       const T* __restrict__ residual, T* __restrict__ sum_out,
+                                       const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+                                       long rows, int N, float eps, int act) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const long row = blockIdx.x;
+  const int nchunk = N >> 3;
+  const long slice = rows * long(N);
+  float v[NORM_MAX_CHUNKS][8];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+      const float* p = ws + row * N + ch * 8;
+      float4 a0 = *reinterpret_cast<const float4*>(p), a1 = *reinterpret_cast<const float4*>(p + 4);
+      for (int k = 1; k < S; ++k) {
+        const float4 b0 = *reinterpret_cast<const float4*>(p + k * slice);
+        const float4 b1 = *reinterpret_cast<const float4*>(p + k * slice + 4);
+        a0.x += b0.x; a0.y += b0.y; a0.z += b0.z; a0.w += b0.w;
+        a1.x += b1.x; a1.y += b1.y; a1.z += b1.z; a1.w += b1.w;
+      }
+      v[c][0] = a0.x; v[c][1] = a0.y; v[c][2] = a0.z; v[c][3] = a0.w;
+      v[c][4] = a1.x; v[c][5] = a1.y; v[c][6] = a1.z; v[c][7] = a1.w;
+      if (bias) {
+        float b[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(bias + ch * 8), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += b[i];
+      }
+      if (act == 1) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] = fmaxf(v[c][i], 0.f);
+      } else if (act == 2) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] = gelu_tanh_f(v[c][i]);
+      }
+      if (residual) {
+        float r[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(residual + row * N + ch * 8), r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] += r[i];
+      }
+      if (sum_out) {
+        const Vec8 pk = pack8<T>(v[c]);
+        *reinterpret_cast<Vec8*>(sum_out + row * N + ch * 8) = pk;
+        if (NORM != 0) unpack8<T>(pk, v[c]);      // normalise exactly what the residual stream stores
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += NORM == 2 ? v[c][i] * v[c][i] : v[c][i];
+    }
+  }
+  if (NORM == 0) return;
+  float mean = 0.f, inv;
+  if (NORM == 2) {
+    inv = rsqrtf(block_sum(s, scratch) / float(N) + eps);
+  } else {
+    mean = block_sum(s, scratch) / float(N);
+    float q = 0.f;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int ch = threadIdx.x + c * blockDim.x;
+      if (ch < nchunk) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float d = v[c][i] - mean;
+          q += d * d;
+        }
+      }
+    }
+    inv = rsqrtf(block_sum(q, scratch) / float(N) + eps);
+  }
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+      float g[8], b[8], o[8];
+      if (gamma) unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + ch * 8), g);
+      if (beta) unpack8<T>(*reinterpret_cast<const Vec8*>(beta + ch * 8), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = (v[c][i] - mean) * inv;
+        if (gamma) t *= g[i];
+        if (beta) t += b[i];
+        o[i] = t;
+      }
+      *reinterpret_cast<Vec8*>(y + row * N + ch * 8) = pack8<T>(o);
     }
   }
 }
@@ -163,6 +272,8 @@ __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, 
 // SwiGLU on a fused [rows, 2*F] gate|up projection: y[r, f] = silu(x[r, f]) * x[r, F + f]
 template <class T>
 __global__ void swiglu_fused_kernel(const T* __restrict__ x, T* __restrict__ y, int F, long rows) {
+  pdl_wait();
+  pdl_trigger();
   const int f8 = F >> 3;
   const long total = rows * f8;
   for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
@@ -182,6 +293,8 @@ template <class T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ pos, const T* __restrict__ table,
                                  const T* __restrict__ pos_table, T* __restrict__ out, int H, int vocab, int max_pos,
                                  long ld_out) {
+  pdl_wait();
+  pdl_trigger();
   const long t = blockIdx.x;
   const int id = ids[t];
   const int p = pos ? pos[t] : 0;
@@ -210,6 +323,8 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
                               long ld, int col_offset) {
   __shared__ float smax[32];
   __shared__ int sidx[32];
+  pdl_wait();
+  pdl_trigger();
   const T* xr = x + long(blockIdx.x) * ld;
   float m = -INFINITY;
   int mi = 0x7fffffff;
@@ -245,6 +360,7 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
 // Combine per-shard (max, idx) pairs: vals/idx are [shards, rows]; picks the largest value, lowest index on ties.
 __global__ void argmax_combine_kernel(const float* __restrict__ vals, const int* __restrict__ idx, int* __restrict__ out,
                                       int shards, int rows) {
+  pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float m = -INFINITY;
@@ -293,12 +409,10 @@ extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, cons
   if (threads < 32) threads = 32;
   if (threads > 1024) threads = 1024;
   RONN_BY_DTYPE(dtype, {
-    if (rms) norm_kernel<T, true><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (const T*)res, (const T*)gamma,
-                                                                          (const T*)beta, (T*)y, (T*)sum_out, H, ld_x,
-                                                                          ld_res, ld_y, eps);
-    else norm_kernel<T, false><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (const T*)res, (const T*)gamma,
-                                                                       (const T*)beta, (T*)y, (T*)sum_out, H, ld_x,
-                                                                       ld_res, ld_y, eps);
+    if (rms) launch(norm_kernel<T, true>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const T*)x, (const T*)res,
+                    (const T*)gamma, (const T*)beta, (T*)y, (T*)sum_out, H, ld_x, ld_res, ld_y, eps);
+    else launch(norm_kernel<T, false>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const T*)x, (const T*)res,
+                (const T*)gamma, (const T*)beta, (T*)y, (T*)sum_out, H, ld_x, ld_res, ld_y, eps);
   });
   return check_launch();
 }
@@ -329,7 +443,7 @@ extern "C" int ronn_binary(const void* a, const void* b, void* y, long n, int op
 extern "C" int ronn_swiglu_fused(const void* x, void* y, long rows, int F, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (F & 7) return -2;
-  RONN_BY_DTYPE(dtype, (swiglu_fused_kernel<T><<<grid_for(rows * (F >> 3), 256), 256, 0, stream>>>((const T*)x, (T*)y, F, rows)));
+  RONN_BY_DTYPE(dtype, launch(swiglu_fused_kernel<T>, dim3(grid_for(rows * (F >> 3), 256)), dim3(256), 0, stream, (const T*)x, (T*)y, F, rows));
   return check_launch();
 }
 
@@ -338,9 +452,8 @@ extern "C" int ronn_embedding(const int* ids, const int* pos, const void* table,
   if (tokens <= 0) return 0;
   if ((H & 7) || (ld_out & 7)) return -2;
   int threads = (H >> 3) >= 128 ? 128 : 64;
-  RONN_BY_DTYPE(dtype, (embedding_kernel<T><<<unsigned(tokens), threads, 0, stream>>>(ids, pos, (const T*)table,
-                                                                                     (const T*)pos_table, (T*)out, H,
-                                                                                     vocab, max_pos, ld_out)));
+  RONN_BY_DTYPE(dtype, launch(embedding_kernel<T>, dim3(unsigned(tokens)), dim3(threads), 0, stream, ids, pos, (const T*)table,
+                                     (const T*)pos_table, (T*)out, H, vocab, max_pos, ld_out));
   return check_launch();
 }
 
@@ -349,15 +462,15 @@ extern "C" int ronn_argmax(const void* x, int* idx_out, float* max_out, long row
                            int dtype, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   const int threads = cols >= 8192 ? 1024 : 256;
-  if (dtype == 2) argmax_kernel<float><<<unsigned(rows), threads, 0, stream>>>((const float*)x, idx_out, max_out, cols, ld, col_offset);
-  else RONN_BY_DTYPE(dtype, (argmax_kernel<T><<<unsigned(rows), threads, 0, stream>>>((const T*)x, idx_out, max_out, cols, ld, col_offset)));
+  if (dtype == 2) launch(argmax_kernel<float>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const float*)x, idx_out, max_out, cols, ld, col_offset);
+  else RONN_BY_DTYPE(dtype, launch(argmax_kernel<T>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const T*)x, idx_out, max_out, cols, ld, col_offset));
   return check_launch();
 }
 
 extern "C" int ronn_argmax_combine(const float* vals, const int* idx, int* out, int shards, int rows,
                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_combine_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(vals, idx, out, shards, rows);
+  launch(argmax_combine_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, vals, idx, out, shards, rows);
   return check_launch();
 }
 
@@ -376,3 +489,26 @@ extern "C" int ronn_cast(const void* x, void* y, long n, int from, int to, cudaS
 #undef RONN_CAST
   return -1;
 }
+
+// norm: 0 none (sum_out only), 1 LayerNorm, 2 RMSNorm.  act: 0 none, 1 relu, 2 gelu (applied before the residual).
+extern "C" int ronn_splitk_finalize(const float* ws, int S, const void* bias, const void* residual, void* sum_out,
+                                    const void* gamma, const void* beta, void* y, long rows, int N, float eps,
+                                    int act, int norm, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((N & 7) || N > 1024 * 8 * NORM_MAX_CHUNKS || S < 1) return -2;
+  int threads = ((N >> 3) + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS;
+  threads = ((threads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 1024) threads = 1024;
+#define RONN_FIN(NORM_) launch(splitk_finalize_kernel<T, NORM_>, dim3(unsigned(rows)), dim3(threads), 0, stream, ws, S, (const T*)bias, (const T*)residual, (T*)sum_out, (const T*)gamma, (const T*)beta, (T*)y, rows, N, eps, act)
+  RONN_BY_DTYPE(dtype, {
+    if (norm == 0) RONN_FIN(0);
+    else if (norm == 1) RONN_FIN(1);
+    else RONN_FIN(2);
+  });
+#undef RONN_FIN
+  return check_launch();
+}
+
+// 1 enables, 0 disables programmatic dependent launch for every kernel of the library.
+extern "C" void ronn_set_pdl(int on) { ronn::g_pdl = on ? 1 : 0; }

@@ -93,7 +93,7 @@ struct DenseEpiCall {
 };
 
 template <int BN, int STAGES, class T>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   DenseEpilogue epi, int K, uint32_t idesc, uint32_t* status) {
   extern __shared__ uint8_t dyn_smem[];
@@ -103,13 +103,21 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   epi.n0 = n0;
   TmaALoader al{&map_a, m0};
   DenseEpiCall<T> call{epi};
-  const int num_kb = (K + 63) / 64;
-  gemm_tile<BN, STAGES, 0, TmaALoader, DenseEpiCall<T>>(dyn_smem, al, &map_b, n0, num_kb, 64, idesc, status, call);
+  int num_kb = (K + 63) / 64;
+  int kb0 = 0;
+  if (gridDim.z > 1) {
+    // split-K: this CTA owns k-blocks [kb0, kb0 + num_kb) and writes raw fp32 partial sums to slice z of the workspace
+    const int per = (num_kb + gridDim.z - 1) / gridDim.z;
+    kb0 = blockIdx.z * per;
+    num_kb = min(per, num_kb - kb0);
+    call.e.C = reinterpret_cast<float*>(epi.C) + size_t(blockIdx.z) * size_t(epi.M) * size_t(epi.ldc);
+  }
+  gemm_tile<BN, STAGES, 0, TmaALoader, DenseEpiCall<T>>(dyn_smem, al, &map_b, n0, num_kb, 64, idesc, status, call, kb0);
 }
 
 template <int BN, int STAGES, class T>
 static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilogue epi, int M, int N, int K,
-                        int is_bf16, uint32_t* status, cudaStream_t stream) {
+                        int is_bf16, uint32_t* status, cudaStream_t stream, int splitk = 1) {
   using L = GemmSmemLayout<BN, STAGES>;
   auto kern = gemm_dense_kernel<BN, STAGES, T>;
   static bool configured = false;
@@ -117,10 +125,10 @@ static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilo
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM);
+  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM, splitk);
   uint32_t idesc = umma_idesc(GEMM_BM, BN, is_bf16 ? 1u : 0u, 1u);
-  kern<<<grid, GEMM_THREADS, L::DYN_SMEM, stream>>>(ma, mb, epi, K, idesc, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  cudaError_t err = launch(kern, grid, dim3(GEMM_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, epi, K, idesc, status);
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
 int pick_bn(int M, int N) {
@@ -160,9 +168,43 @@ extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias
             : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream)
   switch (bn) {
     case 256: RONN_DISPATCH(256, 4);
-    case 128: RONN_DISPATCH(128, 6);
-    case 64: RONN_DISPATCH(64, 8);
-    case 32: RONN_DISPATCH(32, 8);
+    case 128: RONN_DISPATCH(128, 3);
+    case 64: RONN_DISPATCH(64, 4);
+    case 32: RONN_DISPATCH(32, 5);
+    default: return -3;
+  }
+#undef RONN_DISPATCH
+}
+
+// Split-K variant for skinny problems (decode: M <= 256).  Each of `splitk` K-slices writes an fp32 partial
+// [M, N] to workspace slice z; ronn_splitk_finalize sums the slices and applies bias / residual / norm.
+// The effective split count (every slice non-empty) is returned through *splitk_out.
+extern "C" int ronn_gemm_splitk(const void* A, const void* W, float* workspace, int M, int N, int K, int lda, int ldw,
+                                int dtype, int bn, int splitk, int* splitk_out, uint32_t* status,
+                                cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || splitk < 1) return -1;
+  if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 3)) return -2;
+  const int num_kb = (K + 63) / 64;
+  if (splitk > num_kb) splitk = num_kb;
+  const int per = (num_kb + splitk - 1) / splitk;
+  splitk = (num_kb + per - 1) / per;
+  if (splitk_out) *splitk_out = splitk;
+  if (bn == 0) bn = N >= 128 ? 128 : (N >= 64 ? 64 : 32);
+  CUtensorMap ma, mb;
+  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), GEMM_BM, 64, 2);
+  if (rc) return rc - 20;
+  rc = make_tmap_2d(&mb, W, uint64_t(N), uint64_t(K), uint64_t(ldw), uint32_t(bn), 64, 2);
+  if (rc) return rc - 30;
+  DenseEpilogue e{workspace, nullptr, nullptr, M, N, N, 0, 0, 0, 1};
+  const int bf = dtype == 0;
+#define RONN_DISPATCH(BN_, ST_)                                                                          \
+  return bf ? launch_dense<BN_, ST_, __nv_bfloat16>(ma, mb, e, M, N, K, 1, status, stream, splitk)       \
+            : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream, splitk)
+  switch (bn) {
+    case 256: RONN_DISPATCH(256, 4);
+    case 128: RONN_DISPATCH(128, 3);
+    case 64: RONN_DISPATCH(64, 4);
+    case 32: RONN_DISPATCH(32, 5);
     default: return -3;
   }
 #undef RONN_DISPATCH

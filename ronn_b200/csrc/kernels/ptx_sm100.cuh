@@ -24,7 +24,8 @@ enum : uint32_t {
   STATUS_WAIT_EPI = 5,       // MMA issuer never saw the epilogue drain TMEM
 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait (flag waits on %globaltimer)
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;        // about 2 s of SM cycles per mbarrier wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -62,18 +63,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` lives in shared memory and is shared by every wait of the CTA.
-// Returns false when the wait was abandoned.
+// Returns false when the wait was abandoned.  The limit is counted on the SM cycle counter (cheap to read)
+// and checked every 32 polls; each poll is a try_wait, which itself suspends the thread for a short
+// hardware-defined time, so the loop neither floods the issue slots nor delays the wake-up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t code) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = globaltimer_ns();
+  const long long t0 = clock64();
+  uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-      *abort_flag = 1;
-      if (status) atomicCAS(status, 0u, code);
-      return false;
+    if ((++polls & 31u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0u, code);
+        return false;
+      }
     }
   }
 }

@@ -11,6 +11,7 @@
 // chunk of every row.  A-tile loading can be replaced (policy ALoader) so that peers' shards
 // or gathered activations feed the same mainloop.
 #pragma once
+#include "common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace ronn {
@@ -69,7 +70,7 @@ struct TmaALoader {
 template <int BN, int STAGES, int KIND, class ALoader, class Epilogue>
 __device__ __forceinline__ void gemm_tile(uint8_t* dyn_smem, const ALoader& aload, const CUtensorMap* map_b, int n0,
                                           int num_kb, int k_elems_per_block, uint32_t idesc, uint32_t* status,
-                                          Epilogue& epi) {
+                                          Epilogue& epi, int kb0 = 0) {
   using L = GemmSmemLayout<BN, STAGES>;
   GemmCtx c = gemm_ctx<BN, STAGES>(dyn_smem);
   const int warp = threadIdx.x >> 5;
@@ -98,18 +99,30 @@ __device__ __forceinline__ void gemm_tile(uint8_t* dyn_smem, const ALoader& aloa
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+      // Weights (B) never depend on the previous kernel in the stream: their first stages are requested
+      // before the programmatic-dependency wait, the activations (A) after it.
+      const int pre = num_kb < STAGES ? num_kb : STAGES;
+      for (int kb = 0; kb < pre; ++kb) {
+        uint8_t* sa = c.tiles + kb * L::STAGE_BYTES;
+        mbar_expect_tx(&c.full[kb], L::STAGE_BYTES);
+        tma_load_2d(sa + L::A_BYTES, map_b, &c.full[kb], (kb0 + kb) * k_elems_per_block, n0);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < pre; ++kb)
+        aload.load(c.tiles + kb * L::STAGE_BYTES, &c.full[kb], (kb0 + kb) * k_elems_per_block);
+      for (int kb = pre; kb < num_kb; ++kb) {
         const int s = kb % STAGES;
         const uint32_t parity = ((kb / STAGES) & 1) ^ 1;
         if (!mbar_wait(&c.empty[s], parity, c.abort, status, STATUS_WAIT_SLOT)) break;
         uint8_t* sa = c.tiles + s * L::STAGE_BYTES;
         uint8_t* sb = sa + L::A_BYTES;
         mbar_expect_tx(&c.full[s], L::STAGE_BYTES);
-        aload.load(sa, &c.full[s], kb * k_elems_per_block);
-        tma_load_2d(sb, map_b, &c.full[s], kb * k_elems_per_block, n0);
+        aload.load(sa, &c.full[s], (kb0 + kb) * k_elems_per_block);
+        tma_load_2d(sb, map_b, &c.full[s], (kb0 + kb) * k_elems_per_block, n0);
       }
     }
     __syncwarp();
+    pdl_trigger();
   } else if (warp == 1) {
     if (lane == 0) {
       for (int kb = 0; kb < num_kb; ++kb) {
@@ -131,10 +144,13 @@ __device__ __forceinline__ void gemm_tile(uint8_t* dyn_smem, const ALoader& aloa
       umma_commit(c.accum);
     }
     __syncwarp();
+    pdl_trigger();
   } else {
     const int q = warp & 3;                    // TMEM lane quarter this warp may read
+    pdl_wait();                                // the epilogue reads residuals and writes buffers the predecessor may use
     bool ok = mbar_wait(c.accum, 0, c.abort, status, STATUS_WAIT_ACCUM);
     ok = __all_sync(0xffffffffu, ok);
+    pdl_trigger();
     tc_fence_after_sync();
     if (ok) {
       const int row = q * 32 + lane;

@@ -16,6 +16,8 @@ def declare(lib):
         fn.argtypes = args
 
     sig("ronn_gemm", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, V, V])
+    sig("ronn_gemm_splitk", [V, V, V, I, I, I, I, I, I, I, I, V, V, V])
+    sig("ronn_splitk_finalize", [V, I, V, V, V, V, V, V, L, I, F, I, I, I, V])
     sig("ronn_norm", [V, V, V, V, V, V, L, I, L, L, L, F, I, I, V])
     sig("ronn_softmax", [V, V, L, I, I, V])
     sig("ronn_unary", [V, V, L, I, I, V])

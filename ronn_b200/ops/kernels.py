@@ -225,3 +225,50 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                                                head_dim, int(max_ctx), float(sc), _DT[q.dtype], _stream()),
            "paged_attention")
     return out
+
+
+_WORKSPACES = {}
+
+
+def splitk_workspace(device, nfloats: int) -> torch.Tensor:
+    """Per-device fp32 scratch for split-K partial sums, grown on demand and reused by every call."""
+    dev = torch.device(device)
+    w = _WORKSPACES.get(dev)
+    if w is None or w.numel() < nfloats:
+        w = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=dev)
+        _WORKSPACES[dev] = w
+    return w
+
+
+def gemm_splitk(a: torch.Tensor, w_nk: torch.Tensor, splitk: int, bn: int = 0,
+                workspace: Optional[torch.Tensor] = None):
+    """Partial products of a[M,K] @ w_nk[N,K]^T over `splitk` K-slices as fp32 [S, M, N] in the workspace.
+    Returns (workspace, S) with S the effective number of slices."""
+    import ctypes as C
+    M, K = a.shape
+    N = w_nk.shape[0]
+    if workspace is None:
+        workspace = splitk_workspace(a.device, splitk * M * N)
+    if workspace.numel() < splitk * M * N:
+        raise KernelError("split-K workspace too small")
+    s_out = C.c_int(0)
+    rc = _native.cuda().ronn_gemm_splitk(a.data_ptr(), w_nk.data_ptr(), workspace.data_ptr(), M, N, K, a.stride(0),
+                                         w_nk.stride(0), _DT[a.dtype], bn, splitk, C.addressof(s_out),
+                                         status_word(a.device).data_ptr(), _stream())
+    _check(rc, "gemm_splitk")
+    return workspace, s_out.value
+
+
+def splitk_finalize(ws: torch.Tensor, S: int, rows: int, N: int, dtype: torch.dtype, bias=None, residual=None,
+                    gamma=None, beta=None, eps: float = 1e-5, activation: str = "", norm: str = "",
+                    want_sum: bool = True):
+    """sum = sum_s ws[s] + bias (+act) + residual ; y = norm(sum).  Returns (sum or None, y or None)."""
+    nm = {"": 0, "none": 0, "layernorm": 1, "rmsnorm": 2}[norm]
+    dev = ws.device
+    sum_out = torch.empty((rows, N), dtype=dtype, device=dev) if (want_sum or nm == 0) else None
+    y = torch.empty((rows, N), dtype=dtype, device=dev) if nm else None
+    rc = _native.cuda().ronn_splitk_finalize(ws.data_ptr(), S, _ptr(bias), _ptr(residual), _ptr(sum_out), _ptr(gamma),
+                                             _ptr(beta), _ptr(y), rows, N, float(eps), _ACT[activation], nm,
+                                             _DT[dtype], _stream())
+    _check(rc, "splitk_finalize")
+    return sum_out, y

@@ -1,0 +1,225 @@
+"""Kernel micro-benchmarks with CUDA-event timing and roofline accounting.
+
+    python -m ronn_b200.ops.microbench gemm --m 256 --n 1024 --k 1024
+    python -m ronn_b200.ops.microbench attention --batch 256 --ctx 416 --heads 16 --dim 64
+    python -m ronn_b200.ops.microbench decode-shapes          # every GEMM / attention shape of a GPT-2-medium decode step
+
+Timing: warm-up, then ``iters`` launches between two events on the launching stream with an L2 flush
+(a 256 MB write) before each timed launch unless ``--no-flush``; reports the median.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import kernels as K
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    except Exception:
+        return 6650.0, 1590.0, "fallback"
+
+
+_FLUSH = None
+
+
+def time_kernel(fn, iters=20, warmup=5, flush=True):
+    global _FLUSH
+    if flush and _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _FLUSH.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def time_graph(make_call, variants: int, reps: int = 40, iters: int = 5):
+    """Median time per launch of `reps` back-to-back launches replayed from a CUDA graph.  `make_call(i)` launches
+    the kernel on the i-th of `variants` operand sets (rotating operand sets larger than L2 keep DRAM traffic real)."""
+    for i in range(min(variants, 3)):
+        make_call(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for r in range(reps):
+            make_call(r % variants)
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3 / reps)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def sweep_decode_gemm(m=256):
+    """Back-to-back (graph) timing of the decode GEMM shapes over tile width and split-K, weights rotating through
+    more than L2 so every launch streams its weights from HBM."""
+    hbm, tf, src = _peaks()
+    out = []
+    for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]:
+        nvar = max(2, int(300e6 // (n * k * 2)))
+        ws = [(torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(nvar)]
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        bias = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+        roof = max(2.0 * m * n * k / (tf * 1e12), 2.0 * (m * k + n * k + m * n) / (hbm * 1e9)) * 1e6
+        for bn in (32, 64, 128):
+            us = time_graph(lambda i: K.gemm(a, ws[i], bias, out=o, bn=bn), nvar)
+            out.append({"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn, "splitk": 1, "us": round(us, 2),
+                        "roofline_us": round(roof, 2)})
+        for bn in (64, 128, 256):
+            if bn > n:
+                continue
+            for sk in (2, 4, 8, 16):
+                wsp = K.splitk_workspace("cuda", sk * m * n)
+
+                def call(i, bn=bn, sk=sk):
+                    w_, S = K.gemm_splitk(a, ws[i], sk, bn, wsp)
+                    K.splitk_finalize(w_, S, m, n, torch.bfloat16, bias=bias, residual=o, gamma=bias, beta=bias,
+                                      norm="layernorm")
+                us = time_graph(call, nvar)
+                us_g = time_graph(lambda i, bn=bn, sk=sk: K.gemm_splitk(a, ws[i], sk, bn, wsp), nvar)
+                out.append({"kernel": "gemm_splitk+finalize_ln", "m": m, "n": n, "k": k, "bn": bn, "splitk": sk,
+                            "us": round(us, 2), "gemm_only_us": round(us_g, 2), "roofline_us": round(roof, 2)})
+    x = torch.randn(m, 1024, device="cuda").to(torch.bfloat16)
+    g_ = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    out.append({"kernel": "layernorm", "rows": m, "h": 1024, "us": round(time_graph(lambda i: K.layernorm(x, g_, g_), 1), 2)})
+    return out
+
+
+def sweep_attention():
+    out = []
+    hbm, _, src = _peaks()
+    for batch, ctx in [(256, 416), (256, 128), (256, 768), (64, 416)]:
+        heads, dim = 16, 64
+        nb_seq = (ctx + 15) // 16
+        nblocks = batch * nb_seq
+        kc = torch.randn(nblocks, heads, 16, dim, device="cuda").to(torch.bfloat16)
+        vc = torch.randn(nblocks, heads, 16, dim, device="cuda").to(torch.bfloat16)
+        bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
+        q = torch.randn(batch, heads * dim, device="cuda").to(torch.bfloat16)
+        lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+        o = torch.empty(batch, heads * dim, device="cuda", dtype=torch.bfloat16)
+        us = time_graph(lambda i: K.paged_attention(q, kc, vc, bt, lens, heads, heads, dim, max_ctx=1024, out=o), 1, reps=10)
+        byts = 2.0 * batch * ctx * heads * dim * 2
+        out.append({"kernel": "paged_attention", "batch": batch, "ctx": ctx, "us": round(us, 2),
+                    "gbs": round(byts / us / 1e3, 1), "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)})
+    return out
+
+
+def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20):
+    a = torch.randn(m, k, device="cuda").to(dtype)
+    w = (torch.randn(n, k, device="cuda") * 0.05).to(dtype)
+    out = torch.empty(m, n, device="cuda", dtype=dtype)
+    us = time_kernel(lambda: K.gemm(a, w, activation=act, out=out, bn=bn), iters=iters, flush=flush)
+    K.check_status()
+    hbm, tf, src = _peaks()
+    flops = 2.0 * m * n * k
+    byts = 2.0 * (m * k + n * k + m * n)
+    t_roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e6
+    return {"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn, "us": round(us, 2),
+            "tflops": round(flops / us / 1e6, 1), "gbs": round(byts / us / 1e3, 1),
+            "roofline_us": round(t_roof, 2), "frac_of_" + src: round(t_roof / us, 3)}
+
+
+def bench_attention(batch, ctx, heads, dim, kv_heads=None, dtype=torch.bfloat16, flush=True, iters=20):
+    kv_heads = kv_heads or heads
+    nb_seq = (ctx + 15) // 16
+    nblocks = batch * nb_seq
+    kc = torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype)
+    vc = torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype)
+    bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
+    q = torch.randn(batch, heads * dim, device="cuda").to(dtype)
+    lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+    out = torch.empty(batch, heads * dim, device="cuda", dtype=dtype)
+    us = time_kernel(lambda: K.paged_attention(q, kc, vc, bt, lens, heads, kv_heads, dim, max_ctx=max(ctx, 16), out=out),
+                     iters=iters, flush=flush)
+    hbm, tf, src = _peaks()
+    byts = 2.0 * batch * ctx * kv_heads * dim * 2
+    t_roof = byts / (hbm * 1e9) * 1e6
+    return {"kernel": "paged_attention", "batch": batch, "ctx": ctx, "heads": heads, "dim": dim, "us": round(us, 2),
+            "gbs": round(byts / us / 1e3, 1), "roofline_us": round(t_roof, 2), "frac_of_" + src: round(t_roof / us, 3)}
+
+
+def bench_norm(rows, h, dtype=torch.bfloat16, flush=True):
+    x = torch.randn(rows, h, device="cuda").to(dtype)
+    g = torch.ones(h, device="cuda", dtype=dtype)
+    b = torch.zeros(h, device="cuda", dtype=dtype)
+    us = time_kernel(lambda: K.layernorm(x, g, b), flush=flush)
+    hbm, _, src = _peaks()
+    byts = 2.0 * rows * h * 2
+    return {"kernel": "layernorm", "rows": rows, "h": h, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1),
+            "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)}
+
+
+def decode_shapes(batch=256, ctx=416):
+    out = []
+    for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (50257 // 8 * 8 + 8, 1024)]:
+        out.append(bench_gemm(batch, n, k))
+    out.append(bench_attention(batch, ctx, 16, 64))
+    out.append(bench_norm(batch, 1024))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-attention"])
+    ap.add_argument("--m", type=int, default=256)
+    ap.add_argument("--n", type=int, default=1024)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=416)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--dim", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    fl = not a.no_flush
+    if a.what == "gemm":
+        res = [bench_gemm(a.m, a.n, a.k, bn=a.bn, flush=fl, iters=a.iters)]
+    elif a.what == "attention":
+        res = [bench_attention(a.batch, a.ctx, a.heads, a.dim, flush=fl, iters=a.iters)]
+    elif a.what == "norm":
+        res = [bench_norm(a.batch, a.n, flush=fl)]
+    elif a.what == "sweep-decode-gemm":
+        res = sweep_decode_gemm(a.m)
+    elif a.what == "sweep-attention":
+        res = sweep_attention()
+    elif a.what == "prefill-shapes":
+        res = [bench_gemm(8192, n, k) for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]]
+        res += [bench_gemm(8192, 8192, 8192, iters=5)]
+    else:
+        res = decode_shapes(a.batch, a.ctx)
+    for r in res:
+        print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()

@@ -23,6 +23,25 @@ from .request import FinishReason, Priority, Request, RequestState, SamplingPara
 from .sampler import sample_tokens
 from .scheduler import PLAN_DECODE, PLAN_NONE, PLAN_PREFILL, HostBatchBuffers, Scheduler
 
+class StepOutput:
+    """What one iteration produced: ids of the requests that got a token, the tokens, and finish codes
+    (0 running, 1 eos, 2 max_tokens).  Behaves like a sequence of ``Request`` objects."""
+    __slots__ = ("_engine", "req_ids", "tokens", "finished")
+
+    def __init__(self, engine, req_ids, tokens, finished):
+        self._engine, self.req_ids, self.tokens, self.finished = engine, req_ids, tokens, finished
+
+    def __len__(self):
+        return len(self.req_ids)
+
+    def __iter__(self):
+        reqs = self._engine.requests
+        return (reqs[int(i)] for i in self.req_ids)
+
+    def __getitem__(self, k):
+        return self._engine.requests[int(self.req_ids[k])]
+
+
 _BUCKETS = [1, 2, 4, 8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024]
 
 
@@ -62,6 +81,9 @@ class LLMEngine:
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
         self.on_token: Optional[Callable[[Request, int], None]] = None
+        self._non_greedy = 0
+        self._watch_count = 0
+        self.host_seconds_last = (0.0, 0.0)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Iterable[int], params: Optional[SamplingParams] = None,
@@ -76,7 +98,13 @@ class LLMEngine:
         rid = self._next_id if request_id is None else int(request_id)
         self._next_id = max(self._next_id, rid) + 1
         self.sched.add(rid, toks, params.max_new_tokens, int(priority))
-        self.requests[rid] = Request(rid, toks, params, priority)
+        r = Request(rid, toks, params, priority)
+        r._token_source = self.sched.tokens
+        self.requests[rid] = r
+        if params.temperature > 0:
+            self._non_greedy += 1
+        if params.stop_sequences:
+            self._watch_count += 1
         self.metrics.requests_added += 1
         return rid
 
@@ -84,10 +112,17 @@ class LLMEngine:
         r = self.requests.get(request_id)
         if r is None or r.finished:
             return False
+        r._freeze()
         self.sched.cancel(request_id)
+        if r.params.temperature > 0:
+            self._non_greedy -= 1
         r.finish_reason = FinishReason.CANCELLED
         r.finished_at = time.perf_counter()
         return True
+
+    @property
+    def _watch(self) -> bool:
+        return self._watch_count > 0 or self.on_token is not None
 
     def has_unfinished(self) -> bool:
         return self.sched.num_waiting + self.sched.num_running > 0
@@ -114,11 +149,11 @@ class LLMEngine:
         self.h2d_bytes_last = used * 4
 
     # ------------------------------------------------------------------ one iteration
-    def step(self) -> List[Request]:
+    def step(self) -> "StepOutput":
         """Run one scheduling iteration.  Returns the requests that produced a token in it."""
         kind = self.sched.schedule()
         if kind == PLAN_NONE:
-            return []
+            return StepOutput(self, np.zeros(0, np.int64), np.zeros(0, np.int32), np.zeros(0, np.int32))
         t0 = time.perf_counter()
         sb = self.sched.fill(self.host, kind)
         n_items, n_tokens = sb.n_items, sb.n_tokens
@@ -130,7 +165,7 @@ class LLMEngine:
         samples_mask = si[:n_items] >= 0
         np.maximum(si[:n_items], 0, out=si[:n_items])
         try:
-            if decode and self.use_graph:
+            if decode and self.use_graph and self._non_greedy == 0:
                 toks = self._decode_graph(n_items)
             else:
                 self._upload(n_tokens, n_items)
@@ -145,35 +180,47 @@ class LLMEngine:
             self.sched.abort_step()
             self.metrics.failed_steps += 1
             raise
-        sampled = self.sampled_host[:n_items].numpy()
+        t_dev = time.perf_counter()
+        sampled = self.sampled_host[:n_items].numpy().copy()
+        req_ids = sb.req_ids.copy()
         fin = self.sched.commit(sampled, self.cfg.eos_token_id)
         now = time.perf_counter()
-        out = []
-        for i in range(n_items):
-            if not samples_mask[i]:
-                continue
-            r = self.requests[int(sb.req_ids[i])]
-            tok = int(sampled[i])
-            r.output_tokens.append(tok)
-            if r.first_token_at is None:
-                r.first_token_at = now
-                self.metrics.observe_ttft(now - r.created_at)
-            if fin[i]:
-                r.finish_reason = FinishReason.EOS_TOKEN if fin[i] == 1 else FinishReason.MAX_TOKENS
-                r.finished_at = now
-                self.metrics.requests_finished += 1
-            elif r.params.stop_sequences and self._hit_stop(r):
-                self.sched.cancel(r.id)
-                r.finish_reason = FinishReason.STOP_SEQUENCE
-                r.finished_at = now
-                self.metrics.requests_finished += 1
-            if self.on_token is not None:
-                self.on_token(r, tok)
-            out.append(r)
+        if not decode:                                   # first tokens are born in prefill steps
+            for i in np.nonzero(samples_mask)[0]:
+                r = self.requests[int(req_ids[i])]
+                if r.first_token_at is None:
+                    r.first_token_at = now
+                    self.metrics.observe_ttft(now - r.created_at)
+        for i in np.nonzero(fin)[0]:
+            r = self.requests[int(req_ids[i])]
+            r._freeze()
+            r.finish_reason = FinishReason.EOS_TOKEN if fin[i] == 1 else FinishReason.MAX_TOKENS
+            r.finished_at = now
+            self.metrics.requests_finished += 1
+            if r.params.temperature > 0:
+                self._non_greedy -= 1
+        if self._watch:                                  # requests with stop sequences or a token callback
+            for i in np.nonzero(samples_mask)[0]:
+                r = self.requests[int(req_ids[i])]
+                if r.finished:
+                    if self.on_token is not None:
+                        self.on_token(r, int(sampled[i]))
+                    continue
+                if r.params.stop_sequences and self._hit_stop(r):
+                    r._freeze()
+                    self.sched.cancel(r.id)
+                    r.finish_reason = FinishReason.STOP_SEQUENCE
+                    r.finished_at = now
+                    self.metrics.requests_finished += 1
+                    if r.params.temperature > 0:
+                        self._non_greedy -= 1
+                if self.on_token is not None:
+                    self.on_token(r, int(sampled[i]))
         self.metrics.observe_step(decode, n_items, n_tokens, int(samples_mask.sum()), now - t0,
                                   self.sched.num_waiting, self.sched.num_running,
                                   self.sched.num_free_blocks, self.runner.num_blocks)
-        return out
+        self.host_seconds_last = (t_dev - t0, now - t_dev)
+        return StepOutput(self, req_ids[samples_mask], sampled[samples_mask], fin[samples_mask])
 
     @staticmethod
     def _hit_stop(r: Request) -> bool:
@@ -183,7 +230,7 @@ class LLMEngine:
         return False
 
     def _run_and_sample(self, b, decode, n_tokens, n_items, req_ids) -> torch.Tensor:
-        greedy = all(self.requests[int(i)].params.temperature <= 0 for i in req_ids)
+        greedy = self._non_greedy == 0 or all(self.requests[int(i)].params.temperature <= 0 for i in req_ids)
         if greedy:
             return self.runner.forward(b, decode, n_tokens, n_items)
         logits = self.runner.forward(b, decode, n_tokens, n_items, want_logits=True)
@@ -198,11 +245,6 @@ class LLMEngine:
         return self.cfg.max_num_seqs
 
     def _decode_graph(self, n_items: int) -> torch.Tensor:
-        greedy = all(self.requests[int(i)].params.temperature <= 0 for i in self.host.req_ids[:n_items])
-        if not greedy:
-            self._upload(n_items, n_items)
-            b = self._batch_views(n_items, n_items)
-            return self._run_and_sample(b, True, n_items, n_items, self.host.req_ids[:n_items])
         bsz = self._bucket(n_items)
         h = self.host
         if bsz > n_items:       # pad rows: no cache slot, no context

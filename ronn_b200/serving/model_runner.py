@@ -164,7 +164,8 @@ class DecoderRunner:
                 cap = int(free * self.cfg.gpu_memory_utilization) // per_block
                 want = min(want, cap)
             self.num_blocks = max(want, 1)
-        shape = (self.num_blocks, self.n_kv_local, KV_BLOCK, a.head_dim)
+        # one spare block past the pool: padded rows of the library backend scatter there
+        shape = (self.num_blocks + 1, self.n_kv_local, KV_BLOCK, a.head_dim)
         self.kcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
         self.vcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
 

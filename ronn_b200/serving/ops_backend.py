@@ -62,33 +62,34 @@ class TorchOps:
             qkv[:, k_off:k_off + kv_heads * d] = k
         k = qkv[:, k_off:k_off + kv_heads * d].reshape(T, kv_heads, d)
         v = qkv[:, v_off:v_off + kv_heads * d].reshape(T, kv_heads, d)
-        valid = slots >= 0
-        s = slots[valid].long()
+        # rows without a slot (padding) go to the spare last block, so no data-dependent shapes are needed
+        trash = (kcache.shape[0] - 1) * KV_BLOCK
+        s = torch.where(slots >= 0, slots, torch.full_like(slots, trash)).long()
         blk, off = s // KV_BLOCK, s % KV_BLOCK
-        kcache[blk, :, off, :] = k[valid]
-        vcache[blk, :, off, :] = v[valid]
+        kcache[blk, :, off, :] = k
+        vcache[blk, :, off, :] = v
 
     def paged_attention(self, q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row=None):
+        """Gather each row's pages into a dense [rows, heads, L, d] tensor and call the library SDPA."""
         rows = q.shape[0]
-        qh = q[:, :heads * d].reshape(rows, heads, d).float()
+        cdt = torch.float32 if q.device.type == "cpu" else q.dtype
+        qh = q[:, :heads * d].reshape(rows, heads, 1, d).to(cdt)
         bt = block_tables if bt_row is None else block_tables.index_select(0, bt_row.long())
-        nb = (max_ctx + KV_BLOCK - 1) // KV_BLOCK
-        nb = min(nb, bt.shape[1])
+        nb = min((max_ctx + KV_BLOCK - 1) // KV_BLOCK, bt.shape[1])
         idx = bt[:, :nb].long().clamp_min(0)                                   # [rows, nb]
-        k = kcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).float()
-        v = vcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).float()
+        k = kcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).to(cdt)
+        v = vcache[idx].permute(0, 2, 1, 3, 4).reshape(rows, kv_heads, nb * KV_BLOCK, d).to(cdt)
         if kv_heads != heads:
             rep = heads // kv_heads
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
-        scores = torch.einsum("rhd,rhld->rhl", qh, k) / math.sqrt(d)
         pos = torch.arange(nb * KV_BLOCK, device=q.device)
-        mask = pos[None, :] >= ctx_len[:, None].long()
-        scores = scores.masked_fill(mask[:, None, :], float("-inf"))
-        p = torch.softmax(scores, dim=-1)
-        p = torch.nan_to_num(p, nan=0.0)                                         # rows with ctx_len == 0
-        v = torch.where(mask[:, None, :, None], torch.zeros((), device=v.device), v)
-        out = torch.einsum("rhl,rhld->rhd", p, v)
+        keep = pos[None, :] < ctx_len[:, None].long()                             # [rows, L]
+        empty = ~keep.any(dim=1)
+        keep = keep | empty[:, None]                                              # avoid all-masked rows (NaN)
+        v = torch.where(keep[:, None, :, None], v, torch.zeros((), device=v.device, dtype=cdt))
+        out = F.scaled_dot_product_attention(qh, k, v, attn_mask=keep[:, None, None, :])
+        out = torch.where(empty[:, None, None, None], torch.zeros((), device=out.device, dtype=cdt), out)
         return out.reshape(rows, heads * d).to(q.dtype)
 
     def argmax(self, logits, col_offset=0, return_max=False):

@@ -49,12 +49,27 @@ class Request:
     prompt_tokens: List[int]
     params: SamplingParams = field(default_factory=SamplingParams)
     priority: Priority = Priority.NORMAL
-    output_tokens: List[int] = field(default_factory=list)
     finish_reason: Optional[FinishReason] = None
     created_at: float = field(default_factory=time.perf_counter)
     first_token_at: Optional[float] = None
     finished_at: Optional[float] = None
     error: Optional[str] = None
+    _final_tokens: Optional[List[int]] = None
+    _token_source: Optional[object] = None       # callable returning prompt + generated tokens while the request is live
+
+    @property
+    def output_tokens(self) -> List[int]:
+        """Generated tokens so far.  While the request is live they are read from the scheduler's token history
+        (the engine does not copy tokens into Python objects on every step)."""
+        if self._final_tokens is not None:
+            return self._final_tokens
+        if self._token_source is None:
+            return []
+        return self._token_source(self.id)[len(self.prompt_tokens):]
+
+    def _freeze(self) -> None:
+        if self._final_tokens is None:
+            self._final_tokens = self.output_tokens
 
     @property
     def finished(self) -> bool:

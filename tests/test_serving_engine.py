@@ -1,0 +1,225 @@
+"""Scheduler / block manager / continuous-batching engine on CPU (PyTorch operator backend)."""
+import numpy as np
+import pytest
+import torch
+
+from ronn_b200 import Model
+from ronn_b200.api.errors import SessionError
+from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+from ronn_b200.serving import EngineConfig, FinishReason, LLMEngine, Priority, RequestState, SamplingParams
+from ronn_b200.serving.scheduler import PLAN_DECODE, PLAN_NONE, PLAN_PREFILL, HostBatchBuffers, Scheduler
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    return Model.from_graph(build_gpt2(GPT2Config.tiny(), dtype=torch.float32, seed=1))
+
+
+def engine(model, **kw):
+    cfg = dict(max_num_seqs=4, max_batch_tokens=64, max_model_len=128, num_blocks=32, dtype="fp32", backend="torch")
+    cfg.update(kw)
+    return LLMEngine(model, EngineConfig(**cfg), device="cpu")
+
+
+def reference_greedy(model, prompt, n):
+    sess = model.create_session(optimization_level="O0")
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(sess.run({"input_ids": torch.tensor([toks])})["logits"][0, -1].argmax()))
+    return toks[len(prompt):]
+
+
+def drain(s, buf, token=7):
+    steps = []
+    while True:
+        k = s.schedule()
+        if k == PLAN_NONE:
+            break
+        sb = s.fill(buf, k)
+        steps.append((k, sb.n_items, sb.n_tokens))
+        s.commit(np.full(sb.n_items, token, dtype=np.int32))
+    return steps
+
+
+def test_scheduler_plan_layout():
+    s = Scheduler(16, 64, 4, 256)
+    s.add(1, list(range(100, 120)), 3)
+    s.add(2, list(range(5)), 2)
+    buf = HostBatchBuffers(256, 4, 8, False)
+    assert s.schedule() == PLAN_PREFILL
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert (sb.n_items, sb.n_tokens) == (2, 25) and sb.req_ids.tolist() == [1, 2]
+    assert buf.field("q_start")[:3].tolist() == [0, 20, 25] and buf.field("seq_lens")[:2].tolist() == [20, 5]
+    assert buf.field("sample_index")[:2].tolist() == [19, 24]
+    assert buf.field("token_ids")[:3].tolist() == [100, 101, 102] and buf.field("positions")[18:22].tolist() == [18, 19, 0, 1]
+    b1, b2 = s.blocks(1), s.blocks(2)
+    assert len(b1) == 2 and len(b2) == 1 and len(set(b1 + b2)) == 3
+    slots = buf.field("slot_mapping")[:25]
+    assert slots[0] == b1[0] * 16 and slots[16] == b1[1] * 16 and slots[20] == b2[0] * 16
+    assert buf.field("token_item")[:25].tolist() == [0] * 20 + [1] * 5
+    assert buf.field("block_tables")[:8].tolist()[:2] == b1 and buf.field("block_tables")[2] == -1
+    fin = s.commit(np.array([55, 66], dtype=np.int32))
+    assert fin.tolist() == [0, 0] and s.state(1) == RequestState.DECODING
+    assert s.schedule() == PLAN_DECODE
+    sb = s.fill(buf, PLAN_DECODE)
+    assert sb.n_tokens == 2 and buf.field("token_ids")[:2].tolist() == [55, 66] and buf.field("positions")[:2].tolist() == [20, 5]
+    fin = s.commit(np.array([1, 2], dtype=np.int32))
+    assert fin.tolist() == [0, 2] and s.state(2) == RequestState.FINISHED and s.tokens(2) == [0, 1, 2, 3, 4, 66, 2]
+    drain(s, buf)
+    assert s.num_free_blocks == 64 and s.stats()["finished"] == 2
+
+
+def test_scheduler_admission_limits_and_errors():
+    s = Scheduler(16, 8, 2, 32, max_blocks_per_seq=4)
+    with pytest.raises(SessionError, match="never fit"):
+        s.add(1, list(range(60)), 10)                 # exceeds max_blocks_per_seq * 16
+    with pytest.raises(SessionError, match="never fit"):
+        s.add(1, list(range(30)), 10)                 # exceeds the token budget without chunking
+    s.add(1, list(range(20)), 2)
+    with pytest.raises(SessionError, match="already exists"):
+        s.add(1, [1], 1)
+    s.add(2, list(range(20)), 2)
+    s.add(3, list(range(4)), 2)
+    buf = HostBatchBuffers(64, 2, 4, False)
+    assert s.schedule() == PLAN_PREFILL
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert sb.n_items == 1                            # 20 + 20 > 32 tokens: only one prompt fits the budget
+    s.commit(np.array([9], dtype=np.int32))
+    s.schedule()
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert sb.req_ids.tolist() == [2] and s.num_waiting == 1    # max_num_seqs = 2 keeps request 3 waiting
+    s.commit(np.array([9], dtype=np.int32))
+    assert s.schedule() == PLAN_DECODE
+
+
+def test_scheduler_preemption_recompute_and_priority():
+    s = Scheduler(16, 6, 4, 256, policy="priority")
+    s.add(1, list(range(30)), 40, priority=int(Priority.LOW))
+    s.add(2, list(range(30)), 40, priority=int(Priority.CRITICAL))
+    buf = HostBatchBuffers(256, 4, 8, False)
+    s.schedule()
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert sb.req_ids.tolist() == [2, 1]              # critical first
+    s.commit(np.array([5, 5], dtype=np.int32))
+    pre = 0
+    for _ in range(30):                               # both sequences need a fourth block at token 49: only 6 exist
+        k = s.schedule()
+        sb = s.fill(buf, k)
+        s.commit(np.full(sb.n_items, 5, dtype=np.int32))
+        pre = s.preemptions(1)
+        if pre:
+            break
+    assert pre == 1 and s.state(1) == RequestState.PREEMPTED and s.preemptions(2) == 0
+    assert s.stats()["preemptions"] == 1 and len(s.blocks(1)) == 0
+    n_before = len(s.tokens(1))
+    assert n_before > 30                              # generated tokens are kept and recomputed on resume
+    s.cancel(2)
+    assert s.state(2) == RequestState.CANCELLED
+    assert s.schedule() == PLAN_PREFILL
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert sb.req_ids.tolist() == [1] and sb.n_tokens == n_before
+
+
+def test_prefix_cache_shares_blocks():
+    s = Scheduler(16, 32, 4, 256, enable_prefix_cache=True)
+    common = list(range(40))
+    s.add(1, common + [100, 101], 2)
+    buf = HostBatchBuffers(256, 4, 8, False)
+    drain(s, buf)
+    s.add(2, common + [200, 201, 202], 2)
+    assert s.schedule() == PLAN_PREFILL
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert sb.n_tokens == 43 - 32                     # two full blocks (32 tokens) come from the cache
+    assert buf.field("positions")[0] == 32 and s.stats()["prefix_hit_blocks"] == 2
+    shared = s.blocks(2)[:2]
+    s.add(3, common + [300], 2)
+    s.commit(np.array([1], dtype=np.int32))
+    s.schedule()
+    s.fill(buf, PLAN_PREFILL)
+    assert s.blocks(3)[:2] == shared and s.block_ref(shared[0]) == 2
+
+
+def test_engine_matches_single_sequence_reference(tiny):
+    prompts = [[1, 2, 3, 4, 5, 6, 7], [9, 8, 7], list(range(20, 45)), [100, 101], [5] * 18, [7, 7, 7]]
+    eng = engine(tiny)
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=6))
+    for p, o in zip(prompts, outs):
+        assert o == reference_greedy(tiny, p, 6)
+    st = eng.stats()
+    assert st["requests_finished"] == 6 and st["generated_tokens"] == 36 and st["preemptions"] == 0
+    assert all(r.finish_reason == FinishReason.MAX_TOKENS and r.ttft is not None for r in eng.requests.values())
+    assert "ronn_generated_tokens 36" in eng.metrics.prometheus()
+
+
+def test_engine_chunked_prefill_and_preemption_keep_outputs(tiny):
+    prompts = [list(range(3, 40)), list(range(50, 75)), list(range(90, 120)), [4, 5, 6]]
+    want = [reference_greedy(tiny, p, 12) for p in prompts]
+    chunked = engine(tiny, prefill_chunk=8, max_batch_tokens=16).generate(prompts, SamplingParams(max_new_tokens=12))
+    assert chunked == want
+    grow = [[3 + i] * 15 for i in range(4)]            # one block each at admission, three each by the end
+    want_grow = [reference_greedy(tiny, p, 30) for p in grow]
+    tight = engine(tiny, num_blocks=7)                 # 12 blocks would be needed to finish all four together
+    got = tight.generate(grow, SamplingParams(max_new_tokens=30))
+    assert got == want_grow and tight.stats()["preemptions"] >= 1
+    cached = engine(tiny, enable_prefix_cache=True)
+    same = [list(range(3, 40)) + [7], list(range(3, 40)) + [9]]
+    a = cached.generate([same[0]], SamplingParams(max_new_tokens=5))
+    b = cached.generate([same[1]], SamplingParams(max_new_tokens=5))
+    assert a[0] == reference_greedy(tiny, same[0], 5) and b[0] == reference_greedy(tiny, same[1], 5)
+    assert cached.stats()["prefix_hit_blocks"] == 2
+
+
+def test_engine_eos_stop_cancel_and_limits(tiny):
+    first = reference_greedy(tiny, [1, 2, 3], 3)
+    eng = engine(tiny, eos_token_id=first[0])
+    rid = eng.add_request([1, 2, 3], SamplingParams(max_new_tokens=10))
+    while eng.has_unfinished():
+        eng.step()
+    r = eng.requests[rid]
+    assert r.output_tokens == first[:1] and r.finish_reason == FinishReason.EOS_TOKEN
+    eng2 = engine(tiny)
+    rid = eng2.add_request([1, 2, 3], SamplingParams(max_new_tokens=10, stop_sequences=[first[0:2]]))
+    while eng2.has_unfinished():
+        eng2.step()
+    assert eng2.requests[rid].finish_reason == FinishReason.STOP_SEQUENCE and eng2.requests[rid].output_tokens == first[:2]
+    eng3 = engine(tiny)
+    rid = eng3.add_request([1, 2, 3], SamplingParams(max_new_tokens=50))
+    eng3.step()
+    assert eng3.cancel(rid) and not eng3.has_unfinished() and eng3.requests[rid].finish_reason == FinishReason.CANCELLED
+    assert eng3.sched.num_free_blocks == 32
+    with pytest.raises(SessionError, match="max_model_len"):
+        eng3.add_request(list(range(120)), SamplingParams(max_new_tokens=20))
+    with pytest.raises(SessionError, match="empty"):
+        eng3.add_request([])
+    seen = []
+    eng3.on_token = lambda req, tok: seen.append(tok)
+    out = eng3.generate([[5, 6]], SamplingParams(max_new_tokens=3))
+    assert seen == out[0]
+
+
+def test_engine_sampling_is_seeded(tiny):
+    p = SamplingParams(max_new_tokens=8, temperature=0.9, top_k=20, top_p=0.9, repeat_penalty=1.1, seed=11)
+    a = engine(tiny).generate([[1, 2, 3, 4]], p)
+    b = engine(tiny).generate([[1, 2, 3, 4]], p)
+    assert a == b and len(a[0]) == 8
+
+
+def test_failed_step_requeues_requests(tiny):
+    eng = engine(tiny)
+    eng.add_request([1, 2, 3, 4], SamplingParams(max_new_tokens=4))
+    orig = eng.runner.forward
+    calls = {"n": 0}
+
+    def flaky(*a, **k):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise RuntimeError("injected host-side failure")
+        return orig(*a, **k)
+    eng.runner.forward = flaky
+    eng.step()
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.step()
+    assert eng.metrics.failed_steps == 1 and eng.sched.num_waiting == 1      # back in the queue for recompute
+    while eng.has_unfinished():
+        eng.step()
+    assert list(eng.requests.values())[0].output_tokens == reference_greedy(tiny, [1, 2, 3, 4], 4)
