@@ -1,0 +1,292 @@
+// Row-parallel GEMM fused with its collective, in ONE kernel, over NVLink peer memory.
+//
+//   Y = reduce_over_ranks( A_r[M, K_r] * W_r[N, K_r]^T ) + bias + residual
+//
+// Every rank runs the same kernel.  Phase 1 is the persistent tcgen05 GEMM; its epilogue writes
+// the rank's partial products (bf16) into the rank's own slot of a symmetric buffer.  When the last
+// CTA of a rank has stored its tiles, that rank raises a per-call flag on every peer with a remote
+// system-scope atomic.  Phase 2 runs in the same CTAs: each waits (bounded) until all ranks have
+// flagged, then reads the partials of every rank straight from peer memory with 16-byte loads, sums
+// them in fp32 in rank order (so every rank obtains bit-identical results), adds bias and residual
+// and writes the rows it owns:
+//     all-reduce mode      rows [0, M)          -> replicated activations (decode, small M)
+//     reduce-scatter mode  this rank's row shard -> sequence-parallel activations (prefill)
+//
+// Buffers alternate between two parities per call; a rank can never run two calls ahead of a peer
+// (phase 2 of call k needs every peer's phase 1 of call k), so two slots are enough.  Flags only ever
+// count up (one increment per call and source rank), so nothing is reset between calls and CUDA-graph
+// replays need no host-side arguments: the call counter lives in device memory.
+//
+// No TMA multicast is used anywhere; remote data is read with plain loads, flags are written with
+// remote atomics.  All waits are bounded: on expiry the kernel records STATUS_WAIT_PEER and returns.
+//
+// The reference has no collective of any kind (its only multi-GPU code picks one device per sub-graph,
+// crates/ronn-providers/src/gpu/provider.rs:226-249).
+#include "common.cuh"
+#include "tma_desc.cuh"
+#include "umma_persistent.cuh"
+
+namespace ronn {
+
+constexpr int MAX_RANKS = 8;
+
+struct CommArgs {
+  uint8_t* peer_part[MAX_RANKS];   // base of every rank's partial buffer (two parities back to back)
+  int* peer_flags[MAX_RANKS];      // every rank's flag array: [2 parities][MAX_RANKS sources]
+  long part_stride;                // bytes between the two parity slots
+  int* state;                      // local: [0] calls completed, [1] phase-1 CTA counter, [2] phase-2 CTA counter
+  int rank, world;
+  int row_begin, row_end;          // rows this rank reduces and writes
+  void* out;                       // [row_end - row_begin, N]
+  long ld_out;
+  const void* bias;                // [N] or null
+  const void* residual;            // rows aligned with `out`, or null
+  long ld_res;
+  unsigned long long wait_ns;      // limit of the peer wait
+};
+
+__device__ __forceinline__ Vec8 ld_volatile_16(const void* p) {
+  Vec8 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <int BN, class T>
+struct PartialProblem {
+  const CUtensorMap* map_a;
+  const CUtensorMap* map_b;
+  const CommArgs* comm;
+  int M, N, m_tiles, n_tiles, num_kb;
+  mutable T* part;                 // resolved lazily by the epilogue (after the dependency wait)
+
+  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
+  __device__ __forceinline__ void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const {
+    m0 = (t % m_tiles) * PG_BM;
+    n0 = (t / m_tiles) * BN;
+    kb0 = 0;
+    nkb = num_kb;
+  }
+  __device__ __forceinline__ void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const {
+    tma_load_2d(smem, map_a, bar, k_elem, m0);
+  }
+  __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
+    tma_load_2d(smem, map_b, bar, k_elem, n0);
+  }
+  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+    if (part == nullptr) {
+      const int total = *reinterpret_cast<volatile int*>(comm->state);
+      part = reinterpret_cast<T*>(comm->peer_part[comm->rank] + size_t(total & 1) * comm->part_stride);
+    }
+    const int gm = m0 + row, gn = n0 + col;
+    if (gm >= M || gn >= N) return;
+    T* dst = part + size_t(gm) * N + gn;
+    if (gn + 32 <= N) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[j * 8 + i]);
+        *reinterpret_cast<Vec8*>(dst + j * 8) = pack8<T>(f);
+      }
+    } else {
+      for (int i = 0; i < 32 && gn + i < N; ++i) dst[i] = Cvt<T>::from_f(__uint_as_float(r[i]));
+    }
+  }
+};
+
+template <int BN, int STAGES, class T>
+__global__ void __launch_bounds__(PG_THREADS)
+gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CommArgs comm, int M, int N, int K, uint32_t idesc, uint32_t* status) {
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ int s_flag;
+  PartialProblem<BN, T> prob;
+  prob.map_a = &map_a;
+  prob.map_b = &map_b;
+  prob.comm = &comm;
+  prob.M = M;
+  prob.N = N;
+  prob.m_tiles = (M + PG_BM - 1) / PG_BM;
+  prob.n_tiles = (N + BN - 1) / BN;
+  prob.num_kb = (K + 63) / 64;
+  prob.part = nullptr;
+  gemm_persistent<BN, STAGES, 0, PartialProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
+  // ---- end of phase 1: every thread of this CTA has issued its partial stores (teardown barrier passed)
+  pdl_wait();
+  const int total = *reinterpret_cast<volatile int*>(comm.state);
+  const int parity = total & 1;
+  const int want = (total >> 1) + 1;
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int done = atomicAdd(comm.state + 1, 1);
+    if (done == int(gridDim.x) - 1) {            // last CTA of this rank: tell every rank our partials are complete
+      comm.state[1] = 0;
+      __threadfence_system();
+      for (int p = 0; p < comm.world; ++p)
+        atomicAdd_system(comm.peer_flags[p] + parity * MAX_RANKS + comm.rank, 1);
+    }
+    // ---- phase 2: wait for the partials of every rank (bounded)
+    const int* flags = comm.peer_flags[comm.rank] + parity * MAX_RANKS;
+    const unsigned long long t0 = globaltimer_ns();
+    int ok = 1;
+    for (int src = 0; src < comm.world && ok; ++src) {
+      unsigned polls = 0;
+      while (ld_acquire_sys(flags + src) < want) {
+        if ((++polls & 63u) == 0u && globaltimer_ns() - t0 > comm.wait_ns) {
+          if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
+          ok = 0;
+          break;
+        }
+      }
+    }
+    s_flag = ok;
+  }
+  __syncthreads();
+  if (s_flag) {
+    const int rows = comm.row_end - comm.row_begin;
+    const int n8 = N >> 3;
+    const long vecs = long(rows) * n8;
+    const size_t slot = size_t(parity) * comm.part_stride;
+    T* out = reinterpret_cast<T*>(comm.out);
+    const T* bias = reinterpret_cast<const T*>(comm.bias);
+    const T* res = reinterpret_cast<const T*>(comm.residual);
+    for (long v = long(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += long(gridDim.x) * blockDim.x) {
+      const int r = int(v / n8), c = int(v - long(r) * n8) * 8;
+      const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
+      Vec8 pk[MAX_RANKS];
+#pragma unroll
+      for (int src = 0; src < MAX_RANKS; ++src)
+        if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int src = 0; src < MAX_RANKS; ++src)
+        if (src < comm.world) {
+          float f[8];
+          unpack8<T>(pk[src], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
+      if (bias) {
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      if (res) {
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+      }
+      *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = pack8<T>(acc);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(comm.state + 2, 1);
+    if (done == int(gridDim.x) - 1) {            // last CTA: the call is complete on this rank
+      comm.state[2] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(comm.state) = total + 1;
+    }
+  }
+}
+
+static int comm_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int STAGES, class T>
+static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
+                         int is_bf16, uint32_t* status, cudaStream_t stream) {
+  using L = PGemmSmem<BN, STAGES>;
+  auto kern = gemm_reduce_kernel<BN, STAGES, T>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM);
+  // every CTA must be resident at once (phase 2 waits on work of the whole grid): never exceed one wave
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, PG_THREADS, L::DYN_SMEM) != cudaSuccess || per_sm < 1)
+    return -12;
+  if (per_sm > 2) per_sm = 2;
+  const int resident = comm_sm_count() * per_sm;
+  dim3 grid(tiles < resident ? tiles : resident);
+  uint32_t idesc = umma_idesc(PG_BM, BN, is_bf16 ? 1u : 0u, 1u);
+  cudaError_t err = launch(kern, grid, dim3(PG_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, comm, M, N, K, idesc, status);
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+}  // namespace ronn
+
+using namespace ronn;
+
+// peer_part / peer_flags: `world` pointers each.  part_stride: bytes between the two parity slots of a partial
+// buffer (>= M * N * 2).  state: three zero-initialised ints in local device memory, shared by all calls on this
+// rank.  Rows [row_begin, row_end) of the reduced result (+ bias + residual) are written to `out`.
+// dtype 0 bf16, 1 fp16.  N % 8 == 0.  Returns 0 on success.
+extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
+                                int rank, int world, int row_begin, int row_end, void* out, long ld_out,
+                                const void* bias, const void* residual, long ld_res, double wait_seconds, int dtype,
+                                int bn, uint32_t* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return -2;
+  if (row_begin < 0 || row_end > M || row_begin > row_end || part_stride < long(M) * N * 2) return -4;
+  if (bn == 0) {
+    const int mt = (M + PG_BM - 1) / PG_BM;
+    bn = 128;
+    while (bn > 32 && mt * ((N + bn - 1) / bn) < 96) bn >>= 1;
+  }
+  CUtensorMap ma, mb;
+  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), PG_BM, 64, 2);
+  if (rc) return rc - 20;
+  rc = make_tmap_2d(&mb, W, uint64_t(N), uint64_t(K), uint64_t(ldw), uint32_t(bn), 64, 2);
+  if (rc) return rc - 30;
+  CommArgs c;
+  for (int p = 0; p < MAX_RANKS; ++p) {
+    c.peer_part[p] = p < world ? static_cast<uint8_t*>(peer_part[p]) : nullptr;
+    c.peer_flags[p] = p < world ? peer_flags[p] : nullptr;
+  }
+  c.part_stride = part_stride;
+  c.state = state;
+  c.rank = rank;
+  c.world = world;
+  c.row_begin = row_begin;
+  c.row_end = row_end;
+  c.out = out;
+  c.ld_out = ld_out;
+  c.bias = bias;
+  c.residual = residual;
+  c.ld_res = ld_res;
+  c.wait_ns = static_cast<unsigned long long>(wait_seconds * 1e9);
+  const int bf = dtype == 0;
+#define RONN_DISPATCH(BN_, ST_)                                                                        \
+  return bf ? launch_reduce<BN_, ST_, __nv_bfloat16>(ma, mb, c, M, N, K, 1, status, stream)           \
+            : launch_reduce<BN_, ST_, __half>(ma, mb, c, M, N, K, 0, status, stream)
+  switch (bn) {
+    case 128: RONN_DISPATCH(128, 3);
+    case 64: RONN_DISPATCH(64, 4);
+    case 32: RONN_DISPATCH(32, 5);
+    default: return -3;
+  }
+#undef RONN_DISPATCH
+}

@@ -10,7 +10,7 @@
 // (crates/ronn-providers/src/gpu/cuda_kernels.rs:319-347, 479-534).
 #include "common.cuh"
 #include "tma_desc.cuh"
-#include "umma_gemm.cuh"
+#include "umma_persistent.cuh"
 
 namespace ronn {
 
@@ -86,53 +86,87 @@ struct DenseEpilogue {
   }
 };
 
-template <class T>
-struct DenseEpiCall {
+// Tile list of a dense (optionally split-K) GEMM for the persistent mainloop.  Tiles are numbered with the
+// M index fastest so that CTAs running side by side share the same weight tile in L2.
+template <int BN, class T>
+struct DenseProblem {
+  const CUtensorMap* map_a;
+  const CUtensorMap* map_b;
   DenseEpilogue e;
-  __device__ __forceinline__ void operator()(int row, int col, uint32_t (&r)[32]) const { e.run<T>(row, col, r); }
+  int m_tiles, n_tiles, num_kb, splitk, kb_per;
+
+  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles * splitk; }
+  __device__ __forceinline__ void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const {
+    const int per_z = m_tiles * n_tiles;
+    const int z = t / per_z, r = t - z * per_z;
+    m0 = (r % m_tiles) * PG_BM;
+    n0 = (r / m_tiles) * BN;
+    kb0 = z * kb_per;
+    nkb = min(kb_per, num_kb - kb0);
+  }
+  __device__ __forceinline__ void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const {
+    tma_load_2d(smem, map_a, bar, k_elem, m0);
+  }
+  __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
+    tma_load_2d(smem, map_b, bar, k_elem, n0);
+  }
+  __device__ __forceinline__ void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+    DenseEpilogue ep = e;
+    ep.m0 = m0;
+    ep.n0 = n0;
+    if (splitk > 1)     // raw fp32 partial sums go to slice z of the workspace
+      ep.C = reinterpret_cast<float*>(e.C) + size_t(t / (m_tiles * n_tiles)) * size_t(e.M) * size_t(e.ldc);
+    ep.run<T>(row, col, r);
+  }
 };
 
 template <int BN, int STAGES, class T>
-__global__ void __launch_bounds__(GEMM_THREADS)
+__global__ void __launch_bounds__(PG_THREADS)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                  DenseEpilogue epi, int K, uint32_t idesc, uint32_t* status) {
+                  DenseEpilogue epi, int K, int splitk, uint32_t idesc, uint32_t* status) {
   extern __shared__ uint8_t dyn_smem[];
-  const int n0 = blockIdx.x * BN;
-  const int m0 = blockIdx.y * GEMM_BM;
-  epi.m0 = m0;
-  epi.n0 = n0;
-  TmaALoader al{&map_a, m0};
-  DenseEpiCall<T> call{epi};
-  int num_kb = (K + 63) / 64;
-  int kb0 = 0;
-  if (gridDim.z > 1) {
-    // split-K: this CTA owns k-blocks [kb0, kb0 + num_kb) and writes raw fp32 partial sums to slice z of the workspace
-    const int per = (num_kb + gridDim.z - 1) / gridDim.z;
-    kb0 = blockIdx.z * per;
-    num_kb = min(per, num_kb - kb0);
-    call.e.C = reinterpret_cast<float*>(epi.C) + size_t(blockIdx.z) * size_t(epi.M) * size_t(epi.ldc);
+  DenseProblem<BN, T> prob;
+  prob.map_a = &map_a;
+  prob.map_b = &map_b;
+  prob.e = epi;
+  prob.m_tiles = (epi.M + PG_BM - 1) / PG_BM;
+  prob.n_tiles = (epi.N + BN - 1) / BN;
+  prob.num_kb = (K + 63) / 64;
+  prob.splitk = splitk;
+  prob.kb_per = (prob.num_kb + splitk - 1) / splitk;
+  gemm_persistent<BN, STAGES, 0, DenseProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
   }
-  gemm_tile<BN, STAGES, 0, TmaALoader, DenseEpiCall<T>>(dyn_smem, al, &map_b, n0, num_kb, 64, idesc, status, call, kb0);
+  return n;
 }
 
 template <int BN, int STAGES, class T>
 static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilogue epi, int M, int N, int K,
                         int is_bf16, uint32_t* status, cudaStream_t stream, int splitk = 1) {
-  using L = GemmSmemLayout<BN, STAGES>;
+  using L = PGemmSmem<BN, STAGES>;
   auto kern = gemm_dense_kernel<BN, STAGES, T>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + GEMM_BM - 1) / GEMM_BM, splitk);
-  uint32_t idesc = umma_idesc(GEMM_BM, BN, is_bf16 ? 1u : 0u, 1u);
-  cudaError_t err = launch(kern, grid, dim3(GEMM_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, epi, K, idesc, status);
+  const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM) * splitk;
+  const int resident = sm_count() * (L::DYN_SMEM <= 110 * 1024 && L::TMEM_COLS <= 256 ? 2 : 1);
+  dim3 grid(tiles < resident ? tiles : resident);
+  uint32_t idesc = umma_idesc(PG_BM, BN, is_bf16 ? 1u : 0u, 1u);
+  cudaError_t err = launch(kern, grid, dim3(PG_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, epi, K, splitk, idesc, status);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
 int pick_bn(int M, int N) {
-  const int mt = (M + GEMM_BM - 1) / GEMM_BM;
+  const int mt = (M + PG_BM - 1) / PG_BM;
   const int cands[4] = {256, 128, 64, 32};
   for (int i = 0; i < 4; ++i) {
     int bn = cands[i];
@@ -157,7 +191,7 @@ extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias
   if ((K & 7) || (lda & 7) || (ldw & 7)) return -2;
   if (bn == 0) bn = pick_bn(M, N);
   CUtensorMap ma, mb;
-  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), GEMM_BM, 64, 2);
+  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), PG_BM, 64, 2);
   if (rc) return rc - 20;
   rc = make_tmap_2d(&mb, W, uint64_t(N), uint64_t(K), uint64_t(ldw), uint32_t(bn), 64, 2);
   if (rc) return rc - 30;
@@ -191,7 +225,7 @@ extern "C" int ronn_gemm_splitk(const void* A, const void* W, float* workspace, 
   if (splitk_out) *splitk_out = splitk;
   if (bn == 0) bn = N >= 128 ? 128 : (N >= 64 ? 64 : 32);
   CUtensorMap ma, mb;
-  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), GEMM_BM, 64, 2);
+  int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), PG_BM, 64, 2);
   if (rc) return rc - 20;
   rc = make_tmap_2d(&mb, W, uint64_t(N), uint64_t(K), uint64_t(ldw), uint32_t(bn), 64, 2);
   if (rc) return rc - 30;

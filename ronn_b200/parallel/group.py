@@ -58,10 +58,11 @@ class TPComm:
         """[...] -> [world, ...]"""
         if self.world == 1:
             return x.unsqueeze(0)
-        out = torch.empty((self.world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        flat = x.contiguous().reshape(-1)
+        out = torch.empty(self.world * flat.numel(), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, flat, group=self.group)
         self.calls += 1
-        return out
+        return out.reshape((self.world,) + tuple(x.shape))
 
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         """[m, n] shards -> [world*m, n]"""

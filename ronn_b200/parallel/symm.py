@@ -1,0 +1,96 @@
+"""Fused compute + collective communicator over NVLink peer memory.
+
+One symmetric allocation per rank (``torch.distributed._symmetric_memory``: every rank maps every
+peer's copy) holds the partial-product slots (two parities) and the flag words of the fused
+row-parallel GEMM.  ``FusedComm.gemm_allreduce`` / ``gemm_reduce_scatter`` launch ONE kernel that
+computes this rank's partial GEMM on the tensor cores, publishes it, waits for the peers with a
+bounded spin, and reduces straight from peer memory (see ``csrc/kernels/comm_gemm.cu``).  NCCL is
+only used for the rendezvous and for the tiny (max, index) gather of the sharded argmax.
+
+A device-side wait that runs out leaves ``STATUS_WAIT_PEER`` in the status word; ``check()``
+turns it into ``CommTimeoutError`` on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..api.errors import ProviderError
+from ..ops import kernels as K
+from .group import TPComm
+
+MAX_RANKS = 8
+_FLAG_INTS = 2 * MAX_RANKS
+
+
+class FusedComm(TPComm):
+    """Tensor-parallel communicator whose row-parallel collectives are fused into the GEMM kernel."""
+    fused = True
+
+    def __init__(self, device: torch.device, max_rows: int = 8192, max_cols: int = 8192, group=None,
+                 wait_seconds: Optional[float] = None):
+        super().__init__(group)
+        if self.world > MAX_RANKS:
+            raise ProviderError(f"fused collectives support at most {MAX_RANKS} ranks")
+        import torch.distributed._symmetric_memory as symm
+        self.device = torch.device(device)
+        self.max_elems = max_rows * max_cols
+        self.part_stride = self.max_elems * 2                       # bytes of one parity slot (16-bit elements)
+        flag_bytes = 256
+        total = 2 * self.part_stride + flag_bytes
+        self._buf = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self._buf.zero_()
+        torch.cuda.synchronize(self.device)
+        pg = group if group is not None else dist.group.WORLD
+        self._hdl = symm.rendezvous(self._buf, pg.group_name if hasattr(pg, "group_name") else pg)
+        ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        self._part_ptrs = (C.c_void_p * MAX_RANKS)(*[ptrs[p] if p < self.world else None for p in range(MAX_RANKS)])
+        self._flag_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + 2 * self.part_stride) if p < self.world else None
+                                                    for p in range(MAX_RANKS)])
+        self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
+        self.fused_calls = 0
+        dist.barrier(group=group)                                     # flags and counters are zero everywhere
+
+    # ------------------------------------------------------------------ fused row-parallel GEMM
+    def _gemm_reduce(self, a, w_nk, bias, residual, row_begin, row_end, bn=0):
+        M, Kd = a.shape
+        N = w_nk.shape[0]
+        if M * N > self.max_elems:
+            raise ProviderError(f"fused GEMM of {M}x{N} exceeds the symmetric buffer ({self.max_elems} elements)")
+        rows = row_end - row_begin
+        out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+        if residual is not None and (residual.stride(1) != 1 or residual.shape != out.shape):
+            residual = residual.reshape(rows, N).contiguous()
+        if bias is not None and bias.dtype != a.dtype:
+            bias = bias.to(a.dtype)
+        rc = _native.cuda().ronn_gemm_reduce(
+            a.data_ptr(), w_nk.data_ptr(), M, N, Kd, a.stride(0), w_nk.stride(0), self._part_ptrs, self._flag_ptrs,
+            self.part_stride, self._state.data_ptr(), self.rank, self.world, row_begin, row_end, out.data_ptr(),
+            out.stride(0), None if bias is None else bias.data_ptr(), None if residual is None else residual.data_ptr(),
+            residual.stride(0) if residual is not None else 0, self.wait_seconds, 0 if a.dtype == torch.bfloat16 else 1,
+            bn, K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"gemm_reduce failed with code {rc}")
+        self.fused_calls += 1
+        return out
+
+    def gemm_allreduce(self, a, w_nk, bias=None, residual=None, bn=0):
+        """sum over ranks of (a @ w_nk^T) + bias + residual, full result on every rank (bit-identical)."""
+        return self._gemm_reduce(a, w_nk, bias, residual, 0, a.shape[0], bn)
+
+    def gemm_reduce_scatter(self, a, w_nk, bias=None, residual_shard=None, bn=0):
+        """Same sum, but each rank keeps only its contiguous shard of the rows (M must divide by the world size)."""
+        M = a.shape[0]
+        if M % self.world:
+            raise ProviderError("reduce-scatter needs the row count to divide by the world size")
+        per = M // self.world
+        return self._gemm_reduce(a, w_nk, bias, residual_shard, self.rank * per, (self.rank + 1) * per, bn)
+
+    def check(self) -> None:
+        K.check_status(self.device)

@@ -164,6 +164,9 @@ class LLMEngine:
         si = h.field("sample_index")
         samples_mask = si[:n_items] >= 0
         np.maximum(si[:n_items], 0, out=si[:n_items])
+        if self.cfg.backend == "torch":
+            longest = int(h.field("seq_lens")[:n_items].max())
+            self.runner.step_ctx = min(-(-longest // 128) * 128, self.cfg.max_model_len)
         try:
             if decode and self.use_graph and self._non_greedy == 0:
                 toks = self._decode_graph(n_items)
@@ -254,7 +257,8 @@ class LLMEngine:
             h.field("seq_lens")[n_items:bsz] = 0
             h.field("block_tables")[n_items * self.max_blocks: bsz * self.max_blocks] = 0
         self._upload(bsz, bsz)
-        entry = self._graphs.get(bsz)
+        key = (bsz, self.runner.step_ctx)
+        entry = self._graphs.get(key)
         if entry is None:
             b = self._batch_views(bsz, bsz)
             # warm-up outside capture (loads kernels, sizes caches), then capture
@@ -268,7 +272,7 @@ class LLMEngine:
             with torch.cuda.graph(g):
                 out = self.runner.forward(b, True, bsz, bsz)
             entry = (g, out)
-            self._graphs[bsz] = entry
+            self._graphs[key] = entry
         g, out = entry
         g.replay()
         return out

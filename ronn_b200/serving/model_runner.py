@@ -117,6 +117,7 @@ class DecoderRunner:
         self.max_blocks_per_seq = (cfg.max_model_len + KV_BLOCK - 1) // KV_BLOCK
         self._alloc_cache()
         self.launches = 0
+        self.step_ctx = 0
 
     # ------------------------------------------------------------------ weights
     def _dev(self, t: torch.Tensor) -> torch.Tensor:
@@ -180,6 +181,9 @@ class DecoderRunner:
             if residual is not None:
                 y = y + residual
             return y
+        if reduce and self.tp > 1 and getattr(self.comm, "fused", False) and ops.name == "kernels":
+            # one kernel: partial GEMM on the tensor cores + cross-rank reduction over NVLink + bias + residual
+            return self.comm.gemm_allreduce(x, lw.w, lw.bias, residual)
         if reduce and self.tp > 1:
             # bias and residual are applied once, after the partial sums are combined
             y = ops.gemm(x, lw.w)
@@ -211,7 +215,8 @@ class DecoderRunner:
         else:
             ctx, bt_row = b["ctx_per_token"], b["token_item"]
         hn, kn = self.n_head_local * d, self.n_kv_local * d
-        max_ctx = self.cfg.max_model_len
+        # the library backend gathers dense KV, so it is sized by the longest context of this step
+        max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
         for li, L in enumerate(self.layers):
             h = self._norm(x, L["ln1"])
             qkv = self._linear(h, L["qkv"])

@@ -1,0 +1,58 @@
+"""Child process of the tensor-parallel tests: runs the serving engine at the launched world size and
+compares its greedy tokens with a single-rank engine built from the same seeded model."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+import torch  # noqa: E402
+
+from ronn_b200.api.model import Model  # noqa: E402
+from ronn_b200.models.gpt2 import GPT2Config, build_gpt2  # noqa: E402
+from ronn_b200.parallel.fused import make_comm  # noqa: E402
+from ronn_b200.parallel.group import init_distributed  # noqa: E402
+from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1]            # "cpu" | "nccl" | "fused"
+    out_path = sys.argv[2]
+    rank, world, local = init_distributed("gloo" if mode == "cpu" else "nccl", timeout_s=120)
+    if mode == "cpu":
+        dev, dtype, backend = torch.device("cpu"), torch.float32, "torch"
+    else:
+        dev, dtype, backend = torch.device("cuda", local), torch.bfloat16, "kernels"
+    cfg = GPT2Config.tiny(n_layer=2, n_embd=256, n_head=4, vocab_size=1000, n_positions=256)
+    model = Model.from_graph(build_gpt2(cfg, dtype=dtype, seed=7))
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 17, 40, 64, 9, 33)]
+
+    def run(comm, tp_comm):
+        ecfg = EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256, num_blocks=64,
+                            dtype="fp32" if mode == "cpu" else "bf16", backend=backend, tp_size=world if comm else 1,
+                            tp_comm=tp_comm, use_cuda_graph=(mode != "cpu"))
+        eng = LLMEngine(model, ecfg, device=dev, comm=comm)
+        return eng.generate(prompts, SamplingParams(max_new_tokens=8))
+
+    comm = make_comm("nccl" if mode in ("cpu", "nccl") else "fused", dev)
+    tp = run(comm, "nccl" if mode != "fused" else "fused")
+    single = run(None, "nccl")
+    if mode == "fused":
+        comm.check()
+    agree = sum(a == b for x, y in zip(tp, single) for a, b in zip(x, y))
+    total = sum(len(x) for x in single)
+    # every rank must have produced the same tokens (the schedulers run replicated)
+    gathered = [None] * world
+    torch.distributed.all_gather_object(gathered, tp)
+    same_across_ranks = all(g_ == gathered[0] for g_ in gathered)
+    if rank == 0:
+        with open(out_path, "w") as f:
+            json.dump({"agree": agree, "total": total, "same_across_ranks": same_across_ranks, "world": world,
+                       "fused_calls": getattr(comm, "fused_calls", 0)}, f)
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

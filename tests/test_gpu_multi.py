@@ -1,0 +1,75 @@
+"""Multi-GPU tests (child processes, one per GPU): fused GEMM + collective kernel and the TP engine."""
+import json
+import os
+
+import pytest
+import torch
+
+from test_tp_cpu import launch
+
+pytestmark = pytest.mark.gpu
+
+need2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+
+
+def _world():
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else (4 if n >= 4 else 2)
+
+
+@need2
+def test_fused_gemm_allreduce_and_reduce_scatter(tmp_path):
+    out = tmp_path / "r.json"
+    p = launch(_world(), "fused_gemm_worker.py", [str(out)], 29650, env={"NCCL_NVLS_ENABLE": "0"})
+    assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-4000:])
+    for per_rank in json.loads(out.read_text()):
+        for r in per_rank:
+            assert r["identical"], r
+            assert r["err"] < 0.15, r            # bf16 partials of O(10) magnitude summed over ranks
+
+
+@need2
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_tp_engine_matches_single_gpu(tmp_path, mode):
+    out = tmp_path / "r.json"
+    p = launch(_world() if mode == "nccl" else min(_world(), 4), "tp_engine_worker.py", [mode, str(out)], 29660,
+               env={"NCCL_NVLS_ENABLE": "0"})
+    assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-4000:])
+    r = json.loads(out.read_text())
+    assert r["same_across_ranks"]
+    assert r["agree"] >= int(0.85 * r["total"]), r
+    if mode == "fused":
+        assert r["fused_calls"] > 0
+
+
+def test_peer_wait_runs_out_and_context_survives():
+    """A flag that nothing sets: the fused kernel gives up after its limit, reports STATUS_WAIT_PEER through the status
+    word, and the CUDA context stays usable.  Both 'ranks' point at buffers of this one GPU."""
+    import ctypes as C
+    from ronn_b200 import _native
+    from ronn_b200.api.errors import CommTimeoutError
+    from ronn_b200.ops import kernels as K
+    dev = torch.device("cuda", 0)
+    M, N, Kd = 128, 256, 64
+    a = torch.randn(M, Kd, device=dev).bfloat16()
+    w = torch.randn(N, Kd, device=dev).bfloat16()
+    stride = M * N * 2
+    parts = [torch.zeros(2 * stride, dtype=torch.uint8, device=dev) for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+    state = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    pp = (C.c_void_p * 8)(*[parts[0].data_ptr(), parts[1].data_ptr()] + [None] * 6)
+    fp = (C.c_void_p * 8)(*[flags[0].data_ptr(), flags[1].data_ptr()] + [None] * 6)
+    K.check_status(dev)
+    rc = _native.cuda().ronn_gemm_reduce(a.data_ptr(), w.data_ptr(), M, N, Kd, Kd, Kd, pp, fp, stride, state.data_ptr(),
+                                         0, 2, 0, M, out.data_ptr(), N, None, None, 0, 0.3, 0, 0,
+                                         K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(CommTimeoutError, match="peer"):
+        K.check_status(dev)
+    # rank 0 raised its own flags on both "ranks"; rank 1 never did
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1 and int(flags[0][1]) == 0
+    y = K.gemm(a, w)                                # the context is alive and later kernels run
+    torch.testing.assert_close(y.float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
+    K.check_status(dev)

@@ -1,0 +1,60 @@
+"""Tensor-parallel engine logic on CPU ranks (gloo): sharding, replicated scheduling, sharded argmax."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def launch(nproc, script, args, port, timeout=300, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_workers", script)] + args
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_engine_on_cpu_ranks_matches_single_rank(tmp_path, world):
+    out = tmp_path / "r.json"
+    p = launch(world, "tp_engine_worker.py", ["cpu", str(out)], 29610 + world)
+    assert p.returncode == 0, p.stderr[-3000:]
+    r = json.loads(out.read_text())
+    assert r["world"] == world and r["same_across_ranks"]
+    assert r["agree"] == r["total"] == 48          # fp32: sharded and unsharded runs pick the same tokens
+
+
+def test_head_and_vocab_sharding_cover_everything():
+    from ronn_b200.serving.model_runner import shard_heads
+    for heads, tp in ((12, 8), (20, 8), (16, 8), (16, 3), (4, 4)):
+        spans = [shard_heads(heads, tp, r) for r in range(tp)]
+        assert spans[0][0] == 0 and sum(n for _, n in spans) == heads
+        for (s0, n0), (s1, _) in zip(spans, spans[1:]):
+            assert s0 + n0 == s1
+        assert max(n for _, n in spans) - min(n for _, n in spans) <= 1
+
+
+def test_rank_that_never_joins_is_reported_not_hung(tmp_path):
+    """Failure made on the host: one of two ranks exits before the rendezvous; the other gets an error from the
+    process-group timeout instead of hanging."""
+    script = tmp_path / "w.py"
+    script.write_text(
+        "import os, sys, datetime, torch.distributed as dist\n"
+        "rank = int(os.environ['RANK'])\n"
+        "if rank == 1:\n    sys.exit(0)\n"
+        "try:\n"
+        "    dist.init_process_group('gloo', rank=rank, world_size=2, timeout=datetime.timedelta(seconds=5))\n"
+        "    dist.barrier()\n"
+        "    print('UNEXPECTED')\n"
+        "except Exception as e:\n"
+        "    print('DETECTED', type(e).__name__)\n")
+    procs = []
+    for r in range(2):
+        e = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29633")
+        procs.append(subprocess.Popen([sys.executable, str(script)], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=e))
+    out0, _ = procs[0].communicate(timeout=120)
+    procs[1].wait(timeout=30)
+    assert "DETECTED" in out0 and "UNEXPECTED" not in out0
