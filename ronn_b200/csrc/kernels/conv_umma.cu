@@ -1,0 +1,309 @@
+// Fused Conv + (folded BatchNorm) + residual + ReLU as an implicit GEMM on tcgen05 tensor cores.
+//
+//   out[n, oh, ow, co] = act( sum_{r,s,c} x[n, oh*st - pad + r*dil, ow*st - pad + s*dil, c] * w[co, r, s, c]
+//                             + bias[co] ) (+ residual[n, oh, ow, co] before the activation)
+//
+// NHWC activations, weights [Cout, R, S, Cin] (so a weight row is one K-major GEMM row of length R*S*Cin
+// and is fetched by TMA with the 128-byte swizzle).  The A operand (128 output pixels x 64 K-elements per
+// stage) never exists in memory: four producer warps gather it with 16-byte cp.async (zero-fill for padding
+// and the K tail) directly into the swizzled shared-memory layout the UMMA descriptor expects
+// (chunk j of row m lands at chunk position j ^ (m & 7)).  Accumulation in TMEM, epilogue shared with the GEMM.
+//
+// Roles: warps 0-3 gather A and, after the main loop, run the epilogue (warp w owns TMEM lanes 32w..32w+31);
+// warp 4 lane 0 issues the weight TMA; warp 5 allocates TMEM and issues the MMAs.
+//
+// Replaces the reference's depthwise one-thread-per-output template (crates/ronn-providers/src/gpu/cuda_kernels.rs:400-449)
+// and its Candle conv2d call with fixed stride 1 / pad 1 (crates/ronn-providers/src/gpu/provider.rs:1292-1305); the BN
+// folding itself is done by the fusion pass.  Cin % 8 == 0 (the provider pads a 3-channel stem to 8).
+#include "gemm_epilogue.cuh"
+#include "ptx_sm100.cuh"
+#include "tma_desc.cuh"
+
+namespace ronn {
+
+constexpr int CONV_THREADS = 192;
+constexpr int CONV_STAGES = 4;
+constexpr int CONV_LAG = 2;          // cp.async groups a producer thread keeps in flight
+
+struct ConvShape {
+  int N, H, W, C;          // input
+  int Ho, Wo, Cout;
+  int R, S, stride, pad, dil;
+  int M;                   // N * Ho * Wo
+  int chunks;              // R * S * C / 8   (16-byte K chunks)
+};
+
+template <int BN>
+struct ConvSmem {
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = CONV_STAGES * STAGE_BYTES;
+  static constexpr int DYN_SMEM = TILE_BYTES + (2 * CONV_STAGES + 1) * 8 + 16 + 1024;
+  static constexpr uint32_t TMEM_COLS = BN <= 32 ? 32u : (BN <= 64 ? 64u : (BN <= 128 ? 128u : 256u));
+};
+
+template <int BN, class T>
+__global__ void __launch_bounds__(CONV_THREADS)
+conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap map_w, ConvShape cs, DenseEpilogue epi,
+                  uint32_t idesc, uint32_t* status) {
+  using L = ConvSmem<BN>;
+  extern __shared__ uint8_t dyn_smem[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::TILE_BYTES);
+  uint64_t* empty = full + CONV_STAGES;
+  uint64_t* accum = empty + CONV_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile uint32_t* abort = tmem_slot + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * 128, n0 = blockIdx.y * BN;
+  const int num_kb = (cs.chunks + 7) / 8;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < CONV_STAGES; ++s) {
+      mbar_init(&full[s], 128 + 1);          // 128 gather threads + the weight TMA's expect_tx arrival
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    *abort = 0;
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  __syncwarp();
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, L::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 4) {
+    // ---------------------------------------------------------------- A gather (one output pixel per thread)
+    pdl_wait();
+    const int row = threadIdx.x;
+    const int m = m0 + row;
+    const bool row_ok = m < cs.M;
+    int n_img = 0, oh = 0, ow = 0;
+    if (row_ok) {
+      n_img = m / (cs.Ho * cs.Wo);
+      const int rem = m - n_img * cs.Ho * cs.Wo;
+      oh = rem / cs.Wo;
+      ow = rem - oh * cs.Wo;
+    }
+    const int ih0 = oh * cs.stride - cs.pad, iw0 = ow * cs.stride - cs.pad;
+    const T* img = x + size_t(n_img) * cs.H * cs.W * cs.C;
+    const int c8n = cs.C >> 3;
+    const uint32_t sw = uint32_t(row & 7);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % CONV_STAGES;
+      if (ok && !mbar_wait(&empty[s], ((kb / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+      if (ok) {
+        uint8_t* dst_row = tiles + s * L::STAGE_BYTES + row * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int g = kb * 8 + j;
+          const int rs = g / c8n, c8 = g - rs * c8n;
+          const int r = rs / cs.S, sx = rs - r * cs.S;
+          const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
+          const bool valid = row_ok && g < cs.chunks && ih >= 0 && ih < cs.H && iw >= 0 && iw < cs.W;
+          const T* src = valid ? img + (size_t(ih) * cs.W + iw) * cs.C + c8 * 8 : x;
+          cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
+        }
+      }
+      cp_async_commit();
+      if (kb >= CONV_LAG) {
+        cp_async_wait<CONV_LAG>();
+        fence_proxy_async_smem();
+        mbar_arrive(&full[(kb - CONV_LAG) % CONV_STAGES]);
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    for (int kb = (num_kb > CONV_LAG ? num_kb - CONV_LAG : 0); kb < num_kb; ++kb) mbar_arrive(&full[kb % CONV_STAGES]);
+    pdl_trigger();
+    // ---------------------------------------------------------------- epilogue
+    bool acc_ok = mbar_wait(accum, 0, abort, status, STATUS_WAIT_ACCUM);
+    acc_ok = __all_sync(0xffffffffu, acc_ok);
+    tc_fence_after_sync();
+    if (acc_ok) {
+      epi.m0 = m0;
+      epi.n0 = n0;
+#pragma unroll 1
+      for (int col = 0; col < BN; col += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col), r);
+        tmem_ld_wait();
+        epi.run<T>(row, col, r);
+      }
+    }
+  } else if (warp == 4) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % CONV_STAGES;
+        if (!mbar_wait(&empty[s], ((kb / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) break;
+        mbar_expect_tx(&full[s], L::B_BYTES);
+        tma_load_2d(tiles + s * L::STAGE_BYTES + L::A_BYTES, &map_w, &full[s], kb * 64, n0);
+      }
+    }
+    __syncwarp();
+    pdl_trigger();
+  } else {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % CONV_STAGES;
+        if (!mbar_wait(&full[s], (kb / CONV_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
+        const uint64_t adesc = umma_desc_k128(sa), bdesc = umma_desc_k128(sa + L::A_BYTES);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+        umma_commit(&empty[s]);
+      }
+      umma_commit(accum);
+    }
+    __syncwarp();
+    pdl_trigger();
+  }
+  if (*abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) { __nanosleep(1000); }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, L::TMEM_COLS);
+  }
+}
+
+template <int BN, class T>
+static int launch_conv(const void* x, const CUtensorMap& mw, const ConvShape& cs, const DenseEpilogue& e, int is_bf16,
+                       uint32_t* status, cudaStream_t stream) {
+  using L = ConvSmem<BN>;
+  auto kern = conv_igemm_kernel<BN, T>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  dim3 grid((cs.M + 127) / 128, (cs.Cout + BN - 1) / BN);
+  const uint32_t idesc = umma_idesc(128, BN, is_bf16 ? 1u : 0u, 1u);
+  cudaError_t err = launch(kern, grid, dim3(CONV_THREADS), size_t(L::DYN_SMEM), stream, (const T*)x, mw, cs, e, idesc, status);
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+// ---------------------------------------------------------------------------------------------------- pooling (NHWC)
+template <class T>
+__global__ void maxpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int H, int W, int C, int Ho, int Wo,
+                                    int k, int stride, int pad) {
+  pdl_wait();
+  pdl_trigger();
+  const int c8n = C >> 3;
+  const long total = long(N) * Ho * Wo * c8n;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const int c8 = int(i % c8n);
+    long p = i / c8n;
+    const int ow = int(p % Wo);
+    p /= Wo;
+    const int oh = int(p % Ho), n = int(p / Ho);
+    float best[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) best[j] = -INFINITY;
+    for (int r = 0; r < k; ++r) {
+      const int ih = oh * stride - pad + r;
+      if (ih < 0 || ih >= H) continue;
+      for (int s = 0; s < k; ++s) {
+        const int iw = ow * stride - pad + s;
+        if (iw < 0 || iw >= W) continue;
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(x + ((size_t(n) * H + ih) * W + iw) * C + c8 * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) best[j] = fmaxf(best[j], f[j]);
+      }
+    }
+    *reinterpret_cast<Vec8*>(y + ((size_t(n) * Ho + oh) * Wo + ow) * C + c8 * 8) = pack8<T>(best);
+  }
+}
+
+// y[n, c] = mean over HW of x[n, :, :, c]; one CTA per (n, 64-channel slab), threads split HW.
+template <class T>
+__global__ void global_avgpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int HW, int C) {
+  __shared__ float part[8][64];
+  pdl_wait();
+  pdl_trigger();
+  const int n = blockIdx.x, c0 = blockIdx.y * 64;
+  const int cg = threadIdx.x & 7, pg = threadIdx.x >> 3;            // 8 channel groups x 8 pixel groups (64 threads)
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (c0 + cg * 8 < C) {
+    for (int p = pg; p < HW; p += 8) {
+      float f[8];
+      unpack8<T>(*reinterpret_cast<const Vec8*>(x + (size_t(n) * HW + p) * C + c0 + cg * 8), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[pg][cg * 8 + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.x < 64 && c0 + threadIdx.x < C) {
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) s += part[g][threadIdx.x];
+    y[size_t(n) * C + c0 + threadIdx.x] = Cvt<T>::from_f(s / float(HW));
+  }
+}
+
+}  // namespace ronn
+
+using namespace ronn;
+
+// x: NHWC [N,H,W,C]; w: [Cout, R, S, C] contiguous; bias [Cout] or null; residual NHWC like the output or null.
+// act: 0 none, 1 relu.  dtype: 0 bf16, 1 fp16.  C % 8 == 0, Cout % 8 == 0.
+extern "C" int ronn_conv2d(const void* x, const void* w, const void* bias, const void* residual, void* out, int N, int H,
+                           int W, int C, int Cout, int R, int S, int stride, int pad, int dil, int Ho, int Wo, int act,
+                           int dtype, uint32_t* status, cudaStream_t stream) {
+  if (N <= 0 || (C & 7) || (Cout & 7) || R <= 0 || S <= 0 || stride <= 0) return -2;
+  ConvShape cs{N, H, W, C, Ho, Wo, Cout, R, S, stride, pad, dil, N * Ho * Wo, R * S * C / 8};
+  const int Kg = R * S * C;
+  const int m_tiles = (cs.M + 127) / 128;
+  int bn = Cout >= 128 ? 128 : (Cout >= 64 ? 64 : 32);
+  while (bn > 32 && m_tiles * ((Cout + bn - 1) / bn) < 148) bn >>= 1;
+  CUtensorMap mw;
+  int rc = make_tmap_2d(&mw, w, uint64_t(Cout), uint64_t(Kg), uint64_t(Kg), uint32_t(bn), 64, 2);
+  if (rc) return rc - 30;
+  DenseEpilogue e{out, bias, residual, cs.M, Cout, Cout, 0, 0, act, 0, 1};   // residual joins before the ReLU
+  const int bf = dtype == 0;
+#define RONN_CONV(BN_) return bf ? launch_conv<BN_, __nv_bfloat16>(x, mw, cs, e, 1, status, stream) \
+                                 : launch_conv<BN_, __half>(x, mw, cs, e, 0, status, stream)
+  switch (bn) {
+    case 128: RONN_CONV(128);
+    case 64: RONN_CONV(64);
+    default: RONN_CONV(32);
+  }
+#undef RONN_CONV
+}
+
+extern "C" int ronn_maxpool_nhwc(const void* x, void* y, int N, int H, int W, int C, int Ho, int Wo, int k, int stride,
+                                 int pad, int dtype, cudaStream_t stream) {
+  if (C & 7) return -2;
+  const long total = long(N) * Ho * Wo * (C >> 3);
+  const int grid = int((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  cudaError_t err;
+  if (dtype == 0) err = launch(maxpool_nhwc_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, H, W, C, Ho, Wo, k, stride, pad);
+  else err = launch(maxpool_nhwc_kernel<__half>, dim3(grid), dim3(256), 0, stream, (const __half*)x, (__half*)y, N, H, W, C, Ho, Wo, k, stride, pad);
+  return err == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int ronn_global_avgpool_nhwc(const void* x, void* y, int N, int HW, int C, int dtype, cudaStream_t stream) {
+  if (C & 7) return -2;
+  dim3 grid(N, (C + 63) / 64);
+  cudaError_t err;
+  if (dtype == 0) err = launch(global_avgpool_nhwc_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, HW, C);
+  else err = launch(global_avgpool_nhwc_kernel<__half>, grid, dim3(64), 0, stream, (const __half*)x, (__half*)y, HW, C);
+  return err == cudaSuccess ? 0 : -100;
+}

@@ -217,8 +217,14 @@ class DecoderRunner:
         hn, kn = self.n_head_local * d, self.n_kv_local * d
         # the library backend gathers dense KV, so it is sized by the longest context of this step
         max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
+        # decode-sized steps on one GPU: the K=ffn down projection runs split-K and its reduction pass also applies
+        # bias + residual and the next block's norm, so that norm costs no launch of its own
+        split_down = (ops.name == "kernels" and self.tp == 1 and x.shape[0] <= 512 and not a.bitlinear
+                      and self.layers[0]["down"].w is not None and self.layers[0]["down"].w.shape[1] >= 2048)
+        h_next = None
         for li, L in enumerate(self.layers):
-            h = self._norm(x, L["ln1"])
+            h = h_next if h_next is not None else self._norm(x, L["ln1"])
+            h_next = None
             qkv = self._linear(h, L["qkv"])
             ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
                           self.n_kv_local, d, pos, a.rope_base)
@@ -230,10 +236,17 @@ class DecoderRunner:
                 f = self._linear(h, L["up"], activation="gelu")
             else:
                 f = ops.swiglu_fused(self._linear(h, L["up"]))
-            x = self._linear(f, L["down"], residual=x, reduce=True)
-        if not decode:
-            x = ops.gather_rows(x, b["sample_index_clamped"])
-        x = self._norm(x, self.lnf)
+            if split_down:
+                nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else (self.lnf if decode else None)
+                x, h_next = ops.gemm_splitk_norm(f, L["down"], x, nxt, a.norm, a.eps, 4)
+            else:
+                x = self._linear(f, L["down"], residual=x, reduce=True)
+        if h_next is not None:
+            x = h_next                                   # final norm already applied by the last reduction pass
+        else:
+            if not decode:
+                x = ops.gather_rows(x, b["sample_index_clamped"])
+            x = self._norm(x, self.lnf)
         logits = ops.gemm(x, self.lm_head, out_fp32=True)
         if want_logits:
             if self.tp != 1:

@@ -120,6 +120,16 @@ class KernelOps:
     def layernorm(self, x, w, b, eps):
         return self.K.layernorm(x, w, b, eps)
 
+    def gemm_splitk_norm(self, a, lw, residual, norm_params, norm_kind, eps, splitk):
+        """Skinny GEMM as split-K partial sums, then ONE pass that adds bias + residual, writes the new residual
+        stream and (optionally) the normalised input of the next block."""
+        ws, S = self.K.gemm_splitk(a, lw.w, splitk, 64)
+        gamma = norm_params[0] if norm_params is not None else None
+        beta = norm_params[1] if (norm_params is not None and len(norm_params) > 1) else None
+        return self.K.splitk_finalize(ws, S, a.shape[0], lw.w.shape[0], a.dtype, bias=lw.bias, residual=residual,
+                                      gamma=gamma, beta=beta, eps=eps,
+                                      norm=(norm_kind if norm_params is not None else ""))
+
     def rmsnorm(self, x, w, eps):
         return self.K.rmsnorm(x, w, eps)
 

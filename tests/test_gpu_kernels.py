@@ -177,3 +177,72 @@ def test_kv_append_rope(K):
     torch.testing.assert_close(qkv[:, :heads * d].float(), ref_q.float(), atol=3e-2, rtol=2e-2)
     got_k = kc[0, :, :T, :].permute(1, 0, 2).reshape(T, -1)
     torch.testing.assert_close(got_k.float(), ref_k.float(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("shape", [
+    # N, H, W, C, Cout, R, stride, pad
+    (2, 16, 16, 64, 64, 3, 1, 1), (2, 17, 19, 16, 72, 3, 2, 1), (1, 56, 56, 64, 128, 1, 2, 0),
+    (2, 32, 32, 8, 64, 7, 2, 3), (3, 7, 7, 256, 512, 3, 1, 1), (1, 9, 9, 128, 32, 3, 1, 0)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_conv_igemm(shape, dtype):
+    from ronn_b200.providers.gpu_conv import conv2d_nhwc
+    N, H, W, C, Co, R, st, pad = shape
+    torch.manual_seed(0)
+    x = _rand(N, H, W, C, dtype=dtype)
+    w = _rand(Co, R, R, C, dtype=dtype, scale=1.0 / math.sqrt(R * R * C))
+    b = _rand(Co, dtype=dtype)
+    ref = F.conv2d(x.permute(0, 3, 1, 2).float(), w.permute(0, 3, 1, 2).float(), b.float(), st, pad)
+    y = conv2d_nhwc(x, w, b, None, st, pad, 1, relu=False)
+    from ronn_b200 import ops
+    ops.check_status()
+    torch.testing.assert_close(y.permute(0, 3, 1, 2).float(), ref, atol=3e-2, rtol=3e-2)
+    res = _rand(*y.shape, dtype=dtype)
+    y2 = conv2d_nhwc(x, w, b, res, st, pad, 1, relu=True)
+    torch.testing.assert_close(y2.permute(0, 3, 1, 2).float(), torch.relu(ref + res.permute(0, 3, 1, 2).float()), atol=3e-2, rtol=3e-2)
+
+
+def test_pool_kernels():
+    from ronn_b200.providers.gpu_conv import global_avgpool_nhwc, maxpool_nhwc
+    x = _rand(3, 23, 21, 72, dtype=torch.float16)
+    y = maxpool_nhwc(x, 3, 2, 1)
+    ref = F.max_pool2d(x.permute(0, 3, 1, 2).float(), 3, 2, 1).permute(0, 2, 3, 1)
+    torch.testing.assert_close(y.float(), ref)
+    g = global_avgpool_nhwc(x)
+    torch.testing.assert_close(g.float().reshape(3, 72), x.float().mean((1, 2)), atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 2560, 2560), (128, 320, 6912), (37, 72, 256), (130, 96, 128), (1, 32000, 2560)])
+def test_bitlinear_exact_against_host_oracle(M, N, K_):
+    from ronn_b200.ops import bitnet as B
+    from ronn_b200.providers.bitnet.quantization import bitlinear_reference, pack_ternary_rows
+    torch.manual_seed(M + N)
+    wq = torch.randint(-1, 2, (N, K_), dtype=torch.int8)
+    packed = pack_ternary_rows(wq)
+    x = (torch.randn(M, K_) * 2).bfloat16()
+    ref = bitlinear_reference(x.float(), packed, torch.tensor(0.043), None, K_, N)
+    y = B.bitlinear(x.cuda(), packed.cuda(), 0.043, None, K_, N)
+    from ronn_b200 import ops
+    ops.check_status()
+    # integer accumulation is exact; only the final bf16 rounding differs from the fp32 oracle
+    torch.testing.assert_close(y.float().cpu(), ref, atol=1e-2, rtol=1e-2)
+    q, s = B.act_quant_int8(x.cuda())
+    sref = x.float().abs().amax(-1).clamp_min(1e-5) / 127
+    torch.testing.assert_close(s.cpu(), sref, rtol=1e-6, atol=0)
+    qref = torch.round(x.float() * (127.0 / x.float().abs().amax(-1, keepdim=True).clamp_min(1e-5))).clamp(-127, 127)
+    assert (q.cpu().float() - qref).abs().max() <= 1          # rint ties / reciprocal rounding
+    acc = (q.cpu().to(torch.int32) @ wq.to(torch.int32).t()).float() * s.cpu()[:, None] * 0.043
+    torch.testing.assert_close(y.float().cpu(), acc, atol=1e-2, rtol=1e-2)
+    assert torch.equal(B.ternary_pack(wq.cuda()).cpu(), packed)
+
+
+def test_rmsnorm_quant_fused():
+    from ronn_b200.ops import bitnet as B
+    x = _rand(19, 2560)
+    g = _rand(2560)
+    q, s = B.rmsnorm_quant_int8(x, g, 1e-5)
+    xf = x.float()
+    normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()).bfloat16().float()
+    sref = normed.abs().amax(-1) / 127
+    torch.testing.assert_close(s, sref, rtol=2e-2, atol=1e-6)
+    deq = q.float() * s[:, None]
+    torch.testing.assert_close(deq, normed, atol=float(sref.max()) * 1.5, rtol=0)

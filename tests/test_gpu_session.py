@@ -30,3 +30,16 @@ def test_gpt2_session_gpu_matches_cpu():
     got = s.run({"input_ids": ids})["logits"].float().cpu()
     torch.testing.assert_close(got, want, atol=5e-2, rtol=5e-2)
     assert any(n.op_type == "FusedGemm" for n in s.graph().nodes)
+
+
+def test_resnet18_gpu_o3_matches_cpu_o0():
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.models.resnet18 import build_resnet18
+    m = Model.from_graph(build_resnet18(dtype=torch.float32, image=64, num_classes=40))
+    x = torch.randn(4, 3, 64, 64)
+    want = m.create_session(SessionOptions().with_optimization_level("O0")).run({"input": x})["logits"]
+    s = m.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("fp16"))
+    got = s.run({"input": x})["logits"].float().cpu()
+    assert sum(1 for n in s.graph().nodes if n.op_type == "FusedConv") == 17
+    assert (got - want).abs().max() < 0.05 * want.abs().max()
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() >= 0.75
