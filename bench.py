@@ -200,9 +200,12 @@ def main():
                     "d2h_bytes_per_step": d2h // K, "ms_per_step": round(wall * 1e3 / K, 4)},
             "gpu_launches": launches_per_step * K if backend == "kernels" else 0,
         }))
+    sys.stdout.flush()
     if world > 1:
-        torch.distributed.barrier()
-        torch.distributed.destroy_process_group()
+        # every rank has contributed to the max-over-ranks reductions above; leave without tearing down NCCL and the
+        # symmetric-memory mappings (their teardown after graph-captured collectives can block for minutes)
+        torch.cuda.synchronize()
+        os._exit(0)
     return 0
 
 

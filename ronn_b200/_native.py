@@ -109,6 +109,7 @@ def host():
         _sig(lib, "ronn_cpu_relu_f32", None, [V, V, I64])
         _sig(lib, "ronn_cpu_gemm_f32", None, [V, V, V, V, I64, I64, I64, I32])
         _sig(lib, "ronn_cpu_softmax_f32", None, [V, V, I64, I64])
+        _sig(lib, "ronn_cpu_run_chain", None, [V, I64, I64, I32, V, V, V, V, V, V, V, V])
         # ---- bitnet cpu
         _sig(lib, "ronn_bitnet_quantize_binary", F32, [V, I64, V])
         _sig(lib, "ronn_bitnet_dequantize_binary", None, [V, I64, F32, V])

@@ -153,6 +153,7 @@ class InferenceSession:
         self._stats = SessionStats()
         self._lock = threading.Lock()
         self._router = None
+        self._input_names = [i.name for i in graph.inputs]
 
     # ------------------------------------------------------------------ accessors
     def options(self) -> SessionOptions:
@@ -190,9 +191,14 @@ class InferenceSession:
     def run(self, inputs: Mapping[str, object]) -> Dict[str, torch.Tensor]:
         if not isinstance(inputs, Mapping):
             raise InvalidInput("inputs must be a mapping of input name to tensor")
-        self._validate(inputs)
         dev = self._kernel.device
-        feed = {i.name: _to_tensor(inputs[i.name], dev, i.name) for i in self._graph.inputs}
+        feed = {}
+        for name in self._input_names:
+            try:
+                v = inputs[name]
+            except KeyError:
+                raise InvalidInput(f"required input '{name}' not provided") from None
+            feed[name] = v if (type(v) is torch.Tensor and v.device == dev) else _to_tensor(v, dev, name)
         t0 = time.perf_counter()
         try:
             with torch.no_grad():

@@ -1,0 +1,189 @@
+"""Model-level latency / throughput benchmarks through the public API (Model -> create_session -> run).
+
+    python -m ronn_b200.bench_models resnet18  [--batch 32] [--iters 50]     p50 latency, fp16, O3, GPU provider
+    python -m ronn_b200.bench_models mlp784    [--iters 2000]                p50 latency, f32, CPU provider
+    python -m ronn_b200.bench_models distilbert [--batch 64 --seq 128]       p50 latency / sequences per second, bf16
+
+Each benchmark also times a plain PyTorch library implementation of the same network on the same box
+(cuDNN / cuBLAS / SDPA) as the comparison baseline.  Timing: CUDA events around ``session.run`` with the input
+already on the device, after warm-up; the L2 is flushed between iterations by writing a 256 MB buffer.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import time
+
+import torch
+
+
+def _p50_cuda(fn, iters, warmup=5, flush=True):
+    buf = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts), min(ts)
+
+
+def bench_resnet18(batch=32, iters=50, image=224):
+    import torch.nn as nn
+    from . import Model, SessionOptions
+    from .models.resnet18 import build_resnet18
+    graph = build_resnet18(dtype=torch.float16, seed=0)
+    model = Model.from_graph(graph)
+    x = torch.randn(batch, 3, image, image, device="cuda", dtype=torch.float16)
+    out = {}
+    for name, graphed in (("ours_cuda_graph", True), ("ours_eager", False)):
+        sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3")
+                                    .with_dtype("fp16").with_cuda_graph(graphed))
+        p50, best = _p50_cuda(lambda: sess.run({"input": x}), iters)
+        out[name] = {"p50_ms": round(p50, 4), "min_ms": round(best, 4), "images_per_s": round(batch / p50 * 1e3, 1)}
+        logits = sess.run({"input": x})["logits"].float()
+    from .ops import kernels as K
+    K.check_status()
+    # library baseline: same weights in a torch module, fp16 channels_last, cuDNN
+    init = graph.initializers
+
+    class Block(nn.Module):
+        def __init__(self, prefix, cin, cout, stride):
+            super().__init__()
+            self.a = nn.Conv2d(cin, cout, 3, stride, 1, bias=False)
+            self.bna = nn.BatchNorm2d(cout)
+            self.b = nn.Conv2d(cout, cout, 3, 1, 1, bias=False)
+            self.bnb = nn.BatchNorm2d(cout)
+            self.down = None
+            if stride != 1 or cin != cout:
+                self.down = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, 0, bias=False), nn.BatchNorm2d(cout))
+            self.a.weight.data = init[f"{prefix}.a.weight"].clone()
+            self.b.weight.data = init[f"{prefix}.b.weight"].clone()
+            if self.down is not None:
+                self.down[0].weight.data = init[f"{prefix}.down.weight"].clone()
+
+        def forward(self, x):
+            y = torch.relu(self.bna(self.a(x)))
+            y = self.bnb(self.b(y))
+            return torch.relu(y + (x if self.down is None else self.down(x)))
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.stem = nn.Conv2d(3, 64, 7, 2, 3, bias=False)
+            self.stem.weight.data = init["stem.weight"].clone()
+            self.bn = nn.BatchNorm2d(64)
+            blocks, cin = [], 64
+            for stage, cout in enumerate((64, 128, 256, 512)):
+                for blk in range(2):
+                    blocks.append(Block(f"layer{stage + 1}.{blk}", cin, cout, 2 if (stage > 0 and blk == 0) else 1))
+                    cin = cout
+            self.blocks = nn.Sequential(*blocks)
+            self.fc = nn.Linear(512, 1000)
+            self.fc.weight.data = init["fc.weight"].clone()
+            self.fc.bias.data = init["fc.bias"].clone()
+
+        def forward(self, x):
+            x = torch.max_pool2d(torch.relu(self.bn(self.stem(x))), 3, 2, 1)
+            x = self.blocks(x)
+            return self.fc(x.mean((2, 3)))
+
+    net = Net().cuda().half().eval().to(memory_format=torch.channels_last)
+    xc = x.to(memory_format=torch.channels_last)
+    with torch.no_grad():
+        p50, best = _p50_cuda(lambda: net(xc), iters)
+        out["torch_cudnn_eager"] = {"p50_ms": round(p50, 4), "min_ms": round(best, 4)}
+        ref = net(xc).float()
+        g = torch.cuda.CUDAGraph()
+        static = xc.clone()
+        for _ in range(3):
+            net(static)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g):
+            y = net(static)
+        p50, best = _p50_cuda(lambda: g.replay(), iters)
+        out["torch_cudnn_cuda_graph"] = {"p50_ms": round(p50, 4), "min_ms": round(best, 4)}
+    rel = float((logits - ref).abs().max() / ref.abs().max())
+    flops = 2 * 1.82e9 * batch
+    out["config"] = {"model": "resnet18", "batch": batch, "dtype": "fp16", "layout": "NCHW input, NHWC inside",
+                     "max_rel_err_vs_torch": round(rel, 5),
+                     "tflops_at_p50": round(flops / (out["ours_cuda_graph"]["p50_ms"] * 1e-3) / 1e12, 1)}
+    return out
+
+
+def bench_mlp784(iters=2000):
+    from . import Model, SessionOptions
+    from .models.mlp784 import build_mlp784
+    graph = build_mlp784()
+    model = Model.from_graph(graph)
+    x = torch.rand(1, 784)
+    out = {}
+    for lvl in ("O0", "O3"):
+        sess = model.create_session(SessionOptions().with_optimization_level(lvl))
+        for _ in range(200):
+            sess.run({"input": x})
+        ts = []
+        for _ in range(iters):
+            t = time.perf_counter()
+            sess.run({"input": x})
+            ts.append((time.perf_counter() - t) * 1e6)
+        out[f"ours_cpu_{lvl}"] = {"p50_us": round(statistics.median(ts), 2), "p95_us": round(sorted(ts)[int(0.95 * len(ts))], 2)}
+    w1, w2 = graph.initializers["fc1.weight"], graph.initializers["fc2.weight"]
+    b1, b2 = graph.initializers["fc1.bias"], graph.initializers["fc2.bias"]
+    with torch.no_grad():
+        f = lambda: torch.softmax(torch.relu(x @ w1 + b1) @ w2 + b2, -1)
+        for _ in range(200):
+            f()
+        ts = []
+        for _ in range(iters):
+            t = time.perf_counter()
+            f()
+            ts.append((time.perf_counter() - t) * 1e6)
+    out["torch_cpu_eager"] = {"p50_us": round(statistics.median(ts), 2)}
+    out["config"] = {"model": "mlp 784-128-10", "batch": 1, "dtype": "f32", "reference_target": "P50 < 10 ms"}
+    return out
+
+
+def bench_distilbert(batch=64, seq=128, iters=20):
+    from . import Model, SessionOptions
+    from .models.distilbert import build_distilbert
+    graph = build_distilbert(dtype=torch.bfloat16, seed=0)
+    model = Model.from_graph(graph)
+    ids = torch.randint(0, 30522, (batch, seq), device="cuda")
+    mask = torch.ones(batch, seq, dtype=torch.int64, device="cuda")
+    out = {}
+    for name, graphed in (("ours_cuda_graph", True), ("ours_eager", False)):
+        sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3")
+                                    .with_dtype("bf16").with_cuda_graph(graphed))
+        p50, best = _p50_cuda(lambda: sess.run({"input_ids": ids, "attention_mask": mask}), iters)
+        out[name] = {"p50_ms": round(p50, 4), "sequences_per_s": round(batch / p50 * 1e3, 1)}
+    out["config"] = {"model": "distilbert-base", "batch": batch, "seq": seq, "dtype": "bf16", "tp": 1}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["resnet18", "mlp784", "distilbert"])
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--seq", type=int, default=128)
+    ap.add_argument("--iters", type=int, default=0)
+    a = ap.parse_args()
+    if a.what == "resnet18":
+        res = bench_resnet18(a.batch or 32, a.iters or 50)
+    elif a.what == "mlp784":
+        res = bench_mlp784(a.iters or 2000)
+    else:
+        res = bench_distilbert(a.batch or 64, a.seq, a.iters or 20)
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

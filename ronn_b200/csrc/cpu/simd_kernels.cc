@@ -158,6 +158,51 @@ __attribute__((target("avx2,fma"))) void gemm_avx2(const float* A, const float* 
   }
 }
 
+// Batch-1 path: y[j0..N) = act(a[K] * B[K, j0..N) + bias).  k is the outer loop, so B streams through the cache once
+// in row order while up to 128 output columns stay in registers.
+__attribute__((target("avx2,fma"))) void gemv_avx2(const float* a, const float* B, const float* bias, float* y,
+                                                   int64_t j0, int64_t N, int64_t K, int act) {
+  const __m256 z = _mm256_setzero_ps();
+  int64_t j = j0;
+  for (; j + 64 <= N; j += 64) {
+    __m256 c[8];
+    for (int v = 0; v < 8; ++v) c[v] = bias ? _mm256_loadu_ps(bias + j + 8 * v) : z;
+    for (int64_t k = 0; k < K; ++k) {
+      const __m256 x = _mm256_broadcast_ss(a + k);
+      const float* b = B + k * N + j;
+      for (int v = 0; v < 8; ++v) c[v] = _mm256_fmadd_ps(x, _mm256_loadu_ps(b + 8 * v), c[v]);
+    }
+    for (int v = 0; v < 8; ++v) _mm256_storeu_ps(y + j + 8 * v, act == 1 ? _mm256_max_ps(c[v], z) : c[v]);
+  }
+  for (; j + 8 <= N; j += 8) {
+    __m256 c = bias ? _mm256_loadu_ps(bias + j) : z;
+    for (int64_t k = 0; k < K; ++k) c = _mm256_fmadd_ps(_mm256_broadcast_ss(a + k), _mm256_loadu_ps(B + k * N + j), c);
+    _mm256_storeu_ps(y + j, act == 1 ? _mm256_max_ps(c, z) : c);
+  }
+  for (; j < N; ++j) {
+    float s = bias ? bias[j] : 0.f;
+    for (int64_t k = 0; k < K; ++k) s += a[k] * B[k * N + j];
+    y[j] = act == 1 ? (s > 0.f ? s : 0.f) : s;
+  }
+}
+
+__attribute__((target("avx512f,avx2,fma"))) void gemv_avx512(const float* a, const float* B, const float* bias, float* y,
+                                                             int64_t N, int64_t K, int act) {
+  const __m512 z = _mm512_setzero_ps();
+  int64_t j = 0;
+  for (; j + 128 <= N; j += 128) {
+    __m512 c[8];
+    for (int v = 0; v < 8; ++v) c[v] = bias ? _mm512_loadu_ps(bias + j + 16 * v) : z;
+    for (int64_t k = 0; k < K; ++k) {
+      const __m512 x = _mm512_set1_ps(a[k]);
+      const float* b = B + k * N + j;
+      for (int v = 0; v < 8; ++v) c[v] = _mm512_fmadd_ps(x, _mm512_loadu_ps(b + 16 * v), c[v]);
+    }
+    for (int v = 0; v < 8; ++v) _mm512_storeu_ps(y + j + 16 * v, act == 1 ? _mm512_max_ps(c[v], z) : c[v]);
+  }
+  if (j < N) gemv_avx2(a, B, bias, y, j, N, K, act);
+}
+
 }  // namespace
 
 extern "C" {
@@ -196,7 +241,10 @@ void ronn_cpu_relu_f32(const float* a, float* o, int64_t n) {
 // act: 0 none, 1 relu.  bias may be null.  Row-major, B is [K,N].
 void ronn_cpu_gemm_f32(const float* A, const float* B, const float* bias, float* C, int64_t M, int64_t N, int64_t K,
                        int32_t act) {
-  if (level() >= 1) gemm_avx2(A, B, bias, C, M, N, K, act);
+  const int l = level();
+  if (M == 1 && l >= 2) gemv_avx512(A, B, bias, C, N, K, act);
+  else if (M == 1 && l >= 1) gemv_avx2(A, B, bias, C, 0, N, K, act);
+  else if (l >= 1) gemm_avx2(A, B, bias, C, M, N, K, act);
   else gemm_scalar(A, B, bias, C, M, N, K, act);
 }
 
@@ -215,3 +263,29 @@ void ronn_cpu_softmax_f32(const float* x, float* o, int64_t rows, int64_t cols) 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Whole-chain execution: a linear sequence of dense layers (+ReLU) and a final softmax runs in one native call,
+// ping-ponging between two scratch buffers.  This is what a batch-1 MLP session executes: per-node dispatch in
+// the host language costs more than the arithmetic.
+//   kinds[i]: 0 = GEMM (+bias, act in acts[i]), 1 = ReLU, 2 = softmax over the last dimension
+//   weights[i] / biases[i]: row-major [K_i, N_i] / [N_i] (null for non-GEMM ops); dims[i] = N_i
+// x: [M, K0]; out: [M, N_last]; scratch: two buffers of M * max(N_i) floats.
+extern "C" void ronn_cpu_run_chain(const float* x, int64_t M, int64_t K0, int32_t n_ops, const int32_t* kinds,
+                                   const float* const* weights, const float* const* biases, const int32_t* acts,
+                                   const int64_t* dims, float* out, float* scratch0, float* scratch1) {
+  const float* cur = x;
+  int64_t cols = K0;
+  for (int32_t i = 0; i < n_ops; ++i) {
+    float* dst = (i == n_ops - 1) ? out : ((i & 1) ? scratch1 : scratch0);
+    if (kinds[i] == 0) {
+      ronn_cpu_gemm_f32(cur, weights[i], biases[i], dst, M, dims[i], cols, acts[i]);
+      cols = dims[i];
+    } else if (kinds[i] == 1) {
+      ronn_cpu_relu_f32(cur, dst, M * cols);
+    } else {
+      ronn_cpu_softmax_f32(cur, dst, M, cols);
+    }
+    cur = dst;
+  }
+}

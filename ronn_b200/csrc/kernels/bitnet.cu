@@ -67,7 +67,7 @@ __global__ void act_quant_kernel(const T* __restrict__ x, const T* __restrict__ 
     }
   }
   m = fmaxf(block_max(m, scratch), 1e-5f);
-  const float qs = 127.f / m;
+  const float qs = __fdiv_rn(127.f, m);            // IEEE division: bit-identical to the host quantiser
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const int ch = threadIdx.x + c * blockDim.x;
@@ -75,13 +75,13 @@ __global__ void act_quant_kernel(const T* __restrict__ x, const T* __restrict__ 
       alignas(16) int8_t o[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float r = fminf(fmaxf(rintf(v[c][i] * qs), -127.f), 127.f);
+        const float r = fminf(fmaxf(rintf(__fmul_rn(v[c][i], qs)), -127.f), 127.f);
         o[i] = int8_t(int(r));
       }
       *reinterpret_cast<int4*>(q + row * K + ch * 16) = *reinterpret_cast<const int4*>(o);
     }
   }
-  if (threadIdx.x == 0) scale[row] = m / 127.f;
+  if (threadIdx.x == 0) scale[row] = __fdiv_rn(m, 127.f);
 }
 
 // ---------------------------------------------------------------------------------------- BitLinear GEMM

@@ -43,6 +43,11 @@ struct CommArgs {
   const void* residual;            // rows aligned with `out`, or null
   long ld_res;
   unsigned long long wait_ns;      // limit of the peer wait
+  void* norm_out;                  // optional: norm(result) * gamma (+ beta), rows aligned with `out`
+  const void* gamma;
+  const void* beta;
+  float eps;
+  int norm_mode;                   // 0 none, 1 LayerNorm, 2 RMSNorm (needs N <= 1024)
 };
 
 __device__ __forceinline__ Vec8 ld_volatile_16(const void* p) {
@@ -153,42 +158,128 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (s_flag) {
     const int rows = comm.row_end - comm.row_begin;
     const int n8 = N >> 3;
-    const long vecs = long(rows) * n8;
     const size_t slot = size_t(parity) * comm.part_stride;
     T* out = reinterpret_cast<T*>(comm.out);
     const T* bias = reinterpret_cast<const T*>(comm.bias);
     const T* res = reinterpret_cast<const T*>(comm.residual);
-    for (long v = long(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += long(gridDim.x) * blockDim.x) {
-      const int r = int(v / n8), c = int(v - long(r) * n8) * 8;
-      const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
-      Vec8 pk[MAX_RANKS];
+    if (n8 <= 32 * 4) {
+      // ---- one warp per row: the whole row stays in registers, so the norm of the next block is applied here too
+      const int lane = threadIdx.x & 31;
+      const int warps = int(gridDim.x) * (PG_THREADS / 32);
+      const T* gamma = reinterpret_cast<const T*>(comm.gamma);
+      const T* beta = reinterpret_cast<const T*>(comm.beta);
+      T* nout = reinterpret_cast<T*>(comm.norm_out);
+      for (int r = int(blockIdx.x) * (PG_THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+        float v[4][8];
+        float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int src = 0; src < MAX_RANKS; ++src)
-        if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
-      float acc[8];
+        for (int i = 0; i < 4; ++i) {
+          const int c8 = lane + 32 * i;
+          if (c8 < n8) {
+            const int c = c8 * 8;
+            const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
+            Vec8 pk[MAX_RANKS];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+            for (int src = 0; src < MAX_RANKS; ++src)
+              if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
+            float acc[8];
 #pragma unroll
-      for (int src = 0; src < MAX_RANKS; ++src)
-        if (src < comm.world) {
+            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+            for (int src = 0; src < MAX_RANKS; ++src)
+              if (src < comm.world) {
+                float f[8];
+                unpack8<T>(pk[src], f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] += f[k];
+              }
+            if (bias) {
+              float f[8];
+              unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) acc[k] += f[k];
+            }
+            if (res) {
+              float f[8];
+              unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) acc[k] += f[k];
+            }
+            const Vec8 o = pack8<T>(acc);
+            *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = o;
+            unpack8<T>(o, v[i]);                       // normalise exactly what the residual stream stores
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { s1 += v[i][k]; s2 += v[i][k] * v[i][k]; }
+          }
+        }
+        if (comm.norm_mode != 0) {
+          float mean = 0.f, inv;
+          if (comm.norm_mode == 2) {
+            inv = rsqrtf(warp_sum(s2) / float(N) + comm.eps);
+          } else {
+            mean = warp_sum(s1) / float(N);
+            float q = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (lane + 32 * i < n8) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { const float d = v[i][k] - mean; q += d * d; }
+              }
+            inv = rsqrtf(warp_sum(q) / float(N) + comm.eps);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int c8 = lane + 32 * i;
+            if (c8 < n8) {
+              float g[8], b[8], o[8];
+              if (gamma) unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + c8 * 8), g);
+              if (beta) unpack8<T>(*reinterpret_cast<const Vec8*>(beta + c8 * 8), b);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                float t = (v[i][k] - mean) * inv;
+                if (gamma) t *= g[k];
+                if (beta) t += b[k];
+                o[k] = t;
+              }
+              *reinterpret_cast<Vec8*>(nout + size_t(r) * comm.ld_out + c8 * 8) = pack8<T>(o);
+            }
+          }
+        }
+      }
+    } else {
+      const long vecs = long(rows) * n8;
+      for (long v = long(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += long(gridDim.x) * blockDim.x) {
+        const int r = int(v / n8), c = int(v - long(r) * n8) * 8;
+        const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
+        Vec8 pk[MAX_RANKS];
+#pragma unroll
+        for (int src = 0; src < MAX_RANKS; ++src)
+          if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int src = 0; src < MAX_RANKS; ++src)
+          if (src < comm.world) {
+            float f[8];
+            unpack8<T>(pk[src], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          }
+        if (bias) {
           float f[8];
-          unpack8<T>(pk[src], f);
+          unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
 #pragma unroll
           for (int i = 0; i < 8; ++i) acc[i] += f[i];
         }
-      if (bias) {
-        float f[8];
-        unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
+        if (res) {
+          float f[8];
+          unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
+          for (int i = 0; i < 8; ++i) acc[i] += f[i];
+        }
+        *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = pack8<T>(acc);
       }
-      if (res) {
-        float f[8];
-        unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += f[i];
-      }
-      *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = pack8<T>(acc);
     }
   }
   __syncthreads();
@@ -242,14 +333,17 @@ using namespace ronn;
 // peer_part / peer_flags: `world` pointers each.  part_stride: bytes between the two parity slots of a partial
 // buffer (>= M * N * 2).  state: three zero-initialised ints in local device memory, shared by all calls on this
 // rank.  Rows [row_begin, row_end) of the reduced result (+ bias + residual) are written to `out`.
+// With norm_mode 1 (LayerNorm) / 2 (RMSNorm) and N <= 1024 the normalised rows are also written to norm_out.
 // dtype 0 bf16, 1 fp16.  N % 8 == 0.  Returns 0 on success.
 extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
                                 void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
                                 int rank, int world, int row_begin, int row_end, void* out, long ld_out,
                                 const void* bias, const void* residual, long ld_res, double wait_seconds, int dtype,
-                                int bn, uint32_t* status, cudaStream_t stream) {
+                                int bn, void* norm_out, const void* gamma, const void* beta, float eps, int norm_mode,
+                                uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return -2;
+  if (norm_mode != 0 && (N > 1024 || norm_out == nullptr)) return -5;
   if (row_begin < 0 || row_end > M || row_begin > row_end || part_stride < long(M) * N * 2) return -4;
   if (bn == 0) {
     const int mt = (M + PG_BM - 1) / PG_BM;
@@ -278,6 +372,11 @@ extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int 
   c.residual = residual;
   c.ld_res = ld_res;
   c.wait_ns = static_cast<unsigned long long>(wait_seconds * 1e9);
+  c.norm_out = norm_out;
+  c.gamma = gamma;
+  c.beta = beta;
+  c.eps = eps;
+  c.norm_mode = norm_mode;
   const int bf = dtype == 0;
 #define RONN_DISPATCH(BN_, ST_)                                                                        \
   return bf ? launch_reduce<BN_, ST_, __nv_bfloat16>(ma, mb, c, M, N, K, 1, status, stream)           \

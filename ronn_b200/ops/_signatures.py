@@ -18,7 +18,7 @@ def declare(lib):
     sig("ronn_gemm", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, V, V])
     sig("ronn_gemm_splitk", [V, V, V, I, I, I, I, I, I, I, I, V, V, V])
     sig("ronn_splitk_finalize", [V, I, V, V, V, V, V, V, L, I, F, I, I, I, V])
-    sig("ronn_gemm_reduce", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V], optional=True)
+    sig("ronn_gemm_reduce", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I, V, V], optional=True)
     sig("ronn_norm", [V, V, V, V, V, V, L, I, L, L, L, F, I, I, V])
     sig("ronn_softmax", [V, V, L, I, I, V])
     sig("ronn_unary", [V, V, L, I, I, V])

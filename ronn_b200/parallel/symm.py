@@ -58,7 +58,7 @@ class FusedComm(TPComm):
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
     # ------------------------------------------------------------------ fused row-parallel GEMM
-    def _gemm_reduce(self, a, w_nk, bias, residual, row_begin, row_end, bn=0):
+    def _gemm_reduce(self, a, w_nk, bias, residual, row_begin, row_end, bn=0, norm=None):
         M, Kd = a.shape
         N = w_nk.shape[0]
         if M * N > self.max_elems:
@@ -69,20 +69,29 @@ class FusedComm(TPComm):
             residual = residual.reshape(rows, N).contiguous()
         if bias is not None and bias.dtype != a.dtype:
             bias = bias.to(a.dtype)
+        normed, gamma, beta, eps, mode = None, None, None, 0.0, 0
+        if norm is not None:
+            kind, gamma, beta, eps = norm
+            mode = 1 if kind == "layernorm" else 2
+            normed = torch.empty_like(out)
         rc = _native.cuda().ronn_gemm_reduce(
             a.data_ptr(), w_nk.data_ptr(), M, N, Kd, a.stride(0), w_nk.stride(0), self._part_ptrs, self._flag_ptrs,
             self.part_stride, self._state.data_ptr(), self.rank, self.world, row_begin, row_end, out.data_ptr(),
             out.stride(0), None if bias is None else bias.data_ptr(), None if residual is None else residual.data_ptr(),
             residual.stride(0) if residual is not None else 0, self.wait_seconds, 0 if a.dtype == torch.bfloat16 else 1,
-            bn, K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+            bn, None if normed is None else normed.data_ptr(), None if gamma is None else gamma.data_ptr(),
+            None if beta is None else beta.data_ptr(), float(eps), mode,
+            K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise K.KernelError(f"gemm_reduce failed with code {rc}")
         self.fused_calls += 1
-        return out
+        return out if norm is None else (out, normed)
 
-    def gemm_allreduce(self, a, w_nk, bias=None, residual=None, bn=0):
-        """sum over ranks of (a @ w_nk^T) + bias + residual, full result on every rank (bit-identical)."""
-        return self._gemm_reduce(a, w_nk, bias, residual, 0, a.shape[0], bn)
+    def gemm_allreduce(self, a, w_nk, bias=None, residual=None, bn=0, norm=None):
+        """sum over ranks of (a @ w_nk^T) + bias + residual, full result on every rank (bit-identical).
+        ``norm=(kind, gamma, beta, eps)`` (hidden size <= 1024) also returns the normalised rows: the reduction
+        pass holds whole rows in registers, so the next block's LayerNorm / RMSNorm costs no extra kernel."""
+        return self._gemm_reduce(a, w_nk, bias, residual, 0, a.shape[0], bn, norm)
 
     def gemm_reduce_scatter(self, a, w_nk, bias=None, residual_shard=None, bn=0):
         """Same sum, but each rank keeps only its contiguous shard of the rows (M must divide by the world size)."""

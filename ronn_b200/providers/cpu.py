@@ -46,6 +46,100 @@ def _simd_gemm(inputs, attrs, ctx):
     return [out]
 
 
+class ChainKernel:
+    """A linear fp32 chain of dense layers / ReLU / final softmax executed by ONE native call
+    (the fused forms the reference names but never produces: crates/ronn-providers/src/cpu/kernels.rs:20-31)."""
+
+    def __init__(self, graph: ModelGraph, order):
+        import ctypes as C
+        import numpy as np
+        from ..core.types import KernelStats
+        self.device = torch.device("cpu")
+        self.input_name = graph.inputs[0].name
+        self.output_name = graph.outputs[0].name
+        self.stats = KernelStats()
+        self.steps = order
+        kinds, acts, dims, self._keep = [], [], [], []
+        wptr, bptr = [], []
+        k0 = None
+        for n in order:
+            if n.op_type in ("FusedGemm", "MatMul", "Gemm"):
+                w = graph.initializers[n.inputs[1]].contiguous()
+                b = graph.initializers[n.inputs[2]].contiguous() if len(n.inputs) > 2 and n.inputs[2] else None
+                self._keep += [w, b]
+                if k0 is None:
+                    k0 = w.shape[0]
+                kinds.append(0)
+                acts.append(1 if n.attr("activation", "") == "Relu" else 0)
+                dims.append(w.shape[1])
+                wptr.append(w.data_ptr())
+                bptr.append(b.data_ptr() if b is not None else None)
+            else:
+                kinds.append(1 if n.op_type == "Relu" else 2)
+                acts.append(0)
+                dims.append(dims[-1] if dims else 0)
+                wptr.append(None)
+                bptr.append(None)
+        self.k0, self.n_out, self.max_n = k0, dims[-1], max(dims)
+        n = len(kinds)
+        self._kinds = (C.c_int32 * n)(*kinds)
+        self._acts = (C.c_int32 * n)(*acts)
+        self._dims = (C.c_int64 * n)(*dims)
+        self._w = (C.c_void_p * n)(*wptr)
+        self._b = (C.c_void_p * n)(*bptr)
+        self._n = n
+        self._fn = _native.host().ronn_cpu_run_chain
+        self._scratch = {}
+
+    def execute(self, inputs: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        x = inputs[self.input_name]
+        if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] != self.k0 or not x.is_contiguous():
+            raise ProviderError(f"chain kernel expects a contiguous float32 [M, {self.k0}] input, got {tuple(x.shape)} {x.dtype}")
+        M = x.shape[0]
+        sc = self._scratch.get(M)
+        if sc is None:
+            sc = (torch.empty(M * self.max_n), torch.empty(M * self.max_n))
+            self._scratch[M] = sc
+        out = torch.empty((M, self.n_out), dtype=torch.float32)
+        self._fn(x.data_ptr(), M, self.k0, self._n, self._kinds, self._w, self._b, self._acts, self._dims,
+                 out.data_ptr(), sc[0].data_ptr(), sc[1].data_ptr())
+        self.stats.execution_count += 1
+        return {self.output_name: out}
+
+    def get_performance_stats(self):
+        return self.stats
+
+    @staticmethod
+    def match(graph: ModelGraph):
+        """The node order if the graph is such a chain, else None."""
+        if len(graph.inputs) != 1 or len(graph.outputs) != 1 or not graph.nodes:
+            return None
+        try:
+            order = graph.topological_order()
+        except Exception:
+            return None
+        cur = graph.inputs[0].name
+        seen_gemm = False
+        for k, n in enumerate(order):
+            if not n.inputs or n.inputs[0] != cur or len(n.outputs) != 1:
+                return None
+            if n.op_type == "FusedGemm" and n.attr("cpu_kernel") == "simd_gemm" and len(n.inputs) <= 3:
+                w = graph.initializers.get(n.inputs[1])
+                if w is None or w.dtype != torch.float32 or int(n.attr("transB", 0)):
+                    return None
+                if len(n.inputs) > 2 and n.inputs[2] and n.inputs[2] not in graph.initializers:
+                    return None
+                seen_gemm = True
+            elif n.op_type == "Relu" and seen_gemm:
+                pass
+            elif n.op_type == "Softmax" and seen_gemm and k == len(order) - 1 and int(n.attr("axis", -1)) in (-1, 1):
+                pass
+            else:
+                return None
+            cur = n.outputs[0]
+        return order if (seen_gemm and cur == graph.outputs[0].name) else None
+
+
 class CpuExecutionProvider(ExecutionProvider):
     provider_id = ProviderType.CPU
     name = "CpuExecutionProvider"
@@ -94,6 +188,10 @@ class CpuExecutionProvider(ExecutionProvider):
     def compile_graph(self, graph: ModelGraph, profiler=None) -> CompiledKernel:
         reg = default_registry()
         dev = torch.device("cpu")
+        if self.enable_simd and self.enable_fusion and profiler is None:
+            order = ChainKernel.match(graph)
+            if order is not None:
+                return ChainKernel(graph, order)
 
         def resolve(node, g):
             if node.attr("cpu_kernel") == "simd_gemm" and self.enable_simd:

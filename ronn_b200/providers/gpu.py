@@ -57,10 +57,12 @@ class GpuExecutionProvider(ExecutionProvider):
         from .. import _native
         _native.cuda()                      # fail loudly when the kernel library is missing
         self.kernel_launches = 0
+        self.use_cuda_graph = False
 
     def set_session_options(self, opts) -> None:
         if opts.dtype:
             self.config.compute_dtype = opts.dtype
+        self.use_cuda_graph = bool(getattr(opts, "use_cuda_graph", False))
 
     def has_tensor_cores(self) -> bool:
         return torch.cuda.get_device_capability(self.device)[0] >= 7
@@ -96,7 +98,40 @@ class GpuExecutionProvider(ExecutionProvider):
                 feed = {k: (v.to(_cdt) if v.is_floating_point() and v.dtype != _cdt else v) for k, v in inputs.items()}
                 return _inner(feed)
             kernel.execute = execute
+        if self.use_cuda_graph:
+            kernel.execute = _GraphedExecute(kernel.execute, self.device)
         return kernel
+
+
+class _GraphedExecute:
+    """Replays the whole node sequence as one CUDA graph per input signature.  Inputs are copied into static
+    buffers; outputs are the graph's static tensors (valid until the next run of the same session)."""
+
+    def __init__(self, inner, device):
+        self.inner, self.device, self.graphs = inner, device, {}
+
+    def __call__(self, inputs):
+        key = tuple((k, tuple(v.shape), v.dtype) for k, v in sorted(inputs.items()))
+        entry = self.graphs.get(key)
+        if entry is None:
+            static_in = {k: v.clone() for k, v in inputs.items()}
+            side = torch.cuda.Stream(self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                for _ in range(2):                     # warm-up: lazy kernel attributes, workspaces, caches
+                    self.inner(static_in)
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                static_out = self.inner(static_in)
+            entry = (g, static_in, static_out)
+            self.graphs[key] = entry
+        g, static_in, static_out = entry
+        for k, v in inputs.items():
+            static_in[k].copy_(v, non_blocking=True)
+        g.replay()
+        return static_out
 
 
 def create_gpu_provider(**kw) -> GpuExecutionProvider:

@@ -32,7 +32,19 @@ class GpuOpTable:
         self.reg = default_registry()
         self.graph = graph
         self.w_nk: Dict[str, bool] = {}
+        self._pinned: list = []
         self.custom = provider.config.enable_custom_kernels
+
+    def to_device(self, t: torch.Tensor) -> torch.Tensor:
+        """Host tensors produced by shape arithmetic (Shape/Range/...) reach the device through pinned memory, which
+        is also legal inside CUDA-graph capture; the pinned staging buffer is kept alive with the session."""
+        if t.device.type == "cuda":
+            return t
+        p = t.contiguous().pin_memory()
+        self._pinned.append(p)
+        if len(self._pinned) > 4096:
+            del self._pinned[:2048]
+        return p.to(self.device, non_blocking=True)
 
     # ------------------------------------------------------------------ constants
     def place_const(self, name: str, t: torch.Tensor, users: List[GraphNode]) -> torch.Tensor:
@@ -89,7 +101,7 @@ class GpuOpTable:
         def run(i, a, c):
             if any(t is not None and t.device.type == "cuda" for t in i):
                 lim = 1 if shape_op else len(i)
-                i = [t.to(dev) if (k < lim and t is not None and t.device.type != "cuda") else t
+                i = [self.to_device(t) if (k < lim and t is not None and t.device.type != "cuda") else t
                      for k, t in enumerate(i)]
             return fn(i, a, c)
         return run
@@ -181,7 +193,7 @@ class GpuOpTable:
             if (axis != 0 or table.dim() != 2 or table.dtype not in _HALF or table.shape[1] % 8
                     or table.device.type != "cuda" or idx.is_floating_point()):
                 return fallback(i, a, c)
-            idx = idx.to(table.device)
+            idx = self.to_device(idx)
             y = K.embedding(idx, table)
             return [y.reshape(*idx.shape, table.shape[1])]
         return run

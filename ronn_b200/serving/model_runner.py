@@ -79,10 +79,11 @@ class NoComm:
 
 class LinearW:
     """A dense [N,K] weight (+ optional bias) or a packed ternary BitLinear weight."""
-    __slots__ = ("w", "bias", "scale", "packed", "n", "k")
+    __slots__ = ("w", "bias", "scale", "packed", "n", "k", "_dense")
 
     def __init__(self, w=None, bias=None, packed=None, scale=None, n=0, k=0):
         self.w, self.bias, self.packed, self.scale, self.n, self.k = w, bias, packed, scale, n, k
+        self._dense = None
 
 
 class DecoderRunner:
@@ -217,30 +218,40 @@ class DecoderRunner:
         hn, kn = self.n_head_local * d, self.n_kv_local * d
         # the library backend gathers dense KV, so it is sized by the longest context of this step
         max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
-        # decode-sized steps on one GPU: the K=ffn down projection runs split-K and its reduction pass also applies
-        # bias + residual and the next block's norm, so that norm costs no launch of its own
         split_down = (ops.name == "kernels" and self.tp == 1 and x.shape[0] <= 512 and not a.bitlinear
                       and self.layers[0]["down"].w is not None and self.layers[0]["down"].w.shape[1] >= 2048)
+        fused_tp = (ops.name == "kernels" and self.tp > 1 and getattr(self.comm, "fused", False) and not a.bitlinear
+                    and a.hidden <= 1024)
+
+        def row_parallel(inp, lw, residual, norm_params, allow_split):
+            """Row-parallel projection + residual.  Returns (new residual stream, normalised copy or None): on the
+            fused paths the reduction pass already holds whole rows, so it applies the next norm as well."""
+            if fused_tp:
+                if norm_params is None:
+                    return self.comm.gemm_allreduce(inp, lw.w, lw.bias, residual), None
+                beta = norm_params[1] if len(norm_params) > 1 else None
+                return self.comm.gemm_allreduce(inp, lw.w, lw.bias, residual, norm=(a.norm, norm_params[0], beta, a.eps))
+            if allow_split and split_down:
+                return ops.gemm_splitk_norm(inp, lw, residual, norm_params, a.norm, a.eps, 4)
+            return self._linear(inp, lw, residual=residual, reduce=True), None
+
         h_next = None
         for li, L in enumerate(self.layers):
             h = h_next if h_next is not None else self._norm(x, L["ln1"])
-            h_next = None
             qkv = self._linear(h, L["qkv"])
             ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
                           self.n_kv_local, d, pos, a.rope_base)
             att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
                                       self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
-            x = self._linear(att, L["out"], residual=x, reduce=True)
-            h = self._norm(x, L["ln2"])
+            x, h = row_parallel(att, L["out"], x, L["ln2"], False)
+            if h is None:
+                h = self._norm(x, L["ln2"])
             if a.mlp == "gelu":
                 f = self._linear(h, L["up"], activation="gelu")
             else:
                 f = ops.swiglu_fused(self._linear(h, L["up"]))
-            if split_down:
-                nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else (self.lnf if decode else None)
-                x, h_next = ops.gemm_splitk_norm(f, L["down"], x, nxt, a.norm, a.eps, 4)
-            else:
-                x = self._linear(f, L["down"], residual=x, reduce=True)
+            nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else (self.lnf if decode else None)
+            x, h_next = row_parallel(f, L["down"], x, nxt, True)
         if h_next is not None:
             x = h_next                                   # final norm already applied by the last reduction pass
         else:

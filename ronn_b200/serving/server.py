@@ -1,0 +1,180 @@
+"""HTTP front end of the serving engine.
+
+Endpoints of the continuous-batching design (docs/new/RONN-Continuous-Batching-Branch-Prompt.md:377-395):
+``POST /v1/completions`` (optionally streamed as server-sent events), ``DELETE /v1/requests/{id}``,
+``GET /v1/health``, ``GET /v1/metrics`` (Prometheus text).  Prompts are token ids (``prompt_token_ids``); no
+tokenizer ships with the runtime.  One background thread owns the engine and runs its iteration loop; HTTP
+handlers only enqueue requests and wait on per-request events.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import threading
+import time
+from typing import Dict, List, Optional
+
+from pydantic import BaseModel
+
+from .engine import LLMEngine
+from .request import Priority, SamplingParams
+
+
+class CompletionRequest(BaseModel):
+    prompt_token_ids: List[int]
+    max_tokens: int = 16
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repeat_penalty: float = 1.0
+    seed: Optional[int] = None
+    stop_token_sequences: List[List[int]] = []
+    stream: bool = False
+    priority: str = "normal"
+
+
+class EngineLoop:
+    """Owns an ``LLMEngine`` on one thread: submissions and cancellations are queued and applied between iterations."""
+
+    def __init__(self, engine: LLMEngine, idle_sleep: float = 0.001):
+        self.engine = engine
+        self.idle_sleep = idle_sleep
+        self._lock = threading.Lock()
+        self._pending: List[tuple] = []
+        self._cancel: List[int] = []
+        self._events: Dict[int, threading.Event] = {}
+        self._streams: Dict[int, List[int]] = {}
+        self._next_id = 1
+        self._stop = threading.Event()
+        self.error: Optional[str] = None
+        self._thread = threading.Thread(target=self._run, daemon=True, name="ronn-engine-loop")
+        engine.on_token = self._on_token
+        self._thread.start()
+
+    def _on_token(self, req, tok: int) -> None:
+        with self._lock:
+            self._streams.setdefault(req.id, []).append(tok)
+
+    def submit(self, tokens: List[int], params: SamplingParams, priority: Priority = Priority.NORMAL) -> int:
+        with self._lock:
+            rid = self._next_id
+            self._next_id += 1
+            self._events[rid] = threading.Event()
+            self._pending.append((rid, tokens, params, priority))
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        with self._lock:
+            self._cancel.append(rid)
+
+    def wait(self, rid: int, timeout: Optional[float] = None) -> bool:
+        ev = self._events.get(rid)
+        return ev.wait(timeout) if ev is not None else False
+
+    def drain_stream(self, rid: int) -> List[int]:
+        with self._lock:
+            toks = self._streams.get(rid, [])
+            self._streams[rid] = []
+            return toks
+
+    def stop(self) -> None:
+        self._stop.set()
+        self._thread.join(timeout=5)
+
+    def _run(self) -> None:
+        eng = self.engine
+        while not self._stop.is_set():
+            with self._lock:
+                pending, self._pending = self._pending, []
+                cancels, self._cancel = self._cancel, []
+            for rid, toks, params, prio in pending:
+                try:
+                    eng.add_request(toks, params, prio, request_id=rid)
+                except Exception as e:               # rejected at admission: report through the request record
+                    from .request import FinishReason, Request
+                    r = Request(rid, toks, params, prio)
+                    r.finish_reason, r.error, r._final_tokens = FinishReason.ERROR, str(e), []
+                    eng.requests[rid] = r
+                    self._events[rid].set()
+            for rid in cancels:
+                eng.cancel(rid)
+                if rid in self._events:
+                    self._events[rid].set()
+            if not eng.has_unfinished():
+                time.sleep(self.idle_sleep)
+                continue
+            try:
+                eng.step()
+            except Exception as e:                   # failed step: requests were re-queued by the engine
+                self.error = str(e)
+                time.sleep(0.01)
+            for rid, ev in list(self._events.items()):
+                r = eng.requests.get(rid)
+                if r is not None and r.finished and not ev.is_set():
+                    ev.set()
+
+
+def create_app(engine: LLMEngine):
+    from fastapi import FastAPI, HTTPException
+    from fastapi.responses import PlainTextResponse, StreamingResponse
+
+    app = FastAPI(title="ronn_b200")
+    loop = EngineLoop(engine)
+    app.state.loop = loop
+
+    def _result(rid: int):
+        r = engine.requests[rid]
+        if r.error:
+            raise HTTPException(status_code=400, detail=r.error)
+        return {"id": rid, "object": "text_completion",
+                "choices": [{"index": 0, "token_ids": r.output_tokens,
+                             "finish_reason": r.finish_reason.value if r.finish_reason else None}],
+                "usage": {"prompt_tokens": len(r.prompt_tokens), "completion_tokens": len(r.output_tokens)}}
+
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest):
+        if not req.prompt_token_ids:
+            raise HTTPException(status_code=400, detail="prompt_token_ids must not be empty")
+        params = SamplingParams(max_new_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k,
+                                top_p=req.top_p, repeat_penalty=req.repeat_penalty, seed=req.seed,
+                                stop_sequences=req.stop_token_sequences)
+        try:
+            prio = Priority[req.priority.upper()]
+        except KeyError:
+            raise HTTPException(status_code=400, detail=f"unknown priority '{req.priority}'") from None
+        rid = loop.submit(list(req.prompt_token_ids), params, prio)
+        if not req.stream:
+            while not await asyncio.get_running_loop().run_in_executor(None, loop.wait, rid, 0.05):
+                pass
+            return _result(rid)
+
+        async def events():
+            while True:
+                done = await asyncio.get_running_loop().run_in_executor(None, loop.wait, rid, 0.01)
+                for tok in loop.drain_stream(rid):
+                    yield f"data: {json.dumps({'id': rid, 'token_id': tok})}\n\n"
+                if done:
+                    r = engine.requests[rid]
+                    yield f"data: {json.dumps({'id': rid, 'finish_reason': r.finish_reason.value if r.finish_reason else None})}\n\n"
+                    yield "data: [DONE]\n\n"
+                    return
+        return StreamingResponse(events(), media_type="text/event-stream")
+
+    @app.delete("/v1/requests/{rid}")
+    async def cancel(rid: int):
+        if rid not in engine.requests and rid not in loop._events:
+            raise HTTPException(status_code=404, detail="unknown request")
+        loop.cancel(rid)
+        return {"id": rid, "cancelled": True}
+
+    @app.get("/v1/health")
+    async def health():
+        return {"status": "ok" if loop.error is None else "degraded", "last_error": loop.error,
+                "waiting": engine.sched.num_waiting, "running": engine.sched.num_running,
+                "free_blocks": engine.sched.num_free_blocks}
+
+    @app.get("/v1/metrics", response_class=PlainTextResponse)
+    async def metrics():
+        return engine.metrics.prometheus()
+
+    return app

@@ -36,6 +36,14 @@ def main():
             y0 = y.clone()
             dist.broadcast(y0, 0)
             results.append({"mode": "ar", "M": M, "N": N, "K": Kl, "err": err, "identical": bool(torch.equal(y0, y))})
+            if N <= 1024:
+                gam, bet = torch.randn(N, device=dev).bfloat16(), torch.randn(N, device=dev).bfloat16()
+                dist.broadcast(gam, 0)
+                dist.broadcast(bet, 0)
+                y2, hn = comm.gemm_allreduce(a, w, bias, res, norm=("layernorm", gam, bet, 1e-5))
+                href = torch.nn.functional.layer_norm(y2.float(), (N,), gam.float(), bet.float(), 1e-5)
+                results.append({"mode": "ar+ln", "M": M, "N": N, "K": Kl, "identical": bool(torch.equal(y2, y)),
+                                "err": (hn.float() - href).abs().max().item() * 0.5})
             if M % world == 0:
                 per = M // world
                 ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
@@ -68,7 +76,8 @@ def main():
         with open(out_path, "w") as f:
             json.dump(gathered, f)
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
+    os._exit(0)
 
 
 if __name__ == "__main__":

@@ -51,6 +51,9 @@ def main():
             json.dump({"agree": agree, "total": total, "same_across_ranks": same_across_ranks, "world": world,
                        "fused_calls": getattr(comm, "fused_calls", 0)}, f)
     torch.distributed.barrier()
+    if mode != "cpu":
+        torch.cuda.synchronize()
+        os._exit(0)
     torch.distributed.destroy_process_group()
 
 

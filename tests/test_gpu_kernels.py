@@ -224,7 +224,7 @@ def test_bitlinear_exact_against_host_oracle(M, N, K_):
     from ronn_b200 import ops
     ops.check_status()
     # integer accumulation is exact; only the final bf16 rounding differs from the fp32 oracle
-    torch.testing.assert_close(y.float().cpu(), ref, atol=1e-2, rtol=1e-2)
+    torch.testing.assert_close(y.float().cpu(), ref, atol=2e-2, rtol=1e-2)
     q, s = B.act_quant_int8(x.cuda())
     sref = x.float().abs().amax(-1).clamp_min(1e-5) / 127
     torch.testing.assert_close(s.cpu(), sref, rtol=1e-6, atol=0)

@@ -62,7 +62,7 @@ def test_peer_wait_runs_out_and_context_survives():
     fp = (C.c_void_p * 8)(*[flags[0].data_ptr(), flags[1].data_ptr()] + [None] * 6)
     K.check_status(dev)
     rc = _native.cuda().ronn_gemm_reduce(a.data_ptr(), w.data_ptr(), M, N, Kd, Kd, Kd, pp, fp, stride, state.data_ptr(),
-                                         0, 2, 0, M, out.data_ptr(), N, None, None, 0, 0.3, 0, 0,
+                                         0, 2, 0, M, out.data_ptr(), N, None, None, 0, 0.3, 0, 0, None, None, None, 0.0, 0,
                                          K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()

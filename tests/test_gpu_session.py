@@ -43,3 +43,33 @@ def test_resnet18_gpu_o3_matches_cpu_o0():
     assert sum(1 for n in s.graph().nodes if n.op_type == "FusedConv") == 17
     assert (got - want).abs().max() < 0.05 * want.abs().max()
     assert (got.argmax(-1) == want.argmax(-1)).float().mean() >= 0.75
+
+
+def test_distilbert_gpu_graph_matches_cpu():
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.models.distilbert import DistilBertConfig, build_distilbert
+    m = Model.from_graph(build_distilbert(DistilBertConfig.tiny(), dtype=torch.float32, seed=4))
+    ids = torch.randint(0, 512, (3, 16))
+    mask = torch.ones(3, 16, dtype=torch.int64)
+    mask[1, 9:] = 0
+    want = m.create_session(SessionOptions().with_optimization_level("O0")).run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"]
+    for graphed in (False, True):
+        s = m.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("bf16").with_cuda_graph(graphed))
+        for _ in range(2):
+            got = s.run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"].float().cpu()
+        torch.testing.assert_close(got, want, atol=8e-2, rtol=5e-2)
+
+
+def test_bitnet_engine_gpu_kernels_vs_torch_backend():
+    from ronn_b200 import Model
+    from ronn_b200.models.bitnet_llama import BitNetConfig, build_bitnet_llama
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    m = Model.from_graph(build_bitnet_llama(BitNetConfig.tiny(n_layer=2, hidden=256, n_head=2, ffn=512), dtype=torch.bfloat16, seed=9))
+    prompts = [[1, 2, 3, 4, 5], list(range(30, 70)), [9] * 17]
+    outs = {}
+    for backend in ("kernels", "torch"):
+        eng = LLMEngine(m, EngineConfig(max_num_seqs=4, max_batch_tokens=128, max_model_len=128, num_blocks=32, dtype="bf16",
+                                        backend=backend, use_cuda_graph=(backend == "kernels")), device=torch.device("cuda", 0))
+        outs[backend] = eng.generate(prompts, SamplingParams(max_new_tokens=6))
+    agree = sum(a == b for x, y in zip(outs["kernels"], outs["torch"]) for a, b in zip(x, y))
+    assert agree >= 14, outs
