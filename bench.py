@@ -125,7 +125,13 @@ def main():
     else:
         comm = None
     eng = LLMEngine(model, ecfg, device=dev, comm=comm)
-    launches_per_step = 1 + 8 * cfg.n_layer + 3
+    # hand-written kernels launched per decode step (library collectives and torch adds are not counted)
+    if world == 1:
+        launches_per_step = 2 + 7 * cfg.n_layer + 2       # embed, first norm | qkv, attn+append, out, norm, up, down(split-K), finalize+norm | LM head, argmax
+    elif ecfg.tp_comm == "fused":
+        launches_per_step = 2 + 5 * cfg.n_layer + 3       # qkv, attn+append, out+all-reduce+norm, up, down+all-reduce+norm | LM head, argmax, combine
+    else:
+        launches_per_step = 1 + 7 * cfg.n_layer + 4       # embed | norm, qkv, attn+append, out, norm, up, down | final norm, LM head, argmax, combine
 
     rng = np.random.default_rng(1234)
     lens = rng.integers(64, 513, size=args.requests)

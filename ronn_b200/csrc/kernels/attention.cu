@@ -65,10 +65,10 @@ __global__ void kv_append_kernel(T* __restrict__ qkv, long ld, int k_off, int v_
 // bt_row[row]  : which row of block_tables holds its pages (null -> row itself).
 template <class T, int D>
 __global__ void __launch_bounds__(ATTN_THREADS)
-paged_attention_kernel(const T* __restrict__ q, long ld_q, const T* __restrict__ kcache, const T* __restrict__ vcache,
+paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache,
                        const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ ctx_len,
                        const int* __restrict__ bt_row, T* __restrict__ out, long ld_o, int heads, int kv_heads,
-                       float scale) {
+                       float scale, int k_off, int v_off, const int* __restrict__ append_slots) {
   constexpr int LPT = D / 8;                  // lanes cooperating on one token (16-byte chunk each)
   constexpr int TPW = 32 / LPT;               // tokens per warp pass
   constexpr int PASSES = KV_BLOCK / TPW;      // passes per 16-token block
@@ -87,6 +87,20 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, const T* __restrict__
     return;
   }
   const int kvh = head / (heads / kv_heads);
+  if (append_slots != nullptr) {
+    // decode with fused append: this row's new K/V (columns k_off / v_off of the fused QKV row) go to the row's
+    // cache slot first; every CTA of a KV group writes the same bytes, and reads them back only after the barrier
+    const int slot = append_slots[row];
+    if (slot >= 0 && threadIdx.x < 2 * (D / 8)) {
+      const int c = threadIdx.x % (D / 8);
+      const bool is_v = threadIdx.x >= D / 8;
+      const T* src = q + long(row) * ld_q + (is_v ? v_off : k_off) + kvh * D + c * 8;
+      T* dstc = is_v ? vcache : kcache;
+      const long dst = ((long(slot / KV_BLOCK) * kv_heads + kvh) * KV_BLOCK + slot % KV_BLOCK) * D + c * 8;
+      *reinterpret_cast<Vec8*>(dstc + dst) = *reinterpret_cast<const Vec8*>(src);
+    }
+    __syncthreads();
+  }
   const int* bt = block_tables + long(bt_row ? bt_row[row] : row) * max_blocks;
   const int nblk = (L + KV_BLOCK - 1) / KV_BLOCK;
   const int sub = lane / LPT, chunk = lane % LPT;
@@ -194,16 +208,20 @@ extern "C" int ronn_kv_append(void* qkv, long ld, int k_off, int v_off, const in
 }
 
 // max_ctx: upper bound of ctx_len over the rows (sizes the score buffer); must be <= 4096.
-extern "C" int ronn_paged_attention(const void* q, long ld_q, const void* kcache, const void* vcache,
+// append_slots != null (decode, one row per sequence, no rotary): the row's new K/V are taken from columns k_off / v_off
+// of its q row and written to cache slot append_slots[row] by the same kernel before attending.
+extern "C" int ronn_paged_attention(const void* q, long ld_q, void* kcache, void* vcache,
                                     const int* block_tables, int max_blocks, const int* ctx_len, const int* bt_row,
                                     void* out, long ld_o, long rows, int heads, int kv_heads, int head_dim,
-                                    int max_ctx, float scale, int dtype, cudaStream_t stream) {
+                                    int max_ctx, float scale, int dtype, int k_off, int v_off, const int* append_slots,
+                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (max_ctx <= 0 || max_ctx > ATTN_MAX_CTX || heads % kv_heads || (ld_q & 7)) return -2;
+  if (append_slots && ((k_off & 7) || (v_off & 7))) return -2;
   const int padded = (max_ctx + KV_BLOCK - 1) / KV_BLOCK * KV_BLOCK;
   const size_t smem = size_t(padded) * sizeof(float);
   dim3 grid((unsigned)rows, (unsigned)heads);
-#define RONN_PA(T, D) launch(paged_attention_kernel<T, D>, grid, dim3(ATTN_THREADS), smem, stream, (const T*)q, ld_q, (const T*)kcache, (const T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale)
+#define RONN_PA(T, D) launch(paged_attention_kernel<T, D>, grid, dim3(ATTN_THREADS), smem, stream, (const T*)q, ld_q, (T*)kcache, (T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale, k_off, v_off, append_slots)
   if (dtype == 0 && head_dim == 64) RONN_PA(__nv_bfloat16, 64);
   else if (dtype == 0 && head_dim == 128) RONN_PA(__nv_bfloat16, 128);
   else if (dtype == 1 && head_dim == 64) RONN_PA(__half, 64);

@@ -205,7 +205,9 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
             *reinterpret_cast<Vec8*>(dst + jj * 8) = pack8<T>(f);
           }
         } else {
-          for (int i = 0; i < 32 && gn + i < N; ++i) dst[i] = Cvt<T>::from_f(v[i]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (gn + i < N) dst[i] = Cvt<T>::from_f(v[i]);
         }
       }
     }

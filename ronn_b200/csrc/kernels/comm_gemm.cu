@@ -22,7 +22,7 @@
 //
 // The reference has no collective of any kind (its only multi-GPU code picks one device per sub-graph,
 // crates/ronn-providers/src/gpu/provider.rs:226-249).
-#include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include "tma_desc.cuh"
 #include "umma_persistent.cuh"
 
@@ -102,7 +102,9 @@ struct PartialProblem {
         *reinterpret_cast<Vec8*>(dst + j * 8) = pack8<T>(f);
       }
     } else {
-      for (int i = 0; i < 32 && gn + i < N; ++i) dst[i] = Cvt<T>::from_f(__uint_as_float(r[i]));
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (gn + i < N) dst[i] = Cvt<T>::from_f(__uint_as_float(r[i]));
     }
   }
 };
@@ -388,4 +390,190 @@ extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int 
     default: return -3;
   }
 #undef RONN_DISPATCH
+}
+
+// =====================================================================================================================
+// Column-parallel all-gather -> GEMM in ONE kernel.
+//
+//   Y[T, N_local] = concat_r(X_r)[T, K] * W[N_local, K]^T (+ bias, activation)
+//
+// Every rank holds a row shard X_r [T / world, K] in a symmetric buffer.  The gathered activation matrix is never
+// materialised: the TMA producer of each output tile reads the A rows it needs straight from the owning rank's
+// buffer through a per-peer tensor map (plain cp.async.bulk.tensor loads, no multicast).  Before the first load from
+// a peer it waits (bounded) for that peer's "shard ready" flag, so tiles whose rows are local start at once and the
+// NVLink traffic of the remaining tiles overlaps their math.  Flags are raised by ronn_signal_peers, launched on the
+// producing rank right after the kernel that wrote the shard.
+//
+// The symmetric shard buffer is single-buffered: a caller must put a cross-rank synchronising operation (the fused
+// row-parallel GEMM above) between two gathers, which a transformer block does by construction.
+namespace ronn {
+
+struct GatherArgs {
+  CUtensorMap map_a[MAX_RANKS];    // [rows_per_rank, K] view of every rank's shard buffer
+  const int* flags;                // local: [MAX_RANKS] arrival counters, one per source rank
+  int* state;                      // local: [0] gathers completed, [1] CTA counter
+  int rows_per_rank, world, rank;
+  unsigned long long wait_ns;
+};
+
+template <int BN, class T>
+struct GatherProblem {
+  const GatherArgs* g;
+  const CUtensorMap* map_b;
+  DenseEpilogue e;
+  int m_tiles, n_tiles, num_kb;
+  uint32_t* status;
+  mutable int ready_mask;          // peers whose shard has been seen ready by this thread
+  mutable int want;
+
+  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
+  __device__ __forceinline__ void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const {
+    // start with the tiles whose rows are local, then walk the peers round-robin from there
+    const int per = m_tiles / g->world;              // m-tiles per rank (rows_per_rank % 128 == 0)
+    const int mt = t % m_tiles;
+    const int owner = (mt / per + g->rank) % g->world;
+    m0 = (owner * per + mt % per) * PG_BM;
+    n0 = (t / m_tiles) * BN;
+    kb0 = 0;
+    nkb = num_kb;
+  }
+  __device__ __forceinline__ void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const {
+    const int owner = m0 / g->rows_per_rank;
+    if (!(ready_mask & (1 << owner))) {
+      if (want < 0) want = *reinterpret_cast<volatile int*>(g->state) + 1;
+      const unsigned long long t0 = globaltimer_ns();
+      unsigned polls = 0;
+      while (ld_acquire_sys(g->flags + owner) < want) {
+        if ((++polls & 63u) == 0u && globaltimer_ns() - t0 > g->wait_ns) {
+          if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
+          break;                                       // proceed: the result is flagged invalid through the status word
+        }
+      }
+      ready_mask |= 1 << owner;
+    }
+    tma_load_2d(smem, &g->map_a[owner], bar, k_elem, m0 - owner * g->rows_per_rank);
+  }
+  __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
+    tma_load_2d(smem, map_b, bar, k_elem, n0);
+  }
+  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+    DenseEpilogue ep = e;
+    ep.m0 = m0;
+    ep.n0 = n0;
+    ep.run<T>(row, col, r);
+  }
+};
+
+template <int BN, int STAGES, class T>
+__global__ void __launch_bounds__(PG_THREADS)
+ag_gemm_kernel(const __grid_constant__ GatherArgs g, const __grid_constant__ CUtensorMap map_b, DenseEpilogue epi,
+               int K, uint32_t idesc, uint32_t* status) {
+  extern __shared__ uint8_t dyn_smem[];
+  GatherProblem<BN, T> prob;
+  prob.g = &g;
+  prob.map_b = &map_b;
+  prob.e = epi;
+  prob.m_tiles = (epi.M + PG_BM - 1) / PG_BM;
+  prob.n_tiles = (epi.N + BN - 1) / BN;
+  prob.num_kb = (K + 63) / 64;
+  prob.status = status;
+  prob.ready_mask = 0;
+  prob.want = -1;
+  gemm_persistent<BN, STAGES, 0, GatherProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(g.state + 1, 1);
+    if (done == int(gridDim.x) - 1) {                  // last CTA: this gather is complete on this rank
+      g.state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(g.state) = *reinterpret_cast<volatile int*>(g.state) + 1;
+    }
+  }
+}
+
+// One thread: make this rank's earlier writes visible system-wide, then bump its arrival counter on every rank.
+struct PeerFlagPtrs {
+  int* p[MAX_RANKS];
+};
+__global__ void signal_peers_kernel2(PeerFlagPtrs ptrs, int world, int rank) {
+  pdl_wait();
+  __threadfence_system();
+  for (int p = 0; p < world; ++p) atomicAdd_system(ptrs.p[p] + rank, 1);
+}
+
+template <int BN, int STAGES, class T>
+static int launch_ag(const GatherArgs& g, const CUtensorMap& mb, DenseEpilogue e, int M, int N, int K, int is_bf16,
+                     uint32_t* status, cudaStream_t stream) {
+  using L = PGemmSmem<BN, STAGES>;
+  auto kern = ag_gemm_kernel<BN, STAGES, T>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
+    configured = true;
+  }
+  const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM);
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, PG_THREADS, L::DYN_SMEM) != cudaSuccess || per_sm < 1)
+    return -12;
+  if (per_sm > 2) per_sm = 2;
+  const int resident = comm_sm_count() * per_sm;
+  dim3 grid(tiles < resident ? tiles : resident);
+  uint32_t idesc = umma_idesc(PG_BM, BN, is_bf16 ? 1u : 0u, 1u);
+  cudaError_t err = launch(kern, grid, dim3(PG_THREADS), size_t(L::DYN_SMEM), stream, g, mb, e, K, idesc, status);
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+}  // namespace ronn
+
+// peer_shards: `world` pointers to every rank's [rows_per_rank, K] shard (row stride ld_shard elements).
+// flags: this rank's arrival counters (MAX_RANKS ints, symmetric memory); state: two zero-initialised local ints.
+// rows_per_rank % 128 == 0.  Output C [world * rows_per_rank, N] (+bias, activation) in dtype (0 bf16, 1 fp16).
+extern "C" int ronn_ag_gemm(void* const* peer_shards, int ld_shard, const void* W, int ldw, void* C, int ldc,
+                            const void* bias, int rows_per_rank, int N, int K, int rank, int world, const int* flags,
+                            int* state, int act, double wait_seconds, int dtype, int bn, uint32_t* status,
+                            cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || rows_per_rank <= 0 || (rows_per_rank % PG_BM)) return -1;
+  if ((K & 7) || (ld_shard & 7) || (ldw & 7) || (ldc & 7)) return -2;
+  const int M = rows_per_rank * world;
+  if (bn == 0) {
+    const int mt = M / PG_BM;
+    bn = 256;
+    while (bn > 32 && (N < bn || mt * ((N + bn - 1) / bn) < 120)) bn >>= 1;
+    if (bn > 128) bn = 128;
+  }
+  GatherArgs g;
+  for (int p = 0; p < MAX_RANKS; ++p) {
+    const void* base = peer_shards[p < world ? p : 0];
+    int rc = make_tmap_2d(&g.map_a[p], base, uint64_t(rows_per_rank), uint64_t(K), uint64_t(ld_shard), PG_BM, 64, 2);
+    if (rc) return rc - 20;
+  }
+  g.flags = flags;
+  g.state = state;
+  g.rows_per_rank = rows_per_rank;
+  g.world = world;
+  g.rank = rank;
+  g.wait_ns = static_cast<unsigned long long>(wait_seconds * 1e9);
+  CUtensorMap mb;
+  int rc = make_tmap_2d(&mb, W, uint64_t(N), uint64_t(K), uint64_t(ldw), uint32_t(bn), 64, 2);
+  if (rc) return rc - 30;
+  DenseEpilogue e{C, bias, nullptr, M, N, ldc, 0, 0, act, 0, 0};
+  const int bf = dtype == 0;
+#define RONN_DISPATCH(BN_, ST_)                                                                  \
+  return bf ? launch_ag<BN_, ST_, __nv_bfloat16>(g, mb, e, M, N, K, 1, status, stream)          \
+            : launch_ag<BN_, ST_, __half>(g, mb, e, M, N, K, 0, status, stream)
+  switch (bn) {
+    case 128: RONN_DISPATCH(128, 3);
+    case 64: RONN_DISPATCH(64, 4);
+    case 32: RONN_DISPATCH(32, 5);
+    default: return -3;
+  }
+#undef RONN_DISPATCH
+}
+
+// Raise this rank's "shard ready" counter on every rank (stream-ordered after the kernel that wrote the shard).
+extern "C" int ronn_signal_peers(int* const* peer_flags, int rank, int world, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  PeerFlagPtrs ptrs;
+  for (int p = 0; p < MAX_RANKS; ++p) ptrs.p[p] = p < world ? peer_flags[p] : nullptr;
+  cudaError_t err = launch(signal_peers_kernel2, dim3(1), dim3(1), 0, stream, ptrs, world, rank);
+  return err == cudaSuccess ? 0 : -100;
 }

@@ -9,8 +9,8 @@
 // and the K tail) directly into the swizzled shared-memory layout the UMMA descriptor expects
 // (chunk j of row m lands at chunk position j ^ (m & 7)).  Accumulation in TMEM, epilogue shared with the GEMM.
 //
-// Roles: warps 0-3 gather A and, after the main loop, run the epilogue (warp w owns TMEM lanes 32w..32w+31);
-// warp 4 lane 0 issues the weight TMA; warp 5 allocates TMEM and issues the MMAs.
+// Roles: warps 0-3 gather A; warp 4 lane 0 issues the weight TMA; warp 5 allocates TMEM and issues the MMAs;
+// warps 6-9 run the epilogue.  The kernel is persistent with a double-buffered accumulator.
 //
 // Replaces the reference's depthwise one-thread-per-output template (crates/ronn-providers/src/gpu/cuda_kernels.rs:400-449)
 // and its Candle conv2d call with fixed stride 1 / pad 1 (crates/ronn-providers/src/gpu/provider.rs:1292-1305); the BN
@@ -21,7 +21,7 @@
 
 namespace ronn {
 
-constexpr int CONV_THREADS = 192;
+constexpr int CONV_THREADS = 320;    // warps 0-3 gather A, 4 weight TMA, 5 MMA issuer, 6-9 epilogue
 constexpr int CONV_STAGES = 4;
 constexpr int CONV_LAG = 2;          // cp.async groups a producer thread keeps in flight
 
@@ -39,10 +39,12 @@ struct ConvSmem {
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = CONV_STAGES * STAGE_BYTES;
-  static constexpr int DYN_SMEM = TILE_BYTES + (2 * CONV_STAGES + 1) * 8 + 16 + 1024;
-  static constexpr uint32_t TMEM_COLS = BN <= 32 ? 32u : (BN <= 64 ? 64u : (BN <= 128 ? 128u : 256u));
+  static constexpr int DYN_SMEM = TILE_BYTES + (2 * CONV_STAGES + 4) * 8 + 16 + 1024;
+  static constexpr uint32_t TMEM_COLS = 2 * BN <= 64 ? 64u : (2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u));
 };
 
+// Persistent: a CTA walks output tiles (tile = blockIdx.x, += gridDim.x); the smem ring and its barrier phases run
+// across tiles and the accumulator is double-buffered in TMEM, so the gather of tile j+1 overlaps the epilogue of j.
 template <int BN, class T>
 __global__ void __launch_bounds__(CONV_THREADS)
 conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap map_w, ConvShape cs, DenseEpilogue epi,
@@ -52,19 +54,24 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::TILE_BYTES);
   uint64_t* empty = full + CONV_STAGES;
-  uint64_t* accum = empty + CONV_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  uint64_t* acc_full = empty + CONV_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * 128, n0 = blockIdx.y * BN;
   const int num_kb = (cs.chunks + 7) / 8;
+  const int n_tiles = (cs.Cout + BN - 1) / BN;
+  const int ntiles = ((cs.M + 127) / 128) * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < CONV_STAGES; ++s) {
       mbar_init(&full[s], 128 + 1);          // 128 gather threads + the weight TMA's expect_tx arrival
       mbar_init(&empty[s], 1);
     }
-    mbar_init(accum, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
     *abort = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -83,88 +90,119 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
     // ---------------------------------------------------------------- A gather (one output pixel per thread)
     pdl_wait();
     const int row = threadIdx.x;
-    const int m = m0 + row;
-    const bool row_ok = m < cs.M;
-    int n_img = 0, oh = 0, ow = 0;
-    if (row_ok) {
-      n_img = m / (cs.Ho * cs.Wo);
-      const int rem = m - n_img * cs.Ho * cs.Wo;
-      oh = rem / cs.Wo;
-      ow = rem - oh * cs.Wo;
-    }
-    const int ih0 = oh * cs.stride - cs.pad, iw0 = ow * cs.stride - cs.pad;
-    const T* img = x + size_t(n_img) * cs.H * cs.W * cs.C;
     const int c8n = cs.C >> 3;
     const uint32_t sw = uint32_t(row & 7);
+    uint32_t it = 0;
     bool ok = true;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % CONV_STAGES;
-      if (ok && !mbar_wait(&empty[s], ((kb / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
-      if (ok) {
-        uint8_t* dst_row = tiles + s * L::STAGE_BYTES + row * 128;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int g = kb * 8 + j;
-          const int rs = g / c8n, c8 = g - rs * c8n;
-          const int r = rs / cs.S, sx = rs - r * cs.S;
-          const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
-          const bool valid = row_ok && g < cs.chunks && ih >= 0 && ih < cs.H && iw >= 0 && iw < cs.W;
-          const T* src = valid ? img + (size_t(ih) * cs.W + iw) * cs.C + c8 * 8 : x;
-          cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
-        }
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const int m = (t / n_tiles) * 128 + row;
+      const bool row_ok = m < cs.M;
+      int n_img = 0, oh = 0, ow = 0;
+      if (row_ok) {
+        n_img = m / (cs.Ho * cs.Wo);
+        const int rem = m - n_img * cs.Ho * cs.Wo;
+        oh = rem / cs.Wo;
+        ow = rem - oh * cs.Wo;
       }
-      cp_async_commit();
-      if (kb >= CONV_LAG) {
-        cp_async_wait<CONV_LAG>();
-        fence_proxy_async_smem();
-        mbar_arrive(&full[(kb - CONV_LAG) % CONV_STAGES]);
+      const int ih0 = oh * cs.stride - cs.pad, iw0 = ow * cs.stride - cs.pad;
+      const T* img = x + size_t(n_img) * cs.H * cs.W * cs.C;
+      int r = 0, sx = 0, c8 = 0;                 // filter tap and channel chunk of the next K chunk (no divisions)
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % CONV_STAGES;
+        if (ok && !mbar_wait(&empty[s], ((it / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+        if (ok) {
+          uint8_t* dst_row = tiles + s * L::STAGE_BYTES + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
+            const bool valid = row_ok && r < cs.R && ih >= 0 && ih < cs.H && iw >= 0 && iw < cs.W;
+            const T* src = valid ? img + (size_t(ih) * cs.W + iw) * cs.C + c8 * 8 : x;
+            cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
+            if (++c8 == c8n) {
+              c8 = 0;
+              if (++sx == cs.S) { sx = 0; ++r; }
+            }
+          }
+        }
+        cp_async_commit();
+        if (it >= CONV_LAG) {
+          cp_async_wait<CONV_LAG>();
+          fence_proxy_async_smem();
+          mbar_arrive(&full[(it - CONV_LAG) % CONV_STAGES]);
+        }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async_smem();
-    for (int kb = (num_kb > CONV_LAG ? num_kb - CONV_LAG : 0); kb < num_kb; ++kb) mbar_arrive(&full[kb % CONV_STAGES]);
+    for (uint32_t k = (it > CONV_LAG ? it - CONV_LAG : 0); k < it; ++k) mbar_arrive(&full[k % CONV_STAGES]);
     pdl_trigger();
-    // ---------------------------------------------------------------- epilogue
-    bool acc_ok = mbar_wait(accum, 0, abort, status, STATUS_WAIT_ACCUM);
-    acc_ok = __all_sync(0xffffffffu, acc_ok);
-    tc_fence_after_sync();
-    if (acc_ok) {
-      epi.m0 = m0;
-      epi.n0 = n0;
-#pragma unroll 1
-      for (int col = 0; col < BN; col += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col), r);
-        tmem_ld_wait();
-        epi.run<T>(row, col, r);
-      }
-    }
   } else if (warp == 4) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % CONV_STAGES;
-        if (!mbar_wait(&empty[s], ((kb / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) break;
-        mbar_expect_tx(&full[s], L::B_BYTES);
-        tma_load_2d(tiles + s * L::STAGE_BYTES + L::A_BYTES, &map_w, &full[s], kb * 64, n0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+        const int n0 = (t % n_tiles) * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % CONV_STAGES;
+          if (!mbar_wait(&empty[s], ((it / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) { ok = false; break; }
+          mbar_expect_tx(&full[s], L::B_BYTES);
+          tma_load_2d(tiles + s * L::STAGE_BYTES + L::A_BYTES, &map_w, &full[s], kb * 64, n0);
+        }
+      }
+    }
+    __syncwarp();
+    pdl_trigger();
+  } else if (warp == 5) {
+    if (lane == 0) {
+      uint32_t it = 0, j = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, ++j) {
+        const uint32_t buf = j & 1;
+        if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort, status, STATUS_WAIT_EPI)) break;
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % CONV_STAGES;
+          if (!mbar_wait(&full[s], (it / CONV_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
+          const uint64_t adesc = umma_desc_k128(sa), bdesc = umma_desc_k128(sa + L::A_BYTES);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&acc_full[buf]);
       }
     }
     __syncwarp();
     pdl_trigger();
   } else {
-    if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % CONV_STAGES;
-        if (!mbar_wait(&full[s], (kb / CONV_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
-        tc_fence_after_sync();
-        const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
-        const uint64_t adesc = umma_desc_k128(sa), bdesc = umma_desc_k128(sa + L::A_BYTES);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0);
-        umma_commit(&empty[s]);
+    // ---------------------------------------------------------------- epilogue (warps 6-9 own TMEM lane quarters 2,3,0,1)
+    const int q = warp & 3;
+    pdl_wait();
+    uint32_t j = 0;
+    for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
+      const uint32_t buf = j & 1;
+      bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      epi.m0 = (t / n_tiles) * 128;
+      epi.n0 = (t % n_tiles) * BN;
+      const int row = q * 32 + lane;
+#pragma unroll 1
+      for (int col = 0; col < BN; col += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + buf * BN + uint32_t(col), r);
+        tmem_ld_wait();
+        if (col + 32 >= BN) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        epi.run<T>(row, col, r);
       }
-      umma_commit(accum);
     }
-    __syncwarp();
     pdl_trigger();
   }
   if (*abort) {
@@ -185,11 +223,20 @@ static int launch_conv(const void* x, const CUtensorMap& mw, const ConvShape& cs
   using L = ConvSmem<BN>;
   auto kern = conv_igemm_kernel<BN, T>;
   static bool configured = false;
+  static int resident = 0;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
+    int per_sm = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, CONV_THREADS, L::DYN_SMEM) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    if (per_sm * L::TMEM_COLS > 512) per_sm = 512 / L::TMEM_COLS;
+    resident = (sms > 0 ? sms : 148) * per_sm;
     configured = true;
   }
-  dim3 grid((cs.M + 127) / 128, (cs.Cout + BN - 1) / BN);
+  const int tiles = ((cs.M + 127) / 128) * ((cs.Cout + BN - 1) / BN);
+  dim3 grid(tiles < resident ? tiles : resident);
   const uint32_t idesc = umma_idesc(128, BN, is_bf16 ? 1u : 0u, 1u);
   cudaError_t err = launch(kern, grid, dim3(CONV_THREADS), size_t(L::DYN_SMEM), stream, (const T*)x, mw, cs, e, idesc, status);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;

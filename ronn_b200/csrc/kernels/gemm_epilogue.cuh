@@ -41,7 +41,9 @@ struct DenseEpilogue {
           for (int i = 0; i < 8; ++i) v[j * 8 + i] += f[i];
         }
       } else {
-        for (int i = 0; i < 32 && gn + i < N; ++i) v[i] += Cvt<T>::to_f(res[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gn + i < N) v[i] += Cvt<T>::to_f(res[i]);
       }
     }
     if (act == 1) {
@@ -63,7 +65,9 @@ struct DenseEpilogue {
           for (int i = 0; i < 8; ++i) v[j * 8 + i] += f[i];
         }
       } else {
-        for (int i = 0; i < 32 && gn + i < N; ++i) v[i] += Cvt<T>::to_f(res[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gn + i < N) v[i] += Cvt<T>::to_f(res[i]);
       }
     }
     if (out_fp32) {
@@ -73,7 +77,9 @@ struct DenseEpilogue {
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<float4*>(out + j * 4) = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
       } else {
-        for (int i = 0; i < 32 && gn + i < N; ++i) out[i] = v[i];
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gn + i < N) out[i] = v[i];
       }
     } else {
       T* out = reinterpret_cast<T*>(C) + size_t(gm) * ldc + gn;
@@ -86,7 +92,9 @@ struct DenseEpilogue {
           *reinterpret_cast<Vec8*>(out + j * 8) = pack8<T>(f);
         }
       } else {
-        for (int i = 0; i < 32 && gn + i < N; ++i) out[i] = Cvt<T>::from_f(v[i]);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (gn + i < N) out[i] = Cvt<T>::from_f(v[i]);
       }
     }
   }

@@ -19,6 +19,8 @@ def declare(lib):
     sig("ronn_gemm_splitk", [V, V, V, I, I, I, I, I, I, I, I, V, V, V])
     sig("ronn_splitk_finalize", [V, I, V, V, V, V, V, V, L, I, F, I, I, I, V])
     sig("ronn_gemm_reduce", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I, V, V], optional=True)
+    sig("ronn_ag_gemm", [V, I, V, I, V, I, V, I, I, I, I, I, V, V, I, C.c_double, I, I, V, V], optional=True)
+    sig("ronn_signal_peers", [V, I, I, V], optional=True)
     sig("ronn_norm", [V, V, V, V, V, V, L, I, L, L, L, F, I, I, V])
     sig("ronn_softmax", [V, V, L, I, I, V])
     sig("ronn_unary", [V, V, L, I, I, V])
@@ -29,7 +31,7 @@ def declare(lib):
     sig("ronn_argmax_combine", [V, V, V, I, I, V])
     sig("ronn_cast", [V, V, L, I, I, V])
     sig("ronn_kv_append", [V, L, I, I, V, V, V, V, L, I, I, I, F, I, I, V])
-    sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, V])
+    sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V])
     sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, V], optional=True)
     sig("ronn_maxpool_nhwc", [V, V, I, I, I, I, I, I, I, I, I, I, V], optional=True)
     sig("ronn_global_avgpool_nhwc", [V, V, I, I, I, I, V], optional=True)

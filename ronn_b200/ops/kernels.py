@@ -213,8 +213,10 @@ def kv_append(qkv: torch.Tensor, k_off: int, v_off: int, slots: torch.Tensor, kc
 def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                     ctx_len: torch.Tensor, heads: int, kv_heads: int, head_dim: int, max_ctx: int,
                     bt_row: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    scale: Optional[float] = None) -> torch.Tensor:
-    """q: [rows, >= heads*head_dim] (row stride free).  Returns [rows, heads*head_dim]."""
+                    scale: Optional[float] = None, append=None) -> torch.Tensor:
+    """q: [rows, >= heads*head_dim] (row stride free).  Returns [rows, heads*head_dim].
+    ``append=(k_off, v_off, slots)`` (decode, one row per sequence): the new K/V columns of the fused QKV row are
+    written to their cache slots by the same kernel."""
     rows = q.shape[0]
     if out is None:
         out = torch.empty((rows, heads * head_dim), dtype=q.dtype, device=q.device)
@@ -222,7 +224,9 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     _check(_native.cuda().ronn_paged_attention(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                                block_tables.data_ptr(), block_tables.shape[1], ctx_len.data_ptr(),
                                                _ptr(bt_row), out.data_ptr(), out.stride(0), rows, heads, kv_heads,
-                                               head_dim, int(max_ctx), float(sc), _DT[q.dtype], _stream()),
+                                               head_dim, int(max_ctx), float(sc), _DT[q.dtype],
+                                               append[0] if append else 0, append[1] if append else 0,
+                                               append[2].data_ptr() if append else None, _stream()),
            "paged_attention")
     return out
 

@@ -178,6 +178,50 @@ def bench_norm(rows, h, dtype=torch.bfloat16, flush=True):
             "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)}
 
 
+def bench_conv(n=32, h=56, w=56, c=64, cout=64, r=3, stride=1, pad=1, dtype=torch.float16, flush=True, iters=20):
+    from ..providers.gpu_conv import conv2d_nhwc
+    x = torch.randn(n, h, w, c, device="cuda").to(dtype)
+    wt = (torch.randn(cout, r, r, c, device="cuda") / math.sqrt(r * r * c)).to(dtype)
+    b = torch.zeros(cout, device="cuda", dtype=dtype)
+    ho, wo = (h + 2 * pad - r) // stride + 1, (w + 2 * pad - r) // stride + 1
+    out = torch.empty(n, ho, wo, cout, device="cuda", dtype=dtype)
+    us = time_kernel(lambda: conv2d_nhwc(x, wt, b, None, stride, pad, 1, relu=True, out=out), iters=iters, flush=flush)
+    K.check_status()
+    hbm, tf, src = _peaks()
+    flops = 2.0 * n * ho * wo * cout * r * r * c
+    byts = 2.0 * (x.numel() + wt.numel() + out.numel())
+    roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e6
+    xn, wn = x.permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last), wt.permute(0, 3, 1, 2).contiguous(memory_format=torch.channels_last)
+    us_lib = time_kernel(lambda: torch.relu_(torch.nn.functional.conv2d(xn, wn, b, stride, pad)), iters=iters, flush=flush)
+    return {"kernel": "conv_igemm", "shape": [n, h, w, c, cout, r, stride], "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
+            "roofline_us": round(roof, 2), "frac_of_" + src: round(roof / us, 3), "cudnn_us": round(us_lib, 2)}
+
+
+def bench_bitlinear(m=128, n=2560, k=2560, flush=True, iters=20):
+    from . import bitnet as B
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    wq = torch.randint(-1, 2, (n, k), device="cuda", dtype=torch.int8)
+    packed = B.ternary_pack(wq)
+    q, s = B.act_quant_int8(x)
+    us = time_kernel(lambda: B.bitlinear_q(q, s, packed, 0.04, None, n, k, torch.bfloat16), iters=iters, flush=flush)
+    us_q = time_kernel(lambda: B.act_quant_int8(x), iters=iters, flush=flush)
+    K.check_status()
+    hbm, tf, src = _peaks()
+    byts = n * k / 4.0 + m * k + m * n * 2.0
+    wd = wq.to(torch.bfloat16)
+    us_lib = time_kernel(lambda: torch.matmul(x, wd.t()), iters=iters, flush=flush)
+    return {"kernel": "bitlinear", "m": m, "n": n, "k": k, "us": round(us, 2), "act_quant_us": round(us_q, 2),
+            "gbs": round(byts / us / 1e3, 1), "roofline_us": round(byts / (hbm * 1e9) * 1e6, 2),
+            "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3), "dequantised_bf16_cublas_us": round(us_lib, 2)}
+
+
+def resnet_convs():
+    shapes = [(32, 224, 224, 8, 64, 7, 2, 3), (32, 56, 56, 64, 64, 3, 1, 1), (32, 56, 56, 64, 128, 3, 2, 1), (32, 28, 28, 128, 128, 3, 1, 1),
+              (32, 28, 28, 128, 256, 3, 2, 1), (32, 14, 14, 256, 256, 3, 1, 1), (32, 14, 14, 256, 512, 3, 2, 1), (32, 7, 7, 512, 512, 3, 1, 1),
+              (32, 56, 56, 64, 128, 1, 2, 0)]
+    return [bench_conv(*s) for s in shapes]
+
+
 def decode_shapes(batch=256, ctx=416):
     out = []
     for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (50257 // 8 * 8 + 8, 1024)]:
@@ -189,7 +233,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-attention"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -208,6 +252,14 @@ def main():
         res = [bench_attention(a.batch, a.ctx, a.heads, a.dim, flush=fl, iters=a.iters)]
     elif a.what == "norm":
         res = [bench_norm(a.batch, a.n, flush=fl)]
+    elif a.what == "conv":
+        res = [bench_conv(iters=a.iters, flush=fl)]
+    elif a.what == "resnet-convs":
+        res = resnet_convs()
+    elif a.what == "bitlinear":
+        res = [bench_bitlinear(a.m if a.m != 256 else 128, a.n if a.n != 1024 else 2560, a.k if a.k != 1024 else 2560, flush=fl, iters=a.iters)]
+    elif a.what == "bitnet-shapes":
+        res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
     elif a.what == "sweep-decode-gemm":
         res = sweep_decode_gemm(a.m)
     elif a.what == "sweep-attention":

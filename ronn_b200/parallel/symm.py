@@ -41,8 +41,9 @@ class FusedComm(TPComm):
         self.device = torch.device(device)
         self.max_elems = max_rows * max_cols
         self.part_stride = self.max_elems * 2                       # bytes of one parity slot (16-bit elements)
-        flag_bytes = 256
-        total = 2 * self.part_stride + flag_bytes
+        flag_bytes = 512                                            # reduce flags [2][8] ints, gather flags [8] ints
+        self.shard_bytes = (max_rows // max(self.world, 1) + 128) * max_cols * 2
+        total = 2 * self.part_stride + flag_bytes + self.shard_bytes
         self._buf = symm.empty(total, dtype=torch.uint8, device=self.device)
         self._buf.zero_()
         torch.cuda.synchronize(self.device)
@@ -52,6 +53,14 @@ class FusedComm(TPComm):
         self._part_ptrs = (C.c_void_p * MAX_RANKS)(*[ptrs[p] if p < self.world else None for p in range(MAX_RANKS)])
         self._flag_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + 2 * self.part_stride) if p < self.world else None
                                                     for p in range(MAX_RANKS)])
+        self._ag_flag_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + 2 * self.part_stride + 256) if p < self.world else None
+                                                       for p in range(MAX_RANKS)])
+        shard_off = 2 * self.part_stride + flag_bytes
+        self._shard_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + shard_off) if p < self.world else None
+                                                     for p in range(MAX_RANKS)])
+        self._shard_local = self._buf[shard_off: shard_off + self.shard_bytes]
+        self._ag_flags_local = ptrs[self.rank] + 2 * self.part_stride + 256
+        self._ag_state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
         self.fused_calls = 0
@@ -100,6 +109,38 @@ class FusedComm(TPComm):
             raise ProviderError("reduce-scatter needs the row count to divide by the world size")
         per = M // self.world
         return self._gemm_reduce(a, w_nk, bias, residual_shard, self.rank * per, (self.rank + 1) * per, bn)
+
+    # ------------------------------------------------------------------ fused all-gather -> column-parallel GEMM
+    def shard_buffer(self, rows: int, cols: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """This rank's [rows, cols] activation shard inside the symmetric allocation: write the shard here (e.g. as the
+        output of the norm kernel), call ``signal_shard_ready()``, then ``ag_gemm``."""
+        nbytes = rows * cols * 2
+        if nbytes > self.shard_bytes:
+            raise ProviderError(f"shard of {rows}x{cols} exceeds the symmetric shard buffer")
+        return self._shard_local[:nbytes].view(dtype).view(rows, cols)
+
+    def signal_shard_ready(self) -> None:
+        rc = _native.cuda().ronn_signal_peers(self._ag_flag_ptrs, self.rank, self.world,
+                                              torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"signal_peers failed with code {rc}")
+
+    def ag_gemm(self, rows_per_rank: int, k: int, w_nk: torch.Tensor, bias=None, activation: str = "", bn: int = 0):
+        """concat over ranks of the [rows_per_rank, k] shards (read tile by tile from peer memory) @ w_nk^T.
+        rows_per_rank must be a multiple of 128; a fused row-parallel GEMM must separate two gathers."""
+        N = w_nk.shape[0]
+        out = torch.empty((rows_per_rank * self.world, N), dtype=w_nk.dtype, device=w_nk.device)
+        if bias is not None and bias.dtype != w_nk.dtype:
+            bias = bias.to(w_nk.dtype)
+        rc = _native.cuda().ronn_ag_gemm(self._shard_ptrs, k, w_nk.data_ptr(), w_nk.stride(0), out.data_ptr(), out.stride(0),
+                                         None if bias is None else bias.data_ptr(), rows_per_rank, N, k, self.rank, self.world,
+                                         self._ag_flags_local, self._ag_state.data_ptr(), K._ACT[activation],
+                                         self.wait_seconds, 0 if w_nk.dtype == torch.bfloat16 else 1, bn,
+                                         K.status_word(w_nk.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"ag_gemm failed with code {rc}")
+        self.fused_calls += 1
+        return out
 
     def check(self) -> None:
         K.check_status(self.device)

@@ -239,10 +239,14 @@ class DecoderRunner:
         for li, L in enumerate(self.layers):
             h = h_next if h_next is not None else self._norm(x, L["ln1"])
             qkv = self._linear(h, L["qkv"])
-            ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
-                          self.n_kv_local, d, pos, a.rope_base)
-            att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
-                                      self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
+            if decode and a.rope_base == 0 and ops.name == "kernels":
+                att = ops.append_attention(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], b["block_tables"],
+                                           ctx, self.n_head_local, self.n_kv_local, d, max_ctx)
+            else:
+                ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
+                              self.n_kv_local, d, pos, a.rope_base)
+                att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
+                                          self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
             x, h = row_parallel(att, L["out"], x, L["ln2"], False)
             if h is None:
                 h = self._norm(x, L["ln2"])

@@ -148,6 +148,11 @@ class KernelOps:
     def paged_attention(self, q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row=None):
         return self.K.paged_attention(q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row)
 
+    def append_attention(self, qkv, k_off, v_off, slots, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx):
+        """Decode step: cache append and attention in one launch."""
+        return self.K.paged_attention(qkv, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx,
+                                      append=(k_off, v_off, slots))
+
     def argmax(self, logits, col_offset=0, return_max=False):
         return self.K.argmax(logits, col_offset, return_max)
 

@@ -49,6 +49,23 @@ def main():
                 ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
                 errs = (ys.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
                 results.append({"mode": "rs", "M": M, "N": N, "K": Kl, "err": errs, "identical": True})
+    # all-gather -> GEMM: shards live in symmetric memory and are read tile by tile through peer tensor maps
+    for (rows, Kd, N) in [(128, 256, 384), (256, 1024, 512), (128, 64, 72)]:
+        for it in range(2):
+            shard = comm.shard_buffer(rows, Kd)
+            xs = torch.randn(rows, Kd, device=dev).bfloat16()
+            shard.copy_(xs)
+            comm.signal_shard_ready()
+            w = (torch.randn(N, Kd, device=dev) * 0.05).bfloat16()
+            bias = torch.randn(N, device=dev).bfloat16()
+            y = comm.ag_gemm(rows, Kd, w, bias, "gelu")
+            full = torch.empty(world * rows, Kd, device=dev, dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(full, xs)
+            ref = torch.nn.functional.gelu(full.float() @ w.float().t() + bias.float(), approximate="tanh")
+            results.append({"mode": "ag", "M": rows * world, "N": N, "K": Kd, "err": (y.float() - ref).abs().max().item(),
+                            "identical": True})
+            # a synchronising fused call must separate two gathers (single-buffered shards)
+            comm.gemm_allreduce(xs[:, :64].contiguous(), w[:, :64].contiguous())
     # CUDA-graph replay: the call counter lives on the device, so replays need no new arguments
     a = torch.randn(256, 128, device=dev).bfloat16()
     w = (torch.randn(1024, 128, device=dev) * 0.05).bfloat16()

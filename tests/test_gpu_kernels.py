@@ -49,6 +49,34 @@ def test_gemm_epilogue(K, act):
     torch.testing.assert_close(y32, ref - res.float(), atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K_,S,bn", [(256, 1024, 4096, 4, 64), (64, 1024, 4096, 8, 0), (37, 136, 1024, 3, 32),
+                                         (128, 768, 3072, 4, 128)])
+@pytest.mark.parametrize("norm", ["", "layernorm", "rmsnorm"])
+def test_gemm_splitk_and_finalize(K, M, N, K_, S, bn, norm):
+    a, w = _rand(M, K_), _rand(N, K_, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    gamma, beta = _rand(N), _rand(N)
+    ws, s_eff = K.gemm_splitk(a, w, S, bn=bn)
+    K.check_status()
+    assert 1 <= s_eff <= S
+    part = ws[:s_eff * M * N].view(s_eff, M, N)
+    ref = a.float() @ w.float().t()
+    torch.testing.assert_close(part.sum(0), ref, atol=2e-2 * math.sqrt(K_ / 64), rtol=2e-2)
+    total, y = K.splitk_finalize(ws, s_eff, M, N, torch.bfloat16, bias=bias, residual=res, gamma=gamma,
+                                 beta=beta if norm == "layernorm" else None, norm=norm)
+    full = ref + bias.float() + res.float()
+    torch.testing.assert_close(total.float(), full, atol=0.15, rtol=2e-2)
+    if norm:
+        t = total.float()
+        if norm == "layernorm":
+            want = F.layer_norm(t, (N,), gamma.float(), beta.float(), 1e-5)
+        else:
+            want = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+        torch.testing.assert_close(y.float(), want, atol=6e-2, rtol=3e-2)
+    else:
+        assert y is None
+
+
 @pytest.mark.parametrize("H", [128, 768, 1024, 2560])
 def test_layernorm_rmsnorm(K, H):
     x, r = _rand(37, H), _rand(37, H)
