@@ -125,14 +125,6 @@ def main():
     else:
         comm = None
     eng = LLMEngine(model, ecfg, device=dev, comm=comm)
-    # hand-written kernels launched per decode step (library collectives and torch adds are not counted)
-    if world == 1:
-        launches_per_step = 2 + 7 * cfg.n_layer + 2       # embed, first norm | qkv, attn+append, out, norm, up, down(split-K), finalize+norm | LM head, argmax
-    elif ecfg.tp_comm == "fused":
-        launches_per_step = 2 + 5 * cfg.n_layer + 3       # qkv, attn+append, out+all-reduce+norm, up, down+all-reduce+norm | LM head, argmax, combine
-    else:
-        launches_per_step = 1 + 7 * cfg.n_layer + 4       # embed | norm, qkv, attn+append, out, norm, up, down | final norm, LM head, argmax, combine
-
     rng = np.random.default_rng(1234)
     lens = rng.integers(64, 513, size=args.requests)
     for n in lens:
@@ -181,6 +173,17 @@ def main():
         c = TPComm()
         dev_ms = c.max_over_ranks(dev_ms)
         wall = c.max_over_ranks(wall)
+    # hand-written kernels launched per decode step (library collectives and torch copies are not counted); a step
+    # that runs as concurrent part-batches launches the per-layer kernels once per part
+    parts = len(eng._split_rows(eng._bucket(args.requests)) or [None])
+    if world == 1:
+        per_part = 2 + 7 * cfg.n_layer + 2    # embed, first norm | qkv, attn+append, out, norm, up, down(split-K), finalize+norm | LM head, argmax
+        launches_per_step = parts * per_part
+    elif ecfg.tp_comm == "fused":
+        per_part = 2 + 5 * cfg.n_layer + 2    # qkv, attn+append, out+all-reduce+norm, up, down+all-reduce+norm | LM head, argmax
+        launches_per_step = parts * per_part + 1                                  # + combine over ranks
+    else:
+        launches_per_step = 1 + 7 * cfg.n_layer + 4       # embed | norm, qkv, attn+append, out, norm, up, down | final norm, LM head, argmax, combine
     tokens = args.requests * K
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / wall
@@ -199,6 +202,7 @@ def main():
                        "l2": "inputs larger than L2 (KV read per step >> 126 MB)",
                        "prefill_seconds_untimed": round(prefill_s, 3),
                        "pdl": os.environ.get("RONN_PDL", "1") != "0",
+                       "decode_part_batches": parts,
                        "host_ms_per_step": {"schedule_upload_replay_wait": round(host_dev * 1e3 / K, 4),
                                             "commit_bookkeeping": round(host_book * 1e3 / K, 4)}},
             "clocks": clocks,

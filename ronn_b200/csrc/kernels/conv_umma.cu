@@ -23,7 +23,7 @@ namespace ronn {
 
 constexpr int CONV_THREADS = 320;    // warps 0-3 gather A, 4 weight TMA, 5 MMA issuer, 6-9 epilogue
 constexpr int CONV_STAGES = 4;
-constexpr int CONV_LAG = 2;          // cp.async groups a producer thread keeps in flight
+constexpr int CONV_LAG = 3;          // cp.async groups a producer thread keeps in flight
 
 struct ConvShape {
   int N, H, W, C;          // input
@@ -45,7 +45,7 @@ struct ConvSmem {
 
 // Persistent: a CTA walks output tiles (tile = blockIdx.x, += gridDim.x); the smem ring and its barrier phases run
 // across tiles and the accumulator is double-buffered in TMEM, so the gather of tile j+1 overlaps the epilogue of j.
-template <int BN, class T>
+template <int BN, class T, bool FAST>
 __global__ void __launch_bounds__(CONV_THREADS)
 conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap map_w, ConvShape cs, DenseEpilogue epi,
                   uint32_t idesc, uint32_t* status) {
@@ -90,7 +90,6 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
     // ---------------------------------------------------------------- A gather (one output pixel per thread)
     pdl_wait();
     const int row = threadIdx.x;
-    const int c8n = cs.C >> 3;
     const uint32_t sw = uint32_t(row & 7);
     uint32_t it = 0;
     bool ok = true;
@@ -106,21 +105,38 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
       }
       const int ih0 = oh * cs.stride - cs.pad, iw0 = ow * cs.stride - cs.pad;
       const T* img = x + size_t(n_img) * cs.H * cs.W * cs.C;
-      int r = 0, sx = 0, c8 = 0;                 // filter tap and channel chunk of the next K chunk (no divisions)
+      // filter tap and channel position of the next K chunk, advanced incrementally (no divisions in the loop);
+      // offsets inside one image fit 32 bits
+      int r = 0, sx = 0, cpos = 0;
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % CONV_STAGES;
         if (ok && !mbar_wait(&empty[s], ((it / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
         if (ok) {
           uint8_t* dst_row = tiles + s * L::STAGE_BYTES + row * 128;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          if (FAST) {
+            // C % 64 == 0: the whole 128-byte row of this K block is one filter tap, 64 consecutive channels
             const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
-            const bool valid = row_ok && r < cs.R && ih >= 0 && ih < cs.H && iw >= 0 && iw < cs.W;
-            const T* src = valid ? img + (size_t(ih) * cs.W + iw) * cs.C + c8 * 8 : x;
-            cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
-            if (++c8 == c8n) {
-              c8 = 0;
+            const bool valid = row_ok && unsigned(ih) < unsigned(cs.H) && unsigned(iw) < unsigned(cs.W);
+            const T* src = valid ? img + (ih * cs.W + iw) * cs.C + cpos : x;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src + j * 8, valid);
+            cpos += 64;
+            if (cpos == cs.C) {
+              cpos = 0;
               if (++sx == cs.S) { sx = 0; ++r; }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
+              const bool valid = row_ok && r < cs.R && unsigned(ih) < unsigned(cs.H) && unsigned(iw) < unsigned(cs.W);
+              const T* src = valid ? img + (ih * cs.W + iw) * cs.C + cpos : x;
+              cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
+              cpos += 8;
+              if (cpos == cs.C) {
+                cpos = 0;
+                if (++sx == cs.S) { sx = 0; ++r; }
+              }
             }
           }
         }
@@ -217,29 +233,35 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
   }
 }
 
-template <int BN, class T>
-static int launch_conv(const void* x, const CUtensorMap& mw, const ConvShape& cs, const DenseEpilogue& e, int is_bf16,
-                       uint32_t* status, cudaStream_t stream) {
+template <int BN, class T, bool FAST>
+static int launch_conv_impl(const void* x, const CUtensorMap& mw, const ConvShape& cs, const DenseEpilogue& e, int is_bf16,
+                            uint32_t* status, cudaStream_t stream) {
   using L = ConvSmem<BN>;
-  auto kern = conv_igemm_kernel<BN, T>;
+  auto kern = conv_igemm_kernel<BN, T, FAST>;
   static bool configured = false;
-  static int resident = 0;
+  static int sms = 0;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    int per_sm = 0, dev = 0, sms = 0;
+    int dev = 0;
     cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, CONV_THREADS, L::DYN_SMEM) != cudaSuccess || per_sm < 1)
-      per_sm = 1;
-    if (per_sm * L::TMEM_COLS > 512) per_sm = 512 / L::TMEM_COLS;
-    resident = (sms > 0 ? sms : 148) * per_sm;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     configured = true;
   }
+  // two CTAs per SM when shared memory (227 KB) and TMEM (512 columns) allow it
+  const int per_sm = (L::DYN_SMEM <= 110 * 1024 && L::TMEM_COLS <= 256) ? 2 : 1;
+  const int resident = sms * per_sm;
   const int tiles = ((cs.M + 127) / 128) * ((cs.Cout + BN - 1) / BN);
   dim3 grid(tiles < resident ? tiles : resident);
   const uint32_t idesc = umma_idesc(128, BN, is_bf16 ? 1u : 0u, 1u);
   cudaError_t err = launch(kern, grid, dim3(CONV_THREADS), size_t(L::DYN_SMEM), stream, (const T*)x, mw, cs, e, idesc, status);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+template <int BN, class T>
+static int launch_conv(const void* x, const CUtensorMap& mw, const ConvShape& cs, const DenseEpilogue& e, int is_bf16,
+                       uint32_t* status, cudaStream_t stream) {
+  if ((cs.C & 63) == 0) return launch_conv_impl<BN, T, true>(x, mw, cs, e, is_bf16, status, stream);
+  return launch_conv_impl<BN, T, false>(x, mw, cs, e, is_bf16, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------- pooling (NHWC)

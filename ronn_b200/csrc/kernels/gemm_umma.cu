@@ -106,11 +106,21 @@ int pick_bn(int M, int N) {
   return 32;
 }
 
+// Pipeline depth.  A CTA that is alone on its SM is fed by the bytes it keeps in flight, so when the whole problem
+// is at most one CTA per SM the ring is twice as deep (6 / 8 / 10 stages for BN 128 / 64 / 32, one CTA per SM)
+// instead of two co-resident CTAs with half the ring each.  bn | 0x1000 forces the deep ring, bn | 0x2000 the shallow.
+static int deep_mode(int bn) { return (bn & 0x1000) ? 1 : ((bn & 0x2000) ? 0 : -1); }
+static int wants_deep(int M, int N, int bn, int splitk) {
+  const int tiles = ((N + bn - 1) / bn) * ((M + PG_BM - 1) / PG_BM) * splitk;
+  return tiles <= sm_count() ? 1 : 0;
+}
+
 }  // namespace ronn
 
 using namespace ronn;
 
-// dtype: 0 = bf16, 1 = fp16.  act: 0 none, 1 relu, 2 gelu.  bn: 0 = auto, else 32|64|128|256.
+// dtype: 0 = bf16, 1 = fp16.  act: 0 none, 1 relu, 2 gelu.  bn: 0 = auto, else 32|64|128|256 (| 0x1000 deep ring,
+// | 0x2000 shallow ring; default picks by tile count).
 // lda/ldw/ldc in elements; K and the leading dimensions must be multiples of 8.
 // Returns 0 on success, negative on configuration errors.
 extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias, const void* residual, int M, int N,
@@ -118,7 +128,10 @@ extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias
                          uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   if ((K & 7) || (lda & 7) || (ldw & 7)) return -2;
+  int deep = deep_mode(bn);
+  bn &= 0xfff;
   if (bn == 0) bn = pick_bn(M, N);
+  if (deep < 0) deep = wants_deep(M, N, bn, 1);
   CUtensorMap ma, mb;
   int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), PG_BM, 64, 2);
   if (rc) return rc - 20;
@@ -129,11 +142,14 @@ extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias
 #define RONN_DISPATCH(BN_, ST_)                                                                       \
   return bf ? launch_dense<BN_, ST_, __nv_bfloat16>(ma, mb, e, M, N, K, 1, status, stream)            \
             : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream)
-  switch (bn) {
-    case 256: RONN_DISPATCH(256, 4);
+  switch (deep ? -bn : bn) {
+    case 256: case -256: RONN_DISPATCH(256, 4);
     case 128: RONN_DISPATCH(128, 3);
     case 64: RONN_DISPATCH(64, 4);
     case 32: RONN_DISPATCH(32, 5);
+    case -128: RONN_DISPATCH(128, 6);
+    case -64: RONN_DISPATCH(64, 8);
+    case -32: RONN_DISPATCH(32, 10);
     default: return -3;
   }
 #undef RONN_DISPATCH
@@ -152,7 +168,10 @@ extern "C" int ronn_gemm_splitk(const void* A, const void* W, float* workspace, 
   const int per = (num_kb + splitk - 1) / splitk;
   splitk = (num_kb + per - 1) / per;
   if (splitk_out) *splitk_out = splitk;
+  int deep = deep_mode(bn);
+  bn &= 0xfff;
   if (bn == 0) bn = N >= 128 ? 128 : (N >= 64 ? 64 : 32);
+  if (deep < 0) deep = wants_deep(M, N, bn, splitk);
   CUtensorMap ma, mb;
   int rc = make_tmap_2d(&ma, A, uint64_t(M), uint64_t(K), uint64_t(lda), PG_BM, 64, 2);
   if (rc) return rc - 20;
@@ -163,11 +182,14 @@ extern "C" int ronn_gemm_splitk(const void* A, const void* W, float* workspace, 
 #define RONN_DISPATCH(BN_, ST_)                                                                          \
   return bf ? launch_dense<BN_, ST_, __nv_bfloat16>(ma, mb, e, M, N, K, 1, status, stream, splitk)       \
             : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream, splitk)
-  switch (bn) {
-    case 256: RONN_DISPATCH(256, 4);
+  switch (deep ? -bn : bn) {
+    case 256: case -256: RONN_DISPATCH(256, 4);
     case 128: RONN_DISPATCH(128, 3);
     case 64: RONN_DISPATCH(64, 4);
     case 32: RONN_DISPATCH(32, 5);
+    case -128: RONN_DISPATCH(128, 6);
+    case -64: RONN_DISPATCH(64, 8);
+    case -32: RONN_DISPATCH(32, 10);
     default: return -3;
   }
 #undef RONN_DISPATCH

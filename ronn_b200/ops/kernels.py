@@ -235,12 +235,16 @@ _WORKSPACES = {}
 
 
 def splitk_workspace(device, nfloats: int) -> torch.Tensor:
-    """Per-device fp32 scratch for split-K partial sums, grown on demand and reused by every call."""
+    """fp32 scratch for split-K partial sums, one per (device, stream) so that launches on concurrent streams never
+    share it; grown on demand and reused by every call on that stream."""
     dev = torch.device(device)
-    w = _WORKSPACES.get(dev)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    w = _WORKSPACES.get(key)
     if w is None or w.numel() < nfloats:
         w = torch.empty(max(nfloats, 1 << 22), dtype=torch.float32, device=dev)
-        _WORKSPACES[dev] = w
+        _WORKSPACES[key] = w
     return w
 
 

@@ -133,6 +133,23 @@ def sweep_attention():
     return out
 
 
+def sweep_gemm_depth(m=256):
+    """Shallow ring (two CTAs per SM) against deep ring (one CTA per SM, twice the stages) on the decode shapes."""
+    out = []
+    for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (50264, 1024)]:
+        nvar = max(2, int(300e6 // (n * k * 2)))
+        ws = [(torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(nvar)]
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        for bn in (32, 64, 128):
+            row = {"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn}
+            for name, flag in (("shallow_us", 0x2000), ("deep_us", 0x1000)):
+                row[name] = round(time_graph(lambda i: K.gemm(a, ws[i], out=o, bn=bn | flag), nvar), 2)
+            out.append(row)
+        K.check_status()
+    return out
+
+
 def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20):
     a = torch.randn(m, k, device="cuda").to(dtype)
     w = (torch.randn(n, k, device="cuda") * 0.05).to(dtype)
@@ -233,7 +250,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -262,6 +279,8 @@ def main():
         res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
     elif a.what == "sweep-decode-gemm":
         res = sweep_decode_gemm(a.m)
+    elif a.what == "sweep-gemm-depth":
+        res = sweep_gemm_depth(a.m)
     elif a.what == "sweep-attention":
         res = sweep_attention()
     elif a.what == "prefill-shapes":

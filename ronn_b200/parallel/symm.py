@@ -35,6 +35,7 @@ class FusedComm(TPComm):
     def __init__(self, device: torch.device, max_rows: int = 8192, max_cols: int = 8192, group=None,
                  wait_seconds: Optional[float] = None):
         super().__init__(group)
+        self._ctor = dict(max_rows=max_rows, max_cols=max_cols, group=group, wait_seconds=wait_seconds)
         if self.world > MAX_RANKS:
             raise ProviderError(f"fused collectives support at most {MAX_RANKS} ranks")
         import torch.distributed._symmetric_memory as symm
@@ -65,6 +66,14 @@ class FusedComm(TPComm):
         self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
         self.fused_calls = 0
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
+
+    def clone(self, max_rows: Optional[int] = None) -> "FusedComm":
+        """A second communicator with its own symmetric buffers, flags and call counter, for launches that run
+        concurrently with this one's on another stream.  Collective: every rank calls it in the same order."""
+        kw = dict(self._ctor)
+        if max_rows is not None:
+            kw["max_rows"] = max_rows
+        return FusedComm(self.device, **kw)
 
     # ------------------------------------------------------------------ fused row-parallel GEMM
     def _gemm_reduce(self, a, w_nk, bias, residual, row_begin, row_end, bn=0, norm=None):

@@ -24,11 +24,14 @@ class EngineConfig:
     backend: str = "kernels"            # "kernels" (hand-written sm_100a) | "torch" (library baseline / CPU)
     tp_comm: str = "fused"              # "fused" (in-kernel NVLink) | "nccl" (library collectives baseline)
     gpu_memory_utilization: float = 0.85
+    decode_streams: int = 2             # decode batches >= decode_split_min rows run as this many concurrent halves
+    decode_split_min: int = 64          # (one stream each, inside the step's CUDA graph): the bandwidth-bound
+                                        # attention of one overlaps the latency-bound GEMM chain of the others
 
     def __post_init__(self):
         if self.block_size != 16:
             raise ValueError("the paged attention kernels are built for 16-token blocks")
-        for k in ("max_num_seqs", "max_batch_tokens", "max_model_len"):
+        for k in ("max_num_seqs", "max_batch_tokens", "max_model_len", "decode_streams"):
             env = os.environ.get("RONN_" + k.upper())
             if env:
                 setattr(self, k, int(env))

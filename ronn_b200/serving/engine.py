@@ -84,6 +84,8 @@ class LLMEngine:
         self._non_greedy = 0
         self._watch_count = 0
         self.host_seconds_last = (0.0, 0.0)
+        self._part_streams: List[torch.cuda.Stream] = []
+        self._part_comms: list = []
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Iterable[int], params: Optional[SamplingParams] = None,
@@ -260,22 +262,75 @@ class LLMEngine:
         key = (bsz, self.runner.step_ctx)
         entry = self._graphs.get(key)
         if entry is None:
-            b = self._batch_views(bsz, bsz)
+            parts = self._split_rows(bsz)
+            if parts is None:
+                b = self._batch_views(bsz, bsz)
+                run = lambda: self.runner.forward(b, True, bsz, bsz)
+            else:
+                views = self._batch_views(bsz, bsz)
+                subs = [({k: v[r0:r1] for k, v in views.items()}, r1 - r0) for (r0, r1) in parts]
+                run = lambda: self._forward_parts(subs)
             # warm-up outside capture (loads kernels, sizes caches), then capture
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                self.runner.forward(b, True, bsz, bsz)
+                run()
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                out = self.runner.forward(b, True, bsz, bsz)
+                out = run()
             entry = (g, out)
             self._graphs[key] = entry
         g, out = entry
         g.replay()
         return out
+
+    # ------------------------------------------------------------------ concurrent part-batches of a decode step
+    def _split_rows(self, bsz: int):
+        """Row ranges of the part-batches of a decode step, or None when the step runs as one batch.  A decode step
+        alternates HBM-bound attention with GEMMs that are too small to fill the GPU; run as independent halves on
+        separate streams, the attention of one half overlaps the GEMM chain of the other."""
+        n = min(int(self.cfg.decode_streams), 8)
+        r = self.runner
+        if n <= 1 or self.cfg.backend != "kernels" or bsz < self.cfg.decode_split_min * 2:
+            return None
+        if r.tp > 1 and not getattr(self.comm, "fused", False):
+            return None          # library collectives of one communicator must not be issued from concurrent streams
+        n = min(n, bsz // self.cfg.decode_split_min)
+        # fused-collective kernels spin on their peers, so every one of them that can be in flight at once has to
+        # fit on the GPU together: a part-batch stays within two row tiles (at most 64 CTAs per kernel)
+        if r.tp > 1 and -(-bsz // n) > 256:
+            return None
+        per = -(-bsz // n)
+        per = -(-per // 16) * 16
+        parts = [(r0, min(r0 + per, bsz)) for r0 in range(0, bsz, per)]
+        if len(parts) < 2:
+            return None
+        while len(self._part_streams) < len(parts):
+            self._part_streams.append(torch.cuda.Stream(self.device))
+        if r.tp > 1:
+            while len(self._part_comms) < len(parts):        # collective: every rank reaches this at the same step
+                self._part_comms.append(self.comm.clone(max_rows=1024) if self._part_comms else self.comm)
+        return parts
+
+    def _forward_parts(self, subs) -> torch.Tensor:
+        main = torch.cuda.current_stream()
+        tp = self.runner.tp > 1
+        res = []
+        for i, (b, n) in enumerate(subs):
+            st = self._part_streams[i]
+            st.wait_stream(main)
+            with torch.cuda.stream(st):
+                res.append(self.runner.forward(b, True, n, n, comm=self._part_comms[i] if tp else None,
+                                               local_argmax=tp))
+        for i in range(len(subs)):
+            main.wait_stream(self._part_streams[i])
+        if tp:
+            idx = torch.cat([r[0] for r in res])
+            mx = torch.cat([r[1] for r in res])
+            return self.runner.combine_argmax(idx, mx)
+        return torch.cat(res)
 
     # ------------------------------------------------------------------ convenience
     def generate(self, prompts: List[List[int]], params: Optional[SamplingParams] = None,

@@ -172,23 +172,24 @@ class DecoderRunner:
         self.vcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
 
     # ------------------------------------------------------------------ forward
-    def _linear(self, x, lw: LinearW, residual=None, activation="", reduce=False):
+    def _linear(self, x, lw: LinearW, residual=None, activation="", reduce=False, comm=None):
         ops = self.ops
+        comm = comm or self.comm
         if lw.packed is not None:
             from ..providers.bitnet import kernels as BK
             y = BK.bitlinear(x, lw, backend=ops.name)
             if reduce and self.tp > 1:
-                y = self.comm.all_reduce(y)
+                y = comm.all_reduce(y)
             if residual is not None:
                 y = y + residual
             return y
-        if reduce and self.tp > 1 and getattr(self.comm, "fused", False) and ops.name == "kernels":
+        if reduce and self.tp > 1 and getattr(comm, "fused", False) and ops.name == "kernels":
             # one kernel: partial GEMM on the tensor cores + cross-rank reduction over NVLink + bias + residual
-            return self.comm.gemm_allreduce(x, lw.w, lw.bias, residual)
+            return comm.gemm_allreduce(x, lw.w, lw.bias, residual)
         if reduce and self.tp > 1:
             # bias and residual are applied once, after the partial sums are combined
             y = ops.gemm(x, lw.w)
-            y = self.comm.all_reduce(y)
+            y = comm.all_reduce(y)
             if lw.bias is not None:
                 y = y + lw.bias
             if residual is not None:
@@ -202,10 +203,13 @@ class DecoderRunner:
         return self.ops.rmsnorm(x, p[0], self.arch.eps)
 
     def forward(self, b: Dict[str, torch.Tensor], decode: bool, n_tokens: int, n_items: int,
-                want_logits: bool = False) -> torch.Tensor:
+                want_logits: bool = False, comm=None, local_argmax: bool = False):
         """Runs one step over device-side batch tensors (already sliced to n_tokens / n_items) and returns the
-        greedy token of every item as int32 [n_items] (or, with ``want_logits`` and TP=1, the fp32 logits)."""
+        greedy token of every item as int32 [n_items] (or, with ``want_logits`` and TP=1, the fp32 logits).
+        ``comm`` replaces the runner's communicator (concurrent part-batches each need their own); with
+        ``local_argmax`` a tensor-parallel rank returns its (index, max) pair and the caller combines the ranks."""
         a, ops, d = self.arch, self.ops, self.arch.head_dim
+        comm = comm or self.comm
         ids, pos, slots = b["token_ids"], b["positions"], b["slot_mapping"]
         if a.rope_base > 0:
             x = ops.embedding(ids, self.wte)
@@ -220,7 +224,7 @@ class DecoderRunner:
         max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
         split_down = (ops.name == "kernels" and self.tp == 1 and x.shape[0] <= 512 and not a.bitlinear
                       and self.layers[0]["down"].w is not None and self.layers[0]["down"].w.shape[1] >= 2048)
-        fused_tp = (ops.name == "kernels" and self.tp > 1 and getattr(self.comm, "fused", False) and not a.bitlinear
+        fused_tp = (ops.name == "kernels" and self.tp > 1 and getattr(comm, "fused", False) and not a.bitlinear
                     and a.hidden <= 1024)
 
         def row_parallel(inp, lw, residual, norm_params, allow_split):
@@ -228,12 +232,12 @@ class DecoderRunner:
             fused paths the reduction pass already holds whole rows, so it applies the next norm as well."""
             if fused_tp:
                 if norm_params is None:
-                    return self.comm.gemm_allreduce(inp, lw.w, lw.bias, residual), None
+                    return comm.gemm_allreduce(inp, lw.w, lw.bias, residual), None
                 beta = norm_params[1] if len(norm_params) > 1 else None
-                return self.comm.gemm_allreduce(inp, lw.w, lw.bias, residual, norm=(a.norm, norm_params[0], beta, a.eps))
+                return comm.gemm_allreduce(inp, lw.w, lw.bias, residual, norm=(a.norm, norm_params[0], beta, a.eps))
             if allow_split and split_down:
                 return ops.gemm_splitk_norm(inp, lw, residual, norm_params, a.norm, a.eps, 4)
-            return self._linear(inp, lw, residual=residual, reduce=True), None
+            return self._linear(inp, lw, residual=residual, reduce=True, comm=comm), None
 
         h_next = None
         for li, L in enumerate(self.layers):
@@ -270,7 +274,14 @@ class DecoderRunner:
         if self.tp == 1:
             return ops.argmax(logits)
         idx, mx = ops.argmax(logits, col_offset=self.vocab_start, return_max=True)
-        vals = self.comm.all_gather_small(mx)
-        idxs = self.comm.all_gather_small(idx)
-        return ops.argmax_combine(vals.contiguous(), idxs.contiguous())
+        if local_argmax:
+            return idx, mx
+        return self.combine_argmax(idx, mx, comm)
+
+    def combine_argmax(self, idx, mx, comm=None):
+        """Greedy token over the vocabulary shards: gather every rank's (index, max) and keep the largest value."""
+        comm = comm or self.comm
+        vals = comm.all_gather_small(mx)
+        idxs = comm.all_gather_small(idx)
+        return self.ops.argmax_combine(vals.contiguous(), idxs.contiguous())
 

@@ -45,3 +45,24 @@ def test_graph_and_eager_decode_agree():
     a = _engine(model, "kernels", graph=True).generate(prompts, SamplingParams(max_new_tokens=10))
     b = _engine(model, "kernels", graph=False).generate(prompts, SamplingParams(max_new_tokens=10))
     assert a == b
+
+
+def test_concurrent_part_batches_give_the_same_tokens():
+    """A decode step split into part-batches on concurrent streams computes every row exactly as the single-batch
+    step does (rows are independent and the per-row reduction order does not change)."""
+    from ronn_b200.api.model import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    cfg = GPT2Config.tiny(n_layer=2, n_embd=256, n_head=4, vocab_size=1000, n_positions=128)
+    model = Model.from_graph(build_gpt2(cfg, dtype=torch.bfloat16, seed=7))
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1000, (int(n),), generator=g).tolist() for n in torch.randint(1, 40, (150,), generator=g)]
+    outs = []
+    for streams in (1, 2, 3):
+        ecfg = EngineConfig(max_num_seqs=160, max_batch_tokens=2048, max_model_len=128, num_blocks=160 * 8, dtype="bf16",
+                            backend="kernels", use_cuda_graph=True, decode_streams=streams, decode_split_min=32)
+        eng = LLMEngine(model, ecfg, device=torch.device("cuda", 0))
+        outs.append(eng.generate(prompts, SamplingParams(max_new_tokens=6)))
+        if streams > 1:
+            assert len(eng._part_streams) == streams
+    assert outs[0] == outs[1] == outs[2]
