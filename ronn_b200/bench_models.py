@@ -153,19 +153,61 @@ def bench_mlp784(iters=2000):
 
 
 def bench_distilbert(batch=64, seq=128, iters=20):
+    """Encoder forward, batch x seq tokens.  Under ``torchrun`` the runner is tensor parallel over all ranks (fused
+    GEMM + all-reduce + LayerNorm kernels) and the time is the maximum over ranks; on one GPU the graph session and a
+    PyTorch library implementation (cuBLAS + SDPA) are timed as well."""
+    import os
     from . import Model, SessionOptions
     from .models.distilbert import build_distilbert
+    from .serving.encoder_runner import EncoderRunner
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm = None
+    if world > 1:
+        from .parallel.fused import make_comm
+        from .parallel.group import init_distributed
+        rank, world, local = init_distributed()
+        torch.cuda.set_device(local)
+        comm = make_comm(os.environ.get("RONN_TP_COMM", "fused"), torch.device("cuda", local))
+    else:
+        rank = 0
     graph = build_distilbert(dtype=torch.bfloat16, seed=0)
     model = Model.from_graph(graph)
-    ids = torch.randint(0, 30522, (batch, seq), device="cuda")
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 30522, (batch, seq), generator=gen).cuda()
     mask = torch.ones(batch, seq, dtype=torch.int64, device="cuda")
     out = {}
-    for name, graphed in (("ours_cuda_graph", True), ("ours_eager", False)):
-        sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3")
-                                    .with_dtype("bf16").with_cuda_graph(graphed))
-        p50, best = _p50_cuda(lambda: sess.run({"input_ids": ids, "attention_mask": mask}), iters)
-        out[name] = {"p50_ms": round(p50, 4), "sequences_per_s": round(batch / p50 * 1e3, 1)}
-    out["config"] = {"model": "distilbert-base", "batch": batch, "seq": seq, "dtype": "bf16", "tp": 1}
+    runner = EncoderRunner(graph, dtype=torch.bfloat16, comm=comm)
+    static_ids = ids.clone()
+    runner.forward(static_ids, mask)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = runner.forward(static_ids, mask)
+    p50, best = _p50_cuda(g.replay, iters)
+    if comm is not None:
+        p50 = comm.max_over_ranks(p50)
+    out["runner_cuda_graph"] = {"p50_ms": round(p50, 4), "sequences_per_s": round(batch / p50 * 1e3, 1)}
+    runner.ops.check()
+    if world == 1:
+        for name, graphed in (("session_cuda_graph", True), ("session_eager", False)):
+            sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3")
+                                        .with_dtype("bf16").with_cuda_graph(graphed))
+            p50, best = _p50_cuda(lambda: sess.run({"input_ids": ids, "attention_mask": mask}), iters)
+            out[name] = {"p50_ms": round(p50, 4), "sequences_per_s": round(batch / p50 * 1e3, 1)}
+        lib = EncoderRunner(graph, dtype=torch.bfloat16, backend="torch")
+        ref = lib.forward(ids, mask)
+        p50, best = _p50_cuda(lambda: lib.forward(ids, mask), iters)
+        out["torch_ops_eager"] = {"p50_ms": round(p50, 4)}
+        out["max_abs_err_vs_torch_ops"] = round((y.float() - ref.float()).abs().max().item(), 4)
+    out["config"] = {"model": "distilbert-base", "batch": batch, "seq": seq, "dtype": "bf16", "tp": world,
+                     "l2": "flushed between iterations"}
+    if world > 1:
+        import sys
+        if rank == 0:
+            print(json.dumps(out))
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
     return out
 
 

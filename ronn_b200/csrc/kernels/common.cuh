@@ -17,6 +17,11 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 bool pdl_enabled();          // defined in elementwise.cu; RONN_PDL=0 disables
 
+// Every kernel asks for the largest shared-memory carve-out.  The tensor-core kernels need 80-200 KB per CTA; a small
+// kernel that left its SM configured for a large L1 would keep their CTAs off that SM until it has drained, which
+// serialises kernels that run on concurrent streams.  Done once per kernel function.
+void prefer_max_shared(const void* kern);      // defined in elementwise.cu
+
 template <class... KArgs, class... Args>
 inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args... args) {
@@ -30,6 +35,7 @@ inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  prefer_max_shared(reinterpret_cast<const void*>(kern));
   return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 

@@ -65,7 +65,7 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < CONV_STAGES; ++s) {
-      mbar_init(&full[s], 128 + 1);          // 128 gather threads + the weight TMA's expect_tx arrival
+      mbar_init(&full[s], 4 + 1);            // one arrival per gather warp + the weight TMA's expect_tx arrival
       mbar_init(&empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -87,56 +87,69 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    // ---------------------------------------------------------------- A gather (one output pixel per thread)
+    // ---------------------------------------------------------------- A gather
+    // Thread t owns 16-byte chunk (t & 7) of rows (t >> 3) + 16 i, i = 0..7: the 8 lanes of a row fetch one contiguous
+    // 128-byte run of the input (a whole cache line when C % 64 == 0), so a warp instruction touches 4 lines, not 32.
+    // Barrier traffic is per warp: lane 0 waits for the slot and arrives for the warp.
     pdl_wait();
-    const int row = threadIdx.x;
-    const uint32_t sw = uint32_t(row & 7);
+    const int chunk = threadIdx.x & 7;
+    const int rbase = threadIdx.x >> 3;
     uint32_t it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-      const int m = (t / n_tiles) * 128 + row;
-      const bool row_ok = m < cs.M;
-      int n_img = 0, oh = 0, ow = 0;
-      if (row_ok) {
-        n_img = m / (cs.Ho * cs.Wo);
-        const int rem = m - n_img * cs.Ho * cs.Wo;
-        oh = rem / cs.Wo;
-        ow = rem - oh * cs.Wo;
+      int ih0[8], iw0[8], boff[8];               // per row: top-left input coordinate and image offset (elements)
+      uint32_t okmask = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int m = (t / n_tiles) * 128 + rbase + 16 * i;
+        int n_img = 0, oh = 0, ow = 0;
+        if (m < cs.M) {
+          okmask |= 1u << i;
+          n_img = m / (cs.Ho * cs.Wo);
+          const int rem = m - n_img * cs.Ho * cs.Wo;
+          oh = rem / cs.Wo;
+          ow = rem - oh * cs.Wo;
+        }
+        ih0[i] = oh * cs.stride - cs.pad;
+        iw0[i] = ow * cs.stride - cs.pad;
+        boff[i] = n_img * cs.H * cs.W * cs.C;
       }
-      const int ih0 = oh * cs.stride - cs.pad, iw0 = ow * cs.stride - cs.pad;
-      const T* img = x + size_t(n_img) * cs.H * cs.W * cs.C;
-      // filter tap and channel position of the next K chunk, advanced incrementally (no divisions in the loop);
-      // offsets inside one image fit 32 bits
-      int r = 0, sx = 0, cpos = 0;
+      // filter tap (r, sx) and channel offset of this thread's chunk in the current K block, advanced incrementally
+      int r = 0, sx = 0, cpos = chunk * 8;
+      if (!FAST) {
+        while (cpos >= cs.C) {
+          cpos -= cs.C;
+          if (++sx == cs.S) { sx = 0; ++r; }
+        }
+      }
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % CONV_STAGES;
-        if (ok && !mbar_wait(&empty[s], ((it / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+        if (lane == 0 && ok && !mbar_wait(&empty[s], ((it / CONV_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT))
+          ok = false;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok) {
-          uint8_t* dst_row = tiles + s * L::STAGE_BYTES + row * 128;
-          if (FAST) {
-            // C % 64 == 0: the whole 128-byte row of this K block is one filter tap, 64 consecutive channels
-            const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
-            const bool valid = row_ok && unsigned(ih) < unsigned(cs.H) && unsigned(iw) < unsigned(cs.W);
-            const T* src = valid ? img + (ih * cs.W + iw) * cs.C + cpos : x;
+          uint8_t* dst = tiles + s * L::STAGE_BYTES;
+          const bool tap_ok = FAST || r < cs.R;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src + j * 8, valid);
-            cpos += 64;
-            if (cpos == cs.C) {
-              cpos = 0;
+          for (int i = 0; i < 8; ++i) {
+            const int row = rbase + 16 * i;
+            const int ih = ih0[i] + r * cs.dil, iw = iw0[i] + sx * cs.dil;
+            const bool valid = tap_ok && ((okmask >> i) & 1u) && unsigned(ih) < unsigned(cs.H) &&
+                               unsigned(iw) < unsigned(cs.W);
+            const T* src = valid ? x + (boff[i] + (ih * cs.W + iw) * cs.C + cpos) : x;
+            cp_async_16(dst + row * 128 + ((uint32_t(chunk) ^ uint32_t(row & 7)) << 4), src, valid);
+          }
+          // next K block: 64 channels further along (tap-major, channel-minor) order
+          cpos += 64;
+          if (FAST) {
+            if (cpos >= cs.C) {
+              cpos -= cs.C;
               if (++sx == cs.S) { sx = 0; ++r; }
             }
           } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int ih = ih0 + r * cs.dil, iw = iw0 + sx * cs.dil;
-              const bool valid = row_ok && r < cs.R && unsigned(ih) < unsigned(cs.H) && unsigned(iw) < unsigned(cs.W);
-              const T* src = valid ? img + (ih * cs.W + iw) * cs.C + cpos : x;
-              cp_async_16(dst_row + ((uint32_t(j) ^ sw) << 4), src, valid);
-              cpos += 8;
-              if (cpos == cs.C) {
-                cpos = 0;
-                if (++sx == cs.S) { sx = 0; ++r; }
-              }
+            while (cpos >= cs.C) {
+              cpos -= cs.C;
+              if (++sx == cs.S) { sx = 0; ++r; }
             }
           }
         }
@@ -144,13 +157,16 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
         if (it >= CONV_LAG) {
           cp_async_wait<CONV_LAG>();
           fence_proxy_async_smem();
-          mbar_arrive(&full[(it - CONV_LAG) % CONV_STAGES]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full[(it - CONV_LAG) % CONV_STAGES]);
         }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async_smem();
-    for (uint32_t k = (it > CONV_LAG ? it - CONV_LAG : 0); k < it; ++k) mbar_arrive(&full[k % CONV_STAGES]);
+    __syncwarp();
+    if (lane == 0)
+      for (uint32_t k = (it > CONV_LAG ? it - CONV_LAG : 0); k < it; ++k) mbar_arrive(&full[k % CONV_STAGES]);
     pdl_trigger();
   } else if (warp == 4) {
     if (lane == 0) {

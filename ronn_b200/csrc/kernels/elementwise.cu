@@ -8,6 +8,8 @@
 // (crates/ronn-onnx/src/ops/tensor_ops.rs:463-489), argmax (crates/ronn-core/src/ops/reduction.rs:282-304).
 // All kernels move 16 bytes per thread per access and keep a row in registers between passes.
 #include <cstdlib>
+#include <mutex>
+#include <unordered_set>
 #include "common.cuh"
 
 namespace ronn {
@@ -21,6 +23,22 @@ bool pdl_enabled() {
     g_pdl = (e && e[0] == '0') ? 0 : 1;
   }
   return g_pdl != 0;
+}
+
+void prefer_max_shared(const void* kern) {
+  static std::mutex mu;
+  static std::unordered_set<const void*> seen;
+  static int enabled = -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (enabled < 0) {
+    const char* e = getenv("RONN_MAX_SHARED_CARVEOUT");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (enabled && seen.insert(kern).second) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+        cudaSuccess)
+      cudaGetLastError();                    // a preference only: never fail a launch over it
+  }
 }
 
 // y = norm(x [+ res]) * gamma [+ beta];  if sum_out != null the pre-norm sum (x + res) is also written.

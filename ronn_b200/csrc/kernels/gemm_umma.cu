@@ -96,8 +96,11 @@ static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilo
 
 int pick_bn(int M, int N) {
   const int mt = (M + PG_BM - 1) / PG_BM;
+  // 256-wide tiles pay off once the problem is compute bound; with one or two row tiles every CTA is a latency
+  // chain and narrower tiles spread the weight stream over more SMs (measured: M 256, N 50264, K 1024 takes 36 us
+  // with 128-wide tiles against 110 us with 256-wide ones)
   const int cands[4] = {256, 128, 64, 32};
-  for (int i = 0; i < 4; ++i) {
+  for (int i = (mt <= 2 ? 1 : 0); i < 4; ++i) {
     int bn = cands[i];
     if (bn > 32 && N < bn) continue;
     int ctas = mt * ((N + bn - 1) / bn);

@@ -231,6 +231,51 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     return out
 
 
+def dense_attention_plan(kv_lens, device, row_lens=None) -> dict:
+    """Per-sequence index tensors of ``dense_attention`` for sequences stored back to back in the token buffer.
+    ``kv_lens``: host list of sequence lengths; ``row_lens``: rows each sequence occupies in the buffer when that is
+    more than its length (padded batches).  Every sequence gets a 128-aligned column range of the V^T buffer."""
+    starts, vts, t, c = [], [], 0, 0
+    for i, n in enumerate(kv_lens):
+        starts.append(t)
+        vts.append(c)
+        t += int(n if row_lens is None else row_lens[i])
+        c += -(-int(n) // 128) * 128
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return {"seq_start": mk(starts), "kv_len": mk([int(n) for n in kv_lens]), "vt_start": mk(vts),
+            "vt_cols": max(c, 128), "max_len": max(int(n) for n in kv_lens), "n_seq": len(kv_lens)}
+
+
+def dense_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, plan: dict, heads: int, kv_heads: int,
+                    head_dim: int, causal: bool, q_len: Optional[torch.Tensor] = None, max_q_len: Optional[int] = None,
+                    out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
+                    vt: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Tensor-core attention over the fused qkv buffer [tokens, ld] of whole sequences (prefill without cached
+    context, encoders): V is transposed into a scratch V^T buffer, then one kernel per (128 queries, head, sequence)
+    runs S = Q K^T and O = P V on tcgen05 with an online softmax in between.  ``plan`` comes from
+    ``dense_attention_plan``; ``q_len`` defaults to the key lengths (set it to the padded row count for encoders whose
+    padded rows must still be produced).  Returns [tokens, heads * head_dim]."""
+    tokens = qkv.shape[0]
+    lib = _native.cuda()
+    if vt is None:
+        vt = torch.empty((kv_heads * head_dim, plan["vt_cols"]), dtype=qkv.dtype, device=qkv.device)
+    dt = _DT[qkv.dtype]
+    _check(lib.ronn_transpose_v(qkv.data_ptr(), qkv.stride(0), v_off, plan["seq_start"].data_ptr(),
+                                plan["kv_len"].data_ptr(), plan["vt_start"].data_ptr(), vt.data_ptr(), vt.stride(0),
+                                plan["n_seq"], kv_heads, head_dim, plan["max_len"], dt, _stream()), "transpose_v")
+    if out is None:
+        out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    ql = q_len if q_len is not None else plan["kv_len"]
+    mq = int(max_q_len if max_q_len is not None else plan["max_len"])
+    sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    _check(lib.ronn_flash_attention(qkv.data_ptr(), qkv.stride(0), tokens, q_off, k_off, vt.data_ptr(), vt.stride(0),
+                                    plan["seq_start"].data_ptr(), ql.data_ptr(), plan["kv_len"].data_ptr(),
+                                    plan["vt_start"].data_ptr(), out.data_ptr(), out.stride(0), plan["n_seq"], mq,
+                                    heads, kv_heads, head_dim, 1 if causal else 0, float(sc), dt,
+                                    status_word(qkv.device).data_ptr(), _stream()), "flash_attention")
+    return out
+
+
 _WORKSPACES = {}
 
 

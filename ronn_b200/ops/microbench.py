@@ -150,6 +150,53 @@ def sweep_gemm_depth(m=256):
     return out
 
 
+def overlap(batch=128, ctx=416, layers=24):
+    """Do an attention chain and a GEMM chain on two streams of one CUDA graph overlap?  Times each chain alone and
+    both together (same graph, two branches)."""
+    heads, d, H = 16, 64, 1024
+    nb_seq = (ctx + 15) // 16
+    nblocks = batch * nb_seq
+    kc = torch.randn(nblocks, heads, 16, d, device="cuda").bfloat16()
+    vc = torch.randn(nblocks, heads, 16, d, device="cuda").bfloat16()
+    bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
+    q = torch.randn(batch, H, device="cuda").bfloat16()
+    lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+    ao = torch.empty(batch, H, device="cuda", dtype=torch.bfloat16)
+    a = torch.randn(batch, H, device="cuda").bfloat16()
+    ws = [(torch.randn(n, k, device="cuda") * 0.05).bfloat16() for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024)]]
+    outs = [torch.empty(batch, w.shape[0], device="cuda", dtype=torch.bfloat16) for w in ws]
+
+    def attn_chain():
+        for _ in range(layers):
+            K.paged_attention(q, kc, vc, bt, lens, heads, heads, d, max_ctx=ctx, out=ao)
+
+    def gemm_chain():
+        for _ in range(layers):
+            for w, o in zip(ws, outs):
+                K.gemm(a, w, out=o)
+
+    side = torch.cuda.Stream()
+
+    def both():
+        main = torch.cuda.current_stream()
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            gemm_chain()
+        attn_chain()
+        main.wait_stream(side)
+
+    res = {"kernel": "overlap", "batch": batch, "ctx": ctx, "layers": layers}
+    for name, fn in (("attention_chain_us", attn_chain), ("gemm_chain_us", gemm_chain), ("both_us", both)):
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        res[name] = round(time_kernel(g.replay, iters=10, flush=False), 1)
+    K.check_status()
+    return res
+
+
 def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20):
     a = torch.randn(m, k, device="cuda").to(dtype)
     w = (torch.randn(n, k, device="cuda") * 0.05).to(dtype)
@@ -250,7 +297,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -279,6 +326,8 @@ def main():
         res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
     elif a.what == "sweep-decode-gemm":
         res = sweep_decode_gemm(a.m)
+    elif a.what == "overlap":
+        res = [overlap(a.batch if a.batch != 256 else 128, a.ctx)]
     elif a.what == "sweep-gemm-depth":
         res = sweep_gemm_depth(a.m)
     elif a.what == "sweep-attention":

@@ -175,6 +175,8 @@ class LLMEngine:
             else:
                 self._upload(n_tokens, n_items)
                 b = self._batch_views(n_tokens, n_items)
+                if not decode:
+                    b["dense_plan"] = self._dense_prefill_plan(n_tokens, n_items)
                 toks = self._run_and_sample(b, decode, n_tokens, n_items, sb.req_ids)
             self.sampled_host[:n_items].copy_(toks[:n_items], non_blocking=True)
             if self.device.type == "cuda":
@@ -233,6 +235,20 @@ class LLMEngine:
             if s and r.output_tokens[-len(s):] == list(s):
                 return True
         return False
+
+    def _dense_prefill_plan(self, n_tokens: int, n_items: int):
+        """Index tensors for tensor-core prefill attention when every item of the step is a whole prompt starting at
+        position 0 (no prefix-cache hit, no chunk continuation); None otherwise (the paged kernel handles those)."""
+        if self.cfg.backend != "kernels" or self.device.type != "cuda" or not self.cfg.dense_prefill:
+            return None
+        h = self.host
+        item = h.field("token_item")[:n_tokens]
+        starts = np.flatnonzero(np.diff(item, prepend=-1))
+        if len(starts) != n_items or h.field("positions")[:n_tokens][starts].any():
+            return None
+        lens = np.diff(starts, append=n_tokens)
+        from ..ops import kernels as K
+        return K.dense_attention_plan(lens.tolist(), self.device)
 
     def _run_and_sample(self, b, decode, n_tokens, n_items, req_ids) -> torch.Tensor:
         greedy = self._non_greedy == 0 or all(self.requests[int(i)].params.temperature <= 0 for i in req_ids)

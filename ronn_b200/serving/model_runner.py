@@ -220,6 +220,7 @@ class DecoderRunner:
         else:
             ctx, bt_row = b["ctx_per_token"], b["token_item"]
         hn, kn = self.n_head_local * d, self.n_kv_local * d
+        dense_plan = b.get("dense_plan") if (not decode and ops.name == "kernels" and d in (64, 128)) else None
         # the library backend gathers dense KV, so it is sized by the longest context of this step
         max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
         split_down = (ops.name == "kernels" and self.tp == 1 and x.shape[0] <= 512 and not a.bitlinear
@@ -249,8 +250,14 @@ class DecoderRunner:
             else:
                 ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
                               self.n_kv_local, d, pos, a.rope_base)
-                att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
-                                          self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
+                if dense_plan is not None:
+                    # whole prompts without cached context: causal attention on the tensor cores, straight from the
+                    # (already rotated) fused qkv buffer; the cache was filled above for the decode steps to come
+                    att = ops.dense_attention(qkv, 0, hn, hn + kn, dense_plan, self.n_head_local, self.n_kv_local, d,
+                                              True)
+                else:
+                    att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
+                                              self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
             x, h = row_parallel(att, L["out"], x, L["ln2"], False)
             if h is None:
                 h = self._norm(x, L["ln2"])

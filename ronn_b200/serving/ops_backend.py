@@ -153,6 +153,10 @@ class KernelOps:
         return self.K.paged_attention(qkv, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx,
                                       append=(k_off, v_off, slots))
 
+    def dense_attention(self, qkv, q_off, k_off, v_off, plan, heads, kv_heads, d, causal, q_len=None, max_q_len=None):
+        """Whole-sequence attention on the tensor cores, straight from the fused qkv buffer."""
+        return self.K.dense_attention(qkv, q_off, k_off, v_off, plan, heads, kv_heads, d, causal, q_len, max_q_len)
+
     def argmax(self, logits, col_offset=0, return_max=False):
         return self.K.argmax(logits, col_offset, return_max)
 

@@ -274,3 +274,51 @@ def test_rmsnorm_quant_fused():
     torch.testing.assert_close(s, sref, rtol=2e-2, atol=1e-6)
     deq = q.float() * s[:, None]
     torch.testing.assert_close(deq, normed, atol=float(sref.max()) * 1.5, rtol=0)
+
+
+def _sdpa_ref(q, k, v, causal, shift=0):
+    # q [Lq, H, d], k/v [Lk, Hkv, d] fp32
+    H, Hkv = q.shape[1], k.shape[1]
+    k = k.repeat_interleave(H // Hkv, dim=1)
+    v = v.repeat_interleave(H // Hkv, dim=1)
+    s = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(q.shape[-1])
+    if causal:
+        Lq, Lk = q.shape[0], k.shape[0]
+        mask = torch.arange(Lk, device=q.device)[None, :] > (torch.arange(Lq, device=q.device)[:, None] + shift)
+        s = s.masked_fill(mask[None], float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(s, dim=-1), v)
+
+
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (64, 8, 2), (128, 4, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_dense_attention_ragged_causal(K, d, heads, kv_heads, dtype):
+    lens = [1, 5, 128, 129, 300, 64, 517]
+    T = sum(lens)
+    hn, kn = heads * d, kv_heads * d
+    qkv = _rand(T, hn + 2 * kn, dtype=dtype)
+    plan = K.dense_attention_plan(lens, "cuda")
+    out = K.dense_attention(qkv, 0, hn, hn + kn, plan, heads, kv_heads, d, causal=True)
+    K.check_status()
+    t = 0
+    for n in lens:
+        rows = qkv[t:t + n].float()
+        ref = _sdpa_ref(rows[:, :hn].view(n, heads, d), rows[:, hn:hn + kn].view(n, kv_heads, d),
+                        rows[:, hn + kn:].view(n, kv_heads, d), True)
+        torch.testing.assert_close(out[t:t + n].float().view(n, heads, d), ref, atol=2e-2, rtol=2e-2)
+        t += n
+
+
+def test_dense_attention_padded_encoder(K):
+    B, S, heads, d = 6, 128, 12, 64
+    lens = [128, 100, 1, 37, 128, 64]
+    hn = heads * d
+    qkv = _rand(B * S, 3 * hn)
+    plan = K.dense_attention_plan(lens, "cuda", row_lens=[S] * B)
+    q_len = torch.full((B,), S, dtype=torch.int32, device="cuda")
+    out = K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, d, causal=False, q_len=q_len, max_q_len=S)
+    K.check_status()
+    for b, n in enumerate(lens):
+        rows = qkv[b * S:(b + 1) * S].float()
+        ref = _sdpa_ref(rows[:, :hn].view(S, heads, d), rows[:n, hn:2 * hn].view(n, heads, d),
+                        rows[:n, 2 * hn:].view(n, heads, d), False)
+        torch.testing.assert_close(out[b * S:(b + 1) * S].float().view(S, heads, d), ref, atol=2e-2, rtol=2e-2)

@@ -73,3 +73,17 @@ def test_bitnet_engine_gpu_kernels_vs_torch_backend():
         outs[backend] = eng.generate(prompts, SamplingParams(max_new_tokens=6))
     agree = sum(a == b for x, y in zip(outs["kernels"], outs["torch"]) for a, b in zip(x, y))
     assert agree >= 14, outs
+
+
+def test_encoder_runner_kernels_match_operator_backend():
+    from ronn_b200.models.distilbert import DistilBertConfig, build_distilbert
+    from ronn_b200.serving.encoder_runner import EncoderRunner
+    graph = build_distilbert(DistilBertConfig.tiny(n_layers=2, dim=256, n_heads=4, hidden_dim=512), dtype=torch.bfloat16, seed=4)
+    ids = torch.randint(0, 512, (5, 48), device="cuda")
+    mask = torch.ones(5, 48, dtype=torch.int64, device="cuda")
+    mask[1, 30:] = 0
+    mask[3, 5:] = 0
+    got = EncoderRunner(graph, dtype=torch.bfloat16).forward(ids, mask)
+    want = EncoderRunner(graph, dtype=torch.bfloat16, backend="torch").forward(ids, mask)
+    for b, n in enumerate(mask.sum(1).tolist()):
+        torch.testing.assert_close(got[b, :n].float(), want[b, :n].float(), atol=6e-2, rtol=5e-2)
