@@ -3,6 +3,7 @@
     python -m ronn_b200.bench_models resnet18  [--batch 32] [--iters 50]     p50 latency, fp16, O3, GPU provider
     python -m ronn_b200.bench_models mlp784    [--iters 2000]                p50 latency, f32, CPU provider
     python -m ronn_b200.bench_models distilbert [--batch 64 --seq 128]       p50 latency / sequences per second, bf16
+    python -m ronn_b200.bench_models bitnet [--batch 128]                    BitNet 2B-style decode tokens/s (TP under torchrun)
 
 Each benchmark also times a plain PyTorch library implementation of the same network on the same box
 (cuDNN / cuBLAS / SDPA) as the comparison baseline.  Timing: CUDA events around ``session.run`` with the input
@@ -211,9 +212,70 @@ def bench_distilbert(batch=64, seq=128, iters=20):
     return out
 
 
+def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24):
+    """BitNet b1.58 2B-style decoder (24 layers, hidden 2560, 20 heads, FFN 6912, vocab 32000; random ternary weights
+    packed 2-bit, int8 activations), decode tokens/s at a fixed batch through the serving engine (paged KV,
+    CUDA-graph decode).  Under ``torchrun`` the model is tensor parallel over all ranks; the time is the maximum over
+    ranks, measured with CUDA events around whole engine steps."""
+    import os
+    import sys
+    import numpy as np
+    from . import Model
+    from .models.bitnet_llama import BitNetConfig, build_bitnet_llama
+    from .serving import EngineConfig, LLMEngine, SamplingParams
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    comm, rank, local = None, 0, 0
+    if world > 1:
+        from .parallel.fused import make_comm
+        from .parallel.group import init_distributed
+        rank, world, local = init_distributed()
+        torch.cuda.set_device(local)
+        comm = make_comm(os.environ.get("RONN_TP_COMM", "fused"), torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    cfg = BitNetConfig(n_layer=layers)
+    model = Model.from_graph(build_bitnet_llama(cfg, dtype=torch.bfloat16, seed=0, with_lm_head=False))
+    new_tokens = steps + warmup + 4
+    ecfg = EngineConfig(max_num_seqs=batch, max_batch_tokens=8192, max_model_len=1024, dtype="bf16", backend="kernels",
+                        use_cuda_graph=True, tp_size=world, tp_comm=os.environ.get("RONN_TP_COMM", "fused"),
+                        num_blocks=batch * 16)
+    eng = LLMEngine(model, ecfg, device=dev, comm=comm)
+    rng = np.random.default_rng(7)
+    for _ in range(batch):
+        eng.add_request(rng.integers(0, cfg.vocab_size, size=prompt).tolist(), SamplingParams(max_new_tokens=new_tokens))
+    while eng.sched.num_waiting > 0:
+        eng.step()
+    for _ in range(max(warmup, 3)):
+        eng.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        torch.distributed.barrier()
+    e0.record()
+    for _ in range(steps):
+        out = eng.step()
+        assert len(out) == batch
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if comm is not None:
+        ms = comm.max_over_ranks(ms)
+    res = {"decode_tokens_per_s": round(batch * steps / ms * 1e3, 1), "ms_per_step": round(ms / steps, 4),
+           "config": {"model": "bitnet-b1.58-2b-style" if layers == 24 else f"bitnet-{layers}L", "batch": batch,
+                      "prompt": prompt, "steps": steps, "dtype": "ternary 2-bit x int8 (bf16 elsewhere)", "tp": world,
+                      "l2": "KV + packed weights per step exceed L2"}}
+    if world > 1:
+        if rank == 0:
+            print(json.dumps(res))
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        os._exit(0)
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["resnet18", "mlp784", "distilbert"])
+    ap.add_argument("what", choices=["resnet18", "mlp784", "distilbert", "bitnet"])
+    ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--seq", type=int, default=128)
     ap.add_argument("--iters", type=int, default=0)
@@ -222,6 +284,8 @@ def main():
         res = bench_resnet18(a.batch or 32, a.iters or 50)
     elif a.what == "mlp784":
         res = bench_mlp784(a.iters or 2000)
+    elif a.what == "bitnet":
+        res = bench_bitnet(a.batch or 128, a.iters or 32, layers=a.layers)
     else:
         res = bench_distilbert(a.batch or 64, a.seq, a.iters or 20)
     print(json.dumps(res))

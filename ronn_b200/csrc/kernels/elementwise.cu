@@ -161,6 +161,10 @@ __global__ void splitk_finalize_kernel(const float* __restrict__ ws, int S, cons
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[c][i] += r[i];
       }
+      if (act == 3) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[c][i] = fmaxf(v[c][i], 0.f);
+      }
       if (sum_out) {
         const Vec8 pk = pack8<T>(v[c]);
         *reinterpret_cast<Vec8*>(sum_out + row * N + ch * 8) = pk;
@@ -508,7 +512,8 @@ extern "C" int ronn_cast(const void* x, void* y, long n, int from, int to, cudaS
   return -1;
 }
 
-// norm: 0 none (sum_out only), 1 LayerNorm, 2 RMSNorm.  act: 0 none, 1 relu, 2 gelu (applied before the residual).
+// norm: 0 none (sum_out only), 1 LayerNorm, 2 RMSNorm.  act: 0 none, 1 relu, 2 gelu (applied before the residual),
+// 3 relu applied after the residual.
 extern "C" int ronn_splitk_finalize(const float* ws, int S, const void* bias, const void* residual, void* sum_out,
                                     const void* gamma, const void* beta, void* y, long rows, int N, float eps,
                                     int act, int norm, int dtype, cudaStream_t stream) {

@@ -154,9 +154,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
       int m0, n0, kb0, nkb;
       prob.tile(t, m0, n0, kb0, nkb);
       const uint32_t buf = j & 1;
-      bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      if (!mbar_wait_warp_relaxed(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM)) break;
       tc_fence_after_sync();
       const int row = q * 32 + lane;
 #pragma unroll 1

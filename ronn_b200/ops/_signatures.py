@@ -34,7 +34,8 @@ def declare(lib):
     sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V])
     sig("ronn_transpose_v", [V, L, I, V, V, V, V, L, I, I, I, I, I, V])
     sig("ronn_flash_attention", [V, L, L, I, I, V, L, V, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
-    sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, V], optional=True)
+    sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, L, V, V], optional=True)
+    sig("ronn_nchw_to_nhwc8", [V, V, I, I, I, I, I, V], optional=True)
     sig("ronn_maxpool_nhwc", [V, V, I, I, I, I, I, I, I, I, I, I, V], optional=True)
     sig("ronn_global_avgpool_nhwc", [V, V, I, I, I, I, V], optional=True)
     sig("ronn_act_quant_int8", [V, V, V, L, I, I, V], optional=True)

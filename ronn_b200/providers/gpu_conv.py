@@ -30,9 +30,11 @@ def conv2d_nhwc(x, w, bias=None, residual=None, stride=1, pad=0, dil=1, relu=Fal
         out = torch.empty((N, Ho, Wo, Cout), dtype=x.dtype, device=x.device)
     if residual is not None:
         residual = residual.contiguous()
+    ws = K.splitk_workspace(x.device, 1 << 22)      # fp32 scratch for the split-K form of the deep layers
     rc = _native.cuda().ronn_conv2d(x.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
                                     None if residual is None else residual.data_ptr(), out.data_ptr(), N, H, W, C, Cout,
                                     R, S, stride, pad, dil, Ho, Wo, 1 if relu else 0, 0 if x.dtype == torch.bfloat16 else 1,
+                                    ws.data_ptr(), ws.numel(),
                                     K.status_word(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
     if rc != 0:
         raise K.KernelError(f"conv2d failed with code {rc}")
@@ -82,8 +84,20 @@ def conv_resolver(table, node: GraphNode, fallback):
             padc = 8 - C % 8
             if "w" not in cache:
                 cache["w"] = F.pad(w, (0, padc)).contiguous()
-            x = F.pad(x, (0, padc))
             w = cache["w"]
+            nchw = x.permute(0, 3, 1, 2)
+            if C < 8 and nchw.is_contiguous():
+                # an NHWC view of NCHW memory (the graph input after the layout pass): convert and pad in one kernel
+                n_, h_, w_ = x.shape[0], x.shape[1], x.shape[2]
+                xp = torch.empty((n_, h_, w_, 8), dtype=x.dtype, device=x.device)
+                rc = _native.cuda().ronn_nchw_to_nhwc8(nchw.data_ptr(), xp.data_ptr(), n_, C, h_, w_,
+                                                       0 if x.dtype == torch.bfloat16 else 1,
+                                                       torch.cuda.current_stream().cuda_stream)
+                if rc != 0:
+                    raise K.KernelError(f"nchw_to_nhwc8 failed with code {rc}")
+                x = xp
+            else:
+                x = F.pad(x, (0, padc))
         bias = i[2] if len(i) > 2 else None
         res = i[3] if len(i) > 3 else None
         return [conv2d_nhwc(x, w, bias, res, strides[0], pads[0], dil[0], relu)]

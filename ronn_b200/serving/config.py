@@ -25,7 +25,7 @@ class EngineConfig:
     tp_comm: str = "fused"              # "fused" (in-kernel NVLink) | "nccl" (library collectives baseline)
     gpu_memory_utilization: float = 0.85
     dense_prefill: bool = True          # whole-prompt prefill steps use the tensor-core attention kernel
-    decode_streams: int = 2             # decode batches >= decode_split_min rows run as this many concurrent halves
+    decode_streams: int = 1             # >1: decode batches >= 2*decode_split_min rows run as this many concurrent parts
     decode_split_min: int = 64          # (one stream each, inside the step's CUDA graph): the bandwidth-bound
                                         # attention of one overlaps the latency-bound GEMM chain of the others
 

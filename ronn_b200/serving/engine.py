@@ -331,15 +331,25 @@ class LLMEngine:
         return parts
 
     def _forward_parts(self, subs) -> torch.Tensor:
+        """Part-batches on their own streams, each started half a layer after the previous one: part i + 1 waits for
+        the first attention of part i.  Started together, the parts would run their attention kernels at the same
+        time (sharing the HBM bandwidth) and then their GEMM chains at the same time (each as slow as the whole
+        batch's), which gains nothing; half a layer apart, the attention of one runs under the GEMM chain of the other
+        and the offset persists because both chains have the same period."""
         main = torch.cuda.current_stream()
         tp = self.runner.tp > 1
         res = []
+        prev = None
         for i, (b, n) in enumerate(subs):
             st = self._part_streams[i]
             st.wait_stream(main)
             with torch.cuda.stream(st):
+                if prev is not None:
+                    st.wait_event(prev)
+                evt = torch.cuda.Event()
                 res.append(self.runner.forward(b, True, n, n, comm=self._part_comms[i] if tp else None,
-                                               local_argmax=tp))
+                                               local_argmax=tp, on_first_attention=lambda e=evt, s=st: e.record(s)))
+                prev = evt
         for i in range(len(subs)):
             main.wait_stream(self._part_streams[i])
         if tp:

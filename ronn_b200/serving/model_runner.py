@@ -203,11 +203,12 @@ class DecoderRunner:
         return self.ops.rmsnorm(x, p[0], self.arch.eps)
 
     def forward(self, b: Dict[str, torch.Tensor], decode: bool, n_tokens: int, n_items: int,
-                want_logits: bool = False, comm=None, local_argmax: bool = False):
+                want_logits: bool = False, comm=None, local_argmax: bool = False, on_first_attention=None):
         """Runs one step over device-side batch tensors (already sliced to n_tokens / n_items) and returns the
         greedy token of every item as int32 [n_items] (or, with ``want_logits`` and TP=1, the fp32 logits).
         ``comm`` replaces the runner's communicator (concurrent part-batches each need their own); with
-        ``local_argmax`` a tensor-parallel rank returns its (index, max) pair and the caller combines the ranks."""
+        ``local_argmax`` a tensor-parallel rank returns its (index, max) pair and the caller combines the ranks.
+        ``on_first_attention()`` is called right after the first layer's attention has been enqueued."""
         a, ops, d = self.arch, self.ops, self.arch.head_dim
         comm = comm or self.comm
         ids, pos, slots = b["token_ids"], b["positions"], b["slot_mapping"]
@@ -258,6 +259,8 @@ class DecoderRunner:
                 else:
                     att = ops.paged_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"], ctx,
                                               self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
+            if li == 0 and on_first_attention is not None:
+                on_first_attention()
             x, h = row_parallel(att, L["out"], x, L["ln2"], False)
             if h is None:
                 h = self._norm(x, L["ln2"])
