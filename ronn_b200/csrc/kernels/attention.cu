@@ -78,6 +78,7 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcach
   __shared__ float oacc[NW][D];
 
   pdl_wait();
+  pdl_trigger();                 // the successor (a GEMM) may launch now: its set-up and weight prefetch run under this kernel
   const int row = blockIdx.x, head = blockIdx.y;
   const int L = min(ctx_len[row], ATTN_MAX_CTX);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

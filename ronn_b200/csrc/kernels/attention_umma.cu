@@ -113,6 +113,7 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
   if (warp == 0) {
     if (lane == 0) {
       pdl_wait();
+      pdl_trigger();
       mbar_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
       for (int at = 0; at < L::ATOMS; ++at)

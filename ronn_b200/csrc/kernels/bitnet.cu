@@ -214,6 +214,7 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
   } else if (warp == 4) {
     if (lane == 0) {
       pdl_wait();                            // activations come from the previous kernel
+      pdl_trigger();                         // successor may launch and set up under this kernel
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % BL_STAGES;
         if (!mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) break;

@@ -114,6 +114,7 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
     // 128-byte run of the input (a whole cache line when C % 64 == 0), so a warp instruction touches 4 lines, not 32.
     // Barrier traffic is per warp: lane 0 waits for the slot and arrives for the warp.
     pdl_wait();
+    pdl_trigger();                               // successor may launch and set up under this kernel
     const int chunk = threadIdx.x & 7;
     const int rbase = threadIdx.x >> 3;
     uint32_t it = 0;
@@ -380,6 +381,34 @@ __global__ void nchw_to_nhwc8_kernel(const T* __restrict__ x, T* __restrict__ y,
   }
 }
 
+// NCHW [N, C, H, W] (C <= 4, H and W even) -> 2x2 space-to-depth NHWC [N, H/2, W/2, 16]: channel (dy * 2 + dx) * C + c
+// holds x[n, c, 2 y + dy, 2 x + dx], the rest is zero.  A 7x7 stride-2 convolution over x becomes a 4x4 stride-1
+// convolution over this tensor whose K rows are whole 128-byte runs (4 taps x 16 channels).  One output pixel per thread.
+template <class T>
+__global__ void nchw_to_s2d16_kernel(const T* __restrict__ x, T* __restrict__ y, int C, int H, int W, long total) {
+  pdl_wait();
+  pdl_trigger();
+  const int H2 = H >> 1, W2 = W >> 1;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+    const int xo = int(i % W2);
+    const long t = i / W2;
+    const int yo = int(t % H2);
+    const long n = t / H2;
+    alignas(16) T v[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = Cvt<T>::from_f(0.f);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int dy = q >> 1, dx = q & 1;
+      for (int c = 0; c < C; ++c)
+        v[q * C + c] = x[((n * C + c) * H + (2 * yo + dy)) * long(W) + 2 * xo + dx];
+    }
+    Vec8* dst = reinterpret_cast<Vec8*>(y + i * 16);
+    dst[0] = *reinterpret_cast<const Vec8*>(v);
+    dst[1] = *reinterpret_cast<const Vec8*>(v + 8);
+  }
+}
+
 // y[n, c] = mean over HW of x[n, :, :, c]; one CTA per (n, 64-channel slab), threads split HW.
 template <class T>
 __global__ void global_avgpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int HW, int C) {
@@ -492,6 +521,16 @@ extern "C" int ronn_nchw_to_nhwc8(const void* x, void* y, int N, int C, int H, i
   cudaError_t err;
   if (dtype == 0) err = launch(nchw_to_nhwc8_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, C, HW, total);
   else err = launch(nchw_to_nhwc8_kernel<__half>, dim3(grid), dim3(256), 0, stream, (const __half*)x, (__half*)y, C, HW, total);
+  return err == cudaSuccess ? 0 : -100;
+}
+
+extern "C" int ronn_nchw_to_s2d16(const void* x, void* y, int N, int C, int H, int W, int dtype, cudaStream_t stream) {
+  if (C < 1 || C > 4 || N <= 0 || (H & 1) || (W & 1)) return -2;
+  const long total = long(N) * (H / 2) * (W / 2);
+  const int grid = int((total + 255) / 256 > 148 * 64 ? 148 * 64 : (total + 255) / 256);
+  cudaError_t err;
+  if (dtype == 0) err = launch(nchw_to_s2d16_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, C, H, W, total);
+  else err = launch(nchw_to_s2d16_kernel<__half>, dim3(grid), dim3(256), 0, stream, (const __half*)x, (__half*)y, C, H, W, total);
   return err == cudaSuccess ? 0 : -100;
 }
 

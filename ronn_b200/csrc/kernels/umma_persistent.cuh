@@ -94,6 +94,8 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
         }
       }
       pdl_wait();
+      pdl_trigger();                             // the predecessor is complete: let the successor launch and run its
+                                                 // set-up (barriers, TMEM, weight prefetch) under this kernel
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
@@ -154,7 +156,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
       int m0, n0, kb0, nkb;
       prob.tile(t, m0, n0, kb0, nkb);
       const uint32_t buf = j & 1;
-      if (!mbar_wait_warp_relaxed(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM)) break;
+      if (!mbar_wait_warp_relaxed(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM, 20)) break;
       tc_fence_after_sync();
       const int row = q * 32 + lane;
 #pragma unroll 1

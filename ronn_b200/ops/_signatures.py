@@ -36,6 +36,7 @@ def declare(lib):
     sig("ronn_flash_attention", [V, L, L, I, I, V, L, V, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
     sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, L, V, V], optional=True)
     sig("ronn_nchw_to_nhwc8", [V, V, I, I, I, I, I, V], optional=True)
+    sig("ronn_nchw_to_s2d16", [V, V, I, I, I, I, I, V], optional=True)
     sig("ronn_maxpool_nhwc", [V, V, I, I, I, I, I, I, I, I, I, I, V], optional=True)
     sig("ronn_global_avgpool_nhwc", [V, V, I, I, I, I, V], optional=True)
     sig("ronn_act_quant_int8", [V, V, V, L, I, I, V], optional=True)

@@ -223,3 +223,28 @@ def test_failed_step_requeues_requests(tiny):
     while eng.has_unfinished():
         eng.step()
     assert list(eng.requests.values())[0].output_tokens == reference_greedy(tiny, [1, 2, 3, 4], 4)
+
+
+def test_dense_attention_plan_layout():
+    from ronn_b200.ops.kernels import dense_attention_plan
+    p = dense_attention_plan([1, 5, 128, 129], "cpu")
+    assert p["seq_start"].tolist() == [0, 1, 6, 134]
+    assert p["vt_start"].tolist() == [0, 128, 256, 384]          # every sequence starts on a 128-column boundary
+    assert p["vt_cols"] == 640 and p["max_len"] == 129 and p["n_seq"] == 4
+    q = dense_attention_plan([100, 7], "cpu", row_lens=[128, 128])   # padded batch: rows advance by the padded length
+    assert q["seq_start"].tolist() == [0, 128] and q["kv_len"].tolist() == [100, 7]
+
+
+def test_part_batch_split_is_off_on_cpu_and_for_small_batches():
+    eng = _tiny_engine() if "_tiny_engine" in globals() else None
+    if eng is None:
+        import torch
+        from ronn_b200.api.model import Model
+        from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+        from ronn_b200.serving import EngineConfig, LLMEngine
+        cfg = GPT2Config.tiny(n_layer=1, n_embd=64, n_head=2, vocab_size=128, n_positions=64)
+        eng = LLMEngine(Model.from_graph(build_gpt2(cfg, dtype=torch.float32, seed=0)),
+                        EngineConfig(max_num_seqs=8, max_batch_tokens=64, max_model_len=64, num_blocks=32, dtype="fp32",
+                                     backend="torch", decode_streams=4), device="cpu")
+    assert eng._split_rows(256) is None          # operator backend: one batch
+    assert eng._dense_prefill_plan(4, 1) is None
