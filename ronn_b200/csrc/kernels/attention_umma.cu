@@ -293,8 +293,11 @@ template <class T, int D>
 __global__ void __launch_bounds__(256)
 transpose_v_kernel(const T* __restrict__ qkv, long ld, int v_off, const int* __restrict__ seq_start,
                    const int* __restrict__ kv_len, const int* __restrict__ vt_start, T* __restrict__ vt, long ld_vt) {
-  __shared__ T tile[128][D + 8];
+  // rows of D + 2 elements (an odd number of 32-bit words): a column read by consecutive key groups lands in
+  // different banks, and the 4-byte stores of the first phase stay aligned
+  __shared__ __align__(16) T tile[128][D + 2];
   pdl_wait();
+  pdl_trigger();
   const int seq = blockIdx.z, kvh = blockIdx.y, kt = blockIdx.x;
   const int len = kv_len[seq];
   if (kt * 128 >= len) return;
@@ -304,18 +307,21 @@ transpose_v_kernel(const T* __restrict__ qkv, long ld, int v_off, const int* __r
     const int t = i / CPR, c = i % CPR;
     Vec8 v = {};
     if (kt * 128 + t < len) v = *reinterpret_cast<const Vec8*>(qkv + long(row0 + t) * ld + v_off + kvh * D + c * 8);
-    *reinterpret_cast<Vec8*>(&tile[t][c * 8]) = v;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(&tile[t][c * 8]);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) dst[k] = src[k];
   }
   __syncthreads();
   const long col0 = long(vt_start[seq]) + kt * 128;
-  for (int i = threadIdx.x; i < D * 16; i += blockDim.x) {    // 16 chunks of 8 keys per output row
-    const int d = i / 16, c = i % 16;
+  // 8 consecutive lanes write 8 consecutive 16-byte chunks (8 keys each) of one V^T row: 128 contiguous bytes
+  for (int i = threadIdx.x; i < D * 16; i += blockDim.x) {
+    const int c = (i & 7) + 8 * (i / (8 * D)), d = (i >> 3) % D;
     alignas(16) T tmp[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) tmp[k] = tile[c * 8 + k][d];
     *reinterpret_cast<Vec8*>(vt + long(kvh * D + d) * ld_vt + col0 + c * 8) = *reinterpret_cast<const Vec8*>(tmp);
   }
-  pdl_trigger();
 }
 
 template <class T, int D>

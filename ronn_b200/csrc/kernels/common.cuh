@@ -17,9 +17,11 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 bool pdl_enabled();          // defined in elementwise.cu; RONN_PDL=0 disables
 
-// Every kernel asks for the largest shared-memory carve-out.  The tensor-core kernels need 80-200 KB per CTA; a small
-// kernel that left its SM configured for a large L1 would keep their CTAs off that SM until it has drained, which
-// serialises kernels that run on concurrent streams.  Done once per kernel function.
+// With RONN_MAX_SHARED_CARVEOUT=1 every kernel asks for the largest shared-memory carve-out.  The tensor-core kernels
+// need 80-200 KB per CTA; a small kernel that left its SM configured for a large L1 keeps their CTAs off that SM until
+// it has drained, which serialises kernels that run on concurrent streams (measured: 9 % on an attention chain run
+// beside a GEMM chain).  Off by default: on a single stream the attention kernel is 1-2 % faster with the larger L1.
+// Done once per kernel function.
 void prefer_max_shared(const void* kern);      // defined in elementwise.cu
 
 template <class... KArgs, class... Args>

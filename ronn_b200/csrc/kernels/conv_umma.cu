@@ -251,17 +251,34 @@ conv_igemm_kernel(const T* __restrict__ x, const __grid_constant__ CUtensorMap m
       epi.n0 = tl.nt * BN;
       if (cs.splitk > 1) epi.C = reinterpret_cast<float*>(c_base) + size_t(tl.ks) * cs.M * cs.Cout;
       const int row = q * 32 + lane;
-#pragma unroll 1
-      for (int col = 0; col < BN; col += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + buf * BN + uint32_t(col), r);
+      const uint32_t tacc = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+      // the TMEM load of the next 32 columns is in flight while this chunk is converted and stored
+      if (BN == 32) {
+        uint32_t r0[32];
+        tmem_ld_32x32(tacc, r0);
         tmem_ld_wait();
-        if (col + 32 >= BN) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        epi.run<T>(row, 0, r0);
+      } else {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(tacc, r0);
+#pragma unroll 1
+        for (int col = 0; col < BN; col += 64) {
+          tmem_ld_wait();
+          tmem_ld_32x32(tacc + uint32_t(col + 32), r1);
+          epi.run<T>(row, col, r0);
+          tmem_ld_wait();
+          if (col + 64 < BN) {
+            tmem_ld_32x32(tacc + uint32_t(col + 64), r0);
+          } else {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          epi.run<T>(row, col + 32, r1);
         }
-        epi.run<T>(row, col, r);
       }
     }
     pdl_trigger();

@@ -32,7 +32,7 @@ void prefer_max_shared(const void* kern) {
   std::lock_guard<std::mutex> lock(mu);
   if (enabled < 0) {
     const char* e = getenv("RONN_MAX_SHARED_CARVEOUT");
-    enabled = (e && e[0] == '0') ? 0 : 1;
+    enabled = (e && e[0] == '1') ? 1 : 0;
   }
   if (enabled && seen.insert(kern).second) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=

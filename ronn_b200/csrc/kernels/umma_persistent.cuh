@@ -156,20 +156,41 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
       int m0, n0, kb0, nkb;
       prob.tile(t, m0, n0, kb0, nkb);
       const uint32_t buf = j & 1;
-      if (!mbar_wait_warp_relaxed(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM, 20)) break;
+      // the accumulator hand-over is on the critical path of a skinny GEMM (one tile per CTA): every lane polls
+      bool ok = mbar_wait(&acc_full[buf], (j >> 1) & 1, abort, status, STATUS_WAIT_ACCUM);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after_sync();
       const int row = q * 32 + lane;
-#pragma unroll 1
-      for (int col = 0; col < BN; col += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(q * 32) << 16) + buf * BN + uint32_t(col), r);
+      const uint32_t tacc = tmem_base + (uint32_t(q * 32) << 16) + buf * BN;
+      // TMEM loads are long-latency: the load of the next 32 columns is in flight while this chunk is converted and
+      // stored.  The accumulator buffer is handed back as soon as its last load has landed.
+      if (BN == 32) {
+        uint32_t r0[32];
+        tmem_ld_32x32(tacc, r0);
         tmem_ld_wait();
-        if (col + 32 >= BN) {                    // accumulator fully read: hand the buffer back before the stores
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        prob.epilogue(t, m0, n0, row, 0, r0);
+      } else {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(tacc, r0);
+#pragma unroll 1
+        for (int col = 0; col < BN; col += 64) {
+          tmem_ld_wait();                                    // r0 = columns [col, col + 32)
+          tmem_ld_32x32(tacc + uint32_t(col + 32), r1);
+          prob.epilogue(t, m0, n0, row, col, r0);
+          tmem_ld_wait();                                    // r1 = columns [col + 32, col + 64)
+          if (col + 64 < BN) {
+            tmem_ld_32x32(tacc + uint32_t(col + 64), r0);
+          } else {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          prob.epilogue(t, m0, n0, row, col + 32, r1);
         }
-        prob.epilogue(t, m0, n0, row, col, r);
       }
     }
     pdl_trigger();

@@ -231,6 +231,32 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     return out
 
 
+def gemm_rownorm_ok(n: int, k: int) -> bool:
+    """Shapes the cluster GEMM + row-norm kernel takes: a row of at most 8 tiles of 128 columns."""
+    return n % 128 == 0 and 128 <= n <= 1024 and k % 8 == 0
+
+
+def gemm_rownorm(a: torch.Tensor, w_nk: torch.Tensor, bias, residual, gamma, beta=None, eps: float = 1e-5,
+                 norm: str = "layernorm"):
+    """x = a @ w_nk^T + bias + residual and y = LayerNorm / RMSNorm(x) in ONE kernel: the CTAs that share a row block
+    form a thread-block cluster and exchange the row statistics over distributed shared memory.  Returns (x, y)."""
+    M, Kd = a.shape
+    N = w_nk.shape[0]
+    if not gemm_rownorm_ok(N, Kd):
+        raise KernelError(f"gemm_rownorm needs N a multiple of 128 up to 1024 (got N={N}, K={Kd})")
+    x = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    y = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    if residual is not None and residual.stride(1) != 1:
+        residual = residual.contiguous()
+    rc = _native.cuda().ronn_gemm_rownorm(a.data_ptr(), w_nk.data_ptr(), x.data_ptr(), y.data_ptr(), _ptr(bias),
+                                          _ptr(residual), gamma.data_ptr(), _ptr(beta), M, N, Kd, a.stride(0),
+                                          w_nk.stride(0), residual.stride(0) if residual is not None else 0, float(eps),
+                                          {"layernorm": 1, "rmsnorm": 2}[norm], _DT[a.dtype],
+                                          status_word(a.device).data_ptr(), _stream())
+    _check(rc, "gemm_rownorm")
+    return x, y
+
+
 def dense_attention_plan(kv_lens, device, row_lens=None) -> dict:
     """Per-sequence index tensors of ``dense_attention`` for sequences stored back to back in the token buffer.
     ``kv_lens``: host list of sequence lengths; ``row_lens``: rows each sequence occupies in the buffer when that is

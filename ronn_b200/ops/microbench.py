@@ -197,6 +197,60 @@ def overlap(batch=128, ctx=416, layers=24):
     return res
 
 
+def bench_dense_attention(batch=64, seq=128, heads=12, dim=64, causal=False, iters=20, flush=True):
+    """Tensor-core attention over a fused qkv buffer of `batch` sequences of `seq` tokens (V transpose + attention)."""
+    hn = heads * dim
+    qkv = torch.randn(batch * seq, 3 * hn, device="cuda").bfloat16()
+    plan = K.dense_attention_plan([seq] * batch, "cuda")
+    out = torch.empty(batch * seq, hn, device="cuda", dtype=torch.bfloat16)
+    vt = torch.empty(hn, plan["vt_cols"], device="cuda", dtype=torch.bfloat16)
+    us = time_kernel(lambda: K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, dim, causal, out=out, vt=vt),
+                     iters=iters, flush=flush)
+    K.check_status()
+    hbm, tf, src = _peaks()
+    flops = 4.0 * batch * heads * seq * seq * dim * (0.5 if causal else 1.0)
+    byts = 2.0 * (qkv.numel() + out.numel())
+    roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e6
+    return {"kernel": "dense_attention(+transpose_v)", "batch": batch, "seq": seq, "heads": heads, "dim": dim,
+            "causal": causal, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "roofline_us": round(roof, 2),
+            "frac_of_" + src: round(roof / us, 3)}
+
+
+def bench_fused_single_rank(m=256, n=1024, k=1024, iters=20, flush=True):
+    """The fused GEMM + reduction (+ LayerNorm) kernel run as a world of one rank on plain device buffers: the same
+    code path as the tensor-parallel call (partials published, flags raised and awaited, rows reduced and normalised)
+    without a peer, for profiling on a single GPU."""
+    import ctypes as C
+    from .. import _native
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    bias, gamma, beta = (torch.randn(n, device="cuda").bfloat16() for _ in range(3))
+    res = torch.randn(m, n, device="cuda").bfloat16()
+    stride = m * n * 2
+    part = torch.zeros(2 * stride, dtype=torch.uint8, device="cuda")
+    flags = torch.zeros(16, dtype=torch.int32, device="cuda")
+    state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out, normed = torch.empty_like(res), torch.empty_like(res)
+    pp = (C.c_void_p * 8)(*[part.data_ptr()] + [None] * 7)
+    fp = (C.c_void_p * 8)(*[flags.data_ptr()] + [None] * 7)
+    lib = _native.cuda()
+
+    def call():
+        rc = lib.ronn_gemm_reduce(a.data_ptr(), w.data_ptr(), m, n, k, k, k, pp, fp, stride, state.data_ptr(), 0, 1, 0, m,
+                                  out.data_ptr(), n, bias.data_ptr(), res.data_ptr(), n, 2.0, 0, 0, normed.data_ptr(),
+                                  gamma.data_ptr(), beta.data_ptr(), 1e-5, 1, K.status_word("cuda").data_ptr(),
+                                  torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, rc
+    us = time_kernel(call, iters=iters, flush=flush)
+    K.check_status()
+    ref = a.float() @ w.float().t()
+    ref = ref.bfloat16().float() + bias.float() + res.float()
+    err = (out.float() - ref).abs().max().item()
+    us_plain = time_kernel(lambda: K.layernorm(K.gemm(a, w, bias, res), gamma, beta, 1e-5), iters=iters, flush=flush)
+    return {"kernel": "gemm_reduce(world=1)+layernorm", "m": m, "n": n, "k": k, "us": round(us, 2),
+            "gemm_then_layernorm_us": round(us_plain, 2), "max_abs_err": round(err, 4)}
+
+
 def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20):
     a = torch.randn(m, k, device="cuda").to(dtype)
     w = (torch.randn(n, k, device="cuda") * 0.05).to(dtype)
@@ -297,7 +351,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "fused-single-rank", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -308,6 +362,7 @@ def main():
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--causal", action="store_true")
     a = ap.parse_args()
     fl = not a.no_flush
     if a.what == "gemm":
@@ -326,6 +381,11 @@ def main():
         res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
     elif a.what == "sweep-decode-gemm":
         res = sweep_decode_gemm(a.m)
+    elif a.what == "dense-attention":
+        res = [bench_dense_attention(a.batch if a.batch != 256 else 64, a.ctx if a.ctx != 416 else 128, a.heads if a.heads != 16 else 12,
+                                     a.dim, causal=a.causal, iters=a.iters, flush=fl)]
+    elif a.what == "fused-single-rank":
+        res = [bench_fused_single_rank(a.m, a.n, a.k, iters=a.iters, flush=fl)]
     elif a.what == "overlap":
         res = [overlap(a.batch if a.batch != 256 else 128, a.ctx)]
     elif a.what == "sweep-gemm-depth":

@@ -24,6 +24,8 @@ class EngineConfig:
     backend: str = "kernels"            # "kernels" (hand-written sm_100a) | "torch" (library baseline / CPU)
     tp_comm: str = "fused"              # "fused" (in-kernel NVLink) | "nccl" (library collectives baseline)
     gpu_memory_utilization: float = 0.85
+    cluster_norm: bool = False          # TP=1, >= 1024 rows: projection + residual + next norm as one cluster kernel
+                                        # (measured slower than GEMM + norm kernel at every size tried; kept optional)
     dense_prefill: bool = True          # whole-prompt prefill steps use the tensor-core attention kernel
     decode_streams: int = 1             # >1: decode batches >= 2*decode_split_min rows run as this many concurrent parts
     decode_split_min: int = 64          # (one stream each, inside the step's CUDA graph): the bandwidth-bound
@@ -32,7 +34,7 @@ class EngineConfig:
     def __post_init__(self):
         if self.block_size != 16:
             raise ValueError("the paged attention kernels are built for 16-token blocks")
-        for k in ("max_num_seqs", "max_batch_tokens", "max_model_len", "decode_streams"):
+        for k in ("max_num_seqs", "max_batch_tokens", "max_model_len", "decode_streams", "cluster_norm"):
             env = os.environ.get("RONN_" + k.upper())
             if env:
                 setattr(self, k, int(env))

@@ -226,6 +226,12 @@ class DecoderRunner:
         max_ctx = self.step_ctx if (ops.name == "torch" and self.step_ctx) else self.cfg.max_model_len
         split_down = (ops.name == "kernels" and self.tp == 1 and x.shape[0] <= 512 and not a.bitlinear
                       and self.layers[0]["down"].w is not None and self.layers[0]["down"].w.shape[1] >= 2048)
+        # one rank, prefill-sized batches: the projections that end a half block run as a cluster GEMM whose epilogue
+        # also applies the next norm.  Not for decode: with one or two row tiles only 8-16 CTAs would stream the whole
+        # weight matrix (measured 2x slower than split-K + finalize there).
+        cluster_norm = (ops.name == "kernels" and self.tp == 1 and not a.bitlinear and self.cfg.cluster_norm
+                        and a.hidden % 128 == 0 and a.hidden <= 1024)
+        cluster_norm_rows = 1024
         fused_tp = (ops.name == "kernels" and self.tp > 1 and getattr(comm, "fused", False) and not a.bitlinear
                     and a.hidden <= 1024)
 
@@ -237,6 +243,8 @@ class DecoderRunner:
                     return comm.gemm_allreduce(inp, lw.w, lw.bias, residual), None
                 beta = norm_params[1] if len(norm_params) > 1 else None
                 return comm.gemm_allreduce(inp, lw.w, lw.bias, residual, norm=(a.norm, norm_params[0], beta, a.eps))
+            if cluster_norm and norm_params is not None and lw.w is not None and inp.shape[0] >= cluster_norm_rows:
+                return ops.gemm_rownorm(inp, lw, residual, norm_params, a.norm, a.eps)
             if allow_split and split_down:
                 return ops.gemm_splitk_norm(inp, lw, residual, norm_params, a.norm, a.eps, 4)
             return self._linear(inp, lw, residual=residual, reduce=True, comm=comm), None

@@ -130,6 +130,11 @@ class KernelOps:
                                       gamma=gamma, beta=beta, eps=eps,
                                       norm=(norm_kind if norm_params is not None else ""))
 
+    def gemm_rownorm(self, a, lw, residual, norm_params, norm_kind, eps):
+        """Projection + bias + residual + the next block's norm in one cluster kernel; (new residual stream, normed)."""
+        beta = norm_params[1] if len(norm_params) > 1 else None
+        return self.K.gemm_rownorm(a, lw.w, lw.bias, residual, norm_params[0], beta, eps, norm_kind)
+
     def rmsnorm(self, x, w, eps):
         return self.K.rmsnorm(x, w, eps)
 

@@ -322,3 +322,25 @@ def test_dense_attention_padded_encoder(K):
         ref = _sdpa_ref(rows[:, :hn].view(S, heads, d), rows[:n, hn:2 * hn].view(n, heads, d),
                         rows[:n, 2 * hn:].view(n, heads, d), False)
         torch.testing.assert_close(out[b * S:(b + 1) * S].float().view(S, heads, d), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K_", [(256, 1024, 1024), (256, 1024, 4096), (100, 384, 512), (130, 128, 64), (1, 768, 3072)])
+@pytest.mark.parametrize("norm", ["layernorm", "rmsnorm"])
+def test_gemm_rownorm_cluster(K, M, N, K_, norm):
+    a, w = _rand(M, K_), _rand(N, K_, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    gamma, beta = _rand(N), _rand(N)
+    x, y = K.gemm_rownorm(a, w, bias, res, gamma, beta if norm == "layernorm" else None, 1e-5, norm)
+    K.check_status()
+    ref = a.float() @ w.float().t() + bias.float() + res.float()
+    torch.testing.assert_close(x.float(), ref, atol=2e-2 * math.sqrt(K_ / 64) + 0.06, rtol=2e-2)
+    t = x.float()                                      # the norm is taken over the stored (rounded) sums
+    if norm == "layernorm":
+        want = F.layer_norm(t, (N,), gamma.float(), beta.float(), 1e-5)
+    else:
+        want = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+    torch.testing.assert_close(y.float(), want, atol=6e-2, rtol=3e-2)
+    # no residual, no bias
+    x2, y2 = K.gemm_rownorm(a, w, None, None, gamma, None, 1e-5, "rmsnorm")
+    K.check_status()
+    torch.testing.assert_close(x2.float(), a.float() @ w.float().t(), atol=2e-2 * math.sqrt(K_ / 64) + 0.03, rtol=2e-2)
