@@ -85,7 +85,7 @@ struct PartialProblem {
   __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
     tma_load_2d(smem, map_b, bar, k_elem, n0);
   }
-  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     if (part == nullptr) {
       const int total = *reinterpret_cast<volatile int*>(comm->state);
       part = reinterpret_cast<T*>(comm->peer_part[comm->rank] + size_t(total & 1) * comm->part_stride);
@@ -109,7 +109,61 @@ struct PartialProblem {
   }
 };
 
-template <int BN, int STAGES, class T>
+// Chunks I0 .. I0 + G - 1 (32 x 16 bytes each) of row r: sum the partials of all ranks in rank order, add bias and
+// residual, store the row and keep it (as stored) in v for the norm.  All peer loads are issued before any is used.
+template <class T, int I0, int G, int W>
+__device__ __forceinline__ void reduce_row_chunks(const CommArgs& comm, int r, int lane, int n8, int N, size_t slot, T* out,
+                                                  const T* bias, const T* res, float (&v)[4][8], float& s1, float& s2) {
+  Vec8 pk[G][W];                                // W: compile-time bound of the world size (registers)
+#pragma unroll
+  for (int i = 0; i < G; ++i) {
+    const int c8 = lane + 32 * (I0 + i);
+    if (c8 < n8) {
+      const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * sizeof(T);
+#pragma unroll
+      for (int src = 0; src < W; ++src)
+        if (src < comm.world) pk[i][src] = ld_volatile_16(comm.peer_part[src] + slot + off);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < G; ++i) {
+    const int c8 = lane + 32 * (I0 + i);
+    if (c8 < n8) {
+      const int c = c8 * 8;
+      float acc[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+      for (int src = 0; src < W; ++src)
+        if (src < comm.world) {
+          float f[8];
+          unpack8<T>(pk[i][src], f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] += f[k];
+        }
+      if (bias) {
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+      }
+      if (res) {
+        float f[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+      }
+      const Vec8 o = pack8<T>(acc);
+      *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = o;
+      unpack8<T>(o, v[I0 + i]);                  // normalise exactly what the residual stream stores
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { s1 += v[I0 + i][k]; s2 += v[I0 + i][k] * v[I0 + i][k]; }
+    }
+  }
+}
+
+// W: compile-time bound of the world size (2, 4 or 8); it sizes the register arrays of the reduction phase.
+template <int BN, int STAGES, class T, int W>
 __global__ void __launch_bounds__(PG_THREADS)
 gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CommArgs comm, int M, int N, int K, uint32_t idesc, uint32_t* status) {
@@ -174,45 +228,13 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       for (int r = int(blockIdx.x) * (PG_THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
         float v[4][8];
         float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int c8 = lane + 32 * i;
-          if (c8 < n8) {
-            const int c = c8 * 8;
-            const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
-            Vec8 pk[MAX_RANKS];
-#pragma unroll
-            for (int src = 0; src < MAX_RANKS; ++src)
-              if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-#pragma unroll
-            for (int src = 0; src < MAX_RANKS; ++src)
-              if (src < comm.world) {
-                float f[8];
-                unpack8<T>(pk[src], f);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[k] += f[k];
-              }
-            if (bias) {
-              float f[8];
-              unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) acc[k] += f[k];
-            }
-            if (res) {
-              float f[8];
-              unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
-#pragma unroll
-              for (int k = 0; k < 8; ++k) acc[k] += f[k];
-            }
-            const Vec8 o = pack8<T>(acc);
-            *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = o;
-            unpack8<T>(o, v[i]);                       // normalise exactly what the residual stream stores
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { s1 += v[i][k]; s2 += v[i][k] * v[i][k]; }
-          }
+        // Peer loads cost an NVLink round trip each: every load of a group of chunks (all ranks) is issued before the
+        // first one is used, so a row pays one or two round trips instead of one per chunk.
+        if (W <= 4) {
+          reduce_row_chunks<T, 0, 4, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
+        } else {
+          reduce_row_chunks<T, 0, 2, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
+          reduce_row_chunks<T, 2, 2, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
         }
         if (comm.norm_mode != 0) {
           float mean = 0.f, inv;
@@ -305,11 +327,11 @@ static int comm_sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, class T>
-static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
-                         int is_bf16, uint32_t* status, cudaStream_t stream) {
+template <int BN, int STAGES, class T, int W>
+static int launch_reduce_w(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
+                           int is_bf16, uint32_t* status, cudaStream_t stream) {
   using L = PGemmSmem<BN, STAGES>;
-  auto kern = gemm_reduce_kernel<BN, STAGES, T>;
+  auto kern = gemm_reduce_kernel<BN, STAGES, T, W>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
@@ -326,6 +348,14 @@ static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const Com
   uint32_t idesc = umma_idesc(PG_BM, BN, is_bf16 ? 1u : 0u, 1u);
   cudaError_t err = launch(kern, grid, dim3(PG_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, comm, M, N, K, idesc, status);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+template <int BN, int STAGES, class T>
+static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
+                         int is_bf16, uint32_t* status, cudaStream_t stream) {
+  if (comm.world <= 2) return launch_reduce_w<BN, STAGES, T, 2>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  if (comm.world <= 4) return launch_reduce_w<BN, STAGES, T, 4>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  return launch_reduce_w<BN, STAGES, T, 8>(ma, mb, comm, M, N, K, is_bf16, status, stream);
 }
 
 }  // namespace ronn
@@ -456,11 +486,11 @@ struct GatherProblem {
   __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
     tma_load_2d(smem, map_b, bar, k_elem, n0);
   }
-  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     DenseEpilogue ep = e;
     ep.m0 = m0;
     ep.n0 = n0;
-    ep.run<T>(row, col, r);
+    ep.run<T>(row, col, r, stage);
   }
 };
 

@@ -39,13 +39,13 @@ struct DenseProblem {
   __device__ __forceinline__ void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const {
     tma_load_2d(smem, map_b, bar, k_elem, n0);
   }
-  __device__ __forceinline__ void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&r)[32]) const {
+  __device__ __forceinline__ void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     DenseEpilogue ep = e;
     ep.m0 = m0;
     ep.n0 = n0;
     if (splitk > 1)     // raw fp32 partial sums go to slice z of the workspace
       ep.C = reinterpret_cast<float*>(e.C) + size_t(t / (m_tiles * n_tiles)) * size_t(e.M) * size_t(e.ldc);
-    ep.run<T>(row, col, r);
+    ep.run<T>(row, col, r, stage);
   }
 };
 

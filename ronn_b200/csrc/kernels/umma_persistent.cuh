@@ -18,7 +18,8 @@
 //   void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const     k-block range of the tile
 //   void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const
 //   void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const
-//   void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&acc)[32])   row/col within the tile
+//   void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&acc)[32], uint8_t* stage)   row/col within the
+//        tile; stage: 32 x 80 bytes of shared memory owned by the calling warp (to re-shape its stores)
 #pragma once
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -35,7 +36,9 @@ struct PGemmSmem {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;          // full, empty, acc_full[2], acc_empty[2]
-  static constexpr int TOTAL = TILE_BYTES + NUM_BARS * 8 + 16;
+  static constexpr int OUT_STAGE_ROW = 80;                 // 64 bytes of a row + padding against bank conflicts
+  static constexpr int OUT_STAGE_BYTES = 4 * 32 * OUT_STAGE_ROW;   // per epilogue warp: 32 rows of one 32-column chunk
+  static constexpr int TOTAL = TILE_BYTES + NUM_BARS * 8 + 16 + OUT_STAGE_BYTES;
   static constexpr int DYN_SMEM = TOTAL + 1024;            // slack for manual 1024-byte alignment
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32u : (2 * BN <= 64 ? 64u : (2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u)));
 };
@@ -52,6 +55,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile uint32_t* abort = tmem_slot + 1;
+  uint8_t* out_stage = reinterpret_cast<uint8_t*>(tmem_slot + 4);      // 16-byte aligned, behind the barriers
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -150,6 +154,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
     pdl_trigger();
   } else {
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    uint8_t* stage_w = out_stage + q * (32 * L::OUT_STAGE_ROW);
     pdl_wait();                                  // the epilogue reads residuals and writes buffers the predecessor may use
     uint32_t j = 0;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
@@ -172,7 +177,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        prob.epilogue(t, m0, n0, row, 0, r0);
+        prob.epilogue(t, m0, n0, row, 0, r0, stage_w);
       } else {
         uint32_t r0[32], r1[32];
         tmem_ld_32x32(tacc, r0);
@@ -180,7 +185,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
         for (int col = 0; col < BN; col += 64) {
           tmem_ld_wait();                                    // r0 = columns [col, col + 32)
           tmem_ld_32x32(tacc + uint32_t(col + 32), r1);
-          prob.epilogue(t, m0, n0, row, col, r0);
+          prob.epilogue(t, m0, n0, row, col, r0, stage_w);
           tmem_ld_wait();                                    // r1 = columns [col + 32, col + 64)
           if (col + 64 < BN) {
             tmem_ld_32x32(tacc + uint32_t(col + 64), r0);
@@ -189,7 +194,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
           }
-          prob.epilogue(t, m0, n0, row, col + 32, r1);
+          prob.epilogue(t, m0, n0, row, col + 32, r1, stage_w);
         }
       }
     }
