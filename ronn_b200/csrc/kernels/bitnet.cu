@@ -113,7 +113,7 @@ template <int BN, class T>
 __global__ void __launch_bounds__(BL_THREADS)
 bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_packed,
                  const float* __restrict__ x_scale, float w_scale, const T* __restrict__ bias, T* __restrict__ out,
-                 int M, int N, int K, uint32_t idesc, uint32_t* status) {
+                 int M, int N, int K, uint32_t idesc, uint32_t* status, const int* slot_state, long slot_stride) {
   using L = BitSmem<BN>;
   extern __shared__ uint8_t dyn_smem[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
@@ -174,6 +174,11 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
     // -------------------------------------------------- epilogue
     pdl_wait();
     pdl_trigger();
+    // double-buffered destination (the partial-sum slots of a tensor-parallel reduction): the slot is chosen by the low
+    // bit of a device-side call counter, so a replayed CUDA graph follows the alternation without new arguments
+    if (slot_state != nullptr)
+      out = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(out) +
+                                 size_t(*reinterpret_cast<const volatile int*>(slot_state) & 1) * size_t(slot_stride));
     bool acc_ok = mbar_wait(accum, 0, abort, status, STATUS_WAIT_ACCUM);
     acc_ok = __all_sync(0xffffffffu, acc_ok);
     tc_fence_after_sync();
@@ -270,7 +275,8 @@ __global__ void ternary_pack_kernel(const int8_t* __restrict__ v, uint8_t* __res
 
 template <int BN, class T>
 static int launch_bitlinear(const CUtensorMap& mx, const void* w, const float* xs, float ws, const void* bias, void* out,
-                            int M, int N, int K, uint32_t* status, cudaStream_t stream) {
+                            int M, int N, int K, uint32_t* status, cudaStream_t stream, const int* slot_state = nullptr,
+                            long slot_stride = 0) {
   using L = BitSmem<BN>;
   auto kern = bitlinear_kernel<BN, T>;
   static bool configured = false;
@@ -281,7 +287,7 @@ static int launch_bitlinear(const CUtensorMap& mx, const void* w, const float* x
   dim3 grid((N + BN - 1) / BN, (M + 127) / 128);
   const uint32_t idesc = umma_idesc(128, BN, 1u, 2u);       // signed 8-bit operands, int32 accumulate
   cudaError_t err = launch(kern, grid, dim3(BL_THREADS), size_t(L::DYN_SMEM), stream, mx, (const uint8_t*)w, xs, ws,
-                           (const T*)bias, (T*)out, M, N, K, idesc, status);
+                           (const T*)bias, (T*)out, M, N, K, idesc, status, slot_state, slot_stride);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
@@ -318,10 +324,9 @@ extern "C" int ronn_norm_quant_int8(const void* x, const void* gamma, void* q, f
 
 // xq: int8 [M, K] (row stride ldx bytes); w_packed: [N, K/4]; x_scale: fp32 [M]; out: [M, N] in `dtype` (0 bf16, 1 fp16).
 // K % 16 == 0 and ldx % 16 == 0.
-extern "C" int ronn_bitlinear(const void* xq, const void* w_packed, const float* x_scale, float w_scale,
-                              const void* bias, void* out, void* unused, int M, int N, int K, int ldx, int dtype,
-                              uint32_t* status, cudaStream_t stream) {
-  (void)unused;
+static int bitlinear_impl(const void* xq, const void* w_packed, const float* x_scale, float w_scale, const void* bias,
+                          void* out, int M, int N, int K, int ldx, int dtype, const int* slot_state, long slot_stride,
+                          uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   if ((K & 15) || (ldx & 15)) return -2;
   int bn = 128;
@@ -330,14 +335,31 @@ extern "C" int ronn_bitlinear(const void* xq, const void* w_packed, const float*
   CUtensorMap mx;
   int rc = make_tmap_2d(&mx, xq, uint64_t(M), uint64_t(K), uint64_t(ldx), 128, 128, 1);
   if (rc) return rc - 20;
-#define RONN_BL(BN_) return dtype == 0 ? launch_bitlinear<BN_, __nv_bfloat16>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream) \
-                                       : launch_bitlinear<BN_, __half>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream)
+#define RONN_BL(BN_) return dtype == 0 ? launch_bitlinear<BN_, __nv_bfloat16>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream, slot_state, slot_stride) \
+                                       : launch_bitlinear<BN_, __half>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream, slot_state, slot_stride)
   switch (bn) {
     case 128: RONN_BL(128);
     case 64: RONN_BL(64);
     default: RONN_BL(32);
   }
 #undef RONN_BL
+}
+
+extern "C" int ronn_bitlinear(const void* xq, const void* w_packed, const float* x_scale, float w_scale,
+                              const void* bias, void* out, void* unused, int M, int N, int K, int ldx, int dtype,
+                              uint32_t* status, cudaStream_t stream) {
+  (void)unused;
+  return bitlinear_impl(xq, w_packed, x_scale, w_scale, bias, out, M, N, K, ldx, dtype, nullptr, 0, status, stream);
+}
+
+// Same GEMM, but the [M, N] result goes to out_base + (*slot_state & 1) * slot_stride bytes: the current partial-sum
+// slot of a tensor-parallel reduction (ronn_peer_reduce), resolved on the device.
+extern "C" int ronn_bitlinear_to_slot(const void* xq, const void* w_packed, const float* x_scale, float w_scale,
+                                      void* out_base, const int* slot_state, long slot_stride, int M, int N, int K,
+                                      int ldx, int dtype, uint32_t* status, cudaStream_t stream) {
+  if (slot_state == nullptr || out_base == nullptr) return -1;
+  return bitlinear_impl(xq, w_packed, x_scale, w_scale, nullptr, out_base, M, N, K, ldx, dtype, slot_state, slot_stride,
+                        status, stream);
 }
 
 extern "C" int ronn_ternary_pack(const void* values, void* packed, long rows, int K, cudaStream_t stream) {

@@ -34,7 +34,8 @@ struct CommArgs {
   uint8_t* peer_part[MAX_RANKS];   // base of every rank's partial buffer (two parities back to back)
   int* peer_flags[MAX_RANKS];      // every rank's flag array: [2 parities][MAX_RANKS sources]
   long part_stride;                // bytes between the two parity slots
-  int* state;                      // local: [0] calls completed, [1] phase-1 CTA counter, [2] phase-2 CTA counter
+  int* state;                      // local, 8 ints: [0] calls completed, [1] phase-1 CTA counter, [2] phase-2 CTA
+                                   // counter, [4 + parity] flag (pull-mode) calls completed on that parity
   int rank, world;
   int row_begin, row_end;          // rows this rank reduces and writes
   void* out;                       // [row_end - row_begin, N]
@@ -48,6 +49,14 @@ struct CommArgs {
   const void* beta;
   float eps;
   int norm_mode;                   // 0 none, 1 LayerNorm, 2 RMSNorm (needs N <= 1024)
+  // Push mode (small results, N <= 1024): the epilogue stores every partial tile into the receive area of EVERY rank,
+  // slot [parity][source rank], as 8-byte words {two 16-bit values, call sequence number}.  A word is written
+  // atomically, so a reader that sees the current sequence number in a word also sees its data: no fence, no flag
+  // round trip, no atomics; the reduction polls local memory only.  A slot holds M * N / 2 words (4 bytes per value).
+  uint8_t* peer_recv[MAX_RANKS];   // base of every rank's receive area, or all null (pull mode)
+  long recv_parity_stride;         // bytes between the two parities of a receive area
+  long recv_src_stride;            // bytes between source slots
+  int push;
 };
 
 __device__ __forceinline__ Vec8 ld_volatile_16(const void* p) {
@@ -64,13 +73,24 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
-template <int BN, class T>
+__device__ __forceinline__ void st_volatile_16(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+template <int BN, class T, bool PUSH>
 struct PartialProblem {
   const CUtensorMap* map_a;
   const CUtensorMap* map_b;
   const CommArgs* comm;
   int M, N, m_tiles, n_tiles, num_kb;
   mutable T* part;                 // resolved lazily by the epilogue (after the dependency wait)
+  mutable int parity;
+  mutable uint32_t seq;             // sequence number of this call (push mode)
 
   __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
   __device__ __forceinline__ void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const {
@@ -88,10 +108,46 @@ struct PartialProblem {
   __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     if (part == nullptr) {
       const int total = *reinterpret_cast<volatile int*>(comm->state);
-      part = reinterpret_cast<T*>(comm->peer_part[comm->rank] + size_t(total & 1) * comm->part_stride);
+      parity = total & 1;
+      seq = uint32_t(total) + 1u;
+      part = reinterpret_cast<T*>(comm->peer_part[comm->rank] + size_t(parity) * comm->part_stride);
     }
     const int gm = m0 + row, gn = n0 + col;
-    if (gm >= M || gn >= N) return;
+    if (gn >= N) return;                          // uniform across the warp
+    if (PUSH) {                                   // launcher guarantees N % 32 == 0 in this mode
+      // 64 bytes of this lane's row -> stage; then every rank's receive slot gets the chunk as {data, sequence} words,
+      // 4 lanes covering 128 contiguous bytes of a row per store pair
+      const int lane = threadIdx.x & 31;
+      if (gm < M) {
+        uint8_t* mine = stage + lane * 80;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[j * 8 + i]);
+          *reinterpret_cast<Vec8*>(mine + j * 16) = pack8<T>(f);
+        }
+      }
+      __syncwarp();
+      const int base_row = gm - lane, piece = lane & 3;
+      const size_t slot = size_t(parity) * comm->recv_parity_stride + size_t(comm->rank) * comm->recv_src_stride;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = (lane >> 2) + 8 * i;
+        if (base_row + rr < M) {
+          const Vec8 pk = *reinterpret_cast<const Vec8*>(stage + rr * 80 + piece * 16);
+          const size_t off = slot + (size_t(base_row + rr) * N + gn + piece * 8) * 4;     // 4 bytes per value
+#pragma unroll 1
+          for (int p = 0; p < comm->world; ++p) {
+            st_volatile_16(comm->peer_recv[p] + off, pk.w[0], seq, pk.w[1], seq);
+            st_volatile_16(comm->peer_recv[p] + off + 16, pk.w[2], seq, pk.w[3], seq);
+          }
+        }
+      }
+      __syncwarp();
+      return;
+    }
+    if (gm >= M) return;
     T* dst = part + size_t(gm) * N + gn;
     if (gn + 32 <= N) {
 #pragma unroll
@@ -109,83 +165,128 @@ struct PartialProblem {
   }
 };
 
-// Chunks I0 .. I0 + G - 1 (32 x 16 bytes each) of row r: sum the partials of all ranks in rank order, add bias and
-// residual, store the row and keep it (as stored) in v for the norm.  All peer loads are issued before any is used.
-template <class T, int I0, int G, int W>
-__device__ __forceinline__ void reduce_row_chunks(const CommArgs& comm, int r, int lane, int n8, int N, size_t slot, T* out,
-                                                  const T* bias, const T* res, float (&v)[4][8], float& s1, float& s2) {
-  Vec8 pk[G][W];                                // W: compile-time bound of the world size (registers)
+// Tail of a reduced 8-value chunk: bias, residual, store, and the row statistics of the stored (rounded) values.
+template <class T>
+__device__ __forceinline__ void finish_chunk(const CommArgs& comm, float (&acc)[8], int r, int c, T* out, const T* bias,
+                                             const T* res, float (&vrow)[8], float& s1, float& s2) {
+  if (bias) {
+    float f[8];
+    unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
 #pragma unroll
-  for (int i = 0; i < G; ++i) {
-    const int c8 = lane + 32 * (I0 + i);
-    if (c8 < n8) {
-      const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * sizeof(T);
-#pragma unroll
-      for (int src = 0; src < W; ++src)
-        if (src < comm.world) pk[i][src] = ld_volatile_16(comm.peer_part[src] + slot + off);
-    }
+    for (int k = 0; k < 8; ++k) acc[k] += f[k];
   }
+  if (res) {
+    float f[8];
+    unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
 #pragma unroll
-  for (int i = 0; i < G; ++i) {
-    const int c8 = lane + 32 * (I0 + i);
-    if (c8 < n8) {
-      const int c = c8 * 8;
-      float acc[8];
+    for (int k = 0; k < 8; ++k) acc[k] += f[k];
+  }
+  const Vec8 o = pack8<T>(acc);
+  *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = o;
+  unpack8<T>(o, vrow);                           // normalise exactly what the residual stream stores
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  for (int k = 0; k < 8; ++k) { s1 += vrow[k]; s2 += vrow[k] * vrow[k]; }
+}
+
+// Chunks I0 .. I0 + G - 1 (32 x 16 bytes each) of row r: sum the partials of all ranks in rank order, add bias and
+// residual, store the row and keep it (as stored) in v for the norm.
+// LL = false: partials are read from the peers' buffers; all peer loads are issued before any is used.
+// LL = true : the sources are this rank's receive slots in {data, sequence} words (push mode); the words of a chunk
+//             are re-read until every one carries `seq` (bounded by `deadline`; `alive` goes false when it passes).
+template <class T, int I0, int G, int W, bool LL>
+__device__ __forceinline__ void reduce_row_chunks(const CommArgs& comm, const uint8_t* const (&src_base)[W], int r, int lane,
+                                                  int n8, int N, T* out,
+                                                  const T* bias, const T* res, float (&v)[4][8], float& s1, float& s2,
+                                                  uint32_t seq, unsigned long long deadline, bool& alive,
+                                                  uint32_t* status) {
+  if (LL) {
 #pragma unroll
-      for (int src = 0; src < W; ++src)
-        if (src < comm.world) {
-          float f[8];
-          unpack8<T>(pk[i][src], f);
+    for (int i = 0; i < G; ++i) {
+      const int c8 = lane + 32 * (I0 + i);
+      if (c8 < n8) {
+        const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * 4;
+        float acc[8];
+        uint32_t polls = 0;
+        bool ready;
+        do {
+          ready = true;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] += f[k];
-        }
-      if (bias) {
-        float f[8];
-        unpack8<T>(*reinterpret_cast<const Vec8*>(bias + c), f);
+          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+          for (int src = 0; src < W; ++src)
+            if (src < comm.world) {
+              const uint4 lo = ld_volatile_u4(src_base[src] + off);
+              const uint4 hi = ld_volatile_u4(src_base[src] + off + 16);
+              ready = ready && lo.y == seq && lo.w == seq && hi.y == seq && hi.w == seq;
+              Vec8 t;
+              t.w[0] = lo.x;
+              t.w[1] = lo.z;
+              t.w[2] = hi.x;
+              t.w[3] = hi.z;
+              float f[8];
+              unpack8<T>(t, f);
+#pragma unroll
+              for (int k = 0; k < 8; ++k) acc[k] += f[k];
+            }
+          if (!ready && (++polls & 63u) == 0u && globaltimer_ns() > deadline) {
+            if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
+            alive = false;
+          }
+        } while (!ready && alive);
+        finish_chunk<T>(comm, acc, r, c8 * 8, out, bias, res, v[I0 + i], s1, s2);
       }
-      if (res) {
-        float f[8];
-        unpack8<T>(*reinterpret_cast<const Vec8*>(res + size_t(r) * comm.ld_res + c), f);
+    }
+  } else {
+    Vec8 pk[G][W];                              // W: compile-time bound of the world size (registers)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+    for (int i = 0; i < G; ++i) {
+      const int c8 = lane + 32 * (I0 + i);
+      if (c8 < n8) {
+        const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * sizeof(T);
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < comm.world) pk[i][src] = ld_volatile_16(src_base[src] + off);
       }
-      const Vec8 o = pack8<T>(acc);
-      *reinterpret_cast<Vec8*>(out + size_t(r) * comm.ld_out + c) = o;
-      unpack8<T>(o, v[I0 + i]);                  // normalise exactly what the residual stream stores
+    }
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { s1 += v[I0 + i][k]; s2 += v[I0 + i][k] * v[I0 + i][k]; }
+    for (int i = 0; i < G; ++i) {
+      const int c8 = lane + 32 * (I0 + i);
+      if (c8 < n8) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int src = 0; src < W; ++src)
+          if (src < comm.world) {
+            float f[8];
+            unpack8<T>(pk[i][src], f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += f[k];
+          }
+        finish_chunk<T>(comm, acc, r, c8 * 8, out, bias, res, v[I0 + i], s1, s2);
+      }
     }
   }
 }
 
-// W: compile-time bound of the world size (2, 4 or 8); it sizes the register arrays of the reduction phase.
-template <int BN, int STAGES, class T, int W>
-__global__ void __launch_bounds__(PG_THREADS)
-gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                   const __grid_constant__ CommArgs comm, int M, int N, int K, uint32_t idesc, uint32_t* status) {
-  extern __shared__ uint8_t dyn_smem[];
-  __shared__ int s_flag;
-  PartialProblem<BN, T> prob;
-  prob.map_a = &map_a;
-  prob.map_b = &map_b;
-  prob.comm = &comm;
-  prob.M = M;
-  prob.N = N;
-  prob.m_tiles = (M + PG_BM - 1) / PG_BM;
-  prob.n_tiles = (N + BN - 1) / BN;
-  prob.num_kb = (K + 63) / 64;
-  prob.part = nullptr;
-  gemm_persistent<BN, STAGES, 0, PartialProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
-  // ---- end of phase 1: every thread of this CTA has issued its partial stores (teardown barrier passed)
+// Cross-rank phase shared by the fused GEMM kernel and the stand-alone reduction kernel.  On entry every thread of the
+// CTA has issued its stores of this rank's partial result (and passed a CTA barrier).  All CTAs of the grid must be
+// resident at once: the phase waits on work of the whole grid and of the peers.
+template <class T, int W, bool PUSH>
+__device__ __forceinline__ void cross_rank_phase(const CommArgs& comm, int M, int N, uint32_t* status, int& s_flag) {
   pdl_wait();
   const int total = *reinterpret_cast<volatile int*>(comm.state);
   const int parity = total & 1;
-  const int want = (total >> 1) + 1;
-  if (threadIdx.x == 0) {
+  // flag value this call waits for: the flag calls (pull mode) completed on this parity, plus one; push-mode calls do
+  // not touch the flags, so they are not counted
+  const int want = PUSH ? 0 : *reinterpret_cast<volatile int*>(comm.state + 4 + parity) + 1;
+  const uint32_t seq = uint32_t(total) + 1u;
+  const unsigned long long deadline = globaltimer_ns() + comm.wait_ns;
+  bool alive = true;
+  if (PUSH) {
+    // push mode: the data words carry the sequence number themselves; nothing to signal and nothing to wait for here
+    if (threadIdx.x == 0) s_flag = 1;
+  } else if (threadIdx.x == 0) {
     __threadfence_system();
     const int done = atomicAdd(comm.state + 1, 1);
     if (done == int(gridDim.x) - 1) {            // last CTA of this rank: tell every rank our partials are complete
@@ -214,7 +315,16 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (s_flag) {
     const int rows = comm.row_end - comm.row_begin;
     const int n8 = N >> 3;
-    const size_t slot = size_t(parity) * comm.part_stride;
+    // where the partials of source rank `src` are read from: this rank's receive slots (push) or the peers' buffers
+    const uint8_t* src_base[W];
+#pragma unroll
+    for (int src = 0; src < W; ++src) {
+      src_base[src] = nullptr;
+      if (src < comm.world)
+        src_base[src] = PUSH ? comm.peer_recv[comm.rank] + size_t(parity) * comm.recv_parity_stride +
+                                        size_t(src) * comm.recv_src_stride
+                                  : comm.peer_part[src] + size_t(parity) * comm.part_stride;
+    }
     T* out = reinterpret_cast<T*>(comm.out);
     const T* bias = reinterpret_cast<const T*>(comm.bias);
     const T* res = reinterpret_cast<const T*>(comm.residual);
@@ -230,11 +340,13 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         float s1 = 0.f, s2 = 0.f;
         // Peer loads cost an NVLink round trip each: every load of a group of chunks (all ranks) is issued before the
         // first one is used, so a row pays one or two round trips instead of one per chunk.
-        if (W <= 4) {
-          reduce_row_chunks<T, 0, 4, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
+        if (PUSH) {
+          reduce_row_chunks<T, 0, 4, W, true>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+        } else if (W <= 4) {
+          reduce_row_chunks<T, 0, 4, W, false>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
         } else {
-          reduce_row_chunks<T, 0, 2, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
-          reduce_row_chunks<T, 2, 2, W>(comm, r, lane, n8, N, slot, out, bias, res, v, s1, s2);
+          reduce_row_chunks<T, 0, 2, W, false>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+          reduce_row_chunks<T, 2, 2, W, false>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
         }
         if (comm.norm_mode != 0) {
           float mean = 0.f, inv;
@@ -275,15 +387,15 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       for (long v = long(blockIdx.x) * blockDim.x + threadIdx.x; v < vecs; v += long(gridDim.x) * blockDim.x) {
         const int r = int(v / n8), c = int(v - long(r) * n8) * 8;
         const size_t off = (size_t(comm.row_begin + r) * N + c) * sizeof(T);
-        Vec8 pk[MAX_RANKS];
+        Vec8 pk[W];
 #pragma unroll
-        for (int src = 0; src < MAX_RANKS; ++src)
-          if (src < comm.world) pk[src] = ld_volatile_16(comm.peer_part[src] + slot + off);
+        for (int src = 0; src < W; ++src)
+          if (src < comm.world) pk[src] = ld_volatile_16(src_base[src] + off);
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 #pragma unroll
-        for (int src = 0; src < MAX_RANKS; ++src)
+        for (int src = 0; src < W; ++src)
           if (src < comm.world) {
             float f[8];
             unpack8<T>(pk[src], f);
@@ -311,10 +423,46 @@ gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int done = atomicAdd(comm.state + 2, 1);
     if (done == int(gridDim.x) - 1) {            // last CTA: the call is complete on this rank
       comm.state[2] = 0;
+      if (!PUSH) comm.state[4 + parity] = want;
       __threadfence();
       *reinterpret_cast<volatile int*>(comm.state) = total + 1;
     }
   }
+}
+
+// W: compile-time bound of the world size (2, 4 or 8); it sizes the register arrays of the reduction phase.
+template <int BN, int STAGES, class T, int W, bool PUSH>
+__global__ void __launch_bounds__(PG_THREADS)
+gemm_reduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CommArgs comm, int M, int N, int K, uint32_t idesc, uint32_t* status) {
+  extern __shared__ uint8_t dyn_smem[];
+  __shared__ int s_flag;
+  PartialProblem<BN, T, PUSH> prob;
+  prob.map_a = &map_a;
+  prob.map_b = &map_b;
+  prob.comm = &comm;
+  prob.M = M;
+  prob.N = N;
+  prob.m_tiles = (M + PG_BM - 1) / PG_BM;
+  prob.n_tiles = (N + BN - 1) / BN;
+  prob.num_kb = (K + 63) / 64;
+  prob.part = nullptr;
+  gemm_persistent<BN, STAGES, 0, PartialProblem<BN, T, PUSH>>(dyn_smem, prob, 64, idesc, status);
+  // ---- end of phase 1: every thread of this CTA has issued its partial stores (teardown barrier passed)
+  cross_rank_phase<T, W, PUSH>(comm, M, N, status, s_flag);
+}
+
+// Reduction of partial results that another kernel of this rank (e.g. the ternary BitLinear GEMM) has written into the
+// current parity slot of this rank's partial buffer: flags, bounded wait, rank-ordered sum from peer memory, bias,
+// residual and optional norm.  grid <= resident CTAs.
+template <class T, int W>
+__global__ void __launch_bounds__(PG_THREADS)
+peer_reduce_kernel(const __grid_constant__ CommArgs comm, int M, int N, uint32_t* status) {
+  __shared__ int s_flag;
+  pdl_wait();                                    // the producer of the partials is the previous kernel in the stream
+  pdl_trigger();
+  __syncthreads();
+  cross_rank_phase<T, W, false>(comm, M, N, status, s_flag);
 }
 
 static int comm_sm_count() {
@@ -327,11 +475,11 @@ static int comm_sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, class T, int W>
+template <int BN, int STAGES, class T, int W, bool PUSH>
 static int launch_reduce_w(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
                            int is_bf16, uint32_t* status, cudaStream_t stream) {
   using L = PGemmSmem<BN, STAGES>;
-  auto kern = gemm_reduce_kernel<BN, STAGES, T, W>;
+  auto kern = gemm_reduce_kernel<BN, STAGES, T, W, PUSH>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
@@ -353,9 +501,14 @@ static int launch_reduce_w(const CUtensorMap& ma, const CUtensorMap& mb, const C
 template <int BN, int STAGES, class T>
 static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
                          int is_bf16, uint32_t* status, cudaStream_t stream) {
-  if (comm.world <= 2) return launch_reduce_w<BN, STAGES, T, 2>(ma, mb, comm, M, N, K, is_bf16, status, stream);
-  if (comm.world <= 4) return launch_reduce_w<BN, STAGES, T, 4>(ma, mb, comm, M, N, K, is_bf16, status, stream);
-  return launch_reduce_w<BN, STAGES, T, 8>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  if (comm.push) {
+    if (comm.world <= 2) return launch_reduce_w<BN, STAGES, T, 2, true>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+    if (comm.world <= 4) return launch_reduce_w<BN, STAGES, T, 4, true>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+    return launch_reduce_w<BN, STAGES, T, 8, true>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  }
+  if (comm.world <= 2) return launch_reduce_w<BN, STAGES, T, 2, false>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  if (comm.world <= 4) return launch_reduce_w<BN, STAGES, T, 4, false>(ma, mb, comm, M, N, K, is_bf16, status, stream);
+  return launch_reduce_w<BN, STAGES, T, 8, false>(ma, mb, comm, M, N, K, is_bf16, status, stream);
 }
 
 }  // namespace ronn
@@ -363,16 +516,17 @@ static int launch_reduce(const CUtensorMap& ma, const CUtensorMap& mb, const Com
 using namespace ronn;
 
 // peer_part / peer_flags: `world` pointers each.  part_stride: bytes between the two parity slots of a partial
-// buffer (>= M * N * 2).  state: three zero-initialised ints in local device memory, shared by all calls on this
+// buffer (>= M * N * 2).  state: eight zero-initialised ints in local device memory, shared by all calls on this
 // rank.  Rows [row_begin, row_end) of the reduced result (+ bias + residual) are written to `out`.
 // With norm_mode 1 (LayerNorm) / 2 (RMSNorm) and N <= 1024 the normalised rows are also written to norm_out.
 // dtype 0 bf16, 1 fp16.  N % 8 == 0.  Returns 0 on success.
-extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
-                                void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
-                                int rank, int world, int row_begin, int row_end, void* out, long ld_out,
-                                const void* bias, const void* residual, long ld_res, double wait_seconds, int dtype,
-                                int bn, void* norm_out, const void* gamma, const void* beta, float eps, int norm_mode,
-                                uint32_t* status, cudaStream_t stream) {
+static int gemm_reduce_impl(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                            void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
+                            int rank, int world, int row_begin, int row_end, void* out, long ld_out,
+                            const void* bias, const void* residual, long ld_res, double wait_seconds, int dtype,
+                            int bn, void* norm_out, const void* gamma, const void* beta, float eps, int norm_mode,
+                            void* const* peer_recv, long recv_parity_stride, long recv_src_stride,
+                            uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
   if ((K & 7) || (lda & 7) || (ldw & 7) || (N & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return -2;
   if (norm_mode != 0 && (N > 1024 || norm_out == nullptr)) return -5;
@@ -392,6 +546,15 @@ extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int 
     c.peer_part[p] = p < world ? static_cast<uint8_t*>(peer_part[p]) : nullptr;
     c.peer_flags[p] = p < world ? peer_flags[p] : nullptr;
   }
+  c.push = peer_recv != nullptr ? 1 : 0;
+  // push mode: a slot holds 4 bytes per value; whole 32-column chunks and the row-wise reduction (N <= 1024) only
+  if (c.push && (recv_src_stride < long(M) * N * 4 || recv_parity_stride < recv_src_stride * world || (N & 31) ||
+                 N > 1024))
+    return -6;
+  for (int p = 0; p < MAX_RANKS; ++p)
+    c.peer_recv[p] = (c.push && p < world) ? static_cast<uint8_t*>(peer_recv[p]) : nullptr;
+  c.recv_parity_stride = recv_parity_stride;
+  c.recv_src_stride = recv_src_stride;
   c.part_stride = part_stride;
   c.state = state;
   c.rank = rank;
@@ -420,6 +583,87 @@ extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int 
     default: return -3;
   }
 #undef RONN_DISPATCH
+}
+
+extern "C" int ronn_gemm_reduce(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
+                                int rank, int world, int row_begin, int row_end, void* out, long ld_out,
+                                const void* bias, const void* residual, long ld_res, double wait_seconds, int dtype,
+                                int bn, void* norm_out, const void* gamma, const void* beta, float eps, int norm_mode,
+                                uint32_t* status, cudaStream_t stream) {
+  return gemm_reduce_impl(A, W, M, N, K, lda, ldw, peer_part, peer_flags, part_stride, state, rank, world, row_begin,
+                          row_end, out, ld_out, bias, residual, ld_res, wait_seconds, dtype, bn, norm_out, gamma, beta, eps,
+                          norm_mode, nullptr, 0, 0, status, stream);
+}
+
+// Push variant for small results (N a multiple of 32, at most 1024): peer_recv[p] is rank p's receive area of
+// 2 parities x `world` source slots (recv_parity_stride / recv_src_stride bytes apart, a slot holds 4 bytes per
+// value).  Every partial tile is stored into all ranks' slots by the GEMM epilogue as {data, sequence} words; the
+// reduction polls local memory only (no fence, no flags, no atomics between the ranks).
+extern "C" int ronn_gemm_reduce_push(const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                     void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
+                                     int rank, int world, int row_begin, int row_end, void* out, long ld_out,
+                                     const void* bias, const void* residual, long ld_res, double wait_seconds,
+                                     int dtype, int bn, void* norm_out, const void* gamma, const void* beta, float eps,
+                                     int norm_mode, void* const* peer_recv, long recv_parity_stride,
+                                     long recv_src_stride, uint32_t* status, cudaStream_t stream) {
+  if (peer_recv == nullptr) return -6;
+  return gemm_reduce_impl(A, W, M, N, K, lda, ldw, peer_part, peer_flags, part_stride, state, rank, world, row_begin,
+                          row_end, out, ld_out, bias, residual, ld_res, wait_seconds, dtype, bn, norm_out, gamma, beta, eps,
+                          norm_mode, peer_recv, recv_parity_stride, recv_src_stride, status, stream);
+}
+
+// Cross-rank reduction of partial results that are already in the current parity slot of every rank's partial buffer
+// (written by the previous kernel on the stream, e.g. ronn_bitlinear_to_slot).  Same arguments and semantics as the
+// reduction half of ronn_gemm_reduce.
+extern "C" int ronn_peer_reduce(int M, int N, void* const* peer_part, int* const* peer_flags, long part_stride, int* state,
+                                int rank, int world, int row_begin, int row_end, void* out, long ld_out, const void* bias,
+                                const void* residual, long ld_res, double wait_seconds, int dtype, void* norm_out,
+                                const void* gamma, const void* beta, float eps, int norm_mode, uint32_t* status,
+                                cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
+  if ((N & 7) || (ld_out & 7) || (residual && (ld_res & 7))) return -2;
+  if (norm_mode != 0 && (N > 1024 || norm_out == nullptr)) return -5;
+  if (row_begin < 0 || row_end > M || row_begin > row_end || part_stride < long(M) * N * 2) return -4;
+  CommArgs c;
+  for (int p = 0; p < MAX_RANKS; ++p) {
+    c.peer_part[p] = p < world ? static_cast<uint8_t*>(peer_part[p]) : nullptr;
+    c.peer_flags[p] = p < world ? peer_flags[p] : nullptr;
+    c.peer_recv[p] = nullptr;
+  }
+  c.push = 0;
+  c.recv_parity_stride = c.recv_src_stride = 0;
+  c.part_stride = part_stride;
+  c.state = state;
+  c.rank = rank;
+  c.world = world;
+  c.row_begin = row_begin;
+  c.row_end = row_end;
+  c.out = out;
+  c.ld_out = ld_out;
+  c.bias = bias;
+  c.residual = residual;
+  c.ld_res = ld_res;
+  c.wait_ns = static_cast<unsigned long long>(wait_seconds * 1e9);
+  c.norm_out = norm_out;
+  c.gamma = gamma;
+  c.beta = beta;
+  c.eps = eps;
+  c.norm_mode = norm_mode;
+  const int rows = row_end - row_begin;
+  const int warps_per_cta = PG_THREADS / 32;
+  int grid = N <= 1024 ? (rows + warps_per_cta - 1) / warps_per_cta : int((long(rows) * (N >> 3) + PG_THREADS - 1) / PG_THREADS);
+  if (grid > comm_sm_count()) grid = comm_sm_count();         // every CTA resident at once
+  if (grid < 1) grid = 1;
+  cudaError_t err;
+#define RONN_PR(T_, W_) err = launch(peer_reduce_kernel<T_, W_>, dim3(grid), dim3(PG_THREADS), 0, stream, c, M, N, status)
+  if (dtype == 0) {
+    if (world <= 2) RONN_PR(__nv_bfloat16, 2); else if (world <= 4) RONN_PR(__nv_bfloat16, 4); else RONN_PR(__nv_bfloat16, 8);
+  } else {
+    if (world <= 2) RONN_PR(__half, 2); else if (world <= 4) RONN_PR(__half, 4); else RONN_PR(__half, 8);
+  }
+#undef RONN_PR
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
 // =====================================================================================================================

@@ -229,7 +229,7 @@ def bench_fused_single_rank(m=256, n=1024, k=1024, iters=20, flush=True):
     stride = m * n * 2
     part = torch.zeros(2 * stride, dtype=torch.uint8, device="cuda")
     flags = torch.zeros(16, dtype=torch.int32, device="cuda")
-    state = torch.zeros(4, dtype=torch.int32, device="cuda")
+    state = torch.zeros(8, dtype=torch.int32, device="cuda")
     out, normed = torch.empty_like(res), torch.empty_like(res)
     pp = (C.c_void_p * 8)(*[part.data_ptr()] + [None] * 7)
     fp = (C.c_void_p * 8)(*[flags.data_ptr()] + [None] * 7)

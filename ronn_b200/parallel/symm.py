@@ -44,7 +44,13 @@ class FusedComm(TPComm):
         self.part_stride = self.max_elems * 2                       # bytes of one parity slot (16-bit elements)
         flag_bytes = 512                                            # reduce flags [2][8] ints, gather flags [8] ints
         self.shard_bytes = (max_rows // max(self.world, 1) + 128) * max_cols * 2
-        total = 2 * self.part_stride + flag_bytes + self.shard_bytes
+        # receive area of the push variant: [2 parities][world sources][push_elems] values, 4 bytes each (16-bit data
+        # paired with the call's sequence number)
+        self.push_elems = int(os.environ.get("RONN_PUSH_ELEMS", 1 << 20)) if self.world > 1 else 0
+        self.recv_src_stride = self.push_elems * 4
+        self.recv_parity_stride = self.recv_src_stride * self.world
+        recv_bytes = 2 * self.recv_parity_stride
+        total = 2 * self.part_stride + flag_bytes + self.shard_bytes + recv_bytes
         self._buf = symm.empty(total, dtype=torch.uint8, device=self.device)
         self._buf.zero_()
         torch.cuda.synchronize(self.device)
@@ -60,11 +66,16 @@ class FusedComm(TPComm):
         self._shard_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + shard_off) if p < self.world else None
                                                      for p in range(MAX_RANKS)])
         self._shard_local = self._buf[shard_off: shard_off + self.shard_bytes]
+        recv_off = shard_off + self.shard_bytes
+        self._recv_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + recv_off) if p < self.world else None
+                                                    for p in range(MAX_RANKS)])
         self._ag_flags_local = ptrs[self.rank] + 2 * self.part_stride + 256
         self._ag_state = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self._state = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._state = torch.zeros(8, dtype=torch.int32, device=self.device)
         self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
         self.fused_calls = 0
+        self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
+        self.push = self.world > 1 and os.environ.get("RONN_TP_PUSH", "0") == "1"
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
     def clone(self, max_rows: Optional[int] = None) -> "FusedComm":
@@ -92,14 +103,20 @@ class FusedComm(TPComm):
             kind, gamma, beta, eps = norm
             mode = 1 if kind == "layernorm" else 2
             normed = torch.empty_like(out)
-        rc = _native.cuda().ronn_gemm_reduce(
-            a.data_ptr(), w_nk.data_ptr(), M, N, Kd, a.stride(0), w_nk.stride(0), self._part_ptrs, self._flag_ptrs,
-            self.part_stride, self._state.data_ptr(), self.rank, self.world, row_begin, row_end, out.data_ptr(),
-            out.stride(0), None if bias is None else bias.data_ptr(), None if residual is None else residual.data_ptr(),
-            residual.stride(0) if residual is not None else 0, self.wait_seconds, 0 if a.dtype == torch.bfloat16 else 1,
-            bn, None if normed is None else normed.data_ptr(), None if gamma is None else gamma.data_ptr(),
-            None if beta is None else beta.data_ptr(), float(eps), mode,
-            K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        args = (a.data_ptr(), w_nk.data_ptr(), M, N, Kd, a.stride(0), w_nk.stride(0), self._part_ptrs, self._flag_ptrs,
+                self.part_stride, self._state.data_ptr(), self.rank, self.world, row_begin, row_end, out.data_ptr(),
+                out.stride(0), None if bias is None else bias.data_ptr(),
+                None if residual is None else residual.data_ptr(), residual.stride(0) if residual is not None else 0,
+                self.wait_seconds, 0 if a.dtype == torch.bfloat16 else 1, bn,
+                None if normed is None else normed.data_ptr(), None if gamma is None else gamma.data_ptr(),
+                None if beta is None else beta.data_ptr(), float(eps), mode)
+        tail = (K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if self.push and 0 < M * N <= self.push_elems and N % 32 == 0 and N <= 1024:
+            # small result (decode): partial tiles are stored into every rank's receive slots by the GEMM epilogue
+            rc = _native.cuda().ronn_gemm_reduce_push(*args, self._recv_ptrs, self.recv_parity_stride,
+                                                      self.recv_src_stride, *tail)
+        else:
+            rc = _native.cuda().ronn_gemm_reduce(*args, *tail)
         if rc != 0:
             raise K.KernelError(f"gemm_reduce failed with code {rc}")
         self.fused_calls += 1
@@ -108,8 +125,58 @@ class FusedComm(TPComm):
     def gemm_allreduce(self, a, w_nk, bias=None, residual=None, bn=0, norm=None):
         """sum over ranks of (a @ w_nk^T) + bias + residual, full result on every rank (bit-identical).
         ``norm=(kind, gamma, beta, eps)`` (hidden size <= 1024) also returns the normalised rows: the reduction
-        pass holds whole rows in registers, so the next block's LayerNorm / RMSNorm costs no extra kernel."""
+        pass holds whole rows in registers, so the next block's LayerNorm / RMSNorm costs no extra kernel.
+
+        The one-shot exchange (every rank reads every peer's whole partial result) is a latency design: measured
+        1.3-1.6x faster than GEMM + NCCL all-reduce + norm for decode-sized results, but 0.7x at 8192 x 1024 where
+        moving (world - 1) full copies per rank costs more than a ring.  Results above ``one_shot_elems`` therefore
+        take the GEMM kernel + library all-reduce + the fused bias/residual/norm kernel."""
+        M, N = a.shape[0], w_nk.shape[0]
+        if self.world > 1 and M * N > self.one_shot_elems:
+            y = K.gemm(a, w_nk)
+            dist.all_reduce(y, group=self.group)
+            self.calls += 1
+            if bias is not None:
+                y += bias
+            if norm is None:
+                return y + residual if residual is not None else y
+            kind, gamma, beta, eps = norm
+            if kind == "layernorm":
+                normed, total = K.layernorm(y, gamma, beta, eps, residual=residual, return_sum=True)
+            else:
+                normed, total = K.rmsnorm(y, gamma, eps, residual=residual, return_sum=True)
+            return total, normed
         return self._gemm_reduce(a, w_nk, bias, residual, 0, a.shape[0], bn, norm)
+
+    # ------------------------------------------------------------------ BitLinear partials + cross-rank reduction
+    def bitlinear_allreduce(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual=None):
+        """Row-parallel BitLinear: the ternary x int8 GEMM kernel writes this rank's [M, n] partial result straight into
+        the current slot of the symmetric partial buffer (slot chosen on the device), and the reduction kernel sums the
+        ranks' partials over NVLink peer memory in rank order and adds the residual.  Two launches, no library
+        collective, bit-identical on every rank."""
+        from ..ops.bitnet import _check as _bcheck
+        M = q.shape[0]
+        if M * n > self.max_elems:
+            raise ProviderError(f"fused BitLinear of {M}x{n} exceeds the symmetric buffer ({self.max_elems} elements)")
+        lib = _native.cuda()
+        dt = 0 if out_dtype == torch.bfloat16 else 1
+        stream = torch.cuda.current_stream().cuda_stream
+        status = K.status_word(q.device).data_ptr()
+        _bcheck(lib.ronn_bitlinear_to_slot(q.data_ptr(), w_packed.data_ptr(), x_scale.data_ptr(), float(w_scale),
+                                           self._part_ptrs[self.rank], self._state.data_ptr(), self.part_stride, M, n, k,
+                                           q.stride(0), dt, status, stream), "bitlinear_to_slot")
+        out = torch.empty((M, n), dtype=out_dtype, device=q.device)
+        if residual is not None and (residual.stride(1) != 1 or residual.shape != out.shape):
+            residual = residual.reshape(M, n).contiguous()
+        rc = lib.ronn_peer_reduce(M, n, self._part_ptrs, self._flag_ptrs, self.part_stride, self._state.data_ptr(),
+                                  self.rank, self.world, 0, M, out.data_ptr(), out.stride(0), None,
+                                  None if residual is None else residual.data_ptr(),
+                                  residual.stride(0) if residual is not None else 0, self.wait_seconds, dt, None, None,
+                                  None, 0.0, 0, status, stream)
+        if rc != 0:
+            raise K.KernelError(f"peer_reduce failed with code {rc}")
+        self.fused_calls += 1
+        return out
 
     def gemm_reduce_scatter(self, a, w_nk, bias=None, residual_shard=None, bn=0):
         """Same sum, but each rank keeps only its contiguous shard of the rows (M must divide by the world size)."""

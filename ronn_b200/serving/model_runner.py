@@ -177,6 +177,12 @@ class DecoderRunner:
         comm = comm or self.comm
         if lw.packed is not None:
             from ..providers.bitnet import kernels as BK
+            if reduce and self.tp > 1 and getattr(comm, "fused", False) and ops.name == "kernels" and lw.bias is None:
+                # ternary GEMM into the symmetric partial slot + cross-rank reduction kernel over NVLink peer memory
+                from ..ops import bitnet as KB
+                q, s = KB.act_quant_int8(x)
+                ws = float(lw.scale.reshape(-1)[0]) if isinstance(lw.scale, torch.Tensor) else float(lw.scale)
+                return comm.bitlinear_allreduce(q, s, lw.packed, ws, lw.n, lw.k, x.dtype, residual)
             y = BK.bitlinear(x, lw, backend=ops.name)
             if reduce and self.tp > 1:
                 y = comm.all_reduce(y)

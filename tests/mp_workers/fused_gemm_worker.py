@@ -19,36 +19,58 @@ def main():
     comm = FusedComm(dev, max_rows=1024, max_cols=4096, wait_seconds=5.0)
     results = []
     torch.manual_seed(100 + rank)
-    for (M, N, Kl) in [(256, 1024, 128), (256, 1024, 512), (200, 264, 64), (1024, 1024, 256), (16, 4096, 64)]:
-        for it in range(3):                        # consecutive calls alternate the parity slots
-            a = torch.randn(M, Kl, device=dev).bfloat16()
-            w = (torch.randn(N, Kl, device=dev) * 0.05).bfloat16()
-            bias = torch.randn(N, device=dev).bfloat16()
+    for push in (False, True):                     # pull from the peers' buffers / push into every rank's slots
+        comm.push = push
+        tag = "/push" if push else ""
+        for (M, N, Kl) in [(256, 1024, 128), (256, 1024, 512), (200, 264, 64), (1024, 1024, 256), (16, 4096, 64)]:
+            for it in range(3):                        # consecutive calls alternate the parity slots
+                a = torch.randn(M, Kl, device=dev).bfloat16()
+                w = (torch.randn(N, Kl, device=dev) * 0.05).bfloat16()
+                bias = torch.randn(N, device=dev).bfloat16()
+                res = torch.randn(M, N, device=dev).bfloat16()
+                dist.broadcast(bias, 0)
+                dist.broadcast(res, 0)
+                y = comm.gemm_allreduce(a, w, bias, res)
+                part = (a.float() @ w.float().t()).bfloat16().float()
+                dist.all_reduce(part)
+                ref = part + bias.float() + res.float()
+                err = (y.float() - ref).abs().max().item()
+                # bit-identical on every rank
+                y0 = y.clone()
+                dist.broadcast(y0, 0)
+                results.append({"mode": "ar" + tag, "M": M, "N": N, "K": Kl, "err": err, "identical": bool(torch.equal(y0, y))})
+                if N <= 1024:
+                    gam, bet = torch.randn(N, device=dev).bfloat16(), torch.randn(N, device=dev).bfloat16()
+                    dist.broadcast(gam, 0)
+                    dist.broadcast(bet, 0)
+                    y2, hn = comm.gemm_allreduce(a, w, bias, res, norm=("layernorm", gam, bet, 1e-5))
+                    href = torch.nn.functional.layer_norm(y2.float(), (N,), gam.float(), bet.float(), 1e-5)
+                    results.append({"mode": "ar+ln" + tag, "M": M, "N": N, "K": Kl, "identical": bool(torch.equal(y2, y)),
+                                    "err": (hn.float() - href).abs().max().item() * 0.5})
+                if M % world == 0:
+                    per = M // world
+                    ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
+                    errs = (ys.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
+                    results.append({"mode": "rs" + tag, "M": M, "N": N, "K": Kl, "err": errs, "identical": True})
+    comm.push = False
+    # row-parallel BitLinear: ternary x int8 partials written into the symmetric slot, reduced over peer memory
+    from ronn_b200.ops import bitnet as KB
+    for (M, N, Kl) in [(128, 2560, 320), (37, 512, 256), (128, 1024, 864)]:
+        for it in range(2):
+            x = torch.randn(M, Kl, device=dev).bfloat16()
+            wq = torch.randint(-1, 2, (N, Kl), device=dev, dtype=torch.int8)
+            packed = KB.ternary_pack(wq)
             res = torch.randn(M, N, device=dev).bfloat16()
-            dist.broadcast(bias, 0)
             dist.broadcast(res, 0)
-            y = comm.gemm_allreduce(a, w, bias, res)
-            part = (a.float() @ w.float().t()).bfloat16().float()
+            q, sc = KB.act_quant_int8(x)
+            y = comm.bitlinear_allreduce(q, sc, packed, 0.05, N, Kl, torch.bfloat16, res)
+            part = KB.bitlinear_q(q, sc, packed, 0.05, None, N, Kl, torch.bfloat16).float()   # the same bf16 partial
             dist.all_reduce(part)
-            ref = part + bias.float() + res.float()
-            err = (y.float() - ref).abs().max().item()
-            # bit-identical on every rank
+            ref = part + res.float()
             y0 = y.clone()
             dist.broadcast(y0, 0)
-            results.append({"mode": "ar", "M": M, "N": N, "K": Kl, "err": err, "identical": bool(torch.equal(y0, y))})
-            if N <= 1024:
-                gam, bet = torch.randn(N, device=dev).bfloat16(), torch.randn(N, device=dev).bfloat16()
-                dist.broadcast(gam, 0)
-                dist.broadcast(bet, 0)
-                y2, hn = comm.gemm_allreduce(a, w, bias, res, norm=("layernorm", gam, bet, 1e-5))
-                href = torch.nn.functional.layer_norm(y2.float(), (N,), gam.float(), bet.float(), 1e-5)
-                results.append({"mode": "ar+ln", "M": M, "N": N, "K": Kl, "identical": bool(torch.equal(y2, y)),
-                                "err": (hn.float() - href).abs().max().item() * 0.5})
-            if M % world == 0:
-                per = M // world
-                ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
-                errs = (ys.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
-                results.append({"mode": "rs", "M": M, "N": N, "K": Kl, "err": errs, "identical": True})
+            results.append({"mode": "bitlinear+ar", "M": M, "N": N, "K": Kl, "err": (y.float() - ref).abs().max().item(),
+                            "identical": bool(torch.equal(y0, y))})
     # all-gather -> GEMM: shards live in symmetric memory and are read tile by tile through peer tensor maps
     for (rows, Kd, N) in [(128, 256, 384), (256, 1024, 512), (128, 64, 72)]:
         for it in range(2):

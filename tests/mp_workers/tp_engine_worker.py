@@ -23,7 +23,7 @@ def main():
         dev, dtype, backend = torch.device("cpu"), torch.float32, "torch"
     else:
         dev, dtype, backend = torch.device("cuda", local), torch.bfloat16, "kernels"
-    cfg = GPT2Config.tiny(n_layer=2, n_embd=256, n_head=4, vocab_size=1000, n_positions=256)
+    cfg = GPT2Config.tiny(n_layer=2, n_embd=512, n_head=8, vocab_size=1000, n_positions=256)      # 8 heads: shards up to TP=8
     model = Model.from_graph(build_gpt2(cfg, dtype=dtype, seed=7))
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 17, 40, 64, 9, 33)]

@@ -32,7 +32,7 @@ def test_fused_gemm_allreduce_and_reduce_scatter(tmp_path):
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 def test_tp_engine_matches_single_gpu(tmp_path, mode):
     out = tmp_path / "r.json"
-    p = launch(_world() if mode == "nccl" else min(_world(), 4), "tp_engine_worker.py", [mode, str(out)], 29660,
+    p = launch(_world(), "tp_engine_worker.py", [mode, str(out)], 29660,
                env={"NCCL_NVLS_ENABLE": "0"})
     assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-4000:])
     r = json.loads(out.read_text())
@@ -56,7 +56,7 @@ def test_peer_wait_runs_out_and_context_survives():
     stride = M * N * 2
     parts = [torch.zeros(2 * stride, dtype=torch.uint8, device=dev) for _ in range(2)]
     flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
-    state = torch.zeros(4, dtype=torch.int32, device=dev)
+    state = torch.zeros(8, dtype=torch.int32, device=dev)
     out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
     pp = (C.c_void_p * 8)(*[parts[0].data_ptr(), parts[1].data_ptr()] + [None] * 6)
     fp = (C.c_void_p * 8)(*[flags[0].data_ptr(), flags[1].data_ptr()] + [None] * 6)
@@ -71,5 +71,44 @@ def test_peer_wait_runs_out_and_context_survives():
     # rank 0 raised its own flags on both "ranks"; rank 1 never did
     assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1 and int(flags[0][1]) == 0
     y = K.gemm(a, w)                                # the context is alive and later kernels run
+    torch.testing.assert_close(y.float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
+    K.check_status(dev)
+
+
+def test_push_mode_wait_runs_out_and_context_survives():
+    """Push mode carries the call's sequence number inside the data words.  Words that never arrive (the second 'rank'
+    writes nothing) make the bounded poll give up with STATUS_WAIT_PEER; the context stays usable."""
+    import ctypes as C
+    from ronn_b200 import _native
+    from ronn_b200.api.errors import CommTimeoutError
+    from ronn_b200.ops import kernels as K
+    dev = torch.device("cuda", 0)
+    M, N, Kd = 128, 256, 64
+    a = torch.randn(M, Kd, device=dev).bfloat16()
+    w = torch.randn(N, Kd, device=dev).bfloat16()
+    stride = M * N * 2
+    parts = [torch.zeros(2 * stride, dtype=torch.uint8, device=dev) for _ in range(2)]
+    flags = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+    src_stride = M * N * 4
+    recv = [torch.zeros(2 * 2 * src_stride, dtype=torch.uint8, device=dev) for _ in range(2)]
+    state = torch.zeros(8, dtype=torch.int32, device=dev)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    pp = (C.c_void_p * 8)(*[parts[0].data_ptr(), parts[1].data_ptr()] + [None] * 6)
+    fp = (C.c_void_p * 8)(*[flags[0].data_ptr(), flags[1].data_ptr()] + [None] * 6)
+    rp = (C.c_void_p * 8)(*[recv[0].data_ptr(), recv[1].data_ptr()] + [None] * 6)
+    K.check_status(dev)
+    rc = _native.cuda().ronn_gemm_reduce_push(a.data_ptr(), w.data_ptr(), M, N, Kd, Kd, Kd, pp, fp, stride,
+                                              state.data_ptr(), 0, 2, 0, M, out.data_ptr(), N, None, None, 0, 0.3, 0, 0,
+                                              None, None, None, 0.0, 0, rp, 2 * src_stride, src_stride,
+                                              K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(CommTimeoutError, match="peer"):
+        K.check_status(dev)
+    # rank 0 delivered its words (data + sequence number 1) to both receive areas, slot [parity 0][source 0]
+    words = recv[1][:src_stride].view(torch.int32).view(-1, 2)
+    assert bool((words[:, 1] == 1).all())
+    assert bool((recv[0][src_stride:2 * src_stride] == 0).all())      # nothing ever came from 'rank 1'
+    y = K.gemm(a, w)
     torch.testing.assert_close(y.float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
     K.check_status(dev)
