@@ -75,7 +75,7 @@ class FusedComm(TPComm):
         self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
         self.fused_calls = 0
         self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
-        self.push = self.world > 1 and os.environ.get("RONN_TP_PUSH", "0") == "1"
+        self.push = self.world > 1 and os.environ.get("RONN_TP_PUSH", "1") != "0"
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
     def clone(self, max_rows: Optional[int] = None) -> "FusedComm":
