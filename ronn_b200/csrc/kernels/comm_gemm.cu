@@ -200,18 +200,20 @@ __device__ __forceinline__ void reduce_row_chunks(const CommArgs& comm, const ui
                                                   uint32_t seq, unsigned long long deadline, bool& alive,
                                                   uint32_t* status) {
   if (LL) {
+    // one polling round covers all G chunks: every load of the round is issued before the first check, so a row costs
+    // one local round trip when the data has already landed (the usual case: it arrived during the GEMM)
+    float acc[G][8];
+    uint32_t polls = 0;
+    bool ready;
+    do {
+      ready = true;
 #pragma unroll
-    for (int i = 0; i < G; ++i) {
-      const int c8 = lane + 32 * (I0 + i);
-      if (c8 < n8) {
-        const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * 4;
-        float acc[8];
-        uint32_t polls = 0;
-        bool ready;
-        do {
-          ready = true;
+      for (int i = 0; i < G; ++i) {
+        const int c8 = lane + 32 * (I0 + i);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+        if (c8 < n8) {
+          const size_t off = (size_t(comm.row_begin + r) * N + c8 * 8) * 4;
 #pragma unroll
           for (int src = 0; src < W; ++src)
             if (src < comm.world) {
@@ -226,15 +228,19 @@ __device__ __forceinline__ void reduce_row_chunks(const CommArgs& comm, const ui
               float f[8];
               unpack8<T>(t, f);
 #pragma unroll
-              for (int k = 0; k < 8; ++k) acc[k] += f[k];
+              for (int k = 0; k < 8; ++k) acc[i][k] += f[k];
             }
-          if (!ready && (++polls & 63u) == 0u && globaltimer_ns() > deadline) {
-            if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
-            alive = false;
-          }
-        } while (!ready && alive);
-        finish_chunk<T>(comm, acc, r, c8 * 8, out, bias, res, v[I0 + i], s1, s2);
+        }
       }
+      if (!ready && (++polls & 63u) == 0u && globaltimer_ns() > deadline) {
+        if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
+        alive = false;
+      }
+    } while (!ready && alive);
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const int c8 = lane + 32 * (I0 + i);
+      if (c8 < n8) finish_chunk<T>(comm, acc[i], r, c8 * 8, out, bias, res, v[I0 + i], s1, s2);
     }
   } else {
     Vec8 pk[G][W];                              // W: compile-time bound of the world size (registers)
@@ -341,7 +347,12 @@ __device__ __forceinline__ void cross_rank_phase(const CommArgs& comm, int M, in
         // Peer loads cost an NVLink round trip each: every load of a group of chunks (all ranks) is issued before the
         // first one is used, so a row pays one or two round trips instead of one per chunk.
         if (PUSH) {
-          reduce_row_chunks<T, 0, 4, W, true>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+          if (W <= 4) {
+            reduce_row_chunks<T, 0, 4, W, true>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+          } else {
+            reduce_row_chunks<T, 0, 2, W, true>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+            reduce_row_chunks<T, 2, 2, W, true>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
+          }
         } else if (W <= 4) {
           reduce_row_chunks<T, 0, 4, W, false>(comm, src_base, r, lane, n8, N, out, bias, res, v, s1, s2, seq, deadline, alive, status);
         } else {
@@ -663,6 +674,89 @@ extern "C" int ronn_peer_reduce(int M, int N, void* const* peer_part, int* const
     if (world <= 2) RONN_PR(__half, 2); else if (world <= 4) RONN_PR(__half, 4); else RONN_PR(__half, 8);
   }
 #undef RONN_PR
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+// Greedy token over vocabulary shards without a library collective: every rank stores its (max, index) pair of each row
+// into every rank's exchange slot as two 8-byte words {max, sequence} {index, sequence}, then polls its own slots until
+// the words of all ranks carry this call's sequence number and keeps the largest value (lowest index on ties), so all
+// ranks pick the same token.  state: two zero-initialised ints in local memory ([0] calls completed, [1] block counter).
+// Slot layout per rank: [2 parities][world sources][max_rows] records of 16 bytes.
+struct ArgmaxExchangeArgs {
+  uint8_t* peer_slots[MAX_RANKS];
+  int* state;
+  int rank, world, rows, max_rows;
+  unsigned long long wait_ns;
+};
+
+__global__ void __launch_bounds__(256)
+argmax_exchange_kernel(const __grid_constant__ ArgmaxExchangeArgs a, const int* __restrict__ idx,
+                       const float* __restrict__ mx, int* __restrict__ tokens, uint32_t* status) {
+  pdl_wait();
+  pdl_trigger();
+  const int total = *reinterpret_cast<volatile int*>(a.state);
+  const uint32_t seq = uint32_t(total) + 1u;
+  const size_t parity_off = size_t(total & 1) * a.world * a.max_rows * 16;
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < a.rows) {
+    const uint32_t vbits = __float_as_uint(mx[b]);
+    const uint32_t ibits = uint32_t(idx[b]);
+    const size_t mine = parity_off + (size_t(a.rank) * a.max_rows + b) * 16;
+    for (int p = 0; p < a.world; ++p) st_volatile_16(a.peer_slots[p] + mine, vbits, seq, ibits, seq);
+    const unsigned long long deadline = globaltimer_ns() + a.wait_ns;
+    float best = -INFINITY;
+    int best_idx = 0x7fffffff;
+    bool alive = true;
+    for (int src = 0; src < a.world && alive; ++src) {
+      const uint8_t* slot = a.peer_slots[a.rank] + parity_off + (size_t(src) * a.max_rows + b) * 16;
+      uint4 w = ld_volatile_u4(slot);
+      uint32_t polls = 0;
+      while (w.y != seq || w.w != seq) {
+        if ((++polls & 63u) == 0u && globaltimer_ns() > deadline) {
+          if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
+          alive = false;
+          break;
+        }
+        w = ld_volatile_u4(slot);
+      }
+      const float v = __uint_as_float(w.x);
+      const int i = int(w.z);
+      if (alive && (v > best || (v == best && i < best_idx))) {
+        best = v;
+        best_idx = i;
+      }
+    }
+    tokens[b] = alive ? best_idx : 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(a.state + 1, 1);
+    if (done == int(gridDim.x) - 1) {
+      a.state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile int*>(a.state) = total + 1;
+    }
+  }
+}
+
+// idx / mx: this rank's best index (global vocabulary index) and value per row; tokens: int32 [rows] result, the same
+// on every rank.  peer_slots: `world` pointers to the ranks' exchange areas (2 * world * max_rows * 16 bytes each).
+extern "C" int ronn_argmax_exchange(const int* idx, const float* mx, int* tokens, int rows, void* const* peer_slots,
+                                    int max_rows, int* state, int rank, int world, double wait_seconds, uint32_t* status,
+                                    cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (rows > max_rows || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
+  const int blocks = (rows + 255) / 256;
+  if (blocks > comm_sm_count()) return -2;       // every block resident at once (they wait on the peers)
+  ArgmaxExchangeArgs a;
+  for (int p = 0; p < MAX_RANKS; ++p) a.peer_slots[p] = p < world ? static_cast<uint8_t*>(peer_slots[p]) : nullptr;
+  a.state = state;
+  a.rank = rank;
+  a.world = world;
+  a.rows = rows;
+  a.max_rows = max_rows;
+  a.wait_ns = static_cast<unsigned long long>(wait_seconds * 1e9);
+  cudaError_t err = launch(argmax_exchange_kernel, dim3(blocks), dim3(256), 0, stream, a, idx, mx, tokens, status);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 

@@ -19,6 +19,7 @@ def declare(lib):
     sig("ronn_gemm_splitk", [V, V, V, I, I, I, I, I, I, I, I, V, V, V])
     sig("ronn_splitk_finalize", [V, I, V, V, V, V, V, V, L, I, F, I, I, I, V])
     sig("ronn_gemm_reduce", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I, V, V], optional=True)
+    sig("ronn_argmax_exchange", [V, V, V, I, V, I, V, I, I, C.c_double, V, V], optional=True)
     sig("ronn_peer_reduce", [I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, V, V, V, F, I, V, V], optional=True)
     sig("ronn_bitlinear_to_slot", [V, V, V, F, V, V, L, I, I, I, I, I, V, V], optional=True)
     sig("ronn_gemm_reduce_push", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I,

@@ -50,7 +50,10 @@ class FusedComm(TPComm):
         self.recv_src_stride = self.push_elems * 4
         self.recv_parity_stride = self.recv_src_stride * self.world
         recv_bytes = 2 * self.recv_parity_stride
-        total = 2 * self.part_stride + flag_bytes + self.shard_bytes + recv_bytes
+        # exchange area of the sharded argmax: [2 parities][world sources][max_argmax_rows] records of 16 bytes
+        self.max_argmax_rows = 4096
+        argmax_bytes = 2 * self.world * self.max_argmax_rows * 16
+        total = 2 * self.part_stride + flag_bytes + self.shard_bytes + recv_bytes + argmax_bytes
         self._buf = symm.empty(total, dtype=torch.uint8, device=self.device)
         self._buf.zero_()
         torch.cuda.synchronize(self.device)
@@ -69,12 +72,17 @@ class FusedComm(TPComm):
         recv_off = shard_off + self.shard_bytes
         self._recv_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + recv_off) if p < self.world else None
                                                     for p in range(MAX_RANKS)])
+        argmax_off = recv_off + recv_bytes
+        self._argmax_ptrs = (C.c_void_p * MAX_RANKS)(*[(ptrs[p] + argmax_off) if p < self.world else None
+                                                      for p in range(MAX_RANKS)])
+        self._argmax_state = torch.zeros(2, dtype=torch.int32, device=self.device)
         self._ag_flags_local = ptrs[self.rank] + 2 * self.part_stride + 256
         self._ag_state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._state = torch.zeros(8, dtype=torch.int32, device=self.device)
         self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
         self.fused_calls = 0
         self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
+        self.argmax_exchange = self.world > 1 and os.environ.get("RONN_ARGMAX_EXCHANGE", "1") != "0"
         self.push = self.world > 1 and os.environ.get("RONN_TP_PUSH", "1") != "0"
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
@@ -147,6 +155,26 @@ class FusedComm(TPComm):
                 normed, total = K.rmsnorm(y, gamma, eps, residual=residual, return_sum=True)
             return total, normed
         return self._gemm_reduce(a, w_nk, bias, residual, 0, a.shape[0], bn, norm)
+
+    def argmax_combine(self, idx: torch.Tensor, mx: torch.Tensor) -> torch.Tensor:
+        """Greedy token per row over the vocabulary shards: every rank's (index, max) pairs are exchanged through
+        symmetric memory by one small kernel (sequence-numbered words, no library collective); largest value wins,
+        lowest index on ties, the same on every rank."""
+        rows = idx.shape[0]
+        if not self.argmax_exchange or rows > self.max_argmax_rows:
+            vals = self.all_gather_small(mx)
+            idxs = self.all_gather_small(idx)
+            return K.argmax_combine(vals.contiguous(), idxs.contiguous())
+        idx = idx.contiguous()
+        mx = mx.float().contiguous()
+        tokens = torch.empty(rows, dtype=torch.int32, device=idx.device)
+        rc = _native.cuda().ronn_argmax_exchange(idx.data_ptr(), mx.data_ptr(), tokens.data_ptr(), rows, self._argmax_ptrs,
+                                                 self.max_argmax_rows, self._argmax_state.data_ptr(), self.rank,
+                                                 self.world, self.wait_seconds, K.status_word(idx.device).data_ptr(),
+                                                 torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"argmax_exchange failed with code {rc}")
+        return tokens
 
     # ------------------------------------------------------------------ BitLinear partials + cross-rank reduction
     def bitlinear_allreduce(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual=None):

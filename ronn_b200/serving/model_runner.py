@@ -305,6 +305,8 @@ class DecoderRunner:
     def combine_argmax(self, idx, mx, comm=None):
         """Greedy token over the vocabulary shards: gather every rank's (index, max) and keep the largest value."""
         comm = comm or self.comm
+        if hasattr(comm, "argmax_combine") and self.ops.name == "kernels":
+            return comm.argmax_combine(idx, mx)           # exchange + combine in one kernel over peer memory
         vals = comm.all_gather_small(mx)
         idxs = comm.all_gather_small(idx)
         return self.ops.argmax_combine(vals.contiguous(), idxs.contiguous())

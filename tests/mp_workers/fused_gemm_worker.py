@@ -71,6 +71,17 @@ def main():
             dist.broadcast(y0, 0)
             results.append({"mode": "bitlinear+ar", "M": M, "N": N, "K": Kl, "err": (y.float() - ref).abs().max().item(),
                             "identical": bool(torch.equal(y0, y))})
+    # sharded greedy sampling: (index, max) pairs exchanged through sequence-numbered words, against the gathered form
+    from ronn_b200.ops import kernels as KK
+    for rows in (300, 7, 1024):
+        for it in range(3):
+            mx = torch.randn(rows, device=dev)
+            mx[::5] = 0.25                                   # ties across ranks: the lowest index must win everywhere
+            idx = torch.randint(0, 50000, (rows,), device=dev, dtype=torch.int32)
+            tok = comm.argmax_combine(idx, mx)
+            ref = KK.argmax_combine(comm.all_gather_small(mx).contiguous(), comm.all_gather_small(idx).contiguous())
+            results.append({"mode": "argmax", "M": rows, "N": 0, "K": 0, "err": float((tok != ref).sum().item()),
+                            "identical": bool(torch.equal(tok, ref))})
     # all-gather -> GEMM: shards live in symmetric memory and are read tile by tile through peer tensor maps
     for (rows, Kd, N) in [(128, 256, 384), (256, 1024, 512), (128, 64, 72)]:
         for it in range(2):
