@@ -58,3 +58,32 @@ def test_rank_that_never_joins_is_reported_not_hung(tmp_path):
     out0, _ = procs[0].communicate(timeout=120)
     procs[1].wait(timeout=30)
     assert "DETECTED" in out0 and "UNEXPECTED" not in out0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_tp_encoder_on_cpu_ranks_matches_single_rank(tmp_path, world):
+    out = tmp_path / "e.json"
+    p = launch(world, "tp_encoder_worker.py", [str(out)], 29640 + world)
+    assert p.returncode == 0, p.stderr[-3000:]
+    r = json.loads(out.read_text())
+    assert r["world"] == world and r["same_across_ranks"]
+    assert r["err"] < 1e-4
+
+
+def test_space_to_depth_stem_weights_reproduce_the_7x7_stride2_convolution():
+    import torch
+    import torch.nn.functional as F
+    from ronn_b200.providers.gpu_conv import stem_weights_s2d
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 16, 20)
+    w = torch.randn(8, 7, 7, 3)
+    ref = F.conv2d(x, w.permute(0, 3, 1, 2), stride=2, padding=3)
+    n, c, h, wd = x.shape
+    x2 = torch.zeros(n, h // 2, wd // 2, 16)
+    for dy in range(2):
+        for dx in range(2):
+            q = dy * 2 + dx
+            x2[..., q * c:(q + 1) * c] = x[:, :, dy::2, dx::2].permute(0, 2, 3, 1)
+    w2 = stem_weights_s2d(w)
+    out = F.conv2d(F.pad(x2.permute(0, 3, 1, 2), (2, 1, 2, 1)), w2.permute(0, 3, 1, 2))
+    torch.testing.assert_close(out, ref, atol=1e-4, rtol=1e-4)
