@@ -129,7 +129,7 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < BL_STAGES; ++s) {
-      mbar_init(&full[s], 128 + 1);          // 128 expander threads + the activation TMA's expect_tx arrival
+      mbar_init(&full[s], 4 + 1);            // one arrival per expander warp + the activation TMA's expect_tx arrival
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
@@ -151,25 +151,45 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
     // -------------------------------------------------- weight expansion: (row, chunk) pairs striped over 128 threads
     // weights are constants: no dependency wait needed before reading them
     constexpr int TASKS = BN * 8 / 128;      // 16-byte output chunks per thread per stage
+    // The packed words of K block kb + 2 are requested before block kb is expanded, so the global-load latency of
+    // a stage is covered by two stages of expansion; barrier traffic is one wait and one arrival per warp.
+    auto fetch = [&](uint32_t (&dst)[TASKS], int kb) {
+#pragma unroll
+      for (int t = 0; t < TASKS; ++t) {
+        const int task = threadIdx.x + t * 128;
+        const int r = task >> 3, j = task & 7;
+        const int n = n0 + r;
+        const int byte0 = kb * 32 + j * 4;
+        dst[t] = 0x55555555u;                // all-zero weights outside the matrix
+        if (kb < num_kb && n < N && byte0 < kbytes)
+          dst[t] = __ldg(reinterpret_cast<const uint32_t*>(w_packed + size_t(n) * kbytes + byte0));
+      }
+    };
+    uint32_t p0[TASKS], p1[TASKS], p2[TASKS];
+    fetch(p0, 0);
+    fetch(p1, 1);
     bool ok = true;
     for (int kb = 0; kb < num_kb; ++kb) {
       const int s = kb % BL_STAGES;
-      if (ok && !mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+      fetch(p2, kb + 2);
+      if (lane == 0 && ok && !mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (ok) {
         uint8_t* sb = tiles + s * L::STAGE_BYTES + L::A_BYTES;
 #pragma unroll
         for (int t = 0; t < TASKS; ++t) {
           const int task = threadIdx.x + t * 128;
           const int r = task >> 3, j = task & 7;
-          const int n = n0 + r;
-          const int byte0 = kb * 32 + j * 4;
-          uint32_t p = 0x55555555u;          // all-zero weights outside the matrix
-          if (n < N && byte0 < kbytes) p = __ldg(reinterpret_cast<const uint32_t*>(w_packed + size_t(n) * kbytes + byte0));
-          *reinterpret_cast<int4*>(sb + r * 128 + ((uint32_t(j) ^ uint32_t(r & 7)) << 4)) = expand16(p);
+          *reinterpret_cast<int4*>(sb + r * 128 + ((uint32_t(j) ^ uint32_t(r & 7)) << 4)) = expand16(p0[t]);
         }
-        fence_proxy_async_smem();            // generic-proxy stores -> visible to the tensor-core (async) proxy
       }
-      mbar_arrive(&full[s]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[s]);
+#pragma unroll
+      for (int t = 0; t < TASKS; ++t) {
+        p0[t] = p1[t];
+        p1[t] = p2[t];
+      }
     }
     // -------------------------------------------------- epilogue
     pdl_wait();
@@ -234,6 +254,9 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % BL_STAGES;
         if (!mbar_wait(&full[s], (kb / BL_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
+        // the expander warps wrote the weight tile through the generic proxy and released it with their arrivals: one
+        // proxy fence after the acquire orders those writes before the tensor core's reads
+        fence_proxy_async_smem();
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
         const uint64_t adesc = umma_desc_k128(sa), bdesc = umma_desc_k128(sa + L::A_BYTES);

@@ -22,7 +22,9 @@ struct DenseEpilogue {
     const int gm = m0 + row;
     const int gn = n0 + col;
     if (gn >= N) return;                         // uniform across the warp
-    const bool staged = stage != nullptr && !out_fp32 && (gn + 32 <= N) && ((ldc & 7) == 0);
+    // re-shaping the stores through shared memory pays for bandwidth-bound results; a decode-sized GEMM (a few row
+    // tiles) is a latency chain and keeps the direct stores
+    const bool staged = stage != nullptr && M >= 1024 && !out_fp32 && (gn + 32 <= N) && ((ldc & 7) == 0);
     if (gm >= M && !staged) return;
     if (gm >= M) {                               // staged path: rows past the end only take part in the exchange
       __syncwarp();
