@@ -1,5 +1,10 @@
 """HRM routing between a BitNet session and a full-precision session, multi-tier memory and continual learning.
 Counterpart of the reference's examples/brain-features."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))      # run from a source checkout
+
 import torch
 
 from ronn_b200 import Model

@@ -1,5 +1,10 @@
 """Throughput of the hand-written GEMM against the library GEMM (counterpart of the reference's examples/compare_perf,
 which prints GFLOPS of 64/256/512 matmuls)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))      # run from a source checkout
+
 import time
 
 import torch

@@ -1,4 +1,9 @@
 """Continuous batching over a paged KV cache: many requests of different lengths through one engine."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))      # run from a source checkout
+
 import torch
 
 from ronn_b200 import Model

@@ -1,5 +1,10 @@
 """Load (or build) an ONNX model, create sessions at two optimisation levels and run them.
 Counterpart of the reference's examples/simple-inference and examples/onnx-model."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))      # run from a source checkout
+
 import sys
 
 import torch
