@@ -261,9 +261,17 @@ def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20
     flops = 2.0 * m * n * k
     byts = 2.0 * (m * k + n * k + m * n)
     t_roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e6
-    return {"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn, "us": round(us, 2),
-            "tflops": round(flops / us / 1e6, 1), "gbs": round(byts / us / 1e3, 1),
-            "roofline_us": round(t_roof, 2), "frac_of_" + src: round(t_roof / us, 3)}
+    res = {"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn, "us": round(us, 2),
+           "tflops": round(flops / us / 1e6, 1), "gbs": round(byts / us / 1e3, 1),
+           "roofline_us": round(t_roof, 2), "frac_of_" + src: round(t_roof / us, 3)}
+    if m <= 1024:
+        # a single launch of a few microseconds is dominated by the host's launch latency (the GPU idles between the
+        # start event and the kernel): also report back-to-back launches replayed from a CUDA graph, weights rotating
+        # through more than L2
+        nvar = max(2, int(300e6 // (n * k * 2)))
+        ws = [w] + [(torch.randn(n, k, device="cuda") * 0.05).to(dtype) for _ in range(nvar - 1)]
+        res["graph_us"] = round(time_graph(lambda i: K.gemm(a, ws[i], activation=act, out=out, bn=bn), nvar), 2)
+    return res
 
 
 def bench_attention(batch, ctx, heads, dim, kv_heads=None, dtype=torch.bfloat16, flush=True, iters=20):
