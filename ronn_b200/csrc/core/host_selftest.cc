@@ -54,18 +54,19 @@ static int test_scheduler(int policy, int prefix_cache, int chunk) {
   int added = 0;
   for (int64_t id = 0; id < 25; ++id) {
     const int plen = 1 + int(rnd(70)), newt = 1 + int(rnd(20));
-    std::vector<int32_t> prompt(size_t(plen), 0);
+    std::vector<int32_t> prompt(static_cast<size_t>(plen), 0);
     for (int i = 0; i < plen; ++i) prompt[size_t(i)] = int32_t(rnd(4));     // few distinct tokens: prefix hits happen
     if (ronn_sched_add(s, id, prompt.data(), plen, newt, int32_t(rnd(4))) == 0) ++added;
   }
   CHECK(ronn_sched_add(s, 3, nullptr, 0, 1, 0) != 0);                      // duplicate / empty rejected
-  std::vector<int64_t> ids(size_t(max_seqs));
-  std::vector<int32_t> q_start(size_t(max_seqs)), seq_lens(size_t(max_seqs)), sample(size_t(max_seqs)), fin(size_t(max_seqs));
-  std::vector<int32_t> tok(size_t(max_tokens)), pos(size_t(max_tokens)), slot(size_t(max_tokens)), item(size_t(max_tokens));
-  std::vector<int32_t> bt(size_t(max_seqs) * size_t(max_blocks)), sampled(size_t(max_seqs), 1);
+  const size_t ns = size_t(max_seqs), nt = size_t(max_tokens);
+  std::vector<int64_t> ids(ns, 0);
+  std::vector<int32_t> q_start(ns + 1, 0), seq_lens(ns, 0), sample(ns, 0), fin(ns, 0);      // q_start: one past the last item
+  std::vector<int32_t> tok(nt, 0), pos(nt, 0), slot(nt, 0), item(nt, 0);
+  std::vector<int32_t> bt(ns * size_t(max_blocks), 0), sampled(ns, 1);
   int finished = 0, cancelled = 0;
+  if (ronn_sched_cancel(s, 1) == 0) cancelled = 1;                        // still waiting: leaves the queue for good
   for (int step = 0; step < 5000; ++step) {
-    if (step == 7 && ronn_sched_cancel(s, 1) == 0) ++cancelled;
     const int kind = ronn_sched_schedule(s);
     if (kind == 0) break;
     const int n_items = ronn_sched_plan_size(s);
@@ -118,7 +119,7 @@ static int test_graph() {
     int32_t outs[1] = {i + 1};
     CHECK(ronn_graph_add_node(g, ins, 2, outs, 1) == i);
   }
-  std::vector<int32_t> order(size_t(n));
+  std::vector<int32_t> order(static_cast<size_t>(n), 0);
   CHECK(ronn_graph_toposort(g, order.data()) == n);
   for (int i = 0; i < n; ++i) CHECK(order[size_t(i)] == i);
   CHECK(ronn_graph_depth(g) == n);

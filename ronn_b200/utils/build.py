@@ -125,6 +125,31 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
     return CUDA_LIB
 
 
+def build_host_selftest(sanitize: str = "address,undefined") -> Path:
+    """The host runtime (scheduler, block manager, pooled allocator, graph algorithms, model codec) linked with
+    ``csrc/core/host_selftest.cc`` into an executable built with ``-fsanitize=<sanitize>``; running it on a CPU box
+    checks the C++ code for out-of-bounds accesses, leaks and undefined behaviour."""
+    srcs = [CSRC / s for s in HOST_SOURCES] + [CSRC / "core" / "host_selftest.cc"]
+    exe = LIBDIR / ("host_selftest_" + sanitize.replace(",", "_"))
+    if exe.exists() and not _newer(exe, srcs):
+        return exe
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    # not every g++ of a box ships the sanitizer runtimes: try the configured compiler, then the system ones
+    tried, last = [], None
+    for cxx in (os.environ.get("CXX"), shutil.which("g++"), "/usr/bin/g++"):
+        if not cxx or cxx in tried:
+            continue
+        tried.append(cxx)
+        cmd = [cxx, "-O1", "-g", "-std=c++17", "-fno-omit-frame-pointer", f"-fsanitize={sanitize}", "-Wall",
+               "-Wno-unused-function", "-Wno-stringop-overflow", "-pthread", "-o", str(exe)] + [str(s) for s in srcs]
+        try:
+            _run(cmd, "sanitized host self-test build")
+            return exe
+        except BuildError as e:
+            last = e
+    raise BuildError(f"no compiler with the '{sanitize}' sanitizer runtime found (tried {tried}): {last}")
+
+
 def build_all(force: bool = False, verbose: bool = False):
     return build_host(force, verbose), build_cuda(force, verbose)
 
