@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import math
 import threading
+import os
 import time
 from contextlib import contextmanager
 from dataclasses import dataclass, field
@@ -127,11 +128,16 @@ class Profiler:
         if device is not None and getattr(device, "type", "cpu") == "cuda":
             import torch
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            nvtx = os.environ.get("RONN_NVTX", "0") == "1"       # named ranges for external timeline tools
+            if nvtx:
+                torch.cuda.nvtx.range_push(f"{category}:{name}")
             e0.record()
             try:
                 yield
             finally:
                 e1.record()
+                if nvtx:
+                    torch.cuda.nvtx.range_pop()
                 with self._lock:
                     self._pending.append((name, category, start, e0, e1, {k: str(v) for k, v in metadata.items()}))
         else:
