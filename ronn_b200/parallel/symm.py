@@ -83,7 +83,11 @@ class FusedComm(TPComm):
         self.fused_calls = 0
         self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
         self.argmax_exchange = self.world > 1 and os.environ.get("RONN_ARGMAX_EXCHANGE", "1") != "0"
-        self.push = self.world > 1 and os.environ.get("RONN_TP_PUSH", "1") != "0"
+        # Push pays when there is one peer (measured, GPT-2 medium decode: TP=2 85-88K tokens/s against 80K with the pull
+        # protocol).  With more peers every rank stores world copies of its partials as 16-byte NVLink writes at twice
+        # the data volume, and the pull protocol wins (TP=4 103K against 92K, TP=8 102K against 71K).
+        env = os.environ.get("RONN_TP_PUSH")
+        self.push = self.world > 1 and (env == "1" if env is not None else self.world == 2)
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
     def clone(self, max_rows: Optional[int] = None) -> "FusedComm":
