@@ -84,6 +84,7 @@ __device__ __forceinline__ uint4 ld_volatile_u4(const void* p) {
 
 template <int BN, class T, bool PUSH>
 struct PartialProblem {
+  static constexpr bool kForceStage = true;      // the push epilogue re-shapes its stores through the stage
   const CUtensorMap* map_a;
   const CUtensorMap* map_b;
   const CommArgs* comm;
@@ -489,7 +490,7 @@ static int comm_sm_count() {
 template <int BN, int STAGES, class T, int W, bool PUSH>
 static int launch_reduce_w(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
                            int is_bf16, uint32_t* status, cudaStream_t stream) {
-  using L = PGemmSmem<BN, STAGES>;
+  using L = PGemmSmem<BN, STAGES, true>;
   auto kern = gemm_reduce_kernel<BN, STAGES, T, W, PUSH>;
   static bool configured = false;
   if (!configured) {
@@ -786,6 +787,7 @@ struct GatherArgs {
 
 template <int BN, class T>
 struct GatherProblem {
+  static constexpr bool kForceStage = true;
   const GatherArgs* g;
   const CUtensorMap* map_b;
   DenseEpilogue e;
@@ -871,7 +873,7 @@ __global__ void signal_peers_kernel2(PeerFlagPtrs ptrs, int world, int rank) {
 template <int BN, int STAGES, class T>
 static int launch_ag(const GatherArgs& g, const CUtensorMap& mb, DenseEpilogue e, int M, int N, int K, int is_bf16,
                      uint32_t* status, cudaStream_t stream) {
-  using L = PGemmSmem<BN, STAGES>;
+  using L = PGemmSmem<BN, STAGES, true>;
   auto kern = ag_gemm_kernel<BN, STAGES, T>;
   static bool configured = false;
   if (!configured) {

@@ -19,6 +19,7 @@ namespace ronn {
 // M index fastest so that CTAs running side by side share the same weight tile in L2.
 template <int BN, class T>
 struct DenseProblem {
+  static constexpr bool kForceStage = false;
   const CUtensorMap* map_a;
   const CUtensorMap* map_b;
   DenseEpilogue e;
@@ -87,7 +88,7 @@ static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilo
     configured = true;
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM) * splitk;
-  const int resident = sm_count() * (L::DYN_SMEM <= 110 * 1024 && L::TMEM_COLS <= 256 ? 2 : 1);
+  const int resident = sm_count() * (L::DYN_SMEM <= 112 * 1024 && L::TMEM_COLS <= 256 ? 2 : 1);
   dim3 grid(tiles < resident ? tiles : resident);
   uint32_t idesc = umma_idesc(PG_BM, BN, is_bf16 ? 1u : 0u, 1u);
   cudaError_t err = launch(kern, grid, dim3(PG_THREADS), size_t(L::DYN_SMEM), stream, ma, mb, epi, K, splitk, idesc, status);

@@ -18,8 +18,9 @@
 //   void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const     k-block range of the tile
 //   void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const
 //   void load_b(uint8_t* smem, uint64_t* bar, int k_elem, int n0) const
+//   static constexpr bool kForceStage                                 true: `stage` below is never null
 //   void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&acc)[32], uint8_t* stage)   row/col within the
-//        tile; stage: 32 x 80 bytes of shared memory owned by the calling warp (to re-shape its stores)
+//        tile; stage: 32 x 80 bytes of shared memory owned by the calling warp (to re-shape its stores), or null
 #pragma once
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -27,9 +28,12 @@
 namespace ronn {
 
 constexpr int PG_BM = 128;
-constexpr int PG_THREADS = 192;
+constexpr int PG_EPI_WARPS = 8;                  // two warps per TMEM lane quarter, each drains half of the columns
+constexpr int PG_THREADS = 64 + 32 * PG_EPI_WARPS;
 
-template <int BN, int STAGES>
+// FORCE_STAGE: always reserve the per-warp store-staging area (kernels whose epilogue depends on it); otherwise only
+// the deep-ring variants (one CTA per SM) carry it, so the shallow ones still fit two CTAs per SM.
+template <int BN, int STAGES, bool FORCE_STAGE = false>
 struct PGemmSmem {
   static constexpr int A_BYTES = PG_BM * 128;
   static constexpr int B_BYTES = BN * 128;
@@ -37,7 +41,8 @@ struct PGemmSmem {
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;          // full, empty, acc_full[2], acc_empty[2]
   static constexpr int OUT_STAGE_ROW = 80;                 // 64 bytes of a row + padding against bank conflicts
-  static constexpr int OUT_STAGE_BYTES = 4 * 32 * OUT_STAGE_ROW;   // per epilogue warp: 32 rows of one 32-column chunk
+  static constexpr int OUT_STAGE_BYTES =
+      (FORCE_STAGE || STAGES * (PG_BM * 128 + BN * 128) > 100 * 1024) ? PG_EPI_WARPS * 32 * OUT_STAGE_ROW : 0;   // per epilogue warp
   static constexpr int TOTAL = TILE_BYTES + NUM_BARS * 8 + 16 + OUT_STAGE_BYTES;
   static constexpr int DYN_SMEM = TOTAL + 1024;            // slack for manual 1024-byte alignment
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32u : (2 * BN <= 64 ? 64u : (2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u)));
@@ -47,7 +52,7 @@ struct PGemmSmem {
 template <int BN, int STAGES, int KIND, class Problem>
 __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob, int k_elems, uint32_t idesc,
                                                 uint32_t* status) {
-  using L = PGemmSmem<BN, STAGES>;
+  using L = PGemmSmem<BN, STAGES, Problem::kForceStage>;
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::TILE_BYTES);
   uint64_t* empty = full + STAGES;
@@ -66,7 +71,7 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);               // one arrival per epilogue warp
+      mbar_init(&acc_empty[b], PG_EPI_WARPS);    // one arrival per epilogue warp
     }
     *abort = 0;
     mbar_fence_init();
@@ -154,7 +159,8 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
     pdl_trigger();
   } else {
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    uint8_t* stage_w = out_stage + q * (32 * L::OUT_STAGE_ROW);
+    const int half = (warp - 2) >> 2;            // which half of the columns this warp drains
+    uint8_t* stage_w = L::OUT_STAGE_BYTES ? out_stage + (warp - 2) * (32 * L::OUT_STAGE_ROW) : nullptr;
     pdl_wait();                                  // the epilogue reads residuals and writes buffers the predecessor may use
     uint32_t j = 0;
     for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
@@ -171,30 +177,44 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
       // TMEM loads are long-latency: the load of the next 32 columns is in flight while this chunk is converted and
       // stored.  The accumulator buffer is handed back as soon as its last load has landed.
       if (BN == 32) {
-        uint32_t r0[32];
-        tmem_ld_32x32(tacc, r0);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        prob.epilogue(t, m0, n0, row, 0, r0, stage_w);
+        if (half == 0) {
+          uint32_t r0[32];
+          tmem_ld_32x32(tacc, r0);
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          prob.epilogue(t, m0, n0, row, 0, r0, stage_w);
+        } else {
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
       } else {
+        constexpr int HALF = BN / 2;
+        const int c0 = half * HALF;
         uint32_t r0[32], r1[32];
-        tmem_ld_32x32(tacc, r0);
+        tmem_ld_32x32(tacc + uint32_t(c0), r0);
+        if (HALF == 32) {
+          tmem_ld_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          prob.epilogue(t, m0, n0, row, c0, r0, stage_w);
+        } else {
 #pragma unroll 1
-        for (int col = 0; col < BN; col += 64) {
-          tmem_ld_wait();                                    // r0 = columns [col, col + 32)
-          tmem_ld_32x32(tacc + uint32_t(col + 32), r1);
-          prob.epilogue(t, m0, n0, row, col, r0, stage_w);
-          tmem_ld_wait();                                    // r1 = columns [col + 32, col + 64)
-          if (col + 64 < BN) {
-            tmem_ld_32x32(tacc + uint32_t(col + 64), r0);
-          } else {
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          for (int col = c0; col < c0 + HALF; col += 64) {
+            tmem_ld_wait();
+            tmem_ld_32x32(tacc + uint32_t(col + 32), r1);
+            prob.epilogue(t, m0, n0, row, col, r0, stage_w);
+            tmem_ld_wait();
+            if (col + 64 < c0 + HALF) {
+              tmem_ld_32x32(tacc + uint32_t(col + 64), r0);
+            } else {
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            }
+            prob.epilogue(t, m0, n0, row, col + 32, r1, stage_w);
           }
-          prob.epilogue(t, m0, n0, row, col + 32, r1, stage_w);
         }
       }
     }
