@@ -7,8 +7,10 @@
 //   warp 0     TMA producer       waits empty[s]      -> expect_tx + A/B loads into stage s
 //   warp 1     UMMA issuer        waits acc_empty[b], full[s] -> tcgen05.mma into buffer b,
 //                                 tcgen05.commit -> empty[s]; after the tile: commit -> acc_full[b]
-//   warps 2-5  epilogue           waits acc_full[b]   -> tcgen05.ld 32-column chunks -> functor,
-//                                 then one arrival per warp on acc_empty[b]
+//   warps 2-9  epilogue           waits acc_full[b]   -> tcgen05.ld 32-column chunks -> functor,
+//                                 then one arrival per warp on acc_empty[b].  Warp w reads TMEM lane quarter
+//                                 w % 4; the two warps of a quarter drain one half of the columns each (with four
+//                                 epilogue warps the epilogue of a 128 x 256 tile was as long as a 12-block main loop)
 //
 // Because every CTA of the grid is resident at once (grid <= SMs x CTAs/SM), a caller may add a
 // grid-wide or cross-GPU phase after the tile loop without risking a scheduling deadlock.
