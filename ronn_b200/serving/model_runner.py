@@ -203,6 +203,17 @@ class DecoderRunner:
             return y
         return ops.gemm(x, lw.w, lw.bias, residual, activation)
 
+    def _norm_linear(self, x, norm_p, lw: LinearW):
+        """norm(x) followed by a column-parallel projection.  For packed ternary weights on the kernel backend the
+        RMSNorm and the per-token int8 quantisation run as ONE kernel that feeds the ternary GEMM directly."""
+        if (lw.packed is not None and self.ops.name == "kernels" and self.arch.norm == "rmsnorm" and lw.bias is None
+                and x.is_cuda):
+            from ..ops import bitnet as KB
+            q, s = KB.rmsnorm_quant_int8(x, norm_p[0], self.arch.eps)
+            ws = float(lw.scale.reshape(-1)[0]) if isinstance(lw.scale, torch.Tensor) else float(lw.scale)
+            return KB.bitlinear_q(q, s, lw.packed, ws, None, lw.n, lw.k, x.dtype)
+        return self._linear(self._norm(x, norm_p), lw)
+
     def _norm(self, x, p):
         if self.arch.norm == "layernorm":
             return self.ops.layernorm(x, p[0], p[1], self.arch.eps)
@@ -257,8 +268,11 @@ class DecoderRunner:
 
         h_next = None
         for li, L in enumerate(self.layers):
-            h = h_next if h_next is not None else self._norm(x, L["ln1"])
-            qkv = self._linear(h, L["qkv"])
+            if h_next is None and L["qkv"].packed is not None:
+                qkv = self._norm_linear(x, L["ln1"], L["qkv"])
+            else:
+                h = h_next if h_next is not None else self._norm(x, L["ln1"])
+                qkv = self._linear(h, L["qkv"])
             if decode and a.rope_base == 0 and ops.name == "kernels":
                 att = ops.append_attention(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], b["block_tables"],
                                            ctx, self.n_head_local, self.n_kv_local, d, max_ctx)
@@ -276,12 +290,15 @@ class DecoderRunner:
             if li == 0 and on_first_attention is not None:
                 on_first_attention()
             x, h = row_parallel(att, L["out"], x, L["ln2"], False)
-            if h is None:
-                h = self._norm(x, L["ln2"])
-            if a.mlp == "gelu":
-                f = self._linear(h, L["up"], activation="gelu")
+            if h is None and a.mlp != "gelu" and L["up"].packed is not None:
+                f = ops.swiglu_fused(self._norm_linear(x, L["ln2"], L["up"]))
             else:
-                f = ops.swiglu_fused(self._linear(h, L["up"]))
+                if h is None:
+                    h = self._norm(x, L["ln2"])
+                if a.mlp == "gelu":
+                    f = self._linear(h, L["up"], activation="gelu")
+                else:
+                    f = ops.swiglu_fused(self._linear(h, L["up"]))
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else (self.lnf if decode else None)
             x, h_next = row_parallel(f, L["down"], x, nxt, True)
         if h_next is not None:
