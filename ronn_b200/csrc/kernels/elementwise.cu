@@ -41,25 +41,43 @@ void prefer_max_shared(const void* kern) {
   }
 }
 
+// Threads per row of the row-wise kernels: as many 16-byte chunks per thread as the register budget allows when
+// there are rows enough to fill the GPU, fewer (more warps per row) when the row count alone would leave most SMs
+// with a warp or two, as in decode.
+int norm_threads(long rows, int nchunk) {
+  int per_thread = NORM_MAX_CHUNKS;
+  auto warps_of = [&](int c) { return ((nchunk + c - 1) / c + 31) / 32; };
+  while (per_thread > 1 && rows * warps_of(per_thread) < 2048 && warps_of(per_thread / 2) <= 32) per_thread /= 2;
+  int threads = warps_of(per_thread) * 32;
+  if (threads > 1024) threads = 1024;
+  return threads;
+}
+
 // y = norm(x [+ res]) * gamma [+ beta];  if sum_out != null the pre-norm sum (x + res) is also written.
 // RMS = true: y = v * rsqrt(mean(v^2) + eps) * gamma.
 template <class T, bool RMS>
 __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
-                            const T* __restrict__ beta, T* __restrict__ y, T* __restrict__ sum_out, int H,
-                            long ld_x, long ld_res, long ld_y, float eps) {
+                            const T* __restrict__ beta, T* __restrict__ y, T* __restrict__ sum_out, long rows,
+                            int H, long ld_x, long ld_res, long ld_y, float eps) {
   __shared__ float scratch[32];
   pdl_wait();
   pdl_trigger();
-  const long row = blockIdx.x;
+  // Rows of up to 1024 values run one warp per row, blockDim.y rows per CTA, and reduce with shuffles only.
+  const long row = long(blockIdx.x) * blockDim.y + threadIdx.y;
+  if (row >= rows) return;                    // whole warps leave: blockDim.y > 1 only with blockDim.x == 32
+  const bool one_warp = blockDim.x == 32;
   const T* xr = x + row * ld_x;
   const T* rr = res ? res + row * ld_res : nullptr;
   const int nchunk = H >> 3;
   float v[NORM_MAX_CHUNKS][8];
+  Vec8 gp[NORM_MAX_CHUNKS], bp[NORM_MAX_CHUNKS];   // scale and shift, fetched before the reductions need the row
   float s = 0.f;
 #pragma unroll
   for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
     const int ch = threadIdx.x + c * blockDim.x;
     if (ch < nchunk) {
+      if (gamma) gp[c] = *reinterpret_cast<const Vec8*>(gamma + ch * 8);
+      if (beta) bp[c] = *reinterpret_cast<const Vec8*>(beta + ch * 8);
       unpack8<T>(*reinterpret_cast<const Vec8*>(xr + ch * 8), v[c]);
       if (rr) {
         float r[8];
@@ -74,10 +92,10 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, 
   }
   float mean = 0.f, inv;
   if (RMS) {
-    const float ms = block_sum(s, scratch) / float(H);
+    const float ms = (one_warp ? warp_sum(s) : block_sum(s, scratch)) / float(H);
     inv = rsqrtf(ms + eps);
   } else {
-    mean = block_sum(s, scratch) / float(H);
+    mean = (one_warp ? warp_sum(s) : block_sum(s, scratch)) / float(H);
     float q = 0.f;
 #pragma unroll
     for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
@@ -90,7 +108,7 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, 
         }
       }
     }
-    const float var = block_sum(q, scratch) / float(H);
+    const float var = (one_warp ? warp_sum(q) : block_sum(q, scratch)) / float(H);
     inv = rsqrtf(var + eps);
   }
 #pragma unroll
@@ -98,8 +116,8 @@ __global__ void norm_kernel(const T* __restrict__ x, const T* __restrict__ res, 
     const int ch = threadIdx.x + c * blockDim.x;
     if (ch < nchunk) {
       float g[8], b[8], o[8];
-      if (gamma) unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + ch * 8), g);
-      if (beta) unpack8<T>(*reinterpret_cast<const Vec8*>(beta + ch * 8), b);
+      if (gamma) unpack8<T>(gp[c], g);
+      if (beta) unpack8<T>(bp[c], b);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         float t = (v[c][i] - mean) * inv;
@@ -426,15 +444,14 @@ extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, cons
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if ((H & 7) || H > 1024 * 8 * NORM_MAX_CHUNKS || (ld_x & 7) || (ld_y & 7) || (res && (ld_res & 7))) return -2;
-  int threads = ((H >> 3) + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS;
-  threads = ((threads + 31) / 32) * 32;
-  if (threads < 32) threads = 32;
-  if (threads > 1024) threads = 1024;
+  const int threads = norm_threads(rows, H >> 3);
+  const int rows_per_cta = (threads == 32 && rows >= 4096) ? 4 : 1;
+  const dim3 grid(unsigned((rows + rows_per_cta - 1) / rows_per_cta)), block(threads, rows_per_cta);
   RONN_BY_DTYPE(dtype, {
-    if (rms) launch(norm_kernel<T, true>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const T*)x, (const T*)res,
-                    (const T*)gamma, (const T*)beta, (T*)y, (T*)sum_out, H, ld_x, ld_res, ld_y, eps);
-    else launch(norm_kernel<T, false>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const T*)x, (const T*)res,
-                (const T*)gamma, (const T*)beta, (T*)y, (T*)sum_out, H, ld_x, ld_res, ld_y, eps);
+    if (rms) launch(norm_kernel<T, true>, grid, block, 0, stream, (const T*)x, (const T*)res, (const T*)gamma,
+                    (const T*)beta, (T*)y, (T*)sum_out, rows, H, ld_x, ld_res, ld_y, eps);
+    else launch(norm_kernel<T, false>, grid, block, 0, stream, (const T*)x, (const T*)res, (const T*)gamma,
+                (const T*)beta, (T*)y, (T*)sum_out, rows, H, ld_x, ld_res, ld_y, eps);
   });
   return check_launch();
 }
@@ -519,10 +536,7 @@ extern "C" int ronn_splitk_finalize(const float* ws, int S, const void* bias, co
                                     int act, int norm, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if ((N & 7) || N > 1024 * 8 * NORM_MAX_CHUNKS || S < 1) return -2;
-  int threads = ((N >> 3) + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS;
-  threads = ((threads + 31) / 32) * 32;
-  if (threads < 32) threads = 32;
-  if (threads > 1024) threads = 1024;
+  const int threads = norm_threads(rows, N >> 3);
 #define RONN_FIN(NORM_) launch(splitk_finalize_kernel<T, NORM_>, dim3(unsigned(rows)), dim3(threads), 0, stream, ws, S, (const T*)bias, (const T*)residual, (T*)sum_out, (const T*)gamma, (const T*)beta, (T*)y, rows, N, eps, act)
   RONN_BY_DTYPE(dtype, {
     if (norm == 0) RONN_FIN(0);
