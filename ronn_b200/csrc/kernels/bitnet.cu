@@ -10,6 +10,7 @@
 // exact int32 accumulation in TMEM.  Epilogue: acc * x_scale[token] * w_scale (+ bias).
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
+#include "rowwise_stream.h"
 #include "tma_desc.cuh"
 
 namespace ronn {
@@ -323,6 +324,10 @@ extern "C" int ronn_act_quant_int8(const void* x, void* q, float* scale, long ro
                                    cudaStream_t stream) {
   if (rows <= 0) return 0;
   if ((K & 15) || K > 16 * 4 * 1024) return -2;
+  {
+    const int rc = rowwise_stream_try(3, x, nullptr, nullptr, nullptr, q, nullptr, scale, rows, K, K, 0, K, 0.f, dtype, stream);
+    if (rc != 0) return rc < 0 ? rc : 0;
+  }
   int threads = (((K >> 4) + 3) / 4 + 31) / 32 * 32;
   if (threads < 32) threads = 32;
   cudaError_t err;
@@ -337,6 +342,10 @@ extern "C" int ronn_norm_quant_int8(const void* x, const void* gamma, void* q, f
   (void)unused;
   if (rows <= 0) return 0;
   if ((K & 15) || K > 16 * 4 * 1024) return -2;
+  {
+    const int rc = rowwise_stream_try(4, x, nullptr, gamma, nullptr, q, nullptr, scale, rows, K, K, 0, K, eps, dtype, stream);
+    if (rc != 0) return rc < 0 ? rc : 0;
+  }
   int threads = (((K >> 4) + 3) / 4 + 31) / 32 * 32;
   if (threads < 32) threads = 32;
   cudaError_t err;

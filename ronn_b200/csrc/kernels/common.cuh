@@ -60,18 +60,47 @@ struct alignas(16) Vec8 {
   uint32_t w[4];
 };
 
+// Two 16-bit values in one 32-bit word <-> two floats, on register values (no 16-bit memory accesses).
+template <class T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+template <> struct Pair16<__half> {
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    lo = f.x;
+    hi = f.y;
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+};
+
+// `v` may live in registers, global or shared memory: it is read with ONE 16-byte access (reading its 16-bit fields
+// one by one from shared memory costs eight 2-byte loads with four-way bank conflicts each).
 template <class T>
 __device__ __forceinline__ void unpack8(const Vec8& v, float (&f)[8]) {
-  const T* p = reinterpret_cast<const T*>(&v);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) f[i] = Cvt<T>::to_f(p[i]);
+  const uint4 raw = *reinterpret_cast<const uint4*>(&v);
+  Pair16<T>::unpack(raw.x, f[0], f[1]);
+  Pair16<T>::unpack(raw.y, f[2], f[3]);
+  Pair16<T>::unpack(raw.z, f[4], f[5]);
+  Pair16<T>::unpack(raw.w, f[6], f[7]);
 }
 template <class T>
 __device__ __forceinline__ Vec8 pack8(const float (&f)[8]) {
   Vec8 v;
-  T* p = reinterpret_cast<T*>(&v);
-#pragma unroll
-  for (int i = 0; i < 8; ++i) p[i] = Cvt<T>::from_f(f[i]);
+  v.w[0] = Pair16<T>::pack(f[0], f[1]);
+  v.w[1] = Pair16<T>::pack(f[2], f[3]);
+  v.w[2] = Pair16<T>::pack(f[4], f[5]);
+  v.w[3] = Pair16<T>::pack(f[6], f[7]);
   return v;
 }
 

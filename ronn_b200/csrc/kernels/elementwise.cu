@@ -11,6 +11,7 @@
 #include <mutex>
 #include <unordered_set>
 #include "common.cuh"
+#include "rowwise_stream.h"
 
 namespace ronn {
 
@@ -262,19 +263,38 @@ __device__ __forceinline__ float act_apply(float x, int op) {
   }
 }
 
+// The element-wise kernels are grid-stride loops over 16-byte chunks, four chunks per thread and turn with the loads
+// issued together: one resident wave of CTAs then keeps about 128 KB per SM in flight, which a DRAM stream needs.
 template <class T>
 __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n, int op) {
   const long n8 = n >> 3;
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += long(gridDim.x) * blockDim.x) {
+  const long stride = long(gridDim.x) * blockDim.x;
+  const Vec8* xv = reinterpret_cast<const Vec8*>(x);
+  Vec8* yv = reinterpret_cast<Vec8*>(y);
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < n8; i += 4 * stride) {
+    Vec8 in[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) in[u] = xv[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float f[8];
+      unpack8<T>(in[u], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] = act_apply(f[k], op);
+      yv[i + u * stride] = pack8<T>(f);
+    }
+  }
+  for (; i < n8; i += stride) {
     float f[8];
-    unpack8<T>(reinterpret_cast<const Vec8*>(x)[i], f);
+    unpack8<T>(xv[i], f);
 #pragma unroll
     for (int k = 0; k < 8; ++k) f[k] = act_apply(f[k], op);
-    reinterpret_cast<Vec8*>(y)[i] = pack8<T>(f);
+    yv[i] = pack8<T>(f);
   }
   if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
-    const long i = (n8 << 3) + threadIdx.x;
-    y[i] = Cvt<T>::from_f(act_apply(Cvt<T>::to_f(x[i]), op));
+    const long j = (n8 << 3) + threadIdx.x;
+    y[j] = Cvt<T>::from_f(act_apply(Cvt<T>::to_f(x[j]), op));
   }
 }
 
@@ -282,10 +302,14 @@ __global__ void unary_kernel(const T* __restrict__ x, T* __restrict__ y, long n,
 template <class T>
 __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ y, long n, int op) {
   const long n8 = n >> 3;
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += long(gridDim.x) * blockDim.x) {
+  const long stride = long(gridDim.x) * blockDim.x;
+  const Vec8* av = reinterpret_cast<const Vec8*>(a);
+  const Vec8* bv = reinterpret_cast<const Vec8*>(b);
+  Vec8* yv = reinterpret_cast<Vec8*>(y);
+  auto combine = [op](const Vec8& pa, const Vec8& pb) {
     float fa[8], fb[8];
-    unpack8<T>(reinterpret_cast<const Vec8*>(a)[i], fa);
-    unpack8<T>(reinterpret_cast<const Vec8*>(b)[i], fb);
+    unpack8<T>(pa, fa);
+    unpack8<T>(pb, fb);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       float r;
@@ -298,8 +322,20 @@ __global__ void binary_kernel(const T* __restrict__ a, const T* __restrict__ b, 
       }
       fa[k] = r;
     }
-    reinterpret_cast<Vec8*>(y)[i] = pack8<T>(fa);
+    return pack8<T>(fa);
+  };
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < n8; i += 4 * stride) {
+    Vec8 pa[4], pb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      pa[u] = av[i + u * stride];
+      pb[u] = bv[i + u * stride];
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) yv[i + u * stride] = combine(pa[u], pb[u]);
   }
+  for (; i < n8; i += stride) yv[i] = combine(av[i], bv[i]);
   if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
     const long i = (n8 << 3) + threadIdx.x;
     const float fa = Cvt<T>::to_f(a[i]), fb = Cvt<T>::to_f(b[i]);
@@ -316,15 +352,34 @@ __global__ void swiglu_fused_kernel(const T* __restrict__ x, T* __restrict__ y, 
   pdl_trigger();
   const int f8 = F >> 3;
   const long total = rows * f8;
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < total; i += long(gridDim.x) * blockDim.x) {
+  const long stride = long(gridDim.x) * blockDim.x;
+  auto gate_at = [&](long i) {
     const long r = i / f8;
-    const int c = int(i - r * f8) * 8;
+    return x + r * 2 * F + (i - r * f8) * 8;
+  };
+  auto apply = [](const Vec8& pg, const Vec8& pu) {
     float g[8], u[8];
-    unpack8<T>(*reinterpret_cast<const Vec8*>(x + r * 2 * F + c), g);
-    unpack8<T>(*reinterpret_cast<const Vec8*>(x + r * 2 * F + F + c), u);
+    unpack8<T>(pg, g);
+    unpack8<T>(pu, u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) g[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
-    *reinterpret_cast<Vec8*>(y + r * F + c) = pack8<T>(g);
+    return pack8<T>(g);
+  };
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    Vec8 pg[4], pu[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const T* g = gate_at(i + k * stride);
+      pg[k] = *reinterpret_cast<const Vec8*>(g);
+      pu[k] = *reinterpret_cast<const Vec8*>(g + F);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) reinterpret_cast<Vec8*>(y)[i + k * stride] = apply(pg[k], pu[k]);
+  }
+  for (; i < total; i += stride) {
+    const T* g = gate_at(i);
+    reinterpret_cast<Vec8*>(y)[i] = apply(*reinterpret_cast<const Vec8*>(g), *reinterpret_cast<const Vec8*>(g + F));
   }
 }
 
@@ -368,10 +423,37 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
   const T* xr = x + long(blockIdx.x) * ld;
   float m = -INFINITY;
   int mi = 0x7fffffff;
-  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-    const float v = Cvt<T>::to_f(xr[i]);
+  auto take = [&](float v, int i) {
     if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+  };
+  // Rows may start at any element (odd vocabulary sizes): scalar accesses up to the first 16-byte boundary, 16-byte
+  // loads (two in flight per thread) for the body, scalar accesses for what is left.
+  constexpr bool VEC = sizeof(T) == 2;
+  int head = VEC ? int(((16u - unsigned(reinterpret_cast<uintptr_t>(xr) & 15u)) & 15u) / sizeof(T)) : 0;
+  if (head > cols) head = cols;
+  const int nvec = VEC ? (cols - head) >> 3 : 0;
+  if (int(threadIdx.x) < head) take(Cvt<T>::to_f(xr[threadIdx.x]), threadIdx.x);
+  if constexpr (VEC) {
+  const Vec8* xv = reinterpret_cast<const Vec8*>(xr + head);
+  int c = threadIdx.x;
+  for (; c + int(blockDim.x) < nvec; c += 2 * blockDim.x) {
+    const Vec8 p0 = xv[c], p1 = xv[c + blockDim.x];
+    float f0[8], f1[8];
+    unpack8<T>(p0, f0);
+    unpack8<T>(p1, f1);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) take(f0[k], head + c * 8 + k);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) take(f1[k], head + (c + int(blockDim.x)) * 8 + k);
   }
+  for (; c < nvec; c += blockDim.x) {
+    float f[8];
+    unpack8<T>(xv[c], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) take(f[k], head + c * 8 + k);
+  }
+  }
+  for (int i = head + nvec * 8 + threadIdx.x; i < cols; i += blockDim.x) take(Cvt<T>::to_f(xr[i]), i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float om = __shfl_xor_sync(0xffffffffu, m, o);
@@ -415,11 +497,72 @@ __global__ void argmax_combine_kernel(const float* __restrict__ vals, const int*
 
 template <class TI, class TO>
 __global__ void cast_kernel(const TI* __restrict__ x, TO* __restrict__ y, long n) {
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n; i += long(gridDim.x) * blockDim.x)
-    y[i] = Cvt<TO>::from_f(Cvt<TI>::to_f(x[i]));
+  const long stride = long(gridDim.x) * blockDim.x;
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  for (; i + 7 * stride < n; i += 8 * stride) {
+    TI in[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) in[u] = x[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) y[i + u * stride] = Cvt<TO>::from_f(Cvt<TI>::to_f(in[u]));
+  }
+  for (; i < n; i += stride) y[i] = Cvt<TO>::from_f(Cvt<TI>::to_f(x[i]));
 }
 
-static inline int grid_for(long work, int threads, int cap = 148 * 16) {
+// 16-bit <-> fp32 in 8-element chunks (16-byte access on the 16-bit side, two on the fp32 side), four chunks per
+// thread and turn; both pointers 16-byte aligned.  The last n % 8 elements are converted one by one.
+template <class T16, bool WIDEN>
+__global__ void cast_vec_kernel(const void* __restrict__ xin, void* __restrict__ yout, long n) {
+  const long n8 = n >> 3;
+  const long stride = long(gridDim.x) * blockDim.x;
+  long i = blockIdx.x * long(blockDim.x) + threadIdx.x;
+  if (WIDEN) {
+    const Vec8* x = static_cast<const Vec8*>(xin);
+    float4* y = static_cast<float4*>(yout);
+    auto put = [&](long j, const Vec8& p) {
+      float f[8];
+      unpack8<T16>(p, f);
+      y[2 * j] = make_float4(f[0], f[1], f[2], f[3]);
+      y[2 * j + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    };
+    for (; i + 3 * stride < n8; i += 4 * stride) {
+      Vec8 in[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) in[u] = x[i + u * stride];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) put(i + u * stride, in[u]);
+    }
+    for (; i < n8; i += stride) put(i, x[i]);
+    if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+      const long j = (n8 << 3) + threadIdx.x;
+      static_cast<float*>(yout)[j] = Cvt<T16>::to_f(static_cast<const T16*>(xin)[j]);
+    }
+  } else {
+    const float4* x = static_cast<const float4*>(xin);
+    Vec8* y = static_cast<Vec8*>(yout);
+    auto put = [&](long j, const float4& a, const float4& b) {
+      const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      y[j] = pack8<T16>(f);
+    };
+    for (; i + 3 * stride < n8; i += 4 * stride) {
+      float4 a[4], b[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a[u] = x[2 * (i + u * stride)];
+        b[u] = x[2 * (i + u * stride) + 1];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) put(i + u * stride, a[u], b[u]);
+    }
+    for (; i < n8; i += stride) put(i, x[2 * i], x[2 * i + 1]);
+    if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+      const long j = (n8 << 3) + threadIdx.x;
+      static_cast<T16*>(yout)[j] = Cvt<T16>::from_f(static_cast<const float*>(xin)[j]);
+    }
+  }
+}
+
+static inline int grid_for(long work, int threads, int cap = 148 * 8) {
   long g = (work + threads - 1) / threads;
   if (g < 1) g = 1;
   return int(g > cap ? cap : g);
@@ -444,6 +587,11 @@ extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, cons
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if ((H & 7) || H > 1024 * 8 * NORM_MAX_CHUNKS || (ld_x & 7) || (ld_y & 7) || (res && (ld_res & 7))) return -2;
+  {
+    const int rc = rowwise_stream_try(rms ? 1 : 0, x, res, gamma, beta, y, sum_out, nullptr, rows, H, ld_x, ld_res, ld_y,
+                                      eps, dtype, stream);
+    if (rc != 0) return rc < 0 ? rc : check_launch();
+  }
   const int threads = norm_threads(rows, H >> 3);
   const int rows_per_cta = (threads == 32 && rows >= 4096) ? 4 : 1;
   const dim3 grid(unsigned((rows + rows_per_cta - 1) / rows_per_cta)), block(threads, rows_per_cta);
@@ -459,6 +607,11 @@ extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, cons
 // dtype: 0 bf16, 1 fp16, 2 fp32
 extern "C" int ronn_softmax(const void* x, void* y, long rows, int cols, int dtype, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
+  {
+    const int rc = rowwise_stream_try(2, x, nullptr, nullptr, nullptr, y, nullptr, nullptr, rows, cols, cols, 0, cols, 0.f,
+                                      dtype, stream);
+    if (rc != 0) return rc < 0 ? rc : check_launch();
+  }
   int threads = cols >= 1024 ? 256 : (cols >= 256 ? 128 : 64);
   if (dtype == 2) softmax_kernel<float><<<unsigned(rows), threads, 0, stream>>>((const float*)x, (float*)y, cols);
   else RONN_BY_DTYPE(dtype, (softmax_kernel<T><<<unsigned(rows), threads, 0, stream>>>((const T*)x, (T*)y, cols)));
@@ -516,6 +669,16 @@ extern "C" int ronn_argmax_combine(const float* vals, const int* idx, int* out, 
 // from/to: 0 bf16, 1 fp16, 2 fp32
 extern "C" int ronn_cast(const void* x, void* y, long n, int from, int to, cudaStream_t stream) {
   if (n <= 0) return 0;
+  if ((from == 2) != (to == 2) && n >= 8 &&
+      !((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15)) {
+    const int gv = grid_for(n >> 3, 256);
+    const int h = from == 2 ? to : from;
+    if (h == 0 && to == 2) cast_vec_kernel<__nv_bfloat16, true><<<gv, 256, 0, stream>>>(x, y, n);
+    else if (h == 1 && to == 2) cast_vec_kernel<__half, true><<<gv, 256, 0, stream>>>(x, y, n);
+    else if (h == 0) cast_vec_kernel<__nv_bfloat16, false><<<gv, 256, 0, stream>>>(x, y, n);
+    else cast_vec_kernel<__half, false><<<gv, 256, 0, stream>>>(x, y, n);
+    return check_launch();
+  }
   const int g = grid_for(n, 256);
 #define RONN_CAST(FI, TI, FO, TO) \
   if (from == FI && to == FO) { cast_kernel<TI, TO><<<g, 256, 0, stream>>>((const TI*)x, (TO*)y, n); return check_launch(); }

@@ -55,6 +55,11 @@ def check_status(device=None) -> None:
     if code:
         w.zero_()
         raise CommTimeoutError(f"a device-side wait was abandoned: {_STATUS_NAMES.get(code, code)}")
+    lib = _native.cuda()
+    if hasattr(lib, "ronn_rowwise_stream_status"):
+        code = int(lib.ronn_rowwise_stream_status(1))       # the streaming row-wise kernels keep their own word
+        if code > 0:
+            raise CommTimeoutError(f"a device-side wait was abandoned: row load of a streaming row-wise kernel ({code:#x})")
 
 
 def gemm(a: torch.Tensor, w_nk: torch.Tensor, bias: Optional[torch.Tensor] = None,

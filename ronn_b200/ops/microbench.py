@@ -304,6 +304,61 @@ def bench_norm(rows, h, dtype=torch.bfloat16, flush=True):
             "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)}
 
 
+def bench_memory_kernels(flush=True):
+    """Every memory-bound kernel of the library on operands larger than L2: time, algorithmic bytes and the fraction
+    of the copy bandwidth.  Shapes are the serving shapes widened in the row count until DRAM traffic is real."""
+    from . import bitnet as B
+    from ..providers.gpu_conv import maxpool_nhwc, global_avgpool_nhwc
+    hbm, _, src = _peaks()
+    dev, bf = "cuda", torch.bfloat16
+    out = []
+
+    def row(name, shape, byts, fn):
+        us = time_kernel(fn, flush=flush)
+        out.append({"kernel": name, "shape": shape, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1),
+                    "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)})
+
+    R, H = 131072, 1024
+    x = torch.randn(R, H, device=dev).to(bf)
+    r = torch.randn(R, H, device=dev).to(bf)
+    g, b = torch.ones(H, device=dev, dtype=bf), torch.zeros(H, device=dev, dtype=bf)
+    row("layernorm", [R, H], 2.0 * R * H * 2, lambda: K.layernorm(x, g, b))
+    row("layernorm + residual (sum kept)", [R, H], 4.0 * R * H * 2, lambda: K.layernorm(x, g, b, residual=r, return_sum=True))
+    row("rmsnorm", [R, H], 2.0 * R * H * 2, lambda: K.rmsnorm(x, g))
+    row("softmax", [R, H], 2.0 * R * H * 2, lambda: K.softmax(x))
+    row("gelu", [R, H], 2.0 * R * H * 2, lambda: K.unary(x, "gelu"))
+    row("relu", [R, H], 2.0 * R * H * 2, lambda: K.unary(x, "relu"))
+    row("sigmoid", [R, H], 2.0 * R * H * 2, lambda: K.unary(x, "sigmoid"))
+    row("add", [R, H], 3.0 * R * H * 2, lambda: K.binary(x, r, "add"))
+    row("swiglu (gate | up in one buffer)", [R, H], 1.5 * R * H * 2, lambda: K.swiglu_fused(x))
+    row("cast bf16 -> fp32", [R, H], 3.0 * R * H * 2, lambda: K.cast(x, torch.float32))
+    Hq = 2560
+    xq = torch.randn(65536, Hq, device=dev).to(bf)
+    gq = torch.ones(Hq, device=dev, dtype=bf)
+    row("act_quant_int8", [65536, Hq], 65536.0 * Hq * 3, lambda: B.act_quant_int8(xq))
+    row("rmsnorm + act_quant_int8", [65536, Hq], 65536.0 * Hq * 3, lambda: B.rmsnorm_quant_int8(xq, gq))
+    V = 50264
+    table = torch.randn(V, H, device=dev).to(bf)
+    ptab = torch.randn(1024, H, device=dev).to(bf)
+    ids = torch.randint(0, V, (R,), device=dev, dtype=torch.int32)
+    pos = torch.randint(0, 1024, (R,), device=dev, dtype=torch.int32)
+    row("embedding gather + position add", [R, H], 3.0 * R * H * 2, lambda: K.embedding(ids, table, pos, ptab))
+    logits = torch.randn(2048, V, device=dev).to(bf)
+    row("argmax over the vocabulary", [2048, V], 2048.0 * V * 2, lambda: K.argmax(logits))
+    heads, d, T = 16, 64, 65536
+    qkv = torch.randn(T, 3 * heads * d, device=dev).to(bf)
+    kc = torch.zeros(T // 16 + 1, heads, 16, d, device=dev, dtype=bf)
+    vc = torch.zeros_like(kc)
+    slots = torch.randperm(T, device=dev).to(torch.int32)
+    row("kv_append (paged scatter)", [T, heads, d], 4.0 * T * heads * d * 2,
+        lambda: K.kv_append(qkv, heads * d, 2 * heads * d, slots, kc, vc, heads, heads, d))
+    xi = torch.randn(128, 112, 112, 64, device=dev).to(torch.float16)
+    row("maxpool 3x3 / 2 (NHWC)", [128, 112, 112, 64], xi.numel() * 2 * 1.25, lambda: maxpool_nhwc(xi, 3, 2, 1))
+    xa = torch.randn(8192, 7, 7, 512, device=dev).to(torch.float16)
+    row("global average pool (NHWC)", [8192, 7, 7, 512], xa.numel() * 2.0, lambda: global_avgpool_nhwc(xa))
+    return out
+
+
 def bench_conv(n=32, h=56, w=56, c=64, cout=64, r=3, stride=1, pad=1, dtype=torch.float16, flush=True, iters=20):
     from ..providers.gpu_conv import conv2d_nhwc
     x = torch.randn(n, h, w, c, device="cuda").to(dtype)
@@ -359,7 +414,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "fused-single-rank", "sweep-attention", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "fused-single-rank", "sweep-attention", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -377,6 +432,8 @@ def main():
         res = [bench_gemm(a.m, a.n, a.k, bn=a.bn, flush=fl, iters=a.iters)]
     elif a.what == "attention":
         res = [bench_attention(a.batch, a.ctx, a.heads, a.dim, flush=fl, iters=a.iters)]
+    elif a.what == "memory-kernels":
+        res = bench_memory_kernels(flush=fl)
     elif a.what == "norm":
         res = [bench_norm(a.batch, a.n, flush=fl)]
     elif a.what == "conv":

@@ -119,6 +119,85 @@ def test_elementwise(K):
     torch.testing.assert_close(K.cast(x, torch.float32), x.float())
 
 
+@pytest.mark.parametrize("H,rows", [(768, 8192), (1024, 4099), (2560, 2048), (4096, 2050), (136, 3001)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_many_rows_streaming_norms(K, H, rows, dtype):
+    """Row counts that take the shared-memory ring path (one warp per row, bulk-copy loads)."""
+    x, r = _rand(rows, H, dtype=dtype), _rand(rows, H, dtype=dtype)
+    g, b = _rand(H, dtype=dtype), _rand(H, dtype=dtype)
+    y = K.layernorm(x, g, b, 1e-5)
+    ref = F.layer_norm(x.float(), (H,), g.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=2e-2)
+    y2, s2 = K.layernorm(x, g, b, 1e-5, residual=r, return_sum=True)
+    sref = (x.float() + r.float()).to(dtype).float()
+    torch.testing.assert_close(s2.float(), sref, atol=0, rtol=0)
+    torch.testing.assert_close(y2.float(), F.layer_norm(sref, (H,), g.float(), b.float(), 1e-5), atol=5e-2, rtol=2e-2)
+    y3 = K.rmsnorm(x, g, 1e-6)
+    xf = x.float()
+    torch.testing.assert_close(y3.float(), xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float(),
+                               atol=3e-2, rtol=2e-2)
+    y4, s4 = K.rmsnorm(x, g, 1e-6, residual=r, return_sum=True)
+    torch.testing.assert_close(s4.float(), sref, atol=0, rtol=0)
+    torch.testing.assert_close(y4.float(), sref * torch.rsqrt(sref.pow(2).mean(-1, keepdim=True) + 1e-6) * g.float(),
+                               atol=5e-2, rtol=2e-2)
+    K.check_status()
+
+
+@pytest.mark.parametrize("cols,rows", [(128, 5000), (1024, 2048), (1000, 4097), (5000, 2100)])
+def test_many_rows_streaming_softmax(K, cols, rows):
+    x = _rand(rows, cols, scale=3.0)
+    y = K.softmax(x)
+    torch.testing.assert_close(y.float(), torch.softmax(x.float(), -1), atol=1e-2, rtol=2e-2)
+    K.check_status()
+
+
+@pytest.mark.parametrize("H,rows", [(2560, 4096), (6912, 2048), (1024, 3000)])
+def test_many_rows_streaming_quantisers(K, H, rows):
+    from ronn_b200.ops import bitnet as B
+    x, g = _rand(rows, H), _rand(H)
+    q, s = B.act_quant_int8(x)
+    xf = x.float()
+    sref = xf.abs().amax(-1).clamp_min(1e-5) / 127
+    torch.testing.assert_close(s, sref, rtol=1e-6, atol=0)
+    qref = torch.clamp(torch.round(xf * (127.0 / xf.abs().amax(-1, keepdim=True).clamp_min(1e-5))), -127, 127)
+    assert (q.float() - qref).abs().max() <= 1
+    # small-row kernel and streaming kernel agree bit for bit
+    q_small, s_small = B.act_quant_int8(x[:64].contiguous())
+    assert torch.equal(q_small, q[:64]) and torch.equal(s_small, s[:64])
+    q2, s2 = B.rmsnorm_quant_int8(x, g, 1e-5)
+    q2_small, s2_small = B.rmsnorm_quant_int8(x[:64].contiguous(), g, 1e-5)
+    normed = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()).bfloat16().float()
+    sref2 = normed.abs().amax(-1) / 127
+    torch.testing.assert_close(s2, sref2, rtol=2e-2, atol=1e-6)
+    torch.testing.assert_close(q2.float() * s2[:, None], normed, atol=float(sref2.max()) * 1.5, rtol=0)
+    torch.testing.assert_close(s2[:64], s2_small, rtol=1e-2, atol=1e-7)
+    assert (q2[:64].float() - q2_small.float()).abs().max() <= 1
+    K.check_status()
+
+
+def test_elementwise_large_and_unaligned_argmax(K):
+    """Sizes that reach the four-way unrolled loops, and argmax rows that start off a 16-byte boundary."""
+    n = 148 * 8 * 256 * 8 * 5 + 24 + 3                       # five full turns of the resident wave + a tail
+    x, y = _rand(n), _rand(n)
+    torch.testing.assert_close(K.unary(x, "relu").float(), torch.relu(x.float()))
+    torch.testing.assert_close(K.binary(x, y, "add").float(), (x.float() + y.float()).bfloat16().float())
+    torch.testing.assert_close(K.cast(x, torch.float32), x.float())
+    xf = torch.randn(n, device="cuda")
+    assert torch.equal(K.cast(xf, torch.bfloat16), xf.bfloat16())
+    assert torch.equal(K.cast(xf[:1003].contiguous(), torch.float16), xf[:1003].half())
+    assert torch.equal(K.cast(x[:1003].contiguous().half(), torch.float32), x[:1003].half().float())
+    z = _rand(40000, 512)
+    torch.testing.assert_close(K.swiglu_fused(z).float(), (F.silu(z[:, :256].float()) * z[:, 256:].float()),
+                               atol=3e-2, rtol=2e-2)
+    for cols in (50257, 50264, 1001, 7):
+        lb = torch.randn(33, cols, device="cuda").bfloat16()
+        idx, mx = K.argmax(lb, return_max=True)
+        ref_max = lb.float().max(-1).values
+        torch.testing.assert_close(mx, ref_max)
+        first = (lb.float() == ref_max[:, None]).float().argmax(-1)          # lowest index among ties
+        assert torch.equal(idx.long(), first)
+
+
 def test_embedding_argmax(K):
     table, ptab = _rand(1000, 256), _rand(64, 256)
     ids = torch.randint(0, 1000, (50,), device="cuda", dtype=torch.int32)
