@@ -426,39 +426,34 @@ __global__ void nchw_to_s2d16_kernel(const T* __restrict__ x, T* __restrict__ y,
   }
 }
 
-// y[n, c] = mean over HW of x[n, :, :, c]; a CTA of 64 threads takes (n, 64-channel slab) items in a grid-stride loop
-// (one launch-time CTA per item would be bound by the CTA launch rate when N is large), threads split HW.
+// y[n, c] = mean over HW of x[n, :, :, c]; one CTA per (n, 64-channel slab), threads split HW.
 template <class T>
-__global__ void global_avgpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int N, int HW, int C) {
+__global__ void global_avgpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ y, int HW, int C) {
   __shared__ float part[8][64];
   pdl_wait();
   pdl_trigger();
-  const int slabs = (C + 63) / 64;
+  const int n = blockIdx.x, c0 = blockIdx.y * 64;
   const int cg = threadIdx.x & 7, pg = threadIdx.x >> 3;            // 8 channel groups x 8 pixel groups (64 threads)
-  for (long item = blockIdx.x; item < long(N) * slabs; item += gridDim.x) {
-    const int n = int(item / slabs), c0 = int(item % slabs) * 64;
-    float acc[8];
+  float acc[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    if (c0 + cg * 8 < C) {
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (c0 + cg * 8 < C) {
 #pragma unroll 4
-      for (int p = pg; p < HW; p += 8) {
-        float f[8];
-        unpack8<T>(*reinterpret_cast<const Vec8*>(x + (size_t(n) * HW + p) * C + c0 + cg * 8), f);
+    for (int p = pg; p < HW; p += 8) {
+      float f[8];
+      unpack8<T>(*reinterpret_cast<const Vec8*>(x + (size_t(n) * HW + p) * C + c0 + cg * 8), f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += f[j];
-      }
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
     }
+  }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) part[pg][cg * 8 + j] = acc[j];
-    __syncthreads();
-    if (c0 + threadIdx.x < C) {
-      float s = 0.f;
+  for (int j = 0; j < 8; ++j) part[pg][cg * 8 + j] = acc[j];
+  __syncthreads();
+  if (threadIdx.x < 64 && c0 + threadIdx.x < C) {
+    float s = 0.f;
 #pragma unroll
-      for (int g = 0; g < 8; ++g) s += part[g][threadIdx.x];
-      y[size_t(n) * C + c0 + threadIdx.x] = Cvt<T>::from_f(s / float(HW));
-    }
-    __syncthreads();
+    for (int g = 0; g < 8; ++g) s += part[g][threadIdx.x];
+    y[size_t(n) * C + c0 + threadIdx.x] = Cvt<T>::from_f(s / float(HW));
   }
 }
 
@@ -559,10 +554,9 @@ extern "C" int ronn_nchw_to_s2d16(const void* x, void* y, int N, int C, int H, i
 
 extern "C" int ronn_global_avgpool_nhwc(const void* x, void* y, int N, int HW, int C, int dtype, cudaStream_t stream) {
   if (C & 7) return -2;
-  const long items = long(N) * ((C + 63) / 64);
-  dim3 grid(unsigned(items > 148 * 32 ? 148 * 32 : items));
+  dim3 grid(N, (C + 63) / 64);
   cudaError_t err;
-  if (dtype == 0) err = launch(global_avgpool_nhwc_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, N, HW, C);
-  else err = launch(global_avgpool_nhwc_kernel<__half>, grid, dim3(64), 0, stream, (const __half*)x, (__half*)y, N, HW, C);
+  if (dtype == 0) err = launch(global_avgpool_nhwc_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, HW, C);
+  else err = launch(global_avgpool_nhwc_kernel<__half>, grid, dim3(64), 0, stream, (const __half*)x, (__half*)y, HW, C);
   return err == cudaSuccess ? 0 : -100;
 }

@@ -21,7 +21,9 @@ constexpr int RS_WARPS = 8;
 constexpr int RS_MAX_STAGES = 8;
 constexpr uint32_t RS_WAIT_CODE = 0x5201u;      // status value: a row load never completed
 
-__device__ uint32_t g_rowwise_status = 0;
+// Status word of the process for each device (set once by the host library with ronn_set_rowwise_status): the
+// launchers of these kernels have no status parameter of their own.
+static uint32_t* g_status_ptr[64] = {};
 
 struct RowArgs {
   const void* x;
@@ -31,6 +33,7 @@ struct RowArgs {
   void* y;
   void* sum_out;
   float* scale_out;
+  uint32_t* status;
   long rows, ld_x, ld_res, ld_y;
   int H, stages;
   float eps;
@@ -90,7 +93,7 @@ __global__ void __launch_bounds__(RS_WARPS * 32, 4) rowwise_stream_kernel(const 
   bool ok = true;
   for (long row = first; row < a.rows; row += total, ++it) {
     const int stage = int(it % S);
-    if (!mbar_wait(&bars[stage], uint32_t(it / S) & 1u, abort_flag, &g_rowwise_status, RS_WAIT_CODE)) {
+    if (!mbar_wait(&bars[stage], uint32_t(it / S) & 1u, abort_flag, a.status, RS_WAIT_CODE)) {
       ok = false;
       break;
     }
@@ -183,33 +186,38 @@ __global__ void __launch_bounds__(RS_WARPS * 32, 4) rowwise_stream_kernel(const 
       }
     } else {
       int8_t* q = static_cast<int8_t*>(a.y) + row * a.ld_y;
+      float m = 0.f;
       if (MODE == 4) {
         float ss = 0.f;
-  #pragma unroll 4
-      for (int c = lane; c < nchunk; c += 32) {
+#pragma unroll 4
+        for (int c = lane; c < nchunk; c += 32) {
           float v[8];
           unpack8<T>(xs[c], v);
 #pragma unroll
           for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
         }
         const float inv = rsqrtf(warp_sum(ss) * inv_h + a.eps);
-  #pragma unroll 4
-      for (int c = lane; c < nchunk; c += 32) {
+#pragma unroll 4
+        for (int c = lane; c < nchunk; c += 32) {
           float v[8], g[8];
           unpack8<T>(xs[c], v);
           unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + c * 8), g);
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * g[i];
-          xs[c] = pack8<T>(v);                    // rounded through the storage type, like norm-then-quantise
-        }
-      }
-      float m = 0.f;
-#pragma unroll 4
-      for (int c = lane; c < nchunk; c += 32) {
-        float v[8];
-        unpack8<T>(xs[c], v);
+          const Vec8 pk = pack8<T>(v);            // rounded through the storage type, like norm-then-quantise
+          xs[c] = pk;
+          unpack8<T>(pk, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+          for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+        }
+      } else {
+#pragma unroll 4
+        for (int c = lane; c < nchunk; c += 32) {
+          float v[8];
+          unpack8<T>(xs[c], v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+        }
       }
       m = fmaxf(warp_max(m), 1e-5f);
       const float qs = __fdiv_rn(127.f, m);       // IEEE division: bit-identical to the host quantiser
@@ -300,7 +308,10 @@ int rowwise_stream_try(int mode, const void* x, const void* res, const void* gam
   if (per_sm < 1) per_sm = 1;
   long grid = (rows + RS_WARPS - 1) / RS_WARPS;
   if (grid > 148l * per_sm) grid = 148l * per_sm;
-  RowArgs a{x, res, gamma, beta, y, sum_out, scale_out, rows, ld_x, ld_res, ld_y, H, stages, eps};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  uint32_t* status = (dev >= 0 && dev < 64) ? g_status_ptr[dev] : nullptr;
+  RowArgs a{x, res, gamma, beta, y, sum_out, scale_out, status, rows, ld_x, ld_res, ld_y, H, stages, eps};
 #define RS_GO(T_)                                                                                       \
   switch (mode) {                                                                                       \
     case 0: return res ? launch_stream<T_, 0, true>(a, smem, int(grid), stream)                         \
@@ -319,14 +330,11 @@ int rowwise_stream_try(int mode, const void* x, const void* res, const void* gam
 
 }  // namespace ronn
 
-// Reads (and with clear != 0 resets) the status word of the streaming row-wise kernels: 0, or 0x5201 when a row load
-// did not complete within the wait limit.  Synchronises the device.
-extern "C" int ronn_rowwise_stream_status(int clear) {
-  uint32_t v = 0;
-  if (cudaMemcpyFromSymbol(&v, ronn::g_rowwise_status, sizeof(v)) != cudaSuccess) return -1;
-  if (clear && v) {
-    const uint32_t z = 0;
-    if (cudaMemcpyToSymbol(ronn::g_rowwise_status, &z, sizeof(z)) != cudaSuccess) return -1;
-  }
-  return int(v);
+// Registers the device word that receives 0x5201 when a row load of a streaming row-wise kernel does not complete
+// within the wait limit (the first code wins; the host reads and clears the word).  Applies to the current device.
+extern "C" int ronn_set_rowwise_status(uint32_t* word) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  ronn::g_status_ptr[dev] = word;
+  return 0;
 }

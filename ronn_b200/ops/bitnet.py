@@ -16,6 +16,7 @@ def act_quant_int8(x: torch.Tensor):
     rows = x2.shape[0]
     q = torch.empty((rows, K), dtype=torch.int8, device=x.device)
     s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    status_word(x.device)
     _check(_native.cuda().ronn_act_quant_int8(x2.data_ptr(), q.data_ptr(), s.data_ptr(), rows, K, _DT[x.dtype], _stream()),
            "act_quant_int8")
     return q, s
@@ -28,6 +29,7 @@ def rmsnorm_quant_int8(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-5):
     rows = x2.shape[0]
     q = torch.empty((rows, K), dtype=torch.int8, device=x.device)
     s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    status_word(x.device)
     _check(_native.cuda().ronn_norm_quant_int8(x2.data_ptr(), gamma.data_ptr(), q.data_ptr(), s.data_ptr(), None, rows, K,
                                                float(eps), _DT[x.dtype], _stream()), "norm_quant_int8")
     return q, s

@@ -23,7 +23,8 @@ _DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 _ACT = {"": 0, None: 0, "none": 0, "Relu": 1, "relu": 1, "Gelu": 2, "gelu": 2}
 _STATUS = {}
 _STATUS_NAMES = {1: "TMA stage never arrived", 2: "pipeline stage never released", 3: "accumulator never committed",
-                 4: "peer flag never raised", 5: "epilogue never drained"}
+                 4: "peer flag never raised", 5: "epilogue never drained",
+                 0x5201: "row load of a streaming row-wise kernel never completed"}
 
 
 def _stream():
@@ -45,6 +46,10 @@ def status_word(device=None) -> torch.Tensor:
     if w is None:
         w = torch.zeros(4, dtype=torch.int32, device=dev)
         _STATUS[dev] = w
+        lib = _native.cuda()
+        if hasattr(lib, "ronn_set_rowwise_status"):          # launchers without a status parameter report here too
+            with torch.cuda.device(dev):
+                lib.ronn_set_rowwise_status(w.data_ptr())
     return w
 
 
@@ -55,11 +60,6 @@ def check_status(device=None) -> None:
     if code:
         w.zero_()
         raise CommTimeoutError(f"a device-side wait was abandoned: {_STATUS_NAMES.get(code, code)}")
-    lib = _native.cuda()
-    if hasattr(lib, "ronn_rowwise_stream_status"):
-        code = int(lib.ronn_rowwise_stream_status(1))       # the streaming row-wise kernels keep their own word
-        if code > 0:
-            raise CommTimeoutError(f"a device-side wait was abandoned: row load of a streaming row-wise kernel ({code:#x})")
 
 
 def gemm(a: torch.Tensor, w_nk: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -103,6 +103,7 @@ def _norm(x, gamma, beta, residual, eps, rms, sum_out):
         if r2.stride(1) != 1:
             r2 = r2.contiguous()
     s = torch.empty_like(y) if sum_out else None
+    status_word(x.device)                                    # the many-rows kernel reports abandoned waits there
     rc = _native.cuda().ronn_norm(x2.data_ptr(), _ptr(r2), _ptr(gamma), _ptr(beta), y.data_ptr(), _ptr(s), rows, H,
                                   x2.stride(0), r2.stride(0) if r2 is not None else 0, y.stride(0), float(eps),
                                   1 if rms else 0, _DT[x.dtype], _stream())
@@ -125,6 +126,7 @@ def softmax(x: torch.Tensor) -> torch.Tensor:
     xc = x.contiguous()
     y = torch.empty_like(xc)
     cols = xc.shape[-1]
+    status_word(x.device)
     _check(_native.cuda().ronn_softmax(xc.data_ptr(), y.data_ptr(), xc.numel() // cols, cols, _DT[x.dtype], _stream()),
            "softmax")
     return y

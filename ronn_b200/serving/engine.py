@@ -71,8 +71,10 @@ class LLMEngine:
         self.dev_buf = torch.zeros(self.host.total, dtype=torch.int32, device=self.device)
         self.sampled_dev = torch.zeros(self.cfg.max_num_seqs, dtype=torch.int32, device=self.device)
         self.sampled_host = torch.zeros(self.cfg.max_num_seqs, dtype=torch.int32)
+        self._status_host = torch.zeros(4, dtype=torch.int32)
         if self.device.type == "cuda":
             self.sampled_host = self.sampled_host.pin_memory()
+            self._status_host = self._status_host.pin_memory()
         self.requests: Dict[int, Request] = {}
         self._next_id = 0
         self._graphs: Dict[int, tuple] = {}
@@ -179,10 +181,14 @@ class LLMEngine:
                     b["dense_plan"] = self._dense_prefill_plan(n_tokens, n_items)
                 toks = self._run_and_sample(b, decode, n_tokens, n_items, sb.req_ids)
             self.sampled_host[:n_items].copy_(toks[:n_items], non_blocking=True)
+            status = self.runner.ops.status_tensor()
+            if status is not None:                       # rides the same synchronisation as the sampled tokens
+                self._status_host.copy_(status, non_blocking=True)
             if self.device.type == "cuda":
                 torch.cuda.current_stream().synchronize()
-            self.d2h_bytes_last = n_items * 4
-            self.runner.ops.check()
+            self.d2h_bytes_last = n_items * 4 + (16 if status is not None else 0)
+            if status is not None and int(self._status_host[0]) != 0:
+                self.runner.ops.check()                  # reads, clears and raises
         except Exception:
             self.sched.abort_step()
             self.metrics.failed_steps += 1

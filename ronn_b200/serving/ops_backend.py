@@ -106,6 +106,9 @@ class TorchOps:
     def check(self):
         pass
 
+    def status_tensor(self):
+        return None
+
 
 class KernelOps:
     name = "kernels"
@@ -170,6 +173,10 @@ class KernelOps:
 
     def check(self):
         self.K.check_status()
+
+    def status_tensor(self):
+        """Device word that the kernels' bounded waits write; lets a caller fetch it with its own copy."""
+        return self.K.status_word()
 
 
 def make_ops(backend: str, device: torch.device):
