@@ -13,6 +13,7 @@ import argparse
 import json
 import math
 import os
+import sys
 
 import torch
 
@@ -216,6 +217,42 @@ def bench_dense_attention(batch=64, seq=128, heads=12, dim=64, causal=False, ite
             "frac_of_" + src: round(roof / us, 3)}
 
 
+def probe_dense_attention(batch=8, seq=1024, heads=16, dim=64, causal=True):
+    """Cycle counts between the phase boundaries of one attention CTA (last query tile of head 0, sequence 0): where
+    a key-tile iteration spends its time, for the softmax warps and for the MMA thread."""
+    import ctypes as C
+    from .. import _native
+    hn = heads * dim
+    qkv = torch.randn(batch * seq, 3 * hn, device="cuda").bfloat16()
+    plan = K.dense_attention_plan([seq] * batch, "cuda")
+    out = torch.empty(batch * seq, hn, device="cuda", dtype=torch.bfloat16)
+    vt = torch.empty(hn, plan["vt_cols"], device="cuda", dtype=torch.bfloat16)
+    call = lambda: K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, dim, causal, out=out, vt=vt)
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    buf = torch.zeros(128, dtype=torch.int64, device="cuda")
+    lib = _native.cuda()
+    lib.ronn_flash_attention_set_probe.restype = None
+    lib.ronn_flash_attention_set_probe.argtypes = [C.c_void_p]
+    lib.ronn_flash_attention_set_probe(buf.data_ptr())
+    try:
+        call()
+        torch.cuda.synchronize()
+    finally:
+        lib.ronn_flash_attention_set_probe(None)
+    K.check_status()
+    t = buf.cpu().view(2, 8, 8)
+    t0 = int(t[0, 0, 0])
+    res = {"kernel": "flash_attention phase probe", "batch": batch, "seq": seq, "heads": heads, "dim": dim, "causal": causal,
+           "softmax_points": ["before s_full wait", "S ready", "pass 1 done", "maxima exchanged", "O updated", "pass 2 done",
+                              "p_full arrived"],
+           "mma_points": ["before k_full wait", "K ready", "S issued", "P ready", "V ready", "PV issued"],
+           "softmax_cycles": [[int(t[0, j, p_]) - t0 for p_ in range(7)] for j in range(8) if int(t[0, j, 0])],
+           "mma_cycles": [[int(t[1, j, p_]) - t0 for p_ in range(6)] for j in range(8) if int(t[1, j, 0])]}
+    return res
+
+
 def bench_fused_single_rank(m=256, n=1024, k=1024, iters=20, flush=True):
     """The fused GEMM + reduction (+ LayerNorm) kernel run as a world of one rank on plain device buffers: the same
     code path as the tensor-parallel call (partials published, flags raised and awaited, rows reduced and normalised)
@@ -414,7 +451,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "fused-single-rank", "sweep-attention", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "attention-probe", "fused-single-rank", "sweep-attention", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -447,8 +484,13 @@ def main():
     elif a.what == "sweep-decode-gemm":
         res = sweep_decode_gemm(a.m)
     elif a.what == "dense-attention":
-        res = [bench_dense_attention(a.batch if a.batch != 256 else 64, a.ctx if a.ctx != 416 else 128, a.heads if a.heads != 16 else 12,
-                                     a.dim, causal=a.causal, iters=a.iters, flush=fl)]
+        # without --batch / --ctx / --heads: the DistilBERT encoder shape (64 x 128 tokens, 12 heads)
+        given = lambda flag: any(x == flag or x.startswith(flag + "=") for x in sys.argv)
+        res = [bench_dense_attention(a.batch if given("--batch") else 64, a.ctx if given("--ctx") else 128,
+                                     a.heads if given("--heads") else 12, a.dim, causal=a.causal, iters=a.iters, flush=fl)]
+    elif a.what == "attention-probe":
+        res = [probe_dense_attention(a.batch if a.batch != 256 else 8, a.ctx if a.ctx != 416 else 1024, a.heads, a.dim,
+                                     causal=a.causal)]
     elif a.what == "fused-single-rank":
         res = [bench_fused_single_rank(a.m, a.n, a.k, iters=a.iters, flush=fl)]
     elif a.what == "overlap":
