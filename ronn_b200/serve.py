@@ -21,6 +21,8 @@ def main():
     ap.add_argument("--policy", default="fcfs", choices=["fcfs", "priority"])
     ap.add_argument("--prefix-cache", action="store_true")
     ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--tokenizer", default="bytes",
+                    help="'bytes' (UTF-8 bytes as ids), a SentencePiece .model file, or 'none' (token-id endpoints only)")
     a = ap.parse_args()
     import torch
     import uvicorn
@@ -42,7 +44,9 @@ def main():
     engine = LLMEngine(model, EngineConfig(max_num_seqs=a.max_batch_size, max_batch_tokens=a.max_batch_tokens,
                                            max_model_len=a.max_model_len, prefill_chunk=a.prefill_chunk, policy=a.policy,
                                            enable_prefix_cache=a.prefix_cache, dtype=a.dtype))
-    uvicorn.run(create_app(engine), host=a.host, port=a.port, log_level="info")
+    from .serving.tokenizer import load_tokenizer
+    tok = None if a.tokenizer == "none" else load_tokenizer(a.tokenizer, engine.arch.vocab)
+    uvicorn.run(create_app(engine, tok), host=a.host, port=a.port, log_level="info")
 
 
 if __name__ == "__main__":

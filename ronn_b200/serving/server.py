@@ -1,9 +1,10 @@
 """HTTP front end of the serving engine.
 
 Endpoints of the continuous-batching design (docs/new/RONN-Continuous-Batching-Branch-Prompt.md:377-395):
-``POST /v1/completions`` (optionally streamed as server-sent events), ``DELETE /v1/requests/{id}``,
-``GET /v1/health``, ``GET /v1/metrics`` (Prometheus text).  Prompts are token ids (``prompt_token_ids``); no
-tokenizer ships with the runtime.  One background thread owns the engine and runs its iteration loop; HTTP
+``POST /v1/completions`` and ``POST /v1/chat/completions`` (optionally streamed as server-sent events),
+``DELETE /v1/requests/{id}``, ``GET /v1/health``, ``GET /v1/metrics`` (Prometheus text).  Prompts are token ids
+(``prompt_token_ids``) or, when the app was created with a tokenizer (``serving/tokenizer.py``), text (``prompt`` /
+chat ``messages``).  One background thread owns the engine and runs its iteration loop; HTTP
 handlers only enqueue requests and wait on per-request events.
 """
 from __future__ import annotations
@@ -21,7 +22,8 @@ from .request import Priority, SamplingParams
 
 
 class CompletionRequest(BaseModel):
-    prompt_token_ids: List[int]
+    prompt_token_ids: List[int] = []
+    prompt: Optional[str] = None
     max_tokens: int = 16
     temperature: float = 0.0
     top_k: int = 0
@@ -29,6 +31,24 @@ class CompletionRequest(BaseModel):
     repeat_penalty: float = 1.0
     seed: Optional[int] = None
     stop_token_sequences: List[List[int]] = []
+    stream: bool = False
+    priority: str = "normal"
+
+
+class ChatMessage(BaseModel):
+    role: str = "user"
+    content: str = ""
+
+
+class ChatRequest(BaseModel):
+    messages: List[ChatMessage]
+    max_tokens: int = 16
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repeat_penalty: float = 1.0
+    seed: Optional[int] = None
+    stop: List[str] = []
     stream: bool = False
     priority: str = "normal"
 
@@ -114,7 +134,7 @@ class EngineLoop:
                     ev.set()
 
 
-def create_app(engine: LLMEngine):
+def create_app(engine: LLMEngine, tokenizer=None):
     from fastapi import FastAPI, HTTPException
     from fastapi.responses import PlainTextResponse, StreamingResponse
 
@@ -128,21 +148,78 @@ def create_app(engine: LLMEngine):
             raise HTTPException(status_code=400, detail=r.error)
         return {"id": rid, "object": "text_completion",
                 "choices": [{"index": 0, "token_ids": r.output_tokens,
+                             "text": tokenizer.decode(r.output_tokens) if tokenizer is not None else None,
                              "finish_reason": r.finish_reason.value if r.finish_reason else None}],
                 "usage": {"prompt_tokens": len(r.prompt_tokens), "completion_tokens": len(r.output_tokens)}}
 
+    def _priority(name: str) -> Priority:
+        try:
+            return Priority[name.upper()]
+        except KeyError:
+            raise HTTPException(status_code=400, detail=f"unknown priority '{name}'") from None
+
+    async def _wait(rid: int, step: float) -> bool:
+        return await asyncio.get_running_loop().run_in_executor(None, loop.wait, rid, step)
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(req: ChatRequest):
+        if tokenizer is None:
+            raise HTTPException(status_code=400, detail="the server was started without a tokenizer")
+        if not req.messages:
+            raise HTTPException(status_code=400, detail="messages must not be empty")
+        from .tokenizer import render_chat
+        prompt = tokenizer.encode(render_chat([m.model_dump() for m in req.messages]))
+        params = SamplingParams(max_new_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k,
+                                top_p=req.top_p, repeat_penalty=req.repeat_penalty, seed=req.seed,
+                                stop_sequences=[tokenizer.encode(s_) for s_ in req.stop if s_])
+        rid = loop.submit(prompt, params, _priority(req.priority))
+        if not req.stream:
+            while not await _wait(rid, 0.05):
+                pass
+            r = engine.requests[rid]
+            if r.error:
+                raise HTTPException(status_code=400, detail=r.error)
+            return {"id": rid, "object": "chat.completion",
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": tokenizer.decode(r.output_tokens)},
+                                 "token_ids": r.output_tokens,
+                                 "finish_reason": r.finish_reason.value if r.finish_reason else None}],
+                    "usage": {"prompt_tokens": len(r.prompt_tokens), "completion_tokens": len(r.output_tokens)}}
+
+        async def events():
+            sent: List[int] = []
+            text = ""
+            while True:
+                done = await _wait(rid, 0.01)
+                new = loop.drain_stream(rid)
+                if new:
+                    sent.extend(new)
+                    full = tokenizer.decode(sent)            # decode the whole prefix: a character may span tokens
+                    delta, text = full[len(text):], full
+                    chunk = {"id": rid, "object": "chat.completion.chunk",
+                             "choices": [{"index": 0, "delta": {"content": delta}, "token_ids": new}]}
+                    yield f"data: {json.dumps(chunk)}\n\n"
+                if done:
+                    r = engine.requests[rid]
+                    fin = {"id": rid, "object": "chat.completion.chunk",
+                           "choices": [{"index": 0, "delta": {},
+                                        "finish_reason": r.finish_reason.value if r.finish_reason else None}]}
+                    yield f"data: {json.dumps(fin)}\n\n"
+                    yield "data: [DONE]\n\n"
+                    return
+        return StreamingResponse(events(), media_type="text/event-stream")
+
     @app.post("/v1/completions")
     async def completions(req: CompletionRequest):
+        if not req.prompt_token_ids and req.prompt:
+            if tokenizer is None:
+                raise HTTPException(status_code=400, detail="text prompts need a tokenizer; send prompt_token_ids")
+            req.prompt_token_ids = tokenizer.encode(req.prompt)
         if not req.prompt_token_ids:
             raise HTTPException(status_code=400, detail="prompt_token_ids must not be empty")
         params = SamplingParams(max_new_tokens=req.max_tokens, temperature=req.temperature, top_k=req.top_k,
                                 top_p=req.top_p, repeat_penalty=req.repeat_penalty, seed=req.seed,
                                 stop_sequences=req.stop_token_sequences)
-        try:
-            prio = Priority[req.priority.upper()]
-        except KeyError:
-            raise HTTPException(status_code=400, detail=f"unknown priority '{req.priority}'") from None
-        rid = loop.submit(list(req.prompt_token_ids), params, prio)
+        rid = loop.submit(list(req.prompt_token_ids), params, _priority(req.priority))
         if not req.stream:
             while not await asyncio.get_running_loop().run_in_executor(None, loop.wait, rid, 0.05):
                 pass

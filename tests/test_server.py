@@ -36,3 +36,42 @@ def test_completions_health_metrics_cancel_stream():
         assert c.delete("/v1/requests/9999").status_code == 404
         assert c.delete(f"/v1/requests/{body['id']}").json()["cancelled"] is True
     app.state.loop.stop()
+
+
+def test_chat_completions_text_prompts_and_streaming():
+    from ronn_b200.serving.tokenizer import ByteTokenizer, load_tokenizer, render_chat
+    cfg = GPT2Config.tiny()
+    model = Model.from_graph(build_gpt2(cfg, dtype=torch.float32, seed=2))
+    ecfg = dict(max_num_seqs=4, max_batch_tokens=128, max_model_len=256, num_blocks=64, dtype="fp32", backend="torch")
+    tok = load_tokenizer("bytes", cfg.vocab_size)
+    assert isinstance(tok, ByteTokenizer) and tok.decode(tok.encode("héllo")) == "héllo"
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    prompt = tok.encode(render_chat(msgs))
+    ref = LLMEngine(model, EngineConfig(**ecfg), device="cpu").generate([prompt], SamplingParams(max_new_tokens=6))[0]
+    eng = LLMEngine(model, EngineConfig(**ecfg), device="cpu")
+    app = create_app(eng, tok)
+    with TestClient(app) as c:
+        r = c.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 6})
+        assert r.status_code == 200
+        ch = r.json()["choices"][0]
+        assert ch["token_ids"] == ref and ch["message"] == {"role": "assistant", "content": tok.decode(ref)}
+        assert r.json()["usage"]["prompt_tokens"] == len(prompt)
+        with c.stream("POST", "/v1/chat/completions", json={"messages": msgs, "max_tokens": 6, "stream": True}) as s_:
+            lines = [l for l in s_.iter_lines() if l.startswith("data: ")]
+        chunks = [json.loads(l[6:]) for l in lines[:-1]]
+        streamed = [t for ch_ in chunks for t in ch_["choices"][0].get("token_ids", [])]
+        text = "".join(ch_["choices"][0]["delta"].get("content", "") for ch_ in chunks)
+        assert streamed == ref and text == tok.decode(ref) and lines[-1] == "data: [DONE]"
+        assert chunks[-1]["choices"][0]["finish_reason"] == "max_tokens"
+        # text prompt on the completions endpoint
+        r2 = c.post("/v1/completions", json={"prompt": render_chat(msgs), "max_tokens": 6})
+        assert r2.json()["choices"][0]["token_ids"] == ref and r2.json()["choices"][0]["text"] == tok.decode(ref)
+        assert c.post("/v1/chat/completions", json={"messages": []}).status_code == 400
+    app.state.loop.stop()
+    # without a tokenizer the text endpoints refuse
+    eng2 = LLMEngine(model, EngineConfig(**ecfg), device="cpu")
+    app2 = create_app(eng2)
+    with TestClient(app2) as c:
+        assert c.post("/v1/chat/completions", json={"messages": msgs}).status_code == 400
+        assert c.post("/v1/completions", json={"prompt": "hi"}).status_code == 400
+    app2.state.loop.stop()
