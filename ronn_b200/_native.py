@@ -101,6 +101,10 @@ def host():
             _sig(lib, f"ronn_sched_{name}", I32, [V])
         _sig(lib, "ronn_sched_block_ref", I32, [V, I32])
         _sig(lib, "ronn_sched_stats", None, [V, c_i64p])
+        _sig(lib, "ronn_sched_set_swap", I32, [V, I32, I32, I32])
+        _sig(lib, "ronn_sched_swap_counts", None, [V, c_i32p])
+        _sig(lib, "ronn_sched_get_swaps", None, [V, c_i32p, c_i32p, c_i32p, c_i32p])
+        _sig(lib, "ronn_sched_swap_stats", None, [V, c_i64p])
         # ---- cpu kernels
         _sig(lib, "ronn_cpu_simd_level", I32, [])
         _sig(lib, "ronn_cpu_force_level", None, [I32])

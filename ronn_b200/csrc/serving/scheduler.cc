@@ -23,6 +23,9 @@ namespace {
 
 enum State : int32_t { WAITING = 0, PREFILL = 1, DECODING = 2, FINISHED = 3, PREEMPTED = 4, CANCELLED = 5 };
 enum Policy : int32_t { FCFS = 0, PRIORITY = 1 };
+// What happens to the KV blocks of a preempted sequence: dropped and recomputed on resume, copied to a host block pool
+// and copied back on resume, or (AUTO) swapped when the sequence has at least `auto_min_tokens` tokens in the cache.
+enum PreemptMode : int32_t { RECOMPUTE = 0, SWAP = 1, AUTO = 2 };
 
 struct Config {
   int32_t block_size = 16;
@@ -33,6 +36,9 @@ struct Config {
   int32_t policy = FCFS;
   int32_t enable_prefix_cache = 0;
   int32_t max_blocks_per_seq = 64;
+  int32_t preempt_mode = RECOMPUTE;
+  int32_t num_cpu_blocks = 0;
+  int32_t auto_min_tokens = 64;
 };
 
 struct Request {
@@ -48,6 +54,7 @@ struct Request {
   std::vector<int32_t> tokens;    // prompt + generated
   std::vector<int32_t> blocks;    // logical block -> physical block
   std::vector<uint64_t> block_hashes;  // prefix hash of each full block (prefix cache)
+  std::vector<int32_t> cpu_blocks;     // host copies of the first blocks while the request is swapped out
 };
 
 struct BlockMeta {
@@ -60,6 +67,11 @@ struct Stats {
   int64_t steps = 0, prefill_steps = 0, decode_steps = 0;
   int64_t preemptions = 0, prefix_hits_blocks = 0, finished = 0, cancelled = 0;
   int64_t scheduled_tokens = 0;
+  int64_t swap_preemptions = 0, swapped_out_blocks = 0, swapped_in_blocks = 0;
+};
+
+struct SwapOp {
+  int32_t src, dst;
 };
 
 struct PlanItem {
@@ -83,6 +95,11 @@ struct Scheduler {
   int32_t plan_kind = 0;                                // 0 none, 1 prefill, 2 decode
   int64_t arrival_counter = 0;
   Stats stats;
+  // Block copies the engine has to run before this step's forward pass: first every swap_out (device block src ->
+  // host block dst), then every swap_in (host block src -> device block dst).  Host blocks released by a swap-in
+  // become reusable only at the next schedule() so that no swap-out of the same step overwrites them.
+  std::vector<int32_t> cpu_free, cpu_pending_free;
+  std::vector<SwapOp> swap_out, swap_in;
 
   explicit Scheduler(const Config& c) : cfg(c), meta(size_t(c.num_blocks)) {
     free_list.reserve(size_t(c.num_blocks));
@@ -213,10 +230,51 @@ struct Scheduler {
     return a.arrival < b.arrival;
   }
 
-  void preempt(int64_t id) {
+  void set_swap(int32_t mode, int32_t num_cpu_blocks, int32_t auto_min_tokens) {
+    cfg.preempt_mode = mode;
+    cfg.num_cpu_blocks = num_cpu_blocks;
+    cfg.auto_min_tokens = auto_min_tokens;
+    cpu_free.clear();
+    cpu_pending_free.clear();
+    for (int32_t b = num_cpu_blocks - 1; b >= 0; --b) cpu_free.push_back(b);
+  }
+
+  void release_cpu_blocks(Request& r, bool deferred) {
+    for (int32_t c : r.cpu_blocks) (deferred ? cpu_pending_free : cpu_free).push_back(c);
+    r.cpu_blocks.clear();
+  }
+
+  // Bring a swapped-out request's blocks back: device blocks for the tokens it has in its host copy.
+  bool swap_in_request(Request& r) {
+    const int32_t nb = int32_t(r.cpu_blocks.size());
+    if (nb > num_free() - int32_t(running.size())) return false;     // same reserve as admission
+    for (int32_t i = 0; i < nb; ++i) {
+      const int32_t b = alloc_block();
+      r.blocks.push_back(b);
+      swap_in.push_back({r.cpu_blocks[size_t(i)], b});
+    }
+    stats.swapped_in_blocks += nb;
+    release_cpu_blocks(r, true);
+    return true;
+  }
+
+  void preempt(int64_t id, bool allow_swap = true) {
     Request& r = reqs[id];
+    const int32_t nb = (r.num_computed + cfg.block_size - 1) / cfg.block_size;
+    bool swap = allow_swap && nb > 0 && nb <= int32_t(r.blocks.size()) && nb <= int32_t(cpu_free.size()) &&
+                (cfg.preempt_mode == SWAP || (cfg.preempt_mode == AUTO && r.num_computed >= cfg.auto_min_tokens));
+    if (swap) {
+      for (int32_t i = 0; i < nb; ++i) {
+        const int32_t c = cpu_free.back();
+        cpu_free.pop_back();
+        r.cpu_blocks.push_back(c);
+        swap_out.push_back({r.blocks[size_t(i)], c});
+      }
+      stats.swap_preemptions += 1;
+      stats.swapped_out_blocks += nb;
+    }
     free_request_blocks(r);
-    r.num_computed = 0;
+    if (!swap) r.num_computed = 0;
     r.state = PREEMPTED;
     r.preemptions += 1;
     stats.preemptions += 1;
@@ -236,6 +294,10 @@ struct Scheduler {
   int32_t schedule() {
     plan.clear();
     plan_kind = 0;
+    swap_out.clear();
+    swap_in.clear();
+    cpu_free.insert(cpu_free.end(), cpu_pending_free.begin(), cpu_pending_free.end());
+    cpu_pending_free.clear();
     // ---- admission + prefill -------------------------------------------------
     if (cfg.policy == PRIORITY && waiting.size() > 1) {
       std::stable_sort(waiting.begin(), waiting.end(), [this](int64_t a, int64_t b) {
@@ -263,7 +325,7 @@ struct Scheduler {
     while (!waiting.empty() && int32_t(running.size()) < cfg.max_num_seqs && budget > 0) {
       int64_t id = waiting.front();
       Request& r = reqs[id];
-      match_prefix(r);
+      if (r.cpu_blocks.empty()) match_prefix(r);        // a swapped-out request keeps its own cache, not a shared prefix
       int32_t total = int32_t(r.tokens.size());
       int32_t remaining = total - r.num_computed;
       int32_t take = remaining;
@@ -278,6 +340,7 @@ struct Scheduler {
         if (r.blocks.size() && plan.empty()) { /* keep matched prefix blocks; retry next step */ }
         break;
       }
+      if (!r.cpu_blocks.empty() && !swap_in_request(r)) break;      // a swapped-out request resumes with its cache
       if (!ensure_blocks(r, r.num_computed + take)) break;
       waiting.pop_front();
       r.state = PREFILL;
@@ -376,6 +439,7 @@ int32_t ronn_sched_cancel(void* h, int64_t id) {
   Request& r = it->second;
   if (r.state == FINISHED || r.state == CANCELLED) return 0;
   s->free_request_blocks(r);
+  s->release_cpu_blocks(r, true);
   auto w = std::find(s->waiting.begin(), s->waiting.end(), id);
   if (w != s->waiting.end()) s->waiting.erase(w);
   auto ru = std::find(s->running.begin(), s->running.end(), id);
@@ -383,6 +447,35 @@ int32_t ronn_sched_cancel(void* h, int64_t id) {
   r.state = CANCELLED;
   s->stats.cancelled += 1;
   return 0;
+}
+
+// mode: 0 recompute, 1 swap, 2 auto (swap when at least auto_min_tokens tokens are cached).  Call before any request
+// is added; the host pool has num_cpu_blocks blocks of the same size as the device blocks.
+int32_t ronn_sched_set_swap(void* h, int32_t mode, int32_t num_cpu_blocks, int32_t auto_min_tokens) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  if (mode < 0 || mode > 2 || num_cpu_blocks < 0 || !s->reqs.empty()) return -1;
+  s->set_swap(mode, num_cpu_blocks, auto_min_tokens);
+  return 0;
+}
+// Block copies of the current plan: counts[0] swap-outs, counts[1] swap-ins.
+void ronn_sched_swap_counts(void* h, int32_t* counts) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  counts[0] = int32_t(s->swap_out.size());
+  counts[1] = int32_t(s->swap_in.size());
+}
+// out_src/out_dst: device block -> host block; in_src/in_dst: host block -> device block.
+void ronn_sched_get_swaps(void* h, int32_t* out_src, int32_t* out_dst, int32_t* in_src, int32_t* in_dst) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  for (size_t i = 0; i < s->swap_out.size(); ++i) { out_src[i] = s->swap_out[i].src; out_dst[i] = s->swap_out[i].dst; }
+  for (size_t i = 0; i < s->swap_in.size(); ++i) { in_src[i] = s->swap_in[i].src; in_dst[i] = s->swap_in[i].dst; }
+}
+// out[0..3] = preemptions that swapped, blocks swapped out, blocks swapped in, free host blocks
+void ronn_sched_swap_stats(void* h, int64_t* out) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  out[0] = s->stats.swap_preemptions;
+  out[1] = s->stats.swapped_out_blocks;
+  out[2] = s->stats.swapped_in_blocks;
+  out[3] = int64_t(s->cpu_free.size() + s->cpu_pending_free.size());
 }
 
 int32_t ronn_sched_schedule(void* h) { return static_cast<Scheduler*>(h)->schedule(); }
@@ -469,7 +562,7 @@ void ronn_sched_abort_step(void* h) {
   for (auto& it : s->plan) ids.push_back(it.req);
   s->plan.clear();
   s->plan_kind = 0;
-  for (int64_t id : ids) s->preempt(id);
+  for (int64_t id : ids) s->preempt(id, false);    // the failed step may have left their cache half written
 }
 
 int32_t ronn_sched_state(void* h, int64_t id) {

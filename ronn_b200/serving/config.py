@@ -17,6 +17,9 @@ class EngineConfig:
     prefill_chunk: int = 0              # 0 = whole prompts
     policy: str = "fcfs"                # "fcfs" | "priority"
     enable_prefix_cache: bool = False
+    preemption: str = "recompute"       # "recompute" | "swap" | "auto": what a preempted sequence does with its KV blocks
+    num_cpu_blocks: int = 0             # host (pinned) block pool for "swap" / "auto"; 0 = as many as device blocks
+    swap_min_tokens: int = 64           # "auto": sequences with fewer cached tokens are recomputed instead
     eos_token_id: int = -1              # -1 = never stop on a token
     use_cuda_graph: bool = True
     dtype: str = "bf16"

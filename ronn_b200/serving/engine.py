@@ -66,6 +66,14 @@ class LLMEngine:
         self.sched = Scheduler(self.cfg.block_size, self.runner.num_blocks, self.cfg.max_num_seqs,
                                self.cfg.max_batch_tokens, self.cfg.prefill_chunk, self.cfg.policy,
                                self.cfg.enable_prefix_cache, self.max_blocks)
+        self._cpu_k = self._cpu_v = None
+        if self.cfg.preemption != "recompute":
+            # host block pool for swapped-out sequences: same block layout as the device cache, one pool per layer
+            n_cpu = self.cfg.num_cpu_blocks or min(self.runner.num_blocks, 2048)
+            self.sched.set_preemption(self.cfg.preemption, n_cpu, self.cfg.swap_min_tokens)
+            shape = (n_cpu,) + tuple(self.runner.kcache[0].shape[1:])
+            self._cpu_k = [torch.empty(shape, dtype=self.runner.kcache[0].dtype) for _ in self.runner.kcache]
+            self._cpu_v = [torch.empty(shape, dtype=self.runner.kcache[0].dtype) for _ in self.runner.kcache]
         max_tokens = max(self.cfg.max_batch_tokens, self.cfg.max_num_seqs)
         self.host = HostBatchBuffers(max_tokens, self.cfg.max_num_seqs, self.max_blocks, pin=self.device.type == "cuda")
         self.dev_buf = torch.zeros(self.host.total, dtype=torch.int32, device=self.device)
@@ -152,10 +160,31 @@ class LLMEngine:
         self.dev_buf[:used].copy_(self.host.host[:used], non_blocking=True)
         self.h2d_bytes_last = used * 4
 
+    def _run_swaps(self) -> None:
+        """Block copies the scheduler decided on: preempted sequences go to the host pool (device -> host) before their
+        device blocks are reused by this step, resumed ones come back (host -> device)."""
+        if self._cpu_k is None:
+            return
+        o_src, o_dst, i_src, i_dst = self.sched.swaps()
+        if len(o_src):
+            src = torch.as_tensor(o_src, dtype=torch.long, device=self.device)
+            dst = torch.as_tensor(o_dst, dtype=torch.long)
+            for dev_c, cpu_c in ((self.runner.kcache, self._cpu_k), (self.runner.vcache, self._cpu_v)):
+                for l in range(len(dev_c)):
+                    cpu_c[l].index_copy_(0, dst, dev_c[l].index_select(0, src).cpu())
+        if len(i_src):
+            src = torch.as_tensor(i_src, dtype=torch.long)
+            dst = torch.as_tensor(i_dst, dtype=torch.long, device=self.device)
+            for dev_c, cpu_c in ((self.runner.kcache, self._cpu_k), (self.runner.vcache, self._cpu_v)):
+                for l in range(len(dev_c)):
+                    dev_c[l].index_copy_(0, dst, cpu_c[l].index_select(0, src).to(self.device))
+        self.metrics.swapped_blocks += len(o_src) + len(i_src)
+
     # ------------------------------------------------------------------ one iteration
     def step(self) -> "StepOutput":
         """Run one scheduling iteration.  Returns the requests that produced a token in it."""
         kind = self.sched.schedule()
+        self._run_swaps()                                # also when nothing is scheduled: a preemption may have swapped
         if kind == PLAN_NONE:
             return StepOutput(self, np.zeros(0, np.int64), np.zeros(0, np.int32), np.zeros(0, np.int32))
         t0 = time.perf_counter()
@@ -377,4 +406,5 @@ class LLMEngine:
     def stats(self) -> Dict[str, object]:
         d = self.metrics.as_dict()
         d.update(self.sched.stats())
+        d.update(self.sched.swap_stats())
         return d

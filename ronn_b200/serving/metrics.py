@@ -20,6 +20,7 @@ class EngineMetrics:
     requests_added: int = 0
     requests_finished: int = 0
     failed_steps: int = 0
+    swapped_blocks: int = 0            # KV blocks copied to or from the host pool by swap preemption
     prefill_steps: int = 0
     decode_steps: int = 0
     prompt_tokens: int = 0
@@ -57,7 +58,7 @@ class EngineMetrics:
     def as_dict(self) -> Dict[str, object]:
         util = 1.0 - self.free_blocks / self.total_blocks if self.total_blocks else 0.0
         return {"requests_added": self.requests_added, "requests_finished": self.requests_finished,
-                "failed_steps": self.failed_steps, "prefill_steps": self.prefill_steps,
+                "failed_steps": self.failed_steps, "swapped_blocks": self.swapped_blocks, "prefill_steps": self.prefill_steps,
                 "decode_steps": self.decode_steps, "prompt_tokens": self.prompt_tokens,
                 "generated_tokens": self.generated_tokens,
                 "tokens_per_second": self.generated_tokens / self.busy_seconds if self.busy_seconds else 0.0,

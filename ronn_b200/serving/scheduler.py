@@ -75,6 +75,34 @@ class Scheduler:
         except Exception:
             pass
 
+    _PREEMPT_MODES = {"recompute": 0, "swap": 1, "auto": 2}
+
+    def set_preemption(self, mode: str, num_cpu_blocks: int, auto_min_tokens: int = 64) -> None:
+        """How a preempted sequence keeps its KV cache: ``recompute`` (drop it), ``swap`` (copy its blocks to a host
+        pool of ``num_cpu_blocks`` blocks and back on resume) or ``auto`` (swap sequences with at least
+        ``auto_min_tokens`` cached tokens).  Before any request is added."""
+        if mode not in self._PREEMPT_MODES:
+            raise SessionError(f"unknown preemption mode '{mode}'")
+        if self._lib.ronn_sched_set_swap(self._h, self._PREEMPT_MODES[mode], int(num_cpu_blocks), int(auto_min_tokens)):
+            raise SessionError("preemption mode must be set on an empty scheduler with a non-negative host pool")
+
+    def swaps(self):
+        """Block copies to run before this step's forward pass: (out_src, out_dst, in_src, in_dst) int32 arrays;
+        device block -> host block first, then host block -> device block."""
+        cnt = np.zeros(2, dtype=np.int32)
+        self._lib.ronn_sched_swap_counts(self._h, cnt.ctypes.data_as(_native.c_i32p))
+        arrs = [np.zeros(max(int(cnt[0]), 1), dtype=np.int32), np.zeros(max(int(cnt[0]), 1), dtype=np.int32),
+                np.zeros(max(int(cnt[1]), 1), dtype=np.int32), np.zeros(max(int(cnt[1]), 1), dtype=np.int32)]
+        if cnt[0] or cnt[1]:
+            self._lib.ronn_sched_get_swaps(self._h, *[a.ctypes.data_as(_native.c_i32p) for a in arrs])
+        return arrs[0][:cnt[0]], arrs[1][:cnt[0]], arrs[2][:cnt[1]], arrs[3][:cnt[1]]
+
+    def swap_stats(self) -> dict:
+        out = np.zeros(4, dtype=np.int64)
+        self._lib.ronn_sched_swap_stats(self._h, out.ctypes.data_as(_native.c_i64p))
+        return {"swap_preemptions": int(out[0]), "swapped_out_blocks": int(out[1]), "swapped_in_blocks": int(out[2]),
+                "free_cpu_blocks": int(out[3])}
+
     def add(self, req_id: int, prompt: List[int], max_new_tokens: int, priority: int = 2) -> None:
         arr = np.ascontiguousarray(prompt, dtype=np.int32)
         rc = self._lib.ronn_sched_add(self._h, req_id, arr.ctypes.data_as(_native.c_i32p), len(arr), max_new_tokens,

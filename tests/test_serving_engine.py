@@ -120,6 +120,79 @@ def test_scheduler_preemption_recompute_and_priority():
     assert sb.req_ids.tolist() == [1] and sb.n_tokens == n_before
 
 
+def test_scheduler_preemption_swap_keeps_the_cache():
+    s = Scheduler(16, 6, 4, 256, policy="priority")
+    s.set_preemption("swap", 8)
+    s.add(1, list(range(30)), 40, priority=int(Priority.LOW))
+    s.add(2, list(range(30)), 40, priority=int(Priority.CRITICAL))
+    buf = HostBatchBuffers(256, 4, 8, False)
+    s.schedule()
+    s.fill(buf, PLAN_PREFILL)
+    s.commit(np.array([5, 5], dtype=np.int32))
+    blocks_before = []
+    for _ in range(30):
+        blocks_before = s.blocks(1)
+        k = s.schedule()
+        if s.preemptions(1):
+            break
+        sb = s.fill(buf, k)
+        s.commit(np.full(sb.n_items, 5, dtype=np.int32))
+    o_src, o_dst, i_src, i_dst = s.swaps()
+    n_tok = len(s.tokens(1))
+    # the victim's cached tokens (all but the one sampled last) went to the host pool, block by block
+    assert s.state(1) == RequestState.PREEMPTED and len(s.blocks(1)) == 0
+    assert o_src.tolist() == blocks_before[:len(o_src)] and len(o_src) == -(-(n_tok - 1) // 16) and len(i_src) == 0
+    assert sorted(o_dst.tolist()) == sorted(set(o_dst.tolist())) and all(0 <= c < 8 for c in o_dst)
+    st = s.swap_stats()
+    assert st["swap_preemptions"] == 1 and st["swapped_out_blocks"] == len(o_src) and st["free_cpu_blocks"] == 8 - len(o_src)
+    sb = s.fill(buf, PLAN_DECODE)
+    s.commit(np.full(sb.n_items, 5, dtype=np.int32))
+    s.cancel(2)
+    # resume: the blocks come back and only the last token is computed (no recompute of the prompt)
+    assert s.schedule() == PLAN_PREFILL
+    o2, _, i_src2, i_dst2 = s.swaps()
+    sb = s.fill(buf, PLAN_PREFILL)
+    assert len(o2) == 0 and i_src2.tolist() == o_dst.tolist() and i_dst2.tolist() == s.blocks(1)[:len(i_dst2)]
+    assert sb.req_ids.tolist() == [1] and sb.n_tokens == 1 and int(buf.field("positions")[0]) == n_tok - 1
+    s.commit(np.array([5], dtype=np.int32))
+    assert s.state(1) == RequestState.DECODING
+    s.schedule()                                        # host blocks are reusable from the next step on
+    assert s.swap_stats()["free_cpu_blocks"] == 8 and s.swap_stats()["swapped_in_blocks"] == len(i_src2)
+    # cancelling a swapped-out request returns its host blocks; a full host pool falls back to recompute
+    t = Scheduler(16, 6, 4, 256)
+    t.set_preemption("swap", 1)
+    t.add(1, list(range(30)), 40)
+    t.add(2, list(range(30)), 40)
+    t.schedule(); t.fill(buf, PLAN_PREFILL); t.commit(np.array([5, 5], dtype=np.int32))
+    for _ in range(30):
+        k = t.schedule()
+        if t.stats()["preemptions"]:
+            break
+        sb = t.fill(buf, k)
+        t.commit(np.full(sb.n_items, 5, dtype=np.int32))
+    assert t.swap_stats()["swap_preemptions"] == 0 and len(t.swaps()[0]) == 0      # 3 blocks do not fit a pool of 1
+    with pytest.raises(Exception):
+        t.set_preemption("swap", 4)                     # not on a scheduler that has requests
+    with pytest.raises(Exception):
+        Scheduler(16, 6, 4, 256).set_preemption("sometimes", 4)
+
+
+@pytest.mark.parametrize("mode", ["swap", "auto"])
+def test_engine_swap_preemption_keeps_outputs(tiny, mode):
+    grow = [[3 + i] * 15 for i in range(4)]            # one block each at admission, three each by the end
+    want = [reference_greedy(tiny, p, 30) for p in grow]
+    tight = engine(tiny, num_blocks=7, preemption=mode, num_cpu_blocks=16, swap_min_tokens=8)
+    got = tight.generate(grow, SamplingParams(max_new_tokens=30))
+    st = tight.stats()
+    assert got == want and st["preemptions"] >= 1
+    assert st["swap_preemptions"] >= 1 and st["swapped_in_blocks"] == st["swapped_out_blocks"] > 0
+    assert st["swapped_blocks"] == 2 * st["swapped_out_blocks"] and st["free_cpu_blocks"] == 16
+    # "auto" below its threshold recomputes instead
+    lazy = engine(tiny, num_blocks=7, preemption="auto", num_cpu_blocks=16, swap_min_tokens=10_000)
+    assert lazy.generate(grow, SamplingParams(max_new_tokens=30)) == want
+    assert lazy.stats()["swap_preemptions"] == 0 and lazy.stats()["preemptions"] >= 1
+
+
 def test_prefix_cache_shares_blocks():
     s = Scheduler(16, 32, 4, 256, enable_prefix_cache=True)
     common = list(range(40))
