@@ -22,6 +22,10 @@ int32_t ronn_sched_commit(void*, const int32_t*, int32_t, int32_t*);
 int32_t ronn_sched_num_waiting(void*);
 int32_t ronn_sched_num_running(void*);
 int32_t ronn_sched_num_free_blocks(void*);
+int32_t ronn_sched_set_swap(void*, int32_t, int32_t, int32_t);
+void ronn_sched_swap_counts(void*, int32_t*);
+void ronn_sched_get_swaps(void*, int32_t*, int32_t*, int32_t*, int32_t*);
+void ronn_sched_swap_stats(void*, int64_t*);
 void* ronn_pool_new(uint64_t, uint64_t, uint64_t, uint64_t);
 void ronn_pool_free(void*);
 void* ronn_pool_alloc(void*, uint64_t);
@@ -47,10 +51,16 @@ static uint32_t rnd(uint32_t n) {
     }                                                                    \
   } while (0)
 
-static int test_scheduler(int policy, int prefix_cache, int chunk) {
-  const int blocks = 40, max_seqs = 6, max_tokens = 96, max_blocks = 10;
+static int64_t total_swapped_blocks = 0;
+
+static int test_scheduler(int policy, int prefix_cache, int chunk, int swap_mode) {
+  // few blocks when swapping is exercised, so that decode steps preempt
+  const int blocks = swap_mode ? 14 : 40, max_seqs = 6, max_tokens = 96, max_blocks = 10, cpu_blocks = 12;
   void* s = ronn_sched_new(16, blocks, max_seqs, max_tokens, chunk, policy, prefix_cache, max_blocks);
   CHECK(s != nullptr);
+  if (swap_mode) CHECK(ronn_sched_set_swap(s, swap_mode, cpu_blocks, 24) == 0);
+  std::vector<int32_t> so_src(size_t(blocks), 0), so_dst(size_t(blocks), 0), si_src(size_t(blocks), 0), si_dst(size_t(blocks), 0);
+  std::vector<int> cpu_owner(size_t(cpu_blocks), 0);                       // 1 while a host block holds a swapped-out copy
   int added = 0;
   for (int64_t id = 0; id < 25; ++id) {
     const int plen = 1 + int(rnd(70)), newt = 1 + int(rnd(20));
@@ -68,7 +78,26 @@ static int test_scheduler(int policy, int prefix_cache, int chunk) {
   if (ronn_sched_cancel(s, 1) == 0) cancelled = 1;                        // still waiting: leaves the queue for good
   for (int step = 0; step < 5000; ++step) {
     const int kind = ronn_sched_schedule(s);
-    if (kind == 0) break;
+    int32_t swaps[2] = {0, 0};
+    ronn_sched_swap_counts(s, swaps);
+    CHECK(swaps[0] >= 0 && swaps[0] <= blocks && swaps[1] >= 0 && swaps[1] <= blocks);
+    CHECK(swap_mode || (swaps[0] == 0 && swaps[1] == 0));
+    ronn_sched_get_swaps(s, so_src.data(), so_dst.data(), si_src.data(), si_dst.data());
+    for (int i = 0; i < swaps[0]; ++i) {                                     // device -> host: into a host block nobody holds
+      CHECK(so_src[size_t(i)] >= 0 && so_src[size_t(i)] < blocks && so_dst[size_t(i)] >= 0 && so_dst[size_t(i)] < cpu_blocks);
+      CHECK(cpu_owner[size_t(so_dst[size_t(i)])] == 0);
+      cpu_owner[size_t(so_dst[size_t(i)])] = 1;
+    }
+    for (int i = 0; i < swaps[1]; ++i) {                                     // host -> device: from a block that was filled
+      CHECK(si_dst[size_t(i)] >= 0 && si_dst[size_t(i)] < blocks && si_src[size_t(i)] >= 0 && si_src[size_t(i)] < cpu_blocks);
+      CHECK(cpu_owner[size_t(si_src[size_t(i)])] == 1);
+      cpu_owner[size_t(si_src[size_t(i)])] = 0;
+    }
+    if (kind == 0) {
+      if (ronn_sched_num_waiting(s) == 0 && ronn_sched_num_running(s) == 0) break;
+      CHECK(swap_mode != 0);                                               // an all-preempted step: the next one resumes
+      continue;
+    }
     const int n_items = ronn_sched_plan_size(s);
     CHECK(n_items > 0 && n_items <= max_seqs);
     CHECK(ronn_sched_plan_tokens(s) <= max_tokens);
@@ -82,6 +111,10 @@ static int test_scheduler(int policy, int prefix_cache, int chunk) {
   CHECK(finished + cancelled == added);
   CHECK(ronn_sched_num_waiting(s) == 0 && ronn_sched_num_running(s) == 0);
   if (!prefix_cache) CHECK(ronn_sched_num_free_blocks(s) == blocks);
+  int64_t sw[4] = {0, 0, 0, 0};
+  ronn_sched_swap_stats(s, sw);
+  CHECK(sw[1] == sw[2] && sw[3] == (swap_mode ? cpu_blocks : 0));          // everything swapped out came back
+  total_swapped_blocks += sw[1];
   ronn_sched_free(s);
   return 0;
 }
@@ -131,7 +164,9 @@ int main() {
   for (int policy = 0; policy < 2; ++policy)
     for (int prefix = 0; prefix < 2; ++prefix)
       for (int chunk = 0; chunk <= 32; chunk += 32)
-        if (test_scheduler(policy, prefix, chunk)) return 1;
+        for (int swap = 0; swap < 3; ++swap)
+          if (test_scheduler(policy, prefix, chunk, swap)) return 1;
+  CHECK(total_swapped_blocks > 0);                                          // the tight configurations did swap
   if (test_pool()) return 1;
   if (test_graph()) return 1;
   std::printf("host_selftest: ok\n");
