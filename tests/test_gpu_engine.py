@@ -66,3 +66,25 @@ def test_concurrent_part_batches_give_the_same_tokens():
         if streams > 1:
             assert len(eng._part_streams) == streams
     assert outs[0] == outs[1] == outs[2]
+
+
+def test_swap_preemption_on_the_device_cache():
+    """With too few KV blocks for all sequences, preempted ones are copied to the host pool and back; the tokens match
+    an engine that never preempts (up to bf16 ties: a resumed token goes through the prefill path)."""
+    from ronn_b200.api.model import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    cfg = GPT2Config.tiny(n_layer=2, n_embd=128, n_head=2, vocab_size=512, n_positions=256)
+    model = Model.from_graph(build_gpt2(cfg, dtype=torch.bfloat16, seed=8))
+    prompts = [[3 + i] * 15 for i in range(4)]            # one block each at admission, three each by the end
+    dev = torch.device("cuda", 0)
+    roomy = LLMEngine(model, EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256, num_blocks=64,
+                                          dtype="bf16"), device=dev)
+    want = roomy.generate(prompts, SamplingParams(max_new_tokens=30))
+    tight = LLMEngine(model, EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256, num_blocks=7,
+                                          dtype="bf16", preemption="swap", num_cpu_blocks=16), device=dev)
+    got = tight.generate(prompts, SamplingParams(max_new_tokens=30))
+    st = tight.stats()
+    assert st["swap_preemptions"] >= 1 and st["swapped_in_blocks"] == st["swapped_out_blocks"] > 0
+    agree = sum(a == b for x, y in zip(got, want) for a, b in zip(x, y))
+    assert agree >= int(0.9 * 120), (agree, got, want)
