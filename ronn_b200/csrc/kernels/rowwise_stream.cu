@@ -103,7 +103,21 @@ __global__ void __launch_bounds__(RS_WARPS * 32, 4) rowwise_stream_kernel(const 
     if (MODE == 0 || MODE == 1) {
       T* y = static_cast<T*>(a.y) + row * a.ld_y;
       T* so = a.sum_out ? static_cast<T*>(a.sum_out) + row * a.ld_y : nullptr;
-      float s = 0.f;
+      // One pass over the row for the statistics.  LayerNorm accumulates sum and sum of squares of (v - shift) with
+      // the row's first value as the shift, so that var = E[(v - shift)^2] - (E[v - shift])^2 does not cancel when the
+      // mean is large against the spread (the kernel is bound by instruction issue: a separate pass for the squared
+      // deviations costs a shared-memory read and a conversion per value).
+      float shift = 0.f;
+      if (MODE == 0) {
+        float first[8];
+        unpack8<T>(xs[0], first);
+        shift = first[0];
+        if (HAS_RES) {
+          unpack8<T>(rs[0], first);
+          shift += first[0];
+        }
+      }
+      float s = 0.f, s2 = 0.f;
 #pragma unroll 4
       for (int c = lane; c < nchunk; c += 32) {
         float v[8];
@@ -120,26 +134,26 @@ __global__ void __launch_bounds__(RS_WARPS * 32, 4) rowwise_stream_kernel(const 
         } else if (so) {
           *reinterpret_cast<Vec8*>(so + c * 8) = xs[c];
         }
+        if (MODE == 1) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s += MODE == 1 ? v[i] * v[i] : v[i];
+          for (int i = 0; i < 8; ++i) s2 = fmaf(v[i], v[i], s2);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float d = v[i] - shift;
+            s += d;
+            s2 = fmaf(d, d, s2);
+          }
+        }
       }
       float mean = 0.f, inv;
       if (MODE == 1) {
-        inv = rsqrtf(warp_sum(s) * inv_h + a.eps);
+        inv = rsqrtf(warp_sum(s2) * inv_h + a.eps);
       } else {
-        mean = warp_sum(s) * inv_h;
-        float q = 0.f;
-  #pragma unroll 4
-      for (int c = lane; c < nchunk; c += 32) {
-          float v[8];
-          unpack8<T>(xs[c], v);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float d = v[i] - mean;
-            q += d * d;
-          }
-        }
-        inv = rsqrtf(warp_sum(q) * inv_h + a.eps);
+        const float d = warp_sum(s) * inv_h;
+        const float var = fmaxf(warp_sum(s2) * inv_h - d * d, 0.f);
+        mean = shift + d;
+        inv = rsqrtf(var + a.eps);
       }
 #pragma unroll 4
       for (int c = lane; c < nchunk; c += 32) {

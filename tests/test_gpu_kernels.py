@@ -143,6 +143,19 @@ def test_many_rows_streaming_norms(K, H, rows, dtype):
     K.check_status()
 
 
+def test_many_rows_layernorm_with_a_large_mean(K):
+    """The streaming kernel takes its statistics in one pass around a per-row shift: rows whose mean dwarfs their spread
+    must not lose the variance to cancellation."""
+    rows, H = 4096, 1024
+    x = (torch.randn(rows, H, device="cuda") * 0.5 + torch.linspace(-300, 300, rows, device="cuda")[:, None]).to(torch.float16)
+    g, b = _rand(H, dtype=torch.float16), _rand(H, dtype=torch.float16)
+    y = K.layernorm(x, g, b, 1e-5)
+    ref = F.layer_norm(x.float(), (H,), g.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=2e-2)
+    small = K.layernorm(x[:64].contiguous(), g, b, 1e-5)          # the few-rows kernel (two-pass statistics)
+    torch.testing.assert_close(y[:64].float(), small.float(), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("cols,rows", [(128, 5000), (1024, 2048), (1000, 4097), (5000, 2100)])
 def test_many_rows_streaming_softmax(K, cols, rows):
     x = _rand(rows, cols, scale=3.0)
