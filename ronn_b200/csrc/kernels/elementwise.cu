@@ -453,7 +453,29 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
     for (int k = 0; k < 8; ++k) take(f[k], head + c * 8 + k);
   }
   }
-  for (int i = head + nvec * 8 + threadIdx.x; i < cols; i += blockDim.x) take(Cvt<T>::to_f(xr[i]), i);
+  int done = head + nvec * 8;
+  if constexpr (sizeof(T) == 4) {
+    // fp32 rows (logits): the same scheme with 16-byte loads of four values
+    int head4 = int(((16u - unsigned(reinterpret_cast<uintptr_t>(xr) & 15u)) & 15u) / 4u);
+    if (head4 > cols) head4 = cols;
+    const int nvec4 = (cols - head4) >> 2;
+    if (int(threadIdx.x) < head4) take(xr[threadIdx.x], threadIdx.x);
+    const float4* xv4 = reinterpret_cast<const float4*>(xr + head4);
+    int c = threadIdx.x;
+    for (; c + int(blockDim.x) < nvec4; c += 2 * blockDim.x) {
+      const float4 p0 = xv4[c], p1 = xv4[c + blockDim.x];
+      const int i0 = head4 + c * 4, i1 = head4 + (c + int(blockDim.x)) * 4;
+      take(p0.x, i0); take(p0.y, i0 + 1); take(p0.z, i0 + 2); take(p0.w, i0 + 3);
+      take(p1.x, i1); take(p1.y, i1 + 1); take(p1.z, i1 + 2); take(p1.w, i1 + 3);
+    }
+    for (; c < nvec4; c += blockDim.x) {
+      const float4 p0 = xv4[c];
+      const int i0 = head4 + c * 4;
+      take(p0.x, i0); take(p0.y, i0 + 1); take(p0.z, i0 + 2); take(p0.w, i0 + 3);
+    }
+    done = head4 + nvec4 * 4;
+  }
+  for (int i = done + threadIdx.x; i < cols; i += blockDim.x) take(Cvt<T>::to_f(xr[i]), i);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float om = __shfl_xor_sync(0xffffffffu, m, o);

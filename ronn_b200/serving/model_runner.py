@@ -307,7 +307,7 @@ class DecoderRunner:
             if not decode:
                 x = ops.gather_rows(x, b["sample_index_clamped"])
             x = self._norm(x, self.lnf)
-        logits = ops.gemm(x, self.lm_head, out_fp32=True)
+        logits = ops.lm_head(x, self.lm_head)
         if want_logits:
             if self.tp != 1:
                 raise SessionError("full logits are only available without tensor parallelism")

@@ -33,6 +33,9 @@ class TorchOps:
             y = y + residual
         return y.float() if out_fp32 else y
 
+    def lm_head(self, x, w_nk):
+        return self.gemm(x, w_nk, out_fp32=True)
+
     def layernorm(self, x, w, b, eps):
         return F.layer_norm(x.float(), (x.shape[-1],), w.float(), None if b is None else b.float(), eps).to(x.dtype)
 
@@ -119,6 +122,14 @@ class KernelOps:
 
     def gemm(self, a, w_nk, bias=None, residual=None, activation="", out_fp32=False):
         return self.K.gemm(a, w_nk, bias, residual, activation, out_fp32=out_fp32)
+
+    def lm_head(self, x, w_nk):
+        """fp32 logits [rows, vocab].  The buffer's row stride is padded to a multiple of 8 values: with an odd
+        vocabulary (50257) as the stride every row would start off a 16-byte boundary and the GEMM epilogue would fall
+        back to scalar stores (measured: 113 us instead of about 30 for 256 x 50257 x 1024)."""
+        n = w_nk.shape[0]
+        buf = torch.empty((x.shape[0], -(-n // 8) * 8), dtype=torch.float32, device=x.device)
+        return self.K.gemm(x, w_nk, out=buf[:, :n], out_fp32=True)
 
     def layernorm(self, x, w, b, eps):
         return self.K.layernorm(x, w, b, eps)
