@@ -84,27 +84,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Single-thread wait with a short sleep between polls, for a role that shares its scheduler with busy warps (the
-// weight-TMA and MMA threads of the convolution share theirs with the gather warps).
-__device__ __forceinline__ bool mbar_wait_polite(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                                 uint32_t* status, uint32_t code, uint32_t sleep_ns = 32) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t polls = 0;
-  while (true) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++polls & 31u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0u, code);
-        return false;
-      }
-    }
-  }
-}
-
 // Wait of a whole warp for an event that is far away (an epilogue warp waiting for its accumulator): lane 0 polls with
 // a sleep between polls and the result is broadcast, so the warp does not compete for issue slots with the warps
 // that produce the event.  Returns false (to all lanes) when the wait was abandoned.
@@ -153,9 +132,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
 // ------------------------------------------------------------------------- TMEM
