@@ -92,10 +92,11 @@ def host():
         _sig(lib, "ronn_sched_fill", I32, [V, V, V, V, V, V, V, V, V, V, I32])
         _sig(lib, "ronn_sched_commit", I32, [V, V, I32, V])
         _sig(lib, "ronn_sched_abort_step", None, [V])
-        for name in ("state", "num_tokens", "prompt_len", "preemptions"):
+        for name in ("state", "num_tokens", "prompt_len", "preemptions", "num_computed"):
             _sig(lib, f"ronn_sched_{name}", I32, [V, I64])
         _sig(lib, "ronn_sched_get_tokens", I32, [V, I64, c_i32p, I32])
         _sig(lib, "ronn_sched_get_blocks", I32, [V, I64, c_i32p, I32])
+        _sig(lib, "ronn_sched_get_cpu_blocks", I32, [V, I64, c_i32p, I32])
         _sig(lib, "ronn_sched_forget", None, [V, I64])
         for name in ("num_waiting", "num_running", "num_free_blocks"):
             _sig(lib, f"ronn_sched_{name}", I32, [V])

@@ -596,6 +596,21 @@ int32_t ronn_sched_get_blocks(void* h, int64_t id, int32_t* out, int32_t cap) {
   memcpy(out, it->second.blocks.data(), size_t(n) * 4);
   return n;
 }
+// Host-pool blocks holding the request's cache while it is swapped out (empty otherwise).
+int32_t ronn_sched_get_cpu_blocks(void* h, int64_t id, int32_t* out, int32_t cap) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  auto it = s->reqs.find(id);
+  if (it == s->reqs.end()) return -1;
+  int32_t n = std::min<int32_t>(cap, int32_t(it->second.cpu_blocks.size()));
+  memcpy(out, it->second.cpu_blocks.data(), size_t(n) * 4);
+  return n;
+}
+// Tokens of the request whose keys and values are in the cache (device or host copy).
+int32_t ronn_sched_num_computed(void* h, int64_t id) {
+  Scheduler* s = static_cast<Scheduler*>(h);
+  auto it = s->reqs.find(id);
+  return it == s->reqs.end() ? -1 : it->second.num_computed;
+}
 int32_t ronn_sched_preemptions(void* h, int64_t id) {
   Scheduler* s = static_cast<Scheduler*>(h);
   auto it = s->reqs.find(id);

@@ -2,3 +2,4 @@
 from .config import EngineConfig
 from .request import FinishReason, Priority, Request, RequestState, SamplingParams
 from .engine import LLMEngine
+from .cache import BlockLocation, BlockManager, BlockMetadata, CachePrecision, PageTable

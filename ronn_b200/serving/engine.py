@@ -403,6 +403,12 @@ class LLMEngine:
             steps += 1
         return [self.requests[i].output_tokens for i in ids]
 
+    @property
+    def block_manager(self):
+        """Page table, block metadata and pool sizes of the KV cache (``serving/cache.py``)."""
+        from .cache import BlockManager
+        return BlockManager(self)
+
     def stats(self) -> Dict[str, object]:
         d = self.metrics.as_dict()
         d.update(self.sched.stats())

@@ -165,6 +165,15 @@ class Scheduler:
         n = self._lib.ronn_sched_get_blocks(self._h, req_id, out.ctypes.data_as(_native.c_i32p), len(out))
         return out[:max(n, 0)].tolist()
 
+    def cpu_blocks(self, req_id: int) -> List[int]:
+        """Host-pool blocks that hold the request's cache while it is swapped out."""
+        out = np.empty(self.max_blocks_per_seq, dtype=np.int32)
+        n = self._lib.ronn_sched_get_cpu_blocks(self._h, req_id, out.ctypes.data_as(_native.c_i32p), len(out))
+        return out[:max(n, 0)].tolist()
+
+    def num_computed(self, req_id: int) -> int:
+        return self._lib.ronn_sched_num_computed(self._h, req_id)
+
     def preemptions(self, req_id: int) -> int:
         return self._lib.ronn_sched_preemptions(self._h, req_id)
 

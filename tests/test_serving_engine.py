@@ -321,3 +321,33 @@ def test_part_batch_split_is_off_on_cpu_and_for_small_batches():
                                      backend="torch", decode_streams=4), device="cpu")
     assert eng._split_rows(256) is None          # operator backend: one batch
     assert eng._dense_prefill_plan(4, 1) is None
+
+
+def test_block_manager_view_follows_the_scheduler(tiny):
+    from ronn_b200.serving import BlockLocation, CachePrecision
+    eng = engine(tiny, num_blocks=7, preemption="swap", num_cpu_blocks=16)
+    bm = eng.block_manager
+    assert bm.block_size == 16 and bm.precision == CachePrecision.FP32
+    assert bm.gpu_pool == {"total_blocks": 7, "free_blocks": 7} and bm.cpu_pool == {"total_blocks": 16, "free_blocks": 16}
+    assert bm.vram_budget == 7 * bm.block_bytes and bm.utilization() == 0.0
+    ids = [eng.add_request([3 + i] * 15, SamplingParams(max_new_tokens=30)) for i in range(4)]
+    seen_cpu = False
+    for _ in range(200):
+        eng.step()
+        table = bm.page_table.as_dict()
+        for (rid, lb), (loc, phys) in table.items():
+            md = bm.metadata(rid, lb)
+            assert md.location == loc and 0 <= md.num_tokens <= 16 and md.ref_count >= 1
+            if loc == BlockLocation.CPU:
+                seen_cpu = True
+                assert 0 <= phys < 16
+            else:
+                assert loc == BlockLocation.UNIFIED and 0 <= phys < 7          # a CPU engine reads its cache in place
+        if not eng.has_unfinished():
+            break
+    assert seen_cpu and not eng.has_unfinished()
+    assert bm.gpu_pool["free_blocks"] == 7 and bm.cpu_pool["free_blocks"] == 16
+    with pytest.raises(SessionError):
+        CachePrecision.INT4.require_supported()
+    with pytest.raises(KeyError):
+        bm.page_table.lookup(ids[0], 0)                   # finished: no blocks left
