@@ -43,25 +43,60 @@ def reference_arm():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: through NVML inside the process every 25 ms
+    (read-only queries; the device is found by the UUID CUDA reports, so CUDA_VISIBLE_DEVICES does not matter), or, when
+    NVML cannot be loaded, by running nvidia-smi every 150 ms."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.index, self.samples, self._stop, self._t = index, [], threading.Event(), None
+        self.source = "nvidia-smi"
+        self._nvml = self._handle = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = "GPU-" + str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            try:
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._sample_nvml(pynvml)                  # one trial query: any failure falls back to nvidia-smi
+            self.samples.clear()
+            self._nvml, self.source = pynvml, "nvml"
+        except Exception:
+            self._nvml = self._handle = None
+
+    def _sample_nvml(self, nv):
+        sm = float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+        get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        mask = int(get(self._handle))
+        bit = lambda *names: next((int(getattr(nv, n)) for n in names if hasattr(nv, n)), 0)
+        flags = [
+            mask & bit("nvmlClocksEventReasonHwSlowdown", "nvmlClocksThrottleReasonHwSlowdown"),
+            mask & bit("nvmlClocksEventReasonHwThermalSlowdown", "nvmlClocksThrottleReasonHwThermalSlowdown"),
+            mask & bit("nvmlClocksEventReasonSwThermalSlowdown", "nvmlClocksThrottleReasonSwThermalSlowdown"),
+            mask & bit("nvmlClocksEventReasonSwPowerCap", "nvmlClocksThrottleReasonSwPowerCap"),
+        ]
+        self.samples.append([str(sm), str(self._max), "0"] + ["Active" if f else "Not Active" for f in flags])
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
-                f = [x.strip() for x in out.strip().split(",")]
-                if len(f) >= 7:
-                    self.samples.append(f)
+                if self._nvml is not None:
+                    self._sample_nvml(self._nvml)
+                else:
+                    out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                    f = [x.strip() for x in out.strip().split(",")]
+                    if len(f) >= 7:
+                        self.samples.append(f)
             except Exception:
                 pass
-            self._stop.wait(0.15)
+            self._stop.wait(0.025 if self._nvml is not None else 0.15)
 
     def start(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -79,7 +114,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(self.samples)}
+                "reasons": sorted(reasons), "samples": len(self.samples), "source": self.source}
 
 
 def main():
