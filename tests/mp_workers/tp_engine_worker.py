@@ -28,12 +28,26 @@ def main():
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 17, 40, 64, 9, 33)]
 
+    # optional: the tensor-parallel run gets a cache too small for all sequences and swaps preempted ones to the host
+    tight = os.environ.get("RONN_TEST_TIGHT_BLOCKS")
+    stats = {}
+    new_tokens = 8
+    if tight:
+        prompts = [[3 + i] * 15 for i in range(4)]       # one block each at admission, three each by the end
+        new_tokens = 30
+
     def run(comm, tp_comm):
-        ecfg = EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256, num_blocks=64,
+        extra = {}
+        if comm is not None and tight:
+            extra = dict(num_blocks=int(tight), preemption="swap", num_cpu_blocks=32)
+        ecfg = EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256,
                             dtype="fp32" if mode == "cpu" else "bf16", backend=backend, tp_size=world if comm else 1,
-                            tp_comm=tp_comm, use_cuda_graph=(mode != "cpu"))
+                            tp_comm=tp_comm, use_cuda_graph=(mode != "cpu"), **{"num_blocks": 64, **extra})
         eng = LLMEngine(model, ecfg, device=dev, comm=comm)
-        return eng.generate(prompts, SamplingParams(max_new_tokens=8))
+        toks = eng.generate(prompts, SamplingParams(max_new_tokens=new_tokens))
+        if comm is not None:
+            stats.update(eng.stats())
+        return toks
 
     comm = make_comm("nccl" if mode in ("cpu", "nccl") else "fused", dev)
     tp = run(comm, "nccl" if mode != "fused" else "fused")
@@ -49,7 +63,9 @@ def main():
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump({"agree": agree, "total": total, "same_across_ranks": same_across_ranks, "world": world,
-                       "fused_calls": getattr(comm, "fused_calls", 0)}, f)
+                       "fused_calls": getattr(comm, "fused_calls", 0),
+                       "swap_preemptions": stats.get("swap_preemptions", 0),
+                       "swapped_in_blocks": stats.get("swapped_in_blocks", 0)}, f)
     torch.distributed.barrier()
     if mode != "cpu":
         torch.cuda.synchronize()

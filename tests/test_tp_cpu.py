@@ -27,6 +27,16 @@ def test_tp_engine_on_cpu_ranks_matches_single_rank(tmp_path, world):
     assert r["agree"] == r["total"] == 48          # fp32: sharded and unsharded runs pick the same tokens
 
 
+def test_tp_engine_swap_preemption_on_cpu_ranks(tmp_path):
+    """Every rank runs the same scheduler, so every rank swaps the same blocks of its own shard of the cache."""
+    out = tmp_path / "r.json"
+    p = launch(2, "tp_engine_worker.py", ["cpu", str(out)], 29617, env={"RONN_TEST_TIGHT_BLOCKS": "7"})
+    assert p.returncode == 0, p.stderr[-3000:]
+    r = json.loads(out.read_text())
+    assert r["same_across_ranks"] and r["agree"] == r["total"] == 120
+    assert r["swap_preemptions"] >= 1 and r["swapped_in_blocks"] >= 1
+
+
 def test_head_and_vocab_sharding_cover_everything():
     from ronn_b200.serving.model_runner import shard_heads
     for heads, tp in ((12, 8), (20, 8), (16, 8), (16, 3), (4, 4)):
