@@ -272,9 +272,59 @@ def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24):
     return res
 
 
+def bench_serving(concurrency=(1, 4, 16, 32), prompt=128, new_tokens=64, model="gpt2-medium", device=None):
+    """Closed-loop serving at fixed concurrency: `c` requests in flight (each replaced when it finishes, 3 c requests in
+    all), reporting tokens/s and the TTFT / inter-token-latency percentiles of the continuous-batching design's test
+    plan (docs/new/RONN-Continuous-Batching-Branch-Prompt.md:442-470).  On a CUDA device the engine uses the kernel
+    backend in bf16; on CPU the PyTorch backend in fp32 (use a tiny model there)."""
+    from . import Model
+    from .models.gpt2 import GPT2Config, build_gpt2
+    from .serving import EngineConfig, LLMEngine, SamplingParams
+    cuda = torch.cuda.is_available() if device is None else torch.device(device).type == "cuda"
+    dev = torch.device("cuda", 0) if cuda else torch.device("cpu")
+    cfg = GPT2Config.medium() if model == "gpt2-medium" else GPT2Config.tiny()
+    graph = build_gpt2(cfg, dtype=torch.bfloat16 if cuda else torch.float32)
+    m = Model.from_graph(graph)
+    out = []
+    g = torch.Generator().manual_seed(0)
+    for c in concurrency:
+        max_len = prompt + new_tokens + 16
+        blocks = (c + 1) * (-(-max_len // 16)) + 8          # sized for the run, not for the whole device memory
+        eng = LLMEngine(m, EngineConfig(max_num_seqs=max(c, 1), max_batch_tokens=max(2048, prompt * 4),
+                                        max_model_len=max_len, num_blocks=blocks, dtype="bf16" if cuda else "fp32",
+                                        backend="kernels" if cuda else "torch"), device=dev)
+        total = 3 * c
+        make = lambda: torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist()
+        eng.generate([make()], SamplingParams(max_new_tokens=4))                    # warm-up: graphs, workspaces
+        eng.metrics.ttft.clear()
+        eng.metrics.itl.clear()
+        submitted = 0
+        live = set()
+        t0 = time.perf_counter()
+        generated = 0
+        while submitted < total or live:
+            while submitted < total and len(live) < c:
+                live.add(eng.add_request(make(), SamplingParams(max_new_tokens=new_tokens)))
+                submitted += 1
+            eng.step()
+            for rid in [r for r in live if eng.requests[r].finished]:
+                generated += len(eng.requests[rid].output_tokens)
+                live.discard(rid)
+        wall = time.perf_counter() - t0
+        d = eng.metrics.as_dict()
+        out.append({"concurrency": c, "requests": total, "tokens_per_s": round(generated / wall, 1),
+                    "ttft_ms": {k: round(d[f"ttft_{k}"] * 1e3, 2) for k in ("p50", "p95", "p99")},
+                    "itl_ms": {k: round(d[f"itl_{k}"] * 1e3, 3) for k in ("p50", "p95", "p99")}})
+        del eng                                             # the next engine allocates its own cache
+        if cuda:
+            torch.cuda.empty_cache()
+    return {"model": model, "prompt": prompt, "new_tokens": new_tokens, "device": str(dev), "results": out}
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["resnet18", "mlp784", "distilbert", "bitnet"])
+    ap.add_argument("what", choices=["resnet18", "mlp784", "distilbert", "bitnet", "serving"])
+    ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "gpt2-tiny"])
     ap.add_argument("--layers", type=int, default=24)
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--seq", type=int, default=128)
@@ -284,6 +334,8 @@ def main():
         res = bench_resnet18(a.batch or 32, a.iters or 50)
     elif a.what == "mlp784":
         res = bench_mlp784(a.iters or 2000)
+    elif a.what == "serving":
+        res = bench_serving(model=a.model, prompt=a.seq, new_tokens=a.iters or 64)
     elif a.what == "bitnet":
         res = bench_bitnet(a.batch or 128, a.iters or 32, layers=a.layers)
     else:

@@ -351,3 +351,12 @@ def test_block_manager_view_follows_the_scheduler(tiny):
         CachePrecision.INT4.require_supported()
     with pytest.raises(KeyError):
         bm.page_table.lookup(ids[0], 0)                   # finished: no blocks left
+
+
+def test_closed_loop_serving_bench_runs_on_cpu():
+    from ronn_b200.bench_models import bench_serving
+    r = bench_serving(concurrency=(1, 4), prompt=12, new_tokens=5, model="gpt2-tiny", device="cpu")
+    assert [x["concurrency"] for x in r["results"]] == [1, 4]
+    for x in r["results"]:
+        assert x["tokens_per_s"] > 0 and x["requests"] == 3 * x["concurrency"]
+        assert 0 < x["ttft_ms"]["p50"] <= x["ttft_ms"]["p99"] and 0 < x["itl_ms"]["p50"] <= x["itl_ms"]["p99"]
