@@ -140,3 +140,52 @@ def test_scheduler_never_leaks_blocks(data):
     assert finished == n_req
     assert sched.num_waiting == 0 and sched.num_running == 0
     assert sched.num_free_blocks == num_blocks                    # every block came back
+
+
+@SET
+@given(data=st.data())
+def test_swap_preemption_keeps_every_sequence_on_its_own_blocks(data):
+    """A model of the cache contents (which sequence and logical block each device / host block holds) follows the
+    scheduler's swap plan: whenever a sequence is scheduled, the blocks of its cached prefix must hold its own data,
+    whatever preemptions, swap-outs and swap-ins happened in between."""
+    from ronn_b200.serving.scheduler import PLAN_NONE, HostBatchBuffers, Scheduler
+    num_blocks, max_seqs, max_tokens, max_blocks = data.draw(st.integers(6, 12)), 4, 64, 6
+    sched = Scheduler(16, num_blocks, max_seqs, max_tokens, data.draw(st.sampled_from([0, 16])), "fcfs", False, max_blocks)
+    n_cpu = data.draw(st.integers(0, 12))
+    sched.set_preemption(data.draw(st.sampled_from(["swap", "auto"])), n_cpu, data.draw(st.integers(1, 40)))
+    host = HostBatchBuffers(max_tokens, max_seqs, max_blocks, pin=False)
+    n_req = data.draw(st.integers(2, 7))
+    for rid in range(n_req):
+        sched.add(rid, list(range(data.draw(st.integers(1, 30)))), data.draw(st.integers(1, 30)), 1)
+    gpu, cpu = {}, {}
+    finished = idle = 0
+    for _ in range(4000):
+        kind = sched.schedule()
+        o_src, o_dst, i_src, i_dst = sched.swaps()
+        for s_, d_ in zip(o_src.tolist(), o_dst.tolist()):
+            assert 0 <= d_ < n_cpu and d_ not in cpu
+            cpu[d_] = gpu[s_]
+        for s_, d_ in zip(i_src.tolist(), i_dst.tolist()):
+            gpu[d_] = cpu.pop(s_)
+        if kind == PLAN_NONE:
+            if sched.num_waiting == 0 and sched.num_running == 0:
+                break
+            idle += 1
+            assert idle < 50                                  # an all-preempted step is followed by progress
+            continue
+        idle = 0
+        sb = sched.fill(host, kind)
+        q_start, pos = host.field("q_start"), host.field("positions")
+        for i, rid in enumerate(sb.req_ids.tolist()):
+            start, count = int(pos[q_start[i]]), int(q_start[i + 1] - q_start[i])
+            blocks = sched.blocks(rid)
+            for lb in range(-(-start // 16)):                 # blocks of the cached prefix hold this sequence's data
+                assert gpu.get(blocks[lb]) == (rid, lb), (rid, lb, blocks, gpu.get(blocks[lb]))
+            for p_ in range(start, start + count):
+                gpu[blocks[p_ // 16]] = (rid, p_ // 16)
+        fin = sched.commit(np.zeros(sb.n_items, dtype=np.int32), -1)
+        finished += int((fin != 0).sum())
+    assert finished == n_req and not cpu
+    assert sched.num_free_blocks == num_blocks and sched.swap_stats()["free_cpu_blocks"] == n_cpu
+    st_ = sched.swap_stats()
+    assert st_["swapped_in_blocks"] == st_["swapped_out_blocks"]
