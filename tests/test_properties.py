@@ -145,26 +145,28 @@ def test_scheduler_never_leaks_blocks(data):
 @SET
 @given(data=st.data())
 def test_swap_preemption_keeps_every_sequence_on_its_own_blocks(data):
-    """A model of the cache contents (which sequence and logical block each device / host block holds) follows the
-    scheduler's swap plan: whenever a sequence is scheduled, the blocks of its cached prefix must hold its own data,
-    whatever preemptions, swap-outs and swap-ins happened in between."""
+    """A model of the cache contents (the token whose key/value each slot of each device / host block holds) follows
+    the scheduler's swap plan: whenever a sequence is scheduled, every position of its cached prefix must hold that
+    sequence's token, whatever preemptions, swap-outs, swap-ins and prefix-cache sharing happened in between."""
     from ronn_b200.serving.scheduler import PLAN_NONE, HostBatchBuffers, Scheduler
     num_blocks, max_seqs, max_tokens, max_blocks = data.draw(st.integers(6, 12)), 4, 64, 6
-    sched = Scheduler(16, num_blocks, max_seqs, max_tokens, data.draw(st.sampled_from([0, 16])), "fcfs", False, max_blocks)
+    sched = Scheduler(16, num_blocks, max_seqs, max_tokens, data.draw(st.sampled_from([0, 16])), "fcfs",
+                      data.draw(st.booleans()), max_blocks)
     n_cpu = data.draw(st.integers(0, 12))
     sched.set_preemption(data.draw(st.sampled_from(["swap", "auto"])), n_cpu, data.draw(st.integers(1, 40)))
     host = HostBatchBuffers(max_tokens, max_seqs, max_blocks, pin=False)
     n_req = data.draw(st.integers(2, 7))
     for rid in range(n_req):
+        # prompts share prefixes (0, 1, 2, ...), so the prefix cache has something to share
         sched.add(rid, list(range(data.draw(st.integers(1, 30)))), data.draw(st.integers(1, 30)), 1)
-    gpu, cpu = {}, {}
+    gpu, cpu = {}, {}                                         # block -> 16 slots, each the token stored there
     finished = idle = 0
-    for _ in range(4000):
+    for step in range(4000):
         kind = sched.schedule()
         o_src, o_dst, i_src, i_dst = sched.swaps()
         for s_, d_ in zip(o_src.tolist(), o_dst.tolist()):
             assert 0 <= d_ < n_cpu and d_ not in cpu
-            cpu[d_] = gpu[s_]
+            cpu[d_] = list(gpu[s_])
         for s_, d_ in zip(i_src.tolist(), i_dst.tolist()):
             gpu[d_] = cpu.pop(s_)
         if kind == PLAN_NONE:
@@ -178,12 +180,12 @@ def test_swap_preemption_keeps_every_sequence_on_its_own_blocks(data):
         q_start, pos = host.field("q_start"), host.field("positions")
         for i, rid in enumerate(sb.req_ids.tolist()):
             start, count = int(pos[q_start[i]]), int(q_start[i + 1] - q_start[i])
-            blocks = sched.blocks(rid)
-            for lb in range(-(-start // 16)):                 # blocks of the cached prefix hold this sequence's data
-                assert gpu.get(blocks[lb]) == (rid, lb), (rid, lb, blocks, gpu.get(blocks[lb]))
+            blocks, toks = sched.blocks(rid), sched.tokens(rid)
+            for p_ in range(start):                           # the cached prefix holds this sequence's tokens
+                assert gpu[blocks[p_ // 16]][p_ % 16] == toks[p_], (rid, p_, blocks)
             for p_ in range(start, start + count):
-                gpu[blocks[p_ // 16]] = (rid, p_ // 16)
-        fin = sched.commit(np.zeros(sb.n_items, dtype=np.int32), -1)
+                gpu.setdefault(blocks[p_ // 16], [None] * 16)[p_ % 16] = toks[p_]
+        fin = sched.commit(np.full(sb.n_items, 100 + step % 7, dtype=np.int32), -1)
         finished += int((fin != 0).sum())
     assert finished == n_req and not cpu
     assert sched.num_free_blocks == num_blocks and sched.swap_stats()["free_cpu_blocks"] == n_cpu
