@@ -1,6 +1,6 @@
 """Library twins of the hand-written kernels: the same operator shapes timed through cuBLAS / cuDNN / SDPA / NCCL.
 
-    python baseline/library_twins.py gemm | attention-decode | attention-prefill | conv | norm | bitlinear
+    python baseline/library_twins.py gemm | attention-decode | attention-prefill | conv | norm | memory-kernels | bitlinear
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 baseline/library_twins.py gemm-allreduce
 
 Nothing here is on a product path; the numbers are the comparison column of the results tables.  Timing follows the
@@ -88,6 +88,40 @@ def norm():
     return [{"op": "torch_layer_norm", "rows": 256, "h": 1024, "us": timed(lambda: F.layer_norm(x, (1024,), g, g))}]
 
 
+def memory_kernels():
+    """PyTorch operators on the shapes of `python -m ronn_b200.ops.microbench memory-kernels` (operands larger than L2)."""
+    dev, bf = "cuda", torch.bfloat16
+    R, H = 131072, 1024
+    x, r = torch.randn(R, H, device=dev).to(bf), torch.randn(R, H, device=dev).to(bf)
+    g, b = torch.ones(H, device=dev, dtype=bf), torch.zeros(H, device=dev, dtype=bf)
+    out = []
+
+    def row(name, shape, byts, fn):
+        us = timed(fn)
+        out.append({"op": name, "shape": shape, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1)})
+
+    row("torch_layer_norm", [R, H], 2.0 * R * H * 2, lambda: F.layer_norm(x, (H,), g, b))
+    row("torch_add+layer_norm", [R, H], 4.0 * R * H * 2, lambda: F.layer_norm(x + r, (H,), g, b))
+    row("torch_rms_norm", [R, H], 2.0 * R * H * 2, lambda: F.rms_norm(x, (H,), g, 1e-6))
+    row("torch_softmax", [R, H], 2.0 * R * H * 2, lambda: torch.softmax(x, -1))
+    row("torch_gelu_tanh", [R, H], 2.0 * R * H * 2, lambda: F.gelu(x, approximate="tanh"))
+    row("torch_relu", [R, H], 2.0 * R * H * 2, lambda: torch.relu(x))
+    row("torch_add", [R, H], 3.0 * R * H * 2, lambda: x + r)
+    row("torch_silu*mul", [R, H], 1.5 * R * H * 2, lambda: F.silu(x[:, :H // 2]) * x[:, H // 2:])
+    row("torch_cast_bf16_fp32", [R, H], 3.0 * R * H * 2, lambda: x.float())
+    V = 50264
+    table = torch.randn(V, H, device=dev).to(bf)
+    ids = torch.randint(0, V, (R,), device=dev)
+    row("torch_embedding", [R, H], 2.0 * R * H * 2, lambda: F.embedding(ids, table))
+    logits = torch.randn(2048, V, device=dev).to(bf)
+    row("torch_argmax", [2048, V], 2048.0 * V * 2, lambda: logits.argmax(-1))
+    xi = torch.randn(128, 64, 112, 112, device=dev).to(torch.float16).contiguous(memory_format=torch.channels_last)
+    row("cudnn_maxpool_3x3_s2", [128, 112, 112, 64], xi.numel() * 2 * 1.25, lambda: F.max_pool2d(xi, 3, 2, 1))
+    xa = torch.randn(8192, 512, 7, 7, device=dev).to(torch.float16).contiguous(memory_format=torch.channels_last)
+    row("torch_global_avgpool", [8192, 7, 7, 512], xa.numel() * 2.0, lambda: xa.mean(dim=(2, 3)))
+    return out
+
+
 def bitlinear(m=128, n=2560, k=2560):
     x = torch.randn(m, k, device="cuda").bfloat16()
     w = torch.randint(-1, 2, (n, k), device="cuda").bfloat16()
@@ -122,7 +156,7 @@ def gemm_allreduce():
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     fns = {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill, "conv": conv,
-           "norm": norm, "bitlinear": bitlinear, "gemm-allreduce": gemm_allreduce}
+           "norm": norm, "memory-kernels": memory_kernels, "bitlinear": bitlinear, "gemm-allreduce": gemm_allreduce}
     if what not in fns:
         sys.exit(f"unknown twin '{what}'; one of {sorted(fns)}")
     res = fns[what]()
