@@ -790,3 +790,6 @@ _wrap_nhwc("Conv", [0], [1])
 _wrap_nhwc("FusedConv", [0, 3], [1])
 for _n in ("MaxPool", "AveragePool", "GlobalAveragePool", "BatchNormalization"):
     _wrap_nhwc(_n, [0])
+
+
+from . import registry_extra  # noqa: E402,F401  (registers the operators beyond the core set)
