@@ -294,7 +294,7 @@ def _trilu(i, a, c):
 
 @op("Size", 1)
 def _size(i, a, c):
-    return [torch.tensor(i[0].numel(), dtype=torch.int64)]
+    return [torch.tensor(i[0].numel(), dtype=torch.int64, device=i[0].device)]
 
 
 @op("EyeLike", 1)
