@@ -1,0 +1,80 @@
+"""Models written by PyTorch's own ONNX exporter (not by the in-tree encoder) load and run: a transformer block and a
+small CNN, opset 17, compared with the eager module at O0 and O3."""
+import collections
+import io
+import warnings
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ronn_b200 import Model, SessionOptions
+
+
+class Block(nn.Module):
+    def __init__(self, d=32, h=4):
+        super().__init__()
+        self.h = h
+        self.emb = nn.Embedding(50, d)
+        self.ln1, self.ln2 = nn.LayerNorm(d), nn.LayerNorm(d)
+        self.qkv, self.o = nn.Linear(d, 3 * d), nn.Linear(d, d)
+        self.f1, self.f2 = nn.Linear(d, 4 * d), nn.Linear(4 * d, d)
+
+    def forward(self, ids):
+        x = self.emb(ids)
+        B, T, D = x.shape
+        q, k, v = self.qkv(self.ln1(x)).chunk(3, -1)
+        split = lambda t: t.reshape(B, T, self.h, D // self.h).transpose(1, 2)
+        att = torch.softmax(split(q) @ split(k).transpose(-1, -2) / (D // self.h) ** 0.5, -1) @ split(v)
+        x = x + self.o(att.transpose(1, 2).reshape(B, T, D))
+        return x + self.f2(F.gelu(self.f1(self.ln2(x))))
+
+
+class CNN(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1, self.bn, self.c2 = nn.Conv2d(3, 8, 3, 2, 1), nn.BatchNorm2d(8), nn.Conv2d(8, 16, 3, 1, 1)
+        self.fc = nn.Linear(16, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.bn(self.c1(x))), 2)
+        x = F.relu(self.c2(x))
+        return self.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
+
+
+def _export(module, example) -> bytes:
+    """TorchScript-based exporter; its last step (attaching onnxscript functions) needs the `onnx` package, which these
+    graphs do not use, so it is stubbed out when that package is absent."""
+    try:
+        from torch.onnx._internal.torchscript_exporter import onnx_proto_utils
+    except Exception:
+        pytest.skip("this PyTorch has no TorchScript ONNX exporter")
+    try:
+        import onnx  # noqa: F401
+    except ImportError:
+        onnx_proto_utils._add_onnxscript_fn = lambda proto, custom_opsets: proto
+    buf = io.BytesIO()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        try:
+            torch.onnx.export(module, (example,), buf, input_names=["x"], output_names=["y"], opset_version=17,
+                              dynamo=False)
+        except Exception as e:                     # exporter unavailable in this build: nothing to test against
+            pytest.skip(f"torch.onnx.export failed: {type(e).__name__}")
+    return buf.getvalue()
+
+
+@pytest.mark.parametrize("name", ["block", "cnn"])
+def test_models_from_the_pytorch_exporter_run(name):
+    torch.manual_seed(0)
+    module, example = (Block().eval(), torch.randint(0, 50, (2, 6))) if name == "block" else \
+        (CNN().eval(), torch.randn(2, 3, 16, 16))
+    model = Model.from_bytes(_export(module, example))
+    ops = collections.Counter(n.op_type for n in model.graph.nodes)
+    assert ("LayerNormalization" in ops and "Softmax" in ops) if name == "block" else ("Conv" in ops and "Gemm" in ops)
+    with torch.no_grad():
+        want = module(example)
+    for level in ("O0", "O3"):
+        got = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": example})["y"]
+        torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
