@@ -343,3 +343,95 @@ def _dequantize_linear(i, a, c):
     if zp_b is not None:
         v = v - zp_b.to(torch.float32)
     return [(v * scale_b).to(scale.dtype)]
+
+
+# ------------------------------------------------------------------------------ recurrent layers
+# X [seq, batch, input] (layout 0) or [batch, seq, input] (layout 1); W [dirs, G*hidden, input]; R [dirs, G*hidden, hidden];
+# B [dirs, 2*G*hidden] (input bias then recurrent bias); default activations only; no peepholes, no clipping.
+def _str_attr(a, key, default):
+    v = a.get(key, default)
+    return v.decode() if isinstance(v, bytes) else v
+
+
+def _recurrent(kind: str, gates: int):
+    def run(i, a, c):
+        x, w, r = i[0], i[1], i[2]
+        b = i[3] if len(i) > 3 else None
+        seq_lens = i[4] if len(i) > 4 else None
+        h0 = i[5] if len(i) > 5 else None
+        c0 = i[6] if kind == "LSTM" and len(i) > 6 else None
+        if kind == "LSTM" and len(i) > 7 and i[7] is not None:
+            raise InvalidAttribute("LSTM: peephole weights are not supported")
+        if seq_lens is not None:
+            raise InvalidAttribute(f"{kind}: sequence_lens is not supported (pad-free batches only)")
+        if a.get("activations") and kind != "RNN":
+            raise InvalidAttribute(f"{kind}: only the default activations are supported")
+        if a.get("clip") is not None:
+            raise InvalidAttribute(f"{kind}: clip is not supported")
+        hidden = int(a["hidden_size"])
+        direction = _str_attr(a, "direction", "forward")
+        layout = int(a.get("layout", 0))
+        if layout == 1:
+            x = x.transpose(0, 1)
+            h0 = h0.transpose(0, 1) if h0 is not None else None
+            c0 = c0.transpose(0, 1) if c0 is not None else None
+        seq, batch = x.shape[0], x.shape[1]
+        dirs = 2 if direction == "bidirectional" else 1
+        if w.shape[0] != dirs:
+            raise InvalidGraph(f"{kind}: W has {w.shape[0]} directions, attribute direction={direction}")
+        act = torch.tanh
+        if kind == "RNN" and a.get("activations"):
+            names = [n.decode() if isinstance(n, bytes) else n for n in a["activations"]]
+            if any(n not in ("Tanh", "Relu") for n in names):
+                raise InvalidAttribute("RNN: activations other than Tanh / Relu are not supported")
+            act = torch.relu if names[0] == "Relu" else torch.tanh
+        lbr = int(a.get("linear_before_reset", 0))
+        ys, hs, cs = [], [], []
+        for d in range(dirs):
+            wd, rd = w[d], r[d]
+            wb = b[d, :gates * hidden] if b is not None else None
+            rb = b[d, gates * hidden:] if b is not None else None
+            h = h0[d] if h0 is not None else x.new_zeros(batch, hidden)
+            cell = c0[d] if c0 is not None else x.new_zeros(batch, hidden)
+            reverse = direction == "reverse" or d == 1
+            steps = range(seq - 1, -1, -1) if reverse else range(seq)
+            out = [None] * seq
+            xw = F.linear(x, wd, wb)                              # every time step's input projection at once
+            for t_ in steps:
+                if kind == "LSTM":                                # gate order i, o, f, c
+                    g = xw[t_] + F.linear(h, rd, rb)
+                    gi, go, gf, gc = g.chunk(4, -1)
+                    cell = torch.sigmoid(gf) * cell + torch.sigmoid(gi) * torch.tanh(gc)
+                    h = torch.sigmoid(go) * torch.tanh(cell)
+                elif kind == "GRU":                               # gate order z, r, h
+                    xz, xr, xh = xw[t_].chunk(3, -1)
+                    rz, rr, rh = rd.chunk(3, 0)
+                    bz, br, bh = rb.chunk(3, -1) if rb is not None else (None, None, None)
+                    z = torch.sigmoid(xz + F.linear(h, rz, bz))
+                    rg = torch.sigmoid(xr + F.linear(h, rr, br))
+                    if lbr:
+                        cand = torch.tanh(xh + rg * F.linear(h, rh, bh))
+                    else:
+                        cand = torch.tanh(xh + F.linear(rg * h, rh, bh))
+                    h = (1 - z) * cand + z * h
+                else:
+                    h = act(xw[t_] + F.linear(h, rd, rb))
+                out[t_] = h
+            ys.append(torch.stack(out, 0))
+            hs.append(h)
+            cs.append(cell)
+        y = torch.stack(ys, 1)                                    # [seq, dirs, batch, hidden]
+        yh = torch.stack(hs, 0)
+        if layout == 1:
+            y, yh = y.permute(2, 0, 1, 3), yh.transpose(0, 1)
+        outs = [y, yh]
+        if kind == "LSTM":
+            yc = torch.stack(cs, 0)
+            outs.append(yc.transpose(0, 1) if layout == 1 else yc)
+        return outs
+    return run
+
+
+op("LSTM", 3, 8)(_recurrent("LSTM", 4))
+op("GRU", 3, 6)(_recurrent("GRU", 3))
+op("RNN", 3, 6)(_recurrent("RNN", 1))

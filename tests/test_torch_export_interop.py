@@ -78,3 +78,84 @@ def test_models_from_the_pytorch_exporter_run(name):
     for level in ("O0", "O3"):
         got = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": example})["y"]
         torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+
+
+class UNetish(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.down, self.gn = nn.Conv2d(3, 8, 3, 2, 1), nn.GroupNorm(2, 8)
+        self.up, self.out = nn.ConvTranspose2d(8, 4, 2, 2), nn.Conv2d(4 + 3, 2, 1)
+
+    def forward(self, x):
+        h = self.up(F.silu(self.gn(self.down(x))))
+        return self.out(torch.cat([h, x], 1))
+
+
+class Upsample(nn.Module):
+    def forward(self, x):
+        return F.interpolate(x, scale_factor=2, mode="nearest") + \
+            F.interpolate(x, scale_factor=2, mode="bilinear", align_corners=False)
+
+
+class Misc(nn.Module):
+    def forward(self, x):
+        a = x.clamp(-1, 1).abs().sqrt() + torch.where(x > 0, x, torch.zeros_like(x)).mean(-1, keepdim=True)
+        b = torch.cumsum(x, 1) * F.hardswish(x) + F.leaky_relu(x, 0.1) + F.elu(x)
+        v, _ = torch.topk(x, 2, dim=-1)
+        return a + b + v.sum(-1, keepdim=True) + F.log_softmax(x, -1) + x.max(-1, keepdim=True).values + \
+            torch.tril(x @ x.transpose(-1, -2))[..., :1]
+
+
+class SelfAttention(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.m = nn.MultiheadAttention(16, 4, batch_first=True)
+
+    def forward(self, x):
+        return self.m(x, x, x, need_weights=False)[0]
+
+
+class PixelOps(nn.Module):
+    def forward(self, x):
+        return F.pixel_unshuffle(F.pixel_shuffle(x, 2), 2) + F.instance_norm(x) + \
+            F.avg_pool2d(x, 2, 1, padding=1, count_include_pad=False)[..., :4, :4]
+
+
+class Recurrent(nn.Module):
+    def __init__(self, m):
+        super().__init__()
+        self.m = m
+
+    def forward(self, x):
+        out, state = self.m(x)
+        h = state[0] if isinstance(state, tuple) else state
+        return out + 0.0 * h.sum()                 # keeps the final-state output of the operator in the graph
+
+
+WIDER = {
+    "unet": (UNetish, (1, 3, 8, 8), {"ConvTranspose", "InstanceNormalization"}),
+    "upsample": (Upsample, (1, 2, 4, 4), {"Resize"}),
+    "misc": (Misc, (3, 5), {"CumSum", "TopK", "Trilu", "HardSwish"}),
+    "attention": (SelfAttention, (2, 5, 16), {"Softmax", "Gemm"}),
+    "pixel": (PixelOps, (1, 8, 4, 4), {"DepthToSpace", "AveragePool"}),
+    "gru": (lambda: Recurrent(nn.GRU(8, 8, batch_first=True)), (3, 4, 8), {"GRU"}),
+    "gru_bidirectional": (lambda: Recurrent(nn.GRU(8, 6, bidirectional=True)), (3, 4, 8), {"GRU"}),
+    "lstm": (lambda: Recurrent(nn.LSTM(8, 8, batch_first=True)), (3, 4, 8), {"LSTM"}),
+    "lstm_two_layers_bidirectional": (lambda: Recurrent(nn.LSTM(8, 5, num_layers=2, bidirectional=True)), (3, 4, 8), {"LSTM"}),
+    "rnn_relu": (lambda: Recurrent(nn.RNN(8, 7, nonlinearity="relu", batch_first=True)), (3, 4, 8), {"RNN"}),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WIDER))
+def test_wider_operator_coverage_through_the_exporter(name):
+    torch.manual_seed(1)
+    make, shape, expect_ops = WIDER[name]
+    module, example = make().eval(), torch.randn(*shape)
+    model = Model.from_bytes(_export(module, example))
+    ops = {n.op_type for n in model.graph.nodes}
+    assert expect_ops <= ops, (expect_ops, ops)
+    with torch.no_grad():
+        want = module(example)
+    for level in ("O0", "O3"):
+        got = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": example})["y"]
+        torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-5)
