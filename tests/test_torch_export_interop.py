@@ -43,7 +43,7 @@ class CNN(nn.Module):
         return self.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
 
 
-def _export(module, example) -> bytes:
+def _export(module, example, dynamic_axes=None) -> bytes:
     """TorchScript-based exporter; its last step (attaching onnxscript functions) needs the `onnx` package, which these
     graphs do not use, so it is stubbed out when that package is absent."""
     try:
@@ -59,7 +59,7 @@ def _export(module, example) -> bytes:
         warnings.simplefilter("ignore")
         try:
             torch.onnx.export(module, (example,), buf, input_names=["x"], output_names=["y"], opset_version=17,
-                              dynamo=False)
+                              dynamo=False, dynamic_axes={"x": dynamic_axes} if dynamic_axes else None)
         except Exception as e:                     # exporter unavailable in this build: nothing to test against
             pytest.skip(f"torch.onnx.export failed: {type(e).__name__}")
     return buf.getvalue()
@@ -159,3 +159,22 @@ def test_wider_operator_coverage_through_the_exporter(name):
     for level in ("O0", "O3"):
         got = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": example})["y"]
         torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-5)
+
+
+def test_dynamic_axes_run_at_other_sizes():
+    """Symbolic dimensions keep their names, load as 0, and the session runs shapes other than the traced one."""
+    torch.manual_seed(2)
+    block, cnn = Block().eval(), CNN().eval()
+    m1 = Model.from_bytes(_export(block, torch.randint(0, 50, (2, 6)), {0: "batch", 1: "sequence"}))
+    assert [(t.shape, t.dim_params) for t in m1.inputs()] == [([0, 0], ["batch", "sequence"])]
+    m2 = Model.from_bytes(_export(cnn, torch.randn(2, 3, 16, 16), {0: "batch", 2: "height", 3: "width"}))
+    assert m2.inputs()[0].shape == [0, 3, 0, 0] and m2.inputs()[0].dim_params == ["batch", None, "height", "width"]
+    for level in ("O0", "O3"):
+        s1 = m1.create_session(SessionOptions().with_optimization_level(level))
+        s2 = m2.create_session(SessionOptions().with_optimization_level(level))
+        for ids in (torch.randint(0, 50, (2, 6)), torch.randint(0, 50, (3, 9)), torch.randint(0, 50, (1, 1))):
+            with torch.no_grad():
+                torch.testing.assert_close(s1.run({"x": ids})["y"], block(ids), atol=1e-5, rtol=1e-5)
+        for img in (torch.randn(2, 3, 16, 16), torch.randn(1, 3, 24, 20)):
+            with torch.no_grad():
+                torch.testing.assert_close(s2.run({"x": img})["y"], cnn(img), atol=1e-5, rtol=1e-5)
