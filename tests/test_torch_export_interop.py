@@ -178,3 +178,22 @@ def test_dynamic_axes_run_at_other_sizes():
         for img in (torch.randn(2, 3, 16, 16), torch.randn(1, 3, 24, 20)):
             with torch.no_grad():
                 torch.testing.assert_close(s2.run({"x": img})["y"], cnn(img), atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["block", "cnn", "lstm"])
+def test_exporter_models_survive_the_in_tree_encoder(name):
+    """Decode with the in-tree codec, encode again, decode again: same graph, same numbers."""
+    torch.manual_seed(3)
+    if name == "block":
+        module, example = Block().eval(), torch.randint(0, 50, (2, 6))
+    elif name == "cnn":
+        module, example = CNN().eval(), torch.randn(2, 3, 16, 16)
+    else:
+        module, example = Recurrent(nn.LSTM(8, 8, batch_first=True)).eval(), torch.randn(3, 4, 8)
+    first = Model.from_bytes(_export(module, example))
+    second = Model.from_bytes(first.to_bytes())
+    assert [n.op_type for n in first.graph.nodes] == [n.op_type for n in second.graph.nodes]
+    assert sorted(first.graph.initializers) == sorted(second.graph.initializers)
+    a = first.create_session(SessionOptions()).run({"x": example})["y"]
+    b = second.create_session(SessionOptions()).run({"x": example})["y"]
+    torch.testing.assert_close(a, b, atol=0, rtol=0)
