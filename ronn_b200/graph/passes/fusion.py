@@ -12,8 +12,12 @@ crates/ronn-providers/src/compiler.rs:267-314):
 * FusedGemm -> Add(residual)            => FusedGemm with 4th input
 * Add -> LayerNormalization             => com.ronn::SkipLayerNorm (when the sum is used only by the norm
                                            and, at most, one more residual consumer)
+* x * 0.5 * (1 + Erf(x / sqrt(2)))      => Gelu(approximate="none"): the five-node chain exporters write for the exact
+                                           GELU (either multiplication order)
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -31,7 +35,8 @@ class NodeFusionPass(OptimizationPass):
         progress = True
         while progress:
             progress = False
-            for fn in (self._fold_bn, self._conv_act, self._matmul_bias, self._gemm_act, self._gemm_residual):
+            for fn in (self._fold_bn, self._conv_act, self._erf_gelu, self._matmul_bias, self._gemm_act,
+                       self._gemm_residual):
                 n = fn(graph)
                 if n:
                     stats.nodes_fused += n
@@ -45,6 +50,67 @@ class NodeFusionPass(OptimizationPass):
             return None
         c = cons.get(name, [])
         return c[0] if len(c) == 1 else None
+
+    # -------------------------------------------------------------- exact GELU written out with Erf
+    @staticmethod
+    def _scalar(graph, name):
+        t = graph.initializers.get(name)
+        return float(t.reshape(-1)[0]) if t is not None and t.numel() == 1 and t.is_floating_point() else None
+
+    def _erf_gelu(self, graph: ModelGraph) -> int:
+        cons, prod = graph.consumers(), graph.producers()
+        close = lambda v, want: v is not None and abs(v - want) < 1e-3 * abs(want)
+
+        def scaled(node, factor_div, factor_mul):
+            """node computes x / factor_div or x * factor_mul with a scalar constant: returns x's name."""
+            if node is None or len(node.inputs) != 2:
+                return None
+            a, b = node.inputs
+            if node.op_type == "Div" and close(self._scalar(graph, b), factor_div):
+                return a
+            if node.op_type == "Mul":
+                if close(self._scalar(graph, b), factor_mul):
+                    return a
+                if close(self._scalar(graph, a), factor_mul):
+                    return b
+            return None
+
+        def other_input(node, name):
+            return node.inputs[1] if node.inputs[0] == name else node.inputs[0]
+
+        for erf in graph.nodes:
+            if erf.op_type != "Erf":
+                continue
+            pre = prod.get(erf.inputs[0])
+            x = scaled(pre, math.sqrt(2.0), 1.0 / math.sqrt(2.0))
+            if x is None or self._single_consumer(graph, cons, pre.outputs[0]) is not erf:
+                continue
+            add = self._single_consumer(graph, cons, erf.outputs[0])
+            if add is None or add.op_type != "Add" or not close(self._scalar(graph, other_input(add, erf.outputs[0])), 1.0):
+                continue
+            m1 = self._single_consumer(graph, cons, add.outputs[0])
+            if m1 is None or m1.op_type != "Mul":
+                continue
+            partner = other_input(m1, add.outputs[0])
+            dead = [pre, erf, add]
+            if partner == x:                                   # (x * (1 + erf)) * 0.5
+                m2 = self._single_consumer(graph, cons, m1.outputs[0])
+                if m2 is None or m2.op_type != "Mul" or not close(self._scalar(graph, other_input(m2, m1.outputs[0])), 0.5):
+                    continue
+                last = m2
+                dead.append(m1)
+            else:                                              # (x * 0.5) * (1 + erf)
+                half = prod.get(partner)
+                if scaled(half, 2.0, 0.5) != x or self._single_consumer(graph, cons, partner) is not m1:
+                    continue
+                last = m1
+                dead.append(half)
+            last.op_type, last.domain = "Gelu", ""
+            last.inputs = [x]
+            last.attributes = {"approximate": "none"}
+            graph.remove_nodes([n.id for n in dead])
+            return len(dead)
+        return 0
 
     # -------------------------------------------------------------- Conv + BN
     def _fold_bn(self, graph: ModelGraph) -> int:

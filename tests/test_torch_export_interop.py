@@ -197,3 +197,48 @@ def test_exporter_models_survive_the_in_tree_encoder(name):
     a = first.create_session(SessionOptions()).run({"x": example})["y"]
     b = second.create_session(SessionOptions()).run({"x": example})["y"]
     torch.testing.assert_close(a, b, atol=0, rtol=0)
+
+
+def test_exact_gelu_chain_becomes_one_node():
+    """The exporter writes the exact GELU as Div, Erf, Add, Mul, Mul; O2 and above fold the chain into one Gelu node."""
+    from ronn_b200.graph.optimizer import Optimizer
+    import copy
+    torch.manual_seed(4)
+    block, ids = Block().eval(), torch.randint(0, 50, (2, 6))
+    model = Model.from_bytes(_export(block, ids))
+    g = copy.deepcopy(model.graph)
+    before = [n.op_type for n in g.nodes]
+    assert "Erf" in before and "Gelu" not in before
+    Optimizer("O2").optimize(g)
+    after = [n.op_type for n in g.nodes]
+    assert "Erf" not in after and after.count("Gelu") == 1
+    gelu = next(n for n in g.nodes if n.op_type == "Gelu")
+    assert gelu.attr("approximate") == "none"
+    with torch.no_grad():
+        want = block(ids)
+    got = model.create_session(SessionOptions().with_optimization_level("O3")).run({"x": ids})["y"]
+    torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    # the other multiplication order: (x * 0.5) * (1 + erf(x / sqrt 2))
+    from ronn_b200.core.types import DataType
+    from ronn_b200.graph.ir import GraphBuilder
+    b = GraphBuilder().add_input("x", [2, 8], DataType.F32).add_output("y", [2, 8], DataType.F32)
+    for name, v in (("half", 0.5), ("one", 1.0), ("rsqrt2", 0.7071067811865476)):
+        b.add_initializer(name, torch.tensor(v))
+    b.add_op("Mul", ["x", "half"], ["hx"]).add_op("Mul", ["rsqrt2", "x"], ["sx"]).add_op("Erf", ["sx"], ["e"])
+    b.add_op("Add", ["one", "e"], ["e1"]).add_op("Mul", ["hx", "e1"], ["y"])
+    g2 = b.build()
+    Optimizer("O2").optimize(g2)
+    assert [n.op_type for n in g2.nodes] == ["Gelu"]
+    x = torch.randn(2, 8)
+    y = Model.from_graph(g2).create_session(SessionOptions().with_optimization_level("O0")).run({"x": x})["y"]
+    torch.testing.assert_close(y, F.gelu(x), atol=1e-6, rtol=1e-6)
+    # a chain whose intermediate value is used elsewhere must stay
+    b3 = GraphBuilder().add_input("x", [2, 8], DataType.F32).add_output("y", [2, 8], DataType.F32)
+    b3.add_output("e", [2, 8], DataType.F32)
+    for name, v in (("half", 0.5), ("one", 1.0), ("sqrt2", 1.4142135623730951)):
+        b3.add_initializer(name, torch.tensor(v))
+    b3.add_op("Div", ["x", "sqrt2"], ["sx"]).add_op("Erf", ["sx"], ["e"]).add_op("Add", ["e", "one"], ["e1"])
+    b3.add_op("Mul", ["x", "e1"], ["m"]).add_op("Mul", ["m", "half"], ["y"])
+    g3 = b3.build()
+    Optimizer("O2").optimize(g3)
+    assert "Erf" in [n.op_type for n in g3.nodes]
