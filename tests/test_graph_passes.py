@@ -214,3 +214,19 @@ def test_deep_and_wide_graphs():
     wg = w.build()
     st = Optimizer("O3", ProviderType.CPU).optimize(wg)
     assert len(wg.nodes) == 64 and st.nodes_removed == 0
+
+
+def test_exact_gelu_is_not_absorbed_into_the_gpu_elementwise_chain():
+    import torch
+    from ronn_b200.core.types import DataType, ProviderType
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.graph.optimizer import Optimizer
+    def build(approx):
+        b = GraphBuilder().add_input("x", [2, 8], DataType.F32).add_output("y", [2, 8], DataType.F32)
+        b.add_op("Relu", ["x"], ["a"]).add_op("Gelu", ["a"], ["g"], approximate=approx).add_op("Sigmoid", ["g"], ["y"])
+        return b.build()
+    g_tanh, g_exact = build("tanh"), build("none")
+    Optimizer("O3", ProviderType.GPU).optimize(g_tanh)
+    Optimizer("O3", ProviderType.GPU).optimize(g_exact)
+    assert [n.op_type for n in g_tanh.nodes] == ["FusedElementwise"]
+    assert "Gelu" in [n.op_type for n in g_exact.nodes]
