@@ -12,6 +12,9 @@ crates/ronn-providers/src/compiler.rs:267-314):
 * FusedGemm -> Add(residual)            => FusedGemm with 4th input
 * Add -> LayerNormalization             => com.ronn::SkipLayerNorm (when the sum is used only by the norm
                                            and, at most, one more residual consumer)
+* ReduceMean, Sub, Pow, ReduceMean, Add(eps), Sqrt, Div, Mul(gamma), Add(beta)
+                                        => LayerNormalization: the nine-node form exporters write below opset 17
+                                           (the reference's own export scripts use opset 13)
 * x * 0.5 * (1 + Erf(x / sqrt(2)))      => Gelu(approximate="none"): the five-node chain exporters write for the exact
                                            GELU (either multiplication order)
 """
@@ -35,7 +38,8 @@ class NodeFusionPass(OptimizationPass):
         progress = True
         while progress:
             progress = False
-            for fn in (self._fold_bn, self._conv_act, self._erf_gelu, self._matmul_bias, self._gemm_act,
+            for fn in (self._fold_bn, self._conv_act, self._decomposed_layernorm, self._erf_gelu, self._matmul_bias,
+                       self._gemm_act,
                        self._gemm_residual):
                 n = fn(graph)
                 if n:
@@ -50,6 +54,70 @@ class NodeFusionPass(OptimizationPass):
             return None
         c = cons.get(name, [])
         return c[0] if len(c) == 1 else None
+
+    # -------------------------------------------------------------- LayerNorm written out in primitives
+    def _decomposed_layernorm(self, graph: ModelGraph) -> int:
+        cons, prod = graph.consumers(), graph.producers()
+        outputs = set(graph.output_names())
+
+        def last_axis_mean(node):
+            if node is None or node.op_type != "ReduceMean" or int(node.attr("keepdims", 1)) != 1:
+                return False
+            axes = node.attr("axes")
+            if axes is None and len(node.inputs) > 1:
+                t = graph.initializers.get(node.inputs[1])
+                axes = None if t is None else [int(v) for v in t.reshape(-1).tolist()]
+            return axes is not None and list(axes) == [-1]
+
+        def only(name, *want):
+            """the consumers of `name` are exactly `want` nodes (any order) and it is not a graph output"""
+            got = cons.get(name, [])
+            return name not in outputs and len(got) == len(want) and all(any(g is w for g in got) for w in want)
+
+        for sub in graph.nodes:
+            if sub.op_type != "Sub" or len(sub.inputs) != 2:
+                continue
+            x, mean = sub.inputs[0], prod.get(sub.inputs[1])
+            if not last_axis_mean(mean) or mean.inputs[0] != x or not only(mean.outputs[0], sub):
+                continue
+            users = cons.get(sub.outputs[0], [])
+            pw = next((u for u in users if u.op_type == "Pow"), None)
+            div = next((u for u in users if u.op_type == "Div" and u.inputs[0] == sub.outputs[0]), None)
+            if pw is None or div is None or not only(sub.outputs[0], pw, div):
+                continue
+            if self._scalar(graph, pw.inputs[1]) != 2.0:
+                continue
+            var = self._single_consumer(graph, cons, pw.outputs[0])
+            if not last_axis_mean(var):
+                continue
+            add = self._single_consumer(graph, cons, var.outputs[0])
+            if add is None or add.op_type != "Add":
+                continue
+            eps = self._scalar(graph, add.inputs[1] if add.inputs[0] == var.outputs[0] else add.inputs[0])
+            sqrt = self._single_consumer(graph, cons, add.outputs[0])
+            if eps is None or eps <= 0 or sqrt is None or sqrt.op_type != "Sqrt":
+                continue
+            if div.inputs[1] != sqrt.outputs[0] or not only(sqrt.outputs[0], div):
+                continue
+            mul = self._single_consumer(graph, cons, div.outputs[0])
+            if mul is None or mul.op_type != "Mul":
+                continue
+            gname = mul.inputs[1] if mul.inputs[0] == div.outputs[0] else mul.inputs[0]
+            gamma = graph.initializers.get(gname)
+            addb = self._single_consumer(graph, cons, mul.outputs[0])
+            if gamma is None or gamma.dim() != 1 or addb is None or addb.op_type != "Add":
+                continue
+            bname = addb.inputs[1] if addb.inputs[0] == mul.outputs[0] else addb.inputs[0]
+            beta = graph.initializers.get(bname)
+            if beta is None or beta.shape != gamma.shape:
+                continue
+            dead = [mean, sub, pw, var, add, sqrt, div, mul]
+            addb.op_type, addb.domain = "LayerNormalization", ""
+            addb.inputs = [x, gname, bname]
+            addb.attributes = {"axis": -1, "epsilon": float(eps)}
+            graph.remove_nodes([n.id for n in dead])
+            return len(dead)
+        return 0
 
     # -------------------------------------------------------------- exact GELU written out with Erf
     @staticmethod

@@ -43,7 +43,7 @@ class CNN(nn.Module):
         return self.fc(torch.flatten(F.adaptive_avg_pool2d(x, 1), 1))
 
 
-def _export(module, example, dynamic_axes=None) -> bytes:
+def _export(module, example, dynamic_axes=None, opset=17) -> bytes:
     """TorchScript-based exporter; its last step (attaching onnxscript functions) needs the `onnx` package, which these
     graphs do not use, so it is stubbed out when that package is absent."""
     try:
@@ -58,7 +58,7 @@ def _export(module, example, dynamic_axes=None) -> bytes:
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         try:
-            torch.onnx.export(module, (example,), buf, input_names=["x"], output_names=["y"], opset_version=17,
+            torch.onnx.export(module, (example,), buf, input_names=["x"], output_names=["y"], opset_version=opset,
                               dynamo=False, dynamic_axes={"x": dynamic_axes} if dynamic_axes else None)
         except Exception as e:                     # exporter unavailable in this build: nothing to test against
             pytest.skip(f"torch.onnx.export failed: {type(e).__name__}")
@@ -242,3 +242,38 @@ def test_exact_gelu_chain_becomes_one_node():
     g3 = b3.build()
     Optimizer("O2").optimize(g3)
     assert "Erf" in [n.op_type for n in g3.nodes]
+
+
+def test_opset13_layernorm_chain_becomes_one_node():
+    """Below opset 17 exporters write LayerNorm as nine primitive nodes (the reference's export scripts use opset 13);
+    O2 folds each chain back into a LayerNormalization node."""
+    import copy
+    from ronn_b200.graph.optimizer import Optimizer
+    torch.manual_seed(5)
+    block, ids = Block().eval(), torch.randint(0, 50, (2, 6))
+    model = Model.from_bytes(_export(block, ids, opset=13))
+    before = collections.Counter(n.op_type for n in model.graph.nodes)
+    assert before["ReduceMean"] == 4 and "LayerNormalization" not in before
+    g = copy.deepcopy(model.graph)
+    Optimizer("O2").optimize(g)
+    after = collections.Counter(n.op_type for n in g.nodes)
+    assert after["LayerNormalization"] == 2 and "ReduceMean" not in after and "Pow" not in after and after["Gelu"] == 1
+    ln = next(n for n in g.nodes if n.op_type == "LayerNormalization")
+    assert ln.attr("axis") == -1 and abs(ln.attr("epsilon") - 1e-5) < 1e-9
+    with torch.no_grad():
+        want = block(ids)
+    for level in ("O0", "O2", "O3"):
+        got = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": ids})["y"]
+        torch.testing.assert_close(got, want, atol=1e-5, rtol=1e-5)
+    # a mean over another axis is not a LayerNorm over the last one: the chain stays
+    from ronn_b200.core.types import DataType
+    from ronn_b200.graph.ir import GraphBuilder
+    b = GraphBuilder().add_input("x", [2, 4, 8], DataType.F32).add_output("y", [2, 4, 8], DataType.F32)
+    for name, v in (("two", torch.tensor(2.0)), ("eps", torch.tensor(1e-5)), ("g", torch.ones(8)), ("b", torch.zeros(8))):
+        b.add_initializer(name, v)
+    b.add_op("ReduceMean", ["x"], ["m"], axes=[1]).add_op("Sub", ["x", "m"], ["d"]).add_op("Pow", ["d", "two"], ["p"])
+    b.add_op("ReduceMean", ["p"], ["v"], axes=[1]).add_op("Add", ["v", "eps"], ["ve"]).add_op("Sqrt", ["ve"], ["s"])
+    b.add_op("Div", ["d", "s"], ["n"]).add_op("Mul", ["n", "g"], ["ng"]).add_op("Add", ["ng", "b"], ["y"])
+    g2 = b.build()
+    Optimizer("O2").optimize(g2)
+    assert "LayerNormalization" not in [n.op_type for n in g2.nodes]
