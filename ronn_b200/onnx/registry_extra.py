@@ -435,3 +435,48 @@ def _recurrent(kind: str, gates: int):
 op("LSTM", 3, 8)(_recurrent("LSTM", 4))
 op("GRU", 3, 6)(_recurrent("GRU", 3))
 op("RNN", 3, 6)(_recurrent("RNN", 1))
+
+
+# ------------------------------------------------------------------------------ integer matmul (QOperator format)
+def _zp(t, like_rows: bool):
+    """Zero point as an int32 tensor broadcastable against a [.., M, K] (rows) or [.., K, N] (columns) operand."""
+    if t is None:
+        return 0
+    z = t.to(torch.int32)
+    if z.dim() == 0 or z.numel() == 1:
+        return z.reshape(())
+    return z.reshape(-1, 1) if like_rows else z.reshape(1, -1)
+
+
+@op("MatMulInteger", 2, 4)
+def _matmul_integer(i, a, c):
+    x, w = i[0].to(torch.int32), i[1].to(torch.int32)
+    xz = _zp(i[2] if len(i) > 2 else None, True)
+    wz = _zp(i[3] if len(i) > 3 else None, False)
+    # int32 matmul is not available on every device: accumulate in float64, exact up to 2^53
+    return [((x - xz).to(torch.float64) @ (w - wz).to(torch.float64)).to(torch.int32)]
+
+
+@op("DynamicQuantizeLinear", 1)
+def _dynamic_quantize_linear(i, a, c):
+    x = i[0].to(torch.float32)
+    lo, hi = torch.clamp(x.min(), max=0.0), torch.clamp(x.max(), min=0.0)
+    scale = (hi - lo) / 255.0
+    scale = torch.where(scale == 0, torch.ones_like(scale), scale)
+    zp = torch.clamp(torch.round(-lo / scale), 0, 255)
+    y = torch.clamp(torch.round(x / scale) + zp, 0, 255).to(torch.uint8)
+    return [y, scale.reshape(()), zp.to(torch.uint8).reshape(())]
+
+
+@op("QLinearMatMul", 8)
+def _qlinear_matmul(i, a, c):
+    xa, sa, za, xb, sb, zb, sy, zy = i
+    acc = (xa.to(torch.int32) - _zp(za, True)).to(torch.float64) @ (xb.to(torch.int32) - _zp(zb, False)).to(torch.float64)
+    sa_, sb_ = sa.to(torch.float64), sb.to(torch.float64)
+    if sa_.numel() > 1:
+        sa_ = sa_.reshape(-1, 1)
+    if sb_.numel() > 1:
+        sb_ = sb_.reshape(1, -1)
+    y = torch.round(acc * sa_ * sb_ / sy.to(torch.float64)) + zy.to(torch.float64)
+    lo, hi = (0, 255) if zy.dtype == torch.uint8 else (-128, 127)
+    return [y.clamp(lo, hi).to(zy.dtype)]

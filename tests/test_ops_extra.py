@@ -164,3 +164,25 @@ def test_registry_size_and_session_use():
     for level in ("O0", "O3"):
         y = model.create_session(SessionOptions().with_optimization_level(level)).run({"x": x})["y"]
         torch.testing.assert_close(y, ex("DepthToSpace", [x * torch.clamp(x / 6 + 0.5, 0, 1)], blocksize=2)[0])
+
+
+def test_integer_matmul_family():
+    torch.manual_seed(0)
+    a = torch.randint(0, 256, (3, 5), dtype=torch.uint8)
+    b = torch.randint(-128, 128, (5, 4), dtype=torch.int8)
+    az, bz = t(7, dtype=torch.uint8), t(1, -2, 3, 0, dtype=torch.int8)
+    got = ex("MatMulInteger", [a, b, az, bz])[0]
+    want = (a.to(torch.int64) - 7) @ (b.to(torch.int64) - bz.to(torch.int64).reshape(1, -1))
+    assert got.dtype == torch.int32 and torch.equal(got.to(torch.int64), want)
+    assert torch.equal(ex("MatMulInteger", [a, b])[0].to(torch.int64), a.to(torch.int64) @ b.to(torch.int64))
+    x = t([0.0, 2.0, -3.0, -2.5], [1.34, 0.48, 7.0, -0.5])
+    y, scale, zp = ex("DynamicQuantizeLinear", [x])
+    assert y.dtype == torch.uint8 and zp.dtype == torch.uint8 and abs(scale.item() - 10.0 / 255) < 1e-7 and zp.item() == 76
+    torch.testing.assert_close((y.float() - zp.float()) * scale, x, atol=scale.item() / 2 + 1e-6, rtol=0)
+    # QLinearMatMul: dequantise, multiply, requantise
+    sa, sb, sy = t(0.02), t(0.05), t(0.1)
+    za, zb, zy = t(128, dtype=torch.uint8), t(0, dtype=torch.int8), t(3, dtype=torch.uint8)
+    q = ex("QLinearMatMul", [a, sa, za, b, sb, zb, sy, zy])[0]
+    real = ((a.float() - 128) * 0.02) @ (b.float() * 0.05)
+    assert q.dtype == torch.uint8
+    assert (q.float() - torch.clamp(torch.round(real / 0.1) + 3, 0, 255)).abs().max() <= 1       # ties may fall either way
