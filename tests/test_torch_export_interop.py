@@ -277,3 +277,67 @@ def test_opset13_layernorm_chain_becomes_one_node():
     g2 = b.build()
     Optimizer("O2").optimize(g2)
     assert "LayerNormalization" not in [n.op_type for n in g2.nodes]
+
+
+class MaskedEncoder(nn.Module):
+    """DistilBERT-shaped layer: embeddings + positions, padding mask applied with masked_fill, post-LayerNorm."""
+
+    def __init__(self, d=32, h=4, vocab=60, max_pos=16):
+        super().__init__()
+        self.h = h
+        self.wte, self.wpe, self.eln = nn.Embedding(vocab, d), nn.Embedding(max_pos, d), nn.LayerNorm(d, eps=1e-12)
+        self.q, self.k, self.v, self.o = (nn.Linear(d, d) for _ in range(4))
+        self.ln1, self.ln2 = nn.LayerNorm(d, eps=1e-12), nn.LayerNorm(d, eps=1e-12)
+        self.f1, self.f2 = nn.Linear(d, 2 * d), nn.Linear(2 * d, d)
+
+    def forward(self, input_ids, attention_mask):
+        B, T = input_ids.shape
+        pos = torch.arange(T, device=input_ids.device).unsqueeze(0).expand(B, T)
+        x = self.eln(self.wte(input_ids) + self.wpe(pos))
+        D = x.shape[-1]
+        split = lambda t: t.view(B, T, self.h, D // self.h).transpose(1, 2)
+        q, k, v = split(self.q(x)) / (D // self.h) ** 0.5, split(self.k(x)), split(self.v(x))
+        scores = q @ k.transpose(2, 3)
+        mask = (attention_mask == 0).view(B, 1, 1, T).expand_as(scores)
+        scores = scores.masked_fill(mask, torch.finfo(scores.dtype).min)
+        ctx = (torch.softmax(scores, -1) @ v).transpose(1, 2).contiguous().view(B, T, D)
+        x = self.ln1(self.o(ctx) + x)
+        return self.ln2(self.f2(F.gelu(self.f1(x))) + x)
+
+
+@pytest.mark.parametrize("opset", [13, 17])
+def test_masked_encoder_with_two_inputs(opset):
+    torch.manual_seed(6)
+    module = MaskedEncoder().eval()
+    ids = torch.randint(0, 60, (2, 8))
+    mask = torch.ones(2, 8, dtype=torch.int64)
+    mask[1, 5:] = 0
+    try:
+        from torch.onnx._internal.torchscript_exporter import onnx_proto_utils
+    except Exception:
+        pytest.skip("this PyTorch has no TorchScript ONNX exporter")
+    try:
+        import onnx  # noqa: F401
+    except ImportError:
+        onnx_proto_utils._add_onnxscript_fn = lambda proto, custom_opsets: proto
+    buf = io.BytesIO()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        try:
+            torch.onnx.export(module, (ids, mask), buf, input_names=["input_ids", "attention_mask"],
+                              output_names=["last_hidden_state"], opset_version=opset, dynamo=False)
+        except Exception as e:
+            pytest.skip(f"torch.onnx.export failed: {type(e).__name__}")
+    model = Model.from_bytes(buf.getvalue())
+    assert model.input_names() == ["input_ids", "attention_mask"]
+    with torch.no_grad():
+        want = module(ids, mask)
+    for level in ("O0", "O3"):
+        sess = model.create_session(SessionOptions().with_optimization_level(level))
+        got = sess.run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"]
+        torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-5)
+        # rows that differ only in padded positions give the same output on the valid positions
+        ids2 = ids.clone()
+        ids2[1, 5:] = 7
+        again = sess.run({"input_ids": ids2, "attention_mask": mask})["last_hidden_state"]
+        torch.testing.assert_close(again[1, :5], got[1, :5], atol=2e-5, rtol=1e-5)
