@@ -480,3 +480,45 @@ def _qlinear_matmul(i, a, c):
     y = torch.round(acc * sa_ * sb_ / sy.to(torch.float64)) + zy.to(torch.float64)
     lo, hi = (0, 255) if zy.dtype == torch.uint8 else (-128, 127)
     return [y.clamp(lo, hi).to(zy.dtype)]
+
+
+def _conv_args(a, nd):
+    pads = _ints(a.get("pads")) or [0] * (2 * nd)
+    if pads[:nd] != pads[nd:]:
+        raise InvalidAttribute("integer convolution: asymmetric pads are not supported")
+    if a.get("auto_pad", "NOTSET") not in ("NOTSET", b"NOTSET"):
+        raise InvalidAttribute("integer convolution: auto_pad other than NOTSET is not supported")
+    return dict(stride=_ints(a.get("strides")) or [1] * nd, padding=pads[:nd],
+                dilation=_ints(a.get("dilations")) or [1] * nd, groups=int(a.get("group", 1)))
+
+
+def _int_conv(x, w, xz, wz, a):
+    """Exact integer convolution of (x - xz) with (w - wz[per output channel]) computed in float64."""
+    nd = x.dim() - 2
+    xs = x.to(torch.float64) - (float(xz.reshape(-1)[0]) if xz is not None else 0.0)
+    ws = w.to(torch.float64)
+    if wz is not None:
+        ws = ws - wz.to(torch.float64).reshape(-1, *([1] * (w.dim() - 1)))
+    fn = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[nd]
+    # zero padding must add (x - xz) = 0, i.e. pad the shifted tensor, which conv's own padding does
+    return fn(xs, ws, None, **_conv_args(a, nd))
+
+
+@op("ConvInteger", 2, 4)
+def _conv_integer(i, a, c):
+    y = _int_conv(i[0], i[1], i[2] if len(i) > 2 else None, i[3] if len(i) > 3 else None, a)
+    return [y.to(torch.int32)]
+
+
+@op("QLinearConv", 8, 9)
+def _qlinear_conv(i, a, c):
+    x, xs, xz, w, ws, wz, ys, yz = i[:8]
+    bias = i[8] if len(i) > 8 else None
+    acc = _int_conv(x, w, xz, wz, a)
+    if bias is not None:                                         # int32, in units of x_scale * w_scale
+        acc = acc + bias.to(torch.float64).reshape(1, -1, *([1] * (acc.dim() - 2)))
+    wsc = ws.to(torch.float64)
+    wsc = wsc.reshape(1, -1, *([1] * (acc.dim() - 2))) if wsc.numel() > 1 else wsc
+    y = torch.round(acc * xs.to(torch.float64) * wsc / ys.to(torch.float64)) + yz.to(torch.float64)
+    lo, hi = (0, 255) if yz.dtype == torch.uint8 else (-128, 127)
+    return [y.clamp(lo, hi).to(yz.dtype)]

@@ -186,3 +186,23 @@ def test_integer_matmul_family():
     real = ((a.float() - 128) * 0.02) @ (b.float() * 0.05)
     assert q.dtype == torch.uint8
     assert (q.float() - torch.clamp(torch.round(real / 0.1) + 3, 0, 255)).abs().max() <= 1       # ties may fall either way
+
+
+def test_integer_convolutions():
+    torch.manual_seed(1)
+    x = torch.randint(0, 256, (1, 2, 5, 5), dtype=torch.uint8)
+    w = torch.randint(-128, 128, (3, 2, 3, 3), dtype=torch.int8)
+    xz, wz = t(10, dtype=torch.uint8), t(1, 0, -1, dtype=torch.int8)
+    got = ex("ConvInteger", [x, w, xz, wz], pads=[1, 1, 1, 1], strides=[2, 2])[0]
+    ref = F.conv2d(x.double() - 10, w.double() - wz.double().view(3, 1, 1, 1), stride=2, padding=1)
+    assert got.dtype == torch.int32 and got.shape == (1, 3, 3, 3) and torch.equal(got.double(), ref)
+    xs, ws, ys = t(0.02), t(0.01, 0.02, 0.03), t(0.05)
+    yz = t(100, dtype=torch.uint8)
+    bias = torch.tensor([5, -3, 0], dtype=torch.int32)
+    q = ex("QLinearConv", [x, xs, xz, w, ws, wz, ys, yz, bias], pads=[1, 1, 1, 1])[0]
+    real = F.conv2d((x.double() - 10) * 0.02, (w.double() - wz.double().view(3, 1, 1, 1)) * ws.double().view(3, 1, 1, 1),
+                    bias.double() * 0.02 * ws.double(), padding=1)
+    want = torch.clamp(torch.round(real / 0.05) + 100, 0, 255)
+    assert q.dtype == torch.uint8 and q.shape == (1, 3, 5, 5) and (q.double() - want).abs().max() <= 1
+    with pytest.raises(InvalidAttribute):
+        ex("ConvInteger", [x, w], pads=[0, 1, 1, 1])
