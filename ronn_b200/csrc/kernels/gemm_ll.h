@@ -1,0 +1,48 @@
+// C interface of the low-latency tensor-parallel projection (gemm_ll.cu): row-parallel GEMM + two-phase all-reduce
+// over NVLink with {data, sequence} words + bias, residual and LayerNorm / RMSNorm in one launch.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define RONN_LL_MAX_RANKS 8
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// scatter_area[r] / result_area[r]: address of rank r's copy of the two symmetric areas as mapped into this process;
+// result_mc: multicast address of the result area (nvls = 1) or null.  Both areas start zeroed.  A value takes
+// 4 bytes in an area (two 16-bit values share an 8-byte word with the call's sequence number).
+typedef struct RonnGemmLLParams {
+  const void* A;                 // [M, K] activations of this rank's K shard, row stride lda (elements)
+  const void* W;                 // [N, K] weights of this rank's K shard, row stride ldw
+  int M, N, K, lda, ldw;         // N % 32 == 0
+  int bn;                        // 0 = auto, else 32 | 64 | 128
+  int dtype;                     // 0 bf16, 1 fp16
+  void* scatter_area[RONN_LL_MAX_RANKS];
+  long scatter_parity_stride;    // bytes per parity: >= world * ceil(M / world) * N * 4
+  void* result_area[RONN_LL_MAX_RANKS];
+  void* result_mc;
+  long result_parity_stride;     // bytes per parity: >= M * N * 4
+  void* state;                   // 8 zero-initialised uint32 in local memory
+  int rank, world, nvls;
+  void* out;                     // X [M, ld_out], local memory
+  void* norm_out;                // H (norm_mode != 0), same row stride
+  long ld_out;
+  const void* bias;              // [N] or null
+  const void* residual;          // [M, ld_res] or null (the same values on every rank)
+  long ld_res;
+  const void* gamma;
+  const void* beta;
+  float eps;
+  int norm_mode;                 // 0 none, 1 LayerNorm, 2 RMSNorm (N <= 8192)
+  double wait_seconds;           // limit of every poll
+  void* trace;                   // optional: 8 x uint64 %globaltimer stamps per CTA (entry, partials sent, -, owned rows
+                                 // reduced and broadcast, all rows unpacked and normalised, -, -, exit)
+} RonnGemmLLParams;
+
+int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -4,10 +4,16 @@
 
 For the decode shapes of GPT-2 medium at this world size it times, per call (CUDA-graph replay of 20 back-to-back
 calls, device events, max over ranks):
-  fused      ONE kernel: partial GEMM + cross-rank reduction over NVLink + bias + residual + LayerNorm
+  fused      ONE kernel: partial GEMM + cross-rank reduction over NVLink + bias + residual + LayerNorm, once per
+             exchange protocol (two-shot over NVLS multimem, two-shot over peer loads / stores, one-shot pull)
   library    tcgen05 GEMM kernel + NCCL all-reduce + torch add(bias, residual) + LayerNorm kernel
   gemm_only  the local partial GEMM alone (lower bound of both)
-and reports the roofline of the fused op: max(FLOPs / measured GEMM peak, bytes over NVLink / 770 GB/s).
+and reports the roofline of the fused op: max(FLOPs / measured GEMM peak, bytes over NVLink / 770 GB/s), with the
+bytes of a minimal all-reduce, 2 (W - 1) / W x result, which is what the two-shot protocol moves.
+
+For the low-latency and two-shot protocols it also prints where the time of one call goes: %globaltimer stamps taken inside the kernel
+(entry, GEMM stored, counters raised, all ranks' tiles seen, rows reduced and stored, "delivered" raised, all
+deliveries seen), median over the CTAs of a rank, then the max over ranks.
 """
 from __future__ import annotations
 
@@ -71,6 +77,28 @@ def main():
         def fused():
             comm.gemm_allreduce(a, w, bias, res, norm=("layernorm", gam, bias, 1e-5))
 
+        def phases():
+            """One eager call with in-kernel timestamps: ns spent per phase (median over CTAs)."""
+            tr = torch.zeros((600, 8), dtype=torch.int64, device=dev)
+            comm.trace = tr
+            dist.barrier()
+            torch.cuda.synchronize()
+            fused()
+            torch.cuda.synchronize()
+            comm.trace = None
+            t = tr[tr[:, 0] > 0].double()
+            if t.numel() == 0:
+                return {}
+            t0 = t[:, 0].min()
+            med = lambda col: float((t[:, col][t[:, col] > 0] - t0).median().item()) if bool((t[:, col] > 0).any()) else 0.0
+            if comm.proto == "ll":
+                marks = {"partials_sent": med(1), "owned_rows_broadcast": med(3), "all_rows_normalised": med(4),
+                         "exit": float((t[:, 7].max() - t0).item())}
+            else:
+                marks = {"gemm_stored": med(1), "published": med(2), "all_tiles_seen": med(3), "rows_stored": med(4),
+                         "delivered_sent": med(5), "all_delivered_seen": med(6), "exit": float((t[:, 7].max() - t0).item())}
+            return {k: round(lib.max_over_ranks(v) / 1e3, 2) for k, v in marks.items()}
+
         def library():
             y = K.gemm(a, w)
             lib.all_reduce(y)
@@ -80,14 +108,30 @@ def main():
         def gemm_only():
             K.gemm(a, w)
 
-        t_f, t_l, t_g = _time_graph(fused), _time_graph(library), _time_graph(gemm_only)
-        t_f, t_l, t_g = lib.max_over_ranks(t_f), lib.max_over_ranks(t_l), lib.max_over_ranks(t_g)
+        t_l, t_g = lib.max_over_ranks(_time_graph(library)), lib.max_over_ranks(_time_graph(gemm_only))
         flops = 2.0 * M * N * Kl
-        nvlink_bytes = (world - 1) * M * N * 2.0                 # each rank pulls every peer's bf16 partials
+        # per GPU and direction: fp32 partials of the rows it owns come in from W - 1 peers (1/W of the result each),
+        # the finished 16-bit rows (X and H) go out to W - 1 peers
+        nvlink_bytes = (world - 1) / world * M * N * (4.0 + 2 * 2.0)
         roof = max(flops / (tf * 1e12), nvlink_bytes / 770e9) * 1e6
-        out.append({"op": name, "M": M, "N": N, "K_local": Kl, "world": world, "fused_us": round(t_f, 2),
-                    "library_us": round(t_l, 2), "gemm_only_us": round(t_g, 2), "roofline_us": round(roof, 2),
-                    "fused_frac_of_roofline": round(roof / t_f, 3), "speedup_vs_library": round(t_l / t_f, 2)})
+        row = {"op": name, "M": M, "N": N, "K_local": Kl, "world": world, "library_us": round(t_l, 2),
+               "gemm_only_us": round(t_g, 2), "roofline_us": round(roof, 2)}
+        have_mc = comm.nvls_available and os.environ.get("RONN_NVLS", "1") != "0"
+        protos = []
+        if comm._ll_ok(M, N):
+            protos += ([("ll_nvls", "ll", True)] if have_mc else []) + [("ll_p2p", "ll", False)]
+        protos += ([("two_shot_nvls", "two_shot", True)] if have_mc else []) + [("two_shot_p2p", "two_shot", False)]
+        if M * N <= comm.one_shot_elems:
+            protos.append(("one_shot_pull", "pull", False))
+        for tag, proto, nvls in protos:
+            comm.proto, comm.nvls, comm.push = proto, nvls, False
+            t_f = lib.max_over_ranks(_time_graph(fused))
+            row[tag + "_us"] = round(t_f, 2)
+            row[tag + "_frac_of_roofline"] = round(roof / t_f, 3)
+            row[tag + "_speedup_vs_library"] = round(t_l / t_f, 2)
+            if proto in ("two_shot", "ll"):
+                row[tag + "_phases_us"] = phases()
+        out.append(row)
     comm.check()
     if rank == 0:
         for r in out:

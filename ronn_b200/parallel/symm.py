@@ -7,8 +7,21 @@ computes this rank's partial GEMM on the tensor cores, publishes it, waits for t
 bounded spin, and reduces straight from peer memory (see ``csrc/kernels/comm_gemm.cu``).  NCCL is
 only used for the rendezvous and for the tiny (max, index) gather of the sharded argmax.
 
+Four exchange protocols share the class (``RONN_TP_PROTO`` or the ``proto`` argument):
+
+* ``ll`` (default, results up to ``RONN_LL_ELEMS`` elements with N % 32 == 0): ``csrc/kernels/gemm_ll.cu``.  Partial
+  rows travel to their owner rank and finished rows to every rank as {data, sequence} words; readers poll their own
+  memory, so no fence, flag or atomic lies between the ranks and a call costs two one-way NVLink trips.  Larger
+  results fall through to ``pull`` / the library all-reduce.
+* ``two_shot``: ``csrc/kernels/gemm_fuse.cu``.  Every output row has one owner rank; the owner sums the
+  fp32 partials of all ranks (``multimem.ld_reduce`` through the NVSwitch when the allocation has a multicast
+  address, peer loads otherwise), applies bias / residual / norm once and stores the finished rows into every
+  rank's output (``multimem.st`` or peer stores).  Each rank moves 1/W of the result.
+* ``pull`` / ``push``: the one-shot protocols of ``csrc/kernels/comm_gemm.cu`` (every rank reads or receives every
+  peer's whole partial result and reduces redundantly).
+
 A device-side wait that runs out leaves ``STATUS_WAIT_PEER`` in the status word; ``check()``
-turns it into ``CommTimeoutError`` on the host.
+turns it into ``CommTimeoutError`` on the host; ``reset()`` (collective) clears the counters afterwards.
 """
 from __future__ import annotations
 
@@ -33,9 +46,10 @@ class FusedComm(TPComm):
     fused = True
 
     def __init__(self, device: torch.device, max_rows: int = 8192, max_cols: int = 8192, group=None,
-                 wait_seconds: Optional[float] = None):
+                 wait_seconds: Optional[float] = None, proto: Optional[str] = None, nvls: Optional[bool] = None):
         super().__init__(group)
-        self._ctor = dict(max_rows=max_rows, max_cols=max_cols, group=group, wait_seconds=wait_seconds)
+        self._ctor = dict(max_rows=max_rows, max_cols=max_cols, group=group, wait_seconds=wait_seconds, proto=proto,
+                          nvls=nvls)
         if self.world > MAX_RANKS:
             raise ProviderError(f"fused collectives support at most {MAX_RANKS} ranks")
         import torch.distributed._symmetric_memory as symm
@@ -79,7 +93,11 @@ class FusedComm(TPComm):
         self._ag_flags_local = ptrs[self.rank] + 2 * self.part_stride + 256
         self._ag_state = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._state = torch.zeros(8, dtype=torch.int32, device=self.device)
-        self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 10.0))
+        self.wait_seconds = float(os.environ.get("RONN_PEER_WAIT_S", wait_seconds if wait_seconds is not None else 2.0))
+        self.proto = proto or os.environ.get("RONN_TP_PROTO", "ll")
+        if self.proto not in ("ll", "two_shot", "pull", "push"):
+            raise ProviderError(f"unknown tensor-parallel protocol '{self.proto}'")
+        self._init_two_shot(symm, pg, nvls)
         self.fused_calls = 0
         self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
         self.argmax_exchange = self.world > 1 and os.environ.get("RONN_ARGMAX_EXCHANGE", "1") != "0"
@@ -88,6 +106,10 @@ class FusedComm(TPComm):
         # the data volume, and the pull protocol wins (TP=4 103K against 92K, TP=8 102K against 71K).
         env = os.environ.get("RONN_TP_PUSH")
         self.push = self.world > 1 and (env == "1" if env is not None else self.world == 2)
+        if self.proto == "push":
+            self.push = self.world > 1
+        elif self.proto == "pull":
+            self.push = False
         dist.barrier(group=group)                                     # flags and counters are zero everywhere
 
     def clone(self, max_rows: Optional[int] = None) -> "FusedComm":
@@ -97,6 +119,176 @@ class FusedComm(TPComm):
         if max_rows is not None:
             kw["max_rows"] = max_rows
         return FusedComm(self.device, **kw)
+
+    # ------------------------------------------------------------------ two-shot protocol (gemm_fuse.cu)
+    def _init_two_shot(self, symm, pg, nvls: Optional[bool]) -> None:
+        """Second symmetric allocation: counters, fp32 partial slots (two parities) and two alternating pairs of output
+        slots (residual stream X, normalised H).  Outputs must be symmetric because the owner of a row stores it into
+        every rank's copy."""
+        from ..ops import fuse as F
+        lib = F._lib()
+        self._flag_ints = lib.ronn_gemm_fuse_flag_ints()
+        self._flag_bytes = (self._flag_ints * 4 + 1023) // 1024 * 1024
+        self.parity_floats = min(self.max_elems, int(os.environ.get("RONN_TWO_SHOT_ELEMS", 8 << 20)))
+        self._out_bytes = self.parity_floats * 2
+        # areas of the low-latency protocol: [2 parities][world sources][owner rows * N] and [2 parities][M * N]
+        # values of 4 bytes (a 16-bit value and its half of the sequence word)
+        self.ll_elems = min(int(os.environ.get("RONN_LL_ELEMS", 1 << 20)), self.max_elems)
+        self._ll_cols = 8192
+        self._ll_scatter_stride = (self.ll_elems + self.world * self._ll_cols) * 4
+        self._ll_result_stride = self.ll_elems * 4
+        self._ll_off = self._flag_bytes + 2 * self.parity_floats * 4 + 4 * self._out_bytes
+        total = self._ll_off + 2 * self._ll_scatter_stride + 2 * self._ll_result_stride
+        self._buf2 = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self._buf2.zero_()
+        torch.cuda.synchronize(self.device)
+        self._hdl2 = symm.rendezvous(self._buf2, pg.group_name if hasattr(pg, "group_name") else pg)
+        self._ptrs2 = [int(p) for p in self._hdl2.buffer_ptrs]
+        mc = int(getattr(self._hdl2, "multicast_ptr", 0) or 0)
+        want = nvls if nvls is not None else os.environ.get("RONN_NVLS", "1") != "0"
+        self.nvls_available = bool(mc) and self.world > 1
+        self.nvls = bool(want and self.nvls_available)              # may be switched off (not on) later
+        self._mc2 = mc
+        self._state2 = torch.zeros(lib.ronn_gemm_fuse_state_ints(), dtype=torch.int32, device=self.device)
+        self._slot = 0
+        self._ll_state = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.trace = None                                           # set to a uint64 tensor [ctas, 8] to record timestamps
+
+    def _slot_views(self, slot: int, M: int, N: int, dtype):
+        off_x = self._flag_bytes + 2 * self.parity_floats * 4 + (2 * slot) * self._out_bytes
+        off_h = off_x + self._out_bytes
+        n = M * N * 2
+        x = self._buf2[off_x: off_x + n].view(dtype).view(M, N)
+        h = self._buf2[off_h: off_h + n].view(dtype).view(M, N)
+        return off_x, off_h, x, h
+
+    def reset(self) -> None:
+        """Collective: clear every counter after an abandoned wait (the ranks' counters no longer agree)."""
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        self._buf2[: self._flag_bytes].zero_()
+        self._buf2[self._ll_off:].zero_()
+        self._state2.zero_()
+        self._ll_state.zero_()
+        self._buf[2 * self.part_stride: 2 * self.part_stride + 512].zero_()
+        self._state.zero_()
+        self._ag_state.zero_()
+        self._argmax_state.zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    def _gemm_two_shot(self, a, w_nk, bias, residual, norm, scatter: bool, splitk: int = 0, bn: int = 0):
+        from ..ops import fuse as F
+        M, Kd = a.shape
+        N = w_nk.shape[0]
+        S = splitk if splitk > 0 else F.pick_splitk(M, N, Kd)
+        while S > 1 and S * M * N > self.parity_floats:
+            S //= 2
+        if S * M * N > self.parity_floats:
+            raise ProviderError(f"fused GEMM of {M}x{N} exceeds the symmetric buffer of the two-shot protocol")
+        if bias is not None and bias.dtype != a.dtype:
+            bias = bias.to(a.dtype)
+        per = -(-M // self.world)
+        p = F.FuseParams()
+        p.A, p.W = a.data_ptr(), w_nk.data_ptr()
+        p.M, p.N, p.K, p.lda, p.ldw = M, N, Kd, a.stride(0), w_nk.stride(0)
+        p.splitk, p.bn, p.dtype = S, bn, 0 if a.dtype == torch.bfloat16 else 1
+        part_off = self._flag_bytes
+        for r in range(self.world):
+            p.part[r] = self._ptrs2[r] + part_off
+            p.flags[r] = self._ptrs2[r]
+        p.parity_stride = self.parity_floats
+        p.state = self._state2.data_ptr()
+        use_mc = self.nvls and self.nvls_available
+        p.rank, p.world, p.nvls, p.scatter = self.rank, self.world, 1 if use_mc else 0, 1 if scatter else 0
+        if use_mc:
+            p.part_mc, p.flags_mc = self._mc2 + part_off, self._mc2
+        normed = None
+        if scatter:
+            rows = max(min(per, M - self.rank * per), 0)
+            out = torch.empty((rows, N), dtype=a.dtype, device=a.device)
+            p.out[self.rank] = out.data_ptr()
+            for r in range(self.world):
+                if r != self.rank:
+                    p.out[r] = out.data_ptr()                     # never dereferenced in this mode
+            if norm is not None:
+                normed = torch.empty_like(out)
+                for r in range(self.world):
+                    p.norm_out[r] = normed.data_ptr()
+        else:
+            self._slot ^= 1
+            off_x, off_h, out, h = self._slot_views(self._slot, M, N, a.dtype)
+            for r in range(self.world):
+                p.out[r] = self._ptrs2[r] + off_x
+                p.norm_out[r] = self._ptrs2[r] + off_h
+            if use_mc:
+                p.out_mc, p.norm_mc = self._mc2 + off_x, self._mc2 + off_h
+            if norm is not None:
+                normed = h
+        p.ld_out = N
+        if residual is not None:
+            if residual.stride(1) != 1 or residual.shape != out.shape:
+                residual = residual.reshape(out.shape).contiguous()
+            p.residual, p.ld_res = residual.data_ptr(), residual.stride(0)
+        p.bias = None if bias is None else bias.data_ptr()
+        if norm is not None:
+            kind, gamma, beta, eps = norm
+            p.norm_mode, p.eps = (1 if kind == "layernorm" else 2), float(eps)
+            p.gamma = None if gamma is None else gamma.data_ptr()
+            p.beta = None if beta is None else beta.data_ptr()
+        p.wait_seconds = self.wait_seconds
+        p.trace = None if self.trace is None else self.trace.data_ptr()
+        rc = F._lib().ronn_gemm_fuse(C.byref(p), K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"gemm_fuse (world {self.world}) failed with code {rc}")
+        self.fused_calls += 1
+        return out if norm is None else (out, normed)
+
+    # ------------------------------------------------------------------ low-latency protocol (gemm_ll.cu)
+    def _ll_ok(self, M: int, N: int) -> bool:
+        return (self.world > 1 and M * N <= self.ll_elems and N % 32 == 0 and N <= self._ll_cols
+                and -(-M // self.world) * self.world * N * 4 <= self._ll_scatter_stride)
+
+    def _gemm_ll(self, a, w_nk, bias, residual, norm, bn: int = 0):
+        from ..ops import fuse as F
+        M, Kd = a.shape
+        N = w_nk.shape[0]
+        out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        if bias is not None and bias.dtype != a.dtype:
+            bias = bias.to(a.dtype)
+        if residual is not None and (residual.stride(1) != 1 or residual.shape != out.shape):
+            residual = residual.reshape(M, N).contiguous()
+        p = F.LLParams()
+        p.A, p.W = a.data_ptr(), w_nk.data_ptr()
+        p.M, p.N, p.K, p.lda, p.ldw = M, N, Kd, a.stride(0), w_nk.stride(0)
+        p.bn, p.dtype = bn, 0 if a.dtype == torch.bfloat16 else 1
+        res_off = self._ll_off + 2 * self._ll_scatter_stride
+        for r in range(self.world):
+            p.scatter_area[r] = self._ptrs2[r] + self._ll_off
+            p.result_area[r] = self._ptrs2[r] + res_off
+        use_mc = self.nvls and self.nvls_available
+        p.result_mc = (self._mc2 + res_off) if use_mc else None
+        p.scatter_parity_stride, p.result_parity_stride = self._ll_scatter_stride, self._ll_result_stride
+        p.state = self._ll_state.data_ptr()
+        p.rank, p.world, p.nvls = self.rank, self.world, 1 if use_mc else 0
+        p.out, p.ld_out = out.data_ptr(), out.stride(0)
+        p.bias = None if bias is None else bias.data_ptr()
+        if residual is not None:
+            p.residual, p.ld_res = residual.data_ptr(), residual.stride(0)
+        normed = None
+        if norm is not None:
+            kind, gamma, beta, eps = norm
+            normed = torch.empty_like(out)
+            p.norm_out, p.norm_mode, p.eps = normed.data_ptr(), (1 if kind == "layernorm" else 2), float(eps)
+            p.gamma = None if gamma is None else gamma.data_ptr()
+            p.beta = None if beta is None else beta.data_ptr()
+        p.wait_seconds = self.wait_seconds
+        p.trace = None if self.trace is None else self.trace.data_ptr()
+        rc = F._lib().ronn_gemm_ll(C.byref(p), K.status_word(a.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            raise K.KernelError(f"gemm_ll (world {self.world}) failed with code {rc}")
+        self.fused_calls += 1
+        return out if norm is None else (out, normed)
 
     # ------------------------------------------------------------------ fused row-parallel GEMM
     def _gemm_reduce(self, a, w_nk, bias, residual, row_begin, row_end, bn=0, norm=None):
@@ -144,6 +336,10 @@ class FusedComm(TPComm):
         moving (world - 1) full copies per rank costs more than a ring.  Results above ``one_shot_elems`` therefore
         take the GEMM kernel + library all-reduce + the fused bias/residual/norm kernel."""
         M, N = a.shape[0], w_nk.shape[0]
+        if self.proto == "ll" and self._ll_ok(M, N):
+            return self._gemm_ll(a, w_nk, bias, residual, norm, bn=bn)
+        if self.proto == "two_shot" and M <= 8192 and M * N <= self.parity_floats:
+            return self._gemm_two_shot(a, w_nk, bias, residual, norm, scatter=False, bn=bn)
         if self.world > 1 and M * N > self.one_shot_elems:
             y = K.gemm(a, w_nk)
             dist.all_reduce(y, group=self.group)
@@ -216,6 +412,8 @@ class FusedComm(TPComm):
         if M % self.world:
             raise ProviderError("reduce-scatter needs the row count to divide by the world size")
         per = M // self.world
+        if self.proto == "two_shot" and M <= 8192 and M * w_nk.shape[0] <= self.parity_floats:
+            return self._gemm_two_shot(a, w_nk, bias, residual_shard, None, scatter=True, bn=bn)
         return self._gemm_reduce(a, w_nk, bias, residual_shard, self.rank * per, (self.rank + 1) * per, bn)
 
     # ------------------------------------------------------------------ fused all-gather -> column-parallel GEMM

@@ -19,9 +19,14 @@ def main():
     comm = FusedComm(dev, max_rows=1024, max_cols=4096, wait_seconds=5.0)
     results = []
     torch.manual_seed(100 + rank)
-    for push in (False, True):                     # pull from the peers' buffers / push into every rank's slots
-        comm.push = push
-        tag = "/push" if push else ""
+    # two-shot over peer loads / stores, two-shot over NVLS multimem (when the allocation has a multicast address),
+    # one-shot pull from the peers' buffers, one-shot push into every rank's slots
+    modes = [("ll", False, False, "/ll-p2p"), ("two_shot", False, False, "/2shot-p2p")]
+    if comm.nvls_available and os.environ.get("RONN_NVLS", "1") != "0":
+        modes += [("ll", True, False, "/ll-nvls"), ("two_shot", True, False, "/2shot-nvls")]
+    modes += [("pull", False, False, ""), ("push", False, True, "/push")]
+    for proto, nvls, push, tag in modes:
+        comm.proto, comm.nvls, comm.push = proto, nvls, push
         for (M, N, Kl) in [(256, 1024, 128), (256, 1024, 512), (200, 264, 64), (1024, 1024, 256), (16, 4096, 64)]:
             for it in range(3):                        # consecutive calls alternate the parity slots
                 a = torch.randn(M, Kl, device=dev).bfloat16()
@@ -31,9 +36,13 @@ def main():
                 dist.broadcast(bias, 0)
                 dist.broadcast(res, 0)
                 y = comm.gemm_allreduce(a, w, bias, res)
-                part = (a.float() @ w.float().t()).bfloat16().float()
+                # the one-shot protocols exchange bf16 partials, the two-shot protocol fp32 ones
+                part = (a.float() @ w.float().t())
+                if proto != "two_shot":
+                    part = part.bfloat16().float()
                 dist.all_reduce(part)
                 ref = part + bias.float() + res.float()
+                y = y.clone()                                  # two-shot results live in a slot that later calls reuse
                 err = (y.float() - ref).abs().max().item()
                 # bit-identical on every rank
                 y0 = y.clone()
@@ -44,6 +53,7 @@ def main():
                     dist.broadcast(gam, 0)
                     dist.broadcast(bet, 0)
                     y2, hn = comm.gemm_allreduce(a, w, bias, res, norm=("layernorm", gam, bet, 1e-5))
+                    y2, hn = y2.clone(), hn.clone()
                     href = torch.nn.functional.layer_norm(y2.float(), (N,), gam.float(), bet.float(), 1e-5)
                     results.append({"mode": "ar+ln" + tag, "M": M, "N": N, "K": Kl, "identical": bool(torch.equal(y2, y)),
                                     "err": (hn.float() - href).abs().max().item() * 0.5})
@@ -52,7 +62,7 @@ def main():
                     ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
                     errs = (ys.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
                     results.append({"mode": "rs" + tag, "M": M, "N": N, "K": Kl, "err": errs, "identical": True})
-    comm.push = False
+    comm.proto, comm.nvls, comm.push = "pull", False, False
     # row-parallel BitLinear: ternary x int8 partials written into the symmetric slot, reduced over peer memory
     from ronn_b200.ops import bitnet as KB
     for (M, N, Kl) in [(128, 2560, 320), (37, 512, 256), (128, 1024, 864)]:
@@ -119,6 +129,39 @@ def main():
     dist.all_reduce(p2)
     results.append({"mode": "graph", "err": max((y1.float() - p1).abs().max().item(), (y2.float() - p2).abs().max().item()),
                     "identical": True})
+    # the same chain through the two-shot protocol (fp32 partials, results in alternating symmetric slots), with an odd
+    # number of calls per replay so that the parity of the partial slots alternates between replays
+    nv = [False, True] if comm.nvls_available and os.environ.get("RONN_NVLS", "1") != "0" else [False]
+    for proto, nvls in [(pr, n) for pr in ("ll", "two_shot") for n in nv]:
+        comm.proto, comm.nvls = proto, nvls
+        gam = torch.ones(1024, device=dev, dtype=torch.bfloat16)
+        comm.gemm_allreduce(a, w)
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y1 = comm.gemm_allreduce(a, w)
+            y2, h2 = comm.gemm_allreduce(y1[:, :128].contiguous(), w, None, y1, norm=("rmsnorm", gam, None, 1e-5))
+            y1 = y1.clone()                        # results alternate between two slots: the third call reuses y1's
+            y3 = comm.gemm_allreduce(h2[:, :128].contiguous(), w)
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+        rnd = (lambda t: t.bfloat16().float()) if proto == "ll" else (lambda t: t)      # 16-bit partials on the wire
+        q1 = rnd(a.float() @ w.float().t())
+        dist.all_reduce(q1)
+        q2 = rnd(y1[:, :128].float() @ w.float().t())
+        dist.all_reduce(q2)
+        q2 = q2 + y1.float()
+        hh = y2.float() * torch.rsqrt(y2.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+        q3 = rnd(h2[:, :128].float() @ w.float().t())
+        dist.all_reduce(q3)
+        err = max((y1.float() - q1).abs().max().item(), (y2.float() - q2).abs().max().item(),
+                  (h2.float() - hh).abs().max().item(), (y3.float() - q3).abs().max().item())
+        y0 = y3.clone()
+        dist.broadcast(y0, 0)
+        results.append({"mode": f"graph/{proto}-" + ("nvls" if nvls else "p2p"), "err": err, "identical": bool(torch.equal(y0, y3))})
+    comm.proto, comm.nvls = "pull", False
     comm.check()
     gathered = [None] * world
     dist.all_gather_object(gathered, results)

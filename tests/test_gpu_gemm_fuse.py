@@ -1,0 +1,110 @@
+"""Fused skinny GEMM (split-K GEMM + row reduction + bias / activation / residual + norm in one launch), single GPU:
+numerics against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, dtype=torch.bfloat16, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(dtype)
+
+
+def _ref(a, w, bias, res, act, norm, gamma, beta, eps=1e-5):
+    x = a.float() @ w.float().t()
+    if bias is not None:
+        x = x + bias.float()
+    if act == "gelu":
+        x = F.gelu(x, approximate="tanh")
+    elif act == "relu":
+        x = torch.relu(x)
+    if res is not None:
+        x = x + res.float()
+    xs = x.to(a.dtype).float()                       # the norm sees the stored (rounded) residual stream
+    if norm == "layernorm":
+        h = F.layer_norm(xs, (xs.shape[-1],), gamma.float(), beta.float(), eps)
+    elif norm == "rmsnorm":
+        h = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + eps) * gamma.float()
+    else:
+        h = None
+    return x, h
+
+
+@pytest.mark.parametrize("M,N,K_,S,bn", [
+    (256, 1024, 1024, 4, 0), (256, 1024, 4096, 8, 64), (256, 1024, 4096, 4, 32), (200, 264, 320, 2, 32),
+    (37, 136, 1024, 3, 0), (1, 1024, 1024, 0, 0), (128, 2560, 6912, 0, 128), (1024, 1024, 256, 1, 0),
+    (256, 768, 3072, 4, 0)])
+@pytest.mark.parametrize("norm", ["", "layernorm", "rmsnorm"])
+def test_gemm_fuse_rows(M, N, K_, S, bn, norm):
+    from ronn_b200.ops import kernels as K
+    from ronn_b200.ops.fuse import gemm_fuse
+    a, w = _rand(M, K_), _rand(N, K_, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    gamma, beta = _rand(N), _rand(N)
+    for it in range(3):                               # consecutive calls alternate the parity slots and advance the counters
+        r = gemm_fuse(a, w, bias, res, norm=(norm, gamma, beta if norm == "layernorm" else None, 1e-5) if norm else None,
+                      splitk=S, bn=bn)
+        K.check_status()
+        x, h = (r if norm else (r, None))
+        xr, hr = _ref(a, w, bias, res, "", norm, gamma, beta)
+        tol = 3e-2 * math.sqrt(K_ / 64)
+        torch.testing.assert_close(x.float(), xr, atol=tol, rtol=2e-2)
+        if norm:
+            # compare the norm against the norm of the kernel's own stored x: isolates it from GEMM rounding
+            _, hr2 = _ref(a, w, bias, res, "", norm, gamma, beta)
+            xs = x.float()
+            if norm == "layernorm":
+                hk = F.layer_norm(xs, (N,), gamma.float(), beta.float(), 1e-5)
+            else:
+                hk = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()
+            torch.testing.assert_close(h.float(), hk, atol=4e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K_,S,act", [(256, 3072, 1024, 2, ""), (256, 4096, 1024, 4, "gelu"), (100, 6000, 512, 2, "relu"),
+                                           (256, 50264, 256, 1, "")])
+def test_gemm_fuse_flat(M, N, K_, S, act):
+    """Rows wider than 4096 values (and any row without a norm above that width) take the flat path of phase 2."""
+    from ronn_b200.ops import kernels as K
+    from ronn_b200.ops.fuse import gemm_fuse
+    a, w = _rand(M, K_), _rand(N, K_, scale=0.05)
+    bias = _rand(N)
+    for it in range(2):
+        x = gemm_fuse(a, w, bias, None, activation=act, splitk=S)
+        K.check_status()
+        xr, _ = _ref(a, w, bias, None, act, "", None, None)
+        torch.testing.assert_close(x.float(), xr, atol=3e-2 * math.sqrt(K_ / 64), rtol=2e-2)
+
+
+def test_gemm_fuse_graph_replay():
+    """The counters and the call parity live on the device: replays of a captured chain need no new arguments."""
+    from ronn_b200.ops import kernels as K
+    from ronn_b200.ops.fuse import gemm_fuse
+    M, N = 256, 1024
+    a, w1, w2 = _rand(M, N), _rand(N, N, scale=0.03), _rand(N, N, scale=0.03)
+    gamma, beta = _rand(N), _rand(N)
+    gemm_fuse(a, w1, None, a, norm=("layernorm", gamma, beta, 1e-5))
+    torch.cuda.synchronize()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        gemm_fuse(a, w1, None, a, norm=("layernorm", gamma, beta, 1e-5))      # scratch of the capture stream
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        x1, h1 = gemm_fuse(a, w1, None, a, norm=("layernorm", gamma, beta, 1e-5))
+        x2, h2 = gemm_fuse(h1, w2, None, x1, norm=("layernorm", gamma, beta, 1e-5))
+        x3 = gemm_fuse(h2, w1, None, x2)
+    for _ in range(7):                                 # an odd number of calls per replay: the parity alternates between replays
+        g.replay()
+    torch.cuda.synchronize()
+    K.check_status()
+    r1, hr1 = _ref(a, w1, None, a, "", "layernorm", gamma, beta)
+    torch.testing.assert_close(x1.float(), r1, atol=0.15, rtol=2e-2)
+    r2, hr2 = _ref(h1, w2, None, x1, "", "layernorm", gamma, beta)
+    torch.testing.assert_close(x2.float(), r2, atol=0.15, rtol=2e-2)
+    torch.testing.assert_close(h2.float(), F.layer_norm(x2.float(), (N,), gamma.float(), beta.float(), 1e-5), atol=4e-2, rtol=2e-2)
+    r3, _ = _ref(h2, w1, None, x2, "", "", None, None)
+    torch.testing.assert_close(x3.float(), r3, atol=0.15, rtol=2e-2)

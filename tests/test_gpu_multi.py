@@ -112,3 +112,41 @@ def test_push_mode_wait_runs_out_and_context_survives():
     y = K.gemm(a, w)
     torch.testing.assert_close(y.float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
     K.check_status(dev)
+
+
+def test_two_shot_wait_runs_out_and_context_survives():
+    """Two-shot protocol, peer-load mode, with a second 'rank' that never runs: the row-tile counters never complete,
+    the bounded wait gives up with STATUS_WAIT_PEER and the context stays usable.  Both 'ranks' are buffers of this GPU."""
+    import ctypes as C
+    from ronn_b200.api.errors import CommTimeoutError
+    from ronn_b200.ops import fuse as F
+    from ronn_b200.ops import kernels as K
+    dev = torch.device("cuda", 0)
+    M, N, Kd = 128, 256, 64
+    a = torch.randn(M, Kd, device=dev).bfloat16()
+    w = torch.randn(N, Kd, device=dev).bfloat16()
+    lib = F._lib()
+    parts = [torch.zeros(2 * M * N, dtype=torch.float32, device=dev) for _ in range(2)]
+    flags = [torch.zeros(lib.ronn_gemm_fuse_flag_ints(), dtype=torch.int32, device=dev) for _ in range(2)]
+    outs = [torch.zeros(M, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    state = torch.zeros(lib.ronn_gemm_fuse_state_ints(), dtype=torch.int32, device=dev)
+    p = F.FuseParams()
+    p.A, p.W, p.M, p.N, p.K, p.lda, p.ldw = a.data_ptr(), w.data_ptr(), M, N, Kd, Kd, Kd
+    p.splitk, p.bn, p.dtype = 1, 0, 0
+    for r in range(2):
+        p.part[r], p.flags[r], p.out[r] = parts[r].data_ptr(), flags[r].data_ptr(), outs[r].data_ptr()
+    p.parity_stride, p.state = M * N, state.data_ptr()
+    p.rank, p.world, p.nvls, p.scatter, p.ld_out = 0, 2, 0, 0, N
+    p.wait_seconds = 0.3
+    K.check_status(dev)
+    rc = lib.ronn_gemm_fuse(C.byref(p), K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    with pytest.raises(CommTimeoutError, match="peer"):
+        K.check_status(dev)
+    # rank 0 raised the counter of row tile 0 on both 'ranks', but a call completes a counter only with every rank's arrivals
+    assert int(flags[0][0]) == int(flags[1][0]) != 0
+    assert int(flags[0][0]) % 65536 != 0
+    y = K.gemm(a, w)                                # the context is alive and later kernels run
+    torch.testing.assert_close(y.float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
+    K.check_status(dev)
