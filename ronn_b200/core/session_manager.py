@@ -151,3 +151,68 @@ class SessionManager:
     def shutdown(self) -> None:
         for sid in self.list_sessions():
             self.destroy_session(sid)
+
+
+@dataclass
+class AdmissionTicket:
+    client: str
+    admitted_at: float
+    deadline: float
+
+
+class RequestAdmission:
+    """Admission control of the serving front end with the SessionManager's vocabulary: ``max_in_flight`` plays the
+    role of ``max_sessions`` (requests admitted and not yet answered), ``max_per_client`` that of a session's
+    ``max_concurrent_inferences``, ``timeout_seconds`` that of its inference timeout.  ``acquire`` returns a ticket or
+    None (refused); ``release`` returns it and feeds the statistics (count, average / min / max ms, errors)."""
+
+    def __init__(self, max_in_flight: int = 1024, max_per_client: int = 256, timeout_seconds: float = 600.0):
+        self.max_in_flight = max_in_flight
+        self.max_per_client = max_per_client
+        self.timeout_seconds = timeout_seconds
+        self._lock = threading.Lock()
+        self._per_client: Dict[str, int] = {}
+        self._in_flight = 0
+        self.refused = 0
+        self.stats = SessionStatistics()
+
+    def acquire(self, client: str = "local") -> Optional[AdmissionTicket]:
+        now = time.time()
+        with self._lock:
+            if self._in_flight >= self.max_in_flight or self._per_client.get(client, 0) >= self.max_per_client:
+                self.refused += 1
+                return None
+            self._in_flight += 1
+            self._per_client[client] = self._per_client.get(client, 0) + 1
+        return AdmissionTicket(client, now, now + self.timeout_seconds)
+
+    def expired(self, ticket: AdmissionTicket) -> bool:
+        return time.time() > ticket.deadline
+
+    def release(self, ticket: AdmissionTicket, error: bool = False) -> None:
+        ms = (time.time() - ticket.admitted_at) * 1e3
+        with self._lock:
+            if ticket.deadline < 0:
+                return                                  # already released
+            ticket.deadline = -1.0
+            self._in_flight -= 1
+            left = self._per_client.get(ticket.client, 1) - 1
+            if left <= 0:
+                self._per_client.pop(ticket.client, None)
+            else:
+                self._per_client[ticket.client] = left
+            s = self.stats
+            if error:
+                s.error_count += 1
+            else:
+                s.min_time_ms = ms if s.inference_count == 0 else min(s.min_time_ms, ms)
+                s.max_time_ms = max(s.max_time_ms, ms)
+                s.inference_count += 1
+                s.total_time_ms += ms
+            s.last_used = time.time()
+
+    def snapshot(self) -> Dict[str, float]:
+        with self._lock:
+            return {"in_flight": self._in_flight, "clients": len(self._per_client), "refused": self.refused,
+                    "answered": self.stats.inference_count, "errors": self.stats.error_count,
+                    "average_ms": round(self.stats.average_time_ms, 3)}

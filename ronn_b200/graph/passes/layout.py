@@ -66,19 +66,18 @@ class LayoutOptimizationPass(OptimizationPass):
         region_ids = {n.id for n in region}
         cons = graph.consumers()
         gap_outs = {n.outputs[0] for n in region if n.op_type == "GlobalAveragePool"}
-        exits = []
-        for t in image:
-            for c in cons.get(t, []):
-                if c.id in region_ids:
-                    continue
-                if t in gap_outs and c.op_type in ("Flatten", "Reshape", "Squeeze"):
-                    continue
-                exits.append((t, c))
-            if t in set(graph.output_names()) and t not in gap_outs:
-                exits.append((t, None))
+        produced = {o for n in region for o in n.outputs if o}
+        outputs = set(graph.output_names())
+        # --- exits: tensors PRODUCED inside the region that someone outside reads in NCHW.  Entry tensors are not
+        # exits: their other consumers keep reading the original NCHW tensor.
+        exits: Dict[str, list] = {}
+        for t in sorted(produced):
+            outside = [c for c in cons.get(t, []) if c.id not in region_ids
+                       and not (t in gap_outs and c.op_type in ("Flatten", "Reshape", "Squeeze"))]
+            if outside or (t in outputs and t not in gap_outs):
+                exits[t] = outside
         # --- entries: image tensors not produced inside the region
-        produced = {o for n in region for o in n.outputs}
-        entries = [t for t in image if t not in produced]
+        entries = sorted(t for t in image if t not in produced)
         if any(t in graph.initializers for t in entries):
             return stats
         # --- rewrite
@@ -95,22 +94,22 @@ class LayoutOptimizationPass(OptimizationPass):
             first = min((k for k, n in enumerate(graph.nodes) if t in n.inputs and n.id in region_ids))
             for n in region:
                 n.inputs = [new if i == t else i for i in n.inputs]
-            graph.add_node("Transpose", [t], [new], {"perm": [0, 2, 3, 1]}, name=f"to_nhwc_{t}", index=first)
-        for t, c in exits:
-            new = graph.fresh_name(t + "_nchw")
+            graph.add_node("Transpose", [t], [new], {"perm": [0, 2, 3, 1]}, name=graph.fresh_name(f"to_nhwc_{t}"), index=first)
+        for t, outside in exits.items():
             idx = max(k for k, n in enumerate(graph.nodes) if t in n.outputs) + 1
-            graph.add_node("Transpose", [t], [new], {"perm": [0, 3, 1, 2]}, name=f"to_nchw_{t}", index=idx)
-            if c is None:
-                # graph output: keep the public name on the NCHW tensor
-                for n in graph.nodes:
-                    if n.name == f"to_nchw_{t}":
-                        continue
-                    n.outputs = [f"{t}__nhwc" if o == t else o for o in n.outputs]
-                    n.inputs = [f"{t}__nhwc" if i == t else i for i in n.inputs]
-                tr = next(n for n in graph.nodes if n.name == f"to_nchw_{t}")
-                tr.inputs, tr.outputs = [f"{t}__nhwc"], [t]
+            if t in outputs:
+                # graph output: the public name stays on the NCHW tensor; the region works on a renamed NHWC tensor and
+                # outside consumers (which already read `t`) need no change
+                inner = graph.fresh_name(t + "__nhwc")
+                for n in region:
+                    n.outputs = [inner if o == t else o for o in n.outputs]
+                    n.inputs = [inner if i == t else i for i in n.inputs]
+                graph.add_node("Transpose", [inner], [t], {"perm": [0, 3, 1, 2]}, name=graph.fresh_name(f"to_nchw_{t}"), index=idx)
             else:
-                c.inputs = [new if i == t else i for i in c.inputs]
+                new = graph.fresh_name(t + "_nchw")
+                graph.add_node("Transpose", [t], [new], {"perm": [0, 3, 1, 2]}, name=graph.fresh_name(f"to_nchw_{t}"), index=idx)
+                for c in outside:
+                    c.inputs = [new if i == t else i for i in c.inputs]
         graph.metadata["ronn.layout"] = "NHWC"
         graph.sort_in_place()
         return stats

@@ -98,6 +98,50 @@ class ModelLoader:
         return _convert_model(doc, memoryview(data), blobs, base_dir)
 
 
+def _read_external(name: str, base_dir: str, loc: str, ext: Dict[str, str], dt, dims) -> bytes:
+    """Bytes of an external-data tensor.  The location comes from the (untrusted) model file, so it may only name a
+    regular file inside the model's own directory: absolute paths, paths that leave the directory and symbolic links
+    are refused, and offset / length are checked against the file and against the tensor's declared size."""
+    if os.path.isabs(loc) or loc.startswith(("/", "\\")) or (len(loc) > 1 and loc[1] == ":"):
+        raise TypeConversionError(f"tensor '{name}': external data location '{loc}' is an absolute path")
+    root = os.path.realpath(base_dir)
+    rel = os.path.normpath(loc)
+    if rel in (".", "") or rel == ".." or rel.startswith(".." + os.sep):
+        raise TypeConversionError(f"tensor '{name}': external data location '{loc}' leaves the model directory")
+    # every component below the model directory must be a real directory or file, never a link
+    part = root
+    for comp in rel.split(os.sep):
+        part = os.path.join(part, comp)
+        if os.path.islink(part):
+            raise TypeConversionError(f"tensor '{name}': external data location '{loc}' goes through a symbolic link")
+    full = os.path.realpath(part)
+    if os.path.commonpath([root, full]) != root or full == root:
+        raise TypeConversionError(f"tensor '{name}': external data location '{loc}' leaves the model directory")
+    try:
+        offset = int(ext.get("offset", 0))
+        length = int(ext["length"]) if "length" in ext else None
+    except ValueError as e:
+        raise TypeConversionError(f"tensor '{name}': external data offset / length is not a number") from e
+    count = int(np.prod(dims)) if dims else 1
+    need = count * dt.itemsize
+    try:
+        if not os.path.isfile(full):
+            raise IoError(f"tensor '{name}': external data file '{loc}' not found")
+        size = os.path.getsize(full)
+        if offset < 0 or offset > size or (length is not None and (length < 0 or offset + length > size)):
+            raise TypeConversionError(f"tensor '{name}': external data window [{offset}, +{length}) exceeds the "
+                                      f"{size}-byte file '{loc}'")
+        if length is not None and length > need:
+            raise TypeConversionError(f"tensor '{name}': external data length {length} exceeds the {need} bytes its "
+                                      f"shape {list(dims)} holds")
+        with open(full, "rb") as f:
+            f.seek(offset)
+            want = length if length is not None else need
+            return f.read(min(want, size - offset))
+    except OSError as e:
+        raise IoError(f"tensor '{name}': cannot read external data file '{loc}': {e}") from e
+
+
 def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir) -> torch.Tensor:
     code = td["data_type"]
     dt = DataTypeMapper.from_onnx(code)
@@ -109,9 +153,7 @@ def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir) -> 
         loc = ext.get("location")
         if not loc or base_dir is None:
             raise TypeConversionError(f"tensor '{_fix_str(td['name'])}' uses external data that cannot be located")
-        with open(os.path.join(base_dir, loc), "rb") as f:
-            f.seek(int(ext.get("offset", 0)))
-            raw = f.read(int(ext["length"])) if "length" in ext else f.read()
+        raw = _read_external(_fix_str(td["name"]), base_dir, loc, ext, dt, dims)
         return tensor_from_bytes(raw, dt, dims)
     if td["raw_off"] >= 0:
         raw = data[td["raw_off"]: td["raw_off"] + td["raw_len"]]

@@ -10,6 +10,7 @@ bucket), and the sampled tokens are read back and committed.
 from __future__ import annotations
 
 import time
+from collections import deque
 from typing import Callable, Dict, Iterable, List, Optional
 
 import numpy as np
@@ -26,20 +27,20 @@ from .scheduler import PLAN_DECODE, PLAN_NONE, PLAN_PREFILL, HostBatchBuffers, S
 class StepOutput:
     """What one iteration produced: ids of the requests that got a token, the tokens, and finish codes
     (0 running, 1 eos, 2 max_tokens).  Behaves like a sequence of ``Request`` objects."""
-    __slots__ = ("_engine", "req_ids", "tokens", "finished")
+    __slots__ = ("_engine", "req_ids", "tokens", "finished", "_reqs")
 
-    def __init__(self, engine, req_ids, tokens, finished):
+    def __init__(self, engine, req_ids, tokens, finished, reqs=None):
         self._engine, self.req_ids, self.tokens, self.finished = engine, req_ids, tokens, finished
+        self._reqs = reqs if reqs is not None else []
 
     def __len__(self):
         return len(self.req_ids)
 
     def __iter__(self):
-        reqs = self._engine.requests
-        return (reqs[int(i)] for i in self.req_ids)
+        return iter(self._reqs)
 
     def __getitem__(self, k):
-        return self._engine.requests[int(self.req_ids[k])]
+        return self._reqs[k]
 
 
 _BUCKETS = [1, 2, 4, 8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024]
@@ -84,6 +85,9 @@ class LLMEngine:
             self.sampled_host = self.sampled_host.pin_memory()
             self._status_host = self._status_host.pin_memory()
         self.requests: Dict[int, Request] = {}
+        # finished requests stay readable until ``release`` is called or ``max_finished_kept`` newer ones have finished
+        self._finished_order: deque = deque()
+        self.max_finished_kept = 4096
         self._next_id = 0
         self._graphs: Dict[int, tuple] = {}
         self.metrics = EngineMetrics()
@@ -124,13 +128,44 @@ class LLMEngine:
         r = self.requests.get(request_id)
         if r is None or r.finished:
             return False
+        self._finish(r, FinishReason.CANCELLED, time.perf_counter(), cancel=True)
+        return True
+
+    def _finish(self, r: Request, reason: FinishReason, now: float, cancel: bool = False, error: Optional[str] = None) -> None:
+        """End of a request's life in the engine: its tokens are copied out of the scheduler, the scheduler forgets it
+        (token history, block lists), the per-request counters are undone and the record joins the bounded list of
+        finished requests."""
         r._freeze()
-        self.sched.cancel(request_id)
+        if cancel:
+            self.sched.cancel(r.id)
+        self.sched.forget(r.id)
+        r._token_source = None
+        r.finish_reason = reason
+        r.finished_at = now
+        r.error = error
         if r.params.temperature > 0:
             self._non_greedy -= 1
-        r.finish_reason = FinishReason.CANCELLED
-        r.finished_at = time.perf_counter()
-        return True
+        if r.params.stop_sequences:
+            self._watch_count -= 1
+        if not cancel:
+            self.metrics.requests_finished += 1
+        self._finished_order.append(r.id)
+        while len(self._finished_order) > self.max_finished_kept:
+            self.requests.pop(self._finished_order.popleft(), None)
+
+    def release(self, request_id: int) -> None:
+        """Drop the record of a finished request (its result has been read)."""
+        r = self.requests.get(request_id)
+        if r is not None and r.finished:
+            del self.requests[request_id]
+
+    def fail_unfinished(self, reason: str) -> List[int]:
+        """Mark every waiting / running request as failed (used when steps keep failing); returns their ids."""
+        now = time.perf_counter()
+        ids = [rid for rid, r in self.requests.items() if not r.finished]
+        for rid in ids:
+            self._finish(self.requests[rid], FinishReason.ERROR, now, cancel=True, error=reason)
+        return ids
 
     @property
     def _watch(self) -> bool:
@@ -233,36 +268,26 @@ class LLMEngine:
                 if r.first_token_at is None:
                     r.first_token_at = now
                     self.metrics.observe_ttft(now - r.created_at)
+        out_reqs = [self.requests[int(i)] for i in req_ids[samples_mask]]        # records survive pruning below
         for i in np.nonzero(fin)[0]:
-            r = self.requests[int(req_ids[i])]
-            r._freeze()
-            r.finish_reason = FinishReason.EOS_TOKEN if fin[i] == 1 else FinishReason.MAX_TOKENS
-            r.finished_at = now
-            self.metrics.requests_finished += 1
-            if r.params.temperature > 0:
-                self._non_greedy -= 1
+            self._finish(self.requests[int(req_ids[i])], FinishReason.EOS_TOKEN if fin[i] == 1 else FinishReason.MAX_TOKENS, now)
         if self._watch:                                  # requests with stop sequences or a token callback
-            for i in np.nonzero(samples_mask)[0]:
-                r = self.requests[int(req_ids[i])]
+            for k, i in enumerate(np.nonzero(samples_mask)[0]):
+                r = out_reqs[k]
                 if r.finished:
                     if self.on_token is not None:
                         self.on_token(r, int(sampled[i]))
                     continue
                 if r.params.stop_sequences and self._hit_stop(r):
-                    r._freeze()
-                    self.sched.cancel(r.id)
-                    r.finish_reason = FinishReason.STOP_SEQUENCE
-                    r.finished_at = now
+                    self._finish(r, FinishReason.STOP_SEQUENCE, now, cancel=True)
                     self.metrics.requests_finished += 1
-                    if r.params.temperature > 0:
-                        self._non_greedy -= 1
                 if self.on_token is not None:
                     self.on_token(r, int(sampled[i]))
         self.metrics.observe_step(decode, n_items, n_tokens, int(samples_mask.sum()), now - t0,
                                   self.sched.num_waiting, self.sched.num_running,
                                   self.sched.num_free_blocks, self.runner.num_blocks)
         self.host_seconds_last = (t_dev - t0, now - t_dev)
-        return StepOutput(self, req_ids[samples_mask], sampled[samples_mask], fin[samples_mask])
+        return StepOutput(self, req_ids[samples_mask], sampled[samples_mask], fin[samples_mask], out_reqs)
 
     @staticmethod
     def _hit_stop(r: Request) -> bool:

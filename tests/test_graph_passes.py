@@ -230,3 +230,63 @@ def test_exact_gelu_is_not_absorbed_into_the_gpu_elementwise_chain():
     Optimizer("O3", ProviderType.GPU).optimize(g_exact)
     assert [n.op_type for n in g_tanh.nodes] == ["FusedElementwise"]
     assert "Gelu" in [n.op_type for n in g_exact.nodes]
+
+
+def _conv_w(gen, cout, cin):
+    return torch.randn(cout, cin, 3, 3, generator=gen) * 0.2
+
+
+def _check_levels(graph, feeds, names):
+    _, ref = run(graph, feeds)
+    for lvl in ("O2", "O3"):
+        s, out = run(graph, feeds, lvl)
+        s.graph().validate()
+        node_names = [n.name for n in s.graph().nodes if n.name]
+        assert len(node_names) == len(set(node_names))
+        for n in names:
+            assert out[n].shape == ref[n].shape
+            torch.testing.assert_close(out[n], ref[n], atol=1e-4, rtol=1e-4)
+    return s
+
+
+def test_layout_pass_entry_tensor_shared_with_layout_unaware_consumer():
+    """A graph input feeds a convolution AND a Concat / Shape: the other consumers keep reading the NCHW tensor."""
+    gen = torch.Generator().manual_seed(5)
+    b = GraphBuilder().add_input("x", [2, 3, 8, 8]).add_output("y", [2, 6, 8, 8]).add_output("shp", [4])
+    b.add_initializer("w1", _conv_w(gen, 3, 3)).add_initializer("w2", _conv_w(gen, 3, 3))
+    b.add_op("Conv", ["x", "w1"], ["c1"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    b.add_op("Relu", ["c1"], ["r1"])
+    b.add_op("Conv", ["r1", "w2"], ["c2"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    b.add_op("Concat", ["x", "c2"], ["y"], axis=1)
+    b.add_op("Shape", ["x"], ["shp"])
+    _check_levels(b.build(), {"x": torch.randn(2, 3, 8, 8)}, ["y", "shp"])
+
+
+def test_layout_pass_non_region_producer_shared_with_outside_consumer():
+    """Concat -> three convolutions plus Concat -> Concat: the shared tensor stays NCHW for the outside consumer."""
+    gen = torch.Generator().manual_seed(6)
+    b = GraphBuilder().add_input("a", [1, 2, 6, 6]).add_input("bb", [1, 2, 6, 6]).add_output("y", [1, 16, 6, 6])
+    for i in range(3):
+        b.add_initializer(f"w{i}", _conv_w(gen, 4, 4))
+    b.add_op("Concat", ["a", "bb"], ["cat"], axis=1)
+    for i in range(3):
+        b.add_op("Conv", ["cat", f"w{i}"], [f"c{i}"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    b.add_op("Concat", ["cat", "c0", "c1", "c2"], ["y"], axis=1)
+    feeds = {"a": torch.randn(1, 2, 6, 6), "bb": torch.randn(1, 2, 6, 6)}
+    s = _check_levels(b.build(), feeds, ["y"])
+    # the outside Concat still reads the original tensor, not a transposed copy of it
+    last = [n for n in s.graph().nodes if n.op_type == "Concat"][-1]
+    assert last.inputs[0] == "cat"
+
+
+def test_layout_pass_tensor_that_is_graph_output_and_read_outside_the_region():
+    gen = torch.Generator().manual_seed(7)
+    b = GraphBuilder().add_input("x", [2, 3, 8, 8]).add_output("feat", [2, 4, 8, 8]).add_output("flat", [2, 256])
+    b.add_initializer("w1", _conv_w(gen, 4, 3)).add_initializer("w2", _conv_w(gen, 4, 4))
+    b.add_op("Conv", ["x", "w1"], ["c1"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    b.add_op("Relu", ["c1"], ["r1"])
+    b.add_op("Conv", ["r1", "w2"], ["feat"], kernel_shape=[3, 3], pads=[1, 1, 1, 1])
+    b.add_op("Flatten", ["feat"], ["flat"], axis=1)
+    s = _check_levels(b.build(), {"x": torch.randn(2, 3, 8, 8)}, ["feat", "flat"])
+    back = [n for n in s.graph().nodes if n.op_type == "Transpose" and n.attributes["perm"] == [0, 3, 1, 2]]
+    assert len(back) == 1 and back[0].outputs == ["feat"]

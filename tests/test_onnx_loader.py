@@ -167,3 +167,47 @@ def test_model_api_load_errors(tmp_path):
     a, b = Model.load(q), Model.from_bytes(q.read_bytes())
     assert a.input_names() == b.input_names() == ["x"] and a.output_names() == ["y"]
     assert a.ir_version() == 8 and a.producer_name() == "ronn_b200" and a.metadata()["node_count"] == 2
+
+
+def _external_model(location, offset=None, length=None, dims=(4,)):
+    """A model with one float initializer whose bytes live in an external file named by `location` (hand-encoded)."""
+    t = b"".join(_field(1, 0, _varint(d)) for d in dims) + _field(2, 0, _varint(1)) + _ld(8, b"w")
+    entries = {"location": location}
+    if offset is not None:
+        entries["offset"] = str(offset)
+    if length is not None:
+        entries["length"] = str(length)
+    for k, v in entries.items():
+        t += _ld(13, _ld(1, k.encode()) + _ld(2, v.encode()))
+    t += _field(14, 0, _varint(1))                               # data_location = EXTERNAL
+    return _field(1, 0, _varint(8)) + _ld(7, _ld(5, t) + _ld(2, b"g"))
+
+
+@pytest.mark.parametrize("location,offset,length,err", [
+    ("../w.bin", None, None, "leaves the model directory"),
+    ("sub/../../w.bin", None, None, "leaves the model directory"),
+    ("/etc/passwd", None, None, "absolute path"),
+    ("inside.bin", None, 4096, "exceeds"),
+    ("inside.bin", 640, None, "exceeds"),
+    ("inside.bin", 0, 32, "exceeds the 16 bytes"),
+    ("inside.bin", "x", None, "not a number"),
+    ("missing.bin", None, None, "not found"),
+    ("link.bin", None, None, "symbolic link"),
+])
+def test_external_data_locations_are_confined_to_the_model_directory(tmp_path, location, offset, length, err):
+    from ronn_b200.api.errors import RonnError
+    sub = tmp_path / "model"
+    sub.mkdir()
+    (tmp_path / "w.bin").write_bytes(b"\0" * 64)
+    (sub / "inside.bin").write_bytes(b"\0" * 64)
+    (sub / "link.bin").symlink_to(tmp_path / "w.bin")
+    with pytest.raises(RonnError, match=err):
+        ModelLoader.load_from_bytes(_external_model(location, offset, length), base_dir=str(sub))
+
+
+def test_external_data_inside_the_model_directory_loads(tmp_path):
+    (tmp_path / "w.bin").write_bytes(np.arange(8, dtype=np.float32).tobytes())
+    m = ModelLoader.load_from_bytes(_external_model("w.bin", 16, 16), base_dir=str(tmp_path))
+    torch.testing.assert_close(m.initializers["w"], torch.arange(4, 8, dtype=torch.float32))
+    m = ModelLoader.load_from_bytes(_external_model("w.bin", None, None, dims=(8,)), base_dir=str(tmp_path))
+    torch.testing.assert_close(m.initializers["w"], torch.arange(8, dtype=torch.float32))

@@ -34,8 +34,83 @@ def test_completions_health_metrics_cancel_stream():
         assert toks == ref and lines[-1] == "data: [DONE]"
         assert "ronn_generated_tokens" in c.get("/v1/metrics").text
         assert c.delete("/v1/requests/9999").status_code == 404
-        assert c.delete(f"/v1/requests/{body['id']}").json()["cancelled"] is True
+        # an answered request leaves nothing behind: no event, no token stream, no engine or scheduler record
+        assert c.delete(f"/v1/requests/{body['id']}").status_code == 404
+        h = c.get("/v1/health").json()
+        assert h["tracked_requests"] == 0 and h["admission"]["in_flight"] == 0 and h["admission"]["answered"] >= 2
+        assert eng.requests == {} and app.state.loop._streams == {}
     app.state.loop.stop()
+
+
+def _engine(**kw):
+    model = Model.from_graph(build_gpt2(GPT2Config.tiny(), dtype=torch.float32, seed=1))
+    cfg = dict(max_num_seqs=4, max_batch_tokens=64, max_model_len=128, num_blocks=32, dtype="fp32", backend="torch")
+    cfg.update(kw)
+    return LLMEngine(model, EngineConfig(**cfg), device="cpu")
+
+
+def test_admission_refuses_beyond_the_limits_and_deadline_cancels():
+    from ronn_b200.core.session_manager import RequestAdmission
+    adm = RequestAdmission(max_in_flight=2, max_per_client=1, timeout_seconds=60)
+    t1 = adm.acquire("a")
+    assert t1 is not None and adm.acquire("a") is None            # per-client cap
+    t2 = adm.acquire("b")
+    assert t2 is not None and adm.acquire("c") is None            # global cap
+    adm.release(t1)
+    adm.release(t1)                                               # releasing twice is harmless
+    assert adm.acquire("c") is not None and adm.snapshot()["refused"] == 2
+    # through HTTP: a server whose admission is full answers 429; a zero deadline answers 504 and cancels the request
+    eng = _engine()
+    full = RequestAdmission(max_in_flight=0)
+    app = create_app(eng, admission=full)
+    with TestClient(app) as c:
+        assert c.post("/v1/completions", json={"prompt_token_ids": [1, 2], "max_tokens": 3}).status_code == 429
+    app.state.loop.stop()
+    eng2 = _engine()
+    app2 = create_app(eng2, admission=RequestAdmission(timeout_seconds=-1.0))
+    with TestClient(app2) as c:
+        r = c.post("/v1/completions", json={"prompt_token_ids": [1, 2], "max_tokens": 40})
+        assert r.status_code in (200, 504)                        # the engine may finish before the first deadline check
+        import time
+        for _ in range(200):
+            if not eng2.has_unfinished() and app2.state.loop.tracked() == 0:
+                break
+            time.sleep(0.01)
+        assert not eng2.has_unfinished() and app2.state.loop.tracked() == 0 and eng2.requests == {}
+    app2.state.loop.stop()
+
+
+def test_engine_loop_gives_up_after_repeated_failed_steps_and_forgets_released_requests():
+    import time
+    from ronn_b200.serving.request import FinishReason
+    from ronn_b200.serving.server import EngineLoop
+    eng = _engine()
+    loop = EngineLoop(eng, max_failed_steps=3)
+    try:
+        # a client that goes away while its request runs: release() cancels it and every record disappears
+        rid = loop.submit([1, 2, 3], SamplingParams(max_new_tokens=40, stop_sequences=[[7, 7, 7]]))
+        for _ in range(200):
+            if rid in eng.requests:
+                break
+            time.sleep(0.005)
+        loop.release(rid)
+        for _ in range(400):
+            if loop.tracked() == 0 and rid not in eng.requests:
+                break
+            time.sleep(0.005)
+        assert loop.tracked() == 0 and rid not in eng.requests and eng._watch_count == 0
+        assert eng.sched.state(rid) is None                           # the native scheduler has forgotten it too
+        # every step fails: after three in a row the waiting request is failed instead of being retried for ever
+        def boom(*a, **k):
+            raise RuntimeError("injected step failure")
+        eng.runner.forward = boom
+        rid2 = loop.submit([4, 5, 6], SamplingParams(max_new_tokens=4))
+        assert loop.wait(rid2, timeout=10)
+        r = loop.result(rid2)
+        assert r.finish_reason == FinishReason.ERROR and "consecutive iterations failed" in r.error
+        assert not eng.has_unfinished()
+    finally:
+        loop.stop()
 
 
 def test_chat_completions_text_prompts_and_streaming():
