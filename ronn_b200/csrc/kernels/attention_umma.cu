@@ -453,10 +453,9 @@ static int launch_fa(const CUtensorMap& mqk, const CUtensorMap& mvt, const FaArg
                      int is_bf16, uint32_t* status, cudaStream_t stream) {
   using L = FaSmem<D>;
   auto kern = flash_attention_kernel<T, D>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   dim3 grid((max_q_len + FA_BM - 1) / FA_BM, a.heads, n_seq);
   const uint32_t fmt = is_bf16 ? 1u : 0u;

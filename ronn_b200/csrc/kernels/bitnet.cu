@@ -303,10 +303,9 @@ static int launch_bitlinear(const CUtensorMap& mx, const void* w, const float* x
                             long slot_stride = 0) {
   using L = BitSmem<BN>;
   auto kern = bitlinear_kernel<BN, T>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + 127) / 128);
   const uint32_t idesc = umma_idesc(128, BN, 1u, 2u);       // signed 8-bit operands, int32 accumulate

@@ -477,25 +477,16 @@ peer_reduce_kernel(const __grid_constant__ CommArgs comm, int M, int N, uint32_t
   cross_rank_phase<T, W, false>(comm, M, N, status, s_flag);
 }
 
-static int comm_sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+static int comm_sm_count() { return device_sm_count(); }
 
 template <int BN, int STAGES, class T, int W, bool PUSH>
 static int launch_reduce_w(const CUtensorMap& ma, const CUtensorMap& mb, const CommArgs& comm, int M, int N, int K,
                            int is_bf16, uint32_t* status, cudaStream_t stream) {
   using L = PGemmSmem<BN, STAGES, true>;
   auto kern = gemm_reduce_kernel<BN, STAGES, T, W, PUSH>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM);
   // every CTA must be resident at once (phase 2 waits on work of the whole grid): never exceed one wave
@@ -875,10 +866,9 @@ static int launch_ag(const GatherArgs& g, const CUtensorMap& mb, DenseEpilogue e
                      uint32_t* status, cudaStream_t stream) {
   using L = PGemmSmem<BN, STAGES, true>;
   auto kern = ag_gemm_kernel<BN, STAGES, T>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM);
   int per_sm = 0;

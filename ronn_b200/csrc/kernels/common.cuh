@@ -24,6 +24,26 @@ bool pdl_enabled();          // defined in elementwise.cu; RONN_PDL=0 disables
 // Done once per kernel function.
 void prefer_max_shared(const void* kern);      // defined in elementwise.cu
 
+// Launch attributes set with cudaFuncSetAttribute and the SM count belong to a DEVICE, not to the process: launchers
+// keep one flag per device ordinal, so a process that drives several GPUs configures its kernels on each of them.
+constexpr int MAX_DEVICES = 64;
+inline bool first_use_on_device(bool (&seen)[MAX_DEVICES]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return true;
+  if (seen[dev]) return false;
+  seen[dev] = true;
+  return true;
+}
+inline int device_sm_count() {
+  static int n[MAX_DEVICES] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) dev = 0;
+  if (n[dev] == 0 &&
+      (cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n[dev] <= 0))
+    n[dev] = 148;
+  return n[dev];
+}
+
 template <class... KArgs, class... Args>
 inline cudaError_t launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                           Args... args) {

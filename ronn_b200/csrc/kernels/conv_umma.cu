@@ -300,15 +300,11 @@ static int launch_conv_impl(const void* x, const CUtensorMap& mw, const ConvShap
                             uint32_t* status, cudaStream_t stream) {
   using L = ConvSmem<BN>;
   auto kern = conv_igemm_kernel<BN, T, FAST>;
-  static bool configured = false;
-  static int sms = 0;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    configured = true;
   }
+  const int sms = device_sm_count();
   // two CTAs per SM when shared memory (227 KB) and TMEM (512 columns) allow it
   const int per_sm = (L::DYN_SMEM <= 110 * 1024 && L::TMEM_COLS <= 256) ? 2 : 1;
   const int resident = sms * per_sm;

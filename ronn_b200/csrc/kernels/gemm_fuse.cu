@@ -521,32 +521,14 @@ gemm_fuse_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   fuse_phase2<T, MODE>(args, prob.m_tiles, prob.n_tiles, status, s_red);
 }
 
-static bool first_use_on_device(bool (&seen)[64]) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return true;
-  if (seen[dev]) return false;
-  seen[dev] = true;
-  return true;
-}
-
-static int fuse_sm_count() {
-  static int n[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (n[dev] == 0 &&
-      (cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n[dev] <= 0))
-    n[dev] = 148;
-  return n[dev];
-}
+static int fuse_sm_count() { return device_sm_count(); }
 
 // Grid of a (BN, STAGES) variant: every CTA must be resident at once because phase 2 waits on the whole grid.
 template <int BN, int STAGES, class T, int MODE>
 static int fuse_grid(int tiles, int* grid_out) {
   using L = PGemmSmem<BN, STAGES>;
   auto kern = gemm_fuse_kernel<BN, STAGES, T, MODE>;
-  static bool configured[64] = {false};
+  static bool configured[MAX_DEVICES] = {false};
   if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
   }

@@ -31,7 +31,10 @@
 namespace ronn {
 
 constexpr int LL_MAX_RANKS = RONN_LL_MAX_RANKS;
-constexpr uint32_t LL_UNIT = 1u << 16;         // the CTAs of a call add up to exactly one unit on the epoch word
+// The epoch word is 64 bits wide and the CTAs of a call add up to exactly one unit on it, so the call count (and with
+// it the sequence number carried by the words on the wire) only repeats after 2^32 calls: a word left in an area by
+// an old call of another shape can never be mistaken for current data.
+constexpr unsigned long long LL_UNIT = 1ull << 16;
 
 struct LLArgs {
   uint8_t* scatter_peer[LL_MAX_RANKS];   // phase-A receive area of every rank: [2 parities][W sources][owner_rows * N] values, 4 bytes each
@@ -40,7 +43,7 @@ struct LLArgs {
   uint8_t* result_mc;                    // its multicast address (NVLS) or null
   uint8_t* result_local;
   long scatter_parity_stride, result_parity_stride;   // bytes
-  uint32_t* state;                       // [0] epoch word
+  unsigned long long* state;             // [0] epoch word
   void* out;                             // X [M, ld_out], local
   void* norm_out;                        // H, or null
   const void* bias;
@@ -81,8 +84,8 @@ struct LLProblem {
   // phase A: 32 rows x 32 columns of fp32 accumulators -> 16-bit pairs -> {data, sequence} words in the owners' areas
   __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     if (seq == 0u) {
-      const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a->state) / LL_UNIT;
-      seq = epoch + 1u;
+      const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(a->state) / LL_UNIT;
+      seq = uint32_t(epoch) + 1u;
       if (seq == 0u) seq = 1u;
       parity_off = size_t(epoch & 1u) * a->scatter_parity_stride;
     }
@@ -136,8 +139,8 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
   pdl_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = int(gridDim.x);
-  const uint32_t epoch = (*reinterpret_cast<volatile uint32_t*>(a.state) & ~(LL_UNIT - 1u)) / LL_UNIT;
-  uint32_t seq = epoch + 1u;
+  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(a.state) / LL_UNIT;
+  uint32_t seq = uint32_t(epoch) + 1u;
   if (seq == 0u) seq = 1u;
   const size_t pa = size_t(epoch & 1u) * a.scatter_parity_stride;
   const size_t pb = size_t(epoch & 1u) * a.result_parity_stride;
@@ -302,7 +305,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
   // next call reads it after its dependency wait, when this grid has completed)
   __syncthreads();
   if (tid == 0) {
-    red_add_gpu_u32(a.state, blockIdx.x == 0 ? LL_UNIT - uint32_t(G - 1) : 1u);
+    red_add_gpu_u64(a.state, blockIdx.x == 0 ? LL_UNIT - (unsigned long long)(G - 1) : 1ull);
     if (tr) tr[7] = globaltimer_ns();
   }
 }
@@ -327,28 +330,16 @@ gemm_ll_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   ll_phases<T, NVLS>(args, status, s_red);
 }
 
-static int ll_sm_count() {
-  static int n[64] = {0};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) dev = 0;
-  if (n[dev] == 0 &&
-      (cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n[dev] <= 0))
-    n[dev] = 148;
-  return n[dev];
-}
+static int ll_sm_count() { return device_sm_count(); }
 
 template <int BN, int STAGES, class T, bool NVLS>
 static int ll_launch(const CUtensorMap& ma, const CUtensorMap& mb, LLArgs& a, int K, int is_bf16, uint32_t* status,
                      cudaStream_t stream) {
   using L = PGemmSmem<BN, STAGES, true>;
   auto kern = gemm_ll_kernel<BN, STAGES, T, NVLS>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured[dev] = true;
   }
   // every CTA must be resident at once: phases B and C wait on work of the whole grid and of the peers
   int per_sm = 0;
@@ -398,7 +389,7 @@ extern "C" int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStr
   a.result_mc = static_cast<uint8_t*>(p->result_mc);
   a.scatter_parity_stride = p->scatter_parity_stride;
   a.result_parity_stride = p->result_parity_stride;
-  a.state = static_cast<uint32_t*>(p->state);
+  a.state = static_cast<unsigned long long*>(p->state);
   a.out = p->out;
   a.norm_out = p->norm_out;
   a.bias = p->bias;

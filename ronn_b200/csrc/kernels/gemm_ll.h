@@ -24,7 +24,7 @@ typedef struct RonnGemmLLParams {
   void* result_area[RONN_LL_MAX_RANKS];
   void* result_mc;
   long result_parity_stride;     // bytes per parity: >= M * N * 4
-  void* state;                   // 8 zero-initialised uint32 in local memory
+  void* state;                   // 32 zero-initialised bytes in local memory, 8-byte aligned
   int rank, world, nvls;
   void* out;                     // X [M, ld_out], local memory
   void* norm_out;                // H (norm_mode != 0), same row stride

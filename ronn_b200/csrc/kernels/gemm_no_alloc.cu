@@ -66,6 +66,8 @@ extern "C" const char* ronn_no_alloc_strerror(int code) {
              "use fewer slices or the allocating entry point";
     case RONN_NO_ALLOC_E_SYMBOL: return "the scratch array could not be resolved on the current device";
     case RONN_NO_ALLOC_E_ARGS: return "null operand or non-positive size";
+    case RONN_NO_ALLOC_E_SHAPE:
+      return "N must be a multiple of 8 and at most 32768, K / lda / ldw multiples of 8, dtype 0 (bf16) or 1 (fp16)";
     default: return "error reported by the GEMM launcher";
   }
 }
@@ -74,6 +76,10 @@ extern "C" int ronn_gemm_splitk_no_alloc(const void* A, const void* W, void* out
                                          const void* residual, int M, int N, int K, int lda, int ldw, int dtype,
                                          int splitk, uint32_t* status, cudaStream_t stream) {
   if (A == nullptr || W == nullptr || out == nullptr || M <= 0 || N <= 0 || K <= 0) return RONN_NO_ALLOC_E_ARGS;
+  // everything either kernel would refuse is refused here, before the first launch: a call either runs both passes
+  // or touches nothing (neither the scratch nor `out`)
+  if ((N & 7) || N > RONN_NO_ALLOC_MAX_N || (K & 7) || (lda & 7) || (ldw & 7) || (dtype != 0 && dtype != 1))
+    return RONN_NO_ALLOC_E_SHAPE;
   if (ronn_no_alloc_scratch_floats(M, N, K, splitk) > long(RONN_NO_ALLOC_MAX_FLOATS)) return RONN_NO_ALLOC_E_TOO_LARGE;
   float* scratch = nullptr;
   int rc = scratch_for_current_device(&scratch);

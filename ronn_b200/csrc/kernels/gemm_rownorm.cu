@@ -243,10 +243,9 @@ template <class T>
 static int launch_rownorm(const CUtensorMap& ma, const CUtensorMap& mb, const RowNormArgs& a, int is_bf16, uint32_t* status,
                           cudaStream_t stream) {
   auto kern = gemm_rownorm_kernel<T>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, RnSmem::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   const int n_tiles = a.N / RN_BN;
   cudaLaunchConfig_t cfg = {};

@@ -67,25 +67,16 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   gemm_persistent<BN, STAGES, 0, DenseProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
 }
 
-static int sm_count() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+static int sm_count() { return device_sm_count(); }
 
 template <int BN, int STAGES, class T>
 static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilogue epi, int M, int N, int K,
                         int is_bf16, uint32_t* status, cudaStream_t stream, int splitk = 1) {
   using L = PGemmSmem<BN, STAGES>;
   auto kern = gemm_dense_kernel<BN, STAGES, T>;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
-    configured = true;
   }
   const int tiles = ((N + BN - 1) / BN) * ((M + PG_BM - 1) / PG_BM) * splitk;
   const int resident = sm_count() * (L::DYN_SMEM <= 112 * 1024 && L::TMEM_COLS <= 256 ? 2 : 1);

@@ -16,17 +16,24 @@ extern "C" {
 #define RONN_NO_ALLOC_E_TOO_LARGE (-40)   // slices * M * N exceeds RONN_NO_ALLOC_MAX_FLOATS
 #define RONN_NO_ALLOC_E_SYMBOL (-41)      // the scratch symbol could not be resolved on the current device
 #define RONN_NO_ALLOC_E_ARGS (-42)        // null pointer or non-positive size
+#define RONN_NO_ALLOC_E_SHAPE (-43)       // N not a multiple of 8 or above RONN_NO_ALLOC_MAX_N; K, lda or ldw not a multiple of 8
+
+// Widest output row the reduction pass takes (it keeps a row in registers across 1024 threads).
+#define RONN_NO_ALLOC_MAX_N 32768
 
 // out[M, N] = A[M, K] * W[N, K]^T + bias + residual, computed as `splitk` K-slices on the tensor cores whose fp32
 // partial panels live in a fixed scratch array inside the library, followed by one reduction pass.
 //   A, W, out, bias (or null), residual (or null): device pointers, 16-bit elements (dtype 0 = bf16, 1 = fp16);
-//   lda / ldw in elements; out and residual are dense [M, N]; K, lda, ldw multiples of 8; N a multiple of 8.
+//   lda / ldw in elements; out and residual are dense [M, N]; K, lda, ldw multiples of 8; N a multiple of 8 and at
+//   most RONN_NO_ALLOC_MAX_N.  A call that breaks one of these rules returns RONN_NO_ALLOC_E_SHAPE before anything
+//   is launched: neither the scratch nor `out` is written.
 //   status: device word that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
-// Returns 0, or a negative code; ronn_no_alloc_strerror() turns the three codes above into text.
+// Returns 0, or a negative code; ronn_no_alloc_strerror() turns the codes above into text.
 //
 // What a caller has to know:
 //  * The first call on each device resolves the address of the scratch array (cudaGetSymbolAddress) and sets the
-//    kernels' launch attributes.  Make that first call during start-up, before any stream capture begins.
+//    kernels' launch attributes on that device (both are kept per device ordinal, so a process that drives several
+//    GPUs makes one such call on each).  Make that first call during start-up, before any stream capture begins.
 //  * There is ONE scratch array per device, shared by every call.  Two calls whose execution may overlap (different
 //    streams without an ordering between them, or different host threads) race on it; order them on one stream or
 //    with events.

@@ -282,8 +282,8 @@ __global__ void __launch_bounds__(RS_WARPS * 32, 4) rowwise_stream_kernel(const 
 template <class T, int MODE, bool HAS_RES>
 static int launch_stream(const RowArgs& a, size_t smem, int grid, cudaStream_t stream) {
   auto kern = rowwise_stream_kernel<T, MODE, HAS_RES>;
-  static bool configured = false;                 // per instantiation
-  if (!configured) {
+  static bool configured[MAX_DEVICES] = {false};                 // per instantiation
+  if (first_use_on_device(configured)) {
     // The ring of every resident CTA has to fit: ask for the largest shared-memory carve-out, or the driver may
     // size it for a single CTA and leave the SM with eight warps.
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
@@ -292,7 +292,6 @@ static int launch_stream(const RowArgs& a, size_t smem, int grid, cudaStream_t s
       cudaGetLastError();
       return -101;
     }
-    configured = true;
   }
   return launch(kern, dim3(grid), dim3(RS_WARPS * 32), smem, stream, a) == cudaSuccess ? 1 : -100;
 }

@@ -81,3 +81,19 @@ def test_rejects_what_does_not_fit_the_scratch(lib):
     assert _call(lib, a2, w, out2, None, None, 0, status) == 0      # splitk < 1 means one slice
     assert lib.ronn_gemm_splitk_no_alloc(None, w.data_ptr(), out2.data_ptr(), None, None, 256, 4096, 4096, 4096, 4096,
                                          0, 4, None, None) == -42
+
+
+def test_rejects_bad_shapes_before_anything_is_launched(lib):
+    """N = 12 passes the GEMM's own check (multiples of 4) but not the reduction pass's (multiples of 8): the entry
+    point refuses it up front, so neither the scratch nor `out` is touched.  The same goes for rows wider than the
+    reduction pass keeps in registers and for unaligned K."""
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for (M, N, K) in [(64, 12, 256), (8, 32776, 64), (64, 64, 68)]:
+        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+        w = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+        out = torch.full((M, N), 7.0, device="cuda", dtype=torch.bfloat16)
+        rc = _call(lib, a, w, out, None, None, 2, status)
+        assert rc == -43, (M, N, K, rc)
+        assert b"multiple of 8" in lib.ronn_no_alloc_strerror(rc)
+        torch.cuda.synchronize()
+        assert bool((out == 7.0).all()) and status.tolist() == [0, 0, 0, 0]
