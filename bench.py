@@ -18,7 +18,19 @@ timed between barrier + synchronize pairs.  Two numbers come from those same K s
   e2e    wall clock of the K ``engine.step()`` calls (host scheduling, pinned-memory H2D of the
          step inputs, graph replay, D2H of the sampled tokens), max over ranks
 
-``--impl reference`` reports that the reference cannot be built here.
+Further keys of the line:
+  e2e_full          wall-clock tokens/s of a WHOLE run of the workload through ``engine.step()``: 256 requests are
+                    admitted, prefilled in chunks, decoded to 256 new tokens each and retired (continuous batching
+                    from the first admission to the last finished request)
+  gpu_launches      launcher calls of the in-tree sm_100a kernel library inside the timed window, counted by the
+                    library's call counter (graph replays add the count recorded at capture)
+  resnet18_p50_ms   (N = 1) ResNet-18 fp16 batch 32, O3, p50 latency through Model.create_session / session.run
+  bitnet_tp8_tokens_s  (N = 8) BitNet b1.58 2B-style decoder, batch 128 decode, tensor parallel over the 8 GPUs
+  vs_baseline       value divided by the library arm's tokens/s at the same N recorded in BASELINE.md (the reference
+                    publishes no number for this metric)
+
+``--impl baseline`` runs the library arm (``baseline/library_decode.py``: cuBLAS + SDPA + NCCL, one CUDA graph per
+step); ``--impl reference`` reports that the reference cannot be built here.
 """
 from __future__ import annotations
 
@@ -117,6 +129,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(self.samples), "source": self.source}
 
 
+# tokens/s of the library arm (`bench.py --impl baseline`) on this pool's B200s, by GPU count; the same numbers and the
+# logs they come from are listed in BASELINE.md section 5.1.  None: not measured at that GPU count.
+LIBRARY_BASELINE_TOKENS_S = {}
+
+
+def library_baseline_tokens_s(world: int):
+    return LIBRARY_BASELINE_TOKENS_S.get(world)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -127,6 +148,7 @@ def main():
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--tp-comm", default=os.environ.get("RONN_TP_COMM", "fused"), choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=24, help=argparse.SUPPRESS)       # smoke runs only
+    ap.add_argument("--no-extras", action="store_true", help="skip the ResNet-18 (N=1) and BitNet (N=8) side benchmarks")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -143,23 +165,64 @@ def main():
         args.gpus = world
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    if args.impl == "baseline":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import library_decode
+        rec = library_decode.run(args, rank, world, local, ClockSampler)
+        if rank == 0:
+            print(json.dumps(rec))
+        sys.stdout.flush()
+        if world > 1:
+            torch.cuda.synchronize()
+            os._exit(0)
+        return 0
     K, W = args.steps, max(args.warmup, 3)
     new_tokens = max(args.new_tokens, K + W + 2)
 
     cfg = GPT2Config(n_layer=args.layers)
     graph = build_gpt2(cfg, dtype=torch.bfloat16, seed=0, with_lm_head=False)
     model = Model.from_graph(graph)
-    backend = "torch" if args.impl == "baseline" else "kernels"
+    backend = "kernels"
     ecfg = EngineConfig(max_num_seqs=args.requests, max_batch_tokens=8192, max_model_len=1024, dtype="bf16",
-                        backend=backend, use_cuda_graph=True, tp_size=world,
-                        tp_comm="nccl" if args.impl == "baseline" else args.tp_comm,
+                        backend=backend, use_cuda_graph=True, tp_size=world, tp_comm=args.tp_comm,
                         num_blocks=args.requests * 50)
     if world > 1:
-        from ronn_b200.parallel.fused import make_comm
+        from ronn_b200.parallel import make_comm
         comm = make_comm(ecfg.tp_comm, dev)
     else:
         comm = None
     eng = LLMEngine(model, ecfg, device=dev, comm=comm)
+    def sync_all():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    # ---- the whole workload once, end to end: admission, chunked prefill, 256 decode steps per request, retirement
+    rng_full = np.random.default_rng(4321)
+    lens_full = rng_full.integers(64, 513, size=args.requests)
+    prompts_full = [rng_full.integers(0, cfg.vocab_size, size=int(n)).tolist() for n in lens_full]
+    # untimed pass over prompts of the same lengths with a few new tokens each: loads kernels, sizes buffers and captures the
+    # decode graph of the full batch, as a server that has been up for a while would have
+    rng_warm = np.random.default_rng(99)         # other token ids: nothing of the timed pass may sit in the prefix cache
+    warm = [eng.add_request(rng_warm.integers(0, cfg.vocab_size, size=int(n)).tolist(), SamplingParams(max_new_tokens=4))
+            for n in lens_full]
+    while eng.has_unfinished():
+        eng.step()
+    for i in warm:
+        eng.release(i)
+    sync_all()
+    t_full = time.perf_counter()
+    full_ids = [eng.add_request(p, SamplingParams(max_new_tokens=args.new_tokens)) for p in prompts_full]
+    full_steps = 0
+    while eng.has_unfinished():
+        eng.step()
+        full_steps += 1
+    sync_all()
+    full_wall = time.perf_counter() - t_full
+    full_tokens = sum(len(eng.requests[i].output_tokens) for i in full_ids)
+    for i in full_ids:
+        eng.release(i)
+
     rng = np.random.default_rng(1234)
     lens = rng.integers(64, 513, size=args.requests)
     for n in lens:
@@ -178,18 +241,13 @@ def main():
         eng.step()
     assert eng.sched.num_running == args.requests, "all requests must be decoding in the timed window"
 
-    def sync_all():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
     sampler = ClockSampler(local)
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(K)]
     sync_all()
     sampler.start()
     t0 = time.perf_counter()
-    h2d = d2h = 0
+    h2d = d2h = launches = 0
     host_dev = host_book = 0.0
     for i in range(K):
         starts[i].record()
@@ -197,6 +255,7 @@ def main():
         ends[i].record()
         h2d += eng.h2d_bytes_last
         d2h += eng.d2h_bytes_last
+        launches += eng.kernel_launches_last
         host_dev += eng.host_seconds_last[0]
         host_book += eng.host_seconds_last[1]
         assert len(out) == args.requests
@@ -208,27 +267,41 @@ def main():
         c = TPComm()
         dev_ms = c.max_over_ranks(dev_ms)
         wall = c.max_over_ranks(wall)
-    # hand-written kernels launched per decode step (library collectives and torch copies are not counted); a step
-    # that runs as concurrent part-batches launches the per-layer kernels once per part
     parts = len(eng._split_rows(eng._bucket(args.requests)) or [None])
-    if world == 1:
-        per_part = 2 + 7 * cfg.n_layer + 2    # embed, first norm | qkv, attn+append, out, norm, up, down(split-K), finalize+norm | LM head, argmax
-        launches_per_step = parts * per_part
-    elif ecfg.tp_comm == "fused":
-        per_part = 2 + 5 * cfg.n_layer + 2    # qkv, attn+append, out+all-reduce+norm, up, down+all-reduce+norm | LM head, argmax
-        launches_per_step = parts * per_part + 1                                  # + combine over ranks
-    else:
-        launches_per_step = 1 + 7 * cfg.n_layer + 4       # embed | norm, qkv, attn+append, out, norm, up, down | final norm, LM head, argmax, combine
+    if world > 1:
+        c = TPComm()
+        full_wall = c.max_over_ranks(full_wall)
     tokens = args.requests * K
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / wall
     mean_ctx = float(np.mean(lens)) + advance + W + K / 2
+    extra = {}
+    if world == 1 and not args.no_extras:
+        from ronn_b200.bench_models import resnet18_latency
+        try:
+            r18 = resnet18_latency()
+            extra["resnet18_p50_ms"] = r18["p50_ms"]
+            extra["resnet18"] = r18
+        except Exception as e:                       # the headline line must survive a failure of the side benchmark
+            extra["resnet18_error"] = str(e)[:200]
+    if world == 8 and not args.no_extras:
+        from ronn_b200.bench_models import bench_bitnet
+        del eng
+        torch.cuda.empty_cache()
+        try:
+            bn = bench_bitnet(comm=comm, standalone=False)
+            extra["bitnet_tp8_tokens_s"] = bn["decode_tokens_per_s"]
+            extra["bitnet_tp8"] = bn
+        except Exception as e:
+            extra["bitnet_tp8_error"] = str(e)[:200]
+    lib_base = library_baseline_tokens_s(world)
     if rank == 0:
         print(json.dumps({
             "metric": "GPT-2 decode tokens/s (continuous batching, paged KV)", "value": round(value, 1),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 4),
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "ours" if args.impl == "ours" else "library-baseline",
+            "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / lib_base, 3) if lib_base else None, "dtype": "bf16", "data": "synthetic",
+            "impl": "ours",
             "config": {"model": "gpt2-medium" if cfg.n_layer == 24 else f"gpt2-medium-{cfg.n_layer}L",
                        "global_batch": args.requests, "seq_len": "prompts U(64,512) + 256 new tokens",
                        "kv_block": 16, "parallelism": f"tp{world}", "tp_comm": ecfg.tp_comm if world > 1 else "none",
@@ -243,7 +316,14 @@ def main():
             "clocks": clocks,
             "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d // K,
                     "d2h_bytes_per_step": d2h // K, "ms_per_step": round(wall * 1e3 / K, 4)},
-            "gpu_launches": launches_per_step * K if backend == "kernels" else 0,
+            "e2e_full": {"value": round(full_tokens / full_wall, 1), "unit": "tokens/s", "requests": args.requests,
+                         "generated_tokens": int(full_tokens), "engine_steps": full_steps,
+                         "wall_seconds": round(full_wall, 4),
+                         "what": "admission + chunked prefill + decode + retirement of the whole workload, wall clock"},
+            "gpu_launches": int(launches),
+            "baseline_on_this_box": {"tokens_per_s": lib_base, "impl": "bench.py --impl baseline (cuBLAS + SDPA + NCCL, CUDA graph)",
+                                     "source": "BASELINE.md section 5.1"},
+            **extra,
         }))
     sys.stdout.flush()
     if world > 1:

@@ -131,6 +131,47 @@ def host():
         return lib
 
 
+_NOT_LAUNCHERS = {"ronn_set_pdl", "ronn_set_rowwise_status", "ronn_no_alloc_scratch_floats", "ronn_no_alloc_strerror",
+                  "ronn_gemm_fuse_state_ints", "ronn_gemm_fuse_flag_ints", "ronn_flash_attention_set_probe"}
+
+
+class _Counted:
+    """A launcher of the kernel library that bumps its library's launch counter on every call; attribute access
+    (``restype``, ``argtypes``) goes to the ctypes function itself."""
+    __slots__ = ("_fn", "_owner")
+
+    def __init__(self, fn, owner):
+        object.__setattr__(self, "_fn", fn)
+        object.__setattr__(self, "_owner", owner)
+
+    def __call__(self, *args):
+        self._owner.launches += 1
+        return self._fn(*args)
+
+    def __getattr__(self, k):
+        return getattr(self._fn, k)
+
+    def __setattr__(self, k, v):
+        setattr(self._fn, k, v)
+
+
+class _KernelLib:
+    """The loaded kernel library plus ``launches``: how many of its kernel launchers have been called in this process
+    (a launcher enqueues one kernel, a few enqueue two).  Replays of a captured CUDA graph call no launcher; whoever
+    replays a graph adds the count it recorded during capture (see ``LLMEngine.kernel_launches``)."""
+
+    def __init__(self, lib):
+        self.__dict__["_lib"] = lib
+        self.__dict__["launches"] = 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._lib, name)
+        if name.startswith("ronn_") and name not in _NOT_LAUNCHERS:
+            fn = _Counted(fn, self)
+        self.__dict__[name] = fn
+        return fn
+
+
 def cuda_available() -> bool:
     import torch
     return torch.cuda.is_available()
@@ -147,8 +188,8 @@ def cuda():
         path = _build.CUDA_LIB
         if not path.exists() or _build.find_nvcc() is not None:
             path = _build.build_cuda()
-        lib = C.CDLL(str(path))
+        raw = C.CDLL(str(path))
         from .ops import _signatures
-        _signatures.declare(lib)
-        _cuda = lib
-        return lib
+        _signatures.declare(raw)
+        _cuda = _KernelLib(raw)
+        return _cuda

@@ -164,7 +164,7 @@ def bench_distilbert(batch=64, seq=128, iters=20):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     comm = None
     if world > 1:
-        from .parallel.fused import make_comm
+        from .parallel import make_comm
         from .parallel.group import init_distributed
         rank, world, local = init_distributed()
         torch.cuda.set_device(local)
@@ -212,7 +212,7 @@ def bench_distilbert(batch=64, seq=128, iters=20):
     return out
 
 
-def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24):
+def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24, comm=None, standalone=True):
     """BitNet b1.58 2B-style decoder (24 layers, hidden 2560, 20 heads, FFN 6912, vocab 32000; random ternary weights
     packed 2-bit, int8 activations), decode tokens/s at a fixed batch through the serving engine (paged KV,
     CUDA-graph decode).  Under ``torchrun`` the model is tensor parallel over all ranks; the time is the maximum over
@@ -224,13 +224,14 @@ def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24):
     from .models.bitnet_llama import BitNetConfig, build_bitnet_llama
     from .serving import EngineConfig, LLMEngine, SamplingParams
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    comm, rank, local = None, 0, 0
+    rank, local = 0, 0
     if world > 1:
-        from .parallel.fused import make_comm
+        from .parallel import make_comm
         from .parallel.group import init_distributed
         rank, world, local = init_distributed()
         torch.cuda.set_device(local)
-        comm = make_comm(os.environ.get("RONN_TP_COMM", "fused"), torch.device("cuda", local))
+        if comm is None:                     # a caller that already owns a communicator passes it in
+            comm = make_comm(os.environ.get("RONN_TP_COMM", "fused"), torch.device("cuda", local))
     dev = torch.device("cuda", local)
     cfg = BitNetConfig(n_layer=layers)
     model = Model.from_graph(build_bitnet_llama(cfg, dtype=torch.bfloat16, seed=0, with_lm_head=False))
@@ -263,13 +264,39 @@ def bench_bitnet(batch=128, steps=32, warmup=3, prompt=64, layers=24):
            "config": {"model": "bitnet-b1.58-2b-style" if layers == 24 else f"bitnet-{layers}L", "batch": batch,
                       "prompt": prompt, "steps": steps, "dtype": "ternary 2-bit x int8 (bf16 elsewhere)", "tp": world,
                       "l2": "KV + packed weights per step exceed L2"}}
-    if world > 1:
+    if world > 1 and standalone:
         if rank == 0:
             print(json.dumps(res))
         sys.stdout.flush()
         torch.cuda.synchronize()
         os._exit(0)
     return res
+
+
+def resnet18_latency(batch=32, iters=30, image=224):
+    """ResNet-18, fp16, NCHW input [batch, 3, image, image], O3 (Conv + BN + ReLU fused, NHWC inside), GPU provider with
+    CUDA-graph replay, through Model -> create_session -> run.  Returns the p50 latency with the input already on the
+    device and the p50 of the whole call a user makes: input copied from pinned host memory, run, logits copied back."""
+    from . import Model, SessionOptions
+    from .models.resnet18 import build_resnet18
+    model = Model.from_graph(build_resnet18(dtype=torch.float16, seed=0))
+    sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3")
+                                .with_dtype("fp16").with_cuda_graph(True))
+    x_host = torch.randn(batch, 3, image, image, dtype=torch.float16).pin_memory()
+    x = x_host.cuda()
+    p50, best = _p50_cuda(lambda: sess.run({"input": x}), iters)
+    logits_host = torch.empty((batch, 1000), dtype=torch.float16).pin_memory()
+
+    def end_to_end():
+        xd = x_host.to("cuda", non_blocking=True)
+        logits_host.copy_(sess.run({"input": xd})["logits"], non_blocking=True)
+
+    e2e, _ = _p50_cuda(end_to_end, iters)
+    from .ops import kernels as K
+    K.check_status()
+    return {"p50_ms": round(p50, 4), "min_ms": round(best, 4), "e2e_p50_ms": round(e2e, 4),
+            "images_per_s": round(batch / p50 * 1e3, 1), "h2d_bytes": x_host.numel() * 2, "d2h_bytes": logits_host.numel() * 2,
+            "config": "fp16 NCHW [%d,3,%d,%d], O3, CUDA graph, L2 flushed between runs" % (batch, image, image)}
 
 
 def bench_serving(concurrency=(1, 4, 16, 32), prompt=128, new_tokens=64, model="gpt2-medium", device=None):

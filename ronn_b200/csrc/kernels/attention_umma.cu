@@ -59,7 +59,6 @@ struct FaArgs {
   int heads, kv_heads;
   int causal;
   float scale_log2;        // softmax scale * log2(e)
-  long long* probe;        // diagnostics: SM cycle counter at the phase boundaries of one CTA (null = off)
 };
 
 // 2^x on the special-function unit in one instruction (no range fix-up; inputs here are <= 0 or the result is masked)
@@ -69,11 +68,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Phase probe: the CTA of the last query tile of (head 0, sequence 0) records clock64() at the phase boundaries of its
-// first 8 key tiles: slots [0, 64) belong to the first softmax warp (8 per tile), [64, 128) to the MMA thread.
-__device__ __forceinline__ void fa_probe(long long* probe, bool mine, int role, int j, int point) {
-  if (probe && mine && j < 8) probe[role * 64 + j * 8 + point] = clock64();
-}
 
 template <class T, int D>
 __global__ void __launch_bounds__(FA_THREADS, D == 64 ? 2 : 1)
@@ -105,7 +99,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
   const int q_len = a.q_len[seq], kv_len = a.kv_len[seq];
   if (qt * FA_BM >= q_len || kv_len <= 0) return;            // uniform for the CTA, before any barrier or TMEM use
   const int row0 = a.seq_start[seq];
-  const bool probe_cta = a.probe != nullptr && seq == 0 && head == 0 && qt == int(gridDim.x) - 1;
   const int kvh = head / (a.heads / a.kv_heads);
   const int shift = kv_len - q_len;                          // causal: query i sees keys j <= i + shift
   int n_kv = (kv_len + FA_BN - 1) / FA_BN;
@@ -174,9 +167,7 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
       // S(j) = Q K(j)^T into the single S accumulator; frees K's buffer for K(j+2)
       auto issue_s = [&](int j) -> bool {
         const int ks = j % L::K_STAGES;
-        fa_probe(a.probe, probe_cta, 1, j, 0);
         if (!mbar_wait(&k_full[ks], (j / L::K_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) return false;
-        fa_probe(a.probe, probe_cta, 1, j, 1);
         tc_fence_after_sync();
         const uint32_t ak = smem_u32(sk + ks * L::K_BYTES);
 #pragma unroll
@@ -186,7 +177,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
         }
         umma_commit(s_full);
         umma_commit(&k_empty[ks]);
-        fa_probe(a.probe, probe_cta, 1, j, 2);
         return true;
       };
       if (ok && n_kv > 0) ok = issue_s(0);
@@ -194,14 +184,12 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
         const int vs = j % L::V_STAGES;
         // P(j) is in shared memory and the softmax warps have finished reading S(j) and PV(j-1)
         if (!mbar_wait(p_full, j & 1, abort, status, STATUS_WAIT_EPI)) break;
-        fa_probe(a.probe, probe_cta, 1, j, 3);
         // S(j+1) goes first: the softmax of tile j+1 is the critical path (issuing an MMA costs 70-100 cycles, and
         // behind the eight instructions of PV(j) the next S was ready about 1000 cycles later); PV(j) then runs
         // during pass 1 of tile j+1, whose O update waits for it.  P has one buffer: it is rewritten in pass 2 of
         // tile j+1, after that wait.
         if (j + 1 < n_kv && !issue_s(j + 1)) break;
         if (!mbar_wait(&v_full[vs], (j / L::V_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
-        fa_probe(a.probe, probe_cta, 1, j, 4);
         tc_fence_after_sync();
         const uint32_t ap = smem_u32(sp);
         const uint32_t av = smem_u32(sv + vs * L::V_BYTES);
@@ -213,7 +201,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
         }
         umma_commit(pv_full);
         umma_commit(&v_empty[vs]);
-        fa_probe(a.probe, probe_cta, 1, j, 5);
       }
     }
     __syncwarp();
@@ -246,13 +233,10 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
       ++xphase;
       return good;
     };
-    const bool probe_me = probe_cta && warp == 2 && lane == 0;
     for (int j = 0; j < n_kv; ++j) {
-      fa_probe(a.probe, probe_me, 0, j, 0);
       ok = mbar_wait(s_full, j & 1, abort, status, STATUS_WAIT_ACCUM);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      fa_probe(a.probe, probe_me, 0, j, 1);
       tc_fence_after_sync();
       const int key0 = j * FA_BN;
       // Tiles whose 64 keys are visible to every row of the warp (all but the diagonal and the last tile) take a path
@@ -288,7 +272,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
       max16(va, 32);
       tmem_ld_wait();
       max16(vb, 48);
-      fa_probe(a.probe, probe_me, 0, j, 2);
       // the PV tile of the previous key tile joins O before O is rescaled to the new maximum; its load is in flight
       // while the two halves of the row exchange their maxima
       const uint32_t o_addr = tmem_pv + lane_addr + uint32_t(half * DH);
@@ -304,7 +287,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
       if (!ok) break;
       mx = fmaxf(mx, mx_other);
       const float alpha = fast_exp2(m - mx);
-      fa_probe(a.probe, probe_me, 0, j, 3);
       if (j > 0) {
         // O += PV in 16-column pieces, again with the next piece in flight
 #pragma unroll
@@ -319,7 +301,6 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
           for (int i = 0; i < 16; ++i) o[c + 16 + i] += __uint_as_float(vb[i]);
         }
       }
-      fa_probe(a.probe, probe_me, 0, j, 4);
       tmem_ld_32x16(s_addr, va);                             // first piece of pass 2, in flight during the rescale
 #pragma unroll
       for (int i = 0; i < DH; ++i) o[i] *= alpha;
@@ -360,11 +341,9 @@ flash_attention_kernel(const __grid_constant__ CUtensorMap map_qk, const __grid_
       prob16(va, 32);
       tmem_ld_wait();
       prob16(vb, 48);
-      fa_probe(a.probe, probe_me, 0, j, 5);
       tc_fence_before_sync();                                // TMEM reads of S and PV are done
       fence_proxy_async_smem();                              // P is visible to the tensor core
       mbar_arrive(p_full);
-      fa_probe(a.probe, probe_me, 0, j, 6);
     }
     if (ok && n_kv > 0) {
       ok = mbar_wait(pv_full, (n_kv - 1) & 1, abort, status, STATUS_WAIT_ACCUM);
@@ -468,11 +447,7 @@ static int launch_fa(const CUtensorMap& mqk, const CUtensorMap& mvt, const FaArg
 
 using namespace ronn;
 
-static long long* g_fa_probe = nullptr;
 
-// Diagnostics: a device buffer of 128 int64 that the next attention launches fill with the SM cycle counter at the phase
-// boundaries of one CTA (see fa_probe); null switches the probe off.
-extern "C" void ronn_flash_attention_set_probe(long long* buf) { g_fa_probe = buf; }
 
 // qkv: [tokens, ld] with V of kv head h at columns v_off + h * head_dim.  vt: [kv_heads * head_dim, ld_vt].
 // seq_start / kv_len / vt_start: device int32 [n_seq]; vt_start values are multiples of 128 and
@@ -509,7 +484,7 @@ extern "C" int ronn_flash_attention(const void* qkv, long ld, long total_rows, i
   rc = make_tmap_2d(&mvt, vt, uint64_t(kv_heads) * head_dim, uint64_t(ld_vt), uint64_t(ld_vt), uint32_t(head_dim), 64, 2);
   if (rc) return rc - 30;
   FaArgs a{seq_start, q_len, kv_len, vt_start, out, ld_o, q_off, k_off, heads, kv_heads, causal,
-           scale * 1.4426950408889634f, g_fa_probe};
+           scale * 1.4426950408889634f};
   if (dtype == 0) {
     return head_dim == 64 ? launch_fa<__nv_bfloat16, 64>(mqk, mvt, a, n_seq, max_q_len, 1, status, stream)
                           : launch_fa<__nv_bfloat16, 128>(mqk, mvt, a, n_seq, max_q_len, 1, status, stream);

@@ -24,8 +24,8 @@ enum : uint32_t {
   STATUS_WAIT_EPI = 5,       // MMA issuer never saw the epilogue drain TMEM
 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s per wait (flag waits on %globaltimer)
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;        // about 2 s of SM cycles per mbarrier wait
+constexpr unsigned long long WAIT_LIMIT_NS = 500000000ull;    // 0.5 s per wait (flag waits on %globaltimer)
+constexpr long long WAIT_LIMIT_CYCLES = 1000000000ll;        // about 0.5 s of SM cycles per mbarrier wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

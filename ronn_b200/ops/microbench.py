@@ -78,126 +78,6 @@ def time_graph(make_call, variants: int, reps: int = 40, iters: int = 5):
     return ts[len(ts) // 2]
 
 
-def sweep_decode_gemm(m=256):
-    """Back-to-back (graph) timing of the decode GEMM shapes over tile width and split-K, weights rotating through
-    more than L2 so every launch streams its weights from HBM."""
-    hbm, tf, src = _peaks()
-    out = []
-    for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]:
-        nvar = max(2, int(300e6 // (n * k * 2)))
-        ws = [(torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(nvar)]
-        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        bias = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
-        roof = max(2.0 * m * n * k / (tf * 1e12), 2.0 * (m * k + n * k + m * n) / (hbm * 1e9)) * 1e6
-        for bn in (32, 64, 128):
-            us = time_graph(lambda i: K.gemm(a, ws[i], bias, out=o, bn=bn), nvar)
-            out.append({"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn, "splitk": 1, "us": round(us, 2),
-                        "roofline_us": round(roof, 2)})
-        for bn in (64, 128, 256):
-            if bn > n:
-                continue
-            for sk in (2, 4, 8, 16):
-                wsp = K.splitk_workspace("cuda", sk * m * n)
-
-                def call(i, bn=bn, sk=sk):
-                    w_, S = K.gemm_splitk(a, ws[i], sk, bn, wsp)
-                    K.splitk_finalize(w_, S, m, n, torch.bfloat16, bias=bias, residual=o, gamma=bias, beta=bias,
-                                      norm="layernorm")
-                us = time_graph(call, nvar)
-                us_g = time_graph(lambda i, bn=bn, sk=sk: K.gemm_splitk(a, ws[i], sk, bn, wsp), nvar)
-                out.append({"kernel": "gemm_splitk+finalize_ln", "m": m, "n": n, "k": k, "bn": bn, "splitk": sk,
-                            "us": round(us, 2), "gemm_only_us": round(us_g, 2), "roofline_us": round(roof, 2)})
-    x = torch.randn(m, 1024, device="cuda").to(torch.bfloat16)
-    g_ = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
-    out.append({"kernel": "layernorm", "rows": m, "h": 1024, "us": round(time_graph(lambda i: K.layernorm(x, g_, g_), 1), 2)})
-    return out
-
-
-def sweep_attention():
-    out = []
-    hbm, _, src = _peaks()
-    for batch, ctx in [(256, 416), (256, 128), (256, 768), (64, 416)]:
-        heads, dim = 16, 64
-        nb_seq = (ctx + 15) // 16
-        nblocks = batch * nb_seq
-        kc = torch.randn(nblocks, heads, 16, dim, device="cuda").to(torch.bfloat16)
-        vc = torch.randn(nblocks, heads, 16, dim, device="cuda").to(torch.bfloat16)
-        bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
-        q = torch.randn(batch, heads * dim, device="cuda").to(torch.bfloat16)
-        lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
-        o = torch.empty(batch, heads * dim, device="cuda", dtype=torch.bfloat16)
-        us = time_graph(lambda i: K.paged_attention(q, kc, vc, bt, lens, heads, heads, dim, max_ctx=1024, out=o), 1, reps=10)
-        byts = 2.0 * batch * ctx * heads * dim * 2
-        out.append({"kernel": "paged_attention", "batch": batch, "ctx": ctx, "us": round(us, 2),
-                    "gbs": round(byts / us / 1e3, 1), "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3)})
-    return out
-
-
-def sweep_gemm_depth(m=256):
-    """Shallow ring (two CTAs per SM) against deep ring (one CTA per SM, twice the stages) on the decode shapes."""
-    out = []
-    for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (50264, 1024)]:
-        nvar = max(2, int(300e6 // (n * k * 2)))
-        ws = [(torch.randn(n, k, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(nvar)]
-        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
-        o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        for bn in (32, 64, 128):
-            row = {"kernel": "gemm", "m": m, "n": n, "k": k, "bn": bn}
-            for name, flag in (("shallow_us", 0x2000), ("deep_us", 0x1000)):
-                row[name] = round(time_graph(lambda i: K.gemm(a, ws[i], out=o, bn=bn | flag), nvar), 2)
-            out.append(row)
-        K.check_status()
-    return out
-
-
-def overlap(batch=128, ctx=416, layers=24):
-    """Do an attention chain and a GEMM chain on two streams of one CUDA graph overlap?  Times each chain alone and
-    both together (same graph, two branches)."""
-    heads, d, H = 16, 64, 1024
-    nb_seq = (ctx + 15) // 16
-    nblocks = batch * nb_seq
-    kc = torch.randn(nblocks, heads, 16, d, device="cuda").bfloat16()
-    vc = torch.randn(nblocks, heads, 16, d, device="cuda").bfloat16()
-    bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
-    q = torch.randn(batch, H, device="cuda").bfloat16()
-    lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
-    ao = torch.empty(batch, H, device="cuda", dtype=torch.bfloat16)
-    a = torch.randn(batch, H, device="cuda").bfloat16()
-    ws = [(torch.randn(n, k, device="cuda") * 0.05).bfloat16() for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024)]]
-    outs = [torch.empty(batch, w.shape[0], device="cuda", dtype=torch.bfloat16) for w in ws]
-
-    def attn_chain():
-        for _ in range(layers):
-            K.paged_attention(q, kc, vc, bt, lens, heads, heads, d, max_ctx=ctx, out=ao)
-
-    def gemm_chain():
-        for _ in range(layers):
-            for w, o in zip(ws, outs):
-                K.gemm(a, w, out=o)
-
-    side = torch.cuda.Stream()
-
-    def both():
-        main = torch.cuda.current_stream()
-        side.wait_stream(main)
-        with torch.cuda.stream(side):
-            gemm_chain()
-        attn_chain()
-        main.wait_stream(side)
-
-    res = {"kernel": "overlap", "batch": batch, "ctx": ctx, "layers": layers}
-    for name, fn in (("attention_chain_us", attn_chain), ("gemm_chain_us", gemm_chain), ("both_us", both)):
-        fn()
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn()
-        res[name] = round(time_kernel(g.replay, iters=10, flush=False), 1)
-    K.check_status()
-    return res
-
-
 def bench_dense_attention(batch=64, seq=128, heads=12, dim=64, causal=False, iters=20, flush=True):
     """Tensor-core attention over a fused qkv buffer of `batch` sequences of `seq` tokens (V transpose + attention)."""
     hn = heads * dim
@@ -215,42 +95,6 @@ def bench_dense_attention(batch=64, seq=128, heads=12, dim=64, causal=False, ite
     return {"kernel": "dense_attention(+transpose_v)", "batch": batch, "seq": seq, "heads": heads, "dim": dim,
             "causal": causal, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "roofline_us": round(roof, 2),
             "frac_of_" + src: round(roof / us, 3)}
-
-
-def probe_dense_attention(batch=8, seq=1024, heads=16, dim=64, causal=True):
-    """Cycle counts between the phase boundaries of one attention CTA (last query tile of head 0, sequence 0): where
-    a key-tile iteration spends its time, for the softmax warps and for the MMA thread."""
-    import ctypes as C
-    from .. import _native
-    hn = heads * dim
-    qkv = torch.randn(batch * seq, 3 * hn, device="cuda").bfloat16()
-    plan = K.dense_attention_plan([seq] * batch, "cuda")
-    out = torch.empty(batch * seq, hn, device="cuda", dtype=torch.bfloat16)
-    vt = torch.empty(hn, plan["vt_cols"], device="cuda", dtype=torch.bfloat16)
-    call = lambda: K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, dim, causal, out=out, vt=vt)
-    for _ in range(3):
-        call()
-    torch.cuda.synchronize()
-    buf = torch.zeros(128, dtype=torch.int64, device="cuda")
-    lib = _native.cuda()
-    lib.ronn_flash_attention_set_probe.restype = None
-    lib.ronn_flash_attention_set_probe.argtypes = [C.c_void_p]
-    lib.ronn_flash_attention_set_probe(buf.data_ptr())
-    try:
-        call()
-        torch.cuda.synchronize()
-    finally:
-        lib.ronn_flash_attention_set_probe(None)
-    K.check_status()
-    t = buf.cpu().view(2, 8, 8)
-    t0 = int(t[0, 0, 0])
-    res = {"kernel": "flash_attention phase probe", "batch": batch, "seq": seq, "heads": heads, "dim": dim, "causal": causal,
-           "softmax_points": ["before s_full wait", "S ready", "pass 1 done", "maxima exchanged", "O updated", "pass 2 done",
-                              "p_full arrived"],
-           "mma_points": ["before k_full wait", "K ready", "S issued", "P ready", "V ready", "PV issued"],
-           "softmax_cycles": [[int(t[0, j, p_]) - t0 for p_ in range(7)] for j in range(8) if int(t[0, j, 0])],
-           "mma_cycles": [[int(t[1, j, p_]) - t0 for p_ in range(6)] for j in range(8) if int(t[1, j, 0])]}
-    return res
 
 
 def bench_fused_single_rank(m=256, n=1024, k=1024, iters=20, flush=True):
@@ -451,7 +295,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "sweep-decode-gemm", "sweep-gemm-depth", "overlap", "dense-attention", "attention-probe", "fused-single-rank", "sweep-attention", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "dense-attention", "fused-single-rank", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -481,24 +325,13 @@ def main():
         res = [bench_bitlinear(a.m if a.m != 256 else 128, a.n if a.n != 1024 else 2560, a.k if a.k != 1024 else 2560, flush=fl, iters=a.iters)]
     elif a.what == "bitnet-shapes":
         res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
-    elif a.what == "sweep-decode-gemm":
-        res = sweep_decode_gemm(a.m)
     elif a.what == "dense-attention":
         # without --batch / --ctx / --heads: the DistilBERT encoder shape (64 x 128 tokens, 12 heads)
         given = lambda flag: any(x == flag or x.startswith(flag + "=") for x in sys.argv)
         res = [bench_dense_attention(a.batch if given("--batch") else 64, a.ctx if given("--ctx") else 128,
                                      a.heads if given("--heads") else 12, a.dim, causal=a.causal, iters=a.iters, flush=fl)]
-    elif a.what == "attention-probe":
-        res = [probe_dense_attention(a.batch if a.batch != 256 else 8, a.ctx if a.ctx != 416 else 1024, a.heads, a.dim,
-                                     causal=a.causal)]
     elif a.what == "fused-single-rank":
         res = [bench_fused_single_rank(a.m, a.n, a.k, iters=a.iters, flush=fl)]
-    elif a.what == "overlap":
-        res = [overlap(a.batch if a.batch != 256 else 128, a.ctx)]
-    elif a.what == "sweep-gemm-depth":
-        res = sweep_gemm_depth(a.m)
-    elif a.what == "sweep-attention":
-        res = sweep_attention()
     elif a.what == "prefill-shapes":
         res = [bench_gemm(8192, n, k) for (n, k) in [(3072, 1024), (1024, 1024), (4096, 1024), (1024, 4096)]]
         res += [bench_gemm(8192, 8192, 8192, iters=5)]

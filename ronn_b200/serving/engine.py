@@ -94,9 +94,13 @@ class LLMEngine:
         self.use_graph = bool(self.cfg.use_cuda_graph and self.device.type == "cuda")
         self.h2d_bytes_last = 0
         self.d2h_bytes_last = 0
+        # launcher calls of the sm_100a kernel library made for the steps of this engine (replayed graphs included)
+        self.kernel_launches = 0
+        self.kernel_launches_last = 0
         self.on_token: Optional[Callable[[Request, int], None]] = None
         self._non_greedy = 0
         self._watch_count = 0
+        self._replayed_launches = 0
         self.host_seconds_last = (0.0, 0.0)
         self._part_streams: List[torch.cuda.Stream] = []
         self._part_comms: list = []
@@ -167,6 +171,12 @@ class LLMEngine:
             self._finish(self.requests[rid], FinishReason.ERROR, now, cancel=True, error=reason)
         return ids
 
+    def _kernel_lib(self):
+        if self.cfg.backend != "kernels":
+            return None
+        from .. import _native
+        return _native.cuda()
+
     @property
     def _watch(self) -> bool:
         return self._watch_count > 0 or self.on_token is not None
@@ -235,6 +245,9 @@ class LLMEngine:
         if self.cfg.backend == "torch":
             longest = int(h.field("seq_lens")[:n_items].max())
             self.runner.step_ctx = min(-(-longest // 128) * 128, self.cfg.max_model_len)
+        lib = self._kernel_lib()
+        n_launch0 = lib.launches if lib is not None else 0
+        self._replayed_launches = 0
         try:
             if decode and self.use_graph and self._non_greedy == 0:
                 toks = self._decode_graph(n_items)
@@ -257,6 +270,8 @@ class LLMEngine:
             self.sched.abort_step()
             self.metrics.failed_steps += 1
             raise
+        self.kernel_launches_last = ((lib.launches - n_launch0) if lib is not None else 0) + self._replayed_launches
+        self.kernel_launches += self.kernel_launches_last
         t_dev = time.perf_counter()
         sampled = self.sampled_host[:n_items].numpy().copy()
         req_ids = sb.req_ids.copy()
@@ -354,12 +369,15 @@ class LLMEngine:
             torch.cuda.current_stream().wait_stream(s)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            lib = self._kernel_lib()
+            n0 = lib.launches if lib is not None else 0
             with torch.cuda.graph(g):
                 out = run()
-            entry = (g, out)
+            entry = (g, out, (lib.launches - n0) if lib is not None else 0)
             self._graphs[key] = entry
-        g, out = entry
+        g, out, captured = entry
         g.replay()
+        self._replayed_launches += captured
         return out
 
     # ------------------------------------------------------------------ concurrent part-batches of a decode step

@@ -10,7 +10,7 @@ import torch  # noqa: E402
 
 from ronn_b200.api.model import Model  # noqa: E402
 from ronn_b200.models.gpt2 import GPT2Config, build_gpt2  # noqa: E402
-from ronn_b200.parallel.fused import make_comm  # noqa: E402
+from ronn_b200.parallel import make_comm  # noqa: E402
 from ronn_b200.parallel.group import init_distributed  # noqa: E402
 from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams  # noqa: E402
 
