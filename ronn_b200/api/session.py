@@ -37,6 +37,7 @@ class SessionOptions:
     tp_size: int = 1
     enable_hrm: bool = False
     use_cuda_graph: bool = False
+    provider_instance: Optional[object] = None    # an ExecutionProvider object to run on (e.g. a custom-hardware provider)
 
     @staticmethod
     def new() -> "SessionOptions":
@@ -46,7 +47,12 @@ class SessionOptions:
         return replace(self, optimization_level=OptimizationLevel.parse(level))
 
     def with_provider(self, provider) -> "SessionOptions":
-        return replace(self, provider_type=ProviderType.parse(provider))
+        """A provider kind ("cpu" | "gpu" | "bitnet" | "wasm" | "custom" or a ``ProviderType``), or an
+        ``ExecutionProvider`` object (a custom-hardware provider, a pre-configured provider) to run on."""
+        from ..providers.base import ExecutionProvider
+        if isinstance(provider, ExecutionProvider):
+            return replace(self, provider_type=provider.provider_id, provider_instance=provider)
+        return replace(self, provider_type=ProviderType.parse(provider), provider_instance=None)
 
     def with_num_threads(self, n: int) -> "SessionOptions":
         return replace(self, num_threads=int(n))
@@ -97,11 +103,19 @@ class SessionBuilder:
         return self
 
     def build(self) -> "InferenceSession":
-        from ..providers import create_provider_system
+        from ..providers import create_comprehensive_provider_system, create_provider_system
         opts = self.options
         graph: ModelGraph = self.model.graph.clone()
         opt_stats = Optimizer(opts.optimization_level, opts.provider_type).optimize(graph)
-        registry = create_provider_system()
+        if opts.provider_instance is not None:
+            registry = create_provider_system()
+            if registry.get_provider(opts.provider_type) is not None:
+                registry.unregister_provider(opts.provider_type)
+            registry.register_provider(opts.provider_instance)
+        elif opts.provider_type in (ProviderType.WASM, ProviderType.CUSTOM):
+            registry = create_comprehensive_provider_system()
+        else:
+            registry = create_provider_system()
         provider = registry.get_provider(opts.provider_type)
         if provider is None:
             raise ProviderError(f"Provider {opts.provider_type.name} not available")

@@ -36,9 +36,15 @@ def create_provider_system() -> ProviderRegistry:
 
 
 def create_comprehensive_provider_system() -> ProviderRegistry:
-    """Adds the registry stubs for targets that do not exist on a B200 box (WebAssembly, NPU, TPU);
-    they report ``available=False`` and refuse to compile."""
-    from .custom.stubs import NpuProvider, TpuProvider, WasmProvider
+    """Adds the WebAssembly-target provider and an NPU-style custom provider (host-emulated device) to the system."""
+    from .custom.targets import NpuProvider, WasmProvider
     reg = create_provider_system()
     reg.register_provider(WasmProvider())
+    reg.register_provider(NpuProvider())
     return reg
+
+
+def create_custom_provider_registry(plugin_paths=None):
+    """Registry of vendor plugins (``providers/custom/registry.py``)."""
+    from .custom.registry import CustomProviderRegistry
+    return CustomProviderRegistry(plugin_paths)
