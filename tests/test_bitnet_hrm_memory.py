@@ -78,6 +78,58 @@ def test_bitnet_provider_session_close_to_full_precision():
     assert p.provider_id.name == "BITNET" and p.estimate_speedup("MatMul") == 64.0 and p.estimate_speedup("Xor") == 128.0
 
 
+@pytest.mark.parametrize("method", ["binary", "ternary", "asymmetric"])
+@pytest.mark.parametrize("binarize", [False, True])
+def test_bitnet_provider_compiles_constant_weights_to_packed_integer_kernels(method, binarize):
+    """MatMul / Gemm / FusedGemm with constant weights run on 2-bit packed weights and integer activations: the
+    session's result equals the integer arithmetic written out in fp32, and the weights are held packed."""
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.providers.bitnet.provider import BitNetExecutionProvider, BitNetProviderConfig
+    from ronn_b200.providers.bitnet.quantization import QuantizationMethod, quantize_ternary
+    g = torch.Generator().manual_seed(3)
+    K, H, N = 70, 48, 12                                   # K is not a multiple of 64: the packed rows are padded
+    w1, b1 = torch.randn(K, H, generator=g) * 0.2, torch.randn(H, generator=g) * 0.1
+    w2 = torch.randn(N, H, generator=g) * 0.2             # used through Gemm with transB = 1
+    b = GraphBuilder().add_input("x", [5, K]).add_output("y", [5, N])
+    b.add_initializer("w1", w1).add_initializer("b1", b1).add_initializer("w2", w2)
+    b.add_op("MatMul", ["x", "w1"], ["h0"]).add_op("Add", ["h0", "b1"], ["h1"]).add_op("Relu", ["h1"], ["h2"])
+    b.add_op("Gemm", ["h2", "w2"], ["y"], transB=1, alpha=0.5)
+    graph = b.build()
+    x = torch.randn(5, K, generator=g)
+    prov = BitNetExecutionProvider(BitNetProviderConfig(QuantizationMethod(method), binarize_activations=binarize))
+    if torch.cuda.is_available():
+        pytest.skip("the host integer kernel is checked here; the device kernel has its own test")
+    sess = Model.from_graph(graph).create_session(SessionOptions().with_provider(prov).with_optimization_level("O2"))
+    y = sess.run({"x": x})["y"]
+
+    def wq(w_nk):
+        if method == "binary":
+            return torch.where(w_nk >= 0, 1.0, -1.0), float(w_nk.abs().mean())
+        q = quantize_ternary(w_nk, "absmean" if method == "asymmetric" else "threshold")
+        return q.values().reshape(w_nk.shape).float(), q.scale
+
+    def aq(t):
+        if binarize:
+            return torch.where(t >= 0, 1.0, -1.0), t.abs().mean().expand(t.shape[0])
+        s = t.abs().amax(-1).clamp_min(1e-5) / 127.0
+        return torch.round(t / s[:, None]).clamp(-127, 127), s
+
+    v1, s1 = wq(w1.t().contiguous())
+    q, sx = aq(x)
+    h = torch.relu((q @ v1.t()) * sx[:, None] * s1 + b1)
+    v2, s2 = wq(w2)
+    q2, sh = aq(h)
+    ref = 0.5 * (q2 @ v2.t()) * sh[:, None] * s2
+    torch.testing.assert_close(y, ref, atol=1e-4, rtol=1e-4)
+    packed = prov.packed_weights
+    assert len(packed) == 2 and all(p.packed.dtype == torch.uint8 and p.k_padded % 64 == 0 for p in packed.values())
+    assert all(p.compression_ratio() > 8 for p in packed.values())
+    # the dense copies of weights that only the packed kernel reads are not kept by the compiled kernel
+    kept = sum(t.numel() for t in sess._kernel.const_slots.values() if isinstance(t, torch.Tensor))
+    assert kept < w1.numel()
+
+
 def test_complexity_and_routing():
     a = ComplexityAssessor()
     low = a.assess(torch.ones(1, 4))

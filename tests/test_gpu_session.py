@@ -87,3 +87,57 @@ def test_encoder_runner_kernels_match_operator_backend():
     want = EncoderRunner(graph, dtype=torch.bfloat16, backend="torch").forward(ids, mask)
     for b, n in enumerate(mask.sum(1).tolist()):
         torch.testing.assert_close(got[b, :n].float(), want[b, :n].float(), atol=6e-2, rtol=5e-2)
+
+
+@pytest.mark.parametrize("method", ["binary", "ternary", "asymmetric"])
+def test_bitnet_provider_session_runs_the_bitlinear_kernel(method):
+    """A BitNet-provider session compiles constant-weight MatMul / Gemm nodes to packed 2-bit weights and launches the
+    tcgen05 integer kernel for them; the result equals the host integer oracle of the same quantised operands."""
+    from ronn_b200 import Model, SessionOptions, _native
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.providers.bitnet.provider import BitNetExecutionProvider, BitNetProviderConfig
+    from ronn_b200.providers.bitnet.quantization import QuantizationMethod, bitlinear_reference
+    g = torch.Generator().manual_seed(11)
+    K, H, N = 256, 320, 64
+    b = GraphBuilder().add_input("x", [40, K]).add_output("y", [40, N])
+    b.add_initializer("w1", torch.randn(K, H, generator=g) * 0.1).add_initializer("b1", torch.randn(H, generator=g) * 0.1)
+    b.add_initializer("w2", torch.randn(H, N, generator=g) * 0.1)
+    b.add_op("MatMul", ["x", "w1"], ["h0"]).add_op("Add", ["h0", "b1"], ["h1"]).add_op("Relu", ["h1"], ["h2"])
+    b.add_op("MatMul", ["h2", "w2"], ["y"])
+    x = torch.randn(40, K, generator=g).cuda().bfloat16()
+    prov = BitNetExecutionProvider(BitNetProviderConfig(QuantizationMethod(method)))
+    sess = Model.from_graph(b.build()).create_session(SessionOptions().with_provider(prov))
+    lib = _native.cuda()
+    calls = []
+    real = lib.ronn_bitlinear
+    lib.__dict__["ronn_bitlinear"] = lambda *a: (calls.append(1), real(*a))[1]
+    try:
+        y = sess.run({"x": x})["y"]
+    finally:
+        lib.__dict__["ronn_bitlinear"] = real
+    assert len(calls) == 2                                  # one launch of the integer kernel per linear layer
+    # oracle: the same packed weights and the same per-token int8 activations, evaluated exactly on the host
+    p1, p2 = (prov.packed_weights[("w1", False)], prov.packed_weights[("w2", False)])
+    h = bitlinear_reference(x.cpu(), p1.packed.cpu(), p1.scale, None, p1.k_padded, p1.n_padded)[:, :p1.n].float()
+    h = torch.relu(h + b.build().initializers["b1"].float()).bfloat16()
+    ref = bitlinear_reference(h, p2.packed.cpu(), p2.scale, None, p2.k_padded, p2.n_padded)[:, :p2.n].float()
+    torch.testing.assert_close(y.float().cpu(), ref, atol=0.08 * float(ref.abs().max()), rtol=5e-2)
+
+
+def test_hrm_system1_session_launches_bitlinear():
+    """The HRM router's fast path is a BitNet-provider session: a low-complexity input is served by the packed kernel."""
+    from ronn_b200 import Model, _native
+    from ronn_b200.hrm.router import RoutingStrategy
+    from ronn_b200.models.mlp784 import build_mlp784
+    s = Model.from_graph(build_mlp784()).create_session(enable_hrm=True)
+    s._router.hrm.router.set_strategy(RoutingStrategy.ALWAYS_SYSTEM1)
+    lib = _native.cuda()
+    calls = []
+    real = lib.ronn_bitlinear
+    lib.__dict__["ronn_bitlinear"] = lambda *a: (calls.append(1), real(*a))[1]
+    try:
+        out = s.run({"input": torch.rand(1, 784)})
+    finally:
+        lib.__dict__["ronn_bitlinear"] = real
+    assert out["probs"].shape == (1, 10) and abs(float(out["probs"].float().sum()) - 1) < 1e-2
+    assert len(calls) == 2
