@@ -40,7 +40,7 @@ class NodeFusionPass(OptimizationPass):
             progress = False
             for fn in (self._fold_bn, self._conv_act, self._decomposed_layernorm, self._erf_gelu, self._matmul_bias,
                        self._gemm_act,
-                       self._gemm_residual):
+                       self._gemm_residual, self._qkv_projection):
                 n = fn(graph)
                 if n:
                     stats.nodes_fused += n
@@ -279,6 +279,55 @@ class NodeFusionPass(OptimizationPass):
             mm.outputs = [add.outputs[0]]
             graph.remove_nodes([add.id])
             return 1
+        return 0
+
+    def _qkv_projection(self, graph: ModelGraph) -> int:
+        """Q, K and V projections of one Attention node (three linear layers over the same input) become ONE projection
+        with the weights side by side, followed by a Split whose outputs are column slices of the fused result: one
+        GEMM instead of three, and the attention kernel can read Q and K in place."""
+        cons, prod = graph.consumers(), graph.producers()
+        outputs = set(graph.output_names())
+        for att in graph.nodes:
+            if att.op_type not in ("Attention", "MultiHeadAttention") or len(att.inputs) < 3 or att.attr("fused_qkv"):
+                continue
+            ps = [prod.get(t) for t in att.inputs[:3]]
+            if any(p is None or p.op_type not in ("FusedGemm", "MatMul") for p in ps) or len({p.id for p in ps}) != 3:
+                continue
+            if len({p.inputs[0] for p in ps}) != 1 or len({p.op_type for p in ps}) != 1:
+                continue
+            ws = [graph.initializers.get(p.inputs[1]) for p in ps]
+            if any(w is None or w.dim() != 2 for w in ws) or len({(w.shape[0], w.dtype) for w in ws}) != 1:
+                continue
+            if any(p.attr("activation") or int(p.attr("transB", 0)) or len(p.inputs) > 3 for p in ps):
+                continue
+            if any(len(cons.get(p.outputs[0], [])) != 1 or p.outputs[0] in outputs for p in ps):
+                continue
+            has_bias = [len(p.inputs) > 2 and bool(p.inputs[2]) for p in ps]
+            if any(has_bias) and not all(has_bias):
+                continue
+            biases = [graph.initializers.get(p.inputs[2]) for p in ps] if all(has_bias) else []
+            if any(b is None or b.dim() != 1 for b in biases):
+                continue
+            base = ps[0].name or f"node_{ps[0].id}"
+            wname = graph.fresh_name(base + ".qkv_weight")
+            graph.initializers[wname] = torch.cat(ws, dim=1).contiguous()
+            inputs = [ps[0].inputs[0], wname]
+            if biases:
+                bname = graph.fresh_name(base + ".qkv_bias")
+                graph.initializers[bname] = torch.cat(biases).contiguous()
+                inputs.append(bname)
+            fused_out = graph.fresh_name(base + ".qkv")
+            sizes = graph.fresh_name(base + ".qkv_sizes")
+            graph.initializers[sizes] = torch.tensor([int(w.shape[1]) for w in ws], dtype=torch.int64)
+            idx = min(graph.nodes.index(p) for p in ps)
+            outs = [p.outputs[0] for p in ps]
+            op, dom = (("FusedGemm", RONN) if (biases or ps[0].op_type == "FusedGemm") else ("MatMul", ""))
+            graph.remove_nodes([p.id for p in ps])
+            graph.add_node(op, inputs, [fused_out], {"transB": 0} if op == "FusedGemm" else {}, name=base + ".qkv", domain=dom,
+                           index=idx)
+            graph.add_node("Split", [fused_out, sizes], outs, {"axis": -1}, name=base + ".qkv_split", index=idx + 1)
+            att.attributes["fused_qkv"] = 1
+            return 2
         return 0
 
     def _gemm_act(self, graph: ModelGraph) -> int:

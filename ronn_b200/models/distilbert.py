@@ -88,7 +88,10 @@ def build_distilbert(cfg: DistilBertConfig = DistilBertConfig(), dtype: torch.dt
         lin(x, "attention.q_lin", f"{p}.q")
         lin(x, "attention.k_lin", f"{p}.k")
         lin(x, "attention.v_lin", f"{p}.v")
-        g.add_node("Attention", [f"{p}.q", f"{p}.k", f"{p}.v", "mask4"], [f"{p}.ctx"], {"num_heads": cfg.n_heads}, name=f"{p}.attention")
+        # mask_type: the additive mask only hides a padded suffix of every row (the contract of `attention_mask` here),
+        # which lets a provider pass key lengths to its attention kernel instead of the dense mask
+        g.add_node("Attention", [f"{p}.q", f"{p}.k", f"{p}.v", "mask4"], [f"{p}.ctx"],
+                   {"num_heads": cfg.n_heads, "mask_type": "key_padding"}, name=f"{p}.attention")
         lin(f"{p}.ctx", "attention.out_lin", f"{p}.sa")
         g.add_node("Add", [f"{p}.sa", x], [f"{p}.sa_res"], name=f"{p}.sa_res")
         g.add_node("LayerNormalization", [f"{p}.sa_res", f"{p}.sa_layer_norm.weight", f"{p}.sa_layer_norm.bias"], [f"{p}.h"],

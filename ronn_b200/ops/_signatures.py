@@ -32,6 +32,7 @@ def declare(lib):
     sig("ronn_unary", [V, V, L, I, I, V])
     sig("ronn_binary", [V, V, V, L, I, I, V])
     sig("ronn_swiglu_fused", [V, V, L, I, I, V])
+    sig("ronn_fused_elementwise", [V, V, L, I, V, V, V, L, I, V], optional=True)
     sig("ronn_embedding", [V, V, V, V, V, L, I, I, I, L, I, V])
     sig("ronn_argmax", [V, V, V, L, I, L, I, I, V])
     sig("ronn_argmax_combine", [V, V, V, I, I, V])

@@ -154,6 +154,59 @@ def binary(a: torch.Tensor, b: torch.Tensor, op: str) -> torch.Tensor:
     return y
 
 
+_FEW_CODES = {"Relu": 0, "Gelu": 1, "Sigmoid": 2, "Tanh": 3, "Neg": 4, "Abs": 5, "Exp": 6, "Sqrt": 7, "Swish": 8, "SiLU": 8,
+              "Add": 16, "Mul": 17, "Sub": 18, "Div": 19}
+
+
+def fused_elementwise_plan(x: torch.Tensor, op_names, operands):
+    """Checks that a chain of element-wise operators fits the one-launch kernel and returns its launch plan, or None.
+    ``operands[k]`` is the second operand of binary operator k (None for unary ones): a tensor of x's shape, a vector
+    over the last dimension, or a one-element tensor."""
+    if len(op_names) < 1 or len(op_names) > 8 or x.dtype not in (torch.bfloat16, torch.float16) or not x.is_cuda:
+        return None
+    if x.numel() == 0 or x.numel() % 8 or not x.is_contiguous() or x.data_ptr() % 16:
+        return None
+    codes, modes, ops = [], [], []
+    for name, b in zip(op_names, operands):
+        code = _FEW_CODES.get(name)
+        if code is None:
+            return None
+        mode = 0
+        if code >= 16:
+            if b is None or not b.is_cuda or b.dtype != x.dtype:
+                return None
+            if b.numel() == 1:
+                mode = 2
+            elif b.shape == x.shape and b.is_contiguous() and b.data_ptr() % 16 == 0:
+                mode = 0
+            elif (b.numel() == x.shape[-1] and b.shape[-1] == x.shape[-1] and x.shape[-1] % 8 == 0 and b.is_contiguous()
+                  and b.data_ptr() % 16 == 0):
+                mode = 1
+            else:
+                return None
+        codes.append(code)
+        modes.append(mode)
+        ops.append(b if code >= 16 else None)
+    return codes, modes, ops
+
+
+def fused_elementwise(x: torch.Tensor, op_names, operands, plan=None) -> torch.Tensor:
+    """y = op_n(...op_1(x, b_1)..., b_n) in one launch (see ``fused_elementwise_plan`` for what fits)."""
+    import ctypes as C
+    plan = plan or fused_elementwise_plan(x, op_names, operands)
+    if plan is None:
+        raise KernelError("this element-wise chain does not fit the fused kernel")
+    codes, modes, ops = plan
+    n = len(codes)
+    y = torch.empty_like(x)
+    rc = _native.cuda().ronn_fused_elementwise(x.data_ptr(), y.data_ptr(), x.numel(), n, (C.c_int * n)(*codes),
+                                               (C.c_int * n)(*modes),
+                                               (C.c_void_p * n)(*[None if b is None else b.data_ptr() for b in ops]),
+                                               x.shape[-1], _DT[x.dtype], _stream())
+    _check(rc, "fused_elementwise")
+    return y
+
+
 def swiglu_fused(x: torch.Tensor) -> torch.Tensor:
     """x = [rows, 2F] (gate | up) -> silu(gate) * up."""
     F2 = x.shape[-1]

@@ -85,6 +85,10 @@ class GpuOpTable:
             return self._binary(_BINARY_KERNELS[op], fallback)
         if op in ("Gather", "Embedding"):
             return self._gather(node, fallback)
+        if op == "FusedElementwise":
+            return self._fused_elementwise(node, fallback)
+        if op in ("Attention", "MultiHeadAttention"):
+            return self._attention(node, fallback)
         if op in ("Conv", "FusedConv") and node.attr("data_format") == "NHWC":
             from .gpu_conv import conv_resolver
             return conv_resolver(self, node, fallback)
@@ -182,6 +186,87 @@ class GpuOpTable:
                     or y.device.type != "cuda"):
                 return fallback(i, a, c)
             return [K.binary(x, y, kname)]
+        return run
+
+    def _fused_elementwise(self, node, fallback):
+        """A collapsed chain of element-wise nodes: one launch of the chain kernel when the operands fit it."""
+        K = self.K
+        names = list(node.attr("ops"))
+        arity = [int(v) for v in node.attr("arity")]
+
+        def run(i, a, c):
+            x = i[0]
+            operands, k = [], 1
+            for n_in in arity:
+                operands.append(i[k] if n_in == 2 else None)
+                k += n_in - 1
+            if not isinstance(x, torch.Tensor) or x.device.type != "cuda":
+                return fallback(i, a, c)
+            operands = [self.to_device(b) if (b is not None and b.device.type != "cuda") else b for b in operands]
+            operands = [b.to(x.dtype) if (b is not None and b.dtype != x.dtype and b.is_floating_point()) else b for b in operands]
+            plan = K.fused_elementwise_plan(x, names, operands)
+            if plan is None:
+                return fallback(i, a, c)
+            return [K.fused_elementwise(x, names, operands, plan)]
+        return run
+
+    def _attention(self, node, fallback):
+        """Attention / MultiHeadAttention on [B, S, H] tensors -> the tcgen05 attention kernel.  Q and K are read in
+        place when they are column slices of one fused projection buffer (what the QKV fusion of the optimiser
+        produces), otherwise they are packed side by side first.  Masks: none, causal, or a key-padding mask marked
+        ``mask_type="key_padding"`` (additive [B, 1, 1, S] with the padding at the end of every row); anything else
+        runs the operator's library form."""
+        K = self.K
+        heads = int(node.attr("num_heads", 0))
+        causal = bool(int(node.attr("causal", 0)))
+        mask_type = node.attr("mask_type", "")
+        plans = {}
+
+        def plan_for(B, S, dev):
+            p = plans.get((B, S))
+            if p is None:
+                s_pad = -(-S // 128) * 128
+                mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+                p = {"seq_start": mk([b * S for b in range(B)]), "vt_start": mk([b * s_pad for b in range(B)]),
+                     "vt_cols": B * s_pad, "max_len": S, "n_seq": B, "q_len": torch.full((B,), S, dtype=torch.int32, device=dev),
+                     "kv_len": torch.full((B,), S, dtype=torch.int32, device=dev)}
+                plans[(B, S)] = p
+            return p
+
+        def run(i, a, c):
+            q, k, v = i[0], i[1], i[2]
+            mask = i[3] if len(i) > 3 else None
+            ok = (heads > 0 and q.dim() == 3 and q.dtype in _HALF and k.dtype == q.dtype and v.dtype == q.dtype
+                  and q.device.type == "cuda" and q.shape == k.shape == v.shape and q.shape[-1] % heads == 0
+                  and q.shape[-1] // heads in (64, 128) and (mask is None or mask_type == "key_padding"))
+            if not ok:
+                return fallback(i, a, c)
+            B, S, H = q.shape
+            d = H // heads
+            plan = plan_for(B, S, q.device)
+            # column slices of one [B * S, ld] buffer?
+            same = (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr()
+                    and q.stride() == k.stride() == v.stride() and q.stride(2) == 1 and q.stride(0) == S * q.stride(1)
+                    and q.stride(1) % 8 == 0)
+            if same:
+                ld = q.stride(1)
+                offs = [t.storage_offset() for t in (q, k, v)]
+                base = min(offs)
+                row0 = base // ld * ld                       # start of the row that holds the lowest slice
+                cols = [o - row0 for o in offs]
+                same = all(0 <= cc and cc + H <= ld and cc % 8 == 0 for cc in cols) and (row0 * q.element_size()) % 16 == 0
+            if same:
+                buf = torch.as_strided(q, (B * S, ld), (ld, 1), row0)
+                q_off, k_off, v_off = cols
+            else:
+                buf = torch.cat([q.reshape(B * S, H), k.reshape(B * S, H), v.reshape(B * S, H)], dim=1)
+                q_off, k_off, v_off = 0, H, 2 * H
+            if mask is not None:
+                m = mask.reshape(B, -1, mask.shape[-1])[:, 0, :] if mask.dim() > 2 else mask.reshape(B, -1)
+                kv_len = (m > -1e4).sum(dim=-1).clamp_(min=1).to(torch.int32)
+                plan = dict(plan, kv_len=kv_len)
+            out = K.dense_attention(buf, q_off, k_off, v_off, plan, heads, heads, d, causal, plan["q_len"], S)
+            return [out.view(B, S, H)]
         return run
 
     def _gather(self, node, fallback):

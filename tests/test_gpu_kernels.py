@@ -436,3 +436,24 @@ def test_gemm_rownorm_cluster(K, M, N, K_, norm):
     x2, y2 = K.gemm_rownorm(a, w, None, None, gamma, None, 1e-5, "rmsnorm")
     K.check_status()
     torch.testing.assert_close(x2.float(), a.float() @ w.float().t(), atol=2e-2 * math.sqrt(K_ / 64) + 0.03, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fused_elementwise_chain(K, dtype):
+    """Eight element-wise operators in one launch, with a full-size, a last-dimension-vector and a scalar operand."""
+    x = _rand(512, 768, dtype=dtype)
+    bias, full, scal = _rand(768, dtype=dtype), _rand(512, 768, dtype=dtype), torch.tensor([0.5], device="cuda", dtype=dtype)
+    names = ["Add", "Gelu", "Mul", "Sub", "Sigmoid", "Abs", "Sqrt", "Div"]
+    operands = [bias, None, full, scal, None, None, None, full.abs() + 1]
+    y = K.fused_elementwise(x, names, operands)
+    r = F.gelu(x.float() + bias.float(), approximate="tanh") * full.float() - 0.5
+    r = torch.sqrt(torch.sigmoid(r).abs()) / (full.abs() + 1).float()
+    torch.testing.assert_close(y.float(), r, atol=2e-2, rtol=2e-2)
+    for name, ref in (("Relu", torch.relu), ("Tanh", torch.tanh), ("Neg", torch.neg), ("Exp", torch.exp),
+                      ("Swish", lambda t: t * torch.sigmoid(t))):
+        got = K.fused_elementwise(x, [name, "Neg", "Neg"], [None, None, None])
+        torch.testing.assert_close(got.float(), ref(x.float()), atol=3e-2, rtol=2e-2)
+    # what does not fit is reported by the planner, not launched
+    assert K.fused_elementwise_plan(x[:, :100], ["Relu"], [None]) is None              # not contiguous
+    assert K.fused_elementwise_plan(x, ["Add"], [_rand(512, 1, dtype=dtype)]) is None   # broadcast along the rows
+    assert K.fused_elementwise_plan(x, ["Erf"], [None]) is None

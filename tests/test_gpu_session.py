@@ -141,3 +141,54 @@ def test_hrm_system1_session_launches_bitlinear():
         lib.__dict__["ronn_bitlinear"] = real
     assert out["probs"].shape == (1, 10) and abs(float(out["probs"].float().sum()) - 1) < 1e-2
     assert len(calls) == 2
+
+
+def test_gpu_session_runs_elementwise_chains_and_attention_on_kernels():
+    """O3 on the GPU provider: a chain of element-wise nodes is ONE launch of the chain kernel, and Attention nodes with
+    a key-padding mask run the tensor-core attention kernel on the fused QKV projection (no library attention)."""
+    from ronn_b200 import Model, SessionOptions, _native
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.models.distilbert import DistilBertConfig, build_distilbert
+    lib = _native.cuda()
+
+    def counting(names):
+        counts = {n: 0 for n in names}
+        saved = {n: getattr(lib, n) for n in names}
+        for n in names:
+            lib.__dict__[n] = (lambda real, key: (lambda *a: (counts.__setitem__(key, counts[key] + 1), real(*a))[1]))(saved[n], n)
+        return counts, saved
+
+    g = torch.Generator().manual_seed(2)
+    b = GraphBuilder().add_input("x", [64, 256]).add_output("y", [64, 256])
+    b.add_initializer("bias", torch.randn(256, generator=g)).add_initializer("w", torch.randn(64, 256, generator=g))
+    b.add_op("Add", ["x", "bias"], ["a"]).add_op("Relu", ["a"], ["r"]).add_op("Mul", ["r", "w"], ["m"]).add_op("Tanh", ["m"], ["y"])
+    graph = b.build()
+    x = torch.randn(64, 256, generator=g)
+    want = Model.from_graph(graph).create_session(SessionOptions().with_optimization_level("O0")).run({"x": x})["y"]
+    sess = Model.from_graph(graph).create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("bf16"))
+    assert [n.op_type for n in sess.graph().nodes] == ["FusedElementwise"]
+    counts, saved = counting(["ronn_fused_elementwise", "ronn_unary", "ronn_binary"])
+    try:
+        got = sess.run({"x": x})["y"].float().cpu()
+    finally:
+        for n, f in saved.items():
+            lib.__dict__[n] = f
+    assert counts == {"ronn_fused_elementwise": 1, "ronn_unary": 0, "ronn_binary": 0}
+    torch.testing.assert_close(got, want, atol=3e-2, rtol=3e-2)
+
+    m = Model.from_graph(build_distilbert(DistilBertConfig.tiny(n_layers=2, dim=256, n_heads=4, hidden_dim=512), dtype=torch.bfloat16, seed=4))
+    ids = torch.randint(0, 512, (5, 48))
+    mask = torch.ones(5, 48, dtype=torch.int64)
+    mask[1, 30:] = 0
+    mask[3, 5:] = 0
+    want = m.create_session(SessionOptions().with_optimization_level("O0")).run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"]
+    s = m.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("bf16"))
+    counts, saved = counting(["ronn_flash_attention", "ronn_gemm"])
+    try:
+        got = s.run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"].float().cpu()
+    finally:
+        for n, f in saved.items():
+            lib.__dict__[n] = f
+    assert counts["ronn_flash_attention"] == 2 and counts["ronn_gemm"] == 2 * 4        # fused QKV + out + two MLP per layer
+    for bi, n in enumerate(mask.sum(1).tolist()):
+        torch.testing.assert_close(got[bi, :n], want[bi, :n].float(), atol=8e-2, rtol=5e-2)

@@ -290,3 +290,25 @@ def test_layout_pass_tensor_that_is_graph_output_and_read_outside_the_region():
     s = _check_levels(b.build(), {"x": torch.randn(2, 3, 8, 8)}, ["feat", "flat"])
     back = [n for n in s.graph().nodes if n.op_type == "Transpose" and n.attributes["perm"] == [0, 3, 1, 2]]
     assert len(back) == 1 and back[0].outputs == ["feat"]
+
+
+def test_qkv_projections_of_an_attention_node_fuse_into_one_gemm():
+    from ronn_b200.models.distilbert import DistilBertConfig, build_distilbert
+    g = build_distilbert(DistilBertConfig.tiny(n_layers=2, dim=64, n_heads=2, hidden_dim=128), dtype=torch.float32, seed=5)
+    ids = torch.randint(0, 512, (3, 10))
+    mask = torch.ones(3, 10, dtype=torch.int64)
+    mask[1, 6:] = 0
+    feeds = {"input_ids": ids, "attention_mask": mask}
+    _, ref = run(g, feeds)
+    for lvl in ("O2", "O3"):
+        s, out = run(g, feeds, lvl)
+        torch.testing.assert_close(out["last_hidden_state"], ref["last_hidden_state"], atol=1e-5, rtol=1e-5)
+        nodes = s.graph().nodes
+        att = [n for n in nodes if n.op_type == "Attention"]
+        assert len(att) == 2 and all(n.attr("fused_qkv") == 1 for n in att)
+        splits = [n for n in nodes if n.op_type == "Split"]
+        assert len(splits) == 2 and all(len(n.outputs) == 3 for n in splits)
+        # per layer: one fused QKV projection, the output projection and the two MLP projections
+        assert sum(1 for n in nodes if n.op_type == "FusedGemm") == 2 * 4
+        w = s.graph().initializers[[n for n in nodes if n.name and n.name.endswith(".qkv")][0].inputs[1]]
+        assert tuple(w.shape) == (64, 192)
