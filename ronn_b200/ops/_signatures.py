@@ -36,6 +36,7 @@ def declare(lib):
     sig("ronn_embedding", [V, V, V, V, V, L, I, I, I, L, I, V])
     sig("ronn_argmax", [V, V, V, L, I, L, I, I, V])
     sig("ronn_argmax_combine", [V, V, V, I, I, V])
+    sig("ronn_sample", [V, L, I, L, V, V, I, V, V, V], optional=True)
     sig("ronn_cast", [V, V, L, I, I, V])
     sig("ronn_kv_append", [V, L, I, I, V, V, V, V, L, I, I, I, F, I, I, V])
     sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V])

@@ -242,6 +242,38 @@ def argmax(x: torch.Tensor, col_offset: int = 0, return_max: bool = False, out: 
     return (out, mx) if return_max else out
 
 
+SAMPLE_RECORD_BYTES = 32      # {float temperature, top_p, repeat_penalty; int top_k; uint64 seed; int n_recent, use_counter}
+
+
+def pack_sample_params(buf, row: int, temperature: float, top_k: int, top_p: float, repeat_penalty: float, seed: int,
+                       n_recent: int, use_counter: bool = True) -> None:
+    """Writes the sampling record of one row into ``buf`` (a writable bytes-like host buffer of 32-byte records).
+    ``use_counter``: mix the row's device-side draw counter into the seed (fresh draws on every graph replay); off,
+    the draw is a function of ``seed`` alone."""
+    import struct
+    struct.pack_into("<fffiQii", buf, row * SAMPLE_RECORD_BYTES, float(temperature), float(top_p), float(repeat_penalty),
+                     int(top_k), int(seed) & 0xFFFFFFFFFFFFFFFF, int(n_recent), 1 if use_counter else 0)
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, recent: Optional[torch.Tensor], counters: torch.Tensor,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Token per row of fp32 ``logits`` [rows, vocab] (row stride free) on the device: repeat penalty (in place) ->
+    temperature -> top-k -> softmax -> top-p -> draw.  ``params``: uint8 tensor of 32-byte records
+    (``pack_sample_params``), ``recent``: int32 [rows, R] token ids the penalty applies to (or None), ``counters``:
+    int64 [rows] draw counters advanced by the kernel.  Rows with temperature <= 0 return the arg max."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("sample needs fp32 logits [rows, vocab] with unit column stride")
+    rows, vocab = logits.shape
+    if params.numel() < rows * SAMPLE_RECORD_BYTES or counters.numel() < rows:
+        raise KernelError("sample: parameter or counter buffer too small")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(_native.cuda().ronn_sample(logits.data_ptr(), logits.stride(0), vocab, rows, params.data_ptr(), _ptr(recent),
+                                      recent.shape[1] if recent is not None else 0, counters.data_ptr(), out.data_ptr(),
+                                      _stream()), "sample")
+    return out
+
+
 def argmax_combine(vals: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     shards, rows = vals.shape
     out = torch.empty(rows, dtype=torch.int32, device=vals.device)

@@ -101,9 +101,23 @@ class LLMEngine:
         self._non_greedy = 0
         self._watch_count = 0
         self._replayed_launches = 0
+        self._h2d_sampling = 0
         self.host_seconds_last = (0.0, 0.0)
         self._part_streams: List[torch.cuda.Stream] = []
         self._part_comms: list = []
+        # device-side sampling (kernel backend, one GPU): per-row sampling records and the recent-token windows of the
+        # repeat penalty are staged in pinned memory and reach the device in one copy per step, so that a non-greedy
+        # decode step is a CUDA-graph replay like a greedy one
+        self.device_sampling = (self.cfg.backend == "kernels" and self.device.type == "cuda" and self.runner.tp == 1)
+        self._samp_recent = 256
+        if self.device_sampling:
+            from ..ops import kernels as K
+            n = self.cfg.max_num_seqs
+            self._samp_bytes = n * K.SAMPLE_RECORD_BYTES
+            self._samp_host = torch.zeros(self._samp_bytes + n * self._samp_recent * 4, dtype=torch.uint8).pin_memory()
+            self._samp_dev = torch.zeros_like(self._samp_host, device=self.device)
+            self._samp_counters = torch.zeros(n, dtype=torch.int64, device=self.device)
+            self._samp_seed = int(torch.randint(0, 2 ** 62, (1,)).item())
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Iterable[int], params: Optional[SamplingParams] = None,
@@ -203,7 +217,8 @@ class LLMEngine:
         off_bt, _ = self.host.offsets["block_tables"]
         used = off_bt + n_items * self.max_blocks
         self.dev_buf[:used].copy_(self.host.host[:used], non_blocking=True)
-        self.h2d_bytes_last = used * 4
+        self.h2d_bytes_last = used * 4 + self._h2d_sampling
+        self._h2d_sampling = 0
 
     def _run_swaps(self) -> None:
         """Block copies the scheduler decided on: preempted sequences go to the host pool (device -> host) before their
@@ -251,6 +266,9 @@ class LLMEngine:
         try:
             if decode and self.use_graph and self._non_greedy == 0:
                 toks = self._decode_graph(n_items)
+            elif decode and self.use_graph and self.device_sampling:
+                self._stage_sampling(sb.req_ids[:n_items], self._bucket(n_items))
+                toks = self._decode_graph(n_items, sample=True)
             else:
                 self._upload(n_tokens, n_items)
                 b = self._batch_views(n_tokens, n_items)
@@ -330,8 +348,45 @@ class LLMEngine:
         if greedy:
             return self.runner.forward(b, decode, n_tokens, n_items)
         logits = self.runner.forward(b, decode, n_tokens, n_items, want_logits=True)
+        if self.device_sampling:
+            self._stage_sampling(req_ids[:n_items], n_items)
+            return self._sample_on_device(logits, n_items)
         reqs = [self.requests[int(i)] for i in req_ids]
         return sample_tokens(logits, reqs)
+
+    # ------------------------------------------------------------------ device-side sampling
+    def _stage_sampling(self, req_ids, rows: int) -> None:
+        """Fills the pinned sampling records (and the recent-token windows of rows with a repeat penalty) for the rows
+        of this step and copies them to the device.  The seed of a row's draw is a function of the request's seed and
+        of how many tokens it has generated, so a request samples the same tokens whatever batch it shares."""
+        from ..ops import kernels as K
+        buf = self._samp_host.numpy()
+        rec = buf[self._samp_bytes:].view(np.int32).reshape(-1, self._samp_recent)
+        any_recent = False
+        for row in range(rows):
+            if row < len(req_ids):
+                r = self.requests[int(req_ids[row])]
+                p = r.params
+                n_out = self.sched.num_tokens(r.id) - len(r.prompt_tokens)
+                base = p.seed if p.seed is not None else (self._samp_seed ^ (r.id * 0x9E3779B1))
+                n_recent = 0
+                if p.repeat_penalty != 1.0:
+                    window = (r.prompt_tokens[-64:] + r.output_tokens)[-self._samp_recent:]
+                    n_recent = len(window)
+                    rec[row, :n_recent] = window
+                    any_recent = True
+                K.pack_sample_params(buf, row, p.temperature, p.top_k, p.top_p, p.repeat_penalty,
+                                     (int(base) * 0x100000001B3 + n_out) & 0xFFFFFFFFFFFFFFFF, n_recent, use_counter=False)
+            else:
+                K.pack_sample_params(buf, row, 0.0, 0, 1.0, 1.0, 0, 0, use_counter=False)     # padded row
+        used = self._samp_bytes + (rows * self._samp_recent * 4 if any_recent else 0)
+        self._samp_dev[:used].copy_(self._samp_host[:used], non_blocking=True)
+        self._h2d_sampling = used
+
+    def _sample_on_device(self, logits: torch.Tensor, rows: int) -> torch.Tensor:
+        from ..ops import kernels as K
+        recent = self._samp_dev[self._samp_bytes:].view(torch.int32).view(-1, self._samp_recent)
+        return K.sample(logits[:rows], self._samp_dev, recent, self._samp_counters)
 
     # ------------------------------------------------------------------ CUDA-graph decode
     def _bucket(self, n: int) -> int:
@@ -340,7 +395,7 @@ class LLMEngine:
                 return bsz
         return self.cfg.max_num_seqs
 
-    def _decode_graph(self, n_items: int) -> torch.Tensor:
+    def _decode_graph(self, n_items: int, sample: bool = False) -> torch.Tensor:
         bsz = self._bucket(n_items)
         h = self.host
         if bsz > n_items:       # pad rows: no cache slot, no context
@@ -350,11 +405,14 @@ class LLMEngine:
             h.field("seq_lens")[n_items:bsz] = 0
             h.field("block_tables")[n_items * self.max_blocks: bsz * self.max_blocks] = 0
         self._upload(bsz, bsz)
-        key = (bsz, self.runner.step_ctx)
+        key = (bsz, self.runner.step_ctx, sample)
         entry = self._graphs.get(key)
         if entry is None:
-            parts = self._split_rows(bsz)
-            if parts is None:
+            parts = None if sample else self._split_rows(bsz)
+            if sample:
+                b = self._batch_views(bsz, bsz)
+                run = lambda: self._sample_on_device(self.runner.forward(b, True, bsz, bsz, want_logits=True), bsz)
+            elif parts is None:
                 b = self._batch_views(bsz, bsz)
                 run = lambda: self.runner.forward(b, True, bsz, bsz)
             else:

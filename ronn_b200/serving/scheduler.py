@@ -149,6 +149,10 @@ class Scheduler:
         s = self._lib.ronn_sched_state(self._h, req_id)
         return None if s < 0 else RequestState(s)
 
+    def num_tokens(self, req_id: int) -> int:
+        """Prompt plus generated tokens of a live request (-1 when unknown)."""
+        return self._lib.ronn_sched_num_tokens(self._h, req_id)
+
     def tokens(self, req_id: int) -> List[int]:
         n = self._lib.ronn_sched_num_tokens(self._h, req_id)
         if n < 0:

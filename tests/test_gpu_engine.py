@@ -88,3 +88,32 @@ def test_swap_preemption_on_the_device_cache():
     assert st["swap_preemptions"] >= 1 and st["swapped_in_blocks"] == st["swapped_out_blocks"] > 0
     agree = sum(a == b for x, y in zip(got, want) for a, b in zip(x, y))
     assert agree >= int(0.9 * 120), (agree, got, want)
+
+
+def test_non_greedy_decode_replays_a_cuda_graph_and_is_reproducible():
+    """Sampling with temperature / top-k / top-p / repeat penalty runs on the device inside the decode graph: the
+    engine never reads logits back, a seeded request draws the same tokens alone or in a batch, and a request with
+    top_k = 1 equals the greedy one."""
+    from ronn_b200 import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    m = Model.from_graph(build_gpt2(GPT2Config.tiny(n_layer=2, n_embd=128, n_head=2), dtype=torch.bfloat16, seed=5))
+    cfg = lambda: EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=128, num_blocks=64, dtype="bf16",
+                               backend="kernels", use_cuda_graph=True)
+    dev = torch.device("cuda", 0)
+    prompt = [5, 9, 2, 7, 1, 3]
+    sp = SamplingParams(max_new_tokens=12, temperature=0.9, top_k=40, top_p=0.95, repeat_penalty=1.2, seed=77)
+    eng = LLMEngine(m, cfg(), device=dev)
+    assert eng.device_sampling
+    alone = eng.generate([prompt], sp)[0]
+    assert any(k[2] for k in eng._graphs), "the non-greedy step must have been captured as a graph"
+    eng2 = LLMEngine(m, cfg(), device=dev)
+    others = SamplingParams(max_new_tokens=12, temperature=1.1, seed=3)
+    ids = [eng2.add_request([4, 4, 8], others), eng2.add_request(prompt, sp), eng2.add_request([1, 2, 3, 4, 5, 6, 7], others)]
+    while eng2.has_unfinished():
+        eng2.step()
+    assert eng2.requests[ids[1]].output_tokens == alone
+    greedy = LLMEngine(m, cfg(), device=dev).generate([prompt], SamplingParams(max_new_tokens=12))[0]
+    k1 = LLMEngine(m, cfg(), device=dev).generate([prompt], SamplingParams(max_new_tokens=12, temperature=0.8, top_k=1, seed=1))[0]
+    assert k1 == greedy
+    assert len(set(map(tuple, [alone, greedy]))) >= 1 and all(0 <= t < 512 for t in alone)

@@ -457,3 +457,70 @@ def test_fused_elementwise_chain(K, dtype):
     assert K.fused_elementwise_plan(x[:, :100], ["Relu"], [None]) is None              # not contiguous
     assert K.fused_elementwise_plan(x, ["Add"], [_rand(512, 1, dtype=dtype)]) is None   # broadcast along the rows
     assert K.fused_elementwise_plan(x, ["Erf"], [None]) is None
+
+
+def _sample_setup(K, rows, temperature=1.0, top_k=0, top_p=1.0, penalty=1.0, seed=7, recent=None):
+    buf = bytearray(rows * K.SAMPLE_RECORD_BYTES)
+    for r in range(rows):
+        K.pack_sample_params(buf, r, temperature, top_k, top_p, penalty, seed + r, 0 if recent is None else len(recent[r]))
+    params = torch.frombuffer(buf, dtype=torch.uint8).cuda()
+    rec = None
+    if recent is not None:
+        R = max(len(x) for x in recent)
+        rec = torch.full((rows, R), -1, dtype=torch.int32)
+        for r, x in enumerate(recent):
+            rec[r, :len(x)] = torch.tensor(x, dtype=torch.int32)
+        rec = rec.cuda()
+    return params, rec, torch.zeros(rows, dtype=torch.int64, device="cuda")
+
+
+def test_device_sampler_limits_match_argmax(K):
+    logits = torch.randn(64, 50257, device="cuda")
+    want = logits.argmax(-1).int()
+    for kw in (dict(temperature=0.0), dict(top_k=1), dict(top_p=1e-6), dict(temperature=1e-4)):
+        params, rec, ctr = _sample_setup(K, 64, **kw)
+        got = K.sample(logits.clone(), params, rec, ctr)
+        assert torch.equal(got, want), kw
+
+
+def test_device_sampler_distribution_top_k_top_p_and_penalty(K):
+    """Empirical token frequencies of 20 000 draws per setting against the probabilities the pipeline defines
+    (penalty -> temperature -> top-k -> softmax -> top-p, computed in fp32 with torch)."""
+    V, draws = 50, 20000
+    base = torch.tensor([3.0, 2.5, 2.5, 2.0, 1.0, 0.5, 0.0, -0.5, -1.0, -3.0] + [-4.0 - 0.1 * i for i in range(V - 10)], device="cuda")
+
+    def expected(temperature, top_k, top_p, penalty, recent):
+        l = base.clone()
+        if penalty != 1.0:
+            idx = torch.tensor(sorted(set(recent)), device="cuda")
+            l[idx] = torch.where(l[idx] > 0, l[idx] / penalty, l[idx] * penalty)
+        l = l / temperature
+        if top_k:
+            kth = torch.topk(l, top_k).values[-1]
+            l = torch.where(l < kth, torch.full_like(l, float("-inf")), l)
+        p = torch.softmax(l, -1)
+        if top_p < 1.0:
+            sp, si = torch.sort(p, descending=True)
+            drop = torch.cumsum(sp, 0) - sp > top_p
+            sp = torch.where(drop, torch.zeros_like(sp), sp)
+            p = torch.zeros_like(p).scatter_(0, si, sp)
+            p = p / p.sum()
+        return p
+
+    for (t, k, pp, pen, rec) in [(1.0, 0, 1.0, 1.0, None), (0.7, 5, 1.0, 1.0, None), (1.3, 0, 0.8, 1.0, None),
+                                 (1.0, 8, 0.9, 1.5, [0, 0, 3, 7])]:
+        logits = base[None, :].repeat(draws, 1).contiguous()
+        params, recent, ctr = _sample_setup(K, draws, t, k, pp, pen, seed=1234, recent=None if rec is None else [rec] * draws)
+        tok = K.sample(logits, params, recent, ctr)
+        freq = torch.bincount(tok.long(), minlength=V).float() / draws
+        exp = expected(t, k, pp, pen, rec or [])
+        assert float((freq[exp == 0]).sum()) == 0.0, (t, k, pp)            # nothing outside the kept set is ever drawn
+        assert float((freq - exp).abs().max()) < 0.015, (t, k, pp, (freq - exp).abs().max())
+    # the draw counter advances: a second call with the same seeds gives other tokens, the same counters the same tokens
+    logits = base[None, :].repeat(256, 1).contiguous()
+    params, _, ctr = _sample_setup(K, 256, 1.0)
+    a = K.sample(logits.clone(), params, None, ctr)
+    b = K.sample(logits.clone(), params, None, ctr)
+    ctr.zero_()
+    c = K.sample(logits.clone(), params, None, ctr)
+    assert torch.equal(a, c) and not torch.equal(a, b)
