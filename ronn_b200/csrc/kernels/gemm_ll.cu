@@ -9,7 +9,9 @@
 //
 //   phase A  the GEMM epilogue (tcgen05 accumulators from TMEM) stores each partial row, as {data, sequence} words,
 //            into the receive area of the rank that OWNS the row (rank r owns rows [r M / W, (r + 1) M / W)): each
-//            rank sends (W - 1) / W of one result instead of W - 1 whole copies
+//            rank sends (W - 1) / W of one result instead of W - 1 whole copies.  A rank may cut its K range into S
+//            slices (S W <= 8): every (rank, slice) pair is then one source, the K chain of a CTA is S times shorter
+//            and S times as many CTAs stream the weights
 //   phase B  the owner polls its receive area, sums the W partials in rank order, adds bias and residual, and stores
 //            the finished row of X, again as {data, sequence} words, into every rank's result area: one multimem.st
 //            per 16 bytes through the NVSwitch (NVLS), or W peer stores
@@ -56,6 +58,7 @@ struct LLArgs {
   float eps;
   int M, N, rank, world, owner_rows, row_begin, row_end;
   int norm_mode, nvls, wpr;
+  int S, kb_per, num_kb;                 // K slices per rank: every (rank, slice) pair is one source of phase A
 };
 
 template <int BN, class T>
@@ -68,12 +71,14 @@ struct LLProblem {
   mutable uint32_t seq;                          // 0 = not resolved yet (sequence numbers start at 1)
   mutable size_t parity_off;
 
-  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles; }
+  __device__ __forceinline__ int num_tiles() const { return m_tiles * n_tiles * a->S; }
   __device__ __forceinline__ void tile(int t, int& m0, int& n0, int& kb0, int& nkb) const {
-    m0 = (t % m_tiles) * PG_BM;
-    n0 = (t / m_tiles) * BN;
-    kb0 = 0;
-    nkb = num_kb;
+    const int per_z = m_tiles * n_tiles;
+    const int z = t / per_z, r = t - z * per_z;
+    m0 = (r % m_tiles) * PG_BM;
+    n0 = (r / m_tiles) * BN;
+    kb0 = z * a->kb_per;
+    nkb = min(a->kb_per, a->num_kb - kb0);
   }
   __device__ __forceinline__ void load_a(uint8_t* smem, uint64_t* bar, int k_elem, int m0) const {
     tma_load_2d(smem, map_a, bar, k_elem, m0);
@@ -82,7 +87,7 @@ struct LLProblem {
     tma_load_2d(smem, map_b, bar, k_elem, n0);
   }
   // phase A: 32 rows x 32 columns of fp32 accumulators -> 16-bit pairs -> {data, sequence} words in the owners' areas
-  __device__ __forceinline__ void epilogue(int, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
+  __device__ __forceinline__ void epilogue(int t, int m0, int n0, int row, int col, uint32_t (&r)[32], uint8_t* stage) const {
     if (seq == 0u) {
       const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(a->state) / LL_UNIT;
       seq = uint32_t(epoch) + 1u;
@@ -106,6 +111,7 @@ struct LLProblem {
     __syncwarp();
     // lane l sends 16-byte piece (l % 4) of rows (l / 4) + 8 i: four lanes cover 128 contiguous bytes of a row's words
     const int base_row = gm - lane, piece = lane & 3;
+    const int src = a->rank * a->S + t / (m_tiles * n_tiles);        // (rank, K slice) -> source slot
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int rr = (lane >> 2) + 8 * i;
@@ -115,7 +121,7 @@ struct LLProblem {
         const int lrow = grow - owner * a->owner_rows;
         const Vec8 pk = *reinterpret_cast<const Vec8*>(stage + rr * 80 + piece * 16);
         uint8_t* dst = a->scatter_peer[owner] + parity_off +
-                       ((size_t(a->rank) * a->owner_rows + lrow) * N + gn + piece * 8) * 4;
+                       ((size_t(src) * a->owner_rows + lrow) * N + gn + piece * 8) * 4;
         st_volatile_u4(dst, pk.w[0], seq, pk.w[1], seq);
         st_volatile_u4(dst + 16, pk.w[2], seq, pk.w[3], seq);
       }
@@ -157,6 +163,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
     const int R = a.row_end - a.row_begin;
     const int segs = (n8 + 31) / 32;
     const int units = R * segs;
+    const int nsrc = a.world * a.S;               // at most LL_MAX_RANKS (checked by the launcher)
     for (int u = int(blockIdx.x) + G * warp; u < units; u += G * (PG_THREADS / 32)) {
       const int r = u / segs, c8 = (u - r * segs) * 32 + lane;
       if (c8 >= n8) continue;
@@ -171,7 +178,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
         ready = true;
 #pragma unroll
         for (int src = 0; src < LL_MAX_RANKS; ++src)
-          if (src < a.world)
+          if (src < nsrc)
             ready = ll_load8(a.scatter_local + pa + ((size_t(src) * a.owner_rows + r) * N + c8 * 8) * 4, seq, pk[src]) && ready;
         if (!ready && (++polls & 63u) == 0u && globaltimer_ns() > deadline) {
           if (status) atomicCAS(status, 0u, uint32_t(STATUS_WAIT_PEER));
@@ -183,7 +190,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
       for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll
       for (int src = 0; src < LL_MAX_RANKS; ++src)
-        if (src < a.world) {
+        if (src < nsrc) {
           float f[8];
           unpack8<T>(pk[src], f);
 #pragma unroll
@@ -323,7 +330,7 @@ gemm_ll_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   prob.a = &args;
   prob.m_tiles = (args.M + PG_BM - 1) / PG_BM;
   prob.n_tiles = (args.N + BN - 1) / BN;
-  prob.num_kb = (K + 63) / 64;
+  prob.num_kb = args.num_kb;
   prob.seq = 0u;
   prob.parity_off = 0;
   gemm_persistent<BN, STAGES, 0, LLProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
@@ -347,7 +354,7 @@ static int ll_launch(const CUtensorMap& ma, const CUtensorMap& mb, LLArgs& a, in
     return -12;
   if (per_sm > 2) per_sm = 2;
   if (512u / L::TMEM_COLS < unsigned(per_sm)) per_sm = int(512u / L::TMEM_COLS);
-  const int tiles = ((a.N + BN - 1) / BN) * ((a.M + PG_BM - 1) / PG_BM);
+  const int tiles = ((a.N + BN - 1) / BN) * ((a.M + PG_BM - 1) / PG_BM) * a.S;
   const int resident = ll_sm_count() * per_sm;
   const int grid = tiles < resident ? tiles : resident;
   // warps per row of phase C: a lane keeps at most 4 chunks of 8 values; more warps when rows alone leave the grid idle
@@ -377,7 +384,13 @@ extern "C" int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStr
   for (int r = 0; r < world; ++r)
     if (!p->scatter_area[r] || !p->result_area[r]) return -6;
   if (p->nvls && !p->result_mc) return -7;
-  if (p->scatter_parity_stride < long(world) * owner_rows * N * 4 || p->result_parity_stride < long(M) * N * 4) return -8;
+  const int num_kb = (K + 63) / 64;
+  int S = p->splitk < 1 ? 1 : p->splitk;
+  if (S > num_kb) S = num_kb;
+  while (S > 1 && S * world > LL_MAX_RANKS) --S;
+  const int kb_per = (num_kb + S - 1) / S;
+  S = (num_kb + kb_per - 1) / kb_per;              // every slice non-empty
+  if (p->scatter_parity_stride < long(world) * S * owner_rows * N * 4 || p->result_parity_stride < long(M) * N * 4) return -8;
 
   LLArgs a;
   for (int r = 0; r < LL_MAX_RANKS; ++r) {
@@ -411,12 +424,15 @@ extern "C" int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStr
   a.norm_mode = p->norm_mode;
   a.nvls = p->nvls ? 1 : 0;
   a.wpr = 1;
+  a.S = S;
+  a.kb_per = kb_per;
+  a.num_kb = num_kb;
 
   int bn = p->bn;
   const int m_tiles = (M + PG_BM - 1) / PG_BM;
   if (bn == 0) {
     bn = 128;
-    while (bn > 32 && m_tiles * ((N + bn - 1) / bn) < 96) bn >>= 1;
+    while (bn > 32 && m_tiles * ((N + bn - 1) / bn) * S < 96) bn >>= 1;
   }
   CUtensorMap ma, mb;
   int rc = make_tmap_2d(&ma, p->A, uint64_t(M), uint64_t(K), uint64_t(p->lda), PG_BM, 64, 2);

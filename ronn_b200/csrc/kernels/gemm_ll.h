@@ -18,9 +18,10 @@ typedef struct RonnGemmLLParams {
   const void* W;                 // [N, K] weights of this rank's K shard, row stride ldw
   int M, N, K, lda, ldw;         // N % 32 == 0
   int bn;                        // 0 = auto, else 32 | 64 | 128
+  int splitk;                    // K slices per rank (clamped so that slices x world <= 8 and no slice is empty)
   int dtype;                     // 0 bf16, 1 fp16
   void* scatter_area[RONN_LL_MAX_RANKS];
-  long scatter_parity_stride;    // bytes per parity: >= world * ceil(M / world) * N * 4
+  long scatter_parity_stride;    // bytes per parity: >= world * slices * ceil(M / world) * N * 4
   void* result_area[RONN_LL_MAX_RANKS];
   void* result_mc;
   long result_parity_stride;     // bytes per parity: >= M * N * 4

@@ -40,7 +40,7 @@ class LLParams(C.Structure):
     _fields_ = [
         ("A", C.c_void_p), ("W", C.c_void_p),
         ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("lda", C.c_int), ("ldw", C.c_int),
-        ("bn", C.c_int), ("dtype", C.c_int),
+        ("bn", C.c_int), ("splitk", C.c_int), ("dtype", C.c_int),
         ("scatter_area", C.c_void_p * MAX_RANKS), ("scatter_parity_stride", C.c_long),
         ("result_area", C.c_void_p * MAX_RANKS), ("result_mc", C.c_void_p), ("result_parity_stride", C.c_long),
         ("state", C.c_void_p), ("rank", C.c_int), ("world", C.c_int), ("nvls", C.c_int),

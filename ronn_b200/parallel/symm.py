@@ -135,7 +135,7 @@ class FusedComm(TPComm):
         # values of 4 bytes (a 16-bit value and its half of the sequence word)
         self.ll_elems = min(int(os.environ.get("RONN_LL_ELEMS", 1 << 20)), self.max_elems)
         self._ll_cols = 8192
-        self._ll_scatter_stride = (self.ll_elems + self.world * self._ll_cols) * 4
+        self._ll_scatter_stride = (self.ll_elems * max(1, MAX_RANKS // max(self.world, 1)) + MAX_RANKS * self._ll_cols) * 4
         self._ll_result_stride = self.ll_elems * 4
         self._ll_off = self._flag_bytes + 2 * self.parity_floats * 4 + 4 * self._out_bytes
         total = self._ll_off + 2 * self._ll_scatter_stride + 2 * self._ll_result_stride
@@ -249,6 +249,14 @@ class FusedComm(TPComm):
         return (self.world > 1 and M * N <= self.ll_elems and N % 32 == 0 and N <= self._ll_cols
                 and -(-M // self.world) * self.world * N * 4 <= self._ll_scatter_stride)
 
+    def _ll_splitk(self, M: int, N: int, Kd: int) -> int:
+        """K slices per rank: at least eight 64-wide K blocks per slice, at most 8 (rank, slice) sources in all."""
+        env = os.environ.get("RONN_LL_SPLITK")
+        s = int(env) if env else max(1, min(MAX_RANKS // self.world, ((Kd + 63) // 64) // 8))
+        while s > 1 and -(-M // self.world) * self.world * s * N * 4 > self._ll_scatter_stride:
+            s -= 1
+        return s
+
     def _gemm_ll(self, a, w_nk, bias, residual, norm, bn: int = 0):
         from ..ops import fuse as F
         M, Kd = a.shape
@@ -261,7 +269,7 @@ class FusedComm(TPComm):
         p = F.LLParams()
         p.A, p.W = a.data_ptr(), w_nk.data_ptr()
         p.M, p.N, p.K, p.lda, p.ldw = M, N, Kd, a.stride(0), w_nk.stride(0)
-        p.bn, p.dtype = bn, 0 if a.dtype == torch.bfloat16 else 1
+        p.bn, p.dtype, p.splitk = bn, 0 if a.dtype == torch.bfloat16 else 1, self._ll_splitk(M, N, Kd)
         res_off = self._ll_off + 2 * self._ll_scatter_stride
         for r in range(self.world):
             p.scatter_area[r] = self._ptrs2[r] + self._ll_off
