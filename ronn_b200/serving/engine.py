@@ -51,7 +51,8 @@ class LLMEngine:
         """``model`` is a ``ronn_b200.Model`` (or anything with ``.graph``) holding a decoder architecture."""
         self.cfg = config or EngineConfig()
         graph = model.graph
-        self.arch = DecoderArch.from_metadata(graph.metadata)
+        from .graph_match import decoder_from_graph
+        self.arch, weights = decoder_from_graph(graph)     # in-tree metadata, or the decoder recognised in the operators
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
         self.device = torch.device(device)
@@ -62,7 +63,7 @@ class LLMEngine:
         self.comm = comm or NoComm()
         if self.cfg.max_model_len > self.arch.max_pos and self.arch.rope_base == 0:
             self.cfg.max_model_len = self.arch.max_pos
-        self.runner = DecoderRunner(self.arch, graph.initializers, self.cfg, self.device, self.comm)
+        self.runner = DecoderRunner(self.arch, weights, self.cfg, self.device, self.comm)
         self.max_blocks = self.runner.max_blocks_per_seq
         self.sched = Scheduler(self.cfg.block_size, self.runner.num_blocks, self.cfg.max_num_seqs,
                                self.cfg.max_batch_tokens, self.cfg.prefill_chunk, self.cfg.policy,

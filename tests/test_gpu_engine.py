@@ -117,3 +117,41 @@ def test_non_greedy_decode_replays_a_cuda_graph_and_is_reproducible():
     k1 = LLMEngine(m, cfg(), device=dev).generate([prompt], SamplingParams(max_new_tokens=12, temperature=0.8, top_k=1, seed=1))[0]
     assert k1 == greedy
     assert len(set(map(tuple, [alone, greedy]))) >= 1 and all(0 <= t < 512 for t in alone)
+
+
+def test_engine_logits_match_an_fp32_reference_of_the_graph():
+    """Not token agreement: the kernel backend's logits (prefill over paged KV, then a decode step on the cache it
+    filled) against fp32 logits of the same ONNX graph computed by the CPU session, within bf16 rounding."""
+    from ronn_b200 import SessionOptions
+    from ronn_b200.api.model import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    cfg = GPT2Config.tiny(n_layer=3, n_embd=256, n_head=4, vocab_size=1000, n_positions=256)
+    g32 = build_gpt2(cfg, dtype=torch.float32, seed=5)
+    ref = Model.from_graph(g32).create_session(SessionOptions().with_optimization_level("O0"))
+    model = Model.from_graph(build_gpt2(cfg, dtype=torch.bfloat16, seed=5))
+    eng = _engine(model, "kernels", graph=False)
+    r = eng.runner
+    gen = torch.Generator().manual_seed(2)
+    for T in (37, 128):
+        seq = torch.randint(0, 1000, (T + 1,), generator=gen)
+        want = ref.run({"input_ids": seq[None, :]})["logits"][0]                    # [T + 1, vocab], fp32
+        dev = torch.device("cuda", 0)
+        nblk = (T + 1 + 15) // 16
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        blocks = list(range(40, 40 + nblk))
+        slots = [blocks[p // 16] * 16 + p % 16 for p in range(T + 1)]
+        b = {"token_ids": seq[:T].to(dev, torch.int32), "positions": torch.arange(T, dtype=torch.int32, device=dev),
+             "slot_mapping": i32(slots[:T]), "token_item": torch.zeros(T, dtype=torch.int32, device=dev),
+             "ctx_per_token": torch.arange(1, T + 1, dtype=torch.int32, device=dev), "seq_lens": i32([T]),
+             "sample_index_clamped": torch.arange(T, dtype=torch.int32, device=dev),
+             "block_tables": i32([blocks + [0] * (r.max_blocks_per_seq - nblk)])}
+        got = r.forward(b, False, T, T, want_logits=True)[:, :1000].float().cpu()
+        scale = float(want.abs().max())
+        assert float((got - want[:T]).abs().max()) < 0.04 * scale, (T, float((got - want[:T]).abs().max()), scale)
+        # one decode step on top of the cache the prefill wrote
+        d = {"token_ids": seq[T:T + 1].to(dev, torch.int32), "positions": i32([T]), "slot_mapping": i32([slots[T]]),
+             "token_item": i32([0]), "ctx_per_token": i32([T + 1]), "seq_lens": i32([T + 1]), "sample_index_clamped": i32([0]),
+             "block_tables": b["block_tables"]}
+        got1 = r.forward(d, True, 1, 1, want_logits=True)[:, :1000].float().cpu()
+        assert float((got1[0] - want[T]).abs().max()) < 0.04 * scale
+        assert int(got1[0].argmax()) == int(want[T].argmax()) or float(want[T].topk(2).values.diff().abs()) < 0.04 * scale

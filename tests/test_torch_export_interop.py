@@ -341,3 +341,80 @@ def test_masked_encoder_with_two_inputs(opset):
         ids2[1, 5:] = 7
         again = sess.run({"input_ids": ids2, "attention_mask": mask})["last_hidden_state"]
         torch.testing.assert_close(again[1, :5], got[1, :5], atol=2e-5, rtol=1e-5)
+
+
+class ExportedGPT2(nn.Module):
+    """GPT-2 the way the Hugging Face implementation computes it (Conv1D projections as x @ W + b with W [in, out],
+    heads split with view + permute, causal mask from a tril buffer, gelu_new written out), small enough to export."""
+
+    def __init__(self, vocab=211, n_pos=64, d=64, n_head=4, n_layer=2):
+        super().__init__()
+        self.d, self.h = d, n_head
+        self.wte, self.wpe = nn.Embedding(vocab, d), nn.Embedding(n_pos, d)
+        mk = lambda i, o: (nn.Parameter(torch.randn(i, o) * 0.08), nn.Parameter(torch.randn(o) * 0.02))
+        self.blocks = nn.ModuleList()
+        for _ in range(n_layer):
+            b = nn.Module()
+            b.ln_1, b.ln_2 = nn.LayerNorm(d), nn.LayerNorm(d)
+            b.attn_w, b.attn_b = mk(d, 3 * d)
+            b.proj_w, b.proj_b = mk(d, d)
+            b.fc_w, b.fc_b = mk(d, 4 * d)
+            b.out_w, b.out_b = mk(4 * d, d)
+            self.blocks.append(b)
+        self.ln_f = nn.LayerNorm(d)
+        self.register_buffer("tril", torch.tril(torch.ones(n_pos, n_pos, dtype=torch.bool)).view(1, 1, n_pos, n_pos))
+
+    def forward(self, input_ids):
+        B, T = input_ids.shape
+        pos = torch.arange(T, device=input_ids.device).unsqueeze(0)
+        x = self.wte(input_ids) + self.wpe(pos)
+        for b in self.blocks:
+            qkv = torch.addmm(b.attn_b, b.ln_1(x).view(-1, self.d), b.attn_w).view(B, T, 3 * self.d)
+            q, k, v = qkv.split(self.d, dim=2)
+            heads = lambda t: t.view(B, T, self.h, self.d // self.h).permute(0, 2, 1, 3)
+            w = torch.matmul(heads(q), heads(k).transpose(-1, -2)) / float(self.d // self.h) ** 0.5
+            w = torch.where(self.tril[:, :, :T, :T], w, torch.full_like(w, -1e9))
+            a = torch.matmul(torch.softmax(w, dim=-1), heads(v)).permute(0, 2, 1, 3).contiguous().view(B, T, self.d)
+            x = x + torch.addmm(b.proj_b, a.view(-1, self.d), b.proj_w).view(B, T, self.d)
+            hdn = torch.addmm(b.fc_b, b.ln_2(x).view(-1, self.d), b.fc_w)
+            hdn = 0.5 * hdn * (1.0 + torch.tanh(0.7978845608028654 * (hdn + 0.044715 * torch.pow(hdn, 3.0))))
+            x = x + torch.addmm(b.out_b, hdn, b.out_w).view(B, T, self.d)
+        return self.ln_f(x)
+
+
+@pytest.mark.parametrize("opset", [13, 17])
+def test_exporter_written_gpt2_is_served_by_the_engine_with_matching_logits(opset):
+    """A decoder that carries no in-tree metadata and exporter-chosen names is recognised from its operators; the
+    engine's logits (paged KV, prefill then decode) equal the session's logits of the same graph at fp32 tolerance."""
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    from ronn_b200.serving.graph_match import decoder_from_graph
+    torch.manual_seed(3)
+    module = ExportedGPT2().eval()
+    ids = torch.randint(0, 211, (2, 7))
+    model = Model.from_bytes(_export(module, ids, dynamic_axes={0: "batch", 1: "sequence"}, opset=opset))
+    assert "ronn.arch" not in model.graph.metadata
+    arch, init = decoder_from_graph(model.graph)
+    assert (arch.n_layer, arch.hidden, arch.n_head, arch.ffn, arch.vocab, arch.max_pos) == (2, 64, 4, 256, 211, 64)
+    torch.testing.assert_close(init["h.1.mlp.c_fc.weight"], module.blocks[1].fc_w.detach())
+    sess = model.create_session(SessionOptions().with_optimization_level("O0"))
+    eng = LLMEngine(model, EngineConfig(max_num_seqs=4, max_batch_tokens=64, max_model_len=64, num_blocks=32, dtype="fp32",
+                                        backend="torch"), device="cpu")
+    prompt = [5, 17, 200, 3, 3, 9]
+    generated = eng.generate([prompt], SamplingParams(max_new_tokens=5))[0]
+    # teacher forcing through the session: the token the engine chose at every step is the arg max of the session's
+    # logits, and the runner's logits for the whole sequence equal the session's
+    seq = prompt + generated
+    hidden = sess.run({"x": torch.tensor([seq[:-1]])})["y"][0]
+    logits = hidden @ module.wte.weight.detach().t()
+    assert logits[len(prompt) - 1:].argmax(-1).tolist() == generated
+    runner = eng.runner
+    T = len(seq) - 1
+    b = {"token_ids": torch.tensor(seq[:-1], dtype=torch.int32), "positions": torch.arange(T, dtype=torch.int32),
+         "slot_mapping": torch.arange(T, dtype=torch.int32) + 16 * 20, "token_item": torch.zeros(T, dtype=torch.int32),
+         "ctx_per_token": torch.arange(1, T + 1, dtype=torch.int32), "seq_lens": torch.tensor([T], dtype=torch.int32),
+         "sample_index_clamped": torch.arange(T, dtype=torch.int32),
+         "block_tables": torch.tensor([[20, 21, 22, 23]], dtype=torch.int32)}
+    mine = runner.forward(b, False, T, T, want_logits=True)
+    torch.testing.assert_close(mine[:, :211], logits, atol=2e-4, rtol=2e-4)
+    with pytest.raises(Exception, match="four linear layers|not a decoder|position"):
+        decoder_from_graph(Model.from_bytes(_export(Block().eval(), torch.randint(0, 50, (2, 6)))).graph)
