@@ -47,9 +47,11 @@ _NP_VIEW = {DataType.F32: np.float32, DataType.U8: np.uint8, DataType.I8: np.int
 
 def tensor_from_bytes(buf, dt: DataType, shape) -> torch.Tensor:
     """Build a torch tensor (own copy) from little-endian bytes."""
-    count = int(np.prod(shape)) if len(shape) else 1
+    count = 1
+    for d in shape:                 # Python integers: a declared shape may overflow 64 bits
+        count *= int(d)
     need = count * dt.itemsize
-    if len(buf) < need:
+    if count < 0 or len(buf) < need:
         raise TypeConversionError(f"tensor payload has {len(buf)} bytes, shape {list(shape)} of {dt.name} needs {need}")
     arr = np.frombuffer(buf, dtype=_NP_VIEW[dt], count=count).copy()
     t = torch.from_numpy(arr)

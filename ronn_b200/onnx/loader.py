@@ -157,12 +157,18 @@ def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir) -> 
         return tensor_from_bytes(raw, dt, dims)
     if td["raw_off"] >= 0:
         raw = data[td["raw_off"]: td["raw_off"] + td["raw_len"]]
+        need = dt.itemsize
+        for d in dims:
+            need *= int(d)
+        if td["raw_len"] != need:
+            raise TypeConversionError(f"tensor '{_fix_str(td['name'])}': raw_data holds {td['raw_len']} bytes, shape "
+                                      f"{list(dims)} of {dt.name} needs {need}")
         return tensor_from_bytes(raw, dt, dims)
     if td["blob"] >= 0:
         return tensor_from_bytes(blobs[td["blob"]], dt, dims)
-    count = int(np.prod(dims)) if dims else 1
-    if count == 0 or not dims and td["blob"] < 0 and count == 1 and False:
-        return torch.zeros(dims, dtype=dt.torch)
+    count = 1
+    for d in dims:
+        count *= int(d)
     if count == 0:
         return torch.zeros(dims, dtype=dt.torch)
     raise TypeConversionError(f"tensor '{_fix_str(td['name'])}' carries no data for {count} elements")
