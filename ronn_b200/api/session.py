@@ -107,6 +107,8 @@ class SessionBuilder:
         opts = self.options
         graph: ModelGraph = self.model.graph.clone()
         opt_stats = Optimizer(opts.optimization_level, opts.provider_type).optimize(graph)
+        if opts.tp_size > 1:
+            self._shard_for_tensor_parallel(graph, opts.tp_size)
         if opts.provider_instance is not None:
             registry = create_provider_system()
             if registry.get_provider(opts.provider_type) is not None:
@@ -136,6 +138,24 @@ class SessionBuilder:
             from ..hrm.session_router import attach_router
             attach_router(sess)
         return sess
+
+
+def _shard_for_tensor_parallel(graph: ModelGraph, tp_size: int) -> None:
+    """``tp_size > 1``: every rank of the default process group builds the same session and keeps its shard of the
+    weights (``graph/passes/tensor_parallel.py``); the group must already exist and have ``tp_size`` ranks."""
+    import torch.distributed as dist
+    from ..graph.passes.tensor_parallel import TensorParallelPass
+    if not (dist.is_available() and dist.is_initialized()):
+        raise SessionError(f"tp_size={tp_size} needs an initialised torch.distributed process group (one process per "
+                           "GPU, e.g. under torchrun)")
+    if dist.get_world_size() != tp_size:
+        raise SessionError(f"tp_size={tp_size} does not match the process group's world size {dist.get_world_size()}")
+    from ..graph.passes.fusion import NodeFusionPass
+    NodeFusionPass().run(graph)          # MatMul + Add pairs and Q / K / V projections in their fused form, at any level
+    TensorParallelPass(dist.get_rank(), tp_size).run(graph)
+
+
+SessionBuilder._shard_for_tensor_parallel = staticmethod(_shard_for_tensor_parallel)
 
 
 def _to_tensor(v, device, name: str) -> torch.Tensor:

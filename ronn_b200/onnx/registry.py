@@ -714,6 +714,18 @@ def _fused_elementwise(i, a, c):
     return [x]
 
 
+@op("AllReduce", 1, domain="com.ronn")
+def _all_reduce(i, a, c):
+    """Sum over the ranks of the session's process group (inserted by the tensor-parallel pass); the identity in a
+    single-process session."""
+    import torch.distributed as dist
+    x = i[0]
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        x = x.contiguous().clone()
+        dist.all_reduce(x)
+    return [x]
+
+
 @op("SiLU", 1, domain="com.ronn")
 def _silu(i, a, c):
     return [F.silu(i[0])]

@@ -97,3 +97,26 @@ def test_space_to_depth_stem_weights_reproduce_the_7x7_stride2_convolution():
     w2 = stem_weights_s2d(w)
     out = F.conv2d(F.pad(x2.permute(0, 3, 1, 2), (2, 1, 2, 1)), w2.permute(0, 3, 1, 2))
     torch.testing.assert_close(out, ref, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_session_level_tensor_parallelism_on_cpu_ranks(tmp_path, world):
+    """SessionOptions.tp_size: every rank holds 1 / world of the projection weights, AllReduce nodes sum the partial
+    results, and the output equals the unsharded session's."""
+    out = tmp_path / "r.json"
+    p = launch(world, "tp_session_worker.py", [str(out)], 29630 + world)
+    assert p.returncode == 0, p.stderr[-3000:]
+    for rank, r in enumerate(json.loads(out.read_text())):
+        for lvl in ("O0", "O3"):
+            assert r[lvl]["err"] < 1e-4, r
+            assert r[lvl]["all_reduce_nodes"] == 4 and r[lvl]["tp"] == f"{rank}/{world}"      # 2 layers x (attention, MLP)
+            assert abs(r[lvl]["weight_fraction"] - 1.0 / world) < 0.08, r       # the position table stays replicated
+        assert r["odd"]["err"] < 1e-5 and r["odd"]["all_reduce_nodes"] == 0
+
+
+def test_tp_size_without_a_process_group_is_an_error():
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.api.errors import SessionError
+    from ronn_b200.models.mlp784 import build_mlp784
+    with pytest.raises(SessionError, match="process group"):
+        Model.from_graph(build_mlp784()).create_session(SessionOptions().with_tp_size(2))
