@@ -8,10 +8,10 @@ crates/ronn-providers/src/compiler.rs:267-314):
       W' = W * gamma / sqrt(var + eps),  b' = (b - mean) * gamma / sqrt(var + eps) + beta
 * Conv [-> Add(residual)] -> Relu       => com.ronn::FusedConv(activation, optional 4th input)
 * MatMul -> Add(constant bias)          => com.ronn::FusedGemm
-* Gemm / FusedGemm -> Relu | Gelu       => FusedGemm(activation)
+* Gemm / FusedGemm -> Relu | Gelu(tanh) => FusedGemm(activation)
 * FusedGemm -> Add(residual)            => FusedGemm with 4th input
-* Add -> LayerNormalization             => com.ronn::SkipLayerNorm (when the sum is used only by the norm
-                                           and, at most, one more residual consumer)
+* Add -> LayerNormalization             => com.ronn::SkipLayerNorm(x, skip, gamma, beta) -> (normed, sum): the sum
+                                           stays available to its other consumers (the next residual add)
 * ReduceMean, Sub, Pow, ReduceMean, Add(eps), Sqrt, Div, Mul(gamma), Add(beta)
                                         => LayerNormalization: the nine-node form exporters write below opset 17
                                            (the reference's own export scripts use opset 13)
@@ -40,7 +40,7 @@ class NodeFusionPass(OptimizationPass):
             progress = False
             for fn in (self._fold_bn, self._conv_act, self._decomposed_layernorm, self._erf_gelu, self._matmul_bias,
                        self._gemm_act,
-                       self._gemm_residual, self._qkv_projection):
+                       self._gemm_residual, self._qkv_projection, self._skip_layernorm):
                 n = fn(graph)
                 if n:
                     stats.nodes_fused += n
@@ -330,6 +330,29 @@ class NodeFusionPass(OptimizationPass):
             return 2
         return 0
 
+    def _skip_layernorm(self, graph: ModelGraph) -> int:
+        """Add(x, skip) -> LayerNormalization over the last axis: one node that produces the normalised tensor and, as
+        a second output, the sum for whoever else reads it."""
+        cons, prod = graph.consumers(), graph.producers()
+        for add in graph.nodes:
+            if add.op_type != "Add" or len(add.inputs) != 2 or any(i in graph.initializers for i in add.inputs):
+                continue
+            if add.inputs[0] == add.inputs[1]:
+                continue
+            users = cons.get(add.outputs[0], [])
+            lns = [u for u in users if u.op_type == "LayerNormalization" and u.inputs[0] == add.outputs[0]
+                   and int(u.attr("axis", -1)) == -1 and len(u.inputs) >= 2 and len(u.outputs) == 1]
+            if len(lns) != 1:
+                continue
+            ln = lns[0]
+            ln.op_type, ln.domain = "SkipLayerNorm", RONN
+            ln.inputs = [add.inputs[0], add.inputs[1]] + list(ln.inputs[1:3])
+            ln.outputs = [ln.outputs[0], add.outputs[0]]
+            ln.attributes = {"epsilon": float(ln.attr("epsilon", 1e-5))}
+            graph.remove_nodes([add.id])
+            return 1
+        return 0
+
     def _gemm_act(self, graph: ModelGraph) -> int:
         cons = graph.consumers()
         for g in graph.nodes:
@@ -341,7 +364,7 @@ class NodeFusionPass(OptimizationPass):
             act = self._single_consumer(graph, cons, g.outputs[0])
             if act is None or act.op_type not in ("Relu", "Gelu"):
                 continue
-            if act.op_type == "Gelu" and act.attr("approximate", "tanh") != "tanh":
+            if act.op_type == "Gelu" and act.attr("approximate", "none") != "tanh":
                 continue
             g.op_type, g.domain = "FusedGemm", RONN
             g.attributes = {"transB": int(g.attr("transB", 0)), "activation": act.op_type}

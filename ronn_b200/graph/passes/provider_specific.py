@@ -97,7 +97,7 @@ class GpuOptimizationPass(OptimizationPass):
     def _elementwise(n, graph) -> bool:
         if n.attributes and n.op_type != "Gelu":
             return False
-        if n.op_type == "Gelu" and n.attr("approximate", "tanh") != "tanh":
+        if n.op_type == "Gelu" and n.attr("approximate", "none") != "tanh":
             return False                      # the fused chain evaluates the tanh form; the exact (Erf) form stays a node
         if n.op_type in _UNARY and len(n.inputs) == 1:
             return True

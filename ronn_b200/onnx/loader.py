@@ -246,6 +246,10 @@ def _convert_model(doc, data, blobs, base_dir) -> LoadedModel:
         for a in nd["attributes"]:
             attrs[_fix_str(a["name"])] = _convert_attr(a, data, blobs, base_dir)
         name = _fix_str(nd["name"]) or f"node_{idx}"
+        if std is not None and std < 13 and op_type in ("Softmax", "LogSoftmax", "Hardmax") and not nd.get("domain"):
+            # before opset 13 these operators coerce their input to 2-D at `axis` (default 1)
+            attrs.setdefault("axis", 1)
+            attrs["legacy_flatten"] = 1
         graph.add_node(op_type, [_fix_str(s) for s in nd["inputs"]], [_fix_str(s) for s in nd["outputs"]],
                        attrs, name, _fix_str(nd.get("domain", "")))
     meta = {_fix_str(k): _fix_str(v) for k, v in doc.get("metadata_props", [])}

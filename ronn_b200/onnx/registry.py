@@ -143,7 +143,10 @@ _unary("Sign", torch.sign)
 
 @op("Gelu", 1)
 def _gelu(i, a, c):
-    approx = a.get("approximate", "tanh")       # the reference always uses the tanh form
+    """ONNX semantics: ``approximate`` defaults to "none" (the exact erf form).  The reference always evaluates the tanh
+    form (crates/ronn-core/src/ops/arithmetic.rs:281-296); the in-tree model builders ask for it explicitly."""
+    approx = a.get("approximate", "none")
+    approx = approx.decode() if isinstance(approx, bytes) else approx
     return [F.gelu(i[0], approximate="tanh" if approx == "tanh" else "none")]
 
 
@@ -168,14 +171,28 @@ def _hsig(i, a, c):
     return [torch.clamp(float(a.get("alpha", 0.2)) * i[0] + float(a.get("beta", 0.5)), 0.0, 1.0)]
 
 
+def _softmax_like(fn, i, a):
+    """Opset >= 13: along ``axis`` (default -1).  Below opset 13 (the loader marks such nodes ``legacy_flatten``): the
+    input is coerced to 2-D at ``axis`` (default 1) and normalised over the whole trailing block."""
+    x = i[0]
+    if int(a.get("legacy_flatten", 0)):
+        axis = int(a.get("axis", 1))
+        axis = axis + x.dim() if axis < 0 else axis
+        lead = 1
+        for d in x.shape[:axis]:
+            lead *= d
+        return [fn(x.reshape(lead, -1), dim=1).reshape(x.shape)]
+    return [fn(x, dim=int(a.get("axis", -1)))]
+
+
 @op("Softmax", 1)
 def _softmax(i, a, c):
-    return [torch.softmax(i[0], dim=int(a.get("axis", -1)))]
+    return _softmax_like(torch.softmax, i, a)
 
 
 @op("LogSoftmax", 1)
 def _log_softmax(i, a, c):
-    return [torch.log_softmax(i[0], dim=int(a.get("axis", -1)))]
+    return _softmax_like(torch.log_softmax, i, a)
 
 
 @op("Dropout", 1, 3)
@@ -338,26 +355,47 @@ def _pool_args(x, a):
     return k, strides, begin, end, bool(int(a.get("ceil_mode", 0)))
 
 
+def _pad_spatial(x, begin, end, value):
+    arg = []
+    for d in reversed(range(len(begin))):
+        arg += [begin[d], end[d]]
+    return F.pad(x, arg, value=value)
+
+
 @op("MaxPool", 1)
 def _maxpool(i, a, c):
     x = i[0]
     k, s, begin, end, ceil = _pool_args(x, a)
+    nd = len(k)
+    if x.dim() != nd + 2 or nd not in (1, 2, 3):
+        raise InvalidGraph(f"MaxPool over {nd} spatial dimensions on a {x.dim()}-D input")
     if begin != end:
-        x = F.pad(x, [begin[1], end[1], begin[0], end[0]], value=float("-inf"))
-        begin = [0, 0]
-    return [F.max_pool2d(x, k, s, begin, _ints(a.get("dilations")) or 1, ceil)]
+        x = _pad_spatial(x, begin, end, float("-inf"))
+        begin = [0] * nd
+    fn = {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nd]
+    return [fn(x, k, s, begin, _ints(a.get("dilations")) or 1, ceil)]
 
 
 @op("AveragePool", 1)
 def _avgpool(i, a, c):
     x = i[0]
     k, s, begin, end, ceil = _pool_args(x, a)
+    nd = len(k)
+    if x.dim() != nd + 2 or nd not in (1, 2, 3):
+        raise InvalidGraph(f"AveragePool over {nd} spatial dimensions on a {x.dim()}-D input")
     include = bool(int(a.get("count_include_pad", 0)))
+    fn = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nd]
     if begin != end:
-        x = F.pad(x, [begin[1], end[1], begin[0], end[0]])
-        begin = [0, 0]
-        include = True
-    return [F.avg_pool2d(x, k, s, begin, ceil, include)]
+        # asymmetric padding: pad by hand, then divide by the number of VALID elements under each window unless the
+        # operator counts the padding (sum = mean over the padded window * window size)
+        xp = _pad_spatial(x, begin, end, 0.0)
+        y = fn(xp, k, s, 0, ceil, True)
+        if include:
+            return [y]
+        ones = _pad_spatial(torch.ones((1, 1) + tuple(x.shape[2:]), dtype=x.dtype, device=x.device), begin, end, 0.0)
+        frac = fn(ones, k, s, 0, ceil, True)              # valid fraction of every window
+        return [y / frac.clamp_min(1e-12)]
+    return [fn(x, k, s, begin, ceil, include)]
 
 
 @op("GlobalAveragePool", 1)
@@ -667,14 +705,45 @@ def _tile(i, a, c):
 
 @op("Pad", 2, 4)
 def _pad(i, a, c):
+    """Modes constant / reflect / edge; ``axes`` (opset 18, 4th input) selects the padded dimensions; negative pads crop."""
     x = i[0]
     pads = _ints(i[1])
     val = i[2].item() if len(i) > 2 and i[2] is not None else 0.0
     nd = x.dim()
-    arg = []
-    for d in reversed(range(nd)):
-        arg += [pads[d], pads[d + nd]]
-    return [F.pad(x, arg, mode=a.get("mode", "constant"), value=val)]
+    axes = [ax + nd if ax < 0 else ax for ax in _ints(i[3])] if len(i) > 3 and i[3] is not None else list(range(nd))
+    if len(pads) != 2 * len(axes) or len(set(axes)) != len(axes) or any(ax < 0 or ax >= nd for ax in axes):
+        raise InvalidAttribute(f"Pad: {len(pads)} pad values for axes {axes} of a {nd}-D input")
+    begin, end = [0] * nd, [0] * nd
+    for k, ax in enumerate(axes):
+        begin[ax], end[ax] = pads[k], pads[k + len(axes)]
+    mode = a.get("mode", "constant")
+    mode = mode.decode() if isinstance(mode, bytes) else mode
+    if mode not in ("constant", "reflect", "edge"):
+        raise InvalidAttribute(f"Pad mode '{mode}' is not supported")
+    for d in range(nd):                                   # negative pads crop, in every mode
+        if begin[d] < 0 or end[d] < 0:
+            x = x.narrow(d, max(-begin[d], 0), x.shape[d] - max(-begin[d], 0) - max(-end[d], 0))
+            begin[d], end[d] = max(begin[d], 0), max(end[d], 0)
+    if mode == "constant":
+        arg = []
+        for d in reversed(range(nd)):
+            arg += [begin[d], end[d]]
+        return [F.pad(x, arg, mode="constant", value=val)]
+    # reflect / edge: gather along one dimension at a time (works for any rank, any dtype)
+    for d in range(nd):
+        if begin[d] == 0 and end[d] == 0:
+            continue
+        n = x.shape[d]
+        idx = torch.arange(-begin[d], n + end[d], device=x.device)
+        if mode == "edge":
+            idx = idx.clamp(0, n - 1)
+        else:
+            if n < 2 or begin[d] >= n or end[d] >= n:
+                raise InvalidAttribute("Pad reflect: pads must be smaller than the padded dimension")
+            idx = idx.abs()
+            idx = torch.where(idx >= n, 2 * (n - 1) - idx, idx)
+        x = x.index_select(d, idx)
+    return [x]
 
 
 # ------------------------------------------------------------------------------ com.ronn custom domain

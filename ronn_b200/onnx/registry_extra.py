@@ -166,6 +166,19 @@ def _conv_transpose(i, a, c):
     fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}.get(nd)
     if fn is None:
         raise InvalidGraph(f"ConvTranspose over {nd} spatial dimensions")
+    want = _ints(a.get("output_shape"))
+    if want:
+        # output_shape overrides output_padding: out = stride (in - 1) + output_padding + dilation (k - 1) + 1 - 2 pad
+        if len(want) != nd:
+            raise InvalidAttribute(f"ConvTranspose: output_shape has {len(want)} entries for {nd} spatial dimensions")
+        out_pad = []
+        for d in range(nd):
+            base = strides[d] * (x.shape[2 + d] - 1) + dil[d] * (w.shape[2 + d] - 1) + 1 - 2 * pads[d]
+            extra = want[d] - base
+            if extra < 0 or extra >= max(strides[d], dil[d]):
+                raise InvalidAttribute(f"ConvTranspose: output_shape {want} is not reachable with pads {pads} "
+                                       f"(dimension {d} would need output_padding {extra})")
+            out_pad.append(extra)
     return [fn(x, w, b, stride=strides, padding=pads[:nd], output_padding=out_pad, groups=group, dilation=dil)]
 
 

@@ -77,9 +77,11 @@ class GpuOpTable:
             return self._layernorm(node, fallback)
         if op == "RMSNorm":
             return self._rmsnorm(node, fallback)
+        if op == "SkipLayerNorm":
+            return self._skip_layernorm(node, fallback)
         if op == "Softmax":
             return self._softmax(node, fallback)
-        if op in _UNARY_KERNELS and (op != "Gelu" or node.attr("approximate", "tanh") == "tanh"):
+        if op in _UNARY_KERNELS and (op != "Gelu" or node.attr("approximate", "none") == "tanh"):
             return self._unary(_UNARY_KERNELS[op], fallback)
         if op in _BINARY_KERNELS:
             return self._binary(_BINARY_KERNELS[op], fallback)
@@ -144,6 +146,20 @@ class GpuOpTable:
                 return fallback(i, a, c)
             return [K.layernorm(x, i[1] if len(i) > 1 else None, i[2] if len(i) > 2 else None,
                                 float(a.get("epsilon", 1e-5)))]
+        return run
+
+    def _skip_layernorm(self, node, fallback):
+        """LayerNorm(x + skip) and the sum in one launch of the norm kernel."""
+        K = self.K
+
+        def run(i, a, c):
+            x, skip = i[0], i[1]
+            if (x.dtype not in _HALF or skip.dtype != x.dtype or x.shape != skip.shape or x.shape[-1] % 8
+                    or x.shape[-1] > 32768 or (len(i) > 4 and i[4] is not None)):
+                return fallback(i, a, c)
+            y, s = K.layernorm(x, i[2], i[3] if len(i) > 3 else None, float(a.get("epsilon", 1e-5)), residual=skip,
+                               return_sum=True)
+            return [y, s]
         return run
 
     def _rmsnorm(self, node, fallback):

@@ -125,12 +125,17 @@ def match_gpt2(graph: ModelGraph):
             raise SessionError(f"block {i}: linear layers have shapes {got}, a GPT-2 block has {want}")
 
     # ---- LayerNorms: two per block and a final one
-    lns = [n for n in order if n.op_type == "LayerNormalization"]
+    # (the fusion pass may have merged a residual add into the norm: SkipLayerNorm(x, skip, gamma, beta))
+    lns = [n for n in order if n.op_type in ("LayerNormalization", "SkipLayerNorm")]
     if len(lns) != 2 * L + 1:
         raise SessionError(f"expected {2 * L + 1} LayerNormalization nodes for {L} blocks, found {len(lns)}")
     eps = float(lns[0].attr("epsilon", 1e-5))
+
+    def ln_params(n):
+        return n.inputs[1:3] if n.op_type == "LayerNormalization" else n.inputs[2:4]
+
     for n in lns:
-        if len(n.inputs) < 3 or any(g.initializers.get(x) is None for x in n.inputs[1:3]):
+        if len(ln_params(n)) < 2 or any(g.initializers.get(x) is None for x in ln_params(n)):
             raise SessionError("LayerNormalization with non-constant scale / shift")
 
     # ---- activation and attention sanity
@@ -154,10 +159,10 @@ def match_gpt2(graph: ModelGraph):
             init[f"h.{i}.{nm}.bias"] = b if b is not None else torch.zeros(w.shape[1], dtype=w.dtype)
         for k, nm in enumerate(("ln_1", "ln_2")):
             ln = lns[2 * i + k]
-            init[f"h.{i}.{nm}.weight"] = g.initializers[ln.inputs[1]]
-            init[f"h.{i}.{nm}.bias"] = g.initializers[ln.inputs[2]]
-    init["ln_f.weight"] = g.initializers[lns[-1].inputs[1]]
-    init["ln_f.bias"] = g.initializers[lns[-1].inputs[2]]
+            init[f"h.{i}.{nm}.weight"] = g.initializers[ln_params(ln)[0]]
+            init[f"h.{i}.{nm}.bias"] = g.initializers[ln_params(ln)[1]]
+    init["ln_f.weight"] = g.initializers[ln_params(lns[-1])[0]]
+    init["ln_f.bias"] = g.initializers[ln_params(lns[-1])[1]]
     fields = {"n_layer": L, "hidden": H, "n_head": heads, "ffn": F, "vocab": V, "max_pos": int(wpe.shape[0]), "eps": eps}
     return fields, init
 

@@ -206,3 +206,86 @@ def test_integer_convolutions():
     assert q.dtype == torch.uint8 and q.shape == (1, 3, 5, 5) and (q.double() - want).abs().max() <= 1
     with pytest.raises(InvalidAttribute):
         ex("ConvInteger", [x, w], pads=[0, 1, 1, 1])
+
+
+def test_operator_semantics_follow_the_onnx_specification():
+    """Pad axes / edge / reflect / negative pads, ConvTranspose output_shape, AveragePool with asymmetric pads,
+    1-D and 3-D pooling, Softmax below opset 13."""
+    import numpy as np
+    from ronn_b200.api.errors import InvalidAttribute
+    from ronn_b200.onnx.registry import default_registry
+    R = default_registry()
+    ex = lambda op, ins, **a: R.get(op).execute(ins, a)
+    x = torch.arange(24.0).reshape(2, 3, 4)
+    # Pad: axes select the padded dimensions (opset 18); edge and reflect follow numpy's modes
+    got = ex("Pad", [x, torch.tensor([1, 2]), None, torch.tensor([-1])], mode="constant")[0]
+    assert got.shape == (2, 3, 7) and torch.equal(got[..., 1:5], x) and float(got[..., 0].abs().sum()) == 0
+    for mode, npmode in (("edge", "edge"), ("reflect", "reflect")):
+        got = ex("Pad", [x, torch.tensor([0, 1, 2, 0, 1, 1])], mode=mode)[0]
+        want = torch.from_numpy(np.pad(x.numpy(), ((0, 0), (1, 1), (2, 1)), mode=npmode))
+        assert torch.equal(got, want), mode
+    got = ex("Pad", [x, torch.tensor([0, 0, -1, 0, 0, 2])], mode="constant")[0]          # negative pad crops
+    assert got.shape == (2, 3, 5) and torch.equal(got[..., :3], x[..., 1:])
+    with pytest.raises(InvalidAttribute):
+        ex("Pad", [x, torch.tensor([1, 1])], mode="wrap")
+    with pytest.raises(InvalidAttribute):
+        ex("Pad", [x, torch.tensor([1, 1, 1])])
+    # ConvTranspose: output_shape decides the output padding
+    xi, w = torch.randn(1, 2, 5, 5), torch.randn(2, 3, 3, 3)
+    y = ex("ConvTranspose", [xi, w], strides=[2, 2], pads=[1, 1, 1, 1], output_shape=[10, 10])[0]
+    assert y.shape == (1, 3, 10, 10)
+    torch.testing.assert_close(y, torch.nn.functional.conv_transpose2d(xi, w, stride=2, padding=1, output_padding=1))
+    with pytest.raises(InvalidAttribute, match="not reachable"):
+        ex("ConvTranspose", [xi, w], strides=[2, 2], pads=[1, 1, 1, 1], output_shape=[40, 40])
+    # AveragePool, asymmetric pads: the divisor is the number of valid elements unless count_include_pad is set
+    img = torch.arange(16.0).reshape(1, 1, 4, 4)
+    y = ex("AveragePool", [img], kernel_shape=[2, 2], strides=[2, 2], pads=[0, 0, 1, 1])[0]
+    assert y.shape == (1, 1, 2, 2) or y.shape == (1, 1, 3, 3)
+    padded = torch.nn.functional.pad(img, [0, 1, 0, 1])
+    ones = torch.nn.functional.pad(torch.ones_like(img), [0, 1, 0, 1])
+    want = torch.nn.functional.avg_pool2d(padded, 2, 2) * 4 / (torch.nn.functional.avg_pool2d(ones, 2, 2) * 4)
+    torch.testing.assert_close(y, want)
+    y_inc = ex("AveragePool", [img], kernel_shape=[2, 2], strides=[2, 2], pads=[0, 0, 1, 1], count_include_pad=1)[0]
+    torch.testing.assert_close(y_inc, torch.nn.functional.avg_pool2d(padded, 2, 2))
+    # pooling over one and three spatial dimensions
+    s1 = torch.randn(2, 3, 9)
+    torch.testing.assert_close(ex("MaxPool", [s1], kernel_shape=[3], strides=[2])[0], torch.nn.functional.max_pool1d(s1, 3, 2))
+    v3 = torch.randn(1, 2, 4, 6, 6)
+    torch.testing.assert_close(ex("AveragePool", [v3], kernel_shape=[2, 2, 2], strides=[2, 2, 2])[0],
+                               torch.nn.functional.avg_pool3d(v3, 2, 2))
+    # Softmax below opset 13: coerced to 2-D at axis (default 1)
+    t = torch.randn(2, 3, 4)
+    legacy = ex("Softmax", [t], axis=1, legacy_flatten=1)[0]
+    torch.testing.assert_close(legacy, torch.softmax(t.reshape(2, 12), 1).reshape(2, 3, 4))
+    assert not torch.allclose(legacy, torch.softmax(t, 1))
+
+
+def test_softmax_of_an_opset_11_model_uses_the_flattening_semantics():
+    from ronn_b200 import Model
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.onnx.writer import model_to_bytes
+    b = GraphBuilder().add_input("x", [2, 3, 4]).add_output("y", [2, 3, 4])
+    b.add_op("Softmax", ["x"], ["y"])
+    x = torch.randn(2, 3, 4)
+    old = Model.from_bytes(model_to_bytes(b.build(), opset=11)).create_session().run({"x": x})["y"]
+    new = Model.from_bytes(model_to_bytes(b.build(), opset=17)).create_session().run({"x": x})["y"]
+    torch.testing.assert_close(old, torch.softmax(x.reshape(2, 12), 1).reshape(2, 3, 4))
+    torch.testing.assert_close(new, torch.softmax(x, -1))
+
+
+def test_add_followed_by_layernorm_becomes_one_skip_layernorm_node():
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.graph.ir import GraphBuilder
+    g = torch.Generator().manual_seed(4)
+    b = GraphBuilder().add_input("a", [3, 16]).add_input("r", [3, 16]).add_output("y", [3, 16]).add_output("z", [3, 16])
+    b.add_initializer("gamma", torch.rand(16, generator=g) + 0.5).add_initializer("beta", torch.randn(16, generator=g))
+    b.add_op("Add", ["a", "r"], ["s"]).add_op("LayerNormalization", ["s", "gamma", "beta"], ["y"], axis=-1, epsilon=1e-5)
+    b.add_op("Relu", ["s"], ["z"])                       # the sum has a second consumer
+    graph = b.build()
+    feeds = {"a": torch.randn(3, 16, generator=g), "r": torch.randn(3, 16, generator=g)}
+    ref = Model.from_graph(graph).create_session(SessionOptions().with_optimization_level("O0")).run(feeds)
+    s = Model.from_graph(graph).create_session(SessionOptions().with_optimization_level("O2"))
+    assert sorted(n.op_type for n in s.graph().nodes) == ["Relu", "SkipLayerNorm"]
+    out = s.run(feeds)
+    torch.testing.assert_close(out["y"], ref["y"], atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(out["z"], ref["z"])

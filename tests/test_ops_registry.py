@@ -45,7 +45,9 @@ def test_activations():
     assert torch.equal(ex("Relu", [x])[0], x.clamp(min=0))
     torch.testing.assert_close(ex("Sigmoid", [x])[0], 1 / (1 + torch.exp(-x)))
     ref_gelu = 0.5 * x * (1 + torch.tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * x ** 3)))
-    torch.testing.assert_close(ex("Gelu", [x])[0], ref_gelu, atol=1e-6, rtol=1e-5)
+    torch.testing.assert_close(ex("Gelu", [x], approximate="tanh")[0], ref_gelu, atol=1e-6, rtol=1e-5)
+    # ONNX default: the exact (erf) form
+    torch.testing.assert_close(ex("Gelu", [x])[0], 0.5 * x * (1 + torch.erf(x / math.sqrt(2))), atol=1e-6, rtol=1e-5)
     torch.testing.assert_close(ex("FastGelu", [x])[0], x * torch.sigmoid(1.702 * x))
     torch.testing.assert_close(ex("LeakyRelu", [x])[0], torch.where(x > 0, x, 0.01 * x))
     torch.testing.assert_close(ex("Elu", [x])[0], torch.where(x > 0, x, torch.exp(x) - 1))
