@@ -132,7 +132,7 @@ def host():
 
 
 _NOT_LAUNCHERS = {"ronn_set_pdl", "ronn_set_rowwise_status", "ronn_no_alloc_scratch_floats", "ronn_no_alloc_strerror",
-                  "ronn_gemm_fuse_state_ints", "ronn_gemm_fuse_flag_ints", "ronn_flash_attention_set_probe"}
+                  "ronn_gemm_fuse_state_ints", "ronn_gemm_fuse_flag_ints", "ronn_bitlinear_workspace_bytes"}
 
 
 class _Counted:

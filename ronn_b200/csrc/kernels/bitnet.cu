@@ -8,6 +8,9 @@
 // weight-bandwidth bound, 2 bits per weight), are expanded to int8 on the fly by four producer warps straight into
 // the 128-byte-swizzled shared-memory tile, and are multiplied with int8 activations by tcgen05.mma kind::i8 with
 // exact int32 accumulation in TMEM.  Epilogue: acc * x_scale[token] * w_scale (+ bias).
+#include <stdio.h>
+#include <stdlib.h>
+
 #include "gemm_epilogue.cuh"
 #include "ptx_sm100.cuh"
 #include "rowwise_stream.h"
@@ -86,46 +89,83 @@ __global__ void act_quant_kernel(const T* __restrict__ x, const T* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------- BitLinear GEMM
-constexpr int BL_THREADS = 192;
-constexpr int BL_STAGES = 4;
+constexpr int BL_THREADS = 320;          // warps 0-7 expand weights (0-3 also run the epilogue), 8 loads, 9 issues the MMAs
 
+// A CTA's K chain is bound by latency, not by bandwidth (measured: the same time per K block for 8 and for 128
+// activation rows): the time per K block is the round trip stage-freed -> loads issued -> data landed, divided by
+// the number of stages in flight.  So the rings are as deep as shared memory allows, and the packed weights come
+// in by TMA as well (WSTAGES stages of 4 K blocks each) instead of through registers, where the number of loads a
+// warp can keep in flight is small.
 template <int BN>
 struct BitSmem {
+  static constexpr int STAGES = BN <= 32 ? 8 : (BN <= 64 ? 7 : 5);
+  static constexpr int WSTAGES = BN <= 64 ? 4 : 3;          // packed-weight stages: BN rows x 128 bytes = 4 K blocks
   static constexpr int A_BYTES = 128 * 128;
   static constexpr int B_BYTES = BN * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int TILE_BYTES = BL_STAGES * STAGE_BYTES;
-  static constexpr int DYN_SMEM = TILE_BYTES + (2 * BL_STAGES + 1) * 8 + 16 + 1024;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int W_BYTES = BN * 128;
+  static constexpr int WTILE_BYTES = WSTAGES * W_BYTES;
+  static constexpr int DYN_SMEM = TILE_BYTES + WTILE_BYTES + (2 * STAGES + 2 * WSTAGES + 1) * 8 + 16 + 1024;
   static constexpr uint32_t TMEM_COLS = BN <= 32 ? 32u : (BN <= 64 ? 64u : 128u);
 };
 
-// 4 packed bytes (16 ternary codes) -> 16 int8 in {-1, 0, +1}
-__device__ __forceinline__ int4 expand16(uint32_t p) {
-  alignas(16) int8_t o[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t code = (p >> (2 * i)) & 3u;
-    o[i] = code == 0u ? int8_t(-1) : (code == 2u ? int8_t(1) : int8_t(0));
-  }
-  return *reinterpret_cast<const int4*>(o);
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// 4 packed bytes (16 codes of 2 bits: 0 -> -1, 1 -> 0, 2 -> +1; code i at bits 2 * (i mod 4) of byte i / 4) -> 16 int8.
+// Four masks pull codes i, i + 4, i + 8, i + 12 apart (one code per byte), a 4 x 4 byte transpose (eight byte
+// permutes) puts them in order, and (b + 0x7f) ^ 0x80 per byte maps {0, 1, 2} to {-1, 0, +1} without a carry
+// between bytes.
+__device__ __forceinline__ int4 expand16(uint32_t w) {
+  const uint32_t a0 = w & 0x03030303u, a1 = (w >> 2) & 0x03030303u, a2 = (w >> 4) & 0x03030303u, a3 = (w >> 6) & 0x03030303u;
+  const uint32_t t01lo = __byte_perm(a0, a1, 0x5140), t23lo = __byte_perm(a2, a3, 0x5140);
+  const uint32_t t01hi = __byte_perm(a0, a1, 0x7362), t23hi = __byte_perm(a2, a3, 0x7362);
+  int4 o;
+  o.x = int((__byte_perm(t01lo, t23lo, 0x5410) + 0x7f7f7f7fu) ^ 0x80808080u);
+  o.y = int((__byte_perm(t01lo, t23lo, 0x7632) + 0x7f7f7f7fu) ^ 0x80808080u);
+  o.z = int((__byte_perm(t01hi, t23hi, 0x5410) + 0x7f7f7f7fu) ^ 0x80808080u);
+  o.w = int((__byte_perm(t01hi, t23hi, 0x7632) + 0x7f7f7f7fu) ^ 0x80808080u);
+  return o;
 }
 
-template <int BN, class T>
+// WTMA: the packed weights are fetched by TMA (needs K % 64 == 0 and a 16-byte aligned matrix); otherwise by plain loads.
+template <int BN, class T, bool WTMA>
 __global__ void __launch_bounds__(BL_THREADS)
-bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __restrict__ w_packed,
+bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const uint8_t* __restrict__ w_packed,
                  const float* __restrict__ x_scale, float w_scale, const T* __restrict__ bias, T* __restrict__ out,
-                 int M, int N, int K, uint32_t idesc, uint32_t* status, const int* slot_state, long slot_stride) {
+                 int M, int N, int K, uint32_t idesc, uint32_t* status, const int* slot_state, long slot_stride,
+                 int4* __restrict__ partials) {
   using L = BitSmem<BN>;
+  constexpr int BL_STAGES = L::STAGES, WS = L::WSTAGES;
   extern __shared__ uint8_t dyn_smem[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::TILE_BYTES);
+  uint8_t* wtiles = tiles + L::TILE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(wtiles + L::WTILE_BYTES);
   uint64_t* empty = full + BL_STAGES;
-  uint64_t* accum = empty + BL_STAGES;
+  uint64_t* wfull = empty + BL_STAGES;
+  uint64_t* wempty = wfull + WS;
+  uint64_t* accum = wempty + WS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile uint32_t* abort = tmem_slot + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * 128;
-  const int num_kb = (K + 127) / 128;
+  // The K range is cut into gridDim.z slices, one per CTA of a cluster (1, 1, gridDim.z).  A CTA's chain of K blocks
+  // is latency bound (an MMA of 128 rows takes ~70 cycles to issue however narrow it is, a barrier poll ~90: about
+  // 600 cycles per block in each of the producer, expander and MMA loops), so a skinny GEMM that cannot fill the SMs
+  // with output tiles gets faster by the number of slices.  The slices' int32 partial tiles meet in a workspace in
+  // global memory (L2): measured, distributed shared memory moves ~13 bytes per cycle per SM and the same sum took
+  // 3 us through it.
+  const int S = int(gridDim.z);
+  const int total_kb = (K + 127) / 128;
+  const int kb_per = (total_kb + S - 1) / S;
+  const int kb0 = int(blockIdx.z) * kb_per;
+  const int num_kb = min(kb_per, total_kb - kb0);          // >= 1 (the launcher leaves no slice empty)
   const int kbytes = K >> 2;                 // packed bytes per weight row
 
   if (threadIdx.x == 0) {
@@ -133,13 +173,17 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
       mbar_init(&full[s], 4 + 1);            // one arrival per expander warp + the activation TMA's expect_tx arrival
       mbar_init(&empty[s], 1);
     }
+    for (int s = 0; s < WS; ++s) {
+      mbar_init(&wfull[s], 1);               // the weight TMA's expect_tx arrival
+      mbar_init(&wempty[s], WTMA ? 8 : 4);   // one arrival per expander warp
+    }
     mbar_init(accum, 1);
     *abort = 0;
     mbar_fence_init();
     fence_proxy_async_smem();
   }
   __syncwarp();
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, L::TMEM_COLS);
     tmem_relinquish();
   }
@@ -148,117 +192,197 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < 8) {
     // -------------------------------------------------- weight expansion: (row, chunk) pairs striped over 128 threads
     // weights are constants: no dependency wait needed before reading them
     constexpr int TASKS = BN * 8 / 128;      // 16-byte output chunks per thread per stage
-    // The packed words of K block kb + 2 are requested before block kb is expanded, so the global-load latency of
-    // a stage is covered by two stages of expansion; barrier traffic is one wait and one arrival per warp.
-    auto fetch = [&](uint32_t (&dst)[TASKS], int kb) {
-#pragma unroll
-      for (int t = 0; t < TASKS; ++t) {
-        const int task = threadIdx.x + t * 128;
-        const int r = task >> 3, j = task & 7;
-        const int n = n0 + r;
-        const int byte0 = kb * 32 + j * 4;
-        dst[t] = 0x55555555u;                // all-zero weights outside the matrix
-        if (kb < num_kb && n < N && byte0 < kbytes)
-          dst[t] = __ldg(reinterpret_cast<const uint32_t*>(w_packed + size_t(n) * kbytes + byte0));
-      }
-    };
-    uint32_t p0[TASKS], p1[TASKS], p2[TASKS];
-    fetch(p0, 0);
-    fetch(p1, 1);
     bool ok = true;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % BL_STAGES;
-      fetch(p2, kb + 2);
-      if (lane == 0 && ok && !mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (ok) {
-        uint8_t* sb = tiles + s * L::STAGE_BYTES + L::A_BYTES;
+    if constexpr (WTMA) {
+      // packed words come from the TMA-filled ring (128-byte swizzled: 16-byte chunk c of row r sits at c ^ (r & 7)).
+      // Warps 0-3 take the even K blocks and warps 4-7 the odd ones: a group's wait - expand - arrive chain has two
+      // block times to complete.
+      const int grp = warp >> 2, gtid = threadIdx.x & 127;
+      int seen_wb = -1;
+      for (int kb = grp; kb < num_kb; kb += 2) {
+        const int s = kb % BL_STAGES, wb = kb >> 2, ws = wb % WS, sub = kb & 3;
+        if (lane == 0 && ok) {
+          if (wb != seen_wb && !mbar_wait(&wfull[ws], (wb / WS) & 1, abort, status, STATUS_WAIT_TMA)) ok = false;
+          if (ok && !mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+        }
+        seen_wb = wb;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) {
+          uint8_t* sb = tiles + s * L::STAGE_BYTES + L::A_BYTES;
+          const uint8_t* wp = wtiles + ws * L::W_BYTES;
+#pragma unroll
+          for (int t = 0; t < TASKS; ++t) {
+            const int task = gtid + t * 128;
+            const int r = task >> 3, j = task & 7;
+            const uint32_t c = uint32_t(sub * 2 + (j >> 2));
+            const uint32_t word = *reinterpret_cast<const uint32_t*>(wp + r * 128 + ((c ^ uint32_t(r & 7)) << 4) + (j & 3) * 4);
+            *reinterpret_cast<int4*>(sb + r * 128 + ((uint32_t(j) ^ uint32_t(r & 7)) << 4)) = expand16(word);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&full[s]);
+          // the group's last block inside this packed stage: the next one it would take lies in another stage (or past the end)
+          if (((kb + 2) >> 2) != wb || kb + 2 >= num_kb) mbar_arrive(&wempty[ws]);
+        }
+      }
+    } else if (warp < 4) {
+      auto fetch = [&](uint32_t (&dst)[TASKS], int kb) {
 #pragma unroll
         for (int t = 0; t < TASKS; ++t) {
           const int task = threadIdx.x + t * 128;
           const int r = task >> 3, j = task & 7;
-          *reinterpret_cast<int4*>(sb + r * 128 + ((uint32_t(j) ^ uint32_t(r & 7)) << 4)) = expand16(p0[t]);
+          const int n = n0 + r;
+          const int byte0 = (kb0 + kb) * 32 + j * 4;
+          dst[t] = 0x55555555u;              // all-zero weights outside the matrix
+          if (kb < num_kb && n < N && byte0 < kbytes)
+            dst[t] = __ldg(reinterpret_cast<const uint32_t*>(w_packed + size_t(n) * kbytes + byte0));
         }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full[s]);
+      };
+      // the packed words of the next DEPTH K blocks are in flight (in registers) while a block is expanded
+      constexpr int DEPTH = TASKS <= 2 ? 8 : (TASKS <= 4 ? 6 : 4);
+      uint32_t pq[DEPTH][TASKS];
 #pragma unroll
-      for (int t = 0; t < TASKS; ++t) {
-        p0[t] = p1[t];
-        p1[t] = p2[t];
-      }
-    }
-    // -------------------------------------------------- epilogue
-    pdl_wait();
-    pdl_trigger();
-    // double-buffered destination (the partial-sum slots of a tensor-parallel reduction): the slot is chosen by the low
-    // bit of a device-side call counter, so a replayed CUDA graph follows the alternation without new arguments
-    if (slot_state != nullptr)
-      out = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(out) +
-                                 size_t(*reinterpret_cast<const volatile int*>(slot_state) & 1) * size_t(slot_stride));
-    bool acc_ok = mbar_wait(accum, 0, abort, status, STATUS_WAIT_ACCUM);
-    acc_ok = __all_sync(0xffffffffu, acc_ok);
-    tc_fence_after_sync();
-    const int gm = m0 + threadIdx.x;
-    if (acc_ok) {
-      const float rs = gm < M ? x_scale[gm] * w_scale : 0.f;
-#pragma unroll 1
-      for (int col = 0; col < BN; col += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col), r);
-        tmem_ld_wait();
-        const int gn = n0 + col;
-        if (gm >= M || gn >= N) continue;
-        float v[32];
+      for (int d = 0; d < DEPTH; ++d) fetch(pq[d], d);
+      for (int kb0 = 0; kb0 < num_kb; kb0 += DEPTH) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = float(int(r[i])) * rs;
-        if (bias) {
+        for (int d = 0; d < DEPTH; ++d) {
+          const int kb = kb0 + d;
+          if (kb < num_kb) {
+            const int s = kb % BL_STAGES;
+            if (lane == 0 && ok && !mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) ok = false;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok) {
+              uint8_t* sb = tiles + s * L::STAGE_BYTES + L::A_BYTES;
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (gn + i < N) v[i] += Cvt<T>::to_f(bias[gn + i]);
-        }
-        T* dst = out + size_t(gm) * N + gn;
-        if (gn + 32 <= N && (N & 7) == 0) {
-#pragma unroll
-          for (int jj = 0; jj < 4; ++jj) {
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = v[jj * 8 + i];
-            *reinterpret_cast<Vec8*>(dst + jj * 8) = pack8<T>(f);
+              for (int t = 0; t < TASKS; ++t) {
+                const int task = threadIdx.x + t * 128;
+                const int r = task >> 3, j = task & 7;
+                *reinterpret_cast<int4*>(sb + r * 128 + ((uint32_t(j) ^ uint32_t(r & 7)) << 4)) = expand16(pq[d][t]);
+              }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&full[s]);
+            fetch(pq[d], kb + DEPTH);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (gn + i < N) dst[i] = Cvt<T>::from_f(v[i]);
         }
       }
     }
-  } else if (warp == 4) {
+    if (warp < 4) {
+      // -------------------------------------------------- epilogue
+      pdl_wait();
+      pdl_trigger();
+      // double-buffered destination (the partial-sum slots of a tensor-parallel reduction): the slot is chosen by the
+      // low bit of a device-side call counter, so a replayed CUDA graph follows the alternation without new arguments
+      if (slot_state != nullptr)
+        out = reinterpret_cast<T*>(reinterpret_cast<uint8_t*>(out) +
+                                   size_t(*reinterpret_cast<const volatile int*>(slot_state) & 1) * size_t(slot_stride));
+      bool acc_ok = mbar_wait(accum, 0, abort, status, STATUS_WAIT_ACCUM);
+      acc_ok = __all_sync(0xffffffffu, acc_ok);
+      tc_fence_after_sync();
+      const int gm = m0 + threadIdx.x;
+      if (acc_ok && S > 1) {
+        // this slice's partial tile -> the workspace, 16 bytes per (4 columns, row): the rows of a warp are
+        // consecutive, so a warp stores (and later loads) 512 contiguous bytes.  Written after the dependency wait:
+        // the previous kernel on the stream may be another call that uses the same workspace.
+        int4* mine = partials + (size_t(blockIdx.y * gridDim.x + blockIdx.x) * S + blockIdx.z) * (BN / 4) * 128;
+        constexpr int STEP = BN >= 64 ? 64 : 32;               // two TMEM loads in flight where the tile has them
+#pragma unroll 1
+        for (int col = 0; col < BN; col += STEP) {
+          uint32_t r[STEP / 32][32];
+#pragma unroll
+          for (int h = 0; h < STEP / 32; ++h) tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col + 32 * h), r[h]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < STEP / 32; ++h)
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              __stcg(&mine[(((col + 32 * h) >> 2) + g) * 128 + threadIdx.x],
+                     make_int4(int(r[h][4 * g]), int(r[h][4 * g + 1]), int(r[h][4 * g + 2]), int(r[h][4 * g + 3])));
+        }
+      } else if (acc_ok) {
+        const float rs = gm < M ? x_scale[gm] * w_scale : 0.f;
+#pragma unroll 1
+        for (int col = 0; col < BN; col += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col), r);
+          tmem_ld_wait();
+          const int gn = n0 + col;
+          if (gm >= M || gn >= N) continue;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = float(int(r[i])) * rs;
+          if (bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (gn + i < N) v[i] += Cvt<T>::to_f(bias[gn + i]);
+          }
+          T* dst = out + size_t(gm) * N + gn;
+          if (gn + 32 <= N && (N & 7) == 0) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = v[jj * 8 + i];
+              *reinterpret_cast<Vec8*>(dst + jj * 8) = pack8<T>(f);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (gn + i < N) dst[i] = Cvt<T>::from_f(v[i]);
+          }
+        }
+      }
+    }
+  } else if (warp == 8) {
     if (lane == 0) {
+      if constexpr (WTMA) {
+        // weights are constants: their first stages are requested before the dependency wait
+        const int nwb = (num_kb + 3) >> 2;
+        for (int wb = 0; wb < WS && wb < nwb; ++wb) {
+          mbar_expect_tx(&wfull[wb], L::W_BYTES);
+          tma_load_2d(wtiles + wb * L::W_BYTES, &map_w, &wfull[wb], kb0 * 32 + wb * 128, n0);
+        }
+      }
       pdl_wait();                            // activations come from the previous kernel
       pdl_trigger();                         // successor may launch and set up under this kernel
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % BL_STAGES;
+        if constexpr (WTMA) {
+          // the packed-weight stage that the expanders have just released is refilled 4 * (WS - 1) K blocks ahead
+          const int wb = (kb >> 2) + WS - 1;
+          if ((kb & 3) == 0 && kb > 0 && wb < ((num_kb + 3) >> 2)) {
+            const int ws = wb % WS;
+            if (!mbar_wait(&wempty[ws], ((wb / WS) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) break;
+            mbar_expect_tx(&wfull[ws], L::W_BYTES);
+            tma_load_2d(wtiles + ws * L::W_BYTES, &map_w, &wfull[ws], kb0 * 32 + wb * 128, n0);
+          }
+        }
         if (!mbar_wait(&empty[s], ((kb / BL_STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) break;
         mbar_expect_tx(&full[s], L::A_BYTES);
-        tma_load_2d(tiles + s * L::STAGE_BYTES, &map_x, &full[s], kb * 128, m0);
+        tma_load_2d(tiles + s * L::STAGE_BYTES, &map_x, &full[s], (kb0 + kb) * 128, m0);
       }
     }
     __syncwarp();
     pdl_trigger();
   } else {
     if (lane == 0) {
+      // A barrier poll takes ~90 cycles to answer: the poll of the next stage is issued before this stage's MMAs and
+      // read after them.
+      bool ready = mbar_try_wait(&full[0], 0);
       for (int kb = 0; kb < num_kb; ++kb) {
         const int s = kb % BL_STAGES;
-        if (!mbar_wait(&full[s], (kb / BL_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
+        if (!ready && !mbar_wait(&full[s], (kb / BL_STAGES) & 1, abort, status, STATUS_WAIT_TMA)) break;
         // the expander warps wrote the weight tile through the generic proxy and released it with their arrivals: one
         // proxy fence after the acquire orders those writes before the tensor core's reads
         fence_proxy_async_smem();
         tc_fence_after_sync();
+        const int kn = kb + 1;
+        ready = kn < num_kb && mbar_try_wait(&full[kn % BL_STAGES], (kn / BL_STAGES) & 1);
         const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
         const uint64_t adesc = umma_desc_k128(sa), bdesc = umma_desc_k128(sa + L::A_BYTES);
 #pragma unroll
@@ -274,9 +398,69 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const uint8_t* __res
     const long long t0 = clock64();
     while (clock64() - t0 < 400000ll) { __nanosleep(1000); }
   }
+  if (S > 1) {
+    // every CTA of the cluster sums BN / S columns of the tile over all slices (exact: int32) and finishes them.  The
+    // cluster barrier (release / acquire) orders the slices' workspace stores before the loads below.
+    cluster_arrive_release();
+    cluster_wait_acquire();
+    if (warp < 4 && !*abort) {
+      // A load from L2 of data another SM has just written takes over a thousand cycles, so all loads of a pass are
+      // issued before the first is used.  The number of slices is a run-time value but registers want constant
+      // indices: a pass loads PASS consecutive (column group, slice) pairs, slice fastest, sums neighbours in
+      // log2(S) steps, and the pairs whose index is a multiple of S hold the finished groups of 4 columns.
+      constexpr int PASS = BN / 4 < 16 ? BN / 4 : 16;
+      const int lg = 31 - __clz(S);
+      const int cwg = (BN / 4) >> lg;                        // column groups this CTA finishes
+      const int z = int(cluster_ctarank());
+      const int gm = m0 + threadIdx.x;
+      const float rs = gm < M ? x_scale[gm] * w_scale : 0.f;
+      const int4* tile_ws = partials + size_t(blockIdx.y * gridDim.x + blockIdx.x) * S * (BN / 4) * 128 + threadIdx.x;
+#pragma unroll 1
+      for (int p = 0; p < (BN / 4) / PASS; ++p) {
+        int4 v[PASS];
+#pragma unroll
+        for (int j = 0; j < PASS; ++j) {
+          const int flat = p * PASS + j, g = z * cwg + (flat >> lg), r = flat & (S - 1);
+          v[j] = __ldcg(tile_ws + size_t(r * (BN / 4) + g) * 128);
+        }
+#pragma unroll
+        for (int step = 1; step < 8; step <<= 1)
+          if (S > step) {
+#pragma unroll
+            for (int j = 0; j < PASS; j += 2 * step)
+              if (j + step < PASS) {
+                v[j].x += v[j + step].x; v[j].y += v[j + step].y; v[j].z += v[j + step].z; v[j].w += v[j + step].w;
+              }
+          }
+#pragma unroll
+        for (int j = 0; j < PASS; ++j) {
+          if ((j & (S - 1)) != 0) continue;
+          const int gn = n0 + (z * cwg + ((p * PASS + j) >> lg)) * 4;
+          if (gm >= M || gn >= N) continue;
+          float f[4] = {float(v[j].x) * rs, float(v[j].y) * rs, float(v[j].z) * rs, float(v[j].w) * rs};
+          if (bias) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (gn + i < N) f[i] += Cvt<T>::to_f(bias[gn + i]);
+          }
+          T* dst = out + size_t(gm) * N + gn;
+          if (gn + 4 <= N && (N & 3) == 0) {
+            uint2 o;
+            o.x = Pair16<T>::pack(f[0], f[1]);
+            o.y = Pair16<T>::pack(f[2], f[3]);
+            *reinterpret_cast<uint2*>(dst) = o;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              if (gn + i < N) dst[i] = Cvt<T>::from_f(f[i]);
+          }
+        }
+      }
+    }
+  }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, L::TMEM_COLS);
   }
@@ -297,20 +481,34 @@ __global__ void ternary_pack_kernel(const int8_t* __restrict__ v, uint8_t* __res
   }
 }
 
-template <int BN, class T>
-static int launch_bitlinear(const CUtensorMap& mx, const void* w, const float* xs, float ws, const void* bias, void* out,
-                            int M, int N, int K, uint32_t* status, cudaStream_t stream, const int* slot_state = nullptr,
-                            long slot_stride = 0) {
+template <int BN, class T, bool WTMA>
+static int launch_bitlinear(const CUtensorMap& mx, const CUtensorMap& mw, const void* w, const float* xs, float ws,
+                            const void* bias, void* out, int M, int N, int K, int S, uint32_t* status, cudaStream_t stream,
+                            const int* slot_state, long slot_stride, void* workspace) {
   using L = BitSmem<BN>;
-  auto kern = bitlinear_kernel<BN, T>;
+  auto kern = bitlinear_kernel<BN, T, WTMA>;
   static bool configured[MAX_DEVICES] = {false};
   if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
   }
-  dim3 grid((N + BN - 1) / BN, (M + 127) / 128);
   const uint32_t idesc = umma_idesc(128, BN, 1u, 2u);       // signed 8-bit operands, int32 accumulate
-  cudaError_t err = launch(kern, grid, dim3(BL_THREADS), size_t(L::DYN_SMEM), stream, mx, (const uint8_t*)w, xs, ws,
-                           (const T*)bias, (T*)out, M, N, K, idesc, status, slot_state, slot_stride);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((N + BN - 1) / BN, (M + 127) / 128, S);
+  cfg.blockDim = dim3(BL_THREADS);
+  cfg.dynamicSmemBytes = size_t(L::DYN_SMEM);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;         // the K slices of one output tile form a cluster
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = unsigned(S);
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  prefer_max_shared(reinterpret_cast<const void*>(kern));
+  cudaError_t err = cudaLaunchKernelEx(&cfg, kern, mx, mw, (const uint8_t*)w, xs, ws, (const T*)bias, (T*)out, M, N, K,
+                                       idesc, status, slot_state, slot_stride, static_cast<int4*>(workspace));
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
@@ -353,44 +551,99 @@ extern "C" int ronn_norm_quant_int8(const void* x, const void* gamma, void* q, f
   return err == cudaSuccess ? 0 : -100;
 }
 
+// Tile width and number of K slices: the pair with the lowest estimated time, from a model fitted to measurements
+// (128 x 2560..13824 x 864..6912 in a CUDA graph).  A CTA costs a fixed part (launch, barrier and TMEM set-up, first
+// loads from DRAM: 2.3 us) and 0.32 / 0.36 / 0.48 us per 128-deep K block of its slice for 32 / 64 / 128 columns (the
+// MMA issuer's loop: every MMA streams its 128 x 32-byte A operand from shared memory, ~70 cycles, four per block,
+// plus ~220 cycles of barrier traffic; wide tiles add expansion time).  Slicing K costs 1.5 us (cluster barrier and
+// an L2 round trip on data other SMs have just written) plus 0.4 us per MB of partial tiles.  The grid runs in waves
+// of one CTA per SM.
+static void bitlinear_plan(int M, int N, int K, bool may_slice, int& bn, int& S) {
+  const int mt = (M + 127) / 128, total_kb = (K + 127) / 128, sms = device_sm_count();
+  bn = 128;
+  S = 1;
+  float best = 1e30f;
+  const int bns[3] = {128, 64, 32};
+  const float per_kb[3] = {0.476f, 0.364f, 0.324f};
+  for (int i = 0; i < 3; ++i)
+    for (int s = 1; s <= (may_slice ? 8 : 1); s <<= 1) {
+      if (bns[i] / s < 8 || s > total_kb) continue;
+      const int per = (total_kb + s - 1) / s;
+      if ((total_kb + per - 1) / per != s) continue;       // a slice would be empty
+      const int ctas = mt * ((N + bns[i] - 1) / bns[i]) * s;
+      if (s > 1 && ctas > sms) continue;                     // slices only where they fill otherwise idle SMs
+      const int waves = (ctas + sms - 1) / sms;
+      const float part_mb = float(ctas) * float(bns[i]) * 512.f / 1048576.f;
+      const float t = float(waves) * (2.3f + per_kb[i] * float(per)) + (s > 1 ? 1.5f + 0.4f * part_mb : 0.f);
+      if (t < best) { best = t; bn = bns[i]; S = s; }
+    }
+  if (const char* e = getenv("RONN_BITLINEAR_TILE")) {       // "bn,slices" override for experiments
+    int b = 0, s = 0;
+    if (sscanf(e, "%d,%d", &b, &s) == 2 && (b == 32 || b == 64 || b == 128) && s >= 1 && s <= 8 && b / s >= 8 &&
+        (s & (s - 1)) == 0 && (may_slice || s == 1)) {
+      const int per = (total_kb + s - 1) / s;
+      if (s <= total_kb && (total_kb + per - 1) / per == s && (s == 1 || mt * ((N + b - 1) / b) * s <= sms)) { bn = b; S = s; }
+    }
+  }
+}
+
+// Bytes of scratch memory a call of this shape wants for its K slices (0: the shape is not sliced).  At most one CTA
+// per SM is sliced, so the answer never exceeds 148 x 64 KB.
+extern "C" long ronn_bitlinear_workspace_bytes(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  int bn, S;
+  bitlinear_plan(M, N, K, true, bn, S);
+  if (S == 1) return 0;
+  return long((M + 127) / 128) * ((N + bn - 1) / bn) * S * bn * 512;
+}
+
 // xq: int8 [M, K] (row stride ldx bytes); w_packed: [N, K/4]; x_scale: fp32 [M]; out: [M, N] in `dtype` (0 bf16, 1 fp16).
-// K % 16 == 0 and ldx % 16 == 0.
+// K % 16 == 0 and ldx % 16 == 0.  workspace: null, or ronn_bitlinear_workspace_bytes(M, N, K) bytes (16-byte aligned)
+// that no other call in flight uses; without it the K range is not sliced.
 static int bitlinear_impl(const void* xq, const void* w_packed, const float* x_scale, float w_scale, const void* bias,
                           void* out, int M, int N, int K, int ldx, int dtype, const int* slot_state, long slot_stride,
-                          uint32_t* status, cudaStream_t stream) {
+                          void* workspace, uint32_t* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return -1;
   if ((K & 15) || (ldx & 15)) return -2;
-  int bn = 128;
-  const int mt = (M + 127) / 128;
-  while (bn > 32 && mt * ((N + bn - 1) / bn) < 120) bn >>= 1;
+  if (reinterpret_cast<uintptr_t>(workspace) & 15) return -2;
+  int bn, S;
+  bitlinear_plan(M, N, K, workspace != nullptr, bn, S);
   CUtensorMap mx;
   int rc = make_tmap_2d(&mx, xq, uint64_t(M), uint64_t(K), uint64_t(ldx), 128, 128, 1);
   if (rc) return rc - 20;
-#define RONN_BL(BN_) return dtype == 0 ? launch_bitlinear<BN_, __nv_bfloat16>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream, slot_state, slot_stride) \
-                                       : launch_bitlinear<BN_, __half>(mx, w_packed, x_scale, w_scale, bias, out, M, N, K, status, stream, slot_state, slot_stride)
+  // packed weights by TMA: rows of K / 4 bytes must be a multiple of 16 bytes and the matrix 16-byte aligned
+  const bool wtma = (K & 63) == 0 && (reinterpret_cast<uintptr_t>(w_packed) & 15) == 0;
+  CUtensorMap mw = mx;
+  if (wtma) {
+    rc = make_tmap_2d(&mw, w_packed, uint64_t(N), uint64_t(K >> 2), uint64_t(K >> 2), uint32_t(bn), 128, 1);
+    if (rc) return rc - 30;
+  }
+#define RONN_BL2(BN_, T_, W_) launch_bitlinear<BN_, T_, W_>(mx, mw, w_packed, x_scale, w_scale, bias, out, M, N, K, S, status, stream, slot_state, slot_stride, workspace)
+#define RONN_BL(BN_) return dtype == 0 ? (wtma ? RONN_BL2(BN_, __nv_bfloat16, true) : RONN_BL2(BN_, __nv_bfloat16, false)) \
+                                       : (wtma ? RONN_BL2(BN_, __half, true) : RONN_BL2(BN_, __half, false))
   switch (bn) {
     case 128: RONN_BL(128);
     case 64: RONN_BL(64);
     default: RONN_BL(32);
   }
 #undef RONN_BL
+#undef RONN_BL2
 }
 
 extern "C" int ronn_bitlinear(const void* xq, const void* w_packed, const float* x_scale, float w_scale,
-                              const void* bias, void* out, void* unused, int M, int N, int K, int ldx, int dtype,
+                              const void* bias, void* out, void* workspace, int M, int N, int K, int ldx, int dtype,
                               uint32_t* status, cudaStream_t stream) {
-  (void)unused;
-  return bitlinear_impl(xq, w_packed, x_scale, w_scale, bias, out, M, N, K, ldx, dtype, nullptr, 0, status, stream);
+  return bitlinear_impl(xq, w_packed, x_scale, w_scale, bias, out, M, N, K, ldx, dtype, nullptr, 0, workspace, status, stream);
 }
 
 // Same GEMM, but the [M, N] result goes to out_base + (*slot_state & 1) * slot_stride bytes: the current partial-sum
 // slot of a tensor-parallel reduction (ronn_peer_reduce), resolved on the device.
 extern "C" int ronn_bitlinear_to_slot(const void* xq, const void* w_packed, const float* x_scale, float w_scale,
-                                      void* out_base, const int* slot_state, long slot_stride, int M, int N, int K,
-                                      int ldx, int dtype, uint32_t* status, cudaStream_t stream) {
+                                      void* out_base, const int* slot_state, long slot_stride, void* workspace, int M,
+                                      int N, int K, int ldx, int dtype, uint32_t* status, cudaStream_t stream) {
   if (slot_state == nullptr || out_base == nullptr) return -1;
   return bitlinear_impl(xq, w_packed, x_scale, w_scale, nullptr, out_base, M, N, K, ldx, dtype, slot_state, slot_stride,
-                        status, stream);
+                        workspace, status, stream);
 }
 
 extern "C" int ronn_ternary_pack(const void* values, void* packed, long rows, int K, cudaStream_t stream) {

@@ -57,7 +57,7 @@ struct LLArgs {
   long ld_out, ld_res;
   float eps;
   int M, N, rank, world, owner_rows, row_begin, row_end;
-  int norm_mode, nvls, wpr;
+  int norm_mode, nvls, wpr, phases;
   int S, kb_per, num_kb;                 // K slices per rank: every (rank, slice) pair is one source of phase A
 };
 
@@ -159,7 +159,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
   const T* res = reinterpret_cast<const T*>(a.residual);
 
   // ---- phase B: owned rows, one warp per (row, 32 chunks of 8 values); units are dealt to the CTAs round-robin
-  {
+  if (a.phases & 2) {
     const int R = a.row_end - a.row_begin;
     const int segs = (n8 + 31) / 32;
     const int units = R * segs;
@@ -226,7 +226,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
   if (tr) tr[3] = globaltimer_ns();
 
   // ---- phase C: all rows; a group of `wpr` warps takes a row, unpacks X and normalises it
-  if (warp < 8) {
+  if (warp < 8 && (a.phases & 4)) {
     const int wpr = a.wpr, gpc = 8 / wpr, grp = warp / wpr, L = wpr * 32, l = (warp % wpr) * 32 + lane;
     T* out = reinterpret_cast<T*>(a.out);
     T* nout = reinterpret_cast<T*>(a.norm_out);
@@ -311,7 +311,7 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
   // ---- epoch: the CTAs of a call add up to exactly LL_UNIT; no value is read back and nobody waits on the word (the
   // next call reads it after its dependency wait, when this grid has completed)
   __syncthreads();
-  if (tid == 0) {
+  if (tid == 0 && (a.phases & 4)) {
     red_add_gpu_u64(a.state, blockIdx.x == 0 ? LL_UNIT - (unsigned long long)(G - 1) : 1ull);
     if (tr) tr[7] = globaltimer_ns();
   }
@@ -333,7 +333,7 @@ gemm_ll_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   prob.num_kb = args.num_kb;
   prob.seq = 0u;
   prob.parity_off = 0;
-  gemm_persistent<BN, STAGES, 0, LLProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
+  if (args.phases & 1) gemm_persistent<BN, STAGES, 0, LLProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
   ll_phases<T, NVLS>(args, status, s_red);
 }
 
@@ -424,6 +424,7 @@ extern "C" int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStr
   a.norm_mode = p->norm_mode;
   a.nvls = p->nvls ? 1 : 0;
   a.wpr = 1;
+  a.phases = (p->phases & 7) ? (p->phases & 7) : 7;
   a.S = S;
   a.kb_per = kb_per;
   a.num_kb = num_kb;

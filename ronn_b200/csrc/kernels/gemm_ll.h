@@ -40,6 +40,11 @@ typedef struct RonnGemmLLParams {
   double wait_seconds;           // limit of every poll
   void* trace;                   // optional: 8 x uint64 %globaltimer stamps per CTA (entry, partials sent, -, owned rows
                                  // reduced and broadcast, all rows unpacked and normalised, -, -, exit)
+  int phases;                    // 0 = the whole call.  Otherwise a mask (1 GEMM + scatter, 2 owner reduce + broadcast,
+                                 // 4 unpack + norm + epoch advance) of the parts this launch runs: with every rank's
+                                 // areas in ONE device's memory, the ranks of a call can then be run one after the
+                                 // other (all ranks' part 1, then all part 2, then all part 4) and no launch waits
+                                 // for a later one.  That is how W = 4 and 8 are checked on a single GPU.
 } RonnGemmLLParams;
 
 int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStream_t stream);

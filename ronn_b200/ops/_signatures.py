@@ -5,14 +5,14 @@ V, I, L, F = C.c_void_p, C.c_int, C.c_long, C.c_float
 
 
 def declare(lib):
-    def sig(name, args, optional=False):
+    def sig(name, args, optional=False, restype=C.c_int):
         try:
             fn = getattr(lib, name)
         except AttributeError:
             if optional:
                 return
             raise
-        fn.restype = C.c_int
+        fn.restype = restype
         fn.argtypes = args
 
     sig("ronn_gemm", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, V, V])
@@ -21,7 +21,7 @@ def declare(lib):
     sig("ronn_gemm_reduce", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I, V, V], optional=True)
     sig("ronn_argmax_exchange", [V, V, V, I, V, I, V, I, I, C.c_double, V, V], optional=True)
     sig("ronn_peer_reduce", [I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, V, V, V, F, I, V, V], optional=True)
-    sig("ronn_bitlinear_to_slot", [V, V, V, F, V, V, L, I, I, I, I, I, V, V], optional=True)
+    sig("ronn_bitlinear_to_slot", [V, V, V, F, V, V, L, V, I, I, I, I, I, V, V], optional=True)
     sig("ronn_gemm_reduce_push", [V, V, I, I, I, I, I, V, V, L, V, I, I, I, I, V, L, V, V, L, C.c_double, I, I, V, V, V, F, I,
                                   V, L, L, V, V], optional=True)
     sig("ronn_ag_gemm", [V, I, V, I, V, I, V, I, I, I, I, I, V, V, I, C.c_double, I, I, V, V], optional=True)
@@ -51,4 +51,5 @@ def declare(lib):
     sig("ronn_act_quant_int8", [V, V, V, L, I, I, V], optional=True)
     sig("ronn_norm_quant_int8", [V, V, V, V, V, L, I, F, I, V], optional=True)
     sig("ronn_bitlinear", [V, V, V, F, V, V, V, I, I, I, I, I, V, V], optional=True)
+    sig("ronn_bitlinear_workspace_bytes", [I, I, I], restype=L, optional=True)
     sig("ronn_ternary_pack", [V, V, L, I, V], optional=True)

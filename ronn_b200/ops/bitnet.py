@@ -35,6 +35,20 @@ def rmsnorm_quant_int8(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-5):
     return q, s
 
 
+_WS_BYTES = {}
+
+
+def slice_workspace(M: int, n: int, k: int, device) -> Optional[torch.Tensor]:
+    """Scratch memory for the K slices of a skinny BitLinear call (None when the shape is not sliced).  A fresh tensor per
+    call: calls on concurrent streams must not share it, and inside a CUDA-graph capture it comes from the graph's pool."""
+    key = (M, n, k)
+    nbytes = _WS_BYTES.get(key)
+    if nbytes is None:
+        nbytes = int(_native.cuda().ronn_bitlinear_workspace_bytes(M, n, k))
+        _WS_BYTES[key] = nbytes
+    return torch.empty(nbytes, dtype=torch.uint8, device=device) if nbytes else None
+
+
 def bitlinear_q(q: torch.Tensor, x_scale: torch.Tensor, w_packed: torch.Tensor, w_scale: float,
                 bias: Optional[torch.Tensor], n: int, k: int, out_dtype: torch.dtype) -> torch.Tensor:
     """int8 activations [M, K] x packed ternary weights [N, K/4] -> [M, N] in out_dtype."""
@@ -44,8 +58,9 @@ def bitlinear_q(q: torch.Tensor, x_scale: torch.Tensor, w_packed: torch.Tensor, 
     out = torch.empty((M, n), dtype=out_dtype, device=q.device)
     if bias is not None and bias.dtype != out_dtype:
         bias = bias.to(out_dtype)
+    ws = slice_workspace(M, n, k, q.device)
     _check(_native.cuda().ronn_bitlinear(q.data_ptr(), w_packed.data_ptr(), x_scale.data_ptr(), float(w_scale), _ptr(bias),
-                                         out.data_ptr(), None, M, n, k, q.stride(0), _DT[out_dtype],
+                                         out.data_ptr(), _ptr(ws), M, n, k, q.stride(0), _DT[out_dtype],
                                          status_word(q.device).data_ptr(), _stream()), "bitlinear")
     return out
 

@@ -398,8 +398,11 @@ class FusedComm(TPComm):
         dt = 0 if out_dtype == torch.bfloat16 else 1
         stream = torch.cuda.current_stream().cuda_stream
         status = K.status_word(q.device).data_ptr()
+        from ..ops.bitnet import slice_workspace
+        ws = slice_workspace(M, n, k, q.device)
         _bcheck(lib.ronn_bitlinear_to_slot(q.data_ptr(), w_packed.data_ptr(), x_scale.data_ptr(), float(w_scale),
-                                           self._part_ptrs[self.rank], self._state.data_ptr(), self.part_stride, M, n, k,
+                                           self._part_ptrs[self.rank], self._state.data_ptr(), self.part_stride,
+                                           None if ws is None else ws.data_ptr(), M, n, k,
                                            q.stride(0), dt, status, stream), "bitlinear_to_slot")
         out = torch.empty((M, n), dtype=out_dtype, device=q.device)
         if residual is not None and (residual.stride(1) != 1 or residual.shape != out.shape):

@@ -108,3 +108,56 @@ def test_gemm_fuse_graph_replay():
     torch.testing.assert_close(h2.float(), F.layer_norm(x2.float(), (N,), gamma.float(), beta.float(), 1e-5), atol=4e-2, rtol=2e-2)
     r3, _ = _ref(h2, w1, None, x2, "", "", None, None)
     torch.testing.assert_close(x3.float(), r3, atol=0.15, rtol=2e-2)
+
+
+@pytest.mark.parametrize("world,S", [(2, 1), (2, 4), (4, 1), (4, 2), (8, 1)])
+@pytest.mark.parametrize("M,N,Kr", [(148, 1024, 128), (37, 1024, 512), (8, 2048, 64), (300, 256, 192)])
+def test_gemm_ll_many_ranks_emulated_on_one_gpu(world, S, M, N, Kr):
+    """The low-latency tensor-parallel projection at 2, 4 and 8 ranks on ONE device: every rank's receive and result
+    areas live in this GPU's memory and the three parts of a call run as separate launches (all ranks' GEMM + scatter,
+    then all owners' reduce + broadcast, then all ranks' unpack + norm), so no launch waits for a later one.  Checks the
+    owner / source-slot / parity arithmetic for every world size against an fp32 reference of the summed product."""
+    import ctypes as C
+
+    from ronn_b200.ops import fuse as FU
+    from ronn_b200.ops import kernels as K
+    dev = torch.device("cuda", 0)
+    owner_rows = (M + world - 1) // world
+    sc_stride = world * S * owner_rows * N * 4
+    rs_stride = M * N * 4
+    scatter = [torch.zeros(2 * sc_stride, dtype=torch.uint8, device=dev) for _ in range(world)]
+    result = [torch.zeros(2 * rs_stride, dtype=torch.uint8, device=dev) for _ in range(world)]
+    state = [torch.zeros(4, dtype=torch.int64, device=dev) for _ in range(world)]
+    bias, res, gamma, beta = _rand(N), _rand(M, N), _rand(N), _rand(N)
+    lib = FU._lib()
+    for it in range(3):                                    # both parities, then the first again
+        a = [_rand(M, Kr) for _ in range(world)]
+        w = [_rand(N, Kr, scale=0.05) for _ in range(world)]
+        outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        hs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        for phase in (1, 2, 4):
+            for r in range(world):
+                p = FU.LLParams()
+                p.A, p.W = a[r].data_ptr(), w[r].data_ptr()
+                p.M, p.N, p.K, p.lda, p.ldw = M, N, Kr, Kr, Kr
+                p.bn, p.splitk, p.dtype = 0, S, 0
+                for q in range(world):
+                    p.scatter_area[q] = scatter[q].data_ptr()
+                    p.result_area[q] = result[q].data_ptr()
+                p.scatter_parity_stride, p.result_parity_stride = sc_stride, rs_stride
+                p.state, p.rank, p.world, p.nvls = state[r].data_ptr(), r, world, 0
+                p.out, p.norm_out, p.ld_out = outs[r].data_ptr(), hs[r].data_ptr(), N
+                p.bias, p.residual, p.ld_res = bias.data_ptr(), res.data_ptr(), N
+                p.gamma, p.beta, p.eps, p.norm_mode = gamma.data_ptr(), beta.data_ptr(), 1e-5, 1
+                p.wait_seconds, p.phases = 0.25, phase
+                rc = lib.ronn_gemm_ll(C.byref(p), K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                assert rc == 0, rc
+        K.check_status()
+        x32 = sum(a[r].float() @ w[r].float().t() for r in range(world)) + bias.float() + res.float()
+        tol = 3e-2 * math.sqrt(world * Kr / 64) + 2e-2
+        for r in range(world):
+            assert torch.equal(outs[r], outs[0]) and torch.equal(hs[r], hs[0])      # only the owner computes a row
+        torch.testing.assert_close(outs[0].float(), x32, atol=tol, rtol=2e-2)
+        hk = F.layer_norm(outs[0].float(), (N,), gamma.float(), beta.float(), 1e-5)
+        torch.testing.assert_close(hs[0].float(), hk, atol=6e-2, rtol=3e-2)
+        assert all(int(s[0]) == (it + 1) << 16 for s in state)

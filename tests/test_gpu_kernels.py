@@ -331,7 +331,8 @@ def test_pool_kernels():
     torch.testing.assert_close(g.float().reshape(3, 72), x.float().mean((1, 2)), atol=2e-3, rtol=2e-3)
 
 
-@pytest.mark.parametrize("M,N,K_", [(128, 2560, 2560), (128, 320, 6912), (37, 72, 256), (130, 96, 128), (1, 32000, 2560)])
+@pytest.mark.parametrize("M,N,K_", [(128, 2560, 2560), (128, 320, 6912), (37, 72, 256), (130, 96, 128), (1, 32000, 2560),
+                                     (64, 200, 1040), (9, 40, 48), (256, 4096, 832), (300, 130, 2112)])
 def test_bitlinear_exact_against_host_oracle(M, N, K_):
     from ronn_b200.ops import bitnet as B
     from ronn_b200.providers.bitnet.quantization import bitlinear_reference, pack_ternary_rows
