@@ -50,7 +50,7 @@ struct DenseProblem {
   }
 };
 
-template <int BN, int STAGES, class T>
+template <int BN, int STAGES, class T, int KA>
 __global__ void __launch_bounds__(PG_THREADS)
 gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                   DenseEpilogue epi, int K, int splitk, uint32_t idesc, uint32_t* status) {
@@ -64,16 +64,16 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   prob.num_kb = (K + 63) / 64;
   prob.splitk = splitk;
   prob.kb_per = (prob.num_kb + splitk - 1) / splitk;
-  gemm_persistent<BN, STAGES, 0, DenseProblem<BN, T>>(dyn_smem, prob, 64, idesc, status);
+  gemm_persistent<BN, STAGES, 0, DenseProblem<BN, T>, KA>(dyn_smem, prob, 64, idesc, status);
 }
 
 static int sm_count() { return device_sm_count(); }
 
-template <int BN, int STAGES, class T>
+template <int BN, int STAGES, class T, int KA = 1>
 static int launch_dense(const CUtensorMap& ma, const CUtensorMap& mb, DenseEpilogue epi, int M, int N, int K,
                         int is_bf16, uint32_t* status, cudaStream_t stream, int splitk = 1) {
-  using L = PGemmSmem<BN, STAGES>;
-  auto kern = gemm_dense_kernel<BN, STAGES, T>;
+  using L = PGemmSmem<BN, STAGES, false, KA>;
+  auto kern = gemm_dense_kernel<BN, STAGES, T, KA>;
   static bool configured[MAX_DEVICES] = {false};
   if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
@@ -134,17 +134,17 @@ extern "C" int ronn_gemm(const void* A, const void* W, void* C, const void* bias
   if (rc) return rc - 30;
   DenseEpilogue e{C, bias, residual, M, N, ldc, 0, 0, act, out_fp32};
   const int bf = dtype == 0;
-#define RONN_DISPATCH(BN_, ST_)                                                                       \
-  return bf ? launch_dense<BN_, ST_, __nv_bfloat16>(ma, mb, e, M, N, K, 1, status, stream)            \
-            : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream)
+#define RONN_DISPATCH(BN_, ST_, KA_)                                                                  \
+  return bf ? launch_dense<BN_, ST_, __nv_bfloat16, KA_>(ma, mb, e, M, N, K, 1, status, stream)       \
+            : launch_dense<BN_, ST_, __half, KA_>(ma, mb, e, M, N, K, 0, status, stream)
   switch (deep ? -bn : bn) {
-    case 256: case -256: RONN_DISPATCH(256, 4);
-    case 128: RONN_DISPATCH(128, 3);
-    case 64: RONN_DISPATCH(64, 4);
-    case 32: RONN_DISPATCH(32, 5);
-    case -128: RONN_DISPATCH(128, 6);
-    case -64: RONN_DISPATCH(64, 8);
-    case -32: RONN_DISPATCH(32, 10);
+    case 256: case -256: RONN_DISPATCH(256, 4, 1);
+    case 128: RONN_DISPATCH(128, 3, 1);
+    case 64: RONN_DISPATCH(64, 4, 1);
+    case 32: RONN_DISPATCH(32, 5, 1);
+    case -128: RONN_DISPATCH(128, 3, 2);       // deep ring, one CTA per SM: two K atoms per stage
+    case -64: RONN_DISPATCH(64, 4, 2);
+    case -32: RONN_DISPATCH(32, 5, 2);
     default: return -3;
   }
 #undef RONN_DISPATCH
@@ -174,17 +174,17 @@ extern "C" int ronn_gemm_splitk(const void* A, const void* W, float* workspace, 
   if (rc) return rc - 30;
   DenseEpilogue e{workspace, nullptr, nullptr, M, N, N, 0, 0, 0, 1};
   const int bf = dtype == 0;
-#define RONN_DISPATCH(BN_, ST_)                                                                          \
-  return bf ? launch_dense<BN_, ST_, __nv_bfloat16>(ma, mb, e, M, N, K, 1, status, stream, splitk)       \
-            : launch_dense<BN_, ST_, __half>(ma, mb, e, M, N, K, 0, status, stream, splitk)
+#define RONN_DISPATCH(BN_, ST_, KA_)                                                                     \
+  return bf ? launch_dense<BN_, ST_, __nv_bfloat16, KA_>(ma, mb, e, M, N, K, 1, status, stream, splitk)  \
+            : launch_dense<BN_, ST_, __half, KA_>(ma, mb, e, M, N, K, 0, status, stream, splitk)
   switch (deep ? -bn : bn) {
-    case 256: case -256: RONN_DISPATCH(256, 4);
-    case 128: RONN_DISPATCH(128, 3);
-    case 64: RONN_DISPATCH(64, 4);
-    case 32: RONN_DISPATCH(32, 5);
-    case -128: RONN_DISPATCH(128, 6);
-    case -64: RONN_DISPATCH(64, 8);
-    case -32: RONN_DISPATCH(32, 10);
+    case 256: case -256: RONN_DISPATCH(256, 4, 1);
+    case 128: RONN_DISPATCH(128, 3, 1);
+    case 64: RONN_DISPATCH(64, 4, 1);
+    case 32: RONN_DISPATCH(32, 5, 1);
+    case -128: RONN_DISPATCH(128, 3, 2);       // deep ring, one CTA per SM: two K atoms per stage
+    case -64: RONN_DISPATCH(64, 4, 2);
+    case -32: RONN_DISPATCH(32, 5, 2);
     default: return -3;
   }
 #undef RONN_DISPATCH

@@ -35,26 +35,30 @@ constexpr int PG_THREADS = 64 + 32 * PG_EPI_WARPS;
 
 // FORCE_STAGE: always reserve the per-warp store-staging area (kernels whose epilogue depends on it); otherwise only
 // the deep-ring variants (one CTA per SM) carry it, so the shallow ones still fit two CTAs per SM.
-template <int BN, int STAGES, bool FORCE_STAGE = false>
+// KA: 128-byte K atoms per stage.  A hand-over of a stage costs the MMA issuer ~220 cycles of barrier and fence
+// traffic beside the ~70 cycles per MMA (four per atom), whatever the tile width: with two atoms per stage a skinny
+// GEMM, whose CTAs are chains of K blocks, pays it half as often.
+template <int BN, int STAGES, bool FORCE_STAGE = false, int KA = 1>
 struct PGemmSmem {
   static constexpr int A_BYTES = PG_BM * 128;
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int ATOM_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = KA * ATOM_BYTES;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;          // full, empty, acc_full[2], acc_empty[2]
   static constexpr int OUT_STAGE_ROW = 80;                 // 64 bytes of a row + padding against bank conflicts
   static constexpr int OUT_STAGE_BYTES =
-      (FORCE_STAGE || STAGES * (PG_BM * 128 + BN * 128) > 100 * 1024) ? PG_EPI_WARPS * 32 * OUT_STAGE_ROW : 0;   // per epilogue warp
+      (FORCE_STAGE || STAGES * KA * (PG_BM * 128 + BN * 128) > 100 * 1024) ? PG_EPI_WARPS * 32 * OUT_STAGE_ROW : 0;   // per epilogue warp
   static constexpr int TOTAL = TILE_BYTES + NUM_BARS * 8 + 16 + OUT_STAGE_BYTES;
   static constexpr int DYN_SMEM = TOTAL + 1024;            // slack for manual 1024-byte alignment
   static constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32u : (2 * BN <= 64 ? 64u : (2 * BN <= 128 ? 128u : (2 * BN <= 256 ? 256u : 512u)));
 };
 
 // KIND: 0 = f16/bf16 operands, 1 = int8 operands.  k_elems: K elements per 128-byte smem row (64 or 128).
-template <int BN, int STAGES, int KIND, class Problem>
+template <int BN, int STAGES, int KIND, class Problem, int KA = 1>
 __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob, int k_elems, uint32_t idesc,
                                                 uint32_t* status) {
-  using L = PGemmSmem<BN, STAGES, Problem::kForceStage>;
+  using L = PGemmSmem<BN, STAGES, Problem::kForceStage, KA>;
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~uintptr_t(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + L::TILE_BYTES);
   uint64_t* empty = full + STAGES;
@@ -94,14 +98,18 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
     if (lane == 0) {
       // Weights (B) never depend on the previous kernel in the stream: the first stages of the first tile are
       // requested before the programmatic-dependency wait, the activations (A) after it.
+      // A stage holds KA atoms [A_0][B_0][A_1][B_1]...; the last stage of a tile may hold fewer.
       int pre = 0;
       if (int(blockIdx.x) < ntiles) {
         int m0, n0, kb0, nkb;
         prob.tile(blockIdx.x, m0, n0, kb0, nkb);
-        pre = nkb < STAGES ? nkb : STAGES;
-        for (int kb = 0; kb < pre; ++kb) {
-          mbar_expect_tx(&full[kb], L::STAGE_BYTES);
-          prob.load_b(tiles + kb * L::STAGE_BYTES + L::A_BYTES, &full[kb], (kb0 + kb) * k_elems, n0);
+        const int nsb = (nkb + KA - 1) / KA;
+        pre = nsb < STAGES ? nsb : STAGES;
+        for (int sb = 0; sb < pre; ++sb) {
+          const int na = min(KA, nkb - sb * KA);
+          mbar_expect_tx(&full[sb], uint32_t(na * L::ATOM_BYTES));
+          for (int a = 0; a < na; ++a)
+            prob.load_b(tiles + sb * L::STAGE_BYTES + a * L::ATOM_BYTES + L::A_BYTES, &full[sb], (kb0 + sb * KA + a) * k_elems, n0);
         }
       }
       pdl_wait();
@@ -112,17 +120,21 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
       for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
         int m0, n0, kb0, nkb;
         prob.tile(t, m0, n0, kb0, nkb);
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int nsb = (nkb + KA - 1) / KA;
+        for (int sb = 0; sb < nsb; ++sb, ++it) {
           const int s = it % STAGES;
+          const int na = min(KA, nkb - sb * KA);
           uint8_t* sa = tiles + s * L::STAGE_BYTES;
           if (it < uint32_t(pre)) {              // B already in flight, barrier already armed
-            prob.load_a(sa, &full[s], (kb0 + kb) * k_elems, m0);
+            for (int a = 0; a < na; ++a) prob.load_a(sa + a * L::ATOM_BYTES, &full[s], (kb0 + sb * KA + a) * k_elems, m0);
             continue;
           }
           if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort, status, STATUS_WAIT_SLOT)) { ok = false; break; }
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
-          prob.load_a(sa, &full[s], (kb0 + kb) * k_elems, m0);
-          prob.load_b(sa + L::A_BYTES, &full[s], (kb0 + kb) * k_elems, n0);
+          mbar_expect_tx(&full[s], uint32_t(na * L::ATOM_BYTES));
+          for (int a = 0; a < na; ++a) {
+            prob.load_a(sa + a * L::ATOM_BYTES, &full[s], (kb0 + sb * KA + a) * k_elems, m0);
+            prob.load_b(sa + a * L::ATOM_BYTES + L::A_BYTES, &full[s], (kb0 + sb * KA + a) * k_elems, n0);
+          }
         }
       }
     }
@@ -139,18 +151,28 @@ __device__ __forceinline__ void gemm_persistent(uint8_t* dyn_smem, Problem& prob
         if (!mbar_wait(&acc_empty[buf], ((j >> 1) & 1) ^ 1, abort, status, STATUS_WAIT_EPI)) break;
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + buf * BN;
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
+        const int nsb = (nkb + KA - 1) / KA;
+        // a barrier poll takes ~90 cycles to answer: the next stage is probed before this stage's MMAs are issued
+        bool ready = false;
+        for (int sb = 0; sb < nsb; ++sb, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(&full[s], (it / STAGES) & 1, abort, status, STATUS_WAIT_TMA)) { ok = false; break; }
+          if (!ready && !mbar_wait(&full[s], (it / STAGES) & 1, abort, status, STATUS_WAIT_TMA)) { ok = false; break; }
           tc_fence_after_sync();
+          ready = sb + 1 < nsb && mbar_try_wait(&full[(it + 1) % STAGES], ((it + 1) / STAGES) & 1);
+          const int na = min(KA, nkb - sb * KA);
           const uint32_t sa = smem_u32(tiles + s * L::STAGE_BYTES);
-          const uint64_t adesc = umma_desc_k128(sa);
-          const uint64_t bdesc = umma_desc_k128(sa + L::A_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {          // 4 x 32 bytes of K per 128-byte row
-            const uint32_t acc = (kb | k) != 0;
-            if (KIND == 0) umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
-            else umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+          for (int a = 0; a < KA; ++a) {
+            if (a < na) {
+              const uint64_t adesc = umma_desc_k128(sa + a * L::ATOM_BYTES);
+              const uint64_t bdesc = umma_desc_k128(sa + a * L::ATOM_BYTES + L::A_BYTES);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {      // 4 x 32 bytes of K per 128-byte row
+                const uint32_t acc = (sb | a | k) != 0;
+                if (KIND == 0) umma_f16(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+                else umma_i8(tmem_d, adesc + 2 * k, bdesc + 2 * k, idesc, acc);
+              }
+            }
           }
           umma_commit(&empty[s]);                // frees the stage once these MMAs have read it
         }

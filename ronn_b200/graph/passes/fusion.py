@@ -12,6 +12,9 @@ crates/ronn-providers/src/compiler.rs:267-314):
 * FusedGemm -> Add(residual)            => FusedGemm with 4th input
 * Add -> LayerNormalization             => com.ronn::SkipLayerNorm(x, skip, gamma, beta) -> (normed, sum): the sum
                                            stays available to its other consumers (the next residual add)
+* MatMul(Q, K^T) -> [Div | Mul scalar] -> [Where fill] -> [Add mask] -> Softmax(last axis) -> MatMul(., V)
+                                        => com.ronn::ScaledDotProductAttention(Q, K^T, V [, mask]): the attention core
+                                           as exporters write it; the GPU provider runs it on the tensor-core kernel
 * ReduceMean, Sub, Pow, ReduceMean, Add(eps), Sqrt, Div, Mul(gamma), Add(beta)
                                         => LayerNormalization: the nine-node form exporters write below opset 17
                                            (the reference's own export scripts use opset 13)
@@ -40,7 +43,7 @@ class NodeFusionPass(OptimizationPass):
             progress = False
             for fn in (self._fold_bn, self._conv_act, self._decomposed_layernorm, self._erf_gelu, self._matmul_bias,
                        self._gemm_act,
-                       self._gemm_residual, self._qkv_projection, self._skip_layernorm):
+                       self._gemm_residual, self._qkv_projection, self._skip_layernorm, self._sdpa):
                 n = fn(graph)
                 if n:
                     stats.nodes_fused += n
@@ -351,6 +354,117 @@ class NodeFusionPass(OptimizationPass):
             ln.attributes = {"epsilon": float(ln.attr("epsilon", 1e-5))}
             graph.remove_nodes([add.id])
             return 1
+        return 0
+
+    def _sdpa(self, graph: ModelGraph) -> int:
+        """The attention core written in primitives becomes one node.  Matched backwards from a Softmax over the last
+        axis: an optional additive mask, an optional scalar scale (division or multiplication, before or after the
+        mask), and the score MatMul; forwards: the MatMul with V.  Every intermediate must have exactly one reader."""
+        cons, prod = graph.consumers(), graph.producers()
+        outputs = set(graph.output_names())
+
+        def sole(name):
+            return name not in outputs and len(cons.get(name, [])) == 1
+
+        def is_scores(name, allow_fill=False):
+            """`name` is a MatMul of two non-constant tensors, possibly under one scalar Div / Mul (and, with
+            `allow_fill`, under a Where that fills masked scores with a constant)."""
+            for _ in range(3):
+                n = prod.get(name)
+                if n is None or not sole(name):
+                    return False
+                if allow_fill and n.op_type == "Where" and len(n.inputs) == 3:
+                    allow_fill = False
+                    if self._scalar(graph, n.inputs[1]) is not None:
+                        name = n.inputs[2]
+                    elif self._scalar(graph, n.inputs[2]) is not None:
+                        name = n.inputs[1]
+                    else:
+                        return False
+                    continue
+                if len(n.inputs) != 2:
+                    return False
+                if n.op_type == "MatMul":
+                    return not any(t in graph.initializers for t in n.inputs)
+                if n.op_type not in ("Div", "Mul"):
+                    return False
+                if self._scalar(graph, n.inputs[1]) is not None:
+                    name = n.inputs[0]
+                elif n.op_type == "Mul" and self._scalar(graph, n.inputs[0]) is not None:
+                    name = n.inputs[1]
+                else:
+                    return False
+            return False
+
+        for sm in graph.nodes:
+            if sm.op_type != "Softmax" or sm.domain or sm.attr("legacy_flatten") or int(sm.attr("axis", -1)) != -1:
+                continue
+            pv = self._single_consumer(graph, cons, sm.outputs[0])
+            if pv is None or pv.op_type != "MatMul" or pv.inputs[0] != sm.outputs[0] or pv.inputs[1] in graph.initializers:
+                continue
+            # walking back from the Softmax: [Add mask] then [scalar scale] then the score MatMul.  (A scale that sits
+            # between the mask and the Softmax would scale the mask too: not this pattern.)
+            chain, cur, scale, mask, qk = [sm], sm.inputs[0], 1.0, None, None
+            fill = None                                    # (condition tensor, value, fill where the condition is true?)
+            stage = 0                                      # 0: mask, fill, scale or MatMul may follow; 1: fill, scale or
+            while True:                                    # MatMul; 2: scale or MatMul; 3: MatMul
+                n = prod.get(cur)
+                if n is None or not sole(cur):
+                    break
+                if n.op_type == "Where" and len(n.inputs) == 3 and stage <= 1:
+                    # masked_fill as exporters write it: Where(cond, value, scores) or Where(cond, scores, value)
+                    v1, v2 = self._scalar(graph, n.inputs[1]), self._scalar(graph, n.inputs[2])
+                    if v1 is not None and is_scores(n.inputs[2]):
+                        fill, cur = (n.inputs[0], v1, 1), n.inputs[2]
+                    elif v2 is not None and is_scores(n.inputs[1]):
+                        fill, cur = (n.inputs[0], v2, 0), n.inputs[1]
+                    else:
+                        break
+                    stage = 2
+                    chain.append(n)
+                    continue
+                if len(n.inputs) != 2:
+                    break
+                if n.op_type == "MatMul":
+                    qk = n
+                    break
+                if n.op_type == "Add" and stage == 0:
+                    sides = [k for k in (0, 1) if is_scores(n.inputs[k], allow_fill=True)]
+                    if len(sides) != 1:
+                        break
+                    mask, cur, stage = n.inputs[1 - sides[0]], n.inputs[sides[0]], 1
+                    chain.append(n)
+                    continue
+                if n.op_type in ("Div", "Mul") and stage <= 2:
+                    c0, c1 = self._scalar(graph, n.inputs[0]), self._scalar(graph, n.inputs[1])
+                    if c1 is not None and c1 != 0.0:
+                        scale, cur = ((1.0 / c1) if n.op_type == "Div" else c1), n.inputs[0]
+                    elif c0 is not None and n.op_type == "Mul":
+                        scale, cur = c0, n.inputs[1]
+                    else:
+                        break
+                    stage = 3
+                    chain.append(n)
+                    continue
+                break
+            if qk is None:
+                continue
+            if any(t in graph.initializers for t in qk.inputs):
+                continue
+            ins = [qk.inputs[0], qk.inputs[1], pv.inputs[1]] + ([mask] if mask is not None else ([""] if fill else []))
+            attrs = {"scale": float(scale), "k_transposed": 1}
+            if fill:
+                ins.append(fill[0])
+                attrs["fill_value"], attrs["fill_when"] = float(fill[1]), int(fill[2])
+            idx = graph.nodes.index(pv)
+            name = (sm.name or f"node_{sm.id}") + ".sdpa"
+            out = pv.outputs[0]
+            graph.remove_nodes([n.id for n in chain] + [qk.id, pv.id])
+            idx = min(idx, len(graph.nodes))
+            graph.add_node("ScaledDotProductAttention", ins, [out], attrs, name=name,
+                           domain=RONN, index=idx)
+            graph.sort_in_place()
+            return len(chain) + 1
         return 0
 
     def _gemm_act(self, graph: ModelGraph) -> int:

@@ -453,6 +453,25 @@ def _skip_ln(i, a, c):
     return [y, s]
 
 
+@op("ScaledDotProductAttention", 3, 5, domain="com.ronn")
+def _sdpa(i, a, c):
+    """softmax(fill(scale * Q K^T) + mask) V on already head-split tensors: Q [..., Sq, D], V [..., Sk, D], and K either
+    as [..., Sk, D] or, with ``k_transposed = 1``, as the [..., D, Sk] operand exporters feed to the first MatMul.  What
+    the fusion pass makes of MatMul -> (Div | Mul scalar) -> (Where fill) -> (Add mask) -> Softmax(last axis) -> MatMul.
+    The optional 5th input is a condition: scores where it is true (``fill_when = 1``) or false (0) are replaced by
+    ``fill_value`` (a masked_fill)."""
+    q, k, v = i[0], i[1], i[2]
+    mask = i[3] if len(i) > 3 else None
+    kt = k if int(a.get("k_transposed", 0)) else k.transpose(-1, -2)
+    scores = torch.matmul(q.float(), kt.float()) * float(a.get("scale", 1.0))
+    if len(i) > 4 and i[4] is not None:
+        cond = i[4].bool()
+        scores = scores.masked_fill(cond if int(a.get("fill_when", 1)) else ~cond, float(a.get("fill_value", float("-inf"))))
+    if mask is not None:
+        scores = scores + mask.float()
+    return [torch.matmul(torch.softmax(scores, dim=-1), v.float()).to(q.dtype)]
+
+
 def attention(q, k, v, num_heads: int, mask=None, causal: bool = False):
     """softmax(QK^T/sqrt(d) + mask) V per head; q,k,v are [B, S, H]."""
     B, Sq, H = q.shape

@@ -1,6 +1,8 @@
 """Node -> kernel resolution of the GPU provider."""
 from __future__ import annotations
 
+import math
+
 from typing import Dict, List, Optional
 
 import torch
@@ -91,6 +93,8 @@ class GpuOpTable:
             return self._fused_elementwise(node, fallback)
         if op in ("Attention", "MultiHeadAttention"):
             return self._attention(node, fallback)
+        if op == "ScaledDotProductAttention":
+            return self._sdpa(node, fallback)
         if op in ("Conv", "FusedConv") and node.attr("data_format") == "NHWC":
             from .gpu_conv import conv_resolver
             return conv_resolver(self, node, fallback)
@@ -283,6 +287,47 @@ class GpuOpTable:
                 plan = dict(plan, kv_len=kv_len)
             out = K.dense_attention(buf, q_off, k_off, v_off, plan, heads, heads, d, causal, plan["q_len"], S)
             return [out.view(B, S, H)]
+        return run
+
+    def _sdpa(self, node, fallback):
+        """The fused attention core on head-split tensors (Q [B, h, S, d], K^T [B, h, d, S], V [B, h, S, d]).  Without
+        a mask, with the usual 1 / sqrt(d) scale and d of 64 or 128 the three operands are laid side by side as rows of
+        tokens and the tcgen05 attention kernel runs; its [B, S, h, d] result goes back as a transposed view, which the
+        Transpose that exporters put behind the attention core undoes without a copy.  Everything else takes the
+        library's fused attention."""
+        K = self.K
+        scale = float(node.attr("scale", 1.0))
+        kt = bool(int(node.attr("k_transposed", 0)))
+        plans = {}
+
+        def plan_for(B, S, dev):
+            p = plans.get((B, S))
+            if p is None:
+                s_pad = -(-S // 128) * 128
+                mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+                full = torch.full((B,), S, dtype=torch.int32, device=dev)
+                p = {"seq_start": mk([b * S for b in range(B)]), "vt_start": mk([b * s_pad for b in range(B)]),
+                     "vt_cols": B * s_pad, "max_len": S, "n_seq": B, "q_len": full, "kv_len": full}
+                plans[(B, S)] = p
+            return p
+
+        def run(i, a, c):
+            q, k, v = i[0], i[1], i[2]
+            mask = i[3] if len(i) > 3 else None
+            if q.device.type != "cuda" or q.dtype not in _HALF or q.dim() != 4 or (len(i) > 4 and i[4] is not None):
+                return fallback(i, a, c)
+            k_bhsd = k.transpose(-1, -2) if kt else k
+            B, h, S, d = q.shape
+            ok = (mask is None and d in (64, 128) and k_bhsd.shape == q.shape and v.shape == q.shape
+                  and k.dtype == q.dtype and v.dtype == q.dtype and abs(scale * math.sqrt(d) - 1.0) < 1e-3)
+            if not ok:
+                m = None if mask is None else mask.to(q.dtype)
+                return [torch.nn.functional.scaled_dot_product_attention(q, k_bhsd, v, attn_mask=m, scale=scale)]
+            H = h * d
+            buf = torch.cat([t.transpose(1, 2).reshape(B * S, H) for t in (q, k_bhsd, v)], dim=1)
+            plan = plan_for(B, S, q.device)
+            out = K.dense_attention(buf, 0, H, 2 * H, plan, h, h, d, False, plan["q_len"], S)
+            return [out.view(B, S, h, d).transpose(1, 2)]
         return run
 
     def _gather(self, node, fallback):

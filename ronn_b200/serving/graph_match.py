@@ -144,7 +144,7 @@ def match_gpt2(graph: ModelGraph):
                     or (n.op_type == "FusedGemm" and n.attr("activation") == "Gelu")) + ops.count("Tanh")
     if gelu_tanh < L:
         raise SessionError("the MLP activation is not the tanh form of GELU (the decoder runner implements GPT-2's gelu_new)")
-    if ops.count("Softmax") + ops.count("Attention") + ops.count("MultiHeadAttention") < L:
+    if sum(ops.count(t) for t in ("Softmax", "Attention", "MultiHeadAttention", "ScaledDotProductAttention")) < L:
         raise SessionError(f"expected an attention (Softmax or Attention node) per block, found fewer than {L}")
     heads = _num_heads(g, H)
     if heads is None:

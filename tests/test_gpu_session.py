@@ -192,3 +192,62 @@ def test_gpu_session_runs_elementwise_chains_and_attention_on_kernels():
     assert counts["ronn_flash_attention"] == 2 and counts["ronn_gemm"] == 2 * 4        # fused QKV + out + two MLP per layer
     for bi, n in enumerate(mask.sum(1).tolist()):
         torch.testing.assert_close(got[bi, :n], want[bi, :n].float(), atol=8e-2, rtol=5e-2)
+
+
+def test_attention_core_written_in_primitives_runs_the_tensor_core_kernel():
+    """A graph that spells attention out (projection, Reshape, Transpose, MatMul, Div, Softmax, MatMul, Transpose,
+    Reshape: what exporters write) is fused to one ScaledDotProductAttention node at O2+, and on the GPU provider that
+    node launches the tcgen05 attention kernel; with a mask it takes the library's fused attention.  Both against the
+    fp32 CPU session of the unfused graph."""
+    import math
+
+    from ronn_b200 import Model, SessionOptions, _native
+    from ronn_b200.graph.ir import GraphBuilder
+    B, S, H, D = 3, 160, 4, 64
+    g = torch.Generator().manual_seed(3)
+
+    def build(masked):
+        b = GraphBuilder().add_input("x", [B, S, H * D]).add_output("y", [B, S, H * D])
+        if masked:
+            b.add_input("m", [B, 1, 1, S])
+        for nm in ("q", "k", "v"):
+            b.add_initializer("w" + nm, torch.randn(H * D, H * D, generator=g) * 0.05)
+            b.add_op("MatMul", ["x", "w" + nm], [nm + "0"])
+            b.add_initializer("shape_" + nm, torch.tensor([B, S, H, D]))
+            b.add_op("Reshape", [nm + "0", "shape_" + nm], [nm + "1"])
+        b.add_op("Transpose", ["q1"], ["q2"], perm=[0, 2, 1, 3]).add_op("Transpose", ["k1"], ["k2"], perm=[0, 2, 3, 1])
+        b.add_op("Transpose", ["v1"], ["v2"], perm=[0, 2, 1, 3])
+        b.add_initializer("c", torch.tensor(math.sqrt(D)))
+        b.add_op("MatMul", ["q2", "k2"], ["s0"]).add_op("Div", ["s0", "c"], ["s1"])
+        cur = "s1"
+        if masked:
+            b.add_op("Add", ["s1", "m"], ["s2"])
+            cur = "s2"
+        b.add_op("Softmax", [cur], ["p"], axis=-1).add_op("MatMul", ["p", "v2"], ["o0"])
+        b.add_op("Transpose", ["o0"], ["o1"], perm=[0, 2, 1, 3])
+        b.add_initializer("shape_o", torch.tensor([B, S, H * D]))
+        b.add_op("Reshape", ["o1", "shape_o"], ["y"])
+        return b.build()
+
+    lib = _native.cuda()
+    x = torch.randn(B, S, H * D, generator=g)
+    for masked in (False, True):
+        graph = build(masked)
+        feeds = {"x": x}
+        if masked:
+            m = torch.zeros(B, 1, 1, S)
+            m[1, :, :, 100:] = -1e4
+            feeds["m"] = m
+        want = Model.from_graph(graph).create_session(SessionOptions().with_optimization_level("O0")).run(feeds)["y"]
+        sess = Model.from_graph(graph).create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("bf16"))
+        ops = [n.op_type for n in sess.graph().nodes]
+        assert ops.count("ScaledDotProductAttention") == 1 and "Softmax" not in ops
+        calls = {"n": 0}
+        real = lib.ronn_flash_attention
+        lib.__dict__["ronn_flash_attention"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
+        try:
+            got = sess.run(feeds)["y"].float().cpu()
+        finally:
+            lib.__dict__["ronn_flash_attention"] = real
+        assert calls["n"] == (0 if masked else 1)
+        torch.testing.assert_close(got, want, atol=4e-2, rtol=4e-2)
