@@ -211,6 +211,16 @@ class InferenceSession:
     def stats(self) -> Dict[str, float]:
         return self._stats.as_dict()
 
+    def compilation_plan(self):
+        """The kernel compiler's analysis of the optimised graph (fusion groups with cost estimates, tensor lifetimes
+        and the buffer plan, planned peak bytes: ``providers/compiler.py``).  The executor uses its lifetimes to drop
+        every intermediate tensor after its last reader."""
+        plan = getattr(self._kernel, "plan", None)
+        if plan is None:
+            from ..providers.compiler import KernelCompiler
+            plan = KernelCompiler.performance_preset().analyze(self._graph)
+        return plan
+
     def profile_report(self):
         if self._profiler is None:
             raise SessionError("profiling is not enabled on this session")

@@ -54,7 +54,7 @@ class CompiledKernel:
 
     def __init__(self, steps: List[Step], n_slots: int, const_slots: Dict[int, torch.Tensor],
                  input_slots: Dict[str, int], output_slots: Dict[str, int], device: torch.device,
-                 profiler=None):
+                 profiler=None, release_after: Optional[List[List[int]]] = None, plan=None):
         self.steps = steps
         self.n_slots = n_slots
         self.const_slots = const_slots
@@ -63,6 +63,10 @@ class CompiledKernel:
         self.device = device
         self.stats = KernelStats()
         self.profiler = profiler
+        # slots whose last reader is step k (from the compiler's lifetime analysis): dropped right after it, so an
+        # intermediate tensor lives only as long as the graph needs it instead of until the end of the run
+        self.release_after = release_after
+        self.plan = plan
         self._template: List[Any] = [None] * n_slots
         for k, v in const_slots.items():
             self._template[k] = v
@@ -73,7 +77,8 @@ class CompiledKernel:
         for name, slot in self.input_slots.items():
             slots[slot] = inputs[name]
         prof = self.profiler
-        for st in self.steps:
+        release = self.release_after
+        for k, st in enumerate(self.steps):
             args = [slots[s] if s >= 0 else None for s in st.in_slots]
             try:
                 if prof is not None and prof.enabled:
@@ -88,6 +93,10 @@ class CompiledKernel:
             for s, o in zip(st.out_slots, outs):
                 if s >= 0:
                     slots[s] = o
+            if release is not None:
+                args = None
+                for s in release[k]:
+                    slots[s] = None
         out = {name: slots[s] for name, s in self.output_slots.items()}
         self.stats.record((time.perf_counter() - t0) * 1e6)
         return out
@@ -172,4 +181,15 @@ def build_kernel(graph: ModelGraph, device: torch.device, resolve: Callable, pla
         if o.name not in slot_of:
             raise ProviderError(f"graph output '{o.name}' is never produced")
         output_slots[o.name] = slot_of[o.name]
-    return CompiledKernel(steps, len(slot_of), consts, input_slots, output_slots, device, profiler)
+    # lifetimes from the kernel compiler's memory plan (crates/ronn-providers/src/compiler.rs:430-520 plans buffers but
+    # nothing there consumes the plan): a produced tensor is released after its last reader
+    from .compiler import KernelCompiler
+    plan = KernelCompiler.performance_preset().analyze(graph)
+    keep = set(output_slots.values()) | set(consts) | set(input_slots.values())
+    release_after: List[List[int]] = [[] for _ in steps]
+    for b in plan.memory_plan:
+        s = slot_of.get(b.tensor)
+        if s is not None and s not in keep and 0 <= b.last_use < len(steps):
+            release_after[b.last_use].append(s)
+    return CompiledKernel(steps, len(slot_of), consts, input_slots, output_slots, device, profiler,
+                          release_after=release_after, plan=plan)

