@@ -22,68 +22,112 @@ struct FusedEwArgs {
   int mode[FEW_MAX_OPS];              // operand shape: 0 same as x, 1 vector over the last dimension, 2 scalar
 };
 
-__device__ __forceinline__ float few_unary(float v, int code) {
+// One operator on the 8 values of a chunk.  The switch sits outside the loop over the values: one branch per
+// operator and chunk, straight-line vector code inside.
+__device__ __forceinline__ void few_unary8(float (&f)[8], int code) {
+#define RONN_FEW_CASE(C, EXPR)              \
+  case C: {                                 \
+    _Pragma("unroll") for (int j = 0; j < 8; ++j) { const float v = f[j]; f[j] = (EXPR); } \
+  } break;
   switch (code) {
-    case 0: return fmaxf(v, 0.f);
-    case 1: return gelu_tanh_f(v);
-    case 2: return 1.f / (1.f + __expf(-v));
-    case 3: { const float e = __expf(2.f * v); return 1.f - 2.f / (e + 1.f); }
-    case 4: return -v;
-    case 5: return fabsf(v);
-    case 6: return __expf(v);
-    case 7: return sqrtf(v);
-    default: return v / (1.f + __expf(-v));
+    RONN_FEW_CASE(0, fmaxf(v, 0.f))
+    RONN_FEW_CASE(1, gelu_tanh_f(v))
+    RONN_FEW_CASE(2, __fdividef(1.f, 1.f + __expf(-v)))
+    RONN_FEW_CASE(3, 1.f - __fdividef(2.f, __expf(2.f * v) + 1.f))
+    RONN_FEW_CASE(4, -v)
+    RONN_FEW_CASE(5, fabsf(v))
+    RONN_FEW_CASE(6, __expf(v))
+    RONN_FEW_CASE(7, sqrtf(v))
+    default: {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = __fdividef(f[j], 1.f + __expf(-f[j]));
+    }
   }
+#undef RONN_FEW_CASE
 }
-__device__ __forceinline__ float few_binary(float a, float b, int code) {
+__device__ __forceinline__ void few_binary8(float (&f)[8], const float (&g)[8], int code) {
   switch (code) {
-    case 16: return a + b;
-    case 17: return a * b;
-    case 18: return a - b;
-    default: return a / b;
+    case 16:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
+      break;
+    case 17:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= g[j];
+      break;
+    case 18:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] -= g[j];
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = f[j] / g[j];
   }
 }
 
-template <class T>
-__device__ __forceinline__ void few_chunk(const T* __restrict__ x, T* __restrict__ y, long i, const FusedEwArgs& a) {
-  float f[8];
-  unpack8<T>(*reinterpret_cast<const Vec8*>(x + i * 8), f);
-  // every full-size operand of the chunk is requested before the arithmetic starts
-  Vec8 ob[FEW_MAX_OPS];
+// U chunks of 8 values per thread and step: every load of the step (x and the full-size operands of all U chunks) is
+// issued before the arithmetic starts.  `inner8`: chunks per row of the last dimension, for vector operands (the
+// column of a chunk is a 32-bit remainder: a 64-bit one costs ~100 instructions per chunk).
+template <class T, int U>
+__device__ __forceinline__ void few_step(const T* __restrict__ x, T* __restrict__ y, long i0, long stride, long n8,
+                                         const FusedEwArgs& a, uint32_t inner8) {
+  constexpr int PRE = 4;                 // operands of the first PRE operators are requested up front (registers)
+  Vec8 xv[U];
+  Vec8 ob[U][PRE];
+  auto operand_chunk = [&](int k, long i) -> Vec8 {
+    const T* p = reinterpret_cast<const T*>(a.operand[k]);
+    const long off = a.mode[k] == 0 ? i * 8 : long(uint32_t(i) % inner8) * 8;      // n8 < 2^32 (launcher)
+    return *reinterpret_cast<const Vec8*>(p + off);
+  };
 #pragma unroll
-  for (int k = 0; k < FEW_MAX_OPS; ++k)
-    if (k < a.n_ops && a.code[k] >= 16 && a.mode[k] != 2) {
-      const T* p = reinterpret_cast<const T*>(a.operand[k]);
-      ob[k] = *reinterpret_cast<const Vec8*>(a.mode[k] == 0 ? p + i * 8 : p + (i * 8) % a.inner);
+  for (int u = 0; u < U; ++u) {
+    const long i = i0 + u * stride;
+    if (i < n8) {
+      xv[u] = *reinterpret_cast<const Vec8*>(x + i * 8);
+#pragma unroll
+      for (int k = 0; k < PRE; ++k)
+        if (k < a.n_ops && a.code[k] >= 16 && a.mode[k] != 2) ob[u][k] = operand_chunk(k, i);
     }
+  }
 #pragma unroll
-  for (int k = 0; k < FEW_MAX_OPS; ++k)
-    if (k < a.n_ops) {
-      const int code = a.code[k];
-      if (code < 16) {
+  for (int u = 0; u < U; ++u) {
+    const long i = i0 + u * stride;
+    if (i >= n8) continue;
+    float f[8];
+    unpack8<T>(xv[u], f);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = few_unary(f[j], code);
-      } else if (a.mode[k] == 2) {
-        const float s = Cvt<T>::to_f(*reinterpret_cast<const T*>(a.operand[k]));
+    for (int k = 0; k < FEW_MAX_OPS; ++k)
+      if (k < a.n_ops) {
+        const int code = a.code[k];
+        if (code < 16) {
+          few_unary8(f, code);
+        } else {
+          float g[8];
+          if (a.mode[k] == 2) {
+            const float sc = Cvt<T>::to_f(*reinterpret_cast<const T*>(a.operand[k]));
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = few_binary(f[j], s, code);
-      } else {
-        float g[8];
-        unpack8<T>(ob[k], g);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = few_binary(f[j], g[j], code);
+            for (int j = 0; j < 8; ++j) g[j] = sc;
+          } else if (k < PRE) {
+            unpack8<T>(ob[u][k], g);
+          } else {
+            unpack8<T>(operand_chunk(k, i), g);
+          }
+          few_binary8(f, g, code);
+        }
       }
-    }
-  *reinterpret_cast<Vec8*>(y + i * 8) = pack8<T>(f);
+    *reinterpret_cast<Vec8*>(y + i * 8) = pack8<T>(f);
+  }
 }
 
 template <class T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 fused_elementwise_kernel(const T* __restrict__ x, T* __restrict__ y, long n8, const __grid_constant__ FusedEwArgs a) {
   pdl_wait();
   pdl_trigger();
+  constexpr int U = 2;
   const long stride = long(gridDim.x) * blockDim.x;
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += stride) few_chunk<T>(x, y, i, a);
+  const uint32_t inner8 = uint32_t(a.inner >> 3) ? uint32_t(a.inner >> 3) : 1u;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n8; i += U * stride) few_step<T, U>(x, y, i, stride, n8, a, inner8);
 }
 
 }  // namespace ronn
@@ -97,6 +141,7 @@ extern "C" int ronn_fused_elementwise(const void* x, void* y, long n, int n_ops,
   if (n <= 0) return 0;
   if (n_ops < 1 || n_ops > FEW_MAX_OPS) return -1;
   if ((n & 7) || ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15)) return -2;
+  if ((n >> 3) >= (1l << 32)) return -7;                     // chunk indices are reduced modulo the row in 32 bits
   FusedEwArgs a;
   a.n_ops = n_ops;
   a.inner = inner > 0 ? inner : 8;
@@ -116,7 +161,7 @@ extern "C" int ronn_fused_elementwise(const void* x, void* y, long n, int n_ops,
   }
   const long n8 = n >> 3;
   long blocks = (n8 + 255) / 256;
-  const long cap = long(device_sm_count()) * 8;
+  const long cap = long(device_sm_count()) * 6;
   if (blocks > cap) blocks = cap;
   cudaError_t err;
   if (dtype == 0) err = launch(fused_elementwise_kernel<__nv_bfloat16>, dim3(unsigned(blocks)), dim3(256), 0, stream,

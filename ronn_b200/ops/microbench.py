@@ -277,6 +277,57 @@ def bench_bitlinear(m=128, n=2560, k=2560, flush=True, iters=20):
             "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3), "dequantised_bf16_cublas_us": round(us_lib, 2)}
 
 
+def bench_fused_elementwise(rows=131072, h=1024, flush=True, iters=20):
+    """The one-launch chain kernel on a 4-operator chain (add a row vector, ReLU, multiply by a full tensor, tanh)
+    against the same chain as four library kernels; operands larger than L2."""
+    hbm, _, src = _peaks()
+    x = torch.randn(rows, h, device="cuda").bfloat16()
+    bias = torch.randn(h, device="cuda").bfloat16()
+    w = torch.randn(rows, h, device="cuda").bfloat16()
+    names, operands = ["Add", "Relu", "Mul", "Tanh"], [bias, None, w, None]
+    plan = K.fused_elementwise_plan(x, names, operands)
+    us = time_kernel(lambda: K.fused_elementwise(x, names, operands, plan), iters=iters, flush=flush)
+    us_lib = time_kernel(lambda: torch.tanh(torch.relu(x + bias) * w), iters=iters, flush=flush)
+    byts = 3.0 * rows * h * 2
+    return {"kernel": "fused_elementwise", "chain": names, "shape": [rows, h], "us": round(us, 2), "gbs": round(byts / us / 1e3, 1),
+            "frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3), "four_library_kernels_us": round(us_lib, 2)}
+
+
+def bench_sampling(rows=2048, vocab=50264, flush=True, iters=20):
+    """Device sampler (repeat penalty, temperature 0.8, top-k 50, top-p 0.95) on fp32 logits larger than L2, against the
+    library's sort-based form of the same pipeline."""
+    import numpy as np
+    hbm, _, src = _peaks()
+    logits = torch.randn(rows, vocab, device="cuda") * 3
+    buf = bytearray(rows * K.SAMPLE_RECORD_BYTES)
+    for r in range(rows):
+        K.pack_sample_params(buf, r, 0.8, 50, 0.95, 1.1, 1234 + r, 16)
+    params = torch.frombuffer(buf, dtype=torch.uint8).cuda()
+    recent = torch.randint(0, vocab, (rows, 16), device="cuda", dtype=torch.int32)
+    counters = torch.zeros(rows, dtype=torch.int64, device="cuda")
+    work = logits.clone()
+
+    def ours():
+        work.copy_(logits)                      # the penalty is applied in place
+        K.sample(work, params, recent, counters)
+
+    def library():
+        z = logits / 0.8
+        v, idx = torch.topk(z, 50, dim=-1)
+        p = torch.softmax(v, dim=-1)
+        keep = (p.cumsum(-1) - p) <= 0.95
+        p = p * keep
+        return idx.gather(-1, torch.multinomial(p / p.sum(-1, keepdim=True), 1))
+
+    us_copy = time_kernel(lambda: work.copy_(logits), iters=iters, flush=flush)
+    us = time_kernel(ours, iters=iters, flush=flush) - us_copy
+    us_lib = time_kernel(library, iters=iters, flush=flush)
+    K.check_status()
+    byts = float(rows) * vocab * 4               # one pass is the floor; the kernel makes several (L2 / L1 resident rows)
+    return {"kernel": "sample", "shape": [rows, vocab], "us": round(us, 2), "one_pass_gbs": round(byts / us / 1e3, 1),
+            "one_pass_frac_of_" + src: round(byts / (hbm * 1e9) * 1e6 / us, 3), "library_topk_multinomial_us": round(us_lib, 2)}
+
+
 def resnet_convs():
     shapes = [(32, 224, 224, 8, 64, 7, 2, 3), (32, 56, 56, 64, 64, 3, 1, 1), (32, 56, 56, 64, 128, 3, 2, 1), (32, 28, 28, 128, 128, 3, 1, 1),
               (32, 28, 28, 128, 256, 3, 2, 1), (32, 14, 14, 256, 256, 3, 1, 1), (32, 14, 14, 256, 512, 3, 2, 1), (32, 7, 7, 512, 512, 3, 1, 1),
@@ -295,7 +346,7 @@ def decode_shapes(batch=256, ctx=416):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "dense-attention", "fused-single-rank", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes"])
+    ap.add_argument("what", choices=["gemm", "attention", "norm", "decode-shapes", "prefill-shapes", "dense-attention", "fused-single-rank", "memory-kernels", "conv", "resnet-convs", "bitlinear", "bitnet-shapes", "fused-elementwise", "sampling"])
     ap.add_argument("--m", type=int, default=256)
     ap.add_argument("--n", type=int, default=1024)
     ap.add_argument("--k", type=int, default=1024)
@@ -323,6 +374,10 @@ def main():
         res = resnet_convs()
     elif a.what == "bitlinear":
         res = [bench_bitlinear(a.m if a.m != 256 else 128, a.n if a.n != 1024 else 2560, a.k if a.k != 1024 else 2560, flush=fl, iters=a.iters)]
+    elif a.what == "fused-elementwise":
+        res = [bench_fused_elementwise(flush=fl, iters=a.iters)]
+    elif a.what == "sampling":
+        res = [bench_sampling(flush=fl, iters=a.iters)]
     elif a.what == "bitnet-shapes":
         res = [bench_bitlinear(128, n, k) for (n, k) in [(7680, 2560), (2560, 2560), (13824, 2560), (2560, 6912), (960, 2560), (2560, 864)]]
     elif a.what == "dense-attention":
