@@ -8,6 +8,8 @@
 // Replaces the reference's library matmul (crates/ronn-core/src/ops/matrix.rs:27-60) and its two
 // never-compiled templates: the scalar fused matmul+bias and the one-wmma-tile-per-warp GEMM
 // (crates/ronn-providers/src/gpu/cuda_kernels.rs:319-347, 479-534).
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include "tma_desc.cuh"
@@ -106,6 +108,12 @@ int pick_bn(int M, int N) {
 // instead of two co-resident CTAs with half the ring each.  bn | 0x1000 forces the deep ring, bn | 0x2000 the shallow.
 static int deep_mode(int bn) { return (bn & 0x1000) ? 1 : ((bn & 0x2000) ? 0 : -1); }
 static int wants_deep(int M, int N, int bn, int splitk) {
+  static int forced = -2;                                  // RONN_GEMM_RING = deep | shallow overrides the choice
+  if (forced == -2) {
+    const char* e = getenv("RONN_GEMM_RING");
+    forced = !e ? -1 : (e[0] == 'd' ? 1 : (e[0] == 's' ? 0 : -1));
+  }
+  if (forced >= 0) return forced;
   const int tiles = ((N + bn - 1) / bn) * ((M + PG_BM - 1) / PG_BM) * splitk;
   return tiles <= sm_count() ? 1 : 0;
 }

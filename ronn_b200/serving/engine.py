@@ -106,11 +106,20 @@ class LLMEngine:
         self.host_seconds_last = (0.0, 0.0)
         self._part_streams: List[torch.cuda.Stream] = []
         self._part_comms: list = []
-        # device-side sampling (kernel backend, one GPU): per-row sampling records and the recent-token windows of the
-        # repeat penalty are staged in pinned memory and reach the device in one copy per step, so that a non-greedy
-        # decode step is a CUDA-graph replay like a greedy one
-        self.device_sampling = (self.cfg.backend == "kernels" and self.device.type == "cuda" and self.runner.tp == 1)
+        # device-side sampling (kernel backend): per-row sampling records and the recent-token windows of the repeat
+        # penalty are staged in pinned memory and reach the device in one copy per step, so that a non-greedy decode
+        # step is a CUDA-graph replay like a greedy one.  Under tensor parallelism the vocabulary shards of the logits
+        # are gathered first and every rank draws the same tokens from the same seeds.
+        self.device_sampling = self.cfg.backend == "kernels" and self.device.type == "cuda"
         self._samp_recent = 256
+        # base seed of requests that bring none; under tensor parallelism rank 0's, so that every rank draws the same tokens
+        self._samp_seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+        if self.runner.tp > 1:
+            import torch.distributed as dist
+            grp = self.runner.comm.group
+            t = torch.tensor([self._samp_seed], dtype=torch.int64, device=self.device)
+            dist.broadcast(t, src=dist.get_global_rank(grp, 0) if grp is not None else 0, group=grp)
+            self._samp_seed = int(t.item())
         if self.device_sampling:
             from ..ops import kernels as K
             n = self.cfg.max_num_seqs
@@ -118,7 +127,6 @@ class LLMEngine:
             self._samp_host = torch.zeros(self._samp_bytes + n * self._samp_recent * 4, dtype=torch.uint8).pin_memory()
             self._samp_dev = torch.zeros_like(self._samp_host, device=self.device)
             self._samp_counters = torch.zeros(n, dtype=torch.int64, device=self.device)
-            self._samp_seed = int(torch.randint(0, 2 ** 62, (1,)).item())
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_tokens: Iterable[int], params: Optional[SamplingParams] = None,
@@ -353,7 +361,7 @@ class LLMEngine:
             self._stage_sampling(req_ids[:n_items], n_items)
             return self._sample_on_device(logits, n_items)
         reqs = [self.requests[int(i)] for i in req_ids]
-        return sample_tokens(logits, reqs)
+        return sample_tokens(logits, reqs, base_seed=self._samp_seed if self.runner.tp > 1 else None)
 
     # ------------------------------------------------------------------ device-side sampling
     def _stage_sampling(self, req_ids, rows: int) -> None:

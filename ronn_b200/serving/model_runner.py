@@ -111,6 +111,7 @@ class DecoderRunner:
         self.ffn_local = a.ffn // self.tp
         vs = -(-a.vocab // self.tp)
         vs = (vs + 7) // 8 * 8
+        self.vocab_shard = vs
         self.vocab_start = min(self.rank * vs, a.vocab)
         self.vocab_local = max(min(vs, a.vocab - self.vocab_start), 0)
         self._load_weights(initializers)
@@ -309,15 +310,24 @@ class DecoderRunner:
             x = self._norm(x, self.lnf)
         logits = ops.lm_head(x, self.lm_head)
         if want_logits:
-            if self.tp != 1:
-                raise SessionError("full logits are only available without tensor parallelism")
-            return logits
+            return logits if self.tp == 1 else self.gather_vocab(logits, comm)
         if self.tp == 1:
             return ops.argmax(logits)
         idx, mx = ops.argmax(logits, col_offset=self.vocab_start, return_max=True)
         if local_argmax:
             return idx, mx
         return self.combine_argmax(idx, mx, comm)
+
+    def gather_vocab(self, logits: torch.Tensor, comm=None) -> torch.Tensor:
+        """Full-vocabulary fp32 logits on every rank from the vocabulary shards: [rows, world * shard] where column
+        r * shard + j is token r * shard + j (columns past the vocabulary hold -inf).  Every rank then samples with the
+        same seeds and gets the same tokens, so the replicated schedulers stay in step."""
+        comm = comm or self.comm
+        rows = logits.shape[0]
+        local = torch.full((rows, self.vocab_shard), float("-inf"), dtype=torch.float32, device=logits.device)
+        local[:, :self.vocab_local] = logits[:, :self.vocab_local]
+        allr = comm.all_gather_small(local)                                   # [world, rows, shard]
+        return allr.permute(1, 0, 2).reshape(rows, self.tp * self.vocab_shard)
 
     def combine_argmax(self, idx, mx, comm=None):
         """Greedy token over the vocabulary shards: gather every rank's (index, max) and keep the largest value."""

@@ -39,11 +39,17 @@ def sample_row(logits: torch.Tensor, r: Request, generator=None) -> int:
     return int(torch.multinomial(probs, 1, generator=generator))
 
 
-def sample_tokens(logits: torch.Tensor, reqs: List[Request]) -> torch.Tensor:
+def sample_tokens(logits: torch.Tensor, reqs: List[Request], base_seed=None) -> torch.Tensor:
+    """One token per row.  A request with a seed draws from a generator seeded by (seed, tokens generated so far);
+    with ``base_seed`` (tensor-parallel engines: the same on every rank) requests without a seed do so too, from
+    (base_seed, request id), so that replicated engines draw the same tokens."""
     out = []
     for i, r in enumerate(reqs):
         gen = None
-        if r.params.seed is not None:
-            gen = torch.Generator(device=logits.device).manual_seed(r.params.seed + len(r.output_tokens))
+        seed = r.params.seed
+        if seed is None and base_seed is not None and r.params.temperature > 0:
+            seed = (int(base_seed) ^ (r.id * 0x9E3779B1)) & 0x3FFFFFFFFFFFFFFF
+        if seed is not None:
+            gen = torch.Generator(device=logits.device).manual_seed(seed + len(r.output_tokens))
         out.append(sample_row(logits[i], r, gen))
     return torch.tensor(out, dtype=torch.int32, device=logits.device)

@@ -54,6 +54,24 @@ def main():
     single = run(None, "nccl")
     if mode == "fused":
         comm.check()
+    # non-greedy requests (one with its own seed, the others without): the vocabulary shards of the logits are gathered
+    # and every rank must draw the same tokens
+    sampled_same, sampled_ok = True, True
+    if not tight:
+        ecfg = EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=256, dtype="fp32" if mode == "cpu" else "bf16",
+                            backend=backend, tp_size=world, tp_comm="nccl" if mode != "fused" else "fused",
+                            use_cuda_graph=(mode != "cpu"), num_blocks=64)
+        eng = LLMEngine(model, ecfg, device=dev, comm=comm)
+        ids = [eng.add_request(pr, SamplingParams(max_new_tokens=6, temperature=0.9, top_k=40, top_p=0.9,
+                                                  repeat_penalty=1.1, seed=(11 if k == 0 else None)))
+               for k, pr in enumerate(prompts[:4])]
+        while eng.has_unfinished():
+            eng.step()
+        drawn = [eng.requests[i].output_tokens for i in ids]
+        allr = [None] * world
+        torch.distributed.all_gather_object(allr, drawn)
+        sampled_same = all(a == allr[0] for a in allr)
+        sampled_ok = all(len(t) == 6 and all(0 <= x < 1000 for x in t) for t in drawn)
     agree = sum(a == b for x, y in zip(tp, single) for a, b in zip(x, y))
     total = sum(len(x) for x in single)
     # every rank must have produced the same tokens (the schedulers run replicated)
@@ -63,6 +81,7 @@ def main():
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump({"agree": agree, "total": total, "same_across_ranks": same_across_ranks, "world": world,
+                       "sampled_same_across_ranks": sampled_same, "sampled_in_range": sampled_ok,
                        "fused_calls": getattr(comm, "fused_calls", 0),
                        "swap_preemptions": stats.get("swap_preemptions", 0),
                        "swapped_in_blocks": stats.get("swapped_in_blocks", 0)}, f)

@@ -38,6 +38,7 @@ def test_tp_engine_matches_single_gpu(tmp_path, mode):
     r = json.loads(out.read_text())
     assert r["same_across_ranks"]
     assert r["agree"] >= int(0.85 * r["total"]), r
+    assert r["sampled_same_across_ranks"] and r["sampled_in_range"], r      # device sampler on gathered vocabulary shards
     if mode == "fused":
         assert r["fused_calls"] > 0
 

@@ -25,6 +25,7 @@ def test_tp_engine_on_cpu_ranks_matches_single_rank(tmp_path, world):
     r = json.loads(out.read_text())
     assert r["world"] == world and r["same_across_ranks"]
     assert r["agree"] == r["total"] == 48          # fp32: sharded and unsharded runs pick the same tokens
+    assert r["sampled_same_across_ranks"] and r["sampled_in_range"]        # non-greedy requests: gathered logits, one seed
 
 
 def test_tp_engine_swap_preemption_on_cpu_ranks(tmp_path):
