@@ -45,15 +45,18 @@ _NP_VIEW = {DataType.F32: np.float32, DataType.U8: np.uint8, DataType.I8: np.int
             DataType.U32: np.uint32, DataType.BF16: np.int16}
 
 
-def tensor_from_bytes(buf, dt: DataType, shape) -> torch.Tensor:
-    """Build a torch tensor (own copy) from little-endian bytes."""
+def tensor_from_bytes(buf, dt: DataType, shape, share: bool = False) -> torch.Tensor:
+    """Build a torch tensor from little-endian bytes: its own copy, or (``share``, writable buffers only) a view of
+    ``buf`` itself, which then has to outlive the tensor (a memoryview keeps its mapping alive)."""
     count = 1
     for d in shape:                 # Python integers: a declared shape may overflow 64 bits
         count *= int(d)
     need = count * dt.itemsize
     if count < 0 or len(buf) < need:
         raise TypeConversionError(f"tensor payload has {len(buf)} bytes, shape {list(shape)} of {dt.name} needs {need}")
-    arr = np.frombuffer(buf, dtype=_NP_VIEW[dt], count=count).copy()
+    arr = np.frombuffer(buf, dtype=_NP_VIEW[dt], count=count)
+    if not (share and count > 0 and arr.flags.writeable and arr.flags.aligned):
+        arr = arr.copy()
     t = torch.from_numpy(arr)
     if dt == DataType.BF16:
         t = t.view(torch.bfloat16)

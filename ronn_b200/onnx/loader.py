@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes as C
 import json
 import logging
+import mmap
 import os
 from dataclasses import dataclass, field
 from typing import Any, Dict, List, Optional
@@ -44,6 +45,7 @@ class LoadedModel:
     opset_imports: Dict[str, int] = field(default_factory=dict)
     metadata: Dict[str, str] = field(default_factory=dict)
     doc_string: str = ""
+    shared_bytes: int = 0          # bytes of initializers that are views of the mapped model file (not copies)
 
 
 def _fix_str(s: str) -> str:
@@ -63,13 +65,19 @@ def _num(v):
 class ModelLoader:
     @staticmethod
     def load_from_file(path) -> LoadedModel:
+        """The file is mapped (private, copy-on-write), parsed in place, and initializers of SHARE_BYTES or more stay
+        views of the mapping: loading costs no second copy of the weights, and the ranks of a tensor-parallel job that
+        load the same file share its pages and touch only the slices of the weights they move to their device."""
         path = os.fspath(path)
         try:
             with open(path, "rb") as f:
-                data = f.read()
+                size = os.fstat(f.fileno()).st_size
+                if size == 0:
+                    raise ProtobufDecodeError("empty model buffer")
+                mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_COPY)
         except OSError as e:
             raise IoError(f"{e.strerror or e}: '{path}'") from None
-        return ModelLoader.load_from_bytes(data, base_dir=os.path.dirname(os.path.abspath(path)))
+        return ModelLoader._load(mm, memoryview(mm), os.path.dirname(os.path.abspath(path)), share=True)
 
     @staticmethod
     def load_from_bytes(data: bytes, base_dir: Optional[str] = None) -> LoadedModel:
@@ -78,9 +86,16 @@ class ModelLoader:
         data = bytes(data)
         if len(data) == 0:
             raise ProtobufDecodeError("empty model buffer")
+        return ModelLoader._load(bytearray(data), memoryview(data), base_dir, share=False)
+
+    @staticmethod
+    def _load(writable, view: memoryview, base_dir: Optional[str], share: bool) -> LoadedModel:
+        """``writable``: the model bytes as an object with a writable buffer (what ctypes can point into without a
+        copy); ``view``: the bytes the tensors are cut from."""
         lib = _native.host()
-        buf = (C.c_uint8 * len(data)).from_buffer_copy(data)
-        h = lib.ronn_onnx_parse(C.cast(buf, C.c_void_p), len(data))
+        n_bytes = len(view)
+        buf = (C.c_uint8 * n_bytes).from_buffer(writable)
+        h = lib.ronn_onnx_parse(C.cast(buf, C.c_void_p), n_bytes)
         try:
             err = lib.ronn_onnx_error(h)
             if err:
@@ -95,7 +110,8 @@ class ModelLoader:
                 blobs.append(C.string_at(bp, bl.value))
         finally:
             lib.ronn_onnx_free(h)
-        return _convert_model(doc, memoryview(data), blobs, base_dir)
+            del buf
+        return _convert_model(doc, view, blobs, base_dir, share)
 
 
 def _read_external(name: str, base_dir: str, loc: str, ext: Dict[str, str], dt, dims) -> bytes:
@@ -142,7 +158,10 @@ def _read_external(name: str, base_dir: str, loc: str, ext: Dict[str, str], dt, 
         raise IoError(f"tensor '{name}': cannot read external data file '{loc}': {e}") from e
 
 
-def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir) -> torch.Tensor:
+SHARE_BYTES = 1 << 16          # initializers at least this large stay views of a mapped model file
+
+
+def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir, share: bool = False) -> torch.Tensor:
     code = td["data_type"]
     dt = DataTypeMapper.from_onnx(code)
     dims = td["dims"]
@@ -163,7 +182,7 @@ def _tensor_from_desc(td: Dict[str, Any], data: memoryview, blobs, base_dir) -> 
         if td["raw_len"] != need:
             raise TypeConversionError(f"tensor '{_fix_str(td['name'])}': raw_data holds {td['raw_len']} bytes, shape "
                                       f"{list(dims)} of {dt.name} needs {need}")
-        return tensor_from_bytes(raw, dt, dims)
+        return tensor_from_bytes(raw, dt, dims, share=share and need >= SHARE_BYTES)
     if td["blob"] >= 0:
         return tensor_from_bytes(blobs[td["blob"]], dt, dims)
     count = 1
@@ -210,7 +229,7 @@ def _value_info(v: Dict[str, Any]) -> TensorInfo:
     return TensorInfo(_fix_str(v["name"]), shape, dt, params)
 
 
-def _convert_model(doc, data, blobs, base_dir) -> LoadedModel:
+def _convert_model(doc, data, blobs, base_dir, share: bool = False) -> LoadedModel:
     g = doc.get("graph")
     if g is None:
         raise InvalidGraph("Model has no graph")
@@ -223,9 +242,13 @@ def _convert_model(doc, data, blobs, base_dir) -> LoadedModel:
         log.warning("model uses opset %d; opsets below 13 are only partially supported", std)
 
     graph = ModelGraph()
+    shared = 0
     graph.name = _fix_str(g.get("name", ""))
     for td in g["initializers"]:
-        graph.initializers[_fix_str(td["name"])] = _tensor_from_desc(td, data, blobs, base_dir)
+        t = _tensor_from_desc(td, data, blobs, base_dir, share)
+        if share and td["raw_off"] >= 0 and not td.get("external") and t.numel() * t.element_size() >= SHARE_BYTES:
+            shared += t.numel() * t.element_size()
+        graph.initializers[_fix_str(td["name"])] = t
     for v in g["inputs"]:
         info = _value_info(v)
         if info.name not in graph.initializers:
@@ -258,4 +281,4 @@ def _convert_model(doc, data, blobs, base_dir) -> LoadedModel:
                        producer_name=_fix_str(doc.get("producer_name", "")) or None,
                        producer_version=_fix_str(doc.get("producer_version", "")) or None,
                        ir_version=ir, model_version=int(doc.get("model_version", 0)), opset_imports=opsets,
-                       metadata=meta, doc_string=_fix_str(doc.get("doc_string", "")))
+                       metadata=meta, doc_string=_fix_str(doc.get("doc_string", "")), shared_bytes=shared)

@@ -214,3 +214,35 @@ def test_a_large_model_file_loads_without_copying_every_tensor_twice():
     data = model(ld(5, tensor(name=b"w", dims=(w.size,), raw=w.tobytes())))
     m = load(data)
     assert m.initializers["w"].numel() == w.size and float(m.initializers["w"][-1]) == 3.0
+
+
+def test_large_initializers_of_a_model_file_are_views_of_its_mapping(tmp_path):
+    """Loading from a path maps the file copy-on-write: initializers of 64 KB or more share the mapping (no second
+    copy of the weights; the ranks of a tensor-parallel job share the pages), small ones are copied, and writing to a
+    shared tensor never reaches the file."""
+    import numpy as np
+    import torch
+
+    from ronn_b200 import Model
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.onnx.loader import ModelLoader
+    b = GraphBuilder().add_input("x", [4, 512]).add_output("y", [4, 256])
+    w, small = torch.randn(512, 256), torch.randn(256)
+    b.add_initializer("w", w).add_initializer("small", small)
+    b.add_op("MatMul", ["x", "w"], ["m"]).add_op("Add", ["m", "small"], ["y"])
+    path = tmp_path / "m.onnx"
+    Model.from_graph(b.build()).save(str(path))
+    on_disk = path.read_bytes()
+    loaded = ModelLoader.load_from_file(str(path))
+    lw, ls = loaded.initializers["w"], loaded.initializers["small"]
+    assert torch.equal(lw, w) and torch.equal(ls, small)
+    assert loaded.shared_bytes == 512 * 256 * 4          # the large tensor is a view of the mapping, the small one a copy
+    lw[0, 0] = 12345.0                                   # copy-on-write: private to this process
+    assert path.read_bytes() == on_disk
+    x = torch.randn(4, 512)
+    out = Model.load(str(path)).create_session().run({"x": x})["y"]
+    torch.testing.assert_close(out, x @ w + small, atol=1e-4, rtol=1e-4)
+    # from bytes nothing is shared
+    again = ModelLoader.load_from_bytes(on_disk)
+    again.initializers["w"][0, 0] = -1.0
+    assert torch.equal(ModelLoader.load_from_bytes(on_disk).initializers["w"], w)
