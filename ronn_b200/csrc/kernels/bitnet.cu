@@ -12,6 +12,7 @@
 #include <stdlib.h>
 
 #include "gemm_epilogue.cuh"
+#include "gemm_ll_phases.cuh"
 #include "ptx_sm100.cuh"
 #include "rowwise_stream.h"
 #include "tma_desc.cuh"
@@ -89,7 +90,9 @@ __global__ void act_quant_kernel(const T* __restrict__ x, const T* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------- BitLinear GEMM
-constexpr int BL_THREADS = 320;          // warps 0-7 expand weights (0-3 also run the epilogue), 8 loads, 9 issues the MMAs
+constexpr int BL_THREADS = 320;
+static_assert(BL_THREADS == PG_THREADS, "the low-latency all-reduce phases are written for the GEMM kernels' CTA size");
+//          // warps 0-7 expand weights (0-3 also run the epilogue), 8 loads, 9 issues the MMAs
 
 // A CTA's K chain is bound by latency, not by bandwidth (measured: the same time per K block for 8 and for 128
 // activation rows): the time per K block is the round trip stage-freed -> loads issued -> data landed, divided by
@@ -134,13 +137,15 @@ __device__ __forceinline__ int4 expand16(uint32_t w) {
 }
 
 // WTMA: the packed weights are fetched by TMA (needs K % 64 == 0 and a 16-byte aligned matrix); otherwise by plain loads.
-template <int BN, class T, bool WTMA>
-__global__ void __launch_bounds__(BL_THREADS)
-bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+// LLMODE: 0 = the tile is finished and stored by this CTA (or by its cluster); 1 / 2 = row-parallel projection under
+// tensor parallelism: the scaled tile goes to the row owners as {data, sequence} words (phase A of the low-latency
+// all-reduce, gemm_ll_phases.cuh) and the kernel goes on to reduce, broadcast (peer stores / multimem.st) and unpack.
+template <int BN, class T, bool WTMA, int LLMODE>
+__device__ __forceinline__ void bitlinear_cta(const CUtensorMap& map_x, const CUtensorMap& map_w,
                  const uint8_t* __restrict__ w_packed,
                  const float* __restrict__ x_scale, float w_scale, const T* __restrict__ bias, T* __restrict__ out,
                  int M, int N, int K, uint32_t idesc, uint32_t* status, const int* slot_state, long slot_stride,
-                 int4* __restrict__ partials) {
+                 int4* __restrict__ partials, const LLArgs& ll) {
   using L = BitSmem<BN>;
   constexpr int BL_STAGES = L::STAGES, WS = L::WSTAGES;
   extern __shared__ uint8_t dyn_smem[];
@@ -285,7 +290,25 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       acc_ok = __all_sync(0xffffffffu, acc_ok);
       tc_fence_after_sync();
       const int gm = m0 + threadIdx.x;
-      if (acc_ok && S > 1) {
+      if (LLMODE != 0) {
+        if (acc_ok) {
+          uint32_t seq;
+          size_t poff;
+          ll_resolve(ll, seq, poff);
+          const float rs = gm < M ? x_scale[gm] * w_scale : 0.f;
+          uint8_t* stage_w = tiles + warp * (32 * 80);         // the stage ring is idle: every MMA has completed
+#pragma unroll 1
+          for (int col = 0; col < BN; col += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + (uint32_t(warp * 32) << 16) + uint32_t(col), r);
+            tmem_ld_wait();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = float(int(r[i])) * rs;
+            ll_scatter_chunk<T>(ll, seq, poff, ll.rank, gm, n0 + col, v, stage_w);
+          }
+        }
+      } else if (acc_ok && S > 1) {
         // this slice's partial tile -> the workspace, 16 bytes per (4 columns, row): the rows of a warp are
         // consecutive, so a warp stores (and later loads) 512 contiguous bytes.  Written after the dependency wait:
         // the previous kernel on the stream may be another call that uses the same workspace.
@@ -466,6 +489,22 @@ bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   }
 }
 
+template <int BN, class T, bool WTMA, int LLMODE>
+__global__ void __launch_bounds__(BL_THREADS)
+bitlinear_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const uint8_t* __restrict__ w_packed, const float* __restrict__ x_scale, float w_scale,
+                 const T* __restrict__ bias, T* __restrict__ out, int M, int N, int K, uint32_t idesc, uint32_t* status,
+                 const int* slot_state, long slot_stride, int4* __restrict__ partials, const __grid_constant__ LLArgs ll) {
+  if (LLMODE == 0 || (ll.phases & 1))
+    bitlinear_cta<BN, T, WTMA, LLMODE>(map_x, map_w, w_packed, x_scale, w_scale, bias, out, M, N, K, idesc, status,
+                                       slot_state, slot_stride, partials, ll);
+  if constexpr (LLMODE != 0) {
+    __shared__ float s_red[8 * 16];
+    __syncthreads();
+    ll_phases<T, LLMODE == 2>(ll, status, s_red);
+  }
+}
+
 // Offline packing on the device: int8 values in {-1,0,1} [rows, K] -> [rows, K/4] codes.
 __global__ void ternary_pack_kernel(const int8_t* __restrict__ v, uint8_t* __restrict__ packed, long rows, int K) {
   const long total = rows * (K >> 2);
@@ -486,7 +525,8 @@ static int launch_bitlinear(const CUtensorMap& mx, const CUtensorMap& mw, const 
                             const void* bias, void* out, int M, int N, int K, int S, uint32_t* status, cudaStream_t stream,
                             const int* slot_state, long slot_stride, void* workspace) {
   using L = BitSmem<BN>;
-  auto kern = bitlinear_kernel<BN, T, WTMA>;
+  auto kern = bitlinear_kernel<BN, T, WTMA, 0>;
+  LLArgs no_ll = {};
   static bool configured[MAX_DEVICES] = {false};
   if (first_use_on_device(configured)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
@@ -508,7 +548,7 @@ static int launch_bitlinear(const CUtensorMap& mx, const CUtensorMap& mw, const 
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
   prefer_max_shared(reinterpret_cast<const void*>(kern));
   cudaError_t err = cudaLaunchKernelEx(&cfg, kern, mx, mw, (const uint8_t*)w, xs, ws, (const T*)bias, (T*)out, M, N, K,
-                                       idesc, status, slot_state, slot_stride, static_cast<int4*>(workspace));
+                                       idesc, status, slot_state, slot_stride, static_cast<int4*>(workspace), no_ll);
   return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
 }
 
@@ -644,6 +684,59 @@ extern "C" int ronn_bitlinear_to_slot(const void* xq, const void* w_packed, cons
   if (slot_state == nullptr || out_base == nullptr) return -1;
   return bitlinear_impl(xq, w_packed, x_scale, w_scale, nullptr, out_base, M, N, K, ldx, dtype, slot_state, slot_stride,
                         workspace, status, stream);
+}
+
+template <int BN, class T, int LLMODE>
+static int launch_bitlinear_ll(const CUtensorMap& mx, const CUtensorMap& mw, const RonnBitLinearLLParams* p, LLArgs& a,
+                               uint32_t* status, cudaStream_t stream) {
+  using L = BitSmem<BN>;
+  auto kern = bitlinear_kernel<BN, T, true, LLMODE>;
+  static bool configured[MAX_DEVICES] = {false};
+  if (first_use_on_device(configured)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_SMEM) != cudaSuccess) return -10;
+  }
+  const int M = a.M, N = a.N, K = p->ll.K;
+  const int grid_x = (N + BN - 1) / BN, grid_y = (M + 127) / 128;
+  // phases B and C wait on work of the whole grid and of the peers: every CTA must be resident at once
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, BL_THREADS, L::DYN_SMEM) != cudaSuccess || per_sm < 1)
+    return -12;
+  if (grid_x * grid_y > device_sm_count() * per_sm) return -12;
+  a.wpr = ll_pick_wpr(M, N, grid_x * grid_y);
+  if (a.wpr == 0) return -5;
+  const uint32_t idesc = umma_idesc(128, BN, 1u, 2u);
+  cudaError_t err = launch(kern, dim3(grid_x, grid_y, 1), dim3(BL_THREADS), size_t(L::DYN_SMEM), stream, mx, mw,
+                           static_cast<const uint8_t*>(p->w_packed), p->x_scale, p->w_scale, static_cast<const T*>(nullptr),
+                           static_cast<T*>(nullptr), M, N, K, idesc, status, static_cast<const int*>(nullptr), 0l,
+                           static_cast<int4*>(nullptr), a);
+  return (err == cudaSuccess && cudaGetLastError() == cudaSuccess) ? 0 : -11;
+}
+
+// Row-parallel BitLinear of a tensor-parallel rank fused with the cross-rank sum, residual add (and norm) in ONE launch:
+// int8 activations [M, K] of this rank's K shard x packed ternary weights [N, K / 4], the scaled partial rows travel
+// as {data, sequence} words (see gemm_ll.h for the areas and the protocol).  K % 64 == 0, N % 32 == 0, the grid
+// (N / 32 or N / 64 tiles) must fit the SMs.  Returns -12 when it does not: the caller then uses the two-launch path.
+extern "C" int ronn_bitlinear_ll(const RonnBitLinearLLParams* p, uint32_t* status, cudaStream_t stream) {
+  if (!p || !p->xq || !p->w_packed || !p->x_scale) return -1;
+  const int M = p->ll.M, N = p->ll.N, K = p->ll.K;
+  if (K <= 0 || (K & 63) || (p->ldx & 15) || (reinterpret_cast<uintptr_t>(p->w_packed) & 15)) return -2;
+  LLArgs a;
+  if (const int rc = ll_fill_args(&p->ll, a)) return rc;
+  if (p->ll.scatter_parity_stride < long(p->ll.world) * a.owner_rows * N * 4 || p->ll.result_parity_stride < long(M) * N * 4)
+    return -8;
+  const int mt = (M + 127) / 128, sms = device_sm_count();
+  const int bn = mt * ((N + 31) / 32) <= sms ? 32 : 64;
+  CUtensorMap mx, mw;
+  int rc = make_tmap_2d(&mx, p->xq, uint64_t(M), uint64_t(K), uint64_t(p->ldx), 128, 128, 1);
+  if (rc) return rc - 20;
+  rc = make_tmap_2d(&mw, p->w_packed, uint64_t(N), uint64_t(K >> 2), uint64_t(K >> 2), uint32_t(bn), 128, 1);
+  if (rc) return rc - 30;
+  const bool bf = p->ll.dtype == 0;
+#define RONN_BLL(BN_, T_) (a.nvls ? launch_bitlinear_ll<BN_, T_, 2>(mx, mw, p, a, status, stream) \
+                                  : launch_bitlinear_ll<BN_, T_, 1>(mx, mw, p, a, status, stream))
+  if (bn == 32) return bf ? RONN_BLL(32, __nv_bfloat16) : RONN_BLL(32, __half);
+  return bf ? RONN_BLL(64, __nv_bfloat16) : RONN_BLL(64, __half);
+#undef RONN_BLL
 }
 
 extern "C" int ronn_ternary_pack(const void* values, void* packed, long rows, int K, cudaStream_t stream) {

@@ -49,6 +49,20 @@ typedef struct RonnGemmLLParams {
 
 int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStream_t stream);
 
+// The same protocol behind the ternary x int8 BitLinear GEMM (bitnet.cu).  `ll` carries M, N, K (this rank's K shard,
+// K % 64 == 0), dtype of the output, the areas, state, rank / world / nvls, out, residual, norm and wait fields; its
+// A, W, lda, ldw, bn and splitk fields are not used.
+typedef struct RonnBitLinearLLParams {
+  const void* xq;                // int8 activations [M, K], row stride ldx bytes (ldx % 16 == 0)
+  const void* w_packed;          // [N, K / 4] two-bit codes, 16-byte aligned
+  const float* x_scale;          // [M] per-token scales of this rank's activation shard
+  float w_scale;
+  int ldx;
+  RonnGemmLLParams ll;
+} RonnBitLinearLLParams;
+
+int ronn_bitlinear_ll(const RonnBitLinearLLParams* p, uint32_t* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,12 @@ class LLParams(C.Structure):
     ]
 
 
+class BitLinearLLParams(C.Structure):
+    """Mirror of ``RonnBitLinearLLParams`` (csrc/kernels/gemm_ll.h)."""
+    _fields_ = [("xq", C.c_void_p), ("w_packed", C.c_void_p), ("x_scale", C.c_void_p), ("w_scale", C.c_float),
+                ("ldx", C.c_int), ("ll", LLParams)]
+
+
 _NORM = {"": 0, None: 0, "none": 0, "layernorm": 1, "rmsnorm": 2}
 _LOCAL = {}
 
@@ -64,6 +70,8 @@ def _lib():
         lib.ronn_gemm_fuse_flag_ints.restype = C.c_int
         lib.ronn_gemm_ll.restype = C.c_int
         lib.ronn_gemm_ll.argtypes = [C.POINTER(LLParams), C.c_void_p, C.c_void_p]
+        lib.ronn_bitlinear_ll.restype = C.c_int
+        lib.ronn_bitlinear_ll.argtypes = [C.POINTER(BitLinearLLParams), C.c_void_p, C.c_void_p]
         lib._fuse_declared = True
     return lib
 

@@ -99,6 +99,7 @@ class FusedComm(TPComm):
             raise ProviderError(f"unknown tensor-parallel protocol '{self.proto}'")
         self._init_two_shot(symm, pg, nvls)
         self.fused_calls = 0
+        self.bitlinear_ll = os.environ.get("RONN_BITLINEAR_LL", "1") != "0"      # one-launch row-parallel BitLinear
         self.one_shot_elems = int(os.environ.get("RONN_ONE_SHOT_ELEMS", 2 << 20))
         self.argmax_exchange = self.world > 1 and os.environ.get("RONN_ARGMAX_EXCHANGE", "1") != "0"
         # Push pays when there is one peer (measured, GPT-2 medium decode: TP=2 85-88K tokens/s against 80K with the pull
@@ -257,6 +258,45 @@ class FusedComm(TPComm):
             s -= 1
         return s
 
+    def _ll_fill_areas(self, p) -> None:
+        """Areas, epoch word, rank / world and the NVLS choice of a low-latency call (``LLParams``)."""
+        res_off = self._ll_off + 2 * self._ll_scatter_stride
+        for r in range(self.world):
+            p.scatter_area[r] = self._ptrs2[r] + self._ll_off
+            p.result_area[r] = self._ptrs2[r] + res_off
+        use_mc = self.nvls and self.nvls_available
+        p.result_mc = (self._mc2 + res_off) if use_mc else None
+        p.scatter_parity_stride, p.result_parity_stride = self._ll_scatter_stride, self._ll_result_stride
+        p.state = self._ll_state.data_ptr()
+        p.rank, p.world, p.nvls = self.rank, self.world, 1 if use_mc else 0
+        p.wait_seconds = self.wait_seconds
+        p.trace = None if self.trace is None else self.trace.data_ptr()
+
+    def _bitlinear_ll(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual):
+        """Row-parallel BitLinear + cross-rank sum + residual in ONE launch (low-latency protocol).  Returns None when
+        the launcher says the shape does not fit (grid larger than the SMs): the caller takes the two-launch path."""
+        from ..ops import fuse as F
+        M = q.shape[0]
+        out = torch.empty((M, n), dtype=out_dtype, device=q.device)
+        if residual is not None and (residual.stride(1) != 1 or residual.shape != out.shape):
+            residual = residual.reshape(M, n).contiguous()
+        bp = F.BitLinearLLParams()
+        bp.xq, bp.w_packed, bp.x_scale = q.data_ptr(), w_packed.data_ptr(), x_scale.data_ptr()
+        bp.w_scale, bp.ldx = float(w_scale), q.stride(0)
+        p = bp.ll
+        p.M, p.N, p.K, p.dtype = M, n, k, 0 if out_dtype == torch.bfloat16 else 1
+        self._ll_fill_areas(p)
+        p.out, p.ld_out = out.data_ptr(), out.stride(0)
+        if residual is not None:
+            p.residual, p.ld_res = residual.data_ptr(), residual.stride(0)
+        rc = F._lib().ronn_bitlinear_ll(C.byref(bp), K.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        if rc == -12:
+            return None
+        if rc != 0:
+            raise K.KernelError(f"bitlinear_ll (world {self.world}) failed with code {rc}")
+        self.fused_calls += 1
+        return out
+
     def _gemm_ll(self, a, w_nk, bias, residual, norm, bn: int = 0):
         from ..ops import fuse as F
         M, Kd = a.shape
@@ -270,15 +310,7 @@ class FusedComm(TPComm):
         p.A, p.W = a.data_ptr(), w_nk.data_ptr()
         p.M, p.N, p.K, p.lda, p.ldw = M, N, Kd, a.stride(0), w_nk.stride(0)
         p.bn, p.dtype, p.splitk = bn, 0 if a.dtype == torch.bfloat16 else 1, self._ll_splitk(M, N, Kd)
-        res_off = self._ll_off + 2 * self._ll_scatter_stride
-        for r in range(self.world):
-            p.scatter_area[r] = self._ptrs2[r] + self._ll_off
-            p.result_area[r] = self._ptrs2[r] + res_off
-        use_mc = self.nvls and self.nvls_available
-        p.result_mc = (self._mc2 + res_off) if use_mc else None
-        p.scatter_parity_stride, p.result_parity_stride = self._ll_scatter_stride, self._ll_result_stride
-        p.state = self._ll_state.data_ptr()
-        p.rank, p.world, p.nvls = self.rank, self.world, 1 if use_mc else 0
+        self._ll_fill_areas(p)
         p.out, p.ld_out = out.data_ptr(), out.stride(0)
         p.bias = None if bias is None else bias.data_ptr()
         if residual is not None:
@@ -386,12 +418,19 @@ class FusedComm(TPComm):
 
     # ------------------------------------------------------------------ BitLinear partials + cross-rank reduction
     def bitlinear_allreduce(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual=None):
-        """Row-parallel BitLinear: the ternary x int8 GEMM kernel writes this rank's [M, n] partial result straight into
-        the current slot of the symmetric partial buffer (slot chosen on the device), and the reduction kernel sums the
-        ranks' partials over NVLink peer memory in rank order and adds the residual.  Two launches, no library
-        collective, bit-identical on every rank."""
+        """Row-parallel BitLinear + cross-rank sum + residual, bit-identical on every rank, no library collective.
+        Under the low-latency protocol ONE launch: the BitLinear kernel's epilogue scatters its scaled rows to their
+        owner ranks as {data, sequence} words and goes on to reduce, broadcast and unpack (``ronn_bitlinear_ll``;
+        ``RONN_BITLINEAR_LL=0`` turns it off).  Otherwise two launches: the kernel writes this rank's [M, n] partial
+        straight into the current slot of the symmetric partial buffer (slot chosen on the device) and the reduction
+        kernel sums the ranks' partials over NVLink peer memory in rank order."""
         from ..ops.bitnet import _check as _bcheck
         M = q.shape[0]
+        if (self.proto == "ll" and self.bitlinear_ll and self._ll_ok(M, n) and k % 64 == 0
+                and w_packed.data_ptr() % 16 == 0):
+            y = self._bitlinear_ll(q, x_scale, w_packed, w_scale, n, k, out_dtype, residual)
+            if y is not None:
+                return y
         if M * n > self.max_elems:
             raise ProviderError(f"fused BitLinear of {M}x{n} exceeds the symmetric buffer ({self.max_elems} elements)")
         lib = _native.cuda()

@@ -62,25 +62,33 @@ def main():
                     ys = comm.gemm_reduce_scatter(a, w, bias, res[rank * per:(rank + 1) * per])
                     errs = (ys.float() - ref[rank * per:(rank + 1) * per]).abs().max().item()
                     results.append({"mode": "rs" + tag, "M": M, "N": N, "K": Kl, "err": errs, "identical": True})
-    comm.proto, comm.nvls, comm.push = "pull", False, False
-    # row-parallel BitLinear: ternary x int8 partials written into the symmetric slot, reduced over peer memory
+    # row-parallel BitLinear: two launches (ternary x int8 partials written into the symmetric slot + reduction over peer
+    # memory) under the pull protocol, ONE launch under the low-latency protocol (peer stores, then multimem stores)
     from ronn_b200.ops import bitnet as KB
-    for (M, N, Kl) in [(128, 2560, 320), (37, 512, 256), (128, 1024, 864)]:
-        for it in range(2):
-            x = torch.randn(M, Kl, device=dev).bfloat16()
-            wq = torch.randint(-1, 2, (N, Kl), device=dev, dtype=torch.int8)
-            packed = KB.ternary_pack(wq)
-            res = torch.randn(M, N, device=dev).bfloat16()
-            dist.broadcast(res, 0)
-            q, sc = KB.act_quant_int8(x)
-            y = comm.bitlinear_allreduce(q, sc, packed, 0.05, N, Kl, torch.bfloat16, res)
-            part = KB.bitlinear_q(q, sc, packed, 0.05, None, N, Kl, torch.bfloat16).float()   # the same bf16 partial
-            dist.all_reduce(part)
-            ref = part + res.float()
-            y0 = y.clone()
-            dist.broadcast(y0, 0)
-            results.append({"mode": "bitlinear+ar", "M": M, "N": N, "K": Kl, "err": (y.float() - ref).abs().max().item(),
-                            "identical": bool(torch.equal(y0, y))})
+    for proto, nv in (("pull", False), ("ll", False), ("ll", True)):
+        if nv and not comm.nvls_available:
+            continue
+        comm.proto, comm.nvls, comm.push, comm.bitlinear_ll = proto, nv, False, True
+        for (M, N, Kl) in [(128, 2560, 320), (37, 512, 256), (128, 1024, 864), (200, 2560, 896)]:
+            for it in range(3):
+                x = torch.randn(M, Kl, device=dev).bfloat16()
+                wq = torch.randint(-1, 2, (N, Kl), device=dev, dtype=torch.int8)
+                packed = KB.ternary_pack(wq)
+                res = torch.randn(M, N, device=dev).bfloat16()
+                dist.broadcast(res, 0)
+                q, sc = KB.act_quant_int8(x)
+                before = comm.fused_calls
+                y = comm.bitlinear_allreduce(q, sc, packed, 0.05, N, Kl, torch.bfloat16, res)
+                one_launch = proto == "ll" and Kl % 64 == 0
+                part = KB.bitlinear_q(q, sc, packed, 0.05, None, N, Kl, torch.bfloat16).float()   # the same bf16 partial
+                dist.all_reduce(part)
+                ref = part + res.float()
+                y0 = y.clone()
+                dist.broadcast(y0, 0)
+                results.append({"mode": f"bitlinear+ar/{proto}{'/nvls' if nv else ''}", "M": M, "N": N, "K": Kl,
+                                "err": (y.float() - ref).abs().max().item(),
+                                "identical": bool(torch.equal(y0, y)) and (not one_launch or comm.fused_calls == before + 1)})
+    comm.proto, comm.nvls, comm.push = "pull", False, False
     # sharded greedy sampling: (index, max) pairs exchanged through sequence-numbered words, against the gathered form
     from ronn_b200.ops import kernels as KK
     for rows in (300, 7, 1024):

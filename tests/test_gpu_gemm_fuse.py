@@ -161,3 +161,54 @@ def test_gemm_ll_many_ranks_emulated_on_one_gpu(world, S, M, N, Kr):
         hk = F.layer_norm(outs[0].float(), (N,), gamma.float(), beta.float(), 1e-5)
         torch.testing.assert_close(hs[0].float(), hk, atol=6e-2, rtol=3e-2)
         assert all(int(s[0]) == (it + 1) << 16 for s in state)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("M,N,Kr", [(128, 2560, 320), (37, 512, 256), (200, 1024, 896)])
+def test_bitlinear_ll_many_ranks_emulated_on_one_gpu(world, M, N, Kr):
+    """Row-parallel BitLinear fused with the low-latency all-reduce, 2 to 8 ranks on ONE device (every rank's areas in
+    this GPU's memory, the three parts of a call as separate launches): against the sum of the ranks' bf16 partial
+    products from the stand-alone BitLinear kernel plus the residual."""
+    import ctypes as C
+
+    from ronn_b200.ops import bitnet as KB
+    from ronn_b200.ops import fuse as FU
+    from ronn_b200.ops import kernels as K
+    dev = torch.device("cuda", 0)
+    owner_rows = (M + world - 1) // world
+    sc_stride, rs_stride = world * owner_rows * N * 4, M * N * 4
+    scatter = [torch.zeros(2 * sc_stride, dtype=torch.uint8, device=dev) for _ in range(world)]
+    result = [torch.zeros(2 * rs_stride, dtype=torch.uint8, device=dev) for _ in range(world)]
+    state = [torch.zeros(4, dtype=torch.int64, device=dev) for _ in range(world)]
+    res = _rand(M, N)
+    lib = FU._lib()
+    for it in range(3):
+        qs, ss, ws = [], [], []
+        for r in range(world):
+            q, s = KB.act_quant_int8(_rand(M, Kr))
+            qs.append(q)
+            ss.append(s)
+            ws.append(KB.ternary_pack(torch.randint(-1, 2, (N, Kr), device=dev, dtype=torch.int8)))
+        outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        for phase in (1, 2, 4):
+            for r in range(world):
+                bp = FU.BitLinearLLParams()
+                bp.xq, bp.w_packed, bp.x_scale, bp.w_scale, bp.ldx = qs[r].data_ptr(), ws[r].data_ptr(), ss[r].data_ptr(), 0.05, Kr
+                p = bp.ll
+                p.M, p.N, p.K, p.dtype = M, N, Kr, 0
+                for w in range(world):
+                    p.scatter_area[w] = scatter[w].data_ptr()
+                    p.result_area[w] = result[w].data_ptr()
+                p.scatter_parity_stride, p.result_parity_stride = sc_stride, rs_stride
+                p.state, p.rank, p.world, p.nvls = state[r].data_ptr(), r, world, 0
+                p.out, p.ld_out = outs[r].data_ptr(), N
+                p.residual, p.ld_res = res.data_ptr(), N
+                p.wait_seconds, p.phases = 0.25, phase
+                rc = lib.ronn_bitlinear_ll(C.byref(bp), K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
+                assert rc == 0, rc
+        K.check_status()
+        want = sum(KB.bitlinear_q(qs[r], ss[r], ws[r], 0.05, None, N, Kr, torch.bfloat16).float() for r in range(world)) + res.float()
+        for r in range(world):
+            assert torch.equal(outs[r], outs[0])
+        scale = float(want.abs().max())
+        torch.testing.assert_close(outs[0].float(), want, atol=1e-2 * scale, rtol=1e-2)
