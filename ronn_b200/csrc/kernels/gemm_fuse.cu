@@ -206,6 +206,44 @@ __device__ __forceinline__ void fuse_gather8(const FuseArgs& a, size_t off, floa
   }
 }
 
+// The same sums for CH chunks of one row at once.  A peer load is a round trip of several microseconds under load:
+// the loads of all chunks of a source are issued before the first value is used, 2 CH 16-byte loads in flight per
+// lane, where chunk-after-chunk gathers made a row cost CH round trips (measured: 80 us for the
+// owner-side reduction of 4096 x 1024 rows at two ranks).
+template <int MODE, int CH>
+__device__ __forceinline__ void fuse_gather_multi(const FuseArgs& a, const size_t (&off)[CH], const bool (&valid)[CH],
+                                                  float (&acc)[CH][8]) {
+  const size_t slice = size_t(a.M) * a.N;
+  const int total = MODE == FUSE_P2P ? a.S * a.world : a.S;
+#pragma unroll
+  for (int i = 0; i < CH; ++i)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[i][k] = 0.f;
+  for (int idx = 0; idx < total; ++idx) {
+    float4 lo[CH], hi[CH];
+#pragma unroll
+    for (int i = 0; i < CH; ++i)
+      if (valid[i]) {
+        if (MODE == FUSE_NVLS) {
+          const float* p = a.part_mc + off[i] + size_t(idx) * slice;
+          lo[i] = multimem_ld_reduce_f32x4(p);
+          hi[i] = multimem_ld_reduce_f32x4(p + 4);
+        } else {
+          const float* p = MODE == FUSE_P2P ? a.part_peer[idx % a.world] + off[i] + size_t(idx / a.world) * slice
+                                            : a.part_local + off[i] + size_t(idx) * slice;
+          lo[i] = ld_volatile_f4(p);
+          hi[i] = ld_volatile_f4(p + 4);
+        }
+      }
+#pragma unroll
+    for (int i = 0; i < CH; ++i)
+      if (valid[i]) {
+        acc[i][0] += lo[i].x; acc[i][1] += lo[i].y; acc[i][2] += lo[i].z; acc[i][3] += lo[i].w;
+        acc[i][4] += hi[i].x; acc[i][5] += hi[i].y; acc[i][6] += hi[i].z; acc[i][7] += hi[i].w;
+      }
+  }
+}
+
 // 16 bytes of an output row: the local copy, or one copy per rank.
 template <int MODE>
 __device__ __forceinline__ void fuse_store16(const FuseArgs& a, uint8_t* const (&peer)[FUSE_MAX_RANKS], uint8_t* mc,
@@ -307,22 +345,40 @@ struct FuseRows {
       const int out_row = a.scatter ? r : gr;
       float v[CH][8];
       float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-      for (int i = 0; i < CH; ++i) {
-        const int c8 = l + L * i;
+      if (CH == 1) {
+        const int c8 = l;
         if (c8 < n8) {
           float acc[8];
-          Vec8 lb, lr;
-          if (!PRE) {
-            if (a.bias) lb = *reinterpret_cast<const Vec8*>(reinterpret_cast<const T*>(a.bias) + c8 * 8);
-            if (a.residual)
-              lr = *reinterpret_cast<const Vec8*>(reinterpret_cast<const T*>(a.residual) + size_t(out_row) * a.ld_res + c8 * 8);
-          }
           fuse_gather8<MODE>(a, parity_off + size_t(gr) * a.N + c8 * 8, acc);
-          fuse_finish8<T, MODE>(a, acc, PRE ? pb[i] : lb, PRE ? pr[i] : lr, out_row, c8 * 8, v[i]);
+          fuse_finish8<T, MODE>(a, acc, pb[0], pr[0], out_row, c8 * 8, v[0]);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) { s1 += v[i][k]; s2 += v[i][k] * v[i][k]; }
+          for (int k = 0; k < 8; ++k) { s1 += v[0][k]; s2 += v[0][k] * v[0][k]; }
         }
+      } else {
+        // wide rows: the partial sums of all chunks and the side operands are requested together
+        size_t off[CH];
+        bool valid[CH];
+        Vec8 lb[CH], lr[CH];
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+          const int c8 = l + L * i;
+          valid[i] = c8 < n8;
+          off[i] = parity_off + size_t(gr) * a.N + c8 * 8;
+          if (valid[i]) {
+            if (a.bias) lb[i] = *reinterpret_cast<const Vec8*>(reinterpret_cast<const T*>(a.bias) + c8 * 8);
+            if (a.residual)
+              lr[i] = *reinterpret_cast<const Vec8*>(reinterpret_cast<const T*>(a.residual) + size_t(out_row) * a.ld_res + c8 * 8);
+          }
+        }
+        float acc[CH][8];
+        fuse_gather_multi<MODE, CH>(a, off, valid, acc);
+#pragma unroll
+        for (int i = 0; i < CH; ++i)
+          if (valid[i]) {
+            fuse_finish8<T, MODE>(a, acc[i], lb[i], lr[i], out_row, (l + L * i) * 8, v[i]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { s1 += v[i][k]; s2 += v[i][k] * v[i][k]; }
+          }
       }
       if (a.norm_mode != 0) {
         float mean = 0.f, inv;
