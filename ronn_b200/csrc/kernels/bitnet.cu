@@ -89,6 +89,57 @@ __global__ void act_quant_kernel(const T* __restrict__ x, const T* __restrict__ 
   if (threadIdx.x == 0) scale[row] = __fdiv_rn(m, 127.f);
 }
 
+// SwiGLU on a fused [rows, 2 F] gate | up projection followed by the per-token int8 quantisation of the result, in one
+// pass: v = silu(gate) * up (rounded through the storage type, as the two-kernel form stores it), q = rint(v * 127 /
+// max|v|).  Saves the [rows, F] round trip through memory and a launch in front of the down projection.
+// F % 16 == 0, F <= 16 * 4 * blockDim.
+template <class T>
+__global__ void swiglu_quant_kernel(const T* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ scale, int F) {
+  __shared__ float scratch[32];
+  pdl_wait();
+  pdl_trigger();
+  const long row = blockIdx.x;
+  const T* g = x + row * 2 * F;
+  const T* u = g + F;
+  const int nchunk = F >> 4;
+  float v[4][16];
+  float m = 0.f;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float a[8], b[8];
+        unpack8<T>(*reinterpret_cast<const Vec8*>(g + ch * 16 + h * 8), a);
+        unpack8<T>(*reinterpret_cast<const Vec8*>(u + ch * 16 + h * 8), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float t = Cvt<T>::to_f(Cvt<T>::from_f(a[i] / (1.f + __expf(-a[i])) * b[i]));
+          v[c][h * 8 + i] = t;
+          m = fmaxf(m, fabsf(t));
+        }
+      }
+    }
+  }
+  m = fmaxf(block_max(m, scratch), 1e-5f);
+  const float qs = __fdiv_rn(127.f, m);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int ch = threadIdx.x + c * blockDim.x;
+    if (ch < nchunk) {
+      alignas(16) int8_t o[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float r = fminf(fmaxf(rintf(__fmul_rn(v[c][i], qs)), -127.f), 127.f);
+        o[i] = int8_t(int(r));
+      }
+      *reinterpret_cast<int4*>(q + row * F + ch * 16) = *reinterpret_cast<const int4*>(o);
+    }
+  }
+  if (threadIdx.x == 0) scale[row] = __fdiv_rn(m, 127.f);
+}
+
 // ---------------------------------------------------------------------------------------- BitLinear GEMM
 constexpr int BL_THREADS = 320;
 static_assert(BL_THREADS == PG_THREADS, "the low-latency all-reduce phases are written for the GEMM kernels' CTA size");
@@ -635,6 +686,19 @@ extern "C" long ronn_bitlinear_workspace_bytes(int M, int N, int K) {
   bitlinear_plan(M, N, K, true, bn, S);
   if (S == 1) return 0;
   return long((M + 127) / 128) * ((N + bn - 1) / bn) * S * bn * 512;
+}
+
+// x: [rows, 2 F] (gate | up), dtype 0 bf16 / 1 fp16 -> q int8 [rows, F], scale fp32 [rows].
+extern "C" int ronn_swiglu_quant_int8(const void* x, void* q, float* scale, long rows, int F, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((F & 15) || F > 16 * 4 * 1024) return -2;
+  int threads = (((F >> 4) + 3) / 4 + 31) / 32 * 32;
+  if (threads < 32) threads = 32;
+  cudaError_t err;
+  if (dtype == 0) err = launch(swiglu_quant_kernel<__nv_bfloat16>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const __nv_bfloat16*)x, (int8_t*)q, scale, F);
+  else if (dtype == 1) err = launch(swiglu_quant_kernel<__half>, dim3(unsigned(rows)), dim3(threads), 0, stream, (const __half*)x, (int8_t*)q, scale, F);
+  else return -6;
+  return err == cudaSuccess ? 0 : -100;
 }
 
 // xq: int8 [M, K] (row stride ldx bytes); w_packed: [N, K/4]; x_scale: fp32 [M]; out: [M, N] in `dtype` (0 bf16, 1 fp16).

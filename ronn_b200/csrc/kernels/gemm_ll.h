@@ -36,7 +36,8 @@ typedef struct RonnGemmLLParams {
   const void* gamma;
   const void* beta;
   float eps;
-  int norm_mode;                 // 0 none, 1 LayerNorm, 2 RMSNorm (N <= 8192)
+  int norm_mode;                 // 0 none, 1 LayerNorm, 2 RMSNorm (N <= 8192), 3 RMSNorm * gamma then per-row int8
+                                 // quantisation into quant_out / quant_scale (what a BitLinear layer reads next)
   double wait_seconds;           // limit of every poll
   void* trace;                   // optional: 8 x uint64 %globaltimer stamps per CTA (entry, partials sent, -, owned rows
                                  // reduced and broadcast, all rows unpacked and normalised, -, -, exit)
@@ -45,6 +46,8 @@ typedef struct RonnGemmLLParams {
                                  // areas in ONE device's memory, the ranks of a call can then be run one after the
                                  // other (all ranks' part 1, then all part 2, then all part 4) and no launch waits
                                  // for a later one.  That is how W = 4 and 8 are checked on a single GPU.
+  void* quant_out;               // norm_mode 3: int8 [M, N] (row stride N bytes)
+  float* quant_scale;            // norm_mode 3: [M] scales (max |normalised row| / 127)
 } RonnGemmLLParams;
 
 int ronn_gemm_ll(const RonnGemmLLParams* p, uint32_t* status, cudaStream_t stream);

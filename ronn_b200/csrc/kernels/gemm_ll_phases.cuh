@@ -32,6 +32,8 @@ struct LLArgs {
   const void* gamma;
   const void* beta;
   unsigned long long* trace;
+  int8_t* quant_out;                     // norm_mode 3
+  float* quant_scale;
   unsigned long long wait_ns;
   long ld_out, ld_res;
   float eps;
@@ -227,7 +229,47 @@ __device__ __forceinline__ void ll_phases(const LLArgs& a, uint32_t* status, flo
           for (int k = 0; k < 8; ++k) { s1 += v[i][k]; s2 += v[i][k] * v[i][k]; }
         }
       }
-      if (a.norm_mode != 0) {
+      if (a.norm_mode == 3) {
+        // RMSNorm * gamma, rounded through the storage type, then the row's int8 quantisation: the next BitLinear
+        // layer reads (quant_out, quant_scale) directly
+        const float inv = rsqrtf(group_sum(s2, slot) / float(N) + a.eps);
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c8 = l + L * i;
+          if (c8 < n8) {
+            float g[8];
+            unpack8<T>(*reinterpret_cast<const Vec8*>(gamma + c8 * 8), g);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              v[i][k] = Cvt<T>::to_f(Cvt<T>::from_f(v[i][k] * inv * g[k]));
+              m = fmaxf(m, fabsf(v[i][k]));
+            }
+          }
+        }
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (wpr > 1) {
+          float* sl = slot + 8;
+          if (lane == 0) sl[warp % wpr] = m;
+          bar_sync_named(1 + grp, L);
+          m = 0.f;
+          for (int k = 0; k < wpr; ++k) m = fmaxf(m, sl[k]);
+        }
+        m = fmaxf(m, 1e-5f);
+        const float qs = __fdiv_rn(127.f, m);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int c8 = l + L * i;
+          if (c8 < n8) {
+            alignas(8) int8_t o8[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              o8[k] = int8_t(int(fminf(fmaxf(rintf(__fmul_rn(v[i][k], qs)), -127.f), 127.f)));
+            *reinterpret_cast<uint2*>(a.quant_out + size_t(r) * N + c8 * 8) = *reinterpret_cast<const uint2*>(o8);
+          }
+        }
+        if (l == 0) a.quant_scale[r] = __fdiv_rn(m, 127.f);
+      } else if (a.norm_mode != 0) {
         float mean = 0.f, inv;
         if (a.norm_mode == 2) {
           inv = rsqrtf(group_sum(s2, slot) / float(N) + a.eps);
@@ -281,7 +323,9 @@ inline int ll_fill_args(const RonnGemmLLParams* p, LLArgs& a) {
   const int M = p->M, N = p->N, world = p->world, rank = p->rank;
   if (M <= 0 || N <= 0 || world < 2 || world > LL_MAX_RANKS || rank < 0 || rank >= world) return -1;
   if ((N & 31) || (p->ld_out & 7) || (p->residual && (p->ld_res & 7))) return -2;
-  if (p->norm_mode != 0 && (p->norm_out == nullptr || p->norm_mode > 2)) return -5;
+  if (p->norm_mode < 0 || p->norm_mode > 3) return -5;
+  if ((p->norm_mode == 1 || p->norm_mode == 2) && p->norm_out == nullptr) return -5;
+  if (p->norm_mode == 3 && (!p->quant_out || !p->quant_scale || !p->gamma || (N & 7))) return -5;
   if (p->out == nullptr || p->state == nullptr) return -6;
   const int owner_rows = (M + world - 1) / world;
   for (int r = 0; r < world; ++r)
@@ -304,6 +348,8 @@ inline int ll_fill_args(const RonnGemmLLParams* p, LLArgs& a) {
   a.gamma = p->gamma;
   a.beta = p->beta;
   a.trace = static_cast<unsigned long long*>(p->trace);
+  a.quant_out = static_cast<int8_t*>(p->quant_out);
+  a.quant_scale = p->quant_scale;
   a.wait_ns = static_cast<unsigned long long>(p->wait_seconds * 1e9);
   a.ld_out = p->ld_out;
   a.ld_res = p->ld_res;

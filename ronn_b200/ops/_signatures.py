@@ -52,4 +52,5 @@ def declare(lib):
     sig("ronn_norm_quant_int8", [V, V, V, V, V, L, I, F, I, V], optional=True)
     sig("ronn_bitlinear", [V, V, V, F, V, V, V, I, I, I, I, I, V, V], optional=True)
     sig("ronn_bitlinear_workspace_bytes", [I, I, I], restype=L, optional=True)
+    sig("ronn_swiglu_quant_int8", [V, V, V, L, I, I, V], optional=True)
     sig("ronn_ternary_pack", [V, V, L, I, V], optional=True)

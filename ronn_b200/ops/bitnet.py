@@ -35,6 +35,18 @@ def rmsnorm_quant_int8(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-5):
     return q, s
 
 
+def swiglu_quant_int8(x: torch.Tensor):
+    """x = [rows, 2F] (gate | up) -> int8 quantisation of silu(gate) * up in one pass: (q [rows, F], scale [rows])."""
+    F2 = x.shape[-1]
+    xc = x.reshape(-1, F2).contiguous()
+    rows, F = xc.shape[0], F2 // 2
+    q = torch.empty((rows, F), dtype=torch.int8, device=x.device)
+    s = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(_native.cuda().ronn_swiglu_quant_int8(xc.data_ptr(), q.data_ptr(), s.data_ptr(), rows, F, _DT[x.dtype], _stream()),
+           "swiglu_quant_int8")
+    return q, s
+
+
 _WS_BYTES = {}
 
 

@@ -48,6 +48,7 @@ class LLParams(C.Structure):
         ("bias", C.c_void_p), ("residual", C.c_void_p), ("ld_res", C.c_long),
         ("gamma", C.c_void_p), ("beta", C.c_void_p), ("eps", C.c_float), ("norm_mode", C.c_int),
         ("wait_seconds", C.c_double), ("trace", C.c_void_p), ("phases", C.c_int),
+        ("quant_out", C.c_void_p), ("quant_scale", C.c_void_p),
     ]
 
 

@@ -272,9 +272,11 @@ class FusedComm(TPComm):
         p.wait_seconds = self.wait_seconds
         p.trace = None if self.trace is None else self.trace.data_ptr()
 
-    def _bitlinear_ll(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual):
+    def _bitlinear_ll(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual, norm_quant=None):
         """Row-parallel BitLinear + cross-rank sum + residual in ONE launch (low-latency protocol).  Returns None when
-        the launcher says the shape does not fit (grid larger than the SMs): the caller takes the two-launch path."""
+        the launcher says the shape does not fit (grid larger than the SMs): the caller takes the two-launch path.
+        ``norm_quant=(gamma, eps)``: the unpack pass also applies RMSNorm * gamma and the per-token int8 quantisation
+        the next BitLinear layer needs; the result is then (out, q, scale)."""
         from ..ops import fuse as F
         M = q.shape[0]
         out = torch.empty((M, n), dtype=out_dtype, device=q.device)
@@ -289,13 +291,20 @@ class FusedComm(TPComm):
         p.out, p.ld_out = out.data_ptr(), out.stride(0)
         if residual is not None:
             p.residual, p.ld_res = residual.data_ptr(), residual.stride(0)
+        nq = ns = None
+        if norm_quant is not None:
+            gamma, eps = norm_quant
+            nq = torch.empty((M, n), dtype=torch.int8, device=q.device)
+            ns = torch.empty(M, dtype=torch.float32, device=q.device)
+            p.norm_mode, p.gamma, p.eps = 3, gamma.data_ptr(), float(eps)
+            p.quant_out, p.quant_scale = nq.data_ptr(), ns.data_ptr()
         rc = F._lib().ronn_bitlinear_ll(C.byref(bp), K.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
         if rc == -12:
             return None
         if rc != 0:
             raise K.KernelError(f"bitlinear_ll (world {self.world}) failed with code {rc}")
         self.fused_calls += 1
-        return out
+        return out if norm_quant is None else (out, nq, ns)
 
     def _gemm_ll(self, a, w_nk, bias, residual, norm, bn: int = 0):
         from ..ops import fuse as F
@@ -417,7 +426,8 @@ class FusedComm(TPComm):
         return tokens
 
     # ------------------------------------------------------------------ BitLinear partials + cross-rank reduction
-    def bitlinear_allreduce(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual=None):
+    def bitlinear_allreduce(self, q, x_scale, w_packed, w_scale: float, n: int, k: int, out_dtype, residual=None,
+                            norm_quant=None):
         """Row-parallel BitLinear + cross-rank sum + residual, bit-identical on every rank, no library collective.
         Under the low-latency protocol ONE launch: the BitLinear kernel's epilogue scatters its scaled rows to their
         owner ranks as {data, sequence} words and goes on to reduce, broadcast and unpack (``ronn_bitlinear_ll``;
@@ -428,7 +438,9 @@ class FusedComm(TPComm):
         M = q.shape[0]
         if (self.proto == "ll" and self.bitlinear_ll and self._ll_ok(M, n) and k % 64 == 0
                 and w_packed.data_ptr() % 16 == 0):
-            y = self._bitlinear_ll(q, x_scale, w_packed, w_scale, n, k, out_dtype, residual)
+            y = self._bitlinear_ll(q, x_scale, w_packed, w_scale, n, k, out_dtype, residual,
+                                   norm_quant if (norm_quant is not None and n % 8 == 0 and n <= 8192
+                                                  and norm_quant[0].dtype == out_dtype) else None)
             if y is not None:
                 return y
         if M * n > self.max_elems:

@@ -86,6 +86,19 @@ class LinearW:
         self._dense = None
 
 
+class QuantAct:
+    """Activations already quantised per token for a packed (ternary) projection: int8 values, fp32 scales and the
+    dtype the projection should produce."""
+    __slots__ = ("q", "s", "dtype")
+
+    def __init__(self, q, s, dtype):
+        self.q, self.s, self.dtype = q, s, dtype
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+
 class DecoderRunner:
     def __init__(self, arch: DecoderArch, initializers: Dict[str, torch.Tensor], cfg: EngineConfig,
                  device: torch.device, comm=None, num_blocks: Optional[int] = None):
@@ -173,18 +186,30 @@ class DecoderRunner:
         self.vcache = [torch.zeros(shape, dtype=self.dtype, device=self.device) for _ in range(a.n_layer)]
 
     # ------------------------------------------------------------------ forward
-    def _linear(self, x, lw: LinearW, residual=None, activation="", reduce=False, comm=None):
+    def _linear(self, x, lw: LinearW, residual=None, activation="", reduce=False, comm=None, norm_quant=None):
+        """``norm_quant=(gamma, eps)`` (packed row-parallel projections on the fused communicator): the reduction also
+        produces RMSNorm(result) quantised for the next packed projection; the return value is then
+        (result, QuantAct or None)."""
         ops = self.ops
         comm = comm or self.comm
         if lw.packed is not None:
             from ..providers.bitnet import kernels as BK
+            pre = x if isinstance(x, QuantAct) else None          # quantised by the kernel that produced the activations
+            out_dtype = pre.dtype if pre is not None else x.dtype
+            ws = float(lw.scale.reshape(-1)[0]) if isinstance(lw.scale, torch.Tensor) else float(lw.scale)
             if reduce and self.tp > 1 and getattr(comm, "fused", False) and ops.name == "kernels" and lw.bias is None:
-                # ternary GEMM into the symmetric partial slot + cross-rank reduction kernel over NVLink peer memory
+                # ternary GEMM + cross-rank reduction over NVLink (one launch under the low-latency protocol)
                 from ..ops import bitnet as KB
-                q, s = KB.act_quant_int8(x)
-                ws = float(lw.scale.reshape(-1)[0]) if isinstance(lw.scale, torch.Tensor) else float(lw.scale)
-                return comm.bitlinear_allreduce(q, s, lw.packed, ws, lw.n, lw.k, x.dtype, residual)
-            y = BK.bitlinear(x, lw, backend=ops.name)
+                q, s = (pre.q, pre.s) if pre is not None else KB.act_quant_int8(x)
+                r = comm.bitlinear_allreduce(q, s, lw.packed, ws, lw.n, lw.k, out_dtype, residual, norm_quant=norm_quant)
+                if norm_quant is None:
+                    return r
+                return (r[0], QuantAct(r[1], r[2], out_dtype)) if isinstance(r, tuple) else (r, None)
+            if pre is not None:
+                from ..ops import bitnet as KB
+                y = KB.bitlinear_q(pre.q, pre.s, lw.packed, ws, lw.bias, lw.n, lw.k, out_dtype)
+            else:
+                y = BK.bitlinear(x, lw, backend=ops.name)
             if reduce and self.tp > 1:
                 y = comm.all_reduce(y)
             if residual is not None:
@@ -253,7 +278,7 @@ class DecoderRunner:
         fused_tp = (ops.name == "kernels" and self.tp > 1 and getattr(comm, "fused", False) and not a.bitlinear
                     and a.hidden <= 1024)
 
-        def row_parallel(inp, lw, residual, norm_params, allow_split):
+        def row_parallel(inp, lw, residual, norm_params, allow_split, quant_next=False):
             """Row-parallel projection + residual.  Returns (new residual stream, normalised copy or None): on the
             fused paths the reduction pass already holds whole rows, so it applies the next norm as well."""
             if fused_tp:
@@ -265,6 +290,10 @@ class DecoderRunner:
                 return ops.gemm_rownorm(inp, lw, residual, norm_params, a.norm, a.eps)
             if allow_split and split_down:
                 return ops.gemm_splitk_norm(inp, lw, residual, norm_params, a.norm, a.eps, 4)
+            if (quant_next and lw.packed is not None and norm_params is not None and a.norm == "rmsnorm" and self.tp > 1
+                    and getattr(comm, "fused", False) and ops.name == "kernels" and lw.bias is None):
+                # the reduction's unpack pass also normalises and quantises for the packed projection that reads next
+                return self._linear(inp, lw, residual=residual, reduce=True, comm=comm, norm_quant=(norm_params[0], a.eps))
             return self._linear(inp, lw, residual=residual, reduce=True, comm=comm), None
 
         h_next = None
@@ -290,9 +319,16 @@ class DecoderRunner:
                                               self.n_head_local, self.n_kv_local, d, max_ctx, bt_row)
             if li == 0 and on_first_attention is not None:
                 on_first_attention()
-            x, h = row_parallel(att, L["out"], x, L["ln2"], False)
-            if h is None and a.mlp != "gelu" and L["up"].packed is not None:
-                f = ops.swiglu_fused(self._norm_linear(x, L["ln2"], L["up"]))
+            x, h = row_parallel(att, L["out"], x, L["ln2"], False, quant_next=L["up"].packed is not None)
+            if (h is None or isinstance(h, QuantAct)) and a.mlp != "gelu" and L["up"].packed is not None:
+                gu = self._linear(h, L["up"]) if isinstance(h, QuantAct) else self._norm_linear(x, L["ln2"], L["up"])
+                if (ops.name == "kernels" and L["down"].packed is not None and gu.is_cuda and (gu.shape[-1] // 2) % 16 == 0
+                        and gu.shape[-1] // 2 == L["down"].k and gu.shape[-1] // 2 <= 65536):
+                    # SwiGLU and the int8 quantisation in front of the down projection as one kernel
+                    from ..ops import bitnet as KB
+                    f = QuantAct(*KB.swiglu_quant_int8(gu), gu.dtype)
+                else:
+                    f = ops.swiglu_fused(gu)
             else:
                 if h is None:
                     h = self._norm(x, L["ln2"])
@@ -301,7 +337,8 @@ class DecoderRunner:
                 else:
                     f = ops.swiglu_fused(self._linear(h, L["up"]))
             nxt = self.layers[li + 1]["ln1"] if li + 1 < len(self.layers) else (self.lnf if decode else None)
-            x, h_next = row_parallel(f, L["down"], x, nxt, True)
+            x, h_next = row_parallel(f, L["down"], x, nxt, True,
+                                     quant_next=li + 1 < len(self.layers) and self.layers[li + 1]["qkv"].packed is not None)
         if h_next is not None:
             x = h_next                                   # final norm already applied by the last reduction pass
         else:

@@ -181,6 +181,9 @@ def test_bitlinear_ll_many_ranks_emulated_on_one_gpu(world, M, N, Kr):
     result = [torch.zeros(2 * rs_stride, dtype=torch.uint8, device=dev) for _ in range(world)]
     state = [torch.zeros(4, dtype=torch.int64, device=dev) for _ in range(world)]
     res = _rand(M, N)
+    gamma = (_rand(N).float().abs() + 0.5).bfloat16()
+    nq = [torch.zeros(M, N, dtype=torch.int8, device=dev) for _ in range(world)]
+    nscale = [torch.zeros(M, dtype=torch.float32, device=dev) for _ in range(world)]
     lib = FU._lib()
     for it in range(3):
         qs, ss, ws = [], [], []
@@ -204,6 +207,9 @@ def test_bitlinear_ll_many_ranks_emulated_on_one_gpu(world, M, N, Kr):
                 p.out, p.ld_out = outs[r].data_ptr(), N
                 p.residual, p.ld_res = res.data_ptr(), N
                 p.wait_seconds, p.phases = 0.25, phase
+                if it == 2:                               # the unpack pass also normalises and quantises for the next layer
+                    p.norm_mode, p.gamma, p.eps = 3, gamma.data_ptr(), 1e-5
+                    p.quant_out, p.quant_scale = nq[r].data_ptr(), nscale[r].data_ptr()
                 rc = lib.ronn_bitlinear_ll(C.byref(bp), K.status_word(dev).data_ptr(), torch.cuda.current_stream().cuda_stream)
                 assert rc == 0, rc
         K.check_status()
@@ -212,3 +218,9 @@ def test_bitlinear_ll_many_ranks_emulated_on_one_gpu(world, M, N, Kr):
             assert torch.equal(outs[r], outs[0])
         scale = float(want.abs().max())
         torch.testing.assert_close(outs[0].float(), want, atol=1e-2 * scale, rtol=1e-2)
+        if it == 2:
+            q2, s2 = KB.rmsnorm_quant_int8(outs[0], gamma, 1e-5)          # the stand-alone kernel on the same rows
+            for r in range(world):
+                assert torch.equal(nq[r], nq[0]) and torch.equal(nscale[r], nscale[0])
+            torch.testing.assert_close(nscale[0], s2, rtol=2e-2, atol=0)
+            assert float((nq[0].float() * nscale[0][:, None] - q2.float() * s2[:, None]).abs().max()) <= 3 * float(s2.max())

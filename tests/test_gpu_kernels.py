@@ -356,6 +356,25 @@ def test_bitlinear_exact_against_host_oracle(M, N, K_):
     assert torch.equal(B.ternary_pack(wq.cuda()).cpu(), packed)
 
 
+@pytest.mark.parametrize("rows,F_", [(128, 6912), (37, 864), (1, 3456), (300, 1728)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_swiglu_quant_fused_equals_swiglu_then_quant(rows, F_, dtype):
+    """SwiGLU + per-token int8 quantisation in one kernel against the two-kernel form (bit-identical: the fused kernel
+    rounds the product through the storage type as the stand-alone SwiGLU stores it) and against an fp32 reference."""
+    from ronn_b200.ops import bitnet as B
+    from ronn_b200.ops import kernels as K
+    x = (torch.randn(rows, 2 * F_, device="cuda") * 1.5).to(dtype)
+    q, s = B.swiglu_quant_int8(x)
+    y = K.swiglu_fused(x)
+    q2, s2 = B.act_quant_int8(y)
+    assert torch.equal(s, s2)
+    assert int((q.int() - q2.int()).abs().max()) == 0
+    ref = torch.nn.functional.silu(x[:, :F_].float()) * x[:, F_:].float()
+    deq = q.float() * s[:, None]
+    step = ref.abs().amax(-1, keepdim=True) / 127
+    assert bool(((deq - ref).abs() <= step * 0.51 + ref.abs() * (8e-3 if dtype == torch.bfloat16 else 2e-3) + 1e-6).all())
+
+
 def test_rmsnorm_quant_fused():
     from ronn_b200.ops import bitnet as B
     x = _rand(19, 2560)
