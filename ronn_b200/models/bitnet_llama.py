@@ -136,15 +136,41 @@ def load_decoder_weights(runner, init) -> None:
         w = w.contiguous().to(dev)
         return LinearW(packed=w, scale=float(init[f"{name}.scale"]), n=w.shape[0], k=k)
 
+    # The packed-weight TMA of the BitLinear kernel wants K shards that are multiples of 64.  A ragged FFN shard (6912 / 8
+    # = 864) is widened to the next multiple with weights of zero (code 01): the extra gate | up rows produce
+    # silu(0) * 0 = 0 and the extra K columns of the down projection multiply them by zero again.
+    fl = f1 - f0
+    fpad = (-fl) % 64 if runner.tp > 1 else 0
+    zero_code = 0x55                                     # four ternary zeros
+
+    def pad_rows(lw, at, count):
+        """`count` all-zero weight rows inserted at each row index of `at` (ascending)."""
+        pieces, prev = [], 0
+        z = torch.full((count, lw.packed.shape[1]), zero_code, dtype=torch.uint8, device=lw.packed.device)
+        for pos in at:
+            pieces += [lw.packed[prev:pos], z]
+            prev = pos
+        pieces.append(lw.packed[prev:])
+        w = torch.cat(pieces).contiguous()
+        return LinearW(packed=w, scale=lw.scale, n=w.shape[0], k=lw.k)
+
+    def pad_k(lw, count):
+        z = torch.full((lw.packed.shape[0], count // 4), zero_code, dtype=torch.uint8, device=lw.packed.device)
+        return LinearW(packed=torch.cat([lw.packed, z], dim=1).contiguous(), scale=lw.scale, n=lw.n, k=lw.k + count)
+
     for i in range(a.n_layer):
         p = f"layers.{i}"
         qrows = torch.cat([torch.arange(hs, hs + hn), H + torch.arange(hs, hs + hn), 2 * H + torch.arange(hs, hs + hn)])
         gurows = torch.cat([torch.arange(f0, f1), F + torch.arange(f0, f1)])
+        up, down = packed(f"{p}.gate_up", rows=gurows), packed(f"{p}.down", kslice=(f0, f1))
+        if fpad:
+            up = pad_rows(up, [fl, 2 * fl], fpad)        # gate rows, pad, up rows, pad
+            down = pad_k(down, fpad)
         runner.layers.append({
             "ln1": (runner._dev(init[f"{p}.attn_norm.weight"]),),
             "ln2": (runner._dev(init[f"{p}.ffn_norm.weight"]),),
             "qkv": packed(f"{p}.qkv", rows=qrows),
             "out": packed(f"{p}.o", kslice=(hs, hs + hn)),
-            "up": packed(f"{p}.gate_up", rows=gurows),
-            "down": packed(f"{p}.down", kslice=(f0, f1)),
+            "up": up,
+            "down": down,
         })

@@ -23,8 +23,14 @@ def main():
         dev, dtype, backend = torch.device("cpu"), torch.float32, "torch"
     else:
         dev, dtype, backend = torch.device("cuda", local), torch.bfloat16, "kernels"
-    cfg = GPT2Config.tiny(n_layer=2, n_embd=512, n_head=8, vocab_size=1000, n_positions=256)      # 8 heads: shards up to TP=8
-    model = Model.from_graph(build_gpt2(cfg, dtype=dtype, seed=7))
+    if os.environ.get("RONN_TEST_MODEL") == "bitnet":
+        # ternary decoder whose FFN shard (352 / world) is not a multiple of 64: the shards are widened with zero weights
+        from ronn_b200.models.bitnet_llama import BitNetConfig, build_bitnet_llama
+        bcfg = BitNetConfig.tiny(n_layer=2, hidden=256, n_head=4, ffn=352, vocab_size=1000, max_pos=256)
+        model = Model.from_graph(build_bitnet_llama(bcfg, dtype=dtype, seed=7, with_lm_head=False))
+    else:
+        cfg = GPT2Config.tiny(n_layer=2, n_embd=512, n_head=8, vocab_size=1000, n_positions=256)  # 8 heads: shards up to TP=8
+        model = Model.from_graph(build_gpt2(cfg, dtype=dtype, seed=7))
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 17, 40, 64, 9, 33)]
 

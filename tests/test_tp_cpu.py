@@ -28,6 +28,18 @@ def test_tp_engine_on_cpu_ranks_matches_single_rank(tmp_path, world):
     assert r["sampled_same_across_ranks"] and r["sampled_in_range"]        # non-greedy requests: gathered logits, one seed
 
 
+def test_tp_bitnet_engine_with_a_ragged_ffn_shard(tmp_path):
+    """Ternary decoder at two ranks whose FFN shard (176) is widened to 192 with zero weights: every rank produces the
+    same tokens, and they agree with the single-rank run up to the effect of quantising each rank's activation shard
+    with its own scale."""
+    out = tmp_path / "r.json"
+    p = launch(2, "tp_engine_worker.py", ["cpu", str(out)], 29619, env={"RONN_TEST_MODEL": "bitnet"})
+    assert p.returncode == 0, p.stderr[-3000:]
+    r = json.loads(out.read_text())
+    assert r["same_across_ranks"] and r["sampled_same_across_ranks"] and r["sampled_in_range"]
+    assert r["agree"] >= int(0.5 * r["total"]), r
+
+
 def test_tp_engine_swap_preemption_on_cpu_ranks(tmp_path):
     """Every rank runs the same scheduler, so every rank swaps the same blocks of its own shard of the cache."""
     out = tmp_path / "r.json"
