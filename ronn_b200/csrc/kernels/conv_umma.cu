@@ -453,6 +453,51 @@ __global__ void global_avgpool_nhwc_kernel(const T* __restrict__ x, T* __restric
   }
 }
 
+// The same for wide feature maps: one CTA of 256 threads per (n, 512-channel slab), 64 channel groups x 4 pixel groups,
+// so a CTA streams HW x 1 KB instead of HW x 128 bytes (with one small CTA per 64 channels the kernel was bound by
+// the CTA launch rate: 0.49 of the copy bandwidth at 8192 x 7 x 7 x 512).
+template <class T>
+__global__ void __launch_bounds__(256)
+global_avgpool_wide_kernel(const T* __restrict__ x, T* __restrict__ y, int HW, int C) {
+  __shared__ float part[4][512];
+  pdl_wait();
+  pdl_trigger();
+  const int n = blockIdx.x, c0 = blockIdx.y * 512;
+  const int cg = threadIdx.x & 63, pg = threadIdx.x >> 6;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  const bool live = c0 + cg * 8 < C;
+  if (live) {
+    const T* base = x + size_t(n) * HW * C + c0 + cg * 8;
+    int p = pg;
+    for (; p + 12 < HW; p += 16) {                       // four loads in flight per thread
+      Vec8 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const Vec8*>(base + size_t(p + 4 * u) * C);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        float f[8];
+        unpack8<T>(v[u], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += f[j];
+      }
+    }
+    for (; p < HW; p += 4) {
+      float f[8];
+      unpack8<T>(*reinterpret_cast<const Vec8*>(base + size_t(p) * C), f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[pg][cg * 8 + j] = acc[j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < 512; c += 256)
+    if (c0 + c < C)
+      y[size_t(n) * C + c0 + c] = Cvt<T>::from_f((part[0][c] + part[1][c] + part[2][c] + part[3][c]) / float(HW));
+}
+
 }  // namespace ronn
 
 using namespace ronn;
@@ -550,8 +595,14 @@ extern "C" int ronn_nchw_to_s2d16(const void* x, void* y, int N, int C, int H, i
 
 extern "C" int ronn_global_avgpool_nhwc(const void* x, void* y, int N, int HW, int C, int dtype, cudaStream_t stream) {
   if (C & 7) return -2;
-  dim3 grid(N, (C + 63) / 64);
   cudaError_t err;
+  if (C >= 256) {
+    dim3 wide(N, (C + 511) / 512);
+    if (dtype == 0) err = launch(global_avgpool_wide_kernel<__nv_bfloat16>, wide, dim3(256), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, HW, C);
+    else err = launch(global_avgpool_wide_kernel<__half>, wide, dim3(256), 0, stream, (const __half*)x, (__half*)y, HW, C);
+    return err == cudaSuccess ? 0 : -100;
+  }
+  dim3 grid(N, (C + 63) / 64);
   if (dtype == 0) err = launch(global_avgpool_nhwc_kernel<__nv_bfloat16>, grid, dim3(64), 0, stream, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, HW, C);
   else err = launch(global_avgpool_nhwc_kernel<__half>, grid, dim3(64), 0, stream, (const __half*)x, (__half*)y, HW, C);
   return err == cudaSuccess ? 0 : -100;

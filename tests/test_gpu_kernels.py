@@ -329,6 +329,11 @@ def test_pool_kernels():
     torch.testing.assert_close(y.float(), ref)
     g = global_avgpool_nhwc(x)
     torch.testing.assert_close(g.float().reshape(3, 72), x.float().mean((1, 2)), atol=2e-3, rtol=2e-3)
+    for shape, dt in (((5, 7, 7, 512), torch.float16), ((2, 9, 5, 264), torch.bfloat16), ((3, 1, 1, 1024), torch.float16),
+                      ((2, 30, 3, 776), torch.bfloat16)):
+        xw = _rand(*shape, dtype=dt)                      # wide maps: one CTA per 512-channel slab
+        gw = global_avgpool_nhwc(xw)
+        torch.testing.assert_close(gw.float().reshape(shape[0], shape[3]), xw.float().mean((1, 2)), atol=1e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("M,N,K_", [(128, 2560, 2560), (128, 320, 6912), (37, 72, 256), (130, 96, 128), (1, 32000, 2560),
