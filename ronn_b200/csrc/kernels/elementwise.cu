@@ -423,8 +423,9 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
   const T* xr = x + long(blockIdx.x) * ld;
   float m = -INFINITY;
   int mi = 0x7fffffff;
+  // a thread visits its elements in increasing index order, so "strictly greater" already keeps the lowest index
   auto take = [&](float v, int i) {
-    if (v > m || (v == m && i < mi)) { m = v; mi = i; }
+    if (v > m) { m = v; mi = i; }
   };
   // Rows may start at any element (odd vocabulary sizes): scalar accesses up to the first 16-byte boundary, 16-byte
   // loads (two in flight per thread) for the body, scalar accesses for what is left.
@@ -436,15 +437,28 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
   if constexpr (VEC) {
   const Vec8* xv = reinterpret_cast<const Vec8*>(xr + head);
   int c = threadIdx.x;
-  for (; c + int(blockDim.x) < nvec; c += 2 * blockDim.x) {
-    const Vec8 p0 = xv[c], p1 = xv[c + blockDim.x];
+  const int bd = int(blockDim.x);
+  for (; c + 3 * bd < nvec; c += 4 * bd) {               // four 16-byte loads in flight per thread
+    Vec8 p[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) p[u] = xv[c + u * bd];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float f[8];
+      unpack8<T>(p[u], f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) take(f[k], head + (c + u * bd) * 8 + k);
+    }
+  }
+  for (; c + bd < nvec; c += 2 * bd) {
+    const Vec8 p0 = xv[c], p1 = xv[c + bd];
     float f0[8], f1[8];
     unpack8<T>(p0, f0);
     unpack8<T>(p1, f1);
 #pragma unroll
     for (int k = 0; k < 8; ++k) take(f0[k], head + c * 8 + k);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) take(f1[k], head + (c + int(blockDim.x)) * 8 + k);
+    for (int k = 0; k < 8; ++k) take(f1[k], head + (c + bd) * 8 + k);
   }
   for (; c < nvec; c += blockDim.x) {
     float f[8];
@@ -495,6 +509,7 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
       if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
     }
     if (lane == 0) {
+      if (mi == 0x7fffffff) mi = 0;                        // nothing compared greater than -inf (a row of -inf or NaN)
       idx_out[blockIdx.x] = mi + col_offset;
       if (max_out) max_out[blockIdx.x] = m;
     }

@@ -363,15 +363,25 @@ class NodeFusionPass(OptimizationPass):
         cons, prod = graph.consumers(), graph.producers()
         outputs = set(graph.output_names())
 
-        def sole(name):
-            return name not in outputs and len(cons.get(name, [])) == 1
+        def shape_readers(name):
+            return [u for u in cons.get(name, []) if u.op_type == "Shape" and not u.domain]
+
+        def sole(name, but_shapes=False):
+            """One reader; with `but_shapes` (the raw score tensor), Shape nodes beside it do not count: exporters
+            expand a masked_fill condition to the scores' shape, and that shape can be had from Q and K^T."""
+            if name in outputs:
+                return False
+            users = cons.get(name, [])
+            if but_shapes:
+                users = [u for u in users if u.op_type != "Shape" or u.domain]
+            return len(users) == 1
 
         def is_scores(name, allow_fill=False):
             """`name` is a MatMul of two non-constant tensors, possibly under one scalar Div / Mul (and, with
             `allow_fill`, under a Where that fills masked scores with a constant)."""
             for _ in range(3):
                 n = prod.get(name)
-                if n is None or not sole(name):
+                if n is None or not sole(name, but_shapes=n.op_type == "MatMul"):
                     return False
                 if allow_fill and n.op_type == "Where" and len(n.inputs) == 3:
                     allow_fill = False
@@ -409,7 +419,7 @@ class NodeFusionPass(OptimizationPass):
             stage = 0                                      # 0: mask, fill, scale or MatMul may follow; 1: fill, scale or
             while True:                                    # MatMul; 2: scale or MatMul; 3: MatMul
                 n = prod.get(cur)
-                if n is None or not sole(cur):
+                if n is None or not sole(cur, but_shapes=n.op_type == "MatMul"):
                     break
                 if n.op_type == "Where" and len(n.inputs) == 3 and stage <= 1:
                     # masked_fill as exporters write it: Where(cond, value, scores) or Where(cond, scores, value)
@@ -459,6 +469,22 @@ class NodeFusionPass(OptimizationPass):
             idx = graph.nodes.index(pv)
             name = (sm.name or f"node_{sm.id}") + ".sdpa"
             out = pv.outputs[0]
+            # Shape(scores) readers: shape(Q)[:-1] ++ shape(K^T)[-1:] is the same vector without the scores
+            for k, sh in enumerate(shape_readers(qk.outputs[0])):
+                lo, hi = int(sh.attr("start", 0)), sh.attr("end")
+                if lo != 0 or hi is not None:
+                    continue                               # a partial shape: left reading the (still produced) scores
+                a_name, b_name = graph.fresh_name(f"{name}.shape_q{k}"), graph.fresh_name(f"{name}.shape_k{k}")
+                at = graph.nodes.index(sh)
+                res = sh.outputs[0]
+                graph.remove_nodes([sh.id])
+                graph.add_node("Shape", [qk.inputs[0]], [a_name], {"start": 0, "end": -1}, name=a_name, index=at)
+                graph.add_node("Shape", [qk.inputs[1]], [b_name], {"start": -1}, name=b_name, index=at + 1)
+                graph.add_node("Concat", [a_name, b_name], [res], {"axis": 0}, name=graph.fresh_name(f"{name}.shape{k}"),
+                               index=at + 2)
+            if any(u.op_type == "Shape" for u in graph.consumers().get(qk.outputs[0], [])):
+                continue                                   # a reader of the scores is left: they must stay
+            idx = graph.nodes.index(pv)
             graph.remove_nodes([n.id for n in chain] + [qk.id, pv.id])
             idx = min(idx, len(graph.nodes))
             graph.add_node("ScaledDotProductAttention", ins, [out], attrs, name=name,

@@ -336,6 +336,11 @@ def test_masked_encoder_with_two_inputs(opset):
         sess = model.create_session(SessionOptions().with_optimization_level(level))
         got = sess.run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"]
         torch.testing.assert_close(got, want, atol=2e-5, rtol=1e-5)
+        if level == "O3":
+            # the exporter's MatMul / Div / masked_fill (a Where whose condition was expanded to the scores' shape) /
+            # Softmax / MatMul became one fused attention node
+            ops = [n.op_type for n in sess.graph().nodes]
+            assert ops.count("ScaledDotProductAttention") == 1 and "Softmax" not in ops
         # rows that differ only in padded positions give the same output on the valid positions
         ids2 = ids.clone()
         ids2[1, 5:] = 7
