@@ -641,6 +641,41 @@ extern "C" int ronn_norm(const void* x, const void* res, const void* gamma, cons
   return check_launch();
 }
 
+// Softmax over an axis that is not the last one, on the tensor as it lies in memory: [outer, n, inner] with the
+// reduction over n.  One thread per (outer, inner) column: neighbouring threads read neighbouring addresses at every
+// step of the walk over n, so the loads coalesce without a transpose.  Two walks: running maximum and sum (online),
+// then the normalised values.
+template <class T>
+__global__ void softmax_strided_kernel(const T* __restrict__ x, T* __restrict__ y, long outer, int n, long inner) {
+  pdl_wait();
+  pdl_trigger();
+  const long total = outer * inner;
+  for (long col = blockIdx.x * long(blockDim.x) + threadIdx.x; col < total; col += long(gridDim.x) * blockDim.x) {
+    const long o = col / inner, in = col - o * inner;
+    const T* p = x + o * n * inner + in;
+    T* q = y + o * n * inner + in;
+    float m = -INFINITY, s = 0.f;
+    for (int k = 0; k < n; ++k) {
+      const float v = Cvt<T>::to_f(p[long(k) * inner]);
+      const float nm = fmaxf(m, v);
+      s = s * __expf(m - nm) + __expf(v - nm);
+      m = nm;
+    }
+    const float inv = 1.f / s;
+    for (int k = 0; k < n; ++k) q[long(k) * inner] = Cvt<T>::from_f(__expf(Cvt<T>::to_f(p[long(k) * inner]) - m) * inv);
+  }
+}
+
+// x, y: contiguous [outer, n, inner]; softmax over n.  dtype: 0 bf16, 1 fp16, 2 fp32.
+extern "C" int ronn_softmax_strided(const void* x, void* y, long outer, int n, long inner, int dtype, cudaStream_t stream) {
+  if (outer <= 0 || n <= 0 || inner <= 0) return 0;
+  const long total = outer * inner;
+  const int grid = int((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+  if (dtype == 2) launch(softmax_strided_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)x, (float*)y, outer, n, inner);
+  else RONN_BY_DTYPE(dtype, launch(softmax_strided_kernel<T>, dim3(grid), dim3(256), 0, stream, (const T*)x, (T*)y, outer, n, inner));
+  return check_launch();
+}
+
 // dtype: 0 bf16, 1 fp16, 2 fp32
 extern "C" int ronn_softmax(const void* x, void* y, long rows, int cols, int dtype, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;

@@ -28,6 +28,7 @@ def declare(lib):
     sig("ronn_signal_peers", [V, I, I, V], optional=True)
     sig("ronn_norm", [V, V, V, V, V, V, L, I, L, L, L, F, I, I, V])
     sig("ronn_softmax", [V, V, L, I, I, V])
+    sig("ronn_softmax_strided", [V, V, L, I, L, I, V], optional=True)
     sig("ronn_set_rowwise_status", [V], optional=True)
     sig("ronn_unary", [V, V, L, I, I, V])
     sig("ronn_binary", [V, V, V, L, I, I, V])

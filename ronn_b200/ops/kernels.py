@@ -121,10 +121,22 @@ def rmsnorm(x, gamma, eps: float = 1e-5, residual=None, return_sum: bool = False
     return _norm(x, gamma, None, residual, eps, True, return_sum)
 
 
-def softmax(x: torch.Tensor) -> torch.Tensor:
-    """Softmax over the last axis."""
+def softmax(x: torch.Tensor, axis: int = -1) -> torch.Tensor:
+    """Softmax over ``axis`` (the last one by default; any other axis is reduced in place through strides, without
+    a transpose)."""
     xc = x.contiguous()
     y = torch.empty_like(xc)
+    if axis < 0:
+        axis += xc.dim()
+    if axis != xc.dim() - 1 and xc.numel():
+        outer = 1
+        for d in xc.shape[:axis]:
+            outer *= int(d)
+        n = int(xc.shape[axis])
+        inner = xc.numel() // (outer * n)
+        _check(_native.cuda().ronn_softmax_strided(xc.data_ptr(), y.data_ptr(), outer, n, inner, _DT[x.dtype], _stream()),
+               "softmax_strided")
+        return y
     cols = xc.shape[-1]
     status_word(x.device)
     _check(_native.cuda().ronn_softmax(xc.data_ptr(), y.data_ptr(), xc.numel() // cols, cols, _DT[x.dtype], _stream()),

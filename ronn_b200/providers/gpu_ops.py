@@ -182,9 +182,10 @@ class GpuOpTable:
         def run(i, a, c):
             x = i[0]
             axis = int(a.get("axis", -1))
-            if axis not in (-1, x.dim() - 1) or x.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            if (x.dtype not in (torch.bfloat16, torch.float16, torch.float32) or x.device.type != "cuda" or x.dim() == 0
+                    or a.get("legacy_flatten") or not -x.dim() <= axis < x.dim()):
                 return fallback(i, a, c)
-            return [K.softmax(x)]
+            return [K.softmax(x, axis)]
         return run
 
     def _unary(self, kname, fallback):

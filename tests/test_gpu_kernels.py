@@ -321,6 +321,19 @@ def test_conv_igemm(shape, dtype):
     torch.testing.assert_close(y2.permute(0, 3, 1, 2).float(), torch.relu(ref + res.permute(0, 3, 1, 2).float()), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("shape,axis", [((4, 8, 128), 1), ((4, 8, 128), 0), ((2, 3, 5, 7), 2), ((3000, 64), 0), ((6, 1000, 9), 1),
+                                        ((16, 512), -1)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_softmax_over_any_axis(K, shape, axis, dtype):
+    """Softmax over an inner or leading axis runs on the tensor as it lies in memory (strides), no transpose."""
+    x = (torch.randn(*shape, device="cuda") * 3).to(dtype)
+    y = K.softmax(x, axis)
+    ref = torch.softmax(x.float(), dim=axis)
+    tol = {torch.bfloat16: 1e-2, torch.float16: 2e-3, torch.float32: 1e-5}[dtype]
+    torch.testing.assert_close(y.float(), ref, atol=tol, rtol=3e-2 if dtype != torch.float32 else 1e-4)
+    torch.testing.assert_close(y.float().sum(axis), torch.ones_like(ref.sum(axis)), atol=2e-2, rtol=0)
+
+
 def test_pool_kernels():
     from ronn_b200.providers.gpu_conv import global_avgpool_nhwc, maxpool_nhwc
     x = _rand(3, 23, 21, 72, dtype=torch.float16)
