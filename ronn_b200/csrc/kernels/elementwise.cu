@@ -438,18 +438,6 @@ __global__ void argmax_kernel(const T* __restrict__ x, int* __restrict__ idx_out
   const Vec8* xv = reinterpret_cast<const Vec8*>(xr + head);
   int c = threadIdx.x;
   const int bd = int(blockDim.x);
-  for (; c + 3 * bd < nvec; c += 4 * bd) {               // four 16-byte loads in flight per thread
-    Vec8 p[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) p[u] = xv[c + u * bd];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      float f[8];
-      unpack8<T>(p[u], f);
-#pragma unroll
-      for (int k = 0; k < 8; ++k) take(f[k], head + (c + u * bd) * 8 + k);
-    }
-  }
   for (; c + bd < nvec; c += 2 * bd) {
     const Vec8 p0 = xv[c], p1 = xv[c + bd];
     float f0[8], f1[8];
