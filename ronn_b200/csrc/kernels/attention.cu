@@ -68,7 +68,8 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcache, T* __restrict__ vcache,
                        const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ ctx_len,
                        const int* __restrict__ bt_row, T* __restrict__ out, long ld_o, int heads, int kv_heads,
-                       float scale, int k_off, int v_off, const int* __restrict__ append_slots) {
+                       float scale, int k_off, int v_off, const int* __restrict__ append_slots,
+                       const int* __restrict__ positions, float rope_base) {
   constexpr int LPT = D / 8;                  // lanes cooperating on one token (16-byte chunk each)
   constexpr int TPW = 32 / LPT;               // tokens per warp pass
   constexpr int PASSES = KV_BLOCK / TPW;      // passes per 16-token block
@@ -88,6 +89,26 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcach
     return;
   }
   const int kvh = head / (heads / kv_heads);
+  // Rotary embedding fused into the decode step (rope_base > 0): pairs (j, j + D/2) of the row's q and of its new k are
+  // rotated by position x base^(-2j/D), rounded through the storage type as the stand-alone rotation stores them; the
+  // q row in memory stays untouched.  `rot8` returns the rotated 16-byte chunk c of the head vector at `base`.
+  const bool rope = rope_base > 0.f && positions != nullptr;
+  const float pos = rope ? float(positions[row]) : 0.f;
+  auto rot8 = [&](const T* base, int c, float (&o)[8]) {
+    constexpr int HC = D / 16;                // chunks per half
+    float own[8], oth[8];
+    unpack8<T>(*reinterpret_cast<const Vec8*>(base + c * 8), own);
+    unpack8<T>(*reinterpret_cast<const Vec8*>(base + (c < HC ? c + HC : c - HC) * 8), oth);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j = (c < HC ? c : c - HC) * 8 + i;          // index inside the half
+      const float inv = __powf(rope_base, -2.f * float(j) / float(D));
+      float sn, cs;
+      __sincosf(pos * inv, &sn, &cs);
+      const float r = c < HC ? own[i] * cs - oth[i] * sn : own[i] * cs + oth[i] * sn;
+      o[i] = Cvt<T>::to_f(Cvt<T>::from_f(r));
+    }
+  };
   if (append_slots != nullptr) {
     // decode with fused append: this row's new K/V (columns k_off / v_off of the fused QKV row) go to the row's
     // cache slot first; every CTA of a KV group writes the same bytes, and reads them back only after the barrier
@@ -95,10 +116,16 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcach
     if (slot >= 0 && threadIdx.x < 2 * (D / 8)) {
       const int c = threadIdx.x % (D / 8);
       const bool is_v = threadIdx.x >= D / 8;
-      const T* src = q + long(row) * ld_q + (is_v ? v_off : k_off) + kvh * D + c * 8;
+      const T* src = q + long(row) * ld_q + (is_v ? v_off : k_off) + kvh * D;
       T* dstc = is_v ? vcache : kcache;
       const long dst = ((long(slot / KV_BLOCK) * kv_heads + kvh) * KV_BLOCK + slot % KV_BLOCK) * D + c * 8;
-      *reinterpret_cast<Vec8*>(dstc + dst) = *reinterpret_cast<const Vec8*>(src);
+      if (rope && !is_v) {
+        float kr[8];
+        rot8(src, c, kr);
+        *reinterpret_cast<Vec8*>(dstc + dst) = pack8<T>(kr);
+      } else {
+        *reinterpret_cast<Vec8*>(dstc + dst) = *reinterpret_cast<const Vec8*>(src + c * 8);
+      }
     }
     __syncthreads();
   }
@@ -107,7 +134,8 @@ paged_attention_kernel(const T* __restrict__ q, long ld_q, T* __restrict__ kcach
   const int sub = lane / LPT, chunk = lane % LPT;
 
   float qf[8];
-  unpack8<T>(*reinterpret_cast<const Vec8*>(q + long(row) * ld_q + head * D + chunk * 8), qf);
+  if (rope) rot8(q + long(row) * ld_q + head * D, chunk, qf);
+  else unpack8<T>(*reinterpret_cast<const Vec8*>(q + long(row) * ld_q + head * D + chunk * 8), qf);
 #pragma unroll
   for (int i = 0; i < 8; ++i) qf[i] *= scale;
 
@@ -209,20 +237,21 @@ extern "C" int ronn_kv_append(void* qkv, long ld, int k_off, int v_off, const in
 }
 
 // max_ctx: upper bound of ctx_len over the rows (sizes the score buffer); must be <= 4096.
-// append_slots != null (decode, one row per sequence, no rotary): the row's new K/V are taken from columns k_off / v_off
-// of its q row and written to cache slot append_slots[row] by the same kernel before attending.
+// append_slots != null (decode, one row per sequence): the row's new K/V are taken from columns k_off / v_off of its q
+// row and written to cache slot append_slots[row] by the same kernel before attending.  positions != null and
+// rope_base > 0: rotary embedding of q and of the new k (pairs j, j + head_dim / 2) by the same kernel as well.
 extern "C" int ronn_paged_attention(const void* q, long ld_q, void* kcache, void* vcache,
                                     const int* block_tables, int max_blocks, const int* ctx_len, const int* bt_row,
                                     void* out, long ld_o, long rows, int heads, int kv_heads, int head_dim,
                                     int max_ctx, float scale, int dtype, int k_off, int v_off, const int* append_slots,
-                                    cudaStream_t stream) {
+                                    const int* positions, float rope_base, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (max_ctx <= 0 || max_ctx > ATTN_MAX_CTX || heads % kv_heads || (ld_q & 7)) return -2;
   if (append_slots && ((k_off & 7) || (v_off & 7))) return -2;
   const int padded = (max_ctx + KV_BLOCK - 1) / KV_BLOCK * KV_BLOCK;
   const size_t smem = size_t(padded) * sizeof(float);
   dim3 grid((unsigned)rows, (unsigned)heads);
-#define RONN_PA(T, D) launch(paged_attention_kernel<T, D>, grid, dim3(ATTN_THREADS), smem, stream, (const T*)q, ld_q, (T*)kcache, (T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale, k_off, v_off, append_slots)
+#define RONN_PA(T, D) launch(paged_attention_kernel<T, D>, grid, dim3(ATTN_THREADS), smem, stream, (const T*)q, ld_q, (T*)kcache, (T*)vcache, block_tables, max_blocks, ctx_len, bt_row, (T*)out, ld_o, heads, kv_heads, scale, k_off, v_off, append_slots, positions, rope_base)
   if (dtype == 0 && head_dim == 64) RONN_PA(__nv_bfloat16, 64);
   else if (dtype == 0 && head_dim == 128) RONN_PA(__nv_bfloat16, 128);
   else if (dtype == 1 && head_dim == 64) RONN_PA(__half, 64);

@@ -317,10 +317,11 @@ def kv_append(qkv: torch.Tensor, k_off: int, v_off: int, slots: torch.Tensor, kc
 def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                     ctx_len: torch.Tensor, heads: int, kv_heads: int, head_dim: int, max_ctx: int,
                     bt_row: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    scale: Optional[float] = None, append=None) -> torch.Tensor:
+                    scale: Optional[float] = None, append=None, rope=None) -> torch.Tensor:
     """q: [rows, >= heads*head_dim] (row stride free).  Returns [rows, heads*head_dim].
     ``append=(k_off, v_off, slots)`` (decode, one row per sequence): the new K/V columns of the fused QKV row are
-    written to their cache slots by the same kernel."""
+    written to their cache slots by the same kernel.  ``rope=(positions int32 [rows], base)`` with ``append``: q and the
+    new k are rotated by the same kernel too (the q row in memory stays as it is)."""
     rows = q.shape[0]
     if out is None:
         out = torch.empty((rows, heads * head_dim), dtype=q.dtype, device=q.device)
@@ -330,7 +331,9 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                                                _ptr(bt_row), out.data_ptr(), out.stride(0), rows, heads, kv_heads,
                                                head_dim, int(max_ctx), float(sc), _DT[q.dtype],
                                                append[0] if append else 0, append[1] if append else 0,
-                                               append[2].data_ptr() if append else None, _stream()),
+                                               append[2].data_ptr() if append else None,
+                                               rope[0].data_ptr() if rope else None, float(rope[1]) if rope else 0.0,
+                                               _stream()),
            "paged_attention")
     return out
 

@@ -303,9 +303,9 @@ class DecoderRunner:
             else:
                 h = h_next if h_next is not None else self._norm(x, L["ln1"])
                 qkv = self._linear(h, L["qkv"])
-            if decode and a.rope_base == 0 and ops.name == "kernels":
+            if decode and ops.name == "kernels":
                 att = ops.append_attention(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], b["block_tables"],
-                                           ctx, self.n_head_local, self.n_kv_local, d, max_ctx)
+                                           ctx, self.n_head_local, self.n_kv_local, d, max_ctx, pos, a.rope_base)
             else:
                 ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
                               self.n_kv_local, d, pos, a.rope_base)

@@ -167,10 +167,12 @@ class KernelOps:
     def paged_attention(self, q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row=None):
         return self.K.paged_attention(q, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx, bt_row)
 
-    def append_attention(self, qkv, k_off, v_off, slots, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx):
-        """Decode step: cache append and attention in one launch."""
+    def append_attention(self, qkv, k_off, v_off, slots, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx,
+                         positions=None, rope_base=0.0):
+        """Decode step: (rotary embedding,) cache append and attention in one launch."""
+        rope = (positions, rope_base) if rope_base > 0 and positions is not None else None
         return self.K.paged_attention(qkv, kcache, vcache, block_tables, ctx_len, heads, kv_heads, d, max_ctx,
-                                      append=(k_off, v_off, slots))
+                                      append=(k_off, v_off, slots), rope=rope)
 
     def dense_attention(self, qkv, q_off, k_off, v_off, plan, heads, kv_heads, d, causal, q_len=None, max_q_len=None):
         """Whole-sequence attention on the tensor cores, straight from the fused qkv buffer."""

@@ -299,6 +299,47 @@ def test_kv_append_rope(K):
     torch.testing.assert_close(got_k.float(), ref_k.float(), atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (128, 8, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_rope_append_attention_in_one_launch(K, d, heads, kv_heads, dtype):
+    """Decode rows with rotary embedding: the one-launch form (rotate q and the new k, append, attend) against the
+    rotate-and-append kernel followed by plain paged attention, and against an fp32 restatement."""
+    from ronn_b200.onnx.registry import rotary
+    torch.manual_seed(3)
+    lens = [1, 16, 17, 130]
+    B, max_blocks = len(lens), 12
+    nblocks = B * max_blocks
+    perm = torch.randperm(nblocks).reshape(B, max_blocks).to(torch.int32).cuda()
+    kc = (torch.randn(nblocks, kv_heads, 16, d, device="cuda") * 0.5).to(dtype)      # earlier tokens: any values
+    vc = (torch.randn(nblocks, kv_heads, 16, d, device="cuda") * 0.5).to(dtype)
+    ld = (heads + 2 * kv_heads) * d
+    qkv = _rand(B, ld, dtype=dtype)
+    pos = torch.tensor([n - 1 for n in lens], device="cuda", dtype=torch.int32)
+    slots = torch.tensor([int(perm[b, (n - 1) // 16]) * 16 + (n - 1) % 16 for b, n in enumerate(lens)],
+                         device="cuda", dtype=torch.int32)
+    ctx = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    kc2, vc2, qkv2 = kc.clone(), vc.clone(), qkv.clone()
+    out = K.paged_attention(qkv, kc, vc, perm, ctx, heads, kv_heads, d, max_ctx=144,
+                            append=(heads * d, (heads + kv_heads) * d, slots), rope=(pos, 10000.0))
+    assert torch.equal(qkv, qkv2)                      # the fused form leaves the qkv row as it was
+    K.kv_append(qkv2, heads * d, (heads + kv_heads) * d, slots, kc2, vc2, heads, kv_heads, d, pos, 10000.0)
+    ref = K.paged_attention(qkv2, kc2, vc2, perm, ctx, heads, kv_heads, d, max_ctx=144)
+    from ronn_b200 import ops
+    ops.check_status()
+    torch.testing.assert_close(kc.float(), kc2.float(), atol=1e-2, rtol=1e-2)
+    assert torch.equal(vc, vc2)
+    torch.testing.assert_close(out.float(), ref.float(), atol=1e-2, rtol=1e-2)
+    # fp32 restatement for the longest row
+    b, n = B - 1, lens[-1]
+    qr = rotary(qkv[b:b + 1, :heads * d].float(), pos[b:b + 1], 10000.0, heads).reshape(heads, d)
+    kk = torch.stack([kc[int(perm[b, t // 16]), :, t % 16] for t in range(n)]).float()      # [n, kv, d]
+    vv = torch.stack([vc[int(perm[b, t // 16]), :, t % 16] for t in range(n)]).float()
+    rep = heads // kv_heads
+    s_ = torch.einsum("hd,lhd->hl", qr, kk.repeat_interleave(rep, dim=1)) / math.sqrt(d)
+    want = torch.einsum("hl,lhd->hd", torch.softmax(s_, -1), vv.repeat_interleave(rep, dim=1)).reshape(-1)
+    torch.testing.assert_close(out[b].float(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("shape", [
     # N, H, W, C, Cout, R, stride, pad
     (2, 16, 16, 64, 64, 3, 1, 1), (2, 17, 19, 16, 72, 3, 2, 1), (1, 56, 56, 64, 128, 1, 2, 0),
