@@ -42,8 +42,8 @@ def declare(lib):
     sig("ronn_kv_append", [V, L, I, I, V, V, V, V, L, I, I, I, F, I, I, V])
     sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V, F, V])
     sig("ronn_gemm_rownorm", [V, V, V, V, V, V, V, V, I, I, I, I, I, I, F, I, I, V, V], optional=True)
-    sig("ronn_transpose_v", [V, L, I, V, V, V, V, L, I, I, I, I, I, V])
-    sig("ronn_flash_attention", [V, L, L, I, I, V, L, V, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
+    sig("ronn_fmha", [V, L, L, I, I, I, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
+    sig("ronn_fmha_paged", [V, L, L, I, V, V, L, V, I, V, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
     sig("ronn_conv2d", [V, V, V, V, V, I, I, I, I, I, I, I, I, I, I, I, I, I, I, V, L, V, V], optional=True)
     sig("ronn_nchw_to_nhwc8", [V, V, I, I, I, I, I, V], optional=True)
     sig("ronn_nchw_to_s2d16", [V, V, I, I, I, I, I, V], optional=True)

@@ -7,6 +7,7 @@ tensor-core kernels; ``check_status`` reads it (one small device-to-host copy) a
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -367,45 +368,57 @@ def gemm_rownorm(a: torch.Tensor, w_nk: torch.Tensor, bias, residual, gamma, bet
 def dense_attention_plan(kv_lens, device, row_lens=None) -> dict:
     """Per-sequence index tensors of ``dense_attention`` for sequences stored back to back in the token buffer.
     ``kv_lens``: host list of sequence lengths; ``row_lens``: rows each sequence occupies in the buffer when that is
-    more than its length (padded batches).  Every sequence gets a 128-aligned column range of the V^T buffer."""
-    starts, vts, t, c = [], [], 0, 0
+    more than its length (padded batches)."""
+    starts, t = [], 0
     for i, n in enumerate(kv_lens):
         starts.append(t)
-        vts.append(c)
         t += int(n if row_lens is None else row_lens[i])
-        c += -(-int(n) // 128) * 128
     mk = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
-    return {"seq_start": mk(starts), "kv_len": mk([int(n) for n in kv_lens]), "vt_start": mk(vts),
-            "vt_cols": max(c, 128), "max_len": max(int(n) for n in kv_lens), "n_seq": len(kv_lens)}
+    return {"seq_start": mk(starts), "kv_len": mk([int(n) for n in kv_lens]),
+            "max_len": max(int(n) for n in kv_lens), "n_seq": len(kv_lens)}
 
 
 def dense_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, plan: dict, heads: int, kv_heads: int,
                     head_dim: int, causal: bool, q_len: Optional[torch.Tensor] = None, max_q_len: Optional[int] = None,
-                    out: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                    vt: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
     """Tensor-core attention over the fused qkv buffer [tokens, ld] of whole sequences (prefill without cached
-    context, encoders): V is transposed into a scratch V^T buffer, then one kernel per (128 queries, head, sequence)
-    runs S = Q K^T and O = P V on tcgen05 with an online softmax in between.  ``plan`` comes from
+    context, encoders): one kernel per (128 queries, head, sequence) runs S = Q K^T and O = P V on tcgen05 with an
+    online softmax in between; K and V are read where the QKV projection wrote them.  ``plan`` comes from
     ``dense_attention_plan``; ``q_len`` defaults to the key lengths (set it to the padded row count for encoders whose
     padded rows must still be produced).  Returns [tokens, heads * head_dim]."""
     tokens = qkv.shape[0]
-    lib = _native.cuda()
-    if vt is None:
-        vt = torch.empty((kv_heads * head_dim, plan["vt_cols"]), dtype=qkv.dtype, device=qkv.device)
-    dt = _DT[qkv.dtype]
-    _check(lib.ronn_transpose_v(qkv.data_ptr(), qkv.stride(0), v_off, plan["seq_start"].data_ptr(),
-                                plan["kv_len"].data_ptr(), plan["vt_start"].data_ptr(), vt.data_ptr(), vt.stride(0),
-                                plan["n_seq"], kv_heads, head_dim, plan["max_len"], dt, _stream()), "transpose_v")
     if out is None:
         out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     ql = q_len if q_len is not None else plan["kv_len"]
     mq = int(max_q_len if max_q_len is not None else plan["max_len"])
     sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
-    _check(lib.ronn_flash_attention(qkv.data_ptr(), qkv.stride(0), tokens, q_off, k_off, vt.data_ptr(), vt.stride(0),
+    _check(_native.cuda().ronn_fmha(qkv.data_ptr(), qkv.stride(0), tokens, q_off, k_off, v_off,
                                     plan["seq_start"].data_ptr(), ql.data_ptr(), plan["kv_len"].data_ptr(),
-                                    plan["vt_start"].data_ptr(), out.data_ptr(), out.stride(0), plan["n_seq"], mq,
-                                    heads, kv_heads, head_dim, 1 if causal else 0, float(sc), dt,
-                                    status_word(qkv.device).data_ptr(), _stream()), "flash_attention")
+                                    out.data_ptr(), out.stride(0), plan["n_seq"], mq, heads, kv_heads, head_dim,
+                                    1 if causal else 0, float(sc), _DT[qkv.dtype],
+                                    status_word(qkv.device).data_ptr(), _stream()), "fmha")
+    return out
+
+
+def paged_prefill_attention(q: torch.Tensor, q_off: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                            block_tables: torch.Tensor, seq_start: torch.Tensor, q_len: torch.Tensor,
+                            kv_len: torch.Tensor, max_q_len: int, heads: int, kv_heads: int, head_dim: int,
+                            causal: bool = True, bt_row: Optional[torch.Tensor] = None,
+                            out: Optional[torch.Tensor] = None, scale: Optional[float] = None) -> torch.Tensor:
+    """Tensor-core attention of query chunks over the paged KV cache (chunked prefill, prefix hits): sequence s has its
+    ``q_len[s]`` queries at rows ``seq_start[s] ..`` of ``q`` ([tokens, ld], head h at column q_off + h * head_dim) and
+    attends to the ``kv_len[s]`` keys its block-table row lists; the queries are the last positions of that context.
+    The new tokens' K / V must already be in the cache.  Returns [tokens, heads * head_dim]."""
+    tokens = q.shape[0]
+    if out is None:
+        out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=q.device)
+    sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    _check(_native.cuda().ronn_fmha_paged(q.data_ptr(), q.stride(0), tokens, q_off, kcache.data_ptr(), vcache.data_ptr(),
+                                          kcache.shape[0], block_tables.data_ptr(), block_tables.stride(0), _ptr(bt_row),
+                                          seq_start.data_ptr(), q_len.data_ptr(), kv_len.data_ptr(), out.data_ptr(),
+                                          out.stride(0), seq_start.numel(), int(max_q_len), heads, kv_heads, head_dim,
+                                          1 if causal else 0, float(sc), _DT[q.dtype],
+                                          status_word(q.device).data_ptr(), _stream()), "fmha_paged")
     return out
 
 

@@ -79,20 +79,19 @@ def time_graph(make_call, variants: int, reps: int = 40, iters: int = 5):
 
 
 def bench_dense_attention(batch=64, seq=128, heads=12, dim=64, causal=False, iters=20, flush=True):
-    """Tensor-core attention over a fused qkv buffer of `batch` sequences of `seq` tokens (V transpose + attention)."""
+    """Tensor-core attention over a fused qkv buffer of `batch` sequences of `seq` tokens."""
     hn = heads * dim
     qkv = torch.randn(batch * seq, 3 * hn, device="cuda").bfloat16()
     plan = K.dense_attention_plan([seq] * batch, "cuda")
     out = torch.empty(batch * seq, hn, device="cuda", dtype=torch.bfloat16)
-    vt = torch.empty(hn, plan["vt_cols"], device="cuda", dtype=torch.bfloat16)
-    us = time_kernel(lambda: K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, dim, causal, out=out, vt=vt),
+    us = time_kernel(lambda: K.dense_attention(qkv, 0, hn, 2 * hn, plan, heads, heads, dim, causal, out=out),
                      iters=iters, flush=flush)
     K.check_status()
     hbm, tf, src = _peaks()
     flops = 4.0 * batch * heads * seq * seq * dim * (0.5 if causal else 1.0)
     byts = 2.0 * (qkv.numel() + out.numel())
     roof = max(flops / (tf * 1e12), byts / (hbm * 1e9)) * 1e6
-    return {"kernel": "dense_attention(+transpose_v)", "batch": batch, "seq": seq, "heads": heads, "dim": dim,
+    return {"kernel": "dense_attention", "batch": batch, "seq": seq, "heads": heads, "dim": dim,
             "causal": causal, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "roofline_us": round(roof, 2),
             "frac_of_" + src: round(roof / us, 3)}
 

@@ -246,10 +246,9 @@ class GpuOpTable:
         def plan_for(B, S, dev):
             p = plans.get((B, S))
             if p is None:
-                s_pad = -(-S // 128) * 128
                 mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-                p = {"seq_start": mk([b * S for b in range(B)]), "vt_start": mk([b * s_pad for b in range(B)]),
-                     "vt_cols": B * s_pad, "max_len": S, "n_seq": B, "q_len": torch.full((B,), S, dtype=torch.int32, device=dev),
+                p = {"seq_start": mk([b * S for b in range(B)]),
+                     "max_len": S, "n_seq": B, "q_len": torch.full((B,), S, dtype=torch.int32, device=dev),
                      "kv_len": torch.full((B,), S, dtype=torch.int32, device=dev)}
                 plans[(B, S)] = p
             return p
@@ -304,11 +303,9 @@ class GpuOpTable:
         def plan_for(B, S, dev):
             p = plans.get((B, S))
             if p is None:
-                s_pad = -(-S // 128) * 128
                 mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
                 full = torch.full((B,), S, dtype=torch.int32, device=dev)
-                p = {"seq_start": mk([b * S for b in range(B)]), "vt_start": mk([b * s_pad for b in range(B)]),
-                     "vt_cols": B * s_pad, "max_len": S, "n_seq": B, "q_len": full, "kv_len": full}
+                p = {"seq_start": mk([b * S for b in range(B)]), "max_len": S, "n_seq": B, "q_len": full, "kv_len": full}
                 plans[(B, S)] = p
             return p
 

@@ -88,10 +88,8 @@ class EncoderRunner:
             shape = (B * nb + 1, self.heads_local, KV_BLOCK, self.head_dim)
             kc = torch.zeros(shape, dtype=self.dtype, device=dev)
             vc = torch.zeros(shape, dtype=self.dtype, device=dev)
-            s_pad = -(-S // 128) * 128
             mk = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
-            dense = {"seq_start": mk([b * S for b in range(B)]), "vt_start": mk([b * s_pad for b in range(B)]),
-                     "vt_cols": B * s_pad, "max_len": S, "n_seq": B,
+            dense = {"seq_start": mk([b * S for b in range(B)]), "max_len": S, "n_seq": B,
                      "q_len": torch.full((B,), S, dtype=torch.int32, device=dev)}
             plan = (tok_seq, pos, slots, bt, kc, vc, nb * KV_BLOCK, dense)
             self._scratch[key] = plan

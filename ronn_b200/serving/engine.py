@@ -339,18 +339,28 @@ class LLMEngine:
         return False
 
     def _dense_prefill_plan(self, n_tokens: int, n_items: int):
-        """Index tensors for tensor-core prefill attention when every item of the step is a whole prompt starting at
-        position 0 (no prefix-cache hit, no chunk continuation); None otherwise (the paged kernel handles those)."""
+        """Index tensors for tensor-core prefill attention: over the fused qkv buffer when every item of the step is
+        a whole prompt starting at position 0, over the paged cache (``"paged"`` in the plan) when items continue a
+        chunked prompt or start behind a prefix-cache hit; None where the per-row paged kernel is the better fit."""
         if self.cfg.backend != "kernels" or self.device.type != "cuda" or not self.cfg.dense_prefill:
             return None
         h = self.host
         item = h.field("token_item")[:n_tokens]
         starts = np.flatnonzero(np.diff(item, prepend=-1))
-        if len(starts) != n_items or h.field("positions")[:n_tokens][starts].any():
+        if len(starts) != n_items:
             return None
         lens = np.diff(starts, append=n_tokens)
+        first_pos = h.field("positions")[:n_tokens][starts]
         from ..ops import kernels as K
-        return K.dense_attention_plan(lens.tolist(), self.device)
+        if not first_pos.any():
+            return K.dense_attention_plan(lens.tolist(), self.device)
+        # chunk continuations / prefix-cache hits: the same kernel reads K and V from the paged cache.  Its 128-query
+        # tiles do not pay for a handful of tokens per item; those steps stay on the per-row kernel.
+        if n_tokens < 32 * n_items:
+            return None
+        mk = lambda v: torch.tensor(np.asarray(v, dtype=np.int32), device=self.device)
+        return {"paged": True, "seq_start": mk(starts), "q_len": mk(lens), "kv_len": mk(first_pos + lens),
+                "max_q_len": int(lens.max()), "n_seq": n_items}
 
     def _run_and_sample(self, b, decode, n_tokens, n_items, req_ids) -> torch.Tensor:
         greedy = self._non_greedy == 0 or all(self.requests[int(i)].params.temperature <= 0 for i in req_ids)

@@ -309,7 +309,12 @@ class DecoderRunner:
             else:
                 ops.kv_append(qkv, hn, hn + kn, slots, self.kcache[li], self.vcache[li], self.n_head_local,
                               self.n_kv_local, d, pos, a.rope_base)
-                if dense_plan is not None:
+                if dense_plan is not None and dense_plan.get("paged"):
+                    # chunk continuations and prefix hits: the queries of this step against the paged cache, which
+                    # holds the earlier context and (appended above) this step's tokens
+                    att = ops.paged_prefill_attention(qkv, self.kcache[li], self.vcache[li], b["block_tables"],
+                                                      dense_plan, self.n_head_local, self.n_kv_local, d)
+                elif dense_plan is not None:
                     # whole prompts without cached context: causal attention on the tensor cores, straight from the
                     # (already rotated) fused qkv buffer; the cache was filled above for the decode steps to come
                     att = ops.dense_attention(qkv, 0, hn, hn + kn, dense_plan, self.n_head_local, self.n_kv_local, d,

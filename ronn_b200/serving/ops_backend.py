@@ -178,6 +178,11 @@ class KernelOps:
         """Whole-sequence attention on the tensor cores, straight from the fused qkv buffer."""
         return self.K.dense_attention(qkv, q_off, k_off, v_off, plan, heads, kv_heads, d, causal, q_len, max_q_len)
 
+    def paged_prefill_attention(self, q, kcache, vcache, block_tables, plan, heads, kv_heads, d):
+        """Causal attention of this step's query chunks over the paged cache, on the tensor cores."""
+        return self.K.paged_prefill_attention(q, 0, kcache, vcache, block_tables, plan["seq_start"], plan["q_len"],
+                                              plan["kv_len"], plan["max_q_len"], heads, kv_heads, d, causal=True)
+
     def argmax(self, logits, col_offset=0, return_max=False):
         return self.K.argmax(logits, col_offset, return_max)
 

@@ -155,3 +155,43 @@ def test_engine_logits_match_an_fp32_reference_of_the_graph():
         got1 = r.forward(d, True, 1, 1, want_logits=True)[:, :1000].float().cpu()
         assert float((got1[0] - want[T]).abs().max()) < 0.04 * scale
         assert int(got1[0].argmax()) == int(want[T].argmax()) or float(want[T].topk(2).values.diff().abs()) < 0.04 * scale
+
+
+def test_chunked_prefill_and_prefix_hits_use_the_paged_tensor_core_kernel():
+    """Prompts longer than a step's token budget continue in later steps, and a shared prefix is served from the
+    cache: those steps attend through the paged tensor-core kernel and produce the tokens of the per-row paged kernel
+    and of the operator backend."""
+    from ronn_b200 import _native
+    from ronn_b200.api.model import Model
+    from ronn_b200.models.gpt2 import GPT2Config, build_gpt2
+    from ronn_b200.serving import EngineConfig, LLMEngine, SamplingParams
+    cfg = GPT2Config.tiny(n_layer=2, n_embd=256, n_head=4, vocab_size=1000, n_positions=1024)
+    model = Model.from_graph(build_gpt2(cfg, dtype=torch.bfloat16, seed=11))
+    g = torch.Generator().manual_seed(1)
+    shared = torch.randint(0, 1000, (160,), generator=g).tolist()
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (700, 333, 129)]
+    prompts += [shared + [5, 6, 7] * 20, shared + [9] * 70]
+    outs = {}
+    lib = _native.cuda()
+    calls = {"n": 0}
+    real = lib.ronn_fmha_paged
+    lib.__dict__["ronn_fmha_paged"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
+    try:
+        for name, backend, dense in (("tensor", "kernels", True), ("rows", "kernels", False), ("torch", "torch", False)):
+            ec = EngineConfig(max_num_seqs=8, max_batch_tokens=256, max_model_len=1024, num_blocks=512, dtype="bf16",
+                              backend=backend, use_cuda_graph=(backend == "kernels"), enable_prefix_cache=True,
+                              prefill_chunk=128, dense_prefill=dense)
+            eng = LLMEngine(model, ec, device=torch.device("cuda", 0))
+            outs[name] = eng.generate(prompts[:3], SamplingParams(max_new_tokens=6))
+            outs[name] += eng.generate(prompts[3:4], SamplingParams(max_new_tokens=6))
+            outs[name] += eng.generate(prompts[4:], SamplingParams(max_new_tokens=6))         # prefix hit
+            if name == "tensor":
+                assert calls["n"] >= 2 * 3, calls               # at least three continuation steps, two layers each
+                n_tensor = calls["n"]
+        assert calls["n"] == n_tensor                           # the other two engines never reach it
+    finally:
+        lib.__dict__["ronn_fmha_paged"] = real
+    same = lambda a, b: sum(x == y for p, q in zip(outs[a], outs[b]) for x, y in zip(p, q))
+    assert sum(len(x) for x in outs["tensor"]) == 30
+    assert same("tensor", "rows") >= 27, outs
+    assert same("tensor", "torch") >= 24, outs                  # a random tiny model has near ties in bf16

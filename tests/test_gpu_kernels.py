@@ -495,6 +495,52 @@ def test_dense_attention_padded_encoder(K):
         torch.testing.assert_close(out[b * S:(b + 1) * S].float().view(S, heads, d), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (64, 8, 2), (128, 4, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_paged_prefill_attention_cached_context(K, d, heads, kv_heads, dtype):
+    """Query chunks over the paged cache: (cached context, new tokens) per sequence; the new tokens' K / V are in the
+    cache already, every query sees the context and the new tokens up to itself."""
+    torch.manual_seed(7)
+    cases = [(0, 37), (16, 1), (100, 128), (300, 200), (517, 3), (128, 129), (0, 256)]
+    max_blocks = 48
+    nblocks = len(cases) * max_blocks + 1
+    perm = (torch.randperm(nblocks - 1)[: len(cases) * max_blocks] + 1).reshape(len(cases), max_blocks).to(torch.int32).cuda()
+    kc = torch.zeros(nblocks, kv_heads, 16, d, device="cuda", dtype=dtype)
+    vc = torch.zeros_like(kc)
+    hn = heads * d
+    T = sum(c for _, c in cases)
+    qbuf = _rand(T, hn + 24, dtype=dtype)                 # queries at column 8 of a wider buffer
+    ks, vs, starts, t = [], [], [], 0
+    for b, (ctx, new) in enumerate(cases):
+        n = ctx + new
+        k, v = _rand(n, kv_heads, d, dtype=dtype), _rand(n, kv_heads, d, dtype=dtype)
+        for tok in range(n):
+            blk = int(perm[b, tok // 16])
+            kc[blk, :, tok % 16] = k[tok]
+            vc[blk, :, tok % 16] = v[tok]
+        ks.append(k.float())
+        vs.append(v.float())
+        starts.append(t)
+        t += new
+    mk = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    out = K.paged_prefill_attention(qbuf, 8, kc, vc, perm, mk(starts), mk([c for _, c in cases]),
+                                    mk([a + c for a, c in cases]), max(c for _, c in cases), heads, kv_heads, d)
+    K.check_status()
+    for b, (ctx, new) in enumerate(cases):
+        q = qbuf[starts[b]:starts[b] + new, 8:8 + hn].float().view(new, heads, d)
+        ref = _sdpa_ref(q, ks[b], vs[b], True, shift=ctx)
+        torch.testing.assert_close(out[starts[b]:starts[b] + new].float().view(new, heads, d), ref, atol=2e-2, rtol=2e-2)
+    # a table row shared by two sequences (bt_row) and full visibility (no causal mask)
+    bt_row = mk([3, 3])
+    out2 = K.paged_prefill_attention(qbuf[:40], 8, kc, vc, perm, mk([0, 20]), mk([20, 20]), mk([500, 321]), 20, heads,
+                                     kv_heads, d, causal=False, bt_row=bt_row)
+    K.check_status()
+    for i, n in enumerate((500, 321)):
+        q = qbuf[i * 20:(i + 1) * 20, 8:8 + hn].float().view(20, heads, d)
+        ref = _sdpa_ref(q, ks[3][:n], vs[3][:n], False)
+        torch.testing.assert_close(out2[i * 20:(i + 1) * 20].float().view(20, heads, d), ref, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("M,N,K_", [(256, 1024, 1024), (256, 1024, 4096), (100, 384, 512), (130, 128, 64), (1, 768, 3072)])
 @pytest.mark.parametrize("norm", ["layernorm", "rmsnorm"])
 def test_gemm_rownorm_cluster(K, M, N, K_, norm):

@@ -183,13 +183,13 @@ def test_gpu_session_runs_elementwise_chains_and_attention_on_kernels():
     mask[3, 5:] = 0
     want = m.create_session(SessionOptions().with_optimization_level("O0")).run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"]
     s = m.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3").with_dtype("bf16"))
-    counts, saved = counting(["ronn_flash_attention", "ronn_gemm"])
+    counts, saved = counting(["ronn_fmha", "ronn_gemm"])
     try:
         got = s.run({"input_ids": ids, "attention_mask": mask})["last_hidden_state"].float().cpu()
     finally:
         for n, f in saved.items():
             lib.__dict__[n] = f
-    assert counts["ronn_flash_attention"] == 2 and counts["ronn_gemm"] == 2 * 4        # fused QKV + out + two MLP per layer
+    assert counts["ronn_fmha"] == 2 and counts["ronn_gemm"] == 2 * 4        # fused QKV + out + two MLP per layer
     for bi, n in enumerate(mask.sum(1).tolist()):
         torch.testing.assert_close(got[bi, :n], want[bi, :n].float(), atol=8e-2, rtol=5e-2)
 
@@ -243,11 +243,11 @@ def test_attention_core_written_in_primitives_runs_the_tensor_core_kernel():
         ops = [n.op_type for n in sess.graph().nodes]
         assert ops.count("ScaledDotProductAttention") == 1 and "Softmax" not in ops
         calls = {"n": 0}
-        real = lib.ronn_flash_attention
-        lib.__dict__["ronn_flash_attention"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
+        real = lib.ronn_fmha
+        lib.__dict__["ronn_fmha"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
         try:
             got = sess.run(feeds)["y"].float().cpu()
         finally:
-            lib.__dict__["ronn_flash_attention"] = real
+            lib.__dict__["ronn_fmha"] = real
         assert calls["n"] == (0 if masked else 1)
         torch.testing.assert_close(got, want, atol=4e-2, rtol=4e-2)
