@@ -177,7 +177,8 @@ def bench_distilbert(batch=64, seq=128, iters=20):
     ids = torch.randint(0, 30522, (batch, seq), generator=gen).cuda()
     mask = torch.ones(batch, seq, dtype=torch.int64, device="cuda")
     out = {}
-    runner = EncoderRunner(graph, dtype=torch.bfloat16, comm=comm)
+    sp = world > 1 and os.environ.get("RONN_ENCODER_SP", "0") == "1"      # token-sharded layout on the fused kernels
+    runner = EncoderRunner(graph, dtype=torch.bfloat16, comm=comm, sequence_parallel=sp)
     static_ids = ids.clone()
     runner.forward(static_ids, mask)
     torch.cuda.synchronize()
@@ -201,7 +202,7 @@ def bench_distilbert(batch=64, seq=128, iters=20):
         out["torch_ops_eager"] = {"p50_ms": round(p50, 4)}
         out["max_abs_err_vs_torch_ops"] = round((y.float() - ref.float()).abs().max().item(), 4)
     out["config"] = {"model": "distilbert-base", "batch": batch, "seq": seq, "dtype": "bf16", "tp": world,
-                     "l2": "flushed between iterations"}
+                     "sequence_parallel": bool(sp), "l2": "flushed between iterations"}
     if world > 1:
         import sys
         if rank == 0:

@@ -76,7 +76,12 @@ class TPComm:
         """[world*m, n] partial sums -> this rank's [m, n] of the total"""
         if self.world == 1:
             return x
-        out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        per = x.shape[0] // self.world
+        if dist.get_backend(self.group) == "gloo":          # no reduce-scatter there: sum everything, keep the shard
+            full = x.contiguous().clone()
+            dist.all_reduce(full, group=self.group)
+            return full[self.rank * per:(self.rank + 1) * per].contiguous()
+        out = torch.empty((per,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
         dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
         return out
 

@@ -8,6 +8,13 @@ fused device weights once: Q, K and V projections become one column-parallel GEM
 kernel straight from the fused QKV buffer (head sizes 64 / 128; others use the paged kernel over a scratch K/V layout), and every block ends in ONE kernel that does the row-parallel GEMM, the cross-rank
 reduction, the bias, the residual and the LayerNorm (``FusedComm.gemm_allreduce(norm=...)``) when tensor parallelism is
 on.  Without tensor parallelism the GEMM epilogue adds bias + residual and the LayerNorm kernel follows.
+
+``sequence_parallel=True`` keeps the activations between the row-parallel and the column-parallel projections sharded
+by token: every rank embeds and normalises 1/W of the tokens, the column-parallel GEMMs (QKV, MLP-up) read the
+gathered activations tile by tile from the peers' shards (``FusedComm.ag_gemm``), and the row-parallel GEMMs
+(attention output, MLP-down) end in a reduce-scatter that leaves each rank its own tokens
+(``FusedComm.gemm_reduce_scatter``), so LayerNorm, bias and residual touch T / W rows.  With library collectives (or
+token counts that are not a multiple of 128 per rank) the same layout runs on all-gather / reduce-scatter calls.
 """
 from __future__ import annotations
 
@@ -21,7 +28,8 @@ from .ops_backend import make_ops
 
 
 class EncoderRunner:
-    def __init__(self, graph, device=None, dtype: torch.dtype = torch.bfloat16, comm=None, backend: str = "kernels"):
+    def __init__(self, graph, device=None, dtype: torch.dtype = torch.bfloat16, comm=None, backend: str = "kernels",
+                 sequence_parallel: bool = False):
         md = graph.metadata
         if md.get("ronn.arch") != "distilbert":
             raise SessionError(f"EncoderRunner needs a DistilBERT graph (ronn.arch={md.get('ronn.arch')!r})")
@@ -34,6 +42,7 @@ class EncoderRunner:
         self.ops = make_ops(backend, self.device)
         self.comm = comm or NoComm()
         self.tp, self.rank = self.comm.world, self.comm.rank
+        self.sequence_parallel = bool(sequence_parallel) and self.comm.world > 1
         self.n_layers, self.hidden = int(md["ronn.n_layers"]), int(md["ronn.dim"])
         self.n_heads, self.ffn = int(md["ronn.n_heads"]), int(md["ronn.hidden_dim"])
         self.max_pos, self.eps = int(md["ronn.max_pos"]), float(md["ronn.eps"])
@@ -128,6 +137,9 @@ class EncoderRunner:
             ctx = lens.repeat_interleave(S)
         d, hl = self.head_dim, self.heads_local
         hn = hl * d
+        if self.sequence_parallel and (B * S) % self.tp == 0:
+            return self._forward_token_sharded(ids, pos, B, S, tensor_core, dense,
+                                               None if tensor_core else (slots, kc, vc, bt, ctx, max_ctx, tok_seq))
         x = ops.embedding(ids, self.wte, pos, self.wpe)
         x = ops.layernorm(x, self.emb_ln[0], self.emb_ln[1], self.eps)
         for L in self.layers:
@@ -141,3 +153,44 @@ class EncoderRunner:
             f = ops.gemm(x, L["up"].w, L["up"].bias, None, "gelu")
             x = self._row_parallel(f, L["down"], x, L["ln2"])
         return x.view(B, S, self.hidden)
+
+    def _forward_token_sharded(self, ids, pos, B, S, tensor_core, dense, paged):
+        """The sequence-parallel layout: this rank owns tokens [rank * T / W, (rank + 1) * T / W) between the
+        projections; attention still sees every token of the local heads."""
+        ops, comm = self.ops, self.comm
+        T = B * S
+        per = T // self.tp
+        r0 = self.rank * per
+        d, hl, H = self.head_dim, self.heads_local, self.hidden
+        hn = hl * d
+        fused = getattr(comm, "fused", False) and ops.name == "kernels" and per % 128 == 0
+
+        def column_parallel(x_local, lw, act=""):
+            if fused:
+                shard = comm.shard_buffer(per, H, x_local.dtype)
+                shard.copy_(x_local)
+                comm.signal_shard_ready()
+                return comm.ag_gemm(per, H, lw.w, lw.bias, act)
+            return ops.gemm(comm.all_gather_rows(x_local), lw.w, lw.bias, None, act)
+
+        def row_parallel(inp, lw, residual_local, ln):
+            if fused:
+                y = comm.gemm_reduce_scatter(inp, lw.w, lw.bias, residual_local)
+            else:
+                y = comm.reduce_scatter_rows(ops.gemm(inp, lw.w)) + lw.bias + residual_local
+            return ops.layernorm(y, ln[0], ln[1], self.eps)
+
+        x = ops.embedding(ids[r0:r0 + per].contiguous(), self.wte, pos[r0:r0 + per].contiguous(), self.wpe)
+        x = ops.layernorm(x, self.emb_ln[0], self.emb_ln[1], self.eps)
+        for L in self.layers:
+            qkv = column_parallel(x, L["qkv"])
+            if tensor_core:
+                att = ops.dense_attention(qkv, 0, hn, 2 * hn, dense, hl, hl, d, False, dense["q_len"], S)
+            else:
+                slots, kc, vc, bt, ctx, max_ctx, tok_seq = paged
+                ops.kv_append(qkv, hn, 2 * hn, slots, kc, vc, hl, hl, d)
+                att = ops.paged_attention(qkv, kc, vc, bt, ctx, hl, hl, d, max_ctx, tok_seq)
+            x = row_parallel(att, L["out"], x, L["ln1"])
+            f = column_parallel(x, L["up"], "gelu")
+            x = row_parallel(f, L["down"], x, L["ln2"])
+        return comm.all_gather_rows(x).view(B, S, H)

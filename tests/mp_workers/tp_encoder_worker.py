@@ -22,14 +22,16 @@ def main():
     mask[1, 15:] = 0
     tp = EncoderRunner(graph, device="cpu", comm=TPComm()).forward(ids, mask)
     single = EncoderRunner(graph, device="cpu").forward(ids, mask)
-    err = 0.0
+    sp = EncoderRunner(graph, device="cpu", comm=TPComm(), sequence_parallel=True).forward(ids, mask)
+    err, err_sp = 0.0, 0.0
     for b, n in enumerate(mask.sum(1).tolist()):
         err = max(err, (tp[b, :n] - single[b, :n]).abs().max().item())
+        err_sp = max(err_sp, (sp[b, :n] - single[b, :n]).abs().max().item())
     gathered = [None] * world
     torch.distributed.all_gather_object(gathered, tp[0, :5, :8].tolist())
     if rank == 0:
         with open(out_path, "w") as f:
-            json.dump({"world": world, "err": err, "same_across_ranks": all(x == gathered[0] for x in gathered)}, f)
+            json.dump({"world": world, "err": err, "err_sequence_parallel": err_sp, "same_across_ranks": all(x == gathered[0] for x in gathered)}, f)
     torch.distributed.barrier()
     torch.distributed.destroy_process_group()
 

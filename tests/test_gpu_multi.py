@@ -29,6 +29,17 @@ def test_fused_gemm_allreduce_and_reduce_scatter(tmp_path):
 
 
 @need2
+def test_sequence_parallel_encoder_on_fused_kernels_matches_single_gpu(tmp_path):
+    out = tmp_path / "sp.json"
+    p = launch(_world(), "sp_encoder_worker.py", [str(out)], 29670, env={"NCCL_NVLS_ENABLE": "0"})
+    assert p.returncode == 0, (p.stdout[-2000:], p.stderr[-4000:])
+    r = json.loads(out.read_text())
+    assert r["same_across_ranks"]
+    assert r["fused_calls"] == 2 * 4, r              # per layer: two gather-GEMMs and two GEMM-reduce-scatters
+    assert r["err"] < 0.12, r                        # bf16 activations of O(1) through two layers
+
+
+@need2
 @pytest.mark.parametrize("mode", ["nccl", "fused"])
 def test_tp_engine_matches_single_gpu(tmp_path, mode):
     out = tmp_path / "r.json"

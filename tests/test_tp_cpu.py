@@ -91,6 +91,7 @@ def test_tp_encoder_on_cpu_ranks_matches_single_rank(tmp_path, world):
     r = json.loads(out.read_text())
     assert r["world"] == world and r["same_across_ranks"]
     assert r["err"] < 1e-4
+    assert r["err_sequence_parallel"] < 1e-4          # token-sharded layout: all-gather / reduce-scatter around the GEMMs
 
 
 def test_space_to_depth_stem_weights_reproduce_the_7x7_stride2_convolution():
