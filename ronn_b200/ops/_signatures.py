@@ -40,7 +40,7 @@ def declare(lib):
     sig("ronn_sample", [V, L, I, L, V, V, I, V, V, V], optional=True)
     sig("ronn_cast", [V, V, L, I, I, V])
     sig("ronn_kv_append", [V, L, I, I, V, V, V, V, L, I, I, I, F, I, I, V])
-    sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V, F, V])
+    sig("ronn_paged_attention", [V, L, V, V, V, I, V, V, V, L, L, I, I, I, I, F, I, I, I, V, V, F, I, V, V, V])
     sig("ronn_gemm_rownorm", [V, V, V, V, V, V, V, V, I, I, I, I, I, I, F, I, I, V, V], optional=True)
     sig("ronn_fmha", [V, L, L, I, I, I, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])
     sig("ronn_fmha_paged", [V, L, L, I, V, V, L, V, I, V, V, V, V, V, L, I, I, I, I, I, I, F, I, V, V])

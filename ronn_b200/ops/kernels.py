@@ -315,18 +315,52 @@ def kv_append(qkv: torch.Tensor, k_off: int, v_off: int, slots: torch.Tensor, kc
                                          head_dim, float(rope_base), use_rope, _DT[qkv.dtype], _stream()), "kv_append")
 
 
+_ATTN_SPLIT_WS = {}
+
+
+def attention_split_workspace(device, items: int, splits: int, head_dim: int):
+    """(partials, tickets) of the split decode attention, one pair per (device, stream): fp32 partial sums and the
+    int32 ticket of every (row, head), zero between launches (the kernel resets what it used)."""
+    dev = torch.device(device)
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    need = items * splits * (head_dim + 2)
+    ws = _ATTN_SPLIT_WS.get(key)
+    if ws is None or ws[0].numel() < need or ws[1].numel() < items:
+        ws = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=dev),
+              torch.zeros(max(items, 1 << 14), dtype=torch.int32, device=dev))
+        _ATTN_SPLIT_WS[key] = ws
+    return ws
+
+
+def attention_splits(rows: int, heads: int, max_ctx: int) -> int:
+    """CTAs per (row, head) of the decode attention kernel.  One, at every size measured (256 rows, mean context 416,
+    2 to 16 heads per GPU): a split CTA pays its start-up, the ticket and the combining pass for a fraction of the
+    work, and lost 10-50 % against one CTA per (row, head) once the kernel prefetched its next cache block.
+    ``RONN_ATTN_SPLITS`` overrides (long single sequences, few rows)."""
+    env = os.environ.get("RONN_ATTN_SPLITS")
+    if env:
+        return max(1, min(16, int(env)))
+    return 1
+
+
 def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_tables: torch.Tensor,
                     ctx_len: torch.Tensor, heads: int, kv_heads: int, head_dim: int, max_ctx: int,
                     bt_row: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                    scale: Optional[float] = None, append=None, rope=None) -> torch.Tensor:
+                    scale: Optional[float] = None, append=None, rope=None, splits: Optional[int] = None) -> torch.Tensor:
     """q: [rows, >= heads*head_dim] (row stride free).  Returns [rows, heads*head_dim].
     ``append=(k_off, v_off, slots)`` (decode, one row per sequence): the new K/V columns of the fused QKV row are
     written to their cache slots by the same kernel.  ``rope=(positions int32 [rows], base)`` with ``append``: q and the
-    new k are rotated by the same kernel too (the q row in memory stays as it is)."""
+    new k are rotated by the same kernel too (the q row in memory stays as it is).  ``splits`` CTAs share the cache
+    blocks of one (row, head) and the last to finish combines them (default: ``attention_splits``)."""
     rows = q.shape[0]
     if out is None:
         out = torch.empty((rows, heads * head_dim), dtype=q.dtype, device=q.device)
     sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if splits is None:
+        splits = attention_splits(rows, heads, int(max_ctx))
+    part, tickets = attention_split_workspace(q.device, rows * heads, splits, head_dim) if splits > 1 else (None, None)
     _check(_native.cuda().ronn_paged_attention(q.data_ptr(), q.stride(0), kcache.data_ptr(), vcache.data_ptr(),
                                                block_tables.data_ptr(), block_tables.shape[1], ctx_len.data_ptr(),
                                                _ptr(bt_row), out.data_ptr(), out.stride(0), rows, heads, kv_heads,
@@ -334,7 +368,7 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                                                append[0] if append else 0, append[1] if append else 0,
                                                append[2].data_ptr() if append else None,
                                                rope[0].data_ptr() if rope else None, float(rope[1]) if rope else 0.0,
-                                               _stream()),
+                                               int(splits), _ptr(part), _ptr(tickets), _stream()),
            "paged_attention")
     return out
 

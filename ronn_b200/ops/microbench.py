@@ -158,23 +158,34 @@ def bench_gemm(m, n, k, dtype=torch.bfloat16, bn=0, act="", flush=True, iters=20
     return res
 
 
-def bench_attention(batch, ctx, heads, dim, kv_heads=None, dtype=torch.bfloat16, flush=True, iters=20):
+def bench_attention(batch, ctx, heads, dim, kv_heads=None, dtype=torch.bfloat16, flush=True, iters=20, ragged=False,
+                    splits=None):
+    """Decode attention over a paged cache.  ``ragged``: context lengths uniform in [ctx / 4, 7 ctx / 4] (mean ctx)
+    instead of all equal.  Timed as a CUDA-graph replay over caches that together exceed L2."""
     kv_heads = kv_heads or heads
-    nb_seq = (ctx + 15) // 16
+    gen = torch.Generator().manual_seed(0)
+    lens_h = torch.randint(max(ctx // 4, 1), 7 * ctx // 4 + 1, (batch,), generator=gen) if ragged else torch.full((batch,), ctx)
+    max_len = int(lens_h.max())
+    nb_seq = (max_len + 15) // 16
     nblocks = batch * nb_seq
-    kc = torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype)
-    vc = torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype)
+    per_set = 2 * nblocks * kv_heads * 16 * dim * 2
+    nvar = max(2, int(400e6 // per_set) + 1) if flush else 1
+    kcs = [torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype) for _ in range(nvar)]
+    vcs = [torch.randn(nblocks, kv_heads, 16, dim, device="cuda").to(dtype) for _ in range(nvar)]
     bt = torch.randperm(nblocks, device="cuda").to(torch.int32).reshape(batch, nb_seq)
     q = torch.randn(batch, heads * dim, device="cuda").to(dtype)
-    lens = torch.full((batch,), ctx, device="cuda", dtype=torch.int32)
+    lens = lens_h.to("cuda", torch.int32)
     out = torch.empty(batch, heads * dim, device="cuda", dtype=dtype)
-    us = time_kernel(lambda: K.paged_attention(q, kc, vc, bt, lens, heads, kv_heads, dim, max_ctx=max(ctx, 16), out=out),
-                     iters=iters, flush=flush)
+    mc = -(-max_len // 16) * 16
+    sp = splits if splits else K.attention_splits(batch, heads, mc)
+    us = time_graph(lambda i: K.paged_attention(q, kcs[i], vcs[i], bt, lens, heads, kv_heads, dim, max_ctx=mc, out=out,
+                                                splits=sp), nvar, reps=max(nvar, 20), iters=max(3, iters // 4))
     hbm, tf, src = _peaks()
-    byts = 2.0 * batch * ctx * kv_heads * dim * 2
+    byts = 2.0 * float(lens_h.sum()) * kv_heads * dim * 2
     t_roof = byts / (hbm * 1e9) * 1e6
-    return {"kernel": "paged_attention", "batch": batch, "ctx": ctx, "heads": heads, "dim": dim, "us": round(us, 2),
-            "gbs": round(byts / us / 1e3, 1), "roofline_us": round(t_roof, 2), "frac_of_" + src: round(t_roof / us, 3)}
+    return {"kernel": "paged_attention", "batch": batch, "ctx": ctx, "ragged": bool(ragged), "heads": heads, "dim": dim,
+            "splits": sp, "us": round(us, 2), "gbs": round(byts / us / 1e3, 1), "roofline_us": round(t_roof, 2),
+            "frac_of_" + src: round(t_roof / us, 3)}
 
 
 def bench_norm(rows, h, dtype=torch.bfloat16, flush=True):
@@ -359,6 +370,8 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--ragged", action="store_true", help="attention: context lengths spread around --ctx")
+    ap.add_argument("--splits", type=int, default=0, help="attention: CTAs per (row, head); 0 = the default rule")
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--causal", action="store_true")
     a = ap.parse_args()
@@ -366,7 +379,8 @@ def main():
     if a.what == "gemm":
         res = [bench_gemm(a.m, a.n, a.k, bn=a.bn, flush=fl, iters=a.iters)]
     elif a.what == "attention":
-        res = [bench_attention(a.batch, a.ctx, a.heads, a.dim, flush=fl, iters=a.iters)]
+        res = [bench_attention(a.batch, a.ctx, a.heads, a.dim, flush=fl, iters=a.iters, ragged=a.ragged,
+                               splits=a.splits or None)]
     elif a.what == "memory-kernels":
         res = bench_memory_kernels(flush=fl)
     elif a.what == "norm":

@@ -299,6 +299,51 @@ def test_kv_append_rope(K):
     torch.testing.assert_close(got_k.float(), ref_k.float(), atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (128, 4, 2), (64, 2, 2)])
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_paged_attention_split_over_cache_blocks(K, d, heads, kv_heads, splits):
+    """Several CTAs per (row, head), combined by the last one to finish: same result as one CTA, for contexts shorter
+    than the number of splits, empty rows, and twice in a row (the tickets return to zero)."""
+    torch.manual_seed(4)
+    dtype = torch.bfloat16
+    lens = [0, 1, 15, 16, 17, 33, 100, 333, 640, 48]
+    B, max_blocks = len(lens), 40
+    nblocks = B * max_blocks
+    perm = torch.randperm(nblocks).reshape(B, max_blocks).to(torch.int32).cuda()
+    kc = (torch.randn(nblocks, kv_heads, 16, d, device="cuda") * 0.5).to(dtype)
+    vc = (torch.randn(nblocks, kv_heads, 16, d, device="cuda") * 0.5).to(dtype)
+    q = _rand(B, heads * d, dtype=dtype)
+    ctx = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    one = K.paged_attention(q, kc, vc, perm, ctx, heads, kv_heads, d, max_ctx=640, splits=1)
+    for _ in range(2):
+        many = K.paged_attention(q, kc, vc, perm, ctx, heads, kv_heads, d, max_ctx=640, splits=splits)
+        K.check_status()
+        torch.testing.assert_close(many.float(), one.float(), atol=4e-3, rtol=1e-2)
+    assert float(many[0].abs().max()) == 0.0
+    # fp32 restatement of one long row
+    b, n = 8, lens[8]
+    kk = torch.stack([kc[int(perm[b, t // 16]), :, t % 16] for t in range(n)]).float()
+    vv = torch.stack([vc[int(perm[b, t // 16]), :, t % 16] for t in range(n)]).float()
+    rep = heads // kv_heads
+    s_ = torch.einsum("hd,lhd->hl", q[b].float().view(heads, d), kk.repeat_interleave(rep, dim=1)) / math.sqrt(d)
+    want = torch.einsum("hl,lhd->hd", torch.softmax(s_, -1), vv.repeat_interleave(rep, dim=1)).reshape(-1)
+    torch.testing.assert_close(many[b].float(), want, atol=2e-2, rtol=2e-2)
+    # with the fused append and rotary embedding
+    qkv = _rand(B, (heads + 2 * kv_heads) * d, dtype=dtype)
+    pos = torch.tensor([max(n - 1, 0) for n in lens], device="cuda", dtype=torch.int32)
+    slots = torch.tensor([int(perm[i, max(n - 1, 0) // 16]) * 16 + max(n - 1, 0) % 16 if n > 0 else -1
+                          for i, n in enumerate(lens)], device="cuda", dtype=torch.int32)
+    kc1, vc1 = kc.clone(), vc.clone()
+    a1 = K.paged_attention(qkv, kc1, vc1, perm, ctx, heads, kv_heads, d, max_ctx=640,
+                           append=(heads * d, (heads + kv_heads) * d, slots), rope=(pos, 10000.0), splits=1)
+    kc2, vc2 = kc.clone(), vc.clone()
+    a2 = K.paged_attention(qkv, kc2, vc2, perm, ctx, heads, kv_heads, d, max_ctx=640,
+                           append=(heads * d, (heads + kv_heads) * d, slots), rope=(pos, 10000.0), splits=splits)
+    K.check_status()
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    torch.testing.assert_close(a2.float(), a1.float(), atol=4e-3, rtol=1e-2)
+
+
 @pytest.mark.parametrize("d,heads,kv_heads", [(64, 4, 4), (128, 8, 2)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_rope_append_attention_in_one_launch(K, d, heads, kv_heads, dtype):
