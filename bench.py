@@ -131,7 +131,7 @@ class ClockSampler:
 
 # tokens/s of the library arm (`bench.py --impl baseline`) on this pool's B200s, by GPU count; the same numbers and the
 # logs they come from are listed in BASELINE.md section 5.1.  None: not measured at that GPU count.
-LIBRARY_BASELINE_TOKENS_S = {1: 51053.5, 2: 62437.2, 4: 78555.7, 8: 71408.2}
+LIBRARY_BASELINE_TOKENS_S = {1: 51121.5, 2: 62437.2, 4: 78555.7, 8: 71408.2}
 
 
 def library_baseline_tokens_s(world: int):
