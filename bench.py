@@ -26,7 +26,7 @@ Further keys of the line:
                     library's call counter (graph replays add the count recorded at capture)
   resnet18_p50_ms   (N = 1) ResNet-18 fp16 batch 32, O3, p50 latency through Model.create_session / session.run
   bitnet_tp8_tokens_s  (N = 8) BitNet b1.58 2B-style decoder, batch 128 decode, tensor parallel over the 8 GPUs
-  vs_baseline       value divided by the library arm's tokens/s at the same N recorded in BASELINE.md (the reference
+  vs_baseline       value divided by the library arm's tokens/s at the same N, from the kept logs (the reference
                     publishes no number for this metric)
 
 ``--impl baseline`` runs the library arm (``baseline/library_decode.py``: cuBLAS + SDPA + NCCL, one CUDA graph per
@@ -130,7 +130,7 @@ class ClockSampler:
 
 
 # tokens/s of the library arm (`bench.py --impl baseline`) on this pool's B200s, by GPU count; the same numbers and the
-# logs they come from are listed in BASELINE.md section 5.1.  None: not measured at that GPU count.
+# logs they come from are kept under profiles/logs (bench_library_n*.log).  None: not measured at that GPU count.
 LIBRARY_BASELINE_TOKENS_S = {1: 51121.5, 2: 62437.2, 4: 78555.7, 8: 71408.2}
 
 
@@ -322,7 +322,7 @@ def main():
                          "what": "admission + chunked prefill + decode + retirement of the whole workload, wall clock"},
             "gpu_launches": int(launches),
             "baseline_on_this_box": {"tokens_per_s": lib_base, "impl": "bench.py --impl baseline (cuBLAS + SDPA + NCCL, CUDA graph)",
-                                     "source": "BASELINE.md section 5.1"},
+                                     "source": "profiles/logs/bench_library_n%d.log" % world},
             **extra,
         }))
     sys.stdout.flush()
