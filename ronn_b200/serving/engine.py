@@ -46,6 +46,26 @@ class StepOutput:
 _BUCKETS = [1, 2, 4, 8, 16, 32, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 768, 1024]
 
 
+def classify_prefill_step(token_item: np.ndarray, positions: np.ndarray, n_items: int):
+    """Which attention kernel a prefill step takes, from the item index and the position of each of its tokens (items
+    occupy consecutive token ranges).  ``("dense", lens)``: every item is a whole prompt from position 0, attention
+    reads K and V from the fused qkv buffer.  ``("paged", starts, lens, first_pos)``: some item continues a chunked
+    prompt or starts behind a prefix-cache hit, the tensor-core kernel reads the paged cache; its 128-query tiles do
+    not pay for a handful of tokens per item, so steps under 32 tokens per item on average return None (per-row
+    kernel), as do steps whose tokens are not grouped by item."""
+    n_tokens = len(token_item)
+    starts = np.flatnonzero(np.diff(token_item, prepend=-1))
+    if n_tokens == 0 or len(starts) != n_items:
+        return None
+    lens = np.diff(starts, append=n_tokens)
+    first_pos = positions[starts]
+    if not first_pos.any():
+        return ("dense", lens)
+    if n_tokens < 32 * n_items:
+        return None
+    return ("paged", starts, lens, first_pos)
+
+
 class LLMEngine:
     def __init__(self, model, config: Optional[EngineConfig] = None, device=None, comm=None):
         """``model`` is a ``ronn_b200.Model`` (or anything with ``.graph``) holding a decoder architecture."""
@@ -345,19 +365,13 @@ class LLMEngine:
         if self.cfg.backend != "kernels" or self.device.type != "cuda" or not self.cfg.dense_prefill:
             return None
         h = self.host
-        item = h.field("token_item")[:n_tokens]
-        starts = np.flatnonzero(np.diff(item, prepend=-1))
-        if len(starts) != n_items:
+        kind = classify_prefill_step(h.field("token_item")[:n_tokens], h.field("positions")[:n_tokens], n_items)
+        if kind is None:
             return None
-        lens = np.diff(starts, append=n_tokens)
-        first_pos = h.field("positions")[:n_tokens][starts]
         from ..ops import kernels as K
-        if not first_pos.any():
-            return K.dense_attention_plan(lens.tolist(), self.device)
-        # chunk continuations / prefix-cache hits: the same kernel reads K and V from the paged cache.  Its 128-query
-        # tiles do not pay for a handful of tokens per item; those steps stay on the per-row kernel.
-        if n_tokens < 32 * n_items:
-            return None
+        if kind[0] == "dense":
+            return K.dense_attention_plan(kind[1].tolist(), self.device)
+        _, starts, lens, first_pos = kind
         mk = lambda v: torch.tensor(np.asarray(v, dtype=np.int32), device=self.device)
         return {"paged": True, "seq_start": mk(starts), "q_len": mk(lens), "kv_len": mk(first_pos + lens),
                 "max_q_len": int(lens.max()), "n_seq": n_items}

@@ -359,3 +359,23 @@ def test_closed_loop_serving_bench_runs_on_cpu():
     for x in r["results"]:
         assert x["tokens_per_s"] > 0 and x["requests"] == 3 * x["concurrency"]
         assert 0 < x["ttft_ms"]["p50"] <= x["ttft_ms"]["p99"] and 0 < x["itl_ms"]["p50"] <= x["itl_ms"]["p99"]
+
+
+def test_prefill_step_classification():
+    """Whole prompts go to the dense tensor-core kernel, continuations and prefix hits to its paged form when the items
+    are long enough, everything else to the per-row kernel."""
+    import numpy as np
+    from ronn_b200.serving.engine import classify_prefill_step
+    item = np.repeat(np.arange(3), [40, 100, 64]).astype(np.int32)
+    pos0 = np.concatenate([np.arange(40), np.arange(100), np.arange(64)]).astype(np.int32)
+    kind = classify_prefill_step(item, pos0, 3)
+    assert kind[0] == "dense" and kind[1].tolist() == [40, 100, 64]
+    pos1 = pos0.copy()
+    pos1[40:140] += 128                                   # the second item continues at position 128
+    kind = classify_prefill_step(item, pos1, 3)
+    assert kind[0] == "paged" and kind[1].tolist() == [0, 40, 140] and kind[2].tolist() == [40, 100, 64]
+    assert kind[3].tolist() == [0, 128, 0]
+    short = np.repeat(np.arange(4), 8).astype(np.int32)   # 8 tokens per item behind a prefix hit: per-row kernel
+    assert classify_prefill_step(short, np.tile(np.arange(16, 24), 4).astype(np.int32), 4) is None
+    assert classify_prefill_step(item, pos0, 4) is None   # token ranges do not match the item count
+    assert classify_prefill_step(item[:0], pos0[:0], 0) is None
