@@ -472,6 +472,31 @@ def _sdpa(i, a, c):
     return [torch.matmul(torch.softmax(scores, dim=-1), v.float()).to(q.dtype)]
 
 
+@op("PagedAttention", 5, 6, domain="com.ronn")
+def _paged_attention(i, a, c):
+    """Attention of query rows over a paged key / value cache, the serving path's decode operator as a graph node.
+    Inputs: q [rows, num_heads * head_dim]; k_cache and v_cache [blocks, kv_heads, 16, head_dim]; block_tables
+    [*, max_blocks] int32 (cache block of every 16 keys); context_lens [rows] int32 (keys each row attends to, 0 gives
+    a zero row); optional table_rows [rows] int32 (row of block_tables per query row; default its own index).
+    Attributes: num_heads, kv_heads (default num_heads), scale (default 1 / sqrt(head_dim)).  The scale of the
+    kernels is fixed to the default, so another value is applied to q first."""
+    from ..serving.ops_backend import TorchOps
+    q, kc, vc, bt, ctx = i[0], i[1], i[2], i[3], i[4]
+    rows_of = i[5] if len(i) > 5 else None
+    heads = int(a["num_heads"])
+    kv_heads = int(a.get("kv_heads", heads))
+    if kc.dim() != 4 or kc.shape[2] != 16 or kc.shape[1] != kv_heads or heads % kv_heads:
+        raise InvalidGraph("PagedAttention expects caches of shape [blocks, kv_heads, 16, head_dim]")
+    d = kc.shape[3]
+    if q.dim() != 2 or q.shape[1] < heads * d:
+        raise InvalidGraph(f"PagedAttention expects q of shape [rows, {heads * d}], got {list(q.shape)}")
+    scale = float(a.get("scale", 1.0 / math.sqrt(d)))
+    if abs(scale * math.sqrt(d) - 1.0) > 1e-6:
+        q = (q.float() * (scale * math.sqrt(d))).to(q.dtype)
+    max_ctx = bt.shape[1] * 16
+    return [TorchOps().paged_attention(q, kc, vc, bt, ctx.to(torch.int32), heads, kv_heads, d, max_ctx, rows_of)]
+
+
 def attention(q, k, v, num_heads: int, mask=None, causal: bool = False):
     """softmax(QK^T/sqrt(d) + mask) V per head; q,k,v are [B, S, H]."""
     B, Sq, H = q.shape

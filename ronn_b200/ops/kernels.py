@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from .. import _native
+from . import checks as _checks
 from ..api.errors import CommTimeoutError, RonnError
 
 
@@ -235,6 +236,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, positions: Optional[torch.
     ids32 = ids.reshape(-1).to(torch.int32)
     pos32 = positions.reshape(-1).to(torch.int32) if positions is not None else None
     T, H = ids32.numel(), table.shape[1]
+    if _checks.enabled():
+        _run_check(_checks.embedding, ids32, table, pos32, pos_table)
     if out is None:
         out = torch.empty((T, H), dtype=table.dtype, device=table.device)
     _check(_native.cuda().ronn_embedding(ids32.data_ptr(), _ptr(pos32), table.data_ptr(), _ptr(pos_table),
@@ -309,10 +312,19 @@ def kv_append(qkv: torch.Tensor, k_off: int, v_off: int, slots: torch.Tensor, kc
               positions: Optional[torch.Tensor] = None, rope_base: float = 0.0) -> None:
     """Scatter the K/V columns of a fused QKV activation into the paged cache (optionally after rotary)."""
     T = qkv.shape[0]
+    if _checks.enabled():
+        _run_check(_checks.kv_append, qkv, slots, kcache, positions)
     use_rope = 1 if rope_base > 0 and positions is not None else 0
     _check(_native.cuda().ronn_kv_append(qkv.data_ptr(), qkv.stride(0), k_off, v_off, slots.data_ptr(),
                                          _ptr(positions), kcache.data_ptr(), vcache.data_ptr(), T, heads, kv_heads,
                                          head_dim, float(rope_base), use_rope, _DT[qkv.dtype], _stream()), "kv_append")
+
+
+def _run_check(fn, *args) -> None:
+    try:
+        fn(*args)
+    except _checks.IndexCheckError as e:
+        raise KernelError(f"RONN_KERNEL_CHECKS: {e}") from None
 
 
 _ATTN_SPLIT_WS = {}
@@ -358,6 +370,9 @@ def paged_attention(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
     if out is None:
         out = torch.empty((rows, heads * head_dim), dtype=q.dtype, device=q.device)
     sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if _checks.enabled():
+        _run_check(_checks.paged_attention, q, kcache, block_tables, ctx_len, heads, head_dim, int(max_ctx), bt_row,
+                   append[2] if append else None, rope[0] if rope else None)
     if splits is None:
         splits = attention_splits(rows, heads, int(max_ctx))
     part, tickets = attention_split_workspace(q.device, rows * heads, splits, head_dim) if splits > 1 else (None, None)
@@ -426,6 +441,8 @@ def dense_attention(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, plan:
     ql = q_len if q_len is not None else plan["kv_len"]
     mq = int(max_q_len if max_q_len is not None else plan["max_len"])
     sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if _checks.enabled():
+        _run_check(_checks.sequences, tokens, plan["seq_start"], ql, plan["kv_len"], True)
     _check(_native.cuda().ronn_fmha(qkv.data_ptr(), qkv.stride(0), tokens, q_off, k_off, v_off,
                                     plan["seq_start"].data_ptr(), ql.data_ptr(), plan["kv_len"].data_ptr(),
                                     out.data_ptr(), out.stride(0), plan["n_seq"], mq, heads, kv_heads, head_dim,
@@ -447,6 +464,11 @@ def paged_prefill_attention(q: torch.Tensor, q_off: int, kcache: torch.Tensor, v
     if out is None:
         out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=q.device)
     sc = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if _checks.enabled():
+        _run_check(_checks.sequences, tokens, seq_start, q_len, kv_len, False, block_tables.shape[1] * 16)
+        rows_of = bt_row if bt_row is not None else torch.arange(seq_start.numel(), device=q.device, dtype=torch.int32)
+        _run_check(_checks.paged_attention, q[: seq_start.numel()], kcache, block_tables, kv_len, 0, 0,
+                   block_tables.shape[1] * 16, rows_of)
     _check(_native.cuda().ronn_fmha_paged(q.data_ptr(), q.stride(0), tokens, q_off, kcache.data_ptr(), vcache.data_ptr(),
                                           kcache.shape[0], block_tables.data_ptr(), block_tables.stride(0), _ptr(bt_row),
                                           seq_start.data_ptr(), q_len.data_ptr(), kv_len.data_ptr(), out.data_ptr(),

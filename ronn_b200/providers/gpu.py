@@ -58,11 +58,24 @@ class GpuExecutionProvider(ExecutionProvider):
         _native.cuda()                      # fail loudly when the kernel library is missing
         self.kernel_launches = 0
         self.use_cuda_graph = False
+        self._pool = None
 
     def set_session_options(self, opts) -> None:
         if opts.dtype:
             self.config.compute_dtype = opts.dtype
         self.use_cuda_graph = bool(getattr(opts, "use_cuda_graph", False))
+
+    def get_allocator(self):
+        """The provider's device pool (size-keyed reuse, ``memory_limit``, statistics): holds what the provider keeps
+        alive across runs, e.g. the static input buffers of CUDA-graph sessions."""
+        if self._pool is None:
+            from .device_pool import DevicePool
+            self._pool = DevicePool(self.device, self.config.memory_limit)
+        return self._pool
+
+    def shutdown(self) -> None:
+        if self._pool is not None:
+            self._pool.clear_pools()
 
     def has_tensor_cores(self) -> bool:
         return torch.cuda.get_device_capability(self.device)[0] >= 7
@@ -99,7 +112,7 @@ class GpuExecutionProvider(ExecutionProvider):
                 return _inner(feed)
             kernel.execute = execute
         if self.use_cuda_graph:
-            kernel.execute = _GraphedExecute(kernel.execute, self.device)
+            kernel.execute = _GraphedExecute(kernel.execute, self.device, self.get_allocator())
         return kernel
 
 
@@ -107,14 +120,17 @@ class _GraphedExecute:
     """Replays the whole node sequence as one CUDA graph per input signature.  Inputs are copied into static
     buffers; outputs are the graph's static tensors (valid until the next run of the same session)."""
 
-    def __init__(self, inner, device):
-        self.inner, self.device, self.graphs = inner, device, {}
+    def __init__(self, inner, device, pool=None):
+        self.inner, self.device, self.graphs, self.pool = inner, device, {}, pool
 
     def __call__(self, inputs):
         key = tuple((k, tuple(v.shape), v.dtype) for k, v in sorted(inputs.items()))
         entry = self.graphs.get(key)
         if entry is None:
-            static_in = {k: v.clone() for k, v in inputs.items()}
+            if self.pool is not None:               # long-lived staging buffers count against the provider's limit
+                static_in = {k: self.pool.tensor(v.shape, v.dtype).copy_(v) for k, v in inputs.items()}
+            else:
+                static_in = {k: v.clone() for k, v in inputs.items()}
             side = torch.cuda.Stream(self.device)
             side.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(side):

@@ -95,6 +95,8 @@ class GpuOpTable:
             return self._attention(node, fallback)
         if op == "ScaledDotProductAttention":
             return self._sdpa(node, fallback)
+        if op == "PagedAttention":
+            return self._paged_attention(node, fallback)
         if op in ("Conv", "FusedConv") and node.attr("data_format") == "NHWC":
             from .gpu_conv import conv_resolver
             return conv_resolver(self, node, fallback)
@@ -287,6 +289,29 @@ class GpuOpTable:
                 plan = dict(plan, kv_len=kv_len)
             out = K.dense_attention(buf, q_off, k_off, v_off, plan, heads, heads, d, causal, plan["q_len"], S)
             return [out.view(B, S, H)]
+        return run
+
+    def _paged_attention(self, node, fallback):
+        """``com.ronn::PagedAttention`` on the decode attention kernel (16-bit q and caches, head size 64 or 128,
+        default scale, context within the kernel's limit); anything else takes the operator's library form."""
+        K = self.K
+        heads = int(node.attr("num_heads", 0))
+        kv_heads = int(node.attr("kv_heads", heads))
+        scale = node.attr("scale", None)
+
+        def run(i, a, c):
+            q, kc, vc, bt, ctx = i[0], i[1], i[2], i[3], i[4]
+            d = kc.shape[3] if kc.dim() == 4 else 0
+            ok = (q.is_cuda and q.dtype in _HALF and kc.dtype == q.dtype and vc.dtype == q.dtype and d in (64, 128)
+                  and q.dim() == 2 and q.stride(1) == 1 and q.stride(0) % 8 == 0 and kc.is_contiguous()
+                  and vc.is_contiguous() and bt.dtype == torch.int32 and bt.is_contiguous() and ctx.dtype == torch.int32
+                  and bt.shape[1] * 16 <= 4096 and heads > 0 and heads % max(kv_heads, 1) == 0
+                  and (scale is None or abs(float(scale) * math.sqrt(d) - 1.0) < 1e-6)
+                  and (len(i) < 6 or i[5].dtype == torch.int32))
+            if not ok:
+                return fallback(i, a, c)
+            return [K.paged_attention(q, kc, vc, bt, ctx.contiguous(), heads, kv_heads, d, bt.shape[1] * 16,
+                                      i[5].contiguous() if len(i) > 5 else None)]
         return run
 
     def _sdpa(self, node, fallback):

@@ -694,3 +694,32 @@ def test_device_sampler_distribution_top_k_top_p_and_penalty(K):
     ctr.zero_()
     c = K.sample(logits.clone(), params, None, ctr)
     assert torch.equal(a, c) and not torch.equal(a, b)
+
+
+def test_kernel_checks_refuse_a_bad_block_table_before_the_launch(K, monkeypatch):
+    """With RONN_KERNEL_CHECKS=1 a block-table entry past the cache raises on the host and nothing is launched; the
+    same call with valid indices runs as usual."""
+    from ronn_b200 import _native
+    monkeypatch.setenv("RONN_KERNEL_CHECKS", "1")
+    kc = torch.zeros(8, 2, 16, 64, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = _rand(2, 4 * 64)
+    bt = torch.tensor([[0, 1], [2, 3]], device="cuda", dtype=torch.int32)
+    ctx = torch.tensor([20, 32], device="cuda", dtype=torch.int32)
+    out = K.paged_attention(q, kc, vc, bt, ctx, 4, 2, 64, max_ctx=32)
+    assert out.shape == (2, 256)
+    lib = _native.cuda()
+    calls = {"n": 0}
+    real = lib.ronn_paged_attention
+    lib.__dict__["ronn_paged_attention"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
+    try:
+        bad = bt.clone()
+        bad[1, 1] = 8
+        with pytest.raises(K.KernelError, match="block_tables"):
+            K.paged_attention(q, kc, vc, bad, ctx, 4, 2, 64, max_ctx=32)
+        with pytest.raises(K.KernelError, match="slots"):
+            K.kv_append(_rand(2, 8 * 64), 4 * 64, 6 * 64, torch.tensor([0, 128], device="cuda", dtype=torch.int32), kc, vc, 4, 2, 64)
+    finally:
+        lib.__dict__["ronn_paged_attention"] = real
+    assert calls["n"] == 0
+    K.check_status()

@@ -251,3 +251,66 @@ def test_attention_core_written_in_primitives_runs_the_tensor_core_kernel():
             lib.__dict__["ronn_fmha"] = real
         assert calls["n"] == (0 if masked else 1)
         torch.testing.assert_close(got, want, atol=4e-2, rtol=4e-2)
+
+
+def test_paged_attention_node_runs_the_decode_kernel():
+    """com.ronn::PagedAttention through a GPU session: the node takes the decode attention kernel (counted) and agrees
+    with the operator's CPU definition."""
+    import math
+    from ronn_b200 import Model, SessionOptions, _native
+    from ronn_b200.core.types import DataType
+    from ronn_b200.graph.ir import GraphBuilder
+    heads, kv_heads, d, rows, max_blocks, nblocks = 8, 4, 64, 6, 5, 40
+    g = torch.Generator().manual_seed(3)
+    kc = (torch.randn(nblocks, kv_heads, 16, d, generator=g) * 0.5).bfloat16()
+    vc = (torch.randn(nblocks, kv_heads, 16, d, generator=g) * 0.5).bfloat16()
+    bt = torch.randperm(nblocks, generator=g)[: rows * max_blocks].reshape(rows, max_blocks).to(torch.int32)
+    ctx = torch.tensor([1, 16, 17, 80, 0, 45], dtype=torch.int32)
+    q = torch.randn(rows, heads * d, generator=g).bfloat16()
+    b = GraphBuilder()
+    b.add_input("q", [rows, heads * d], DataType.BF16).add_input("kc", list(kc.shape), DataType.BF16)
+    b.add_input("vc", list(vc.shape), DataType.BF16).add_input("bt", list(bt.shape), DataType.I32)
+    b.add_input("ctx", [rows], DataType.I32).add_output("y", [rows, heads * d], DataType.BF16)
+    b.add_op("PagedAttention", ["q", "kc", "vc", "bt", "ctx"], ["y"], domain="com.ronn", num_heads=heads, kv_heads=kv_heads)
+    model = Model.from_graph(b.build())
+    feeds = {"q": q, "kc": kc, "vc": vc, "bt": bt, "ctx": ctx}
+    want = model.create_session(SessionOptions().with_optimization_level("O0")).run(feeds)["y"].float()
+    sess = model.create_session(SessionOptions().with_provider("gpu").with_optimization_level("O3"))
+    lib = _native.cuda()
+    calls = {"n": 0}
+    real = lib.ronn_paged_attention
+    lib.__dict__["ronn_paged_attention"] = lambda *a: (calls.__setitem__("n", calls["n"] + 1), real(*a))[1]
+    try:
+        got = sess.run(feeds)["y"].float().cpu()
+    finally:
+        lib.__dict__["ronn_paged_attention"] = real
+    assert calls["n"] == 1
+    torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+    assert float(got[4].abs().max()) == 0.0
+
+
+def test_graph_session_inputs_live_in_the_provider_device_pool():
+    """A CUDA-graph session stages its inputs in buffers from the provider's device pool, which counts them against
+    ``memory_limit`` and reports them in its statistics."""
+    from ronn_b200 import Model, SessionOptions
+    from ronn_b200.graph.ir import GraphBuilder
+    from ronn_b200.providers.gpu import GpuExecutionProvider, GpuProviderConfig
+    prov = GpuExecutionProvider(GpuProviderConfig(memory_limit=1 << 20))
+    b = GraphBuilder().add_input("x", [32, 128]).add_output("y", [32, 128])
+    b.add_op("Relu", ["x"], ["y"])
+    sess = Model.from_graph(b.build()).create_session(
+        SessionOptions().with_provider(prov).with_optimization_level("O1").with_cuda_graph(True))
+    x = torch.randn(32, 128)
+    for _ in range(3):
+        y = sess.run({"x": x})["y"]
+    torch.testing.assert_close(y.float().cpu(), torch.relu(x))
+    pool = prov.get_allocator()
+    st = pool.stats()
+    assert st.live_buffers == 1 and st.allocated_bytes == 32 * 128 * 4          # one staging buffer, made once
+    t = pool.tensor((256, 256), torch.float32)                                  # 256 KB more
+    assert t.is_cuda and pool.get_memory_info().total_bytes == 1 << 20
+    with pytest.raises(Exception, match="limit"):
+        pool.tensor((1024, 1024), torch.float32)
+    pool.release(t)
+    prov.shutdown()
+    assert pool.stats().pooled_buffers == 0

@@ -384,3 +384,40 @@ def test_math_constants_are_exact_where_they_must_be():
     check(run_node("Sin", [("x", x)]), torch.sin(x))
     check(run_node("Exp", [("x", torch.tensor([0.0]))]), torch.tensor([1.0]), atol=0, rtol=0)
     check(run_node("Relu", [("x", torch.tensor([-0.0, 0.0, 3.0]))]), torch.tensor([0.0, 0.0, 3.0]), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("heads,kv_heads,d", [(4, 4, 8), (4, 2, 16)])
+@pytest.mark.parametrize("level", ["O0", "O3"])
+def test_paged_attention_operator(heads, kv_heads, d, level):
+    """com.ronn::PagedAttention: every query row attends to the first context_lens[row] keys of the cache blocks its
+    table row lists; an empty context gives a zero row, table_rows lets rows share a table row, a custom scale is
+    honoured."""
+    lens = [5, 16, 0, 33]
+    rows, max_blocks = len(lens), 3
+    nblocks = 7
+    kc, vc = rnd(nblocks, kv_heads, 16, d), rnd(nblocks, kv_heads, 16, d)
+    bt = torch.tensor([[1, 0, 0], [2, 0, 0], [0, 0, 0], [3, 4, 5]], dtype=torch.int32)
+    q = rnd(rows, heads * d)
+    ctx = torch.tensor(lens, dtype=torch.int32)
+
+    def want(q, rows_of, scale):
+        out = torch.zeros(q.shape[0], heads * d)
+        for r in range(q.shape[0]):
+            n = int(ctx[r])
+            if n == 0:
+                continue
+            tb = bt[rows_of[r]]
+            k = torch.stack([kc[int(tb[t // 16]), :, t % 16] for t in range(n)])      # [n, kv, d]
+            v = torch.stack([vc[int(tb[t // 16]), :, t % 16] for t in range(n)])
+            k, v = k.repeat_interleave(heads // kv_heads, 1), v.repeat_interleave(heads // kv_heads, 1)
+            s = torch.einsum("hd,nhd->hn", q[r].view(heads, d), k) * scale
+            out[r] = torch.einsum("hn,nhd->hd", torch.softmax(s, -1), v).reshape(-1)
+        return out
+    ins = [("q", q), ("kc", kc), ("vc", vc), ("bt", bt), ("ctx", ctx)]
+    got = run_node("PagedAttention", ins, {"num_heads": heads, "kv_heads": kv_heads}, domain="com.ronn", level=level)[0]
+    torch.testing.assert_close(got, want(q, list(range(rows)), 1 / math.sqrt(d)), atol=1e-5, rtol=1e-4)
+    assert float(got[2].abs().max()) == 0.0
+    shared = torch.tensor([3, 3, 3, 3], dtype=torch.int32)
+    got = run_node("PagedAttention", ins + [("rows_of", shared)], {"num_heads": heads, "kv_heads": kv_heads, "scale": 0.5},
+                   domain="com.ronn", level=level)[0]
+    torch.testing.assert_close(got, want(q, [3, 3, 3, 3], 0.5), atol=1e-5, rtol=1e-4)
