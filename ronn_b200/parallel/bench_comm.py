@@ -14,6 +14,9 @@ bytes of a minimal all-reduce, 2 (W - 1) / W x result, which is what the two-sho
 For the low-latency and two-shot protocols it also prints where the time of one call goes: %globaltimer stamps taken inside the kernel
 (entry, GEMM stored, counters raised, all ranks' tiles seen, rows reduced and stored, "delivered" raised, all
 deliveries seen), median over the CTAs of a rank, then the max over ranks.
+
+``--sequence-parallel`` times only the two kernels of the token-sharded layout (gather inside the column-parallel GEMM,
+reduce-scatter inside the row-parallel GEMM) at prefill size; ``--all`` adds them to the list above.
 """
 from __future__ import annotations
 
@@ -54,6 +57,51 @@ def _time_graph(fn, reps=20, iters=5):
     return ts[len(ts) // 2]
 
 
+def sequence_parallel_rows(comm, lib, dev, world, tf):
+    """The two fused kernels of the token-sharded layout at GPT-2-medium prefill size (8192 tokens): the gather inside
+    the column-parallel GEMM (``ag_gemm``) and the reduce-scatter inside the row-parallel GEMM, against all-gather /
+    reduce-scatter calls around the same tcgen05 GEMM.  The shard buffer is single-buffered, so a gather is timed
+    together with the reduce-scatter that has to follow it; the gather's own time is the difference."""
+    T, H = 8192, 1024
+    per = T // world
+    x_local = torch.randn(per, H, device=dev).bfloat16()
+    w_col = (torch.randn(3 * H // world, H, device=dev) * 0.05).bfloat16()            # QKV, column shard
+    att = torch.randn(T, H // world, device=dev).bfloat16()
+    w_row = (torch.randn(H, H // world, device=dev) * 0.05).bfloat16()                # out-projection, row shard
+    bias = torch.zeros(H, device=dev, dtype=torch.bfloat16)
+    res = torch.randn(per, H, device=dev).bfloat16()
+    shard = comm.shard_buffer(per, H)
+
+    def fused_rs():
+        comm.gemm_reduce_scatter(att, w_row, bias, res)
+
+    def fused_pair():
+        shard.copy_(x_local)
+        comm.signal_shard_ready()
+        comm.ag_gemm(per, H, w_col)
+        comm.gemm_reduce_scatter(att, w_row, bias, res)
+
+    def lib_rs():
+        lib.reduce_scatter_rows(K.gemm(att, w_row)) + bias + res
+
+    def lib_pair():
+        K.gemm(lib.all_gather_rows(x_local), w_col)
+        lib.reduce_scatter_rows(K.gemm(att, w_row)) + bias + res
+
+    t = {k: lib.max_over_ranks(_time_graph(f, reps=10)) for k, f in
+         (("fused_rs", fused_rs), ("fused_pair", fused_pair), ("lib_rs", lib_rs), ("lib_pair", lib_pair))}
+    link = (world - 1) / world * T * H * 2.0 / 770e9 * 1e6                              # one shard set over NVLink, 16-bit
+    roof_ag = max(2.0 * T * (3 * H // world) * H / (tf * 1e12) * 1e6, link)
+    roof_rs = max(2.0 * T * H * (H // world) / (tf * 1e12) * 1e6, link)
+    ag_f, ag_l = t["fused_pair"] - t["fused_rs"], t["lib_pair"] - t["lib_rs"]
+    return [{"op": "ag_gemm (QKV, token-sharded input)", "tokens": T, "N_local": 3 * H // world, "K": H, "world": world,
+             "fused_us": round(ag_f, 2), "library_us": round(ag_l, 2), "roofline_us": round(roof_ag, 2),
+             "fused_frac_of_roofline": round(roof_ag / max(ag_f, 1e-3), 3)},
+            {"op": "gemm + reduce-scatter (attention output)", "tokens": T, "N": H, "K_local": H // world, "world": world,
+             "fused_us": round(t["fused_rs"], 2), "library_us": round(t["lib_rs"], 2), "roofline_us": round(roof_rs, 2),
+             "fused_frac_of_roofline": round(roof_rs / t["fused_rs"], 3)}]
+
+
 def main():
     rank, world, local = init_distributed("nccl", timeout_s=120)
     dev = torch.device("cuda", local)
@@ -65,7 +113,10 @@ def main():
     except Exception:
         tf = 1590.0
     out = []
-    for (M, N, Kfull, name) in [(256, 1024, 1024, "attn-out"), (256, 1024, 4096, "mlp-down"), (8192, 1024, 1024, "attn-out prefill"),
+    only_sp = "--sequence-parallel" in sys.argv
+    if only_sp or "--all" in sys.argv:
+        out += sequence_parallel_rows(comm, lib, dev, world, tf)
+    for (M, N, Kfull, name) in [] if only_sp else [(256, 1024, 1024, "attn-out"), (256, 1024, 4096, "mlp-down"), (8192, 1024, 1024, "attn-out prefill"),
                                 (8192, 1024, 4096, "mlp-down prefill")]:
         Kl = Kfull // world
         a = torch.randn(M, Kl, device=dev).bfloat16()
