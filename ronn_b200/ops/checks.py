@@ -22,7 +22,14 @@ class IndexCheckError(ValueError):
 
 
 def enabled() -> bool:
-    return os.environ.get("RONN_KERNEL_CHECKS", "0") == "1"
+    """On when the switch is set, except while the current stream is being captured into a CUDA graph: the checks
+    read device tensors on the host, which a capture does not allow (check the eager warm-up run instead)."""
+    if os.environ.get("RONN_KERNEL_CHECKS", "0") != "1":
+        return False
+    try:
+        return not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing())
+    except Exception:
+        return True
 
 
 def _first_bad(t: torch.Tensor, bad: torch.Tensor):
