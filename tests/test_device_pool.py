@@ -106,3 +106,36 @@ def test_concurrent_use_keeps_the_books_straight():
     st = pool.stats()
     assert not errors and st.live_buffers == 0 and st.allocated_bytes == 0
     assert st.allocation_count == st.deallocation_count == 1600 and st.hits + st.misses == 1600
+
+
+def test_random_sequences_keep_the_invariants():
+    """Property test: under any interleaving of acquire / release the books balance, the limit holds, blocks handed out
+    never alias, and a pooled block is reused only within the size factor."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=60, deadline=None)
+    @given(st.lists(st.tuples(st.booleans(), st.integers(min_value=1, max_value=20000)), min_size=1, max_size=60))
+    def run(ops):
+        limit = 64 * 1024
+        pool = DevicePool("cpu", limit_bytes=limit, max_pool_bytes=16 * 1024)
+        live = []
+        for is_alloc, n in ops:
+            if is_alloc or not live:
+                try:
+                    blk = pool.acquire(n)
+                except ProviderError:
+                    assert sum(b.numel() for b in live) + pool._round(n) > limit      # refused only when it cannot fit
+                    continue
+                assert blk.numel() >= n and blk.numel() <= 2 * pool._round(n)
+                assert all(blk.data_ptr() != b.data_ptr() for b in live)
+                live.append(blk)
+            else:
+                pool.release(live.pop(n % len(live)))
+            s = pool.stats()
+            assert s.live_buffers == len(live) and s.allocated_bytes == sum(b.numel() for b in live)
+            assert s.allocated_bytes + s.pooled_bytes <= limit and s.pooled_bytes <= 16 * 1024
+            assert s.peak_bytes >= s.allocated_bytes
+        for b in live:
+            pool.release(b)
+        assert pool.stats().allocated_bytes == 0
+    run()
