@@ -47,6 +47,8 @@ sys.path.insert(0, ROOT)
 
 
 def reference_arm():
+    if os.environ.get("RANK", "0") != "0":          # launched once per GPU for N > 1: one line, from rank 0
+        return 0
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a Rust/Cargo workspace (no setup.py/pyproject at its root, no cargo/"
                                      "rustc/maturin in the image, 12 workspace members missing, gpu feature does not "
